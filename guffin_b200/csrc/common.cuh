@@ -85,6 +85,35 @@ __device__ __forceinline__ float warp_sum(float v) {
     for (int offset = 16; offset > 0; offset >>= 1) v += __shfl_xor_sync(0xffffffffu, v, offset);
     return v;
 }
+// Butterfly reduction of eight per-lane column sums: afterwards lane (4*c') with
+// c' = bit-reversed column holds the warp total of that column; returns it for lanes
+// whose low two bits are zero.  column_of_lane() gives the column such a lane holds.
+__device__ __forceinline__ float reduce_columns8(float (&acc)[8], uint32_t lane) {
+    float v4[4], v2[2];
+    const bool b16 = lane & 16u, b8 = lane & 8u, b4 = lane & 4u;
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+        const float keep = b16 ? acc[i + 4] : acc[i];
+        const float send = b16 ? acc[i] : acc[i + 4];
+        v4[i] = keep + __shfl_xor_sync(0xffffffffu, send, 16);
+    }
+#pragma unroll
+    for (int i = 0; i < 2; ++i) {
+        const float keep = b8 ? v4[i + 2] : v4[i];
+        const float send = b8 ? v4[i] : v4[i + 2];
+        v2[i] = keep + __shfl_xor_sync(0xffffffffu, send, 8);
+    }
+    const float keep = b4 ? v2[1] : v2[0];
+    const float send = b4 ? v2[0] : v2[1];
+    float v = keep + __shfl_xor_sync(0xffffffffu, send, 4);
+    v += __shfl_xor_sync(0xffffffffu, v, 2);
+    v += __shfl_xor_sync(0xffffffffu, v, 1);
+    return v;
+}
+__device__ __forceinline__ uint32_t column_of_lane(uint32_t lane) {
+    return ((lane & 16u) ? 4u : 0u) | ((lane & 8u) ? 2u : 0u) | ((lane & 4u) ? 1u : 0u);
+}
+
 #endif
 
 }  // namespace gf

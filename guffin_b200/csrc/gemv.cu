@@ -143,6 +143,9 @@ size_t gf_matmul_workspace_bytes(int dtype, uint32_t rows, uint64_t k, uint64_t 
 
 int gf_matmul(int dtype, const void* packed_dev, const float* x_dev, float* y_dev, uint32_t rows, uint64_t k,
               uint64_t n, void* workspace_dev, void* stream) {
+    GemvPlan plan;
+    const int status = gemv_plan(dtype, rows, k, n, plan);   // argument errors come before any GPU work
+    if (status != GF_OK) return status;
     int* flag = device_error_flag();
     if (!flag) return fail(GF_ERR_CUDA, "gf_matmul: cannot allocate the device error word");
     return gemv_launch(dtype, packed_dev, x_dev, y_dev, rows, k, n, workspace_dev, flag, as_stream(stream), false);

@@ -1,0 +1,463 @@
+// Resident model plan and block schedule (see model.cuh).
+#include "model.cuh"
+#include "gemv.cuh"
+
+#include <algorithm>
+#include <cmath>
+#include <cstring>
+
+namespace gf {
+
+size_t candidates_workspace_bytes(uint32_t rows, uint32_t vocab);
+int launch_candidates(const float* logits, uint32_t rows, uint32_t vocab, float softcap, const void* requests,
+                      void* workspace, void* results, cudaStream_t stream, bool pdl);
+
+static __global__ void advance_position_kernel(uint32_t* state, uint32_t delta) {
+    pdl_wait();
+    if (threadIdx.x == 0) state[0] += delta;
+}
+
+static uint32_t next_pow2(uint32_t v) {
+    uint32_t p = 1;
+    while (p < v) p <<= 1;
+    return p;
+}
+
+Model::Model(const gf_model_config& config) : config_(config) {
+    layers_.resize(config.layers);
+    caches_.resize(config.layers);
+}
+
+Model::~Model() {
+    for (auto& per_rows : graphs_)
+        for (auto& graph : per_rows)
+            if (graph) cudaGraphExecDestroy(graph);
+    for (void* p : allocations_) cudaFree(p);
+    if (tokens_pinned_) cudaFreeHost(tokens_pinned_);
+    if (requests_pinned_) cudaFreeHost(requests_pinned_);
+    if (stream_) cudaStreamDestroy(stream_);
+}
+
+bool Model::layer_is_local(uint32_t layer) const {
+    if (config_.sliding_pattern == 6u) return (layer + 1u) % 6u != 0u;      // model.cpp:607-619 (Gemma 3)
+    if (config_.sliding_pattern == 2u) return layer % 2u == 0u;              // Gemma 2: even layers slide
+    return false;
+}
+
+#define GF_TRY(expr) do { const int gf_s_ = (expr); if (gf_s_ != GF_OK) return gf_s_; } while (0)
+
+template <typename T>
+static int device_alloc(std::vector<void*>& owner, T** out, size_t count) {
+    void* p = nullptr;
+    GF_CUDA(cudaMalloc(&p, std::max<size_t>(count * sizeof(T), 16)));
+    owner.push_back(p);
+    *out = static_cast<T*>(p);
+    return GF_OK;
+}
+
+int Model::set_matrix(int kind, uint32_t layer, int dtype, const void* native_host, uint64_t k, uint64_t n) {
+    if (finalized_) return fail(GF_ERR_STATE, "gf_model_set_matrix: the plan is already finalized");
+    if (!native_host) return fail(GF_ERR_INVALID, "gf_model_set_matrix: null payload");
+    const gf_model_config& c = config_;
+    const uint64_t qw = (uint64_t)c.heads * c.head_dim, kvw = (uint64_t)c.kv_heads * c.head_dim;
+    uint64_t want_k = 0, want_n = 0;
+    PackedMatrix* dst = nullptr;
+    if (kind >= GF_MAT_ATTN_Q && layer >= c.layers) return fail(GF_ERR_INVALID, "gf_model_set_matrix: layer %u out of range", layer);
+    switch (kind) {
+        case GF_MAT_TOKEN_EMBD: dst = &token_embd_; want_k = c.hidden; want_n = c.vocab; break;
+        case GF_MAT_OUTPUT: dst = &head_; want_k = c.hidden; want_n = c.vocab; break;
+        case GF_MAT_ATTN_Q: dst = &layers_[layer].q; want_k = c.hidden; want_n = qw; break;
+        case GF_MAT_ATTN_K: dst = &layers_[layer].k; want_k = c.hidden; want_n = kvw; break;
+        case GF_MAT_ATTN_V: dst = &layers_[layer].v; want_k = c.hidden; want_n = kvw; break;
+        case GF_MAT_ATTN_OUTPUT: dst = &layers_[layer].o; want_k = qw; want_n = c.hidden; break;
+        case GF_MAT_FFN_GATE: dst = &layers_[layer].gate; want_k = c.hidden; want_n = c.ffn; break;
+        case GF_MAT_FFN_UP: dst = &layers_[layer].up; want_k = c.hidden; want_n = c.ffn; break;
+        case GF_MAT_FFN_DOWN: dst = &layers_[layer].down; want_k = c.ffn; want_n = c.hidden; break;
+        default: return fail(GF_ERR_INVALID, "gf_model_set_matrix: unknown tensor kind %d", kind);
+    }
+    if (k != want_k || n != want_n)
+        return fail(GF_ERR_INVALID, "gf_model_set_matrix: kind %d expects [%llu, %llu], got [%llu, %llu]", kind,
+                    (unsigned long long)want_k, (unsigned long long)want_n, (unsigned long long)k, (unsigned long long)n);
+    if (dst->data) return fail(GF_ERR_STATE, "gf_model_set_matrix: tensor kind %d layer %u bound twice", kind, layer);
+    const size_t packed = gf_packed_weight_bytes(dtype, k, n);
+    if (packed == 0) return GF_ERR_INVALID;
+    const size_t native = (size_t)n * (k / block_elements(dtype)) * block_bytes(dtype);
+    if (!stream_) GF_CUDA(cudaStreamCreateWithFlags(&stream_, cudaStreamNonBlocking));
+    uint8_t* staging = nullptr;
+    GF_CUDA(cudaMalloc(&staging, native));
+    uint8_t* data = nullptr;
+    int status = device_alloc(allocations_, &data, packed);
+    if (status == GF_OK) status = check_cuda(cudaMemcpyAsync(staging, native_host, native, cudaMemcpyHostToDevice, stream_), "upload");
+    if (status == GF_OK) status = gf_pack_weight(dtype, staging, k, n, data, stream_);
+    if (status == GF_OK) status = check_cuda(cudaStreamSynchronize(stream_), "pack");
+    cudaFree(staging);
+    if (status != GF_OK) return status;
+    *dst = PackedMatrix{dtype, k, n, data, packed, native};
+    weight_bytes_ += packed;
+    native_weight_bytes_ += native;
+    if (kind == GF_MAT_OUTPUT) has_head_ = true;
+    return GF_OK;
+}
+
+int Model::set_vector(int kind, uint32_t layer, const float* host, uint32_t count) {
+    if (finalized_) return fail(GF_ERR_STATE, "gf_model_set_vector: the plan is already finalized");
+    if (!host) return fail(GF_ERR_INVALID, "gf_model_set_vector: null payload");
+    if (kind != GF_VEC_OUTPUT_NORM && layer >= config_.layers) return fail(GF_ERR_INVALID, "gf_model_set_vector: layer out of range");
+    float** dst = nullptr;
+    uint32_t want = config_.hidden;
+    switch (kind) {
+        case GF_VEC_OUTPUT_NORM: dst = &output_norm_; break;
+        case GF_VEC_ATTN_NORM: dst = &layers_[layer].attn_norm; break;
+        case GF_VEC_POST_ATTENTION_NORM: dst = &layers_[layer].post_attention_norm; break;
+        case GF_VEC_FFN_NORM: dst = &layers_[layer].ffn_norm; break;
+        case GF_VEC_POST_FFW_NORM: dst = &layers_[layer].post_ffw_norm; break;
+        case GF_VEC_ATTN_Q_NORM: dst = &layers_[layer].q_norm; want = config_.head_dim; break;
+        case GF_VEC_ATTN_K_NORM: dst = &layers_[layer].k_norm; want = config_.head_dim; break;
+        default: return fail(GF_ERR_INVALID, "gf_model_set_vector: unknown vector kind %d", kind);
+    }
+    if (count != want) return fail(GF_ERR_INVALID, "gf_model_set_vector: kind %d expects %u values, got %u", kind, want, count);
+    if (*dst) return fail(GF_ERR_STATE, "gf_model_set_vector: vector bound twice");
+    GF_TRY(device_alloc(allocations_, dst, count));
+    GF_CUDA(cudaMemcpy(*dst, host, (size_t)count * 4, cudaMemcpyHostToDevice));
+    native_weight_bytes_ += (size_t)count * 4;
+    return GF_OK;
+}
+
+int Model::finalize() {
+    if (finalized_) return fail(GF_ERR_STATE, "gf_model_finalize: already finalized");
+    const gf_model_config& c = config_;
+    if (c.row_capacity == 0 || c.row_capacity > GF_MAX_ROWS) return fail(GF_ERR_INVALID, "row_capacity must be 1..%d", GF_MAX_ROWS);
+    if (c.head_dim != 256u) return fail(GF_ERR_INVALID, "head_dim must be 256 (the reference's kernels share this limit)");
+    if (c.context == 0 || c.heads % c.kv_heads) return fail(GF_ERR_INVALID, "bad context or head geometry");
+    if (!token_embd_.data || !output_norm_) return fail(GF_ERR_STATE, "token embedding or output norm missing");
+    for (uint32_t l = 0; l < c.layers; ++l) {
+        const LayerWeights& w = layers_[l];
+        if (!w.q.data || !w.k.data || !w.v.data || !w.o.data || !w.gate.data || !w.up.data || !w.down.data || !w.attn_norm
+            || !w.post_attention_norm || !w.ffn_norm || !w.post_ffw_norm || (c.uses_qk_norm && (!w.q_norm || !w.k_norm)))
+            return fail(GF_ERR_STATE, "layer %u has unbound tensors", l);
+    }
+    if (!stream_) GF_CUDA(cudaStreamCreateWithFlags(&stream_, cudaStreamNonBlocking));
+    const uint32_t R = c.row_capacity, kvw = c.kv_heads * c.head_dim, qw = c.heads * c.head_dim;
+    const size_t element = c.kv_f16 ? 2 : 4;
+    for (uint32_t l = 0; l < c.layers; ++l) {
+        LayerCache& cache = caches_[l];
+        const bool local = layer_is_local(l);
+        cache.window = local ? c.sliding_window : 0u;
+        // A local ring keeps its window plus the rows a pass may publish, so the rows of an
+        // unpublished pass never alias keys still inside a live window.
+        cache.ring_rows = next_pow2(local ? std::min(c.context, c.sliding_window + R) : c.context);
+        cache.rope_base = local ? c.rope_base_local : c.rope_base_global;
+        cache.rope_scale = local ? c.rope_scale_local : c.rope_scale_global;
+        uint8_t *rk, *rv, *pk, *pv;
+        GF_TRY(device_alloc(allocations_, &rk, (size_t)cache.ring_rows * kvw * element));
+        GF_TRY(device_alloc(allocations_, &rv, (size_t)cache.ring_rows * kvw * element));
+        GF_TRY(device_alloc(allocations_, &pk, (size_t)R * kvw * element));
+        GF_TRY(device_alloc(allocations_, &pv, (size_t)R * kvw * element));
+        cache.ring_k = rk; cache.ring_v = rv; cache.private_k = pk; cache.private_v = pv;
+        GF_CUDA(cudaMemsetAsync(rk, 0, (size_t)cache.ring_rows * kvw * element, stream_));
+        GF_CUDA(cudaMemsetAsync(rv, 0, (size_t)cache.ring_rows * kvw * element, stream_));
+    }
+    GF_TRY(device_alloc(allocations_, &residual_, (size_t)R * c.hidden));
+    GF_TRY(device_alloc(allocations_, &normalized_, (size_t)R * c.hidden));
+    GF_TRY(device_alloc(allocations_, &raw_q_, (size_t)R * qw));
+    GF_TRY(device_alloc(allocations_, &raw_k_, (size_t)R * kvw));
+    GF_TRY(device_alloc(allocations_, &raw_v_, (size_t)R * kvw));
+    GF_TRY(device_alloc(allocations_, &query_, (size_t)R * qw));
+    GF_TRY(device_alloc(allocations_, &attention_out_, (size_t)R * qw));
+    GF_TRY(device_alloc(allocations_, &projected_, (size_t)R * c.hidden));
+    GF_TRY(device_alloc(allocations_, &post_attention_, (size_t)R * c.hidden));
+    GF_TRY(device_alloc(allocations_, &gate_, (size_t)R * c.ffn));
+    GF_TRY(device_alloc(allocations_, &up_, (size_t)R * c.ffn));
+    GF_TRY(device_alloc(allocations_, &gated_, (size_t)R * c.ffn));
+    GF_TRY(device_alloc(allocations_, &logits_, (size_t)R * c.vocab));
+    size_t ws = 16;
+    auto grow = [&](const PackedMatrix& m) { ws = std::max(ws, gf_matmul_workspace_bytes(m.dtype, R, m.k, m.n)); };
+    for (const LayerWeights& w : layers_) { grow(w.q); grow(w.k); grow(w.v); grow(w.o); grow(w.gate); grow(w.up); grow(w.down); }
+    grow(has_head_ ? head_ : token_embd_);
+    uint8_t* bytes = nullptr;
+    GF_TRY(device_alloc(allocations_, &bytes, ws)); matmul_ws_ = bytes;
+    GF_TRY(device_alloc(allocations_, &bytes, gf_attention_workspace_bytes(R, c.heads))); attention_ws_ = bytes;
+    GF_TRY(device_alloc(allocations_, &bytes, candidates_workspace_bytes(R, c.vocab))); candidates_ws_ = bytes;
+    GF_TRY(device_alloc(allocations_, &bytes, (size_t)R * gf_selection_request_bytes())); requests_dev_ = bytes;
+    GF_TRY(device_alloc(allocations_, &bytes, (size_t)R * gf_candidate_result_bytes())); results_dev_ = bytes;
+    GF_TRY(device_alloc(allocations_, &tokens_dev_, GF_MAX_ROWS));
+    GF_TRY(device_alloc(allocations_, &state_dev_, 8));
+    GF_TRY(device_alloc(allocations_, &status_dev_, 4));
+    GF_TRY(device_alloc(allocations_, &error_flag_, 4));
+    GF_CUDA(cudaMemsetAsync(state_dev_, 0, 32, stream_));
+    GF_CUDA(cudaMemsetAsync(status_dev_, 0, 16, stream_));
+    GF_CUDA(cudaMemsetAsync(error_flag_, 0, 16, stream_));
+    GF_CUDA(cudaHostAlloc(reinterpret_cast<void**>(&tokens_pinned_), GF_MAX_ROWS * sizeof(uint32_t), cudaHostAllocDefault));
+    GF_CUDA(cudaHostAlloc(&requests_pinned_, (size_t)R * gf_selection_request_bytes(), cudaHostAllocDefault));
+    GF_CUDA(cudaStreamSynchronize(stream_));
+    finalized_ = true;
+    position_ = 0;
+    return GF_OK;
+}
+
+int Model::reset() {
+    if (!finalized_) return fail(GF_ERR_STATE, "plan is not finalized");
+    GF_CUDA(cudaMemsetAsync(state_dev_, 0, 32, stream_));
+    GF_CUDA(cudaMemsetAsync(status_dev_, 0, 16, stream_));
+    position_ = 0;
+    poisoned_ = false;
+    return GF_OK;
+}
+
+int Model::matmul(const PackedMatrix& w, const float* x, float* y, uint32_t rows) {
+    ++launches_;
+    return gemv_launch(w.dtype, w.data, x, y, rows, w.k, w.n, matmul_ws_, error_flag_, stream_, true);
+}
+
+// One transformer pass: the operator order of encode_gemma_target_blocks
+// (gemma_target_runtime.cpp:28-219).
+int Model::encode_blocks(uint32_t rows, uint32_t flags) {
+    const gf_model_config& c = config_;
+    const float embedding_scale = sqrtf((float)c.hidden);     // f32, not bf16-rounded (model.cpp:599-605)
+    GF_TRY(launch_embedding(token_embd_.dtype, token_embd_.data, c.hidden, c.vocab, tokens_dev_, rows, embedding_scale,
+                            residual_, status_dev_, stream_, false));
+    float* x = residual_;
+    float* x2 = post_attention_;
+    for (uint32_t l = 0; l < c.layers; ++l) {
+        const LayerWeights& w = layers_[l];
+        const LayerCache& cache = caches_[l];
+        GF_TRY(launch_rms_norm(x, w.attn_norm, nullptr, normalized_, rows, c.hidden, c.rms_eps, stream_, true));
+        GF_TRY(matmul(w.q, normalized_, raw_q_, rows));
+        GF_TRY(matmul(w.k, normalized_, raw_k_, rows));
+        GF_TRY(matmul(w.v, normalized_, raw_v_, rows));
+        RopeStoreParams rp{raw_q_, raw_k_, raw_v_, c.uses_qk_norm ? w.q_norm : nullptr, c.uses_qk_norm ? w.k_norm : nullptr,
+                           query_, cache.private_k, cache.private_v, state_dev_, status_dev_, rows, c.heads, c.kv_heads,
+                           c.head_dim, c.rms_eps, cache.rope_base, cache.rope_scale, c.kv_f16};
+        GF_TRY(launch_rope_store(rp, stream_, true));
+        AttentionParams ap;
+        ap.q = query_; ap.ring_k = cache.ring_k; ap.ring_v = cache.ring_v; ap.private_k = cache.private_k;
+        ap.private_v = cache.private_v; ap.out = attention_out_;
+        ap.partial_out = static_cast<float*>(attention_ws_);
+        ap.partial_ml = ap.partial_out + (size_t)c.row_capacity * c.heads * kMaxAttentionPartitions * 256u;
+        ap.base_position = state_dev_; ap.rows = rows; ap.heads = c.heads; ap.kv_heads = c.kv_heads; ap.head_dim = c.head_dim;
+        ap.ring_mask = cache.ring_rows - 1u; ap.window = cache.window; ap.scale = c.attention_scale;
+        ap.softcap = c.attn_softcap; ap.kv_f16 = c.kv_f16;
+        GF_TRY(launch_attention(ap, stream_, true));
+        GF_TRY(matmul(w.o, attention_out_, projected_, rows));
+        GF_TRY(launch_rms_norm(projected_, w.post_attention_norm, x, x2, rows, c.hidden, c.rms_eps, stream_, true));
+        GF_TRY(launch_rms_norm(x2, w.ffn_norm, nullptr, normalized_, rows, c.hidden, c.rms_eps, stream_, true));
+        GF_TRY(matmul(w.gate, normalized_, gate_, rows));
+        GF_TRY(matmul(w.up, normalized_, up_, rows));
+        GF_TRY(launch_geglu(gate_, up_, gated_, (uint64_t)rows * c.ffn, stream_, true));
+        GF_TRY(matmul(w.down, gated_, projected_, rows));
+        GF_TRY(launch_rms_norm(projected_, w.post_ffw_norm, x2, x, rows, c.hidden, c.rms_eps, stream_, true));
+        launches_ += 8;
+    }
+    if (flags & kForwardLogits) {
+        GF_TRY(launch_rms_norm(x, output_norm_, nullptr, normalized_, rows, c.hidden, c.rms_eps, stream_, true));
+        GF_TRY(matmul(has_head_ ? head_ : token_embd_, normalized_, logits_, rows));
+        ++launches_;
+    }
+    return GF_OK;
+}
+
+int Model::run_graph_or_encode(uint32_t rows, uint32_t flags) {
+    const int with_logits = (flags & kForwardLogits) ? 1 : 0;
+    if (!use_graph_) return encode_blocks(rows, flags);
+    cudaGraphExec_t& exec = graphs_[rows][with_logits];
+    if (!exec) {
+        // Record the pass once; every later token replays it (positions and ids live in device memory).
+        const uint32_t before = launches_;
+        cudaGraph_t graph = nullptr;
+        GF_CUDA(cudaStreamBeginCapture(stream_, cudaStreamCaptureModeThreadLocal));
+        const int status = encode_blocks(rows, flags);
+        const cudaError_t end = cudaStreamEndCapture(stream_, &graph);
+        launches_ = before;
+        if (status != GF_OK) { if (graph) cudaGraphDestroy(graph); return status; }
+        GF_CUDA(end);
+        const cudaError_t inst = cudaGraphInstantiate(&exec, graph, 0);
+        cudaGraphDestroy(graph);
+        GF_CUDA(inst);
+    }
+    GF_CUDA(cudaGraphLaunch(exec, stream_));
+    launches_ += config_.layers * 15u + 3u;
+    return GF_OK;
+}
+
+int Model::forward(const uint32_t* tokens_host, uint32_t rows, uint32_t flags) {
+    if (!finalized_) return fail(GF_ERR_STATE, "plan is not finalized");
+    if (poisoned_) return fail(GF_ERR_STATE, "plan is poisoned after an unknown GPU outcome; reset it");
+    if (rows == 0 || rows > config_.row_capacity) return fail(GF_ERR_INVALID, "rows=%u outside [1, %u]", rows, config_.row_capacity);
+    if (position_ > config_.context || rows > config_.context - position_)
+        return fail(GF_ERR_INVALID, "pass exceeds the bound context (%u + %u > %u)", position_, rows, config_.context);
+    if (!(flags & kForwardDeviceTokens)) {
+        if (!tokens_host) return fail(GF_ERR_INVALID, "null token ids");
+        for (uint32_t r = 0; r < rows; ++r)
+            if (tokens_host[r] >= config_.vocab) return fail(GF_ERR_INVALID, "token id %u outside the vocabulary", tokens_host[r]);
+        // The previous pass may still be reading the pinned staging word: order the rewrite after it.
+        GF_CUDA(cudaStreamSynchronize(stream_));
+        std::memcpy(tokens_pinned_, tokens_host, rows * sizeof(uint32_t));
+        GF_CUDA(cudaMemcpyAsync(tokens_dev_, tokens_pinned_, rows * sizeof(uint32_t), cudaMemcpyHostToDevice, stream_));
+    }
+    return run_graph_or_encode(rows, flags);
+}
+
+int Model::publish(uint32_t rows) {
+    if (!finalized_) return fail(GF_ERR_STATE, "plan is not finalized");
+    if (rows == 0 || rows > config_.row_capacity || rows > config_.context - position_)
+        return fail(GF_ERR_INVALID, "cannot publish %u rows", rows);
+    const uint32_t kvw = config_.kv_heads * config_.head_dim;
+    for (uint32_t l = 0; l < config_.layers; ++l) {
+        const LayerCache& cache = caches_[l];
+        GF_TRY(launch_kv_scatter(cache.private_k, cache.private_v, cache.ring_k, cache.ring_v, state_dev_, rows, kvw,
+                                 cache.ring_rows - 1u, config_.kv_f16, stream_, false));
+    }
+    GF_TRY(launch_kernel(advance_position_kernel, dim3(1), dim3(32), 0, stream_, false, state_dev_, rows));
+    launches_ += config_.layers + 1u;
+    position_ += rows;
+    return GF_OK;
+}
+
+int Model::truncate(uint32_t position) {
+    if (!finalized_) return fail(GF_ERR_STATE, "plan is not finalized");
+    if (position > position_) return fail(GF_ERR_INVALID, "cannot truncate forward");
+    if (position_ - position > config_.row_capacity)
+        return fail(GF_ERR_INVALID, "published sliding-window rows older than one pass cannot be restored");
+    if (position != position_) {
+        GF_CUDA(cudaMemcpyAsync(state_dev_, &position, sizeof(uint32_t), cudaMemcpyHostToDevice, stream_));
+        GF_CUDA(cudaStreamSynchronize(stream_));
+        position_ = position;
+    }
+    return GF_OK;
+}
+
+int Model::prefill(const uint32_t* tokens_host, uint32_t count) {
+    if (!tokens_host || count == 0) return fail(GF_ERR_INVALID, "empty prompt");
+    uint32_t done = 0;
+    while (done < count) {
+        const uint32_t rows = std::min(config_.row_capacity, count - done);
+        const bool last = done + rows == count;
+        GF_TRY(forward(tokens_host + done, rows, last ? kForwardLogits : 0u));
+        GF_TRY(publish(rows));
+        done += rows;
+    }
+    return GF_OK;
+}
+
+int Model::select_device(uint32_t rows) {
+    launches_ += 2;
+    return launch_candidates(logits_, rows, config_.vocab, config_.final_softcap, requests_dev_, candidates_ws_, results_dev_,
+                             stream_, false);
+}
+
+int Model::select(const void* requests_host, uint32_t rows) {
+    if (!finalized_) return fail(GF_ERR_STATE, "plan is not finalized");
+    if (!requests_host || rows == 0 || rows > config_.row_capacity) return fail(GF_ERR_INVALID, "bad selection request");
+    const size_t bytes = (size_t)rows * gf_selection_request_bytes();
+    GF_CUDA(cudaStreamSynchronize(stream_));
+    std::memcpy(requests_pinned_, requests_host, bytes);
+    GF_CUDA(cudaMemcpyAsync(requests_dev_, requests_pinned_, bytes, cudaMemcpyHostToDevice, stream_));
+    return select_device(rows);
+}
+
+int Model::read_candidates(void* results_host, uint32_t rows) {
+    if (!results_host || rows == 0 || rows > config_.row_capacity) return fail(GF_ERR_INVALID, "bad candidate readback");
+    GF_CUDA(cudaMemcpyAsync(results_host, results_dev_, (size_t)rows * gf_candidate_result_bytes(), cudaMemcpyDeviceToHost, stream_));
+    return synchronize();
+}
+
+int Model::read_logits(uint32_t row, float* host) {
+    if (!host || row >= config_.row_capacity) return fail(GF_ERR_INVALID, "bad logits readback");
+    GF_CUDA(cudaMemcpyAsync(host, logits_ + (size_t)row * config_.vocab, (size_t)config_.vocab * 4, cudaMemcpyDeviceToHost, stream_));
+    return synchronize();
+}
+
+int Model::synchronize() {
+    const cudaError_t error = cudaStreamSynchronize(stream_);
+    if (error != cudaSuccess) { poisoned_ = true; return check_cuda(error, "stream synchronize"); }
+    return GF_OK;
+}
+
+int Model::status_word(uint32_t* out) {
+    uint32_t host[2] = {0, 0};
+    GF_CUDA(cudaMemcpyAsync(&host[0], status_dev_, 4, cudaMemcpyDeviceToHost, stream_));
+    GF_CUDA(cudaMemcpyAsync(&host[1], error_flag_, 4, cudaMemcpyDeviceToHost, stream_));
+    GF_TRY(synchronize());
+    if (out) *out = host[0];
+    if (host[1] != 0) { poisoned_ = true; return fail(GF_ERR_TIMEOUT, "a weight-streaming wait gave up"); }
+    if (host[0] & kStatusKvNonFinite) { poisoned_ = true; return fail(GF_ERR_NUMERIC, "non-finite F16 K/V (status %u)", host[0]); }
+    return GF_OK;
+}
+
+size_t Model::kv_bytes_per_pass(uint32_t rows) const {
+    // Cached rows one pass reads: every committed row inside each layer's window, K and V.
+    const size_t row_bytes = (size_t)config_.kv_heads * config_.head_dim * (config_.kv_f16 ? 2 : 4) * 2;
+    size_t total = 0;
+    for (const LayerCache& cache : caches_) {
+        const uint32_t seen = cache.window ? std::min(position_, cache.window) : position_;
+        total += (size_t)seen * row_bytes * rows;
+    }
+    return total;
+}
+
+}  // namespace gf
+
+using namespace gf;
+
+struct gf_model { Model impl; explicit gf_model(const gf_model_config& c) : impl(c) {} };
+
+extern "C" {
+
+int gf_model_create(const gf_model_config* config, gf_model** out_model) {
+    if (!config || !out_model) return fail(GF_ERR_INVALID, "gf_model_create: null argument");
+    int count = 0;
+    if (cudaGetDeviceCount(&count) != cudaSuccess || count == 0)
+        return fail(GF_ERR_UNAVAILABLE, "no CUDA device is available; this backend has no CPU path");
+    if (config->layers == 0 || config->hidden == 0 || config->vocab == 0 || config->hidden % 128u || config->ffn % 128u)
+        return fail(GF_ERR_INVALID, "gf_model_create: bad geometry");
+    *out_model = new gf_model(*config);
+    return GF_OK;
+}
+int gf_model_destroy(gf_model* model) { delete model; return GF_OK; }
+int gf_model_set_matrix(gf_model* m, int kind, uint32_t layer, int dtype, const void* native_host, uint64_t k, uint64_t n) {
+    return m ? m->impl.set_matrix(kind, layer, dtype, native_host, k, n) : fail(GF_ERR_INVALID, "null model");
+}
+int gf_model_set_vector(gf_model* m, int kind, uint32_t layer, const float* values_host, uint32_t count) {
+    return m ? m->impl.set_vector(kind, layer, values_host, count) : fail(GF_ERR_INVALID, "null model");
+}
+int gf_model_finalize(gf_model* m) { return m ? m->impl.finalize() : fail(GF_ERR_INVALID, "null model"); }
+int gf_model_reset(gf_model* m) { return m ? m->impl.reset() : fail(GF_ERR_INVALID, "null model"); }
+int gf_model_position(const gf_model* m, uint32_t* out) {
+    if (!m || !out) return fail(GF_ERR_INVALID, "null argument");
+    *out = m->impl.position();
+    return GF_OK;
+}
+int gf_model_forward(gf_model* m, const uint32_t* tokens_host, uint32_t rows, uint32_t flags) {
+    return m ? m->impl.forward(tokens_host, rows, flags) : fail(GF_ERR_INVALID, "null model");
+}
+int gf_model_publish(gf_model* m, uint32_t rows) { return m ? m->impl.publish(rows) : fail(GF_ERR_INVALID, "null model"); }
+int gf_model_prefill(gf_model* m, const uint32_t* tokens_host, uint32_t count) {
+    return m ? m->impl.prefill(tokens_host, count) : fail(GF_ERR_INVALID, "null model");
+}
+int gf_model_truncate(gf_model* m, uint32_t position) { return m ? m->impl.truncate(position) : fail(GF_ERR_INVALID, "null model"); }
+int gf_model_select(gf_model* m, const void* requests_host, uint32_t rows) {
+    return m ? m->impl.select(requests_host, rows) : fail(GF_ERR_INVALID, "null model");
+}
+int gf_model_read_candidates(gf_model* m, void* results_host, uint32_t rows) {
+    return m ? m->impl.read_candidates(results_host, rows) : fail(GF_ERR_INVALID, "null model");
+}
+int gf_model_read_logits(gf_model* m, uint32_t row, float* logits_host) {
+    return m ? m->impl.read_logits(row, logits_host) : fail(GF_ERR_INVALID, "null model");
+}
+int gf_model_synchronize(gf_model* m) { return m ? m->impl.synchronize() : fail(GF_ERR_INVALID, "null model"); }
+int gf_model_status(gf_model* m, uint32_t* out_status) { return m ? m->impl.status_word(out_status) : fail(GF_ERR_INVALID, "null model"); }
+void* gf_model_stream(gf_model* m) { return m ? m->impl.stream() : nullptr; }
+uint32_t* gf_model_tokens_dev(gf_model* m) { return m ? m->impl.tokens_dev() : nullptr; }
+float* gf_model_logits_dev(gf_model* m) { return m ? m->impl.logits_dev() : nullptr; }
+size_t gf_model_weight_bytes(const gf_model* m, int native) {
+    return m ? (native ? m->impl.native_weight_bytes() : m->impl.weight_bytes()) : 0;
+}
+size_t gf_model_kv_bytes_per_pass(const gf_model* m, uint32_t rows) { return m ? m->impl.kv_bytes_per_pass(rows) : 0; }
+uint32_t gf_model_kernel_launches(const gf_model* m) { return m ? m->impl.kernel_launches() : 0; }
+int gf_model_use_graph(gf_model* m, int enable) {
+    if (!m) return fail(GF_ERR_INVALID, "null model");
+    m->impl.set_use_graph(enable != 0);
+    return GF_OK;
+}
+
+}  // extern "C"

@@ -1,0 +1,112 @@
+// Resident Gemma model plan: packed weights, KV rings + private rows, scratch, and the block
+// schedule.  One class serves the 12B target, the Gemma 2 target and the 270M drafter; they
+// differ only in configuration (weight types, KV precision, RoPE, softcaps, QK norm).
+#pragma once
+
+#include "common.cuh"
+#include "ops.cuh"
+
+#include <string>
+#include <vector>
+
+namespace gf {
+
+struct PackedMatrix {
+    int dtype = 0;
+    uint64_t k = 0, n = 0;
+    uint8_t* data = nullptr;     // streaming layout, device
+    size_t bytes = 0;
+    size_t native_bytes = 0;
+};
+
+struct LayerWeights {
+    PackedMatrix q, k, v, o, gate, up, down;
+    float *attn_norm = nullptr, *post_attention_norm = nullptr, *ffn_norm = nullptr, *post_ffw_norm = nullptr;
+    float *q_norm = nullptr, *k_norm = nullptr;
+};
+
+struct LayerCache {
+    void *ring_k = nullptr, *ring_v = nullptr;        // [ring_rows][kv_width]
+    void *private_k = nullptr, *private_v = nullptr;  // [row_capacity][kv_width]
+    uint32_t ring_rows = 0;                           // power of two (gemma2_metal_plan.cpp:356-366)
+    uint32_t window = 0;                              // 0 = global layer
+    float rope_base = 0.0f, rope_scale = 1.0f;
+};
+
+enum ForwardFlags : uint32_t {
+    kForwardLogits = 1u,        // final norm + output head for every row
+    kForwardDeviceTokens = 2u,  // token ids are already in the device token buffer
+};
+
+class Model {
+public:
+    explicit Model(const gf_model_config& config);
+    ~Model();
+    Model(const Model&) = delete;
+    Model& operator=(const Model&) = delete;
+
+    int set_matrix(int kind, uint32_t layer, int dtype, const void* native_host, uint64_t k, uint64_t n);
+    int set_vector(int kind, uint32_t layer, const float* host, uint32_t count);
+    int finalize();
+
+    int reset();
+    int forward(const uint32_t* tokens_host, uint32_t rows, uint32_t flags);
+    int publish(uint32_t rows);
+    int select(const void* requests_host, uint32_t rows);
+    int read_candidates(void* results_host, uint32_t rows);
+    int read_logits(uint32_t row, float* host);
+    int synchronize();
+    int status_word(uint32_t* out);
+    int prefill(const uint32_t* tokens_host, uint32_t count);
+    int truncate(uint32_t position);
+
+    const gf_model_config& config() const { return config_; }
+    uint32_t position() const { return position_; }
+    cudaStream_t stream() const { return stream_; }
+    float* logits_dev() const { return logits_; }
+    uint32_t* tokens_dev() const { return tokens_dev_; }
+    uint32_t* base_position_dev() const { return state_dev_; }
+    void* requests_dev() const { return requests_dev_; }
+    void* results_dev() const { return results_dev_; }
+    size_t weight_bytes() const { return weight_bytes_; }
+    size_t native_weight_bytes() const { return native_weight_bytes_; }
+    size_t kv_bytes_per_pass(uint32_t rows) const;
+    uint32_t kernel_launches() const { return launches_; }
+    void set_use_graph(bool on) { use_graph_ = on; }
+
+    // Enqueues the selection for rows whose requests already sit in requests_dev().
+    int select_device(uint32_t rows);
+
+private:
+    int encode_blocks(uint32_t rows, uint32_t flags);
+    int matmul(const PackedMatrix& w, const float* x, float* y, uint32_t rows);
+    int run_graph_or_encode(uint32_t rows, uint32_t flags);
+    bool layer_is_local(uint32_t layer) const;
+
+    gf_model_config config_;
+    bool finalized_ = false, use_graph_ = true, poisoned_ = false;
+    cudaStream_t stream_ = nullptr;
+    PackedMatrix token_embd_, head_;
+    bool has_head_ = false;
+    float* output_norm_ = nullptr;
+    std::vector<LayerWeights> layers_;
+    std::vector<LayerCache> caches_;
+    std::vector<void*> allocations_;
+    size_t weight_bytes_ = 0, native_weight_bytes_ = 0;
+
+    // scratch (rows x width), names after target_verifier.hpp:228-257
+    float *residual_ = nullptr, *normalized_ = nullptr, *raw_q_ = nullptr, *raw_k_ = nullptr, *raw_v_ = nullptr;
+    float *query_ = nullptr, *attention_out_ = nullptr, *projected_ = nullptr, *post_attention_ = nullptr;
+    float *gate_ = nullptr, *up_ = nullptr, *gated_ = nullptr, *logits_ = nullptr;
+    void *attention_ws_ = nullptr, *matmul_ws_ = nullptr, *candidates_ws_ = nullptr;
+    void *requests_dev_ = nullptr, *results_dev_ = nullptr;
+    uint32_t *tokens_dev_ = nullptr, *state_dev_ = nullptr, *status_dev_ = nullptr;
+    int* error_flag_ = nullptr;
+    uint32_t* tokens_pinned_ = nullptr;
+    void* requests_pinned_ = nullptr;
+    uint32_t position_ = 0;
+    uint32_t launches_ = 0;
+    cudaGraphExec_t graphs_[GF_MAX_ROWS + 1][2] = {};
+};
+
+}  // namespace gf

@@ -1,0 +1,496 @@
+// Embedding gather, RMSNorm (+residual), per-head norm + NEOX RoPE + private KV store, GeGLU,
+// split-KV grouped-query attention over ring + private rows, and KV publication.
+#include "ops.cuh"
+
+#include <cmath>
+
+namespace gf {
+
+// ------------------------------------------------------------------ embedding
+
+// Decodes element e of output column `token` straight from the streaming layout, with the
+// reference's rounding (quantization.cpp:457,517,590), then scales it (model.cpp:599-605).
+__device__ __forceinline__ float packed_element(int dtype, const uint8_t* packed, uint32_t units, uint32_t token,
+                                                uint32_t e) {
+    const uint32_t tile = token >> 3, c = token & 7u;
+    if (dtype == GF_Q6_K) {
+        const uint8_t* base = packed + ((size_t)tile * units + e / 256u) * 1680u;
+        const uint32_t i = e % 256u, half = i / 128u, w = i % 128u, lane = w % 32u, quarter = w / 32u;
+        const uint32_t lowbyte = base[c * 128u + half * 64u + (quarter % 2u) * 32u + lane];
+        const uint32_t low = quarter < 2u ? (lowbyte & 15u) : (lowbyte >> 4);
+        const uint32_t high = (base[1024u + c * 64u + half * 32u + lane] >> (quarter * 2u)) & 3u;
+        const int q = (int)(low | (high << 4)) - 32;
+        const float d = __half2float(__ushort_as_half(*reinterpret_cast<const unsigned short*>(base + 1664u + c * 2u)));
+        const float s = (float)(int)(signed char)base[1536u + c * 16u + i / 16u];
+        return __fmul_rn(__fmul_rn(d, s), (float)q);
+    }
+    if (dtype == GF_Q8_0) {
+        const uint8_t* base = packed + ((size_t)tile * units + e / 128u) * 1088u;
+        const uint32_t i = e % 128u;
+        const float d = __half2float(__ushort_as_half(
+            *reinterpret_cast<const unsigned short*>(base + 1024u + c * 8u + (i / 32u) * 2u)));
+        return __fmul_rn(d, (float)(int)(signed char)base[c * 128u + i]);
+    }
+    const uint8_t* base = packed + ((size_t)tile * units + e / 256u) * 1152u;
+    const uint8_t* hdr = base + 1024u + c * 16u;
+    const uint32_t i = e % 256u, group = i / 32u, in64 = i % 64u;
+    const float d = __half2float(__ushort_as_half(*reinterpret_cast<const unsigned short*>(hdr)));
+    const float dmin = __half2float(__ushort_as_half(*reinterpret_cast<const unsigned short*>(hdr + 2)));
+    const uint8_t* s = hdr + 4;
+    uint32_t sc, mn;
+    if (group < 4u) { sc = s[group] & 63u; mn = s[group + 4u] & 63u; }
+    else { sc = (s[group + 4u] & 15u) | ((s[group - 4u] >> 6) << 4); mn = (s[group + 4u] >> 4) | ((s[group] >> 6) << 4); }
+    const uint32_t byte = base[c * 128u + (i / 64u) * 32u + in64 % 32u];
+    const uint32_t q = in64 < 32u ? (byte & 15u) : (byte >> 4);
+    return __fsub_rn(__fmul_rn(__fmul_rn(d, (float)sc), (float)q), __fmul_rn(dmin, (float)mn));
+}
+
+__global__ void __launch_bounds__(256) embedding_kernel(int dtype, const uint8_t* __restrict__ packed, uint32_t k,
+                                                        uint32_t vocab, const uint32_t* __restrict__ tokens,
+                                                        uint32_t rows, float scale, float* __restrict__ out,
+                                                        uint32_t* status) {
+    pdl_wait();
+    pdl_launch_dependents();
+    const uint32_t units = k / unit_elements(dtype);
+    for (uint32_t i = blockIdx.x * blockDim.x + threadIdx.x; i < rows * k; i += gridDim.x * blockDim.x) {
+        const uint32_t row = i / k, e = i % k;
+        const uint32_t token = tokens[row];
+        if (token >= vocab) {          // out-of-range id: flag it and poison the row (metal_kernels.mm:461)
+            if (e == 0) atomicOr(status, kStatusBadToken);
+            out[i] = __int_as_float(0x7fc00000);
+            continue;
+        }
+        out[i] = __fmul_rn(packed_element(dtype, packed, units, token, e), scale);
+    }
+}
+
+// ------------------------------------------------------------------ RMSNorm (+ residual)
+
+__device__ __forceinline__ float block_sum(float v, float* scratch) {
+    v = warp_sum(v);
+    const uint32_t warp = threadIdx.x >> 5, lane = threadIdx.x & 31u, warps = blockDim.x >> 5;
+    if (lane == 0) scratch[warp] = v;
+    __syncthreads();
+    float total = 0.0f;
+    for (uint32_t w = 0; w < warps; ++w) total += scratch[w];   // same order in every thread
+    __syncthreads();
+    return total;
+}
+
+// out = x * rsqrt(mean(x^2) + eps) * gamma [+ residual]   (ops/normalization.cpp:70-101,
+// metal_kernels.mm:2019-2158).  One block per row.
+__global__ void __launch_bounds__(256) rms_norm_kernel(const float* __restrict__ x, const float* __restrict__ gamma,
+                                                       const float* __restrict__ residual, float* __restrict__ out,
+                                                       uint32_t hidden, float eps) {
+    __shared__ float scratch[8];
+    pdl_wait();
+    pdl_launch_dependents();
+    const float* xr = x + (size_t)blockIdx.x * hidden;
+    float sum = 0.0f;
+    for (uint32_t c = threadIdx.x; c < hidden; c += blockDim.x) sum = fmaf(xr[c], xr[c], sum);
+    const float total = block_sum(sum, scratch);
+    const float inv = __fdiv_rn(1.0f, __fsqrt_rn(__fadd_rn(__fdiv_rn(total, (float)hidden), eps)));
+    for (uint32_t c = threadIdx.x; c < hidden; c += blockDim.x) {
+        float v = __fmul_rn(__fmul_rn(xr[c], inv), gamma[c]);
+        if (residual) v = __fadd_rn(residual[(size_t)blockIdx.x * hidden + c], v);
+        out[(size_t)blockIdx.x * hidden + c] = v;
+    }
+}
+
+// ------------------------------------------------------------------ QK norm + RoPE + private KV store
+
+// One block per (head, row); thread i owns the NEOX pair (i, i + head_dim/2).
+// Query heads: optional per-head RMSNorm, rotate, write f32.  KV heads: K is normalised,
+// rotated and rounded to the cache type, V is rounded and stored; non-finite F16 sets status
+// bit 8 (metal_kernels.mm:1915-1930, 2406-2517; angle as ops/rope.cpp:109-117 in double).
+__global__ void __launch_bounds__(256) rope_store_kernel(RopeStoreParams p) {
+    __shared__ float scratch[8];
+    pdl_wait();
+    pdl_launch_dependents();
+    const uint32_t head = blockIdx.x, row = blockIdx.y, half = p.head_dim / 2u, i = threadIdx.x;
+    const bool is_query = head < p.heads;
+    const uint32_t kvh = head - p.heads;
+    const float* src = is_query ? p.raw_q + ((size_t)row * p.heads + head) * p.head_dim
+                                : p.raw_k + ((size_t)row * p.kv_heads + kvh) * p.head_dim;
+    const float* gamma = is_query ? p.q_norm : p.k_norm;
+    float first = src[i], second = src[i + half];
+    if (gamma) {
+        const float total = block_sum(fmaf(first, first, second * second), scratch);
+        const float inv = __fdiv_rn(1.0f, __fsqrt_rn(__fadd_rn(__fdiv_rn(total, (float)p.head_dim), p.eps)));
+        first = __fmul_rn(__fmul_rn(first, inv), gamma[i]);
+        second = __fmul_rn(__fmul_rn(second, inv), gamma[i + half]);
+    }
+    const uint32_t position = *p.base_position + row;
+    const double exponent = (double)(2u * i) / (double)p.head_dim;
+    const double angle = (double)position * (double)p.freq_scale / pow((double)p.freq_base, exponent);
+    double sd, cd;
+    sincos(angle, &sd, &cd);
+    const float c = (float)cd, s = (float)sd;
+    const float r0 = __fsub_rn(__fmul_rn(first, c), __fmul_rn(second, s));
+    const float r1 = __fadd_rn(__fmul_rn(first, s), __fmul_rn(second, c));
+    if (is_query) {
+        float* dst = p.q_out + ((size_t)row * p.heads + head) * p.head_dim;
+        dst[i] = r0;
+        dst[i + half] = r1;
+        return;
+    }
+    const size_t o = ((size_t)row * p.kv_heads + kvh) * p.head_dim;
+    const float* vsrc = p.raw_v + o;
+    const float v0 = vsrc[i], v1 = vsrc[i + half];
+    if (p.kv_f16) {
+        __half* kd = static_cast<__half*>(p.private_k) + o;
+        __half* vd = static_cast<__half*>(p.private_v) + o;
+        const __half k0 = __float2half_rn(r0), k1 = __float2half_rn(r1), h0 = __float2half_rn(v0), h1 = __float2half_rn(v1);
+        kd[i] = k0; kd[i + half] = k1; vd[i] = h0; vd[i + half] = h1;
+        if (!isfinite(__half2float(k0)) || !isfinite(__half2float(k1)) || !isfinite(__half2float(h0)) || !isfinite(__half2float(h1)))
+            atomicOr(p.status, kStatusKvNonFinite);
+    } else {
+        float* kd = static_cast<float*>(p.private_k) + o;
+        float* vd = static_cast<float*>(p.private_v) + o;
+        kd[i] = r0; kd[i + half] = r1; vd[i] = v0; vd[i + half] = v1;
+    }
+}
+
+// ------------------------------------------------------------------ attention
+
+__device__ __forceinline__ void load8(const __half* p, float (&v)[8]) {
+    const uint4 raw = *reinterpret_cast<const uint4*>(p);
+    const __half2* h = reinterpret_cast<const __half2*>(&raw);
+#pragma unroll
+    for (int i = 0; i < 4; ++i) { const float2 f = __half22float2(h[i]); v[2 * i] = f.x; v[2 * i + 1] = f.y; }
+}
+__device__ __forceinline__ void load8(const float* p, float (&v)[8]) {
+    const float4 a = *reinterpret_cast<const float4*>(p), b = *reinterpret_cast<const float4*>(p + 4);
+    v[0] = a.x; v[1] = a.y; v[2] = a.z; v[3] = a.w; v[4] = b.x; v[5] = b.y; v[6] = b.z; v[7] = b.w;
+}
+
+struct AttentionWindow { uint32_t base_first, base_count, private_start, private_count, count, parts; };
+
+// Which cached rows a verify/decode row sees: the committed ring rows inside its window, then
+// the private rows of its ancestors, itself included (gemma_target_runtime.cpp:256-268,
+// target_verifier.cpp:186-202).  The sliding window includes the row itself.
+__device__ __forceinline__ AttentionWindow attention_window(uint32_t base, uint32_t row, uint32_t window) {
+    AttentionWindow w;
+    const uint32_t position = base + row;
+    const uint32_t window_start = (window != 0u && position + 1u > window) ? position + 1u - window : 0u;
+    w.base_first = min(base, window_start);
+    w.base_count = base - w.base_first;
+    w.private_start = window_start > base ? window_start - base : 0u;
+    w.private_count = row + 1u - w.private_start;
+    w.count = w.base_count + w.private_count;
+    w.parts = min((uint32_t)kMaxAttentionPartitions,
+                  (w.count + kAttentionTokensPerPartition - 1u) / kAttentionTokensPerPartition);
+    return w;
+}
+
+// Online-softmax GQA, head_dim 256: grid (kv_head, partition, row), four warps per block.  A warp
+// walks quads of cached rows; a lane owns eight of the 256 dimensions, so K and V rows are read
+// as one coalesced 512-byte (F16) or 1-KiB (F32) line per row, shared by the G query heads.
+template <typename KV, int G>
+__global__ void __launch_bounds__(128) attention_kernel(AttentionParams p) {
+    __shared__ float scores[4][16];
+    __shared__ float warp_m[4][G], warp_l[4][G];
+    __shared__ float warp_acc[4][G][256];
+    pdl_wait();
+    pdl_launch_dependents();
+    const uint32_t kvh = blockIdx.x, part = blockIdx.y, row = blockIdx.z;
+    const uint32_t warp = threadIdx.x >> 5, lane = threadIdx.x & 31u;
+    const AttentionWindow win = attention_window(*p.base_position, row, p.window);
+    if (part >= win.parts) return;
+    const uint32_t kv_width = p.kv_heads * 256u;
+    const KV* ring_k = static_cast<const KV*>(p.ring_k);
+    const KV* ring_v = static_cast<const KV*>(p.ring_v);
+    const KV* priv_k = static_cast<const KV*>(p.private_k);
+    const KV* priv_v = static_cast<const KV*>(p.private_v);
+
+    float q[G][8];
+#pragma unroll
+    for (int g = 0; g < G; ++g) {
+        const float* qp = p.q + ((size_t)row * p.heads + kvh * G + g) * 256u + lane * 8u;
+        load8(qp, q[g]);
+    }
+    float m[G], l[G], acc[G][8];
+#pragma unroll
+    for (int g = 0; g < G; ++g) {
+        m[g] = -INFINITY; l[g] = 0.0f;
+#pragma unroll
+        for (int d = 0; d < 8; ++d) acc[g][d] = 0.0f;
+    }
+    const uint32_t quads = (win.count + 3u) / 4u;
+    for (uint32_t quad = part * 4u + warp; quad < quads; quad += win.parts * 4u) {
+        float kf[4][8], vf[4][8];
+        bool valid[4];
+#pragma unroll
+        for (int t = 0; t < 4; ++t) {
+            const uint32_t token = quad * 4u + t;
+            valid[t] = token < win.count;
+            const KV *kp, *vp;
+            if (token < win.base_count) {
+                const size_t slot = ((size_t)((win.base_first + token) & p.ring_mask)) * kv_width + kvh * 256u + lane * 8u;
+                kp = ring_k + slot; vp = ring_v + slot;
+            } else {
+                const uint32_t prow = valid[t] ? win.private_start + (token - win.base_count) : 0u;
+                const size_t slot = (size_t)prow * kv_width + kvh * 256u + lane * 8u;
+                kp = priv_k + slot; vp = priv_v + slot;
+            }
+            load8(kp, kf[t]);
+            load8(vp, vf[t]);
+        }
+        // Partial dot products (token t, head g) -> column t*G+g, reduced across the warp eight at a time.
+        float s[4][G];
+#pragma unroll
+        for (int half = 0; half < (4 * G + 7) / 8; ++half) {
+            float cols[8];
+#pragma unroll
+            for (int cidx = 0; cidx < 8; ++cidx) {
+                const int flat = half * 8 + cidx, t = flat / G, g = flat % G;
+                float dot = 0.0f;
+                if (flat < 4 * G) {
+#pragma unroll
+                    for (int d = 0; d < 8; ++d) dot = fmaf(q[g][d], kf[t][d], dot);
+                }
+                cols[cidx] = dot;
+            }
+            const float total = reduce_columns8(cols, lane);
+            if ((lane & 3u) == 0u) scores[warp][half * 8 + column_of_lane(lane)] = total;
+        }
+        __syncwarp();
+#pragma unroll
+        for (int t = 0; t < 4; ++t)
+#pragma unroll
+            for (int g = 0; g < G; ++g) {
+                float v = scores[warp][t * G + g] * p.scale;
+                if (p.softcap > 0.0f) v = tanhf(v / p.softcap) * p.softcap;
+                s[t][g] = valid[t] ? v : -INFINITY;
+            }
+        __syncwarp();
+#pragma unroll
+        for (int g = 0; g < G; ++g) {
+            float m_new = m[g];
+#pragma unroll
+            for (int t = 0; t < 4; ++t) m_new = fmaxf(m_new, s[t][g]);
+            const float corr = m[g] == -INFINITY ? 0.0f : expf(m[g] - m_new);
+            float pr[4];
+#pragma unroll
+            for (int t = 0; t < 4; ++t) pr[t] = valid[t] ? expf(s[t][g] - m_new) : 0.0f;
+            l[g] = l[g] * corr + ((pr[0] + pr[1]) + (pr[2] + pr[3]));
+#pragma unroll
+            for (int d = 0; d < 8; ++d) {
+                float a = acc[g][d] * corr;
+#pragma unroll
+                for (int t = 0; t < 4; ++t) a = fmaf(pr[t], vf[t][d], a);
+                acc[g][d] = a;
+            }
+            m[g] = m_new;
+        }
+    }
+    // Combine the four warps in warp order.
+#pragma unroll
+    for (int g = 0; g < G; ++g) {
+        if (lane == 0) { warp_m[warp][g] = m[g]; warp_l[warp][g] = l[g]; }
+#pragma unroll
+        for (int d = 0; d < 8; ++d) warp_acc[warp][g][lane * 8 + d] = acc[g][d];
+    }
+    __syncthreads();
+    for (uint32_t idx = threadIdx.x; idx < (uint32_t)G * 256u; idx += blockDim.x) {
+        const uint32_t g = idx / 256u, d = idx % 256u;
+        float mm = -INFINITY;
+        for (int w = 0; w < 4; ++w) mm = fmaxf(mm, warp_m[w][g]);
+        float a = 0.0f, ll = 0.0f;
+        for (int w = 0; w < 4; ++w) {
+            if (warp_l[w][g] == 0.0f) continue;
+            const float f = expf(warp_m[w][g] - mm);
+            a = fmaf(warp_acc[w][g][d], f, a);
+            ll = fmaf(warp_l[w][g], f, ll);
+        }
+        const uint32_t head = kvh * G + g;
+        if (win.parts == 1u) {
+            p.out[((size_t)row * p.heads + head) * 256u + d] = a / ll;
+        } else {
+            const size_t slot = ((size_t)row * p.heads + head) * kMaxAttentionPartitions + part;
+            p.partial_out[slot * 256u + d] = a;
+            if (d == 0) { p.partial_ml[slot * 2u] = mm; p.partial_ml[slot * 2u + 1u] = ll; }
+        }
+    }
+}
+
+// Merges the partitions of one (row, head) in partition order.
+__global__ void __launch_bounds__(256) attention_reduce_kernel(AttentionParams p) {
+    pdl_wait();
+    pdl_launch_dependents();
+    const uint32_t head = blockIdx.x, row = blockIdx.y, d = threadIdx.x;
+    const AttentionWindow win = attention_window(*p.base_position, row, p.window);
+    if (win.parts <= 1u) return;
+    const size_t base = ((size_t)row * p.heads + head) * kMaxAttentionPartitions;
+    float mm = -INFINITY;
+    for (uint32_t i = 0; i < win.parts; ++i) mm = fmaxf(mm, p.partial_ml[(base + i) * 2u]);
+    float a = 0.0f, ll = 0.0f;
+    for (uint32_t i = 0; i < win.parts; ++i) {
+        const float f = expf(p.partial_ml[(base + i) * 2u] - mm);
+        a = fmaf(p.partial_out[(base + i) * 256u + d], f, a);
+        ll = fmaf(p.partial_ml[(base + i) * 2u + 1u], f, ll);
+    }
+    p.out[((size_t)row * p.heads + head) * 256u + d] = a / ll;
+}
+
+// ------------------------------------------------------------------ GeGLU, KV publication
+
+// gelu_tanh(gate) * up   (ops/elementwise.cpp:79-94, metal_kernels.mm:1827-1843)
+__global__ void __launch_bounds__(256) geglu_kernel(const float* __restrict__ gate, const float* __restrict__ up,
+                                                    float* __restrict__ out, uint64_t count) {
+    pdl_wait();
+    pdl_launch_dependents();
+    for (uint64_t i = blockIdx.x * (uint64_t)blockDim.x + threadIdx.x; i < count; i += (uint64_t)gridDim.x * blockDim.x) {
+        const float v = gate[i];
+        const float inner = __fmul_rn(0.7978845608028654f, __fadd_rn(v, __fmul_rn(__fmul_rn(__fmul_rn(0.044715f, v), v), v)));
+        out[i] = __fmul_rn(__fmul_rn(__fmul_rn(0.5f, v), __fadd_rn(1.0f, tanhf(inner))), up[i]);
+    }
+}
+
+// Publishes private rows 0..rows-1 into ring slots (base + r) & mask   (metal_kernels.mm:2519-2557).
+__global__ void __launch_bounds__(256) kv_scatter_kernel(const uint8_t* __restrict__ private_k, const uint8_t* __restrict__ private_v,
+                                                         uint8_t* __restrict__ ring_k, uint8_t* __restrict__ ring_v,
+                                                         const uint32_t* base_position, uint32_t row_bytes, uint32_t ring_mask) {
+    pdl_wait();
+    pdl_launch_dependents();
+    const uint32_t row = blockIdx.x;
+    const size_t dst = (size_t)((*base_position + row) & ring_mask) * row_bytes, src = (size_t)row * row_bytes;
+    for (uint32_t b = threadIdx.x * 16u; b < row_bytes; b += blockDim.x * 16u) {
+        *reinterpret_cast<uint4*>(ring_k + dst + b) = *reinterpret_cast<const uint4*>(private_k + src + b);
+        *reinterpret_cast<uint4*>(ring_v + dst + b) = *reinterpret_cast<const uint4*>(private_v + src + b);
+    }
+}
+
+// ------------------------------------------------------------------ launchers
+
+int launch_embedding(int dtype, const void* packed, uint32_t k, uint32_t vocab, const uint32_t* tokens, uint32_t rows,
+                     float scale, float* out, uint32_t* status, cudaStream_t stream, bool pdl) {
+    const uint32_t blocks = (rows * k + 255u) / 256u;
+    return launch_kernel(embedding_kernel, dim3(blocks), dim3(256), 0, stream, pdl, dtype,
+                         static_cast<const uint8_t*>(packed), k, vocab, tokens, rows, scale, out, status);
+}
+
+int launch_rms_norm(const float* x, const float* gamma, const float* residual, float* out, uint32_t rows,
+                    uint32_t hidden, float eps, cudaStream_t stream, bool pdl) {
+    return launch_kernel(rms_norm_kernel, dim3(rows), dim3(256), 0, stream, pdl, x, gamma, residual, out, hidden, eps);
+}
+
+int launch_rope_store(const RopeStoreParams& p, cudaStream_t stream, bool pdl) {
+    if (p.head_dim < 64u || p.head_dim > 512u || (p.head_dim & 63u))
+        return fail(GF_ERR_INVALID, "rope/store: head_dim=%u unsupported", p.head_dim);
+    return launch_kernel(rope_store_kernel, dim3(p.heads + p.kv_heads, p.rows), dim3(p.head_dim / 2u), 0, stream, pdl, p);
+}
+
+template <typename KV>
+static int launch_attention_typed(const AttentionParams& p, cudaStream_t stream, bool pdl) {
+    const dim3 grid(p.kv_heads, kMaxAttentionPartitions, p.rows);
+    const uint32_t group = p.heads / p.kv_heads;
+    int status;
+    if (group == 1u) status = launch_kernel(attention_kernel<KV, 1>, grid, dim3(128), 0, stream, pdl, p);
+    else if (group == 2u) status = launch_kernel(attention_kernel<KV, 2>, grid, dim3(128), 0, stream, pdl, p);
+    else if (group == 4u) status = launch_kernel(attention_kernel<KV, 4>, grid, dim3(128), 0, stream, pdl, p);
+    else return fail(GF_ERR_INVALID, "attention: query/KV head ratio %u unsupported (1, 2, 4)", group);
+    if (status != GF_OK) return status;
+    return launch_kernel(attention_reduce_kernel, dim3(p.heads, p.rows), dim3(256), 0, stream, pdl, p);
+}
+
+int launch_attention(const AttentionParams& p, cudaStream_t stream, bool pdl) {
+    if (p.head_dim != 256u) return fail(GF_ERR_INVALID, "attention: head_dim must be 256 (got %u)", p.head_dim);
+    if (p.heads % p.kv_heads) return fail(GF_ERR_INVALID, "attention: heads %u not a multiple of kv heads %u", p.heads, p.kv_heads);
+    return p.kv_f16 ? launch_attention_typed<__half>(p, stream, pdl) : launch_attention_typed<float>(p, stream, pdl);
+}
+
+int launch_geglu(const float* gate, const float* up, float* out, uint64_t count, cudaStream_t stream, bool pdl) {
+    const uint32_t blocks = (uint32_t)((count + 255u) / 256u);
+    return launch_kernel(geglu_kernel, dim3(blocks), dim3(256), 0, stream, pdl, gate, up, out, count);
+}
+
+int launch_kv_scatter(const void* private_k, const void* private_v, void* ring_k, void* ring_v,
+                      const uint32_t* base_position, uint32_t rows, uint32_t row_width, uint32_t ring_mask, int kv_f16,
+                      cudaStream_t stream, bool pdl) {
+    const uint32_t row_bytes = row_width * (kv_f16 ? 2u : 4u);
+    return launch_kernel(kv_scatter_kernel, dim3(rows), dim3(128), 0, stream, pdl,
+                         static_cast<const uint8_t*>(private_k), static_cast<const uint8_t*>(private_v),
+                         static_cast<uint8_t*>(ring_k), static_cast<uint8_t*>(ring_v), base_position, row_bytes, ring_mask);
+}
+
+}  // namespace gf
+
+using namespace gf;
+
+// ------------------------------------------------------------------ C entry points (operator level)
+
+extern "C" {
+
+int gf_embedding(int dtype, const void* packed_dev, uint32_t k, uint32_t vocab, const uint32_t* tokens_dev,
+                 uint32_t rows, float scale, float* out_dev, uint32_t* status_dev, void* stream) {
+    if (!packed_dev || !tokens_dev || !out_dev || !status_dev || rows == 0 || k % unit_elements(dtype))
+        return fail(GF_ERR_INVALID, "gf_embedding: bad arguments");
+    return launch_embedding(dtype, packed_dev, k, vocab, tokens_dev, rows, scale, out_dev, status_dev, as_stream(stream), false);
+}
+
+int gf_rms_norm(const float* x_dev, const float* gamma_dev, float* out_dev, uint32_t rows, uint32_t hidden, float eps,
+                void* stream) {
+    if (!x_dev || !gamma_dev || !out_dev || rows == 0 || hidden == 0 || !(eps > 0.0f))
+        return fail(GF_ERR_INVALID, "gf_rms_norm: bad arguments (epsilon must be positive)");
+    return launch_rms_norm(x_dev, gamma_dev, nullptr, out_dev, rows, hidden, eps, as_stream(stream), false);
+}
+
+int gf_rms_norm_add(const float* x_dev, const float* gamma_dev, const float* residual_dev, float* out_dev, uint32_t rows,
+                    uint32_t hidden, float eps, void* stream) {
+    if (!x_dev || !gamma_dev || !residual_dev || !out_dev || rows == 0 || hidden == 0 || !(eps > 0.0f))
+        return fail(GF_ERR_INVALID, "gf_rms_norm_add: bad arguments");
+    return launch_rms_norm(x_dev, gamma_dev, residual_dev, out_dev, rows, hidden, eps, as_stream(stream), false);
+}
+
+int gf_qk_norm_rope_store(const float* raw_q_dev, const float* raw_k_dev, const float* raw_v_dev,
+                          const float* q_norm_dev, const float* k_norm_dev, float* q_out_dev, void* private_k_dev,
+                          void* private_v_dev, const uint32_t* base_position_dev, uint32_t* status_dev, uint32_t rows,
+                          uint32_t heads, uint32_t kv_heads, uint32_t head_dim, float eps, float freq_base,
+                          float freq_scale, int kv_f16, void* stream) {
+    if (!raw_q_dev || !raw_k_dev || !raw_v_dev || !q_out_dev || !private_k_dev || !private_v_dev || !base_position_dev
+        || !status_dev || rows == 0 || !(freq_base > 0.0f))
+        return fail(GF_ERR_INVALID, "gf_qk_norm_rope_store: bad arguments");
+    RopeStoreParams p{raw_q_dev, raw_k_dev, raw_v_dev, q_norm_dev, k_norm_dev, q_out_dev, private_k_dev, private_v_dev,
+                      base_position_dev, status_dev, rows, heads, kv_heads, head_dim, eps, freq_base, freq_scale, kv_f16};
+    return launch_rope_store(p, as_stream(stream), false);
+}
+
+size_t gf_attention_workspace_bytes(uint32_t rows, uint32_t heads) {
+    return (size_t)rows * heads * kMaxAttentionPartitions * (256u + 2u) * sizeof(float);
+}
+
+int gf_attention(const float* q_dev, const void* ring_k_dev, const void* ring_v_dev, const void* private_k_dev,
+                 const void* private_v_dev, float* out_dev, void* workspace_dev, const uint32_t* base_position_dev,
+                 uint32_t rows, uint32_t heads, uint32_t kv_heads, uint32_t head_dim, uint32_t ring_rows,
+                 uint32_t window, float scale, float softcap, int kv_f16, void* stream) {
+    if (!q_dev || !ring_k_dev || !ring_v_dev || !private_k_dev || !private_v_dev || !out_dev || !workspace_dev
+        || !base_position_dev || rows == 0 || rows > GF_MAX_ROWS || ring_rows == 0 || (ring_rows & (ring_rows - 1u)))
+        return fail(GF_ERR_INVALID, "gf_attention: bad arguments (ring rows must be a power of two)");
+    AttentionParams p;
+    p.q = q_dev; p.ring_k = ring_k_dev; p.ring_v = ring_v_dev; p.private_k = private_k_dev; p.private_v = private_v_dev;
+    p.out = out_dev;
+    p.partial_out = static_cast<float*>(workspace_dev);
+    p.partial_ml = p.partial_out + (size_t)rows * heads * kMaxAttentionPartitions * 256u;
+    p.base_position = base_position_dev;
+    p.rows = rows; p.heads = heads; p.kv_heads = kv_heads; p.head_dim = head_dim;
+    p.ring_mask = ring_rows - 1u; p.window = window; p.scale = scale; p.softcap = softcap; p.kv_f16 = kv_f16;
+    return launch_attention(p, as_stream(stream), false);
+}
+
+int gf_gelu_tanh_multiply(const float* gate_dev, const float* up_dev, float* out_dev, uint64_t count, void* stream) {
+    if (!gate_dev || !up_dev || !out_dev || count == 0) return fail(GF_ERR_INVALID, "gf_gelu_tanh_multiply: bad arguments");
+    return launch_geglu(gate_dev, up_dev, out_dev, count, as_stream(stream), false);
+}
+
+int gf_kv_scatter(const void* private_k_dev, const void* private_v_dev, void* ring_k_dev, void* ring_v_dev,
+                  const uint32_t* base_position_dev, uint32_t rows, uint32_t row_width, uint32_t ring_rows, int kv_f16,
+                  void* stream) {
+    if (!private_k_dev || !private_v_dev || !ring_k_dev || !ring_v_dev || !base_position_dev || rows == 0
+        || (ring_rows & (ring_rows - 1u)) || (row_width * (kv_f16 ? 2u : 4u)) % 16u)
+        return fail(GF_ERR_INVALID, "gf_kv_scatter: bad arguments");
+    return launch_kv_scatter(private_k_dev, private_v_dev, ring_k_dev, ring_v_dev, base_position_dev, rows, row_width,
+                             ring_rows - 1u, kv_f16, as_stream(stream), false);
+}
+
+}  // extern "C"

@@ -1,0 +1,78 @@
+// Small fused operators of the Gemma block schedule (everything that is not a weight GEMV).
+// All per-pass scalars (committed position, token ids) are read from device memory so that a
+// captured CUDA graph can be replayed for every token without re-recording.
+#pragma once
+
+#include "common.cuh"
+
+namespace gf {
+
+constexpr int kMaxAttentionPartitions = 32;   // verifier_max_partitions in the reference
+constexpr int kAttentionTokensPerPartition = 256;
+
+// Status bits shared with the reference's validation word
+// (metal_kernels.mm:2332,2357,2370,2484; metal_command_context.hpp:17).
+enum : uint32_t { kStatusBadToken = 1u, kStatusBadRequest = 2u, kStatusBadHistory = 4u, kStatusKvNonFinite = 8u };
+
+struct RopeStoreParams {
+    const float* raw_q;        // [rows][heads*hd]
+    const float* raw_k;        // [rows][kv_heads*hd]
+    const float* raw_v;        // [rows][kv_heads*hd]
+    const float* q_norm;       // [hd] or null (no QK norm)
+    const float* k_norm;
+    float* q_out;              // [rows][heads*hd]
+    void* private_k;           // [row_capacity][kv_heads*hd], f16 or f32
+    void* private_v;
+    const uint32_t* base_position;   // device scalar: position of row 0
+    uint32_t* status;
+    uint32_t rows, heads, kv_heads, head_dim;
+    float eps, freq_base, freq_scale;
+    int kv_f16;
+};
+
+struct AttentionParams {
+    const float* q;            // [rows][heads*hd]
+    const void* ring_k;        // [ring_rows][kv_heads*hd]
+    const void* ring_v;
+    const void* private_k;     // [row_capacity][kv_heads*hd]
+    const void* private_v;
+    float* out;                // [rows][heads*hd]
+    float* partial_out;        // [rows][heads][kMaxAttentionPartitions][hd]
+    float* partial_ml;         // [rows][heads][kMaxAttentionPartitions][2]
+    const uint32_t* base_position;
+    uint32_t rows, heads, kv_heads, head_dim;
+    uint32_t ring_mask;        // ring_rows - 1
+    uint32_t window;           // 0 = global layer
+    float scale, softcap;
+    int kv_f16;
+};
+
+int launch_embedding(int dtype, const void* packed, uint32_t k, uint32_t vocab, const uint32_t* tokens,
+                     uint32_t rows, float scale, float* out, uint32_t* status, cudaStream_t stream, bool pdl);
+int launch_rms_norm(const float* x, const float* gamma, const float* residual, float* out, uint32_t rows,
+                    uint32_t hidden, float eps, cudaStream_t stream, bool pdl);
+int launch_rope_store(const RopeStoreParams& p, cudaStream_t stream, bool pdl);
+int launch_attention(const AttentionParams& p, cudaStream_t stream, bool pdl);
+int launch_geglu(const float* gate, const float* up, float* out, uint64_t count, cudaStream_t stream, bool pdl);
+int launch_kv_scatter(const void* private_k, const void* private_v, void* ring_k, void* ring_v,
+                      const uint32_t* base_position, uint32_t rows, uint32_t row_width, uint32_t ring_mask,
+                      int kv_f16, cudaStream_t stream, bool pdl);
+
+// Launch helper: optional programmatic stream serialisation (PDL).
+template <typename Kernel, typename... Args>
+int launch_kernel(Kernel kernel, dim3 grid, dim3 block, size_t smem, cudaStream_t stream, bool pdl, Args... args) {
+    cudaLaunchConfig_t config = {};
+    config.gridDim = grid;
+    config.blockDim = block;
+    config.dynamicSmemBytes = smem;
+    config.stream = stream;
+    cudaLaunchAttribute attribute;
+    attribute.id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attribute.val.programmaticStreamSerializationAllowed = 1;
+    config.attrs = &attribute;
+    config.numAttrs = pdl ? 1 : 0;
+    GF_CUDA(cudaLaunchKernelEx(&config, kernel, args...));
+    return GF_OK;
+}
+
+}  // namespace gf

@@ -121,4 +121,27 @@ int gf_stream_destroy(void* stream) { GF_CUDA(cudaStreamDestroy(as_stream(stream
 
 int gf_stream_synchronize(void* stream) { GF_CUDA(cudaStreamSynchronize(as_stream(stream))); return GF_OK; }
 
+int gf_event_create(void** out_event) {
+    if (!out_event) return fail(GF_ERR_INVALID, "gf_event_create: null output");
+    cudaEvent_t event = nullptr;
+    GF_CUDA(cudaEventCreate(&event));
+    *out_event = event;
+    return GF_OK;
+}
+
+int gf_event_destroy(void* event) { GF_CUDA(cudaEventDestroy(static_cast<cudaEvent_t>(event))); return GF_OK; }
+
+int gf_event_record(void* event, void* stream) {
+    GF_CUDA(cudaEventRecord(static_cast<cudaEvent_t>(event), as_stream(stream)));
+    return GF_OK;
+}
+
+int gf_event_synchronize(void* event) { GF_CUDA(cudaEventSynchronize(static_cast<cudaEvent_t>(event))); return GF_OK; }
+
+int gf_event_elapsed_ms(void* start, void* end, float* out_ms) {
+    if (!out_ms) return fail(GF_ERR_INVALID, "gf_event_elapsed_ms: null output");
+    GF_CUDA(cudaEventElapsedTime(out_ms, static_cast<cudaEvent_t>(start), static_cast<cudaEvent_t>(end)));
+    return GF_OK;
+}
+
 }  // extern "C"

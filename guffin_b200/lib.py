@@ -60,6 +60,11 @@ def _declare(L: C.CDLL) -> None:
         "gf_stream_create": [C.POINTER(vp)],
         "gf_stream_destroy": [vp],
         "gf_stream_synchronize": [vp],
+        "gf_event_create": [C.POINTER(vp)],
+        "gf_event_destroy": [vp],
+        "gf_event_record": [vp, vp],
+        "gf_event_synchronize": [vp],
+        "gf_event_elapsed_ms": [vp, vp, C.POINTER(C.c_float)],
         "gf_pack_weight": [i32, vp, u64, u64, vp, vp],
         "gf_unpack_weight": [i32, vp, u64, u64, vp, vp],
         "gf_dequantize": [i32, vp, u64, vp, vp],
@@ -75,15 +80,24 @@ def _declare(L: C.CDLL) -> None:
     L.gf_packed_weight_bytes.restype = sz
     L.gf_matmul_workspace_bytes.argtypes = [i32, u32, u64, u64]
     L.gf_matmul_workspace_bytes.restype = sz
-    for name, (res, args) in OPTIONAL_SIGNATURES.items():
-        if hasattr(L, name):
-            fn = getattr(L, name)
-            fn.argtypes = args
-            fn.restype = res
+    _apply(L, SIGNATURES)
 
 
-# Filled by the higher-level modules (ops, engine) so that one loader declares everything.
-OPTIONAL_SIGNATURES: dict = {}
+def _apply(L: C.CDLL, signatures: dict) -> None:
+    for name, (res, args) in signatures.items():
+        fn = getattr(L, name)
+        fn.argtypes = args
+        fn.restype = res
+
+
+# Signatures registered by the higher-level modules (model, engine).
+SIGNATURES: dict = {}
+
+
+def register(signatures: dict) -> None:
+    SIGNATURES.update(signatures)
+    if _lib is not None:
+        _apply(_lib, signatures)
 
 
 def check(status: int) -> None:
@@ -95,6 +109,26 @@ def device_count() -> int:
     n = C.c_int(0)
     status = load().gf_device_count(C.byref(n))
     return n.value if status == GF_OK else 0
+
+
+class Event:
+    """A device timestamp on a stream (gf_event_*)."""
+
+    def __init__(self):
+        ptr = C.c_void_p()
+        check(load().gf_event_create(C.byref(ptr)))
+        self.ptr = ptr.value
+
+    def record(self, stream=None):
+        check(load().gf_event_record(self.ptr, stream))
+
+    def synchronize(self):
+        check(load().gf_event_synchronize(self.ptr))
+
+    def elapsed_ms(self, end: "Event") -> float:
+        ms = C.c_float()
+        check(load().gf_event_elapsed_ms(self.ptr, end.ptr, C.byref(ms)))
+        return ms.value
 
 
 class DeviceBuffer:

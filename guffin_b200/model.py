@@ -1,0 +1,197 @@
+"""ctypes view of the resident model plan (gf_model_*) and of operator-level entry points."""
+from __future__ import annotations
+
+import ctypes as C
+
+import numpy as np
+
+from . import lib
+from .lib import check, load
+
+vp, u32, u64, i32, sz, f32 = C.c_void_p, C.c_uint32, C.c_uint64, C.c_int, C.c_size_t, C.c_float
+
+
+class ModelConfig(C.Structure):
+    _fields_ = [(n, u32) for n in ("hidden", "ffn", "heads", "kv_heads", "head_dim", "layers", "vocab",
+                                   "sliding_window", "sliding_pattern")] + \
+               [(n, f32) for n in ("rope_base_global", "rope_scale_global", "rope_base_local", "rope_scale_local",
+                                   "rms_eps", "attn_softcap", "final_softcap")] + \
+               [("uses_qk_norm", C.c_int32), ("kv_f16", C.c_int32), ("attention_scale", f32),
+                ("context", u32), ("row_capacity", u32)]
+
+
+class SelectionRequest(C.Structure):
+    _fields_ = [("retain", u32), ("history_count", u32), ("history", u32 * 64)]
+
+
+class CandidateResult(C.Structure):
+    class _Pair(C.Structure):
+        _fields_ = [("token", u32), ("logit", f32)]
+    _fields_ = [("status", u32), ("count", u32), ("candidates", _Pair * 384)]
+
+    def pairs(self):
+        out = np.zeros(self.count, np.dtype([("token", np.uint32), ("logit", np.float32)]))
+        for i in range(self.count):
+            out[i] = (self.candidates[i].token, self.candidates[i].logit)
+        return out
+
+
+lib.register({
+    "gf_embedding": (i32, [i32, vp, u32, u32, vp, u32, f32, vp, vp, vp]),
+    "gf_rms_norm": (i32, [vp, vp, vp, u32, u32, f32, vp]),
+    "gf_rms_norm_add": (i32, [vp, vp, vp, vp, u32, u32, f32, vp]),
+    "gf_qk_norm_rope_store": (i32, [vp, vp, vp, vp, vp, vp, vp, vp, vp, vp, u32, u32, u32, u32, f32, f32, f32, i32, vp]),
+    "gf_attention_workspace_bytes": (sz, [u32, u32]),
+    "gf_attention": (i32, [vp, vp, vp, vp, vp, vp, vp, vp, u32, u32, u32, u32, u32, u32, f32, f32, i32, vp]),
+    "gf_gelu_tanh_multiply": (i32, [vp, vp, vp, u64, vp]),
+    "gf_kv_scatter": (i32, [vp, vp, vp, vp, vp, u32, u32, u32, i32, vp]),
+    "gf_selection_request_bytes": (sz, []),
+    "gf_candidate_result_bytes": (sz, []),
+    "gf_token_candidates_workspace_bytes": (sz, [u32, u32]),
+    "gf_token_candidates": (i32, [vp, u32, u32, f32, vp, vp, vp, vp]),
+    "gf_model_create": (i32, [C.POINTER(ModelConfig), C.POINTER(vp)]),
+    "gf_model_destroy": (i32, [vp]),
+    "gf_model_set_matrix": (i32, [vp, i32, u32, i32, vp, u64, u64]),
+    "gf_model_set_vector": (i32, [vp, i32, u32, vp, u32]),
+    "gf_model_finalize": (i32, [vp]),
+    "gf_model_reset": (i32, [vp]),
+    "gf_model_position": (i32, [vp, C.POINTER(u32)]),
+    "gf_model_forward": (i32, [vp, vp, u32, u32]),
+    "gf_model_publish": (i32, [vp, u32]),
+    "gf_model_prefill": (i32, [vp, vp, u32]),
+    "gf_model_truncate": (i32, [vp, u32]),
+    "gf_model_select": (i32, [vp, vp, u32]),
+    "gf_model_read_candidates": (i32, [vp, vp, u32]),
+    "gf_model_read_logits": (i32, [vp, u32, vp]),
+    "gf_model_synchronize": (i32, [vp]),
+    "gf_model_status": (i32, [vp, C.POINTER(u32)]),
+    "gf_model_stream": (vp, [vp]),
+    "gf_model_tokens_dev": (vp, [vp]),
+    "gf_model_logits_dev": (vp, [vp]),
+    "gf_model_weight_bytes": (sz, [vp, i32]),
+    "gf_model_kv_bytes_per_pass": (sz, [vp, u32]),
+    "gf_model_kernel_launches": (u32, [vp]),
+    "gf_model_use_graph": (i32, [vp, i32]),
+})
+
+MATRIX_KINDS = {"token_embd": 0, "output": 1, "attn_q": 2, "attn_k": 3, "attn_v": 4, "attn_output": 5,
+                "ffn_gate": 6, "ffn_up": 7, "ffn_down": 8}
+VECTOR_KINDS = {"output_norm": 0, "attn_norm": 1, "post_attention_norm": 2, "ffn_norm": 3, "post_ffw_norm": 4,
+                "attn_q_norm": 5, "attn_k_norm": 6}
+FORWARD_LOGITS, FORWARD_DEVICE_TOKENS = 1, 2
+
+
+def make_config(config: dict, context: int, row_capacity: int = 2) -> ModelConfig:
+    cfg = ModelConfig()
+    for name, _ in ModelConfig._fields_:
+        if name in config:
+            setattr(cfg, name, config[name])
+    cfg.context, cfg.row_capacity = context, row_capacity
+    return cfg
+
+
+def selection_request(retain: int, history=()) -> SelectionRequest:
+    request = SelectionRequest()
+    request.retain = retain
+    request.history_count = len(history)
+    for i, token in enumerate(history):
+        request.history[i] = int(token)
+    return request
+
+
+class Model:
+    """A resident Gemma plan on the current device.  `weights` is the dict produced by
+    guffin_b200.synthetic.make_model_weights (GGUF tensor names)."""
+
+    def __init__(self, config: dict, weights: dict, context: int, row_capacity: int = 2):
+        self.L = load()
+        self.config = dict(config)
+        self.cfg = make_config(config, context, row_capacity)
+        handle = vp()
+        check(self.L.gf_model_create(C.byref(self.cfg), C.byref(handle)))
+        self.handle = handle.value
+        for name, value in weights.items():
+            parts = name.split(".")
+            layer, short = (int(parts[1]), parts[2]) if parts[0] == "blk" else (0, parts[0])
+            if isinstance(value, tuple):
+                dtype, k, n, data = value
+                data = np.ascontiguousarray(data, np.uint8)
+                check(self.L.gf_model_set_matrix(self.handle, MATRIX_KINDS[short], layer, dtype, data.ctypes.data, k, n))
+            else:
+                data = np.ascontiguousarray(value, np.float32)
+                check(self.L.gf_model_set_vector(self.handle, VECTOR_KINDS[short], layer, data.ctypes.data, data.size))
+        check(self.L.gf_model_finalize(self.handle))
+
+    @property
+    def position(self) -> int:
+        out = u32()
+        check(self.L.gf_model_position(self.handle, C.byref(out)))
+        return out.value
+
+    def forward(self, tokens, logits: bool = True) -> None:
+        tokens = np.ascontiguousarray(tokens, np.uint32)
+        check(self.L.gf_model_forward(self.handle, tokens.ctypes.data, tokens.size, FORWARD_LOGITS if logits else 0))
+
+    def forward_device_tokens(self, rows: int, logits: bool = True) -> None:
+        check(self.L.gf_model_forward(self.handle, None, rows, (FORWARD_LOGITS if logits else 0) | FORWARD_DEVICE_TOKENS))
+
+    def publish(self, rows: int) -> None:
+        check(self.L.gf_model_publish(self.handle, rows))
+
+    def prefill(self, tokens) -> None:
+        tokens = np.ascontiguousarray(tokens, np.uint32)
+        check(self.L.gf_model_prefill(self.handle, tokens.ctypes.data, tokens.size))
+
+    def truncate(self, position: int) -> None:
+        check(self.L.gf_model_truncate(self.handle, position))
+
+    def reset(self) -> None:
+        check(self.L.gf_model_reset(self.handle))
+
+    def logits(self, row: int = 0) -> np.ndarray:
+        out = np.empty(self.cfg.vocab, np.float32)
+        check(self.L.gf_model_read_logits(self.handle, row, out.ctypes.data))
+        return out
+
+    def select(self, requests) -> list:
+        rows = len(requests)
+        array = (SelectionRequest * rows)(*requests)
+        check(self.L.gf_model_select(self.handle, C.byref(array), rows))
+        results = (CandidateResult * rows)()
+        check(self.L.gf_model_read_candidates(self.handle, C.byref(results), rows))
+        return list(results)
+
+    def synchronize(self) -> None:
+        check(self.L.gf_model_synchronize(self.handle))
+
+    def status(self) -> int:
+        out = u32()
+        check(self.L.gf_model_status(self.handle, C.byref(out)))
+        return out.value
+
+    def use_graph(self, enable: bool) -> None:
+        check(self.L.gf_model_use_graph(self.handle, int(enable)))
+
+    @property
+    def stream(self):
+        return self.L.gf_model_stream(self.handle)
+
+    def weight_bytes(self, native: bool = True) -> int:
+        return self.L.gf_model_weight_bytes(self.handle, int(native))
+
+    def kv_bytes_per_pass(self, rows: int) -> int:
+        return self.L.gf_model_kv_bytes_per_pass(self.handle, rows)
+
+    def kernel_launches(self) -> int:
+        return self.L.gf_model_kernel_launches(self.handle)
+
+    def close(self) -> None:
+        if getattr(self, "handle", None):
+            self.L.gf_model_destroy(self.handle)
+            self.handle = None
+
+    def __del__(self):
+        try:
+            self.close()
+        except Exception:
+            pass

@@ -57,6 +57,13 @@ GF_API int gf_copy(void* dst_dev, const void* src_dev, size_t bytes, void* strea
 GF_API int gf_stream_create(void** out_stream);
 GF_API int gf_stream_destroy(void* stream);
 GF_API int gf_stream_synchronize(void* stream);     /* MetalCommandContext::wait_until_completed */
+/* Device timestamps on a stream: the gpu_duration_ns of MetalCommandStats
+ * (metal_command_context.hpp:19-45) comes from a pair of these. */
+GF_API int gf_event_create(void** out_event);
+GF_API int gf_event_destroy(void* event);
+GF_API int gf_event_record(void* event, void* stream);
+GF_API int gf_event_synchronize(void* event);
+GF_API int gf_event_elapsed_ms(void* start_event, void* end_event, float* out_ms);
 
 /* ---- weight preparation: replaces repack_kquant_weight_columns8 / restore_native_kquant_weight
  * (src/tensor/kquant_packing.cpp:154,250).  The streaming layout keeps every bit of the native
@@ -92,6 +99,137 @@ GF_API int gf_matmul_check(void* stream);
  * `packed_dev` stays device-resident (weights are uploaded once at load time). */
 GF_API int gf_matmul_host(int dtype, const void* packed_dev, const float* x_host, float* y_host,
                           uint32_t rows, uint64_t k, uint64_t n);
+
+/* ---- block-schedule operators.  Per-pass scalars (the committed position) are read from
+ * device memory, so one captured CUDA graph serves every token. ---- */
+
+/* MetalCommandContext::encode_embedding (metal_command_context.hpp:75-82; kernels
+ * metal_kernels.mm:235-255,452-474): gathers rows of the packed [K, vocab] matrix, dequantises
+ * with the reference's rounding and multiplies by `scale` (sqrt(hidden)).  A token id >= vocab
+ * sets status bit 1 and yields NaN for that row. */
+GF_API int gf_embedding(int dtype, const void* packed_dev, uint32_t k, uint32_t vocab,
+                        const uint32_t* tokens_dev, uint32_t rows, float scale, float* out_dev,
+                        uint32_t* status_dev, void* stream);
+/* encode_rms_norm / encode_rms_norm_add (metal_command_context.hpp:131-147; CPU reference
+ * ops/normalization.cpp:70): out = x * rsqrt(mean(x^2) + eps) * gamma [+ residual]. */
+GF_API int gf_rms_norm(const float* x_dev, const float* gamma_dev, float* out_dev, uint32_t rows,
+                       uint32_t hidden, float eps, void* stream);
+GF_API int gf_rms_norm_add(const float* x_dev, const float* gamma_dev, const float* residual_dev,
+                           float* out_dev, uint32_t rows, uint32_t hidden, float eps, void* stream);
+/* encode_head_rms_norm + encode_verifier_rope + encode_verifier_kv_store fused
+ * (metal_command_context.hpp:121-130,215-241): per-head RMSNorm of Q and K (skipped when the
+ * norm pointers are NULL), NEOX rotation at position base+row with
+ * angle = position * freq_scale / freq_base^(2i/d), Q written as f32, K and V written to the
+ * pass's private rows as F16 (round to nearest even) or F32.  Non-finite F16 sets status bit 8. */
+GF_API int gf_qk_norm_rope_store(const float* raw_q_dev, const float* raw_k_dev, const float* raw_v_dev,
+                                 const float* q_norm_dev, const float* k_norm_dev, float* q_out_dev,
+                                 void* private_k_dev, void* private_v_dev,
+                                 const uint32_t* base_position_dev, uint32_t* status_dev, uint32_t rows,
+                                 uint32_t heads, uint32_t kv_heads, uint32_t head_dim, float eps,
+                                 float freq_base, float freq_scale, int kv_f16, void* stream);
+/* encode_verifier_attention (metal_command_context.hpp:245-268; kernels
+ * metal_kernels.mm:3070-3382): grouped-query attention of rows 0..rows-1 at positions base+row
+ * over the committed ring rows inside each row's window followed by the private rows of its
+ * chain ancestors, itself included.  window = 0 means a global layer.  head_dim must be 256. */
+GF_API size_t gf_attention_workspace_bytes(uint32_t rows, uint32_t heads);
+GF_API int gf_attention(const float* q_dev, const void* ring_k_dev, const void* ring_v_dev,
+                        const void* private_k_dev, const void* private_v_dev, float* out_dev,
+                        void* workspace_dev, const uint32_t* base_position_dev, uint32_t rows,
+                        uint32_t heads, uint32_t kv_heads, uint32_t head_dim, uint32_t ring_rows,
+                        uint32_t window, float scale, float softcap, int kv_f16, void* stream);
+/* encode_gelu_tanh_multiply (metal_command_context.hpp:289-295; ops/elementwise.cpp:79). */
+GF_API int gf_gelu_tanh_multiply(const float* gate_dev, const float* up_dev, float* out_dev,
+                                 uint64_t count, void* stream);
+/* encode_verifier_kv_scatter (metal_command_context.hpp:269-279): publishes private rows
+ * 0..rows-1 to ring slots (base + row) & (ring_rows - 1). */
+GF_API int gf_kv_scatter(const void* private_k_dev, const void* private_v_dev, void* ring_k_dev,
+                         void* ring_v_dev, const uint32_t* base_position_dev, uint32_t rows,
+                         uint32_t row_width, uint32_t ring_rows, int kv_f16, void* stream);
+
+/* ---- candidate selection: encode_target_token_candidates / read_target_token_candidates
+ * (metal_command_context.hpp:316-323,351-355; kernels metal_kernels.mm:3444-3884).
+ * Per row: optional final softcap c*tanh(l/c), the best `retain` = top_k + unique-history pairs
+ * by (logit descending, token ascending), then the history tokens' logits.
+ * Request row (device): { u32 retain; u32 history_count; u32 history[64] }.
+ * Result row  (device): { u32 status; u32 count; { u32 token; f32 logit }[384] }. ---- */
+GF_API size_t gf_selection_request_bytes(void);
+GF_API size_t gf_candidate_result_bytes(void);
+GF_API size_t gf_token_candidates_workspace_bytes(uint32_t rows, uint32_t vocab);
+GF_API int gf_token_candidates(const float* logits_dev, uint32_t rows, uint32_t vocab, float softcap,
+                               const void* requests_dev, void* workspace_dev, void* results_dev,
+                               void* stream);
+
+/* ---- resident model plan: replaces Gemma2MetalModelPlan + its verifier arena
+ * (include/local_gguf_engine/engine/gemma2_metal_plan.hpp:229-319, target_verifier.hpp:228-257)
+ * and the block schedule encode_gemma_target_blocks (src/engine/gemma_target_runtime.cpp:13-221).
+ * The same plan type serves the 12B target, the Gemma 2 target and the 270M drafter. ---- */
+typedef struct gf_model gf_model;
+
+typedef struct gf_model_config {         /* the GemmaModelConfig fields the path uses (engine/model.hpp:52-86) */
+    uint32_t hidden, ffn, heads, kv_heads, head_dim, layers, vocab;
+    uint32_t sliding_window;
+    uint32_t sliding_pattern;            /* 6: local iff (layer+1)%6 != 0; 2: local iff layer%2 == 0; 0: all global */
+    float rope_base_global, rope_scale_global, rope_base_local, rope_scale_local;
+    float rms_eps, attn_softcap, final_softcap;
+    int32_t uses_qk_norm;
+    int32_t kv_f16;                      /* 1: K/V cached as binary16 (round to nearest even), 0: f32 */
+    float attention_scale;
+    uint32_t context;                    /* positions the caches are sized for */
+    uint32_t row_capacity;               /* rows per pass, 1..GF_MAX_ROWS (2 = H1 verification) */
+} gf_model_config;
+
+enum { GF_MAT_TOKEN_EMBD = 0, GF_MAT_OUTPUT = 1, GF_MAT_ATTN_Q = 2, GF_MAT_ATTN_K = 3, GF_MAT_ATTN_V = 4,
+       GF_MAT_ATTN_OUTPUT = 5, GF_MAT_FFN_GATE = 6, GF_MAT_FFN_UP = 7, GF_MAT_FFN_DOWN = 8 };
+enum { GF_VEC_OUTPUT_NORM = 0, GF_VEC_ATTN_NORM = 1, GF_VEC_POST_ATTENTION_NORM = 2, GF_VEC_FFN_NORM = 3,
+       GF_VEC_POST_FFW_NORM = 4, GF_VEC_ATTN_Q_NORM = 5, GF_VEC_ATTN_K_NORM = 6 };
+enum { GF_FORWARD_LOGITS = 1, GF_FORWARD_DEVICE_TOKENS = 2 };
+
+GF_API int gf_model_create(const gf_model_config* config, gf_model** out_model);
+GF_API int gf_model_destroy(gf_model* model);
+/* Uploads one native GGUF tensor and repacks it on the device (WeightMaterializer,
+ * gemma2_metal_plan.cpp:266-336).  GF_MAT_OUTPUT is optional: without it the head is tied to
+ * the token embedding (resolve_gemma_output_head_policy, gemma2_metal_plan.cpp:799-828). */
+GF_API int gf_model_set_matrix(gf_model* model, int kind, uint32_t layer, int dtype,
+                               const void* native_host, uint64_t k, uint64_t n);
+GF_API int gf_model_set_vector(gf_model* model, int kind, uint32_t layer, const float* values_host,
+                               uint32_t count);
+/* Checks every tensor is bound and allocates KV rings, private rows and scratch
+ * (allocate_kv_cache, gemma2_metal_plan.cpp:514-537). */
+GF_API int gf_model_finalize(gf_model* model);
+GF_API int gf_model_reset(gf_model* model);
+GF_API int gf_model_position(const gf_model* model, uint32_t* out_position);
+/* One pass over `rows` chained tokens at positions position..position+rows-1
+ * (run_gemma3_resident_decode / run_gemma_target_width_two_verifier,
+ * gemma_target_runtime.cpp:390,457): K/V go to private rows, nothing is published.
+ * flags: GF_FORWARD_LOGITS computes the final norm and the output head for every row;
+ * GF_FORWARD_DEVICE_TOKENS takes the ids already stored in gf_model_tokens_dev().
+ * Asynchronous on the model's stream. */
+GF_API int gf_model_forward(gf_model* model, const uint32_t* tokens_host, uint32_t rows, uint32_t flags);
+/* Publishes private rows 0..rows-1 into the rings and advances the position
+ * (publish_contiguous_rows, gemma_target_runtime.cpp:273; provisional commit,
+ * target_verifier_runtime.cpp:535).  Rows left unpublished are the rollback. */
+GF_API int gf_model_publish(gf_model* model, uint32_t rows);
+/* Chunked prompt ingestion through the row path (run_gemma3_resident_prefill semantics,
+ * gemma_target_runtime.cpp:420); logits are produced for the last token only. */
+GF_API int gf_model_prefill(gf_model* model, const uint32_t* tokens_host, uint32_t count);
+GF_API int gf_model_truncate(gf_model* model, uint32_t position);
+/* Candidate selection over the last pass's logits; requests_host holds `rows` request rows
+ * (gf_selection_request_bytes each).  gf_model_read_candidates synchronises and copies
+ * `rows` result rows (gf_candidate_result_bytes each) (read_target_token_candidates). */
+GF_API int gf_model_select(gf_model* model, const void* requests_host, uint32_t rows);
+GF_API int gf_model_read_candidates(gf_model* model, void* results_host, uint32_t rows);
+GF_API int gf_model_read_logits(gf_model* model, uint32_t row, float* logits_host);
+GF_API int gf_model_synchronize(gf_model* model);
+/* Synchronises and returns the validation word (bit 1 bad token id, bit 2 bad request,
+ * bit 8 non-finite F16 K/V; read_verifier_status) and GF_ERR_TIMEOUT / GF_ERR_NUMERIC. */
+GF_API int gf_model_status(gf_model* model, uint32_t* out_status);
+GF_API void* gf_model_stream(gf_model* model);
+GF_API uint32_t* gf_model_tokens_dev(gf_model* model);
+GF_API float* gf_model_logits_dev(gf_model* model);
+GF_API size_t gf_model_weight_bytes(const gf_model* model, int native);
+GF_API size_t gf_model_kv_bytes_per_pass(const gf_model* model, uint32_t rows);
+GF_API uint32_t gf_model_kernel_launches(const gf_model* model);
+GF_API int gf_model_use_graph(gf_model* model, int enable);
 
 #ifdef __cplusplus
 }

@@ -1,0 +1,44 @@
+"""CPU checks on the C-ABI boundary: the library loads and exports every declared symbol, and
+argument validation fails with the documented status before any GPU work."""
+import ctypes
+import re
+
+from guffin_b200 import lib
+
+
+def declared_symbols():
+    text = open(lib.HEADER_PATH).read()
+    return sorted(set(re.findall(r"GF_API\s+[\w\s\*]+?\b(gf_\w+)\s*\(", text)))
+
+
+def test_library_exports_every_declared_symbol():
+    L = lib.load()
+    names = declared_symbols()
+    assert len(names) >= 20
+    for name in names:
+        assert hasattr(L, name), f"{name} is declared in include/guffin_b200.h but not exported"
+
+
+def test_version_and_error_text():
+    L = lib.load()
+    assert b"sm_100a" in L.gf_version()
+    assert L.gf_packed_weight_bytes(12, 100, 8) == 0          # K not a multiple of 256
+    assert b"multiple" in L.gf_last_error()
+
+
+def test_packed_sizes_keep_native_byte_count():
+    L = lib.load()
+    # 8 columns x one unit: exactly the native bytes, no padding
+    assert L.gf_packed_weight_bytes(lib.Q4_K, 3840, 15360) == 15360 * 15 * 144
+    assert L.gf_packed_weight_bytes(lib.Q6_K, 15360, 3840) == 3840 * 60 * 210
+    assert L.gf_packed_weight_bytes(lib.Q8_0, 640, 262144) == 262144 * 20 * 34
+    # a ragged last tile is zero-padded to 8 columns
+    assert L.gf_packed_weight_bytes(lib.Q4_K, 256, 9) == 2 * 1152
+
+
+def test_matmul_rejects_bad_arguments_without_a_gpu():
+    L = lib.load()
+    assert L.gf_matmul_workspace_bytes(lib.Q4_K, 9, 3840, 15360) == 0      # rows > GF_MAX_ROWS
+    assert L.gf_matmul_workspace_bytes(7, 1, 3840, 15360) == 0             # unknown dtype
+    assert L.gf_matmul(lib.Q4_K, None, None, None, 0, 3840, 15360, None, None) == lib.GF_ERR_INVALID
+    assert L.gf_matmul(lib.Q4_K, None, None, None, 1, 100, 15360, None, None) == lib.GF_ERR_INVALID
