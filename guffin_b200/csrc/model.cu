@@ -33,6 +33,8 @@ Model::~Model() {
         for (auto& graph : per_rows)
             if (graph) cudaGraphExecDestroy(graph);
     for (void* p : allocations_) cudaFree(p);
+    if (tokens_copied_) cudaEventDestroy(tokens_copied_);
+    if (requests_copied_) cudaEventDestroy(requests_copied_);
     if (tokens_pinned_) cudaFreeHost(tokens_pinned_);
     if (requests_pinned_) cudaFreeHost(requests_pinned_);
     if (stream_) cudaStreamDestroy(stream_);
@@ -189,6 +191,8 @@ int Model::finalize() {
     GF_CUDA(cudaMemsetAsync(error_flag_, 0, 16, stream_));
     GF_CUDA(cudaHostAlloc(reinterpret_cast<void**>(&tokens_pinned_), GF_MAX_ROWS * sizeof(uint32_t), cudaHostAllocDefault));
     GF_CUDA(cudaHostAlloc(&requests_pinned_, (size_t)R * gf_selection_request_bytes(), cudaHostAllocDefault));
+    GF_CUDA(cudaEventCreateWithFlags(&tokens_copied_, cudaEventDisableTiming));
+    GF_CUDA(cudaEventCreateWithFlags(&requests_copied_, cudaEventDisableTiming));
     GF_CUDA(cudaStreamSynchronize(stream_));
     finalized_ = true;
     position_ = 0;
@@ -289,10 +293,11 @@ int Model::forward(const uint32_t* tokens_host, uint32_t rows, uint32_t flags) {
         if (!tokens_host) return fail(GF_ERR_INVALID, "null token ids");
         for (uint32_t r = 0; r < rows; ++r)
             if (tokens_host[r] >= config_.vocab) return fail(GF_ERR_INVALID, "token id %u outside the vocabulary", tokens_host[r]);
-        // The previous pass may still be reading the pinned staging word: order the rewrite after it.
-        GF_CUDA(cudaStreamSynchronize(stream_));
+        // The previous upload may still be reading the pinned staging words: wait for that copy only.
+        GF_CUDA(cudaEventSynchronize(tokens_copied_));
         std::memcpy(tokens_pinned_, tokens_host, rows * sizeof(uint32_t));
         GF_CUDA(cudaMemcpyAsync(tokens_dev_, tokens_pinned_, rows * sizeof(uint32_t), cudaMemcpyHostToDevice, stream_));
+        GF_CUDA(cudaEventRecord(tokens_copied_, stream_));
     }
     return run_graph_or_encode(rows, flags);
 }
@@ -339,6 +344,15 @@ int Model::prefill(const uint32_t* tokens_host, uint32_t count) {
     return GF_OK;
 }
 
+int Model::set_device_token(uint32_t row, uint32_t token) {
+    if (row >= GF_MAX_ROWS || token >= config_.vocab) return fail(GF_ERR_INVALID, "bad device token slot or id");
+    GF_CUDA(cudaEventSynchronize(tokens_copied_));
+    tokens_pinned_[row] = token;
+    GF_CUDA(cudaMemcpyAsync(tokens_dev_ + row, tokens_pinned_ + row, sizeof(uint32_t), cudaMemcpyHostToDevice, stream_));
+    GF_CUDA(cudaEventRecord(tokens_copied_, stream_));
+    return GF_OK;
+}
+
 int Model::select_device(uint32_t rows) {
     launches_ += 2;
     return launch_candidates(logits_, rows, config_.vocab, config_.final_softcap, requests_dev_, candidates_ws_, results_dev_,
@@ -349,9 +363,10 @@ int Model::select(const void* requests_host, uint32_t rows) {
     if (!finalized_) return fail(GF_ERR_STATE, "plan is not finalized");
     if (!requests_host || rows == 0 || rows > config_.row_capacity) return fail(GF_ERR_INVALID, "bad selection request");
     const size_t bytes = (size_t)rows * gf_selection_request_bytes();
-    GF_CUDA(cudaStreamSynchronize(stream_));
+    GF_CUDA(cudaEventSynchronize(requests_copied_));
     std::memcpy(requests_pinned_, requests_host, bytes);
     GF_CUDA(cudaMemcpyAsync(requests_dev_, requests_pinned_, bytes, cudaMemcpyHostToDevice, stream_));
+    GF_CUDA(cudaEventRecord(requests_copied_, stream_));
     return select_device(rows);
 }
 
@@ -398,8 +413,6 @@ size_t Model::kv_bytes_per_pass(uint32_t rows) const {
 }  // namespace gf
 
 using namespace gf;
-
-struct gf_model { Model impl; explicit gf_model(const gf_model_config& c) : impl(c) {} };
 
 extern "C" {
 

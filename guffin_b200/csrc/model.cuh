@@ -76,6 +76,8 @@ public:
 
     // Enqueues the selection for rows whose requests already sit in requests_dev().
     int select_device(uint32_t rows);
+    // Uploads one token id into the device token buffer slot `row` (asynchronous).
+    int set_device_token(uint32_t row, uint32_t token);
 
 private:
     int encode_blocks(uint32_t rows, uint32_t flags);
@@ -107,6 +109,13 @@ private:
     uint32_t position_ = 0;
     uint32_t launches_ = 0;
     cudaGraphExec_t graphs_[GF_MAX_ROWS + 1][2] = {};
+    cudaEvent_t tokens_copied_ = nullptr, requests_copied_ = nullptr;
 };
 
 }  // namespace gf
+
+// The opaque handle of the C ABI.
+struct gf_model {
+    gf::Model impl;
+    explicit gf_model(const gf_model_config& c) : impl(c) {}
+};

@@ -21,7 +21,7 @@ BLOCK_BYTES = {Q8_0: 34, Q4_K: 144, Q6_K: 210}
 
 def _positive_f16(rng: np.random.Generator, count: int, sigma: float) -> np.ndarray:
     values = np.abs(rng.normal(0.0, sigma, count)).astype(np.float16)
-    values[values == 0] = np.float16(sigma)
+    values[values == 0] = max(np.float16(sigma), np.float16(6e-8))
     return values.view(np.uint8).reshape(count, 2)
 
 
@@ -145,10 +145,18 @@ def make_model_weights(name: str, seed: int, config: dict | None = None) -> dict
     def gamma(n):
         return (1.0 + 0.1 * rng.standard_normal(n)).astype(np.float32)
 
-    weights["token_embd.weight"] = (types["token_embd.weight"], H, V,
-                                    make_weight(rng, types["token_embd.weight"], H, V))
+    # Embedding / head blocks are scaled so that an embedded token has unit RMS after the
+    # sqrt(hidden) factor, as trained checkpoints roughly do; otherwise a random tied model just
+    # echoes its input token and every proposal is trivially accepted.
+    def table_sigma(dtype):
+        code_rms = {Q6_K: 685.0, Q8_0: 73.3, Q4_K: 300.0}[dtype]
+        return 1.0 / (code_rms * math.sqrt(H))
+
+    embd_type = types["token_embd.weight"]
+    weights["token_embd.weight"] = (embd_type, H, V, make_weight(rng, embd_type, H, V, table_sigma(embd_type)))
     if "output.weight" in types:
-        weights["output.weight"] = (types["output.weight"], H, V, make_weight(rng, types["output.weight"], H, V))
+        head_type = types["output.weight"]
+        weights["output.weight"] = (head_type, H, V, make_weight(rng, head_type, H, V, table_sigma(head_type)))
     weights["output_norm.weight"] = gamma(H)
     for l in range(config["layers"]):
         for t, (k, n) in shapes.items():

@@ -231,6 +231,95 @@ GF_API size_t gf_model_kv_bytes_per_pass(const gf_model* model, uint32_t rows);
 GF_API uint32_t gf_model_kernel_launches(const gf_model* model);
 GF_API int gf_model_use_graph(gf_model* model, int enable);
 
+/* ---- drafter proposal law: the device sampler of Gemma3DraftPlan::propose and the receipts
+ * Gemma3DraftPlan::gather reads (src/engine/gemma3_draft.mm:995-1167,1528-1581; kernels :191-294).
+ * Builds the compact law (top_k <= 64): support = every token whose processed score reaches the
+ * top_k-th best, filtered by the ascending-tail top-p rule and min-p, integer CDF of total 2^32
+ * in token-id order; the drafted token is the bin holding `word`.
+ * Receipt (device): { u32 status; u32 count; u32 token; u32 word; u32 ids[256]; u64 cdf[257] }.
+ * status 20 = support larger than 256 (the caller falls back to ordinary decoding). ---- */
+GF_API size_t gf_draft_receipt_bytes(void);
+GF_API size_t gf_draft_sample_workspace_bytes(uint32_t vocab);
+GF_API int gf_draft_sample(const float* logits_dev, uint32_t vocab, float temperature, uint32_t top_k,
+                           float top_p, float min_p, float repetition_penalty,
+                           const uint32_t* history_host, uint32_t history_count, uint32_t word,
+                           void* workspace_dev, void* receipt_dev, uint32_t* out_token_dev, void* stream);
+
+/* ---- host sampler and lossless acceptance: TokenSampler / TokenSamplerFork
+ * (include/local_gguf_engine/engine/sampling.hpp:184-395, src/engine/sampling.cpp).  Double
+ * precision on the host, two mt19937_64 streams; decisions are bit-identical to the reference
+ * for identical candidates, draft masses and seed. ---- */
+typedef struct gf_sampler gf_sampler;
+typedef struct gf_sampler_options {      /* TokenSamplerOptions (sampling.hpp:184-196) */
+    float temperature;
+    uint32_t top_k;
+    float top_p, min_p, repetition_penalty;
+    uint32_t repetition_window;
+    uint64_t seed;
+} gf_sampler_options;
+typedef struct gf_token_logit { uint32_t token; float logit; } gf_token_logit;   /* TokenLogit (sampling.hpp:25-28) */
+typedef struct gf_gathered_draft {       /* GatheredDraftTokenDistribution (sampling.hpp:150-156) */
+    uint32_t proposal;
+    uint32_t count;
+    uint64_t proposal_mass, proposal_cdf_begin;
+    uint64_t target_mass[256];           /* draft mass of the i-th token of the prepared target support */
+} gf_gathered_draft;
+GF_API int gf_sampler_create(const gf_sampler_options* options, gf_sampler** out_sampler);
+GF_API int gf_sampler_destroy(gf_sampler* sampler);
+GF_API int gf_sampler_observe(gf_sampler* sampler, const uint32_t* tokens, uint32_t count);    /* observe_tokens */
+GF_API int gf_sampler_preview_proposal_word(const gf_sampler* sampler, uint32_t* out_word);   /* preview_proposal_words(1) */
+/* prepare_distribution (sampling.cpp:394-499) for the row whose context is the observed history
+ * plus `suffix`: writes the support tokens and their sampling weights. */
+GF_API int gf_sampler_prepare(const gf_sampler* sampler, const gf_token_logit* candidates, uint32_t count,
+                              const uint32_t* suffix, uint32_t suffix_count, uint32_t* out_tokens,
+                              double* out_weights, uint32_t* out_count, double* out_total_weight);
+GF_API int gf_sampler_sample(gf_sampler* sampler, const gf_token_logit* candidates, uint32_t count,
+                             const uint32_t* suffix, uint32_t suffix_count, uint32_t* out_token);   /* TokenSampler::sample */
+/* TokenSamplerFork::sample_speculative with a gathered draft law (sampling.cpp:896-934). */
+GF_API int gf_sampler_sample_speculative(gf_sampler* sampler, const gf_gathered_draft* draft,
+                                         const gf_token_logit* candidates, uint32_t count,
+                                         const uint32_t* suffix, uint32_t suffix_count, uint32_t* out_token,
+                                         int* out_accepted, uint32_t* out_target_draws);
+
+/* ---- the H1 cycle: draft -> verify -> accept / rollback.  Replaces StandaloneChatPlan::run
+ * (src/engine/standalone_chat.cpp:508-615), ChainChatVerifier::run for one 2-row tile
+ * (src/engine/chain_chat.mm:245-543) and the H1 branch of the generation loop
+ * (src/engine/gemma2_runtime.cpp:1630-1699).  One host synchronisation per cycle. ---- */
+typedef struct gf_h1 gf_h1;
+typedef struct gf_h1_options {
+    gf_sampler_options sampler;          /* target sampler; the drafter reuses it (standalone_chat.cpp:11-32) */
+    int32_t speculative;                 /* 0: ordinary decode with the target only */
+    int32_t forced_schedule;             /* 1: accept/reject control flow follows a seeded Bernoulli schedule
+                                            while the real acceptance law still runs and is recorded */
+    float forced_accept_probability;
+    uint64_t schedule_seed;
+    int32_t record_cycles;               /* keep per-cycle acceptance inputs for exactness checks */
+} gf_h1_options;
+typedef struct gf_h1_stats {
+    uint64_t cycles, accepted, rejected, ordinary_steps, fallback_cycles, emitted_tokens;
+    uint64_t law_agreements;             /* cycles whose real decision equals the forced one (forced mode) */
+} gf_h1_stats;
+typedef struct gf_h1_cycle_record {      /* inputs and result of one real acceptance test */
+    uint32_t root, proposal, word, candidate_count;
+    gf_token_logit candidates[384];
+    gf_gathered_draft draft;
+    uint32_t token;
+    int32_t accepted;
+    uint32_t target_draws;
+    int32_t status;
+} gf_h1_cycle_record;
+GF_API int gf_h1_create(gf_model* target, gf_model* draft /* may be NULL when speculative == 0 */,
+                        const gf_h1_options* options, gf_h1** out_engine);
+GF_API int gf_h1_destroy(gf_h1* engine);
+/* Ingests the prompt into both models and samples the first token from the target. */
+GF_API int gf_h1_prefill(gf_h1* engine, const uint32_t* tokens_host, uint32_t count);
+/* Generates until `max_tokens` tokens have been emitted (the first emitted token is the one
+ * sampled by prefill).  Returns the tokens and the number written. */
+GF_API int gf_h1_generate(gf_h1* engine, uint32_t max_tokens, uint32_t* out_tokens, uint32_t* out_count);
+GF_API int gf_h1_stats_read(const gf_h1* engine, gf_h1_stats* out_stats);
+GF_API int gf_h1_cycle_record_read(const gf_h1* engine, uint32_t index, gf_h1_cycle_record* out_record);
+GF_API uint32_t gf_h1_cycle_record_count(const gf_h1* engine);
+
 #ifdef __cplusplus
 }
 #endif
