@@ -119,13 +119,14 @@ public:
         return GF_OK;
     }
 
-    int generate(uint32_t max_tokens, uint32_t* out, uint32_t* out_count) {
+    int generate(uint32_t max_tokens, uint32_t* out, uint32_t* out_count, uint32_t max_steps = 0xffffffffu) {
         if (!has_root_) return fail(GF_ERR_STATE, "generate needs a prefilled prompt");
         if (!out || !out_count) return fail(GF_ERR_INVALID, "null output");
-        uint32_t produced = 0;
+        uint32_t produced = 0, steps = 0;
         auto emit = [&](uint32_t token) { if (produced < max_tokens) out[produced++] = token; ++stats_.emitted_tokens; };
         if (!first_emitted_ && max_tokens) { emit(root_); first_emitted_ = true; }
-        while (produced < max_tokens) {
+        while (produced < max_tokens && steps < max_steps) {
+            ++steps;
             const uint32_t room = target_.config().context - target_.position();
             if (room < 2) break;                                            // context exhausted
             const bool spec = options_.speculative && max_tokens - produced >= 2 && room >= 3
@@ -410,6 +411,9 @@ int gf_h1_prefill(gf_h1* e, const uint32_t* tokens_host, uint32_t count) {
 }
 int gf_h1_generate(gf_h1* e, uint32_t max_tokens, uint32_t* out_tokens, uint32_t* out_count) {
     return e ? e->impl.generate(max_tokens, out_tokens, out_count) : fail(GF_ERR_INVALID, "null engine");
+}
+int gf_h1_generate_steps(gf_h1* e, uint32_t steps, uint32_t max_tokens, uint32_t* out_tokens, uint32_t* out_count) {
+    return e ? e->impl.generate(max_tokens, out_tokens, out_count, steps) : fail(GF_ERR_INVALID, "null engine");
 }
 int gf_h1_stats_read(const gf_h1* e, gf_h1_stats* out_stats) {
     if (!e || !out_stats) return fail(GF_ERR_INVALID, "null argument");

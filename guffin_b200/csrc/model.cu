@@ -344,6 +344,31 @@ int Model::prefill(const uint32_t* tokens_host, uint32_t count) {
     return GF_OK;
 }
 
+int Model::weight_sweep(uint32_t rows, uint32_t* out_launches, uint64_t* out_bytes) {
+    if (!finalized_) return fail(GF_ERR_STATE, "plan is not finalized");
+    if (rows == 0 || rows > config_.row_capacity) return fail(GF_ERR_INVALID, "bad row count");
+    uint32_t launches = 0;
+    uint64_t bytes = 0;
+    auto run = [&](const PackedMatrix& w, const float* x, float* y) {
+        ++launches;
+        bytes += w.native_bytes;
+        return gemv_launch(w.dtype, w.data, x, y, rows, w.k, w.n, matmul_ws_, error_flag_, stream_, true);
+    };
+    for (const LayerWeights& w : layers_) {
+        GF_TRY(run(w.q, normalized_, raw_q_));
+        GF_TRY(run(w.k, normalized_, raw_k_));
+        GF_TRY(run(w.v, normalized_, raw_v_));
+        GF_TRY(run(w.o, attention_out_, projected_));
+        GF_TRY(run(w.gate, normalized_, gate_));
+        GF_TRY(run(w.up, normalized_, up_));
+        GF_TRY(run(w.down, gated_, projected_));
+    }
+    GF_TRY(run(has_head_ ? head_ : token_embd_, normalized_, logits_));
+    if (out_launches) *out_launches = launches;
+    if (out_bytes) *out_bytes = bytes;
+    return GF_OK;
+}
+
 int Model::set_device_token(uint32_t row, uint32_t token) {
     if (row >= GF_MAX_ROWS || token >= config_.vocab) return fail(GF_ERR_INVALID, "bad device token slot or id");
     GF_CUDA(cudaEventSynchronize(tokens_copied_));
@@ -467,6 +492,9 @@ size_t gf_model_weight_bytes(const gf_model* m, int native) {
 }
 size_t gf_model_kv_bytes_per_pass(const gf_model* m, uint32_t rows) { return m ? m->impl.kv_bytes_per_pass(rows) : 0; }
 uint32_t gf_model_kernel_launches(const gf_model* m) { return m ? m->impl.kernel_launches() : 0; }
+int gf_model_weight_sweep(gf_model* m, uint32_t rows, uint32_t* out_launches, uint64_t* out_weight_bytes) {
+    return m ? m->impl.weight_sweep(rows, out_launches, out_weight_bytes) : fail(GF_ERR_INVALID, "null model");
+}
 int gf_model_use_graph(gf_model* m, int enable) {
     if (!m) return fail(GF_ERR_INVALID, "null model");
     m->impl.set_use_graph(enable != 0);

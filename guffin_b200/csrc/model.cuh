@@ -59,6 +59,7 @@ public:
     int status_word(uint32_t* out);
     int prefill(const uint32_t* tokens_host, uint32_t count);
     int truncate(uint32_t position);
+    int weight_sweep(uint32_t rows, uint32_t* out_launches, uint64_t* out_bytes);
 
     const gf_model_config& config() const { return config_; }
     uint32_t position() const { return position_; }

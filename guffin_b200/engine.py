@@ -67,6 +67,7 @@ lib.register({
     "gf_h1_destroy": (i32, [vp]),
     "gf_h1_prefill": (i32, [vp, vp, u32]),
     "gf_h1_generate": (i32, [vp, u32, vp, C.POINTER(u32)]),
+    "gf_h1_generate_steps": (i32, [vp, u32, u32, vp, C.POINTER(u32)]),
     "gf_h1_stats_read": (i32, [vp, C.POINTER(H1Stats)]),
     "gf_h1_cycle_record_read": (i32, [vp, u32, C.POINTER(CycleRecord)]),
     "gf_h1_cycle_record_count": (u32, [vp]),
@@ -174,6 +175,13 @@ class H1:
         out = np.zeros(max_tokens, np.uint32)
         count = u32()
         check(self.L.gf_h1_generate(self.handle, max_tokens, out.ctypes.data, C.byref(count)))
+        return out[:count.value]
+
+    def generate_steps(self, steps: int, max_tokens: int | None = None) -> np.ndarray:
+        max_tokens = max_tokens or 2 * steps + 2
+        out = np.zeros(max_tokens, np.uint32)
+        count = u32()
+        check(self.L.gf_h1_generate_steps(self.handle, steps, max_tokens, out.ctypes.data, C.byref(count)))
         return out[:count.value]
 
     def stats(self) -> H1Stats:

@@ -72,6 +72,7 @@ lib.register({
     "gf_model_kv_bytes_per_pass": (sz, [vp, u32]),
     "gf_model_kernel_launches": (u32, [vp]),
     "gf_model_use_graph": (i32, [vp, i32]),
+    "gf_model_weight_sweep": (i32, [vp, u32, C.POINTER(u32), C.POINTER(u64)]),
 })
 
 MATRIX_KINDS = {"token_embd": 0, "output": 1, "attn_q": 2, "attn_k": 3, "attn_v": 4, "attn_output": 5,
@@ -101,7 +102,8 @@ def selection_request(retain: int, history=()) -> SelectionRequest:
 
 class Model:
     """A resident Gemma plan on the current device.  `weights` is the dict produced by
-    guffin_b200.synthetic.make_model_weights (GGUF tensor names)."""
+    guffin_b200.synthetic.make_model_weights (GGUF tensor names), or any iterable of
+    (name, value) pairs such as synthetic.iter_model_weights."""
 
     def __init__(self, config: dict, weights: dict, context: int, row_capacity: int = 2):
         self.L = load()
@@ -110,7 +112,7 @@ class Model:
         handle = vp()
         check(self.L.gf_model_create(C.byref(self.cfg), C.byref(handle)))
         self.handle = handle.value
-        for name, value in weights.items():
+        for name, value in (weights.items() if hasattr(weights, "items") else weights):
             parts = name.split(".")
             layer, short = (int(parts[1]), parts[2]) if parts[0] == "blk" else (0, parts[0])
             if isinstance(value, tuple):
@@ -168,6 +170,11 @@ class Model:
         out = u32()
         check(self.L.gf_model_status(self.handle, C.byref(out)))
         return out.value
+
+    def weight_sweep(self, rows: int):
+        launches, nbytes = u32(), u64()
+        check(self.L.gf_model_weight_sweep(self.handle, rows, C.byref(launches), C.byref(nbytes)))
+        return launches.value, nbytes.value
 
     def use_graph(self, enable: bool) -> None:
         check(self.L.gf_model_use_graph(self.handle, int(enable)))

@@ -133,13 +133,14 @@ def matrix_shapes(config: dict) -> dict:
             "ffn_gate": (H, F), "ffn_up": (H, F), "ffn_down": (F, H)}
 
 
-def make_model_weights(name: str, seed: int, config: dict | None = None) -> dict:
-    """name -> (dtype, K, N, uint8 payload) for matrices, float32 arrays for norm vectors."""
+def iter_model_weights(name: str, seed: int, config: dict | None = None):
+    """Yields (GGUF tensor name, value) one tensor at a time: value is (dtype, K, N, uint8 payload)
+    for matrices and a float32 array for norm vectors.  Lets a loader upload a 12B model without
+    holding all of it in host memory."""
     config = config or model_config(name)
     rng = np.random.default_rng(seed)
     types = tensor_types(name, config)
     shapes = matrix_shapes(config)
-    weights = {}
     H, V = config["hidden"], config["vocab"]
 
     def gamma(n):
@@ -153,21 +154,25 @@ def make_model_weights(name: str, seed: int, config: dict | None = None) -> dict
         return 1.0 / (code_rms * math.sqrt(H))
 
     embd_type = types["token_embd.weight"]
-    weights["token_embd.weight"] = (embd_type, H, V, make_weight(rng, embd_type, H, V, table_sigma(embd_type)))
+    yield "token_embd.weight", (embd_type, H, V, make_weight(rng, embd_type, H, V, table_sigma(embd_type)))
     if "output.weight" in types:
         head_type = types["output.weight"]
-        weights["output.weight"] = (head_type, H, V, make_weight(rng, head_type, H, V, table_sigma(head_type)))
-    weights["output_norm.weight"] = gamma(H)
+        yield "output.weight", (head_type, H, V, make_weight(rng, head_type, H, V, table_sigma(head_type)))
+    yield "output_norm.weight", gamma(H)
     for l in range(config["layers"]):
         for t, (k, n) in shapes.items():
             key = f"blk.{l}.{t}.weight"
-            weights[key] = (types[key], k, n, make_weight(rng, types[key], k, n))
+            yield key, (types[key], k, n, make_weight(rng, types[key], k, n))
         for t in ("attn_norm", "post_attention_norm", "ffn_norm", "post_ffw_norm"):
-            weights[f"blk.{l}.{t}.weight"] = gamma(H)
+            yield f"blk.{l}.{t}.weight", gamma(H)
         if config["uses_qk_norm"]:
-            weights[f"blk.{l}.attn_q_norm.weight"] = gamma(config["head_dim"])
-            weights[f"blk.{l}.attn_k_norm.weight"] = gamma(config["head_dim"])
-    return weights
+            yield f"blk.{l}.attn_q_norm.weight", gamma(config["head_dim"])
+            yield f"blk.{l}.attn_k_norm.weight", gamma(config["head_dim"])
+
+
+def make_model_weights(name: str, seed: int, config: dict | None = None) -> dict:
+    """All tensors of iter_model_weights in one dict."""
+    return dict(iter_model_weights(name, seed, config))
 
 
 def model_weight_bytes(name: str, config: dict | None = None) -> int:

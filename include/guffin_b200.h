@@ -230,6 +230,12 @@ GF_API size_t gf_model_weight_bytes(const gf_model* model, int native);
 GF_API size_t gf_model_kv_bytes_per_pass(const gf_model* model, uint32_t rows);
 GF_API uint32_t gf_model_kernel_launches(const gf_model* model);
 GF_API int gf_model_use_graph(gf_model* model, int enable);
+/* Enqueues exactly the weight-streaming GEMVs of one `rows`-row pass (every projection of every
+ * layer and the output head, in schedule order) and nothing else: the measurement the
+ * reference's quick benchmark calls "effective weight GB/s"
+ * (include/local_gguf_engine/benchmarks/quick_benchmark.hpp:24-30).  Scratch activations are
+ * reused as inputs; results are not meaningful. */
+GF_API int gf_model_weight_sweep(gf_model* model, uint32_t rows, uint32_t* out_launches, uint64_t* out_weight_bytes);
 
 /* ---- drafter proposal law: the device sampler of Gemma3DraftPlan::propose and the receipts
  * Gemma3DraftPlan::gather reads (src/engine/gemma3_draft.mm:995-1167,1528-1581; kernels :191-294).
@@ -316,6 +322,9 @@ GF_API int gf_h1_prefill(gf_h1* engine, const uint32_t* tokens_host, uint32_t co
 /* Generates until `max_tokens` tokens have been emitted (the first emitted token is the one
  * sampled by prefill).  Returns the tokens and the number written. */
 GF_API int gf_h1_generate(gf_h1* engine, uint32_t max_tokens, uint32_t* out_tokens, uint32_t* out_count);
+/* Same, but stops after `steps` cycles (or ordinary steps) as well. */
+GF_API int gf_h1_generate_steps(gf_h1* engine, uint32_t steps, uint32_t max_tokens, uint32_t* out_tokens,
+                                uint32_t* out_count);
 GF_API int gf_h1_stats_read(const gf_h1* engine, gf_h1_stats* out_stats);
 GF_API int gf_h1_cycle_record_read(const gf_h1* engine, uint32_t index, gf_h1_cycle_record* out_record);
 GF_API uint32_t gf_h1_cycle_record_count(const gf_h1* engine);
