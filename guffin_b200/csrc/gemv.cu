@@ -5,31 +5,47 @@
 
 namespace gf {
 
-constexpr uint32_t kMaxDynamicSmem = 227u * 1024u;
+static uint32_t max_chunk_units(uint32_t rows, uint32_t unit_elems, uint32_t variants, bool sums) {
+    uint32_t best = 0;
+    for (uint32_t cu = 1; cu <= 16u; ++cu)
+        if (gemv_smem_layout(rows, cu, unit_elems, variants, sums).total <= kGemvSmemBudget) best = cu;
+    return best;
+}
 
-int gemv_plan(int dtype, uint32_t rows, uint64_t k, uint64_t n, GemvPlan& plan) {
-    if (dtype != GF_Q8_0 && dtype != GF_Q4_K && dtype != GF_Q6_K)
-        return fail(GF_ERR_INVALID, "gf_matmul: unsupported weight dtype %d", dtype);
-    if (rows == 0 || rows > GF_MAX_ROWS) return fail(GF_ERR_INVALID, "gf_matmul: rows=%u outside [1, %d]", rows, GF_MAX_ROWS);
-    const uint32_t unit = unit_elements(dtype);
-    if (k == 0 || n == 0 || k % unit != 0 || k > (1ull << 24) || n > (1ull << 28))
-        return fail(GF_ERR_INVALID, "gf_matmul: K=%llu must be a positive multiple of %u and N=%llu positive",
-                    (unsigned long long)k, unit, (unsigned long long)n);
-    plan.units = (uint32_t)(k / unit);
-    plan.tiles = (uint32_t)((n + 7u) / 8u);
-    const uint32_t sms = (uint32_t)sm_count();
+int gemv_plan(const GemvLaunch& launch, GemvPlan& plan) {
+    if (launch.count == 0 || launch.count > (uint32_t)kGemvMaxMatrices) return fail(GF_ERR_INVALID, "gf_matmul: 1..3 matrices per launch");
+    if (launch.rows == 0 || launch.rows > GF_MAX_ROWS) return fail(GF_ERR_INVALID, "gf_matmul: rows=%u outside [1, %d]", launch.rows, GF_MAX_ROWS);
+    plan.needs_scaled = plan.needs_plain = 0;
+    plan.total_tiles = 0;
+    plan.unit_elems = 0;
+    for (uint32_t i = 0; i < launch.count; ++i) {
+        const int dtype = launch.matrices[i].dtype;
+        if (dtype != GF_Q8_0 && dtype != GF_Q4_K && dtype != GF_Q6_K) return fail(GF_ERR_INVALID, "gf_matmul: unsupported weight dtype %d", dtype);
+        const uint32_t unit = unit_elements(dtype);
+        if (plan.unit_elems && plan.unit_elems != unit) return fail(GF_ERR_INVALID, "gf_matmul: Q8_0 and K-quant matrices cannot share a launch");
+        plan.unit_elems = unit;
+        if (launch.matrices[i].n == 0 || launch.matrices[i].n > (1ull << 28)) return fail(GF_ERR_INVALID, "gf_matmul: N must be positive");
+        plan.total_tiles += (uint32_t)((launch.matrices[i].n + 7u) / 8u);
+        if (dtype == GF_Q4_K) plan.needs_scaled = 1; else plan.needs_plain = 1;
+    }
+    if (launch.k == 0 || launch.k % plan.unit_elems != 0 || launch.k > (1ull << 24))
+        return fail(GF_ERR_INVALID, "gf_matmul: K=%llu must be a positive multiple of %u", (unsigned long long)launch.k, plan.unit_elems);
+    plan.units = (uint32_t)(launch.k / plan.unit_elems);
+    const uint32_t variants = plan.needs_scaled + plan.needs_plain;
+    const uint32_t limit = max_chunk_units(launch.rows, plan.unit_elems, variants, plan.needs_scaled != 0);
+    if (limit == 0) return fail(GF_ERR_INVALID, "gf_matmul: no decomposition fits");
+    const uint32_t slots = (uint32_t)sm_count() * 2u;      // two CTAs per SM
     double best = -1.0;
     plan.chunks = 0;
-    for (uint32_t chunks = 1; chunks <= 64 && chunks <= plan.units && chunks <= sms; ++chunks) {
+    for (uint32_t chunks = 1; chunks <= 64u && chunks <= plan.units && chunks <= slots; ++chunks) {
         const uint32_t chunk_units = (plan.units + chunks - 1u) / chunks;
         if ((chunks - 1u) * chunk_units >= plan.units) continue;          // an empty last chunk
-        if (chunk_units > (uint32_t)kGemvMaxChunkUnits) continue;
-        if (gemv_smem_layout(dtype, (int)rows, chunk_units).total > kMaxDynamicSmem) continue;
-        const uint32_t group_ctas = sms / chunks;
+        if (chunk_units > limit) continue;
+        const uint32_t group_ctas = slots / chunks;
         const uint32_t group_warps = group_ctas * kGemvWarps;
-        const uint32_t rounds = (plan.tiles + group_warps - 1u) / group_warps;
-        // Share of the machine's warp-slots doing useful work; ties go to fewer chunks.
-        double efficiency = (double)plan.tiles / ((double)rounds * group_warps) * (double)(group_ctas * chunks) / sms;
+        const uint32_t rounds = (plan.total_tiles + group_warps - 1u) / group_warps;
+        // Share of the machine's warp slots doing useful work; ties go to fewer chunks.
+        double efficiency = (double)plan.total_tiles / ((double)rounds * group_warps) * (double)(group_ctas * chunks) / slots;
         efficiency -= 0.002 * chunks;
         if (efficiency > best) {
             best = efficiency;
@@ -38,20 +54,33 @@ int gemv_plan(int dtype, uint32_t rows, uint64_t k, uint64_t n, GemvPlan& plan) 
             plan.grid = group_ctas * chunks;
         }
     }
-    if (plan.chunks == 0) return fail(GF_ERR_INVALID, "gf_matmul: no decomposition fits K=%llu rows=%u", (unsigned long long)k, rows);
-    plan.smem = gemv_smem_layout(dtype, (int)rows, plan.chunk_units).total;
+    if (plan.chunks == 0) return fail(GF_ERR_INVALID, "gf_matmul: no decomposition fits K=%llu rows=%u", (unsigned long long)launch.k, launch.rows);
+    plan.smem = gemv_smem_layout(launch.rows, plan.chunk_units, plan.unit_elems, variants, plan.needs_scaled != 0).total;
     return GF_OK;
 }
 
-template <int DTYPE, int ROWS>
+static size_t counters_bytes(const GemvPlan& plan) { return ((size_t)plan.total_tiles * 4u + 255u) & ~(size_t)255u; }
+
+size_t gemv_partial_bytes(const GemvLaunch& launch) {
+    GemvPlan plan;
+    if (gemv_plan(launch, plan) != GF_OK || plan.chunks == 1) return 0;
+    return (size_t)plan.chunks * launch.rows * plan.total_tiles * 8u * sizeof(float);
+}
+
+size_t gemv_counter_bytes(const GemvLaunch& launch) {
+    GemvPlan plan;
+    if (gemv_plan(launch, plan) != GF_OK || plan.chunks == 1) return 0;
+    return counters_bytes(plan);
+}
+
+template <int ROWS>
 static int launch_instance(const GemvParams& p, const GemvPlan& plan, cudaStream_t stream, bool programmatic) {
     static std::once_flag once[64];
     int device = 0;
     cudaGetDevice(&device);
     cudaError_t attr_error = cudaSuccess;
     std::call_once(once[device & 63], [&] {
-        attr_error = cudaFuncSetAttribute(gemv_kernel<DTYPE, ROWS>, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                                          (int)kMaxDynamicSmem);
+        attr_error = cudaFuncSetAttribute(gemv_kernel<ROWS>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)kGemvSmemBudget);
     });
     GF_CUDA(attr_error);
     cudaLaunchConfig_t config = {};
@@ -64,56 +93,69 @@ static int launch_instance(const GemvParams& p, const GemvPlan& plan, cudaStream
     attribute.val.programmaticStreamSerializationAllowed = 1;
     config.attrs = &attribute;
     config.numAttrs = programmatic ? 1 : 0;
-    GF_CUDA(cudaLaunchKernelEx(&config, gemv_kernel<DTYPE, ROWS>, p));
+    GF_CUDA(cudaLaunchKernelEx(&config, gemv_kernel<ROWS>, p));
     return GF_OK;
 }
 
-template <int DTYPE>
-static int launch_rows(uint32_t rows, const GemvParams& p, const GemvPlan& plan, cudaStream_t stream, bool programmatic) {
-    switch (rows) {
-        case 1: return launch_instance<DTYPE, 1>(p, plan, stream, programmatic);
-        case 2: return launch_instance<DTYPE, 2>(p, plan, stream, programmatic);
-        case 3: return launch_instance<DTYPE, 3>(p, plan, stream, programmatic);
-        default: return launch_instance<DTYPE, 4>(p, plan, stream, programmatic);
-    }
-}
-
-int gemv_launch(int dtype, const void* packed, const float* x, float* y, uint32_t rows, uint64_t k, uint64_t n,
-                void* workspace, int* error_flag, cudaStream_t stream, bool programmatic) {
+int gemv_launch(const GemvLaunch& launch, uint32_t* counters, float* partial, size_t partial_bytes, int* error_flag,
+                cudaStream_t stream, bool programmatic) {
     GemvPlan plan;
-    int status = gemv_plan(dtype, rows, k, n, plan);
+    const int status = gemv_plan(launch, plan);
     if (status != GF_OK) return status;
-    if (!packed || !x || !y || !error_flag) return fail(GF_ERR_INVALID, "gf_matmul: null buffer");
-    if (plan.chunks > 1 && !workspace) return fail(GF_ERR_INVALID, "gf_matmul: this shape needs a split-K workspace");
-    GemvParams p;
-    p.weight = static_cast<const uint8_t*>(packed);
-    p.x = x;
-    p.out = plan.chunks > 1 ? static_cast<float*>(workspace) : y;
-    p.k = (uint32_t)k;
-    p.n = (uint32_t)n;
+    if (!launch.in || !error_flag) return fail(GF_ERR_INVALID, "gf_matmul: null buffer");
+    if ((launch.prologue == kPrologueNorm && !launch.gamma1)
+        || (launch.prologue == kPrologueAddNorm && (!launch.gamma0 || !launch.gamma1 || !launch.residual || !launch.residual_out))
+        || (launch.prologue == kPrologueGeglu && !launch.residual) || launch.prologue > kPrologueGeglu)
+        return fail(GF_ERR_INVALID, "gf_matmul: prologue operands missing");
+    GemvParams p = {};
+    uint32_t first = 0;
+    for (uint32_t i = 0; i < launch.count; ++i) {
+        const GemvMatrixDesc& d = launch.matrices[i];
+        if (!d.packed || !d.out) return fail(GF_ERR_INVALID, "gf_matmul: null buffer");
+        p.m[i].weight = static_cast<const uint8_t*>(d.packed);
+        p.m[i].out = d.out;
+        p.m[i].n = (uint32_t)d.n;
+        p.m[i].tiles = (uint32_t)((d.n + 7u) / 8u);
+        p.m[i].dtype = (uint32_t)d.dtype;
+        p.m[i].first_tile = first;
+        first += p.m[i].tiles;
+    }
+    p.matrices = launch.count;
+    p.total_tiles = plan.total_tiles;
+    p.k = (uint32_t)launch.k;
     p.units = plan.units;
-    p.tiles = plan.tiles;
+    p.unit_elems = plan.unit_elems;
     p.chunks = plan.chunks;
     p.chunk_units = plan.chunk_units;
+    p.needs_scaled = plan.needs_scaled;
+    p.needs_plain = plan.needs_plain;
+    p.prologue = launch.prologue;
+    p.in = launch.in; p.residual = launch.residual; p.gamma0 = launch.gamma0; p.gamma1 = launch.gamma1;
+    p.residual_out = launch.residual_out;
+    p.eps = launch.eps;
     p.error_flag = error_flag;
-    if (dtype == GF_Q4_K) status = launch_rows<GF_Q4_K>(rows, p, plan, stream, programmatic);
-    else if (dtype == GF_Q6_K) status = launch_rows<GF_Q6_K>(rows, p, plan, stream, programmatic);
-    else status = launch_rows<GF_Q8_0>(rows, p, plan, stream, programmatic);
-    if (status != GF_OK) return status;
     if (plan.chunks > 1) {
-        const uint32_t elements = rows * (uint32_t)n;
-        cudaLaunchConfig_t config = {};
-        config.gridDim = dim3((elements + 255u) / 256u);
-        config.blockDim = dim3(256);
-        config.stream = stream;
-        cudaLaunchAttribute attribute;
-        attribute.id = cudaLaunchAttributeProgrammaticStreamSerialization;
-        attribute.val.programmaticStreamSerializationAllowed = 1;
-        config.attrs = &attribute;
-        config.numAttrs = programmatic ? 1 : 0;
-        GF_CUDA(cudaLaunchKernelEx(&config, gemv_reduce_kernel, (const float*)workspace, y, plan.chunks, elements));
+        const size_t need = (size_t)plan.chunks * launch.rows * plan.total_tiles * 8u * sizeof(float);
+        if (!counters || !partial || partial_bytes < need) return fail(GF_ERR_INVALID, "gf_matmul: this shape needs a %zu-byte split-K workspace", need);
+        p.counters = counters;
+        p.partial = partial;
     }
-    return GF_OK;
+    switch (launch.rows) {
+        case 1: return launch_instance<1>(p, plan, stream, programmatic);
+        case 2: return launch_instance<2>(p, plan, stream, programmatic);
+        case 3: return launch_instance<3>(p, plan, stream, programmatic);
+        default: return launch_instance<4>(p, plan, stream, programmatic);
+    }
+}
+
+static GemvLaunch single(int dtype, const void* packed, const float* x, float* y, uint32_t rows, uint64_t k, uint64_t n) {
+    GemvLaunch launch;
+    launch.matrices[0] = GemvMatrixDesc{dtype, packed, y, n};
+    launch.count = 1;
+    launch.k = k;
+    launch.rows = rows;
+    launch.in = x;
+    return launch;
 }
 
 // Process-wide error word for the plain entry points (one per device).
@@ -136,19 +178,26 @@ using namespace gf;
 extern "C" {
 
 size_t gf_matmul_workspace_bytes(int dtype, uint32_t rows, uint64_t k, uint64_t n) {
-    GemvPlan plan;
-    if (gemv_plan(dtype, rows, k, n, plan) != GF_OK) return 0;
-    return plan.chunks > 1 ? (size_t)plan.chunks * rows * n * sizeof(float) : 0;
+    const GemvLaunch launch = single(dtype, reinterpret_cast<const void*>(1), nullptr, reinterpret_cast<float*>(1), rows, k, n);
+    return gemv_counter_bytes(launch) + gemv_partial_bytes(launch);
 }
 
 int gf_matmul(int dtype, const void* packed_dev, const float* x_dev, float* y_dev, uint32_t rows, uint64_t k,
               uint64_t n, void* workspace_dev, void* stream) {
+    const GemvLaunch launch = single(dtype, packed_dev ? packed_dev : reinterpret_cast<const void*>(1), x_dev, y_dev ? y_dev : reinterpret_cast<float*>(1), rows, k, n);
     GemvPlan plan;
-    const int status = gemv_plan(dtype, rows, k, n, plan);   // argument errors come before any GPU work
+    const int status = gemv_plan(launch, plan);      // argument errors come before any GPU work
     if (status != GF_OK) return status;
+    if (!packed_dev || !x_dev || !y_dev) return fail(GF_ERR_INVALID, "gf_matmul: null buffer");
     int* flag = device_error_flag();
     if (!flag) return fail(GF_ERR_CUDA, "gf_matmul: cannot allocate the device error word");
-    return gemv_launch(dtype, packed_dev, x_dev, y_dev, rows, k, n, workspace_dev, flag, as_stream(stream), false);
+    const size_t bytes = gemv_partial_bytes(launch);
+    if (bytes && !workspace_dev) return fail(GF_ERR_INVALID, "gf_matmul: this shape needs a split-K workspace");
+    // The arrival counters at the head of the workspace must start at zero.
+    if (bytes) GF_CUDA(cudaMemsetAsync(workspace_dev, 0, counters_bytes(plan), as_stream(stream)));
+    return gemv_launch(launch, static_cast<uint32_t*>(workspace_dev),
+                       reinterpret_cast<float*>(static_cast<uint8_t*>(workspace_dev) + counters_bytes(plan)), bytes, flag,
+                       as_stream(stream), false);
 }
 
 int gf_matmul_check(void* stream) {
@@ -166,8 +215,9 @@ int gf_matmul_check(void* stream) {
 
 int gf_matmul_host(int dtype, const void* packed_dev, const float* x_host, float* y_host, uint32_t rows,
                    uint64_t k, uint64_t n) {
+    const size_t wb = gf_matmul_workspace_bytes(dtype, rows, k, n);
     GemvPlan plan;
-    int status = gemv_plan(dtype, rows, k, n, plan);
+    int status = gemv_plan(single(dtype, reinterpret_cast<const void*>(1), nullptr, reinterpret_cast<float*>(1), rows, k, n), plan);
     if (status != GF_OK) return status;
     if (!x_host || !y_host) return fail(GF_ERR_INVALID, "gf_matmul_host: null host buffer");
     // Per-thread scratch grown on demand; the timed path reuses it, so no allocation per call.
@@ -177,7 +227,6 @@ int gf_matmul_host(int dtype, const void* packed_dev, const float* x_host, float
     GF_CUDA(cudaGetDevice(&device));
     if (s.device != device) { s = Scratch(); s.device = device; }
     const size_t xb = (size_t)rows * k * 4, yb = (size_t)rows * n * 4;
-    const size_t wb = plan.chunks > 1 ? (size_t)plan.chunks * rows * n * 4 : 0;
     if (xb > s.xb) { cudaFree(s.x); GF_CUDA(cudaMalloc(&s.x, xb)); s.xb = xb; }
     if (yb > s.yb) { cudaFree(s.y); GF_CUDA(cudaMalloc(&s.y, yb)); s.yb = yb; }
     if (wb > s.wb) { cudaFree(s.ws); GF_CUDA(cudaMalloc(&s.ws, wb)); s.wb = wb; }

@@ -16,24 +16,42 @@
 
 namespace gf {
 
-constexpr int kGemvWarps = 16;       // warps per CTA (one CTA per SM)
+constexpr int kGemvWarps = 8;        // warps per CTA; two CTAs share an SM so that the next
+                                     // kernel's CTAs can prefetch weights while this one drains
 constexpr int kGemvStages = 3;       // ring depth per warp
-constexpr int kGemvMaxChunkUnits = 16;
+constexpr uint32_t kGemvStageBytes = 3456u;          // 3 Q4_K / 2 Q6_K / 3 Q8_0 unit rows
+constexpr uint32_t kGemvTableFloats = 128u;          // per unit row, per warp (Q6_K needs 8 x 16)
+constexpr uint32_t kGemvSmemBudget = 113u * 1024u;   // two CTAs per SM
+constexpr int kGemvMaxMatrices = 3;
 
-__host__ __device__ constexpr int gemv_stage_units(int dtype) { return dtype == GF_Q6_K ? 2 : 3; }
-__host__ __device__ constexpr int gemv_table_floats(int dtype) {
-    return dtype == GF_Q4_K ? 64 : dtype == GF_Q6_K ? 128 : 32;   // per unit row, per warp
-}
+__host__ __device__ constexpr uint32_t gemv_stage_units(int dtype) { return dtype == GF_Q6_K ? 2u : 3u; }
+
+// How the activation rows are produced from global memory before the weights are applied.
+enum GemvPrologue : uint32_t {
+    kProloguePlain = 0,      // xs = in
+    kPrologueNorm = 1,       // xs = rmsnorm(in; gamma1)
+    kPrologueAddNorm = 2,    // r = residual + rmsnorm(in; gamma0) -> residual_out;  xs = rmsnorm(r; gamma1)
+    kPrologueGeglu = 3,      // xs = gelu_tanh(in) * residual
+};
+
+struct GemvMatrix {
+    const uint8_t* weight;   // streaming layout
+    float* out;              // [rows][n]
+    uint32_t n, tiles, dtype, first_tile;
+};
 
 struct GemvParams {
-    const uint8_t* weight;     // streaming layout
-    const float* x;            // [rows][k]
-    float* out;                // chunks == 1: y [rows][n]; else partial [chunks][rows][n]
-    uint32_t k, n;
-    uint32_t units;            // K units per column
-    uint32_t tiles;            // ceil(n / 8)
-    uint32_t chunks;           // K chunks (gridDim.x is a multiple of this)
-    uint32_t chunk_units;      // units per chunk (last chunk may be shorter)
+    GemvMatrix m[kGemvMaxMatrices];
+    uint32_t matrices, total_tiles;
+    uint32_t k, units, unit_elems;
+    uint32_t chunks, chunk_units;
+    uint32_t needs_scaled, needs_plain;   // which activation variants the matrices read
+    uint32_t prologue;
+    const float *in, *residual, *gamma0, *gamma1;
+    float* residual_out;
+    float eps;
+    float* partial;            // [chunks][rows][total_tiles * 8] when chunks > 1
+    uint32_t* counters;        // [total_tiles] arrival counts, zero between launches
     int* error_flag;           // set to 1 when a bounded wait gives up
 };
 
@@ -41,14 +59,15 @@ struct GemvSmemLayout {
     uint32_t xs_bytes, sx_bytes, ring_bytes, table_bytes, total;
 };
 
-__host__ __device__ inline GemvSmemLayout gemv_smem_layout(int dtype, int rows, uint32_t chunk_units) {
+__host__ __device__ inline GemvSmemLayout gemv_smem_layout(uint32_t rows, uint32_t chunk_units, uint32_t unit_elems,
+                                                           uint32_t variants, bool needs_sums) {
     GemvSmemLayout s;
-    const uint32_t slice = chunk_units * unit_elements(dtype);
-    s.xs_bytes = (uint32_t)rows * slice * 4u;
-    s.sx_bytes = dtype == GF_Q4_K ? (uint32_t)rows * (slice / 32u) * 4u : 0u;
-    s.ring_bytes = (uint32_t)kGemvWarps * kGemvStages * gemv_stage_units(dtype) * unit_row_bytes(dtype);
-    s.table_bytes = (uint32_t)kGemvWarps * 2u * gemv_table_floats(dtype) * 4u;
-    s.total = s.xs_bytes + s.sx_bytes + s.ring_bytes + s.table_bytes + kGemvWarps * kGemvStages * 8u + 16u;
+    const uint32_t slice = chunk_units * unit_elems;
+    s.xs_bytes = rows * slice * 4u * variants;
+    s.sx_bytes = needs_sums ? rows * (slice / 32u) * 4u : 0u;
+    s.ring_bytes = (uint32_t)kGemvWarps * kGemvStages * kGemvStageBytes;
+    s.table_bytes = (uint32_t)kGemvWarps * 2u * kGemvTableFloats * 4u;
+    s.total = s.xs_bytes + s.sx_bytes + s.ring_bytes + s.table_bytes + kGemvWarps * kGemvStages * 8u + 64u;
     return s;
 }
 
@@ -212,55 +231,119 @@ __device__ __forceinline__ void unit_row_q80(const uint8_t* row, const float* xs
     }
 }
 
-// Stages this CTA's K slice of the activation rows: xs (Q4_K: scaled by 2^-bitpos of the
-// element's nibble) and, for Q4_K, the per-32 sums the min term needs.
-template <int DTYPE, int ROWS>
-__device__ __forceinline__ void stage_activations(const float* __restrict__ x, uint32_t k, uint32_t first,
-                                                  uint32_t count, uint32_t slice, float* xs, float* sx) {
+// ---- activation prologue ----
+
+__device__ __forceinline__ float gelu_tanh_exact(float v) {
+    const float inner = __fmul_rn(0.7978845608028654f, __fadd_rn(v, __fmul_rn(__fmul_rn(__fmul_rn(0.044715f, v), v), v)));
+    return __fmul_rn(__fmul_rn(0.5f, v), __fadd_rn(1.0f, tanhf(inner)));
+}
+
+// Sum over the block of one value per thread; every thread gets the total (fixed order).
+__device__ __forceinline__ float gemv_block_sum(float v, float* scratch) {
+    v = warp_sum(v);
+    const uint32_t warp = threadIdx.x >> 5, lane = threadIdx.x & 31u;
+    if (lane == 0) scratch[warp] = v;
+    __syncthreads();
+    float total = 0.0f;
+#pragma unroll
+    for (int w = 0; w < kGemvWarps; ++w) total += scratch[w];
+    __syncthreads();
+    return total;
+}
+
+// Produces this CTA's K slice of the activation rows in shared memory: the plain values, the
+// copy pre-scaled by 2^-bitpos of each element's nibble (what the Q4_K lanes multiply with),
+// and the per-32 sums the Q4_K min term needs.  The RMS norms of prologues 1 and 2 need the
+// whole row, so every CTA recomputes them from global memory (a few tens of KB out of L2).
+template <int ROWS>
+__device__ __forceinline__ void stage_activations(const GemvParams& p, uint32_t first, uint32_t count, uint32_t slice,
+                                                  float* xs_plain, float* xs_scaled, float* sx, float* scratch) {
+    float inv0[ROWS], inv1[ROWS];
+#pragma unroll
+    for (int r = 0; r < ROWS; ++r) { inv0[r] = 1.0f; inv1[r] = 1.0f; }
+    if (p.prologue == kPrologueNorm || p.prologue == kPrologueAddNorm) {
+#pragma unroll
+        for (int r = 0; r < ROWS; ++r) {
+            const float* in = p.in + (size_t)r * p.k;
+            float sum = 0.0f;
+            for (uint32_t c = threadIdx.x; c < p.k; c += blockDim.x) sum = fmaf(in[c], in[c], sum);
+            const float total = gemv_block_sum(sum, scratch);
+            const float inv = __fdiv_rn(1.0f, __fsqrt_rn(__fadd_rn(__fdiv_rn(total, (float)p.k), p.eps)));
+            if (p.prologue == kPrologueNorm) { inv1[r] = inv; continue; }
+            inv0[r] = inv;
+            // r = residual + norm(in) * gamma0; its mean square feeds the second norm.
+            const float* res = p.residual + (size_t)r * p.k;
+            float sum2 = 0.0f;
+            for (uint32_t c = threadIdx.x; c < p.k; c += blockDim.x) {
+                const float v = __fadd_rn(res[c], __fmul_rn(__fmul_rn(in[c], inv), p.gamma0[c]));
+                sum2 = fmaf(v, v, sum2);
+                if (blockIdx.x == 0) p.residual_out[(size_t)r * p.k + c] = v;
+            }
+            const float total2 = gemv_block_sum(sum2, scratch);
+            inv1[r] = __fdiv_rn(1.0f, __fsqrt_rn(__fadd_rn(__fdiv_rn(total2, (float)p.k), p.eps)));
+        }
+    }
     for (uint32_t e = threadIdx.x; e < (uint32_t)ROWS * slice; e += blockDim.x) {
         const uint32_t r = e / slice, o = e % slice;
-        float v = o < count ? x[(size_t)r * k + first + o] : 0.0f;
-        if (DTYPE == GF_Q4_K) {
+        float v = 0.0f;
+        if (o < count) {
+            const size_t g = (size_t)r * p.k + first + o;
+            const uint32_t c = first + o;
+            float i0 = 1.0f, i1 = 1.0f;
+#pragma unroll
+            for (int rr = 0; rr < ROWS; ++rr) if (rr == (int)r) { i0 = inv0[rr]; i1 = inv1[rr]; }
+            if (p.prologue == kProloguePlain) v = p.in[g];
+            else if (p.prologue == kPrologueNorm) v = __fmul_rn(__fmul_rn(p.in[g], i1), p.gamma1[c]);
+            else if (p.prologue == kPrologueAddNorm) {
+                const float t = __fadd_rn(p.residual[g], __fmul_rn(__fmul_rn(p.in[g], i0), p.gamma0[c]));
+                v = __fmul_rn(__fmul_rn(t, i1), p.gamma1[c]);
+            } else v = __fmul_rn(gelu_tanh_exact(p.in[g]), p.residual[g]);
+        }
+        if (p.needs_plain) xs_plain[e] = v;
+        if (p.needs_scaled) {
             const float sum = warp_sum(v);   // slice is a multiple of 32 and e is warp-aligned
             if ((threadIdx.x & 31u) == 0u) sx[r * (slice / 32u) + o / 32u] = sum;
             const uint32_t bitpos = 8u * (o & 1u) + ((o & 32u) ? 4u : 0u);
-            v *= __uint_as_float((127u - bitpos) << 23);
+            xs_scaled[e] = v * __uint_as_float((127u - bitpos) << 23);
         }
-        xs[e] = v;
     }
 }
 
-template <int DTYPE, int ROWS>
-__global__ void __launch_bounds__(kGemvWarps * 32, 1) gemv_kernel(GemvParams p) {
+template <int ROWS>
+__global__ void __launch_bounds__(kGemvWarps * 32, 2) gemv_kernel(const __grid_constant__ GemvParams p) {
     extern __shared__ __align__(128) uint8_t smem[];
-    constexpr uint32_t kUnitRow = DTYPE == GF_Q8_0 ? 1088u : DTYPE == GF_Q4_K ? 1152u : 1680u;
-    constexpr uint32_t kUnitElems = DTYPE == GF_Q8_0 ? 128u : 256u;
-    constexpr uint32_t kStageUnits = gemv_stage_units(DTYPE);
-    constexpr uint32_t kStageBytes = kStageUnits * kUnitRow;
-    constexpr uint32_t kTable = gemv_table_floats(DTYPE);
-
-    const GemvSmemLayout lay = gemv_smem_layout(DTYPE, ROWS, p.chunk_units);
-    float* xs = reinterpret_cast<float*>(smem);
+    __shared__ float scratch[kGemvWarps];
+    const uint32_t variants = p.needs_plain + p.needs_scaled;
+    const GemvSmemLayout lay = gemv_smem_layout(ROWS, p.chunk_units, p.unit_elems, variants, p.needs_scaled != 0u);
+    const uint32_t slice = p.chunk_units * p.unit_elems;
+    float* xs_plain = reinterpret_cast<float*>(smem);
+    float* xs_scaled = xs_plain + (p.needs_plain ? (size_t)ROWS * slice : 0u);
     float* sx = reinterpret_cast<float*>(smem + lay.xs_bytes);
     uint8_t* ring_base = smem + lay.xs_bytes + lay.sx_bytes;
     float* table_base = reinterpret_cast<float*>(ring_base + lay.ring_bytes);
     uint64_t* bars = reinterpret_cast<uint64_t*>(reinterpret_cast<uint8_t*>(table_base) + lay.table_bytes);
 
     const uint32_t warp = threadIdx.x >> 5, lane = threadIdx.x & 31u;
-    uint8_t* ring = ring_base + warp * (kGemvStages * kStageBytes);
-    float* table = table_base + warp * (2u * kTable);
+    uint8_t* ring = ring_base + warp * (kGemvStages * kGemvStageBytes);
+    float* table = table_base + warp * (2u * kGemvTableFloats);
     uint64_t* bar = bars + warp * kGemvStages;
 
-    // This CTA's K chunk and this warp's sequence of column tiles.
+    // This CTA's K chunk and this warp's sequence of column tiles (over all matrices).
     const uint32_t chunk = blockIdx.x % p.chunks;
     const uint32_t group_ctas = gridDim.x / p.chunks;
     const uint32_t first_unit = chunk * p.chunk_units;
     const uint32_t chunk_count = min(p.chunk_units, p.units - first_unit);
     const uint32_t stride = group_ctas * kGemvWarps;
     const uint32_t first_tile = (blockIdx.x / p.chunks) * kGemvWarps + warp;
-    const uint32_t my_tiles = first_tile < p.tiles ? (p.tiles - first_tile + stride - 1u) / stride : 0u;
-    const uint32_t stages_per_item = (chunk_count + kStageUnits - 1u) / kStageUnits;
-    const uint32_t jobs = my_tiles * stages_per_item;
+    const uint32_t my_tiles = first_tile < p.total_tiles ? (p.total_tiles - first_tile + stride - 1u) / stride : 0u;
+
+    auto matrix_of = [&](uint32_t tile) -> uint32_t {
+        uint32_t m = 0;
+        if (p.matrices > 1u && tile >= p.m[1].first_tile) m = 1;
+        if (p.matrices > 2u && tile >= p.m[2].first_tile) m = 2;
+        return m;
+    };
+    auto stages_of = [&](uint32_t dtype) { const uint32_t su = gemv_stage_units((int)dtype); return (chunk_count + su - 1u) / su; };
 
     if (lane == 0) {
         for (int s = 0; s < kGemvStages; ++s) mbar_init(&bar[s], 1);
@@ -268,98 +351,142 @@ __global__ void __launch_bounds__(kGemvWarps * 32, 1) gemv_kernel(GemvParams p) 
     }
     __syncwarp();
 
-    auto issue = [&](uint32_t job) {   // lane 0 only
-        const uint32_t item = job / stages_per_item, s = job % stages_per_item;
-        const uint32_t tile = first_tile + item * stride;
-        const uint32_t u0 = s * kStageUnits;
-        const uint32_t cnt = min(kStageUnits, chunk_count - u0);
-        const uint8_t* src = p.weight + ((size_t)tile * p.units + first_unit + u0) * kUnitRow;
-        const uint32_t slot = job % kGemvStages;
-        mbar_expect_tx(&bar[slot], cnt * kUnitRow);
-        bulk_load(ring + slot * kStageBytes, src, cnt * kUnitRow, &bar[slot]);
+    // Producer cursor (lane 0): the next stage to request, walking items then stages.
+    uint32_t prod_item = 0, prod_stage = 0, prod_slot = 0;
+    auto issue_next = [&]() -> bool {   // lane 0 only
+        if (prod_item >= my_tiles) return false;
+        const uint32_t tile = first_tile + prod_item * stride;
+        const GemvMatrix& mat = p.m[matrix_of(tile)];
+        const uint32_t su = gemv_stage_units((int)mat.dtype), row_bytes = unit_row_bytes((int)mat.dtype);
+        const uint32_t u0 = prod_stage * su;
+        const uint32_t cnt = min(su, chunk_count - u0);
+        const uint8_t* src = mat.weight + ((size_t)(tile - mat.first_tile) * p.units + first_unit + u0) * row_bytes;
+        mbar_expect_tx(&bar[prod_slot], cnt * row_bytes);
+        bulk_load(ring + prod_slot * kGemvStageBytes, src, cnt * row_bytes, &bar[prod_slot]);
+        prod_slot = prod_slot + 1u == (uint32_t)kGemvStages ? 0u : prod_slot + 1u;
+        if (++prod_stage == stages_of(mat.dtype)) { prod_stage = 0; ++prod_item; }
+        return true;
     };
     // Weights do not depend on the previous kernel: start streaming before waiting for it.
     if (lane == 0)
-        for (uint32_t j = 0; j < (uint32_t)kGemvStages && j < jobs; ++j) issue(j);
+        for (int j = 0; j < kGemvStages; ++j) issue_next();
 
     pdl_wait();
-    const uint32_t slice = p.chunk_units * kUnitElems;
-    stage_activations<DTYPE, ROWS>(p.x, p.k, first_unit * kUnitElems, chunk_count * kUnitElems, slice, xs, sx);
+    stage_activations<ROWS>(p, first_unit * p.unit_elems, chunk_count * p.unit_elems, slice, xs_plain, xs_scaled, sx, scratch);
     __syncthreads();
     pdl_launch_dependents();
 
     float acc[ROWS][8];
     float macc[ROWS];
     bool failed = false;
+    uint32_t slot = 0, phase = 0;
     for (uint32_t item = 0; item < my_tiles && !failed; ++item) {
+        const uint32_t tile = first_tile + item * stride;
+        const GemvMatrix& mat = p.m[matrix_of(tile)];
+        const uint32_t dtype = mat.dtype, su = gemv_stage_units((int)dtype), row_bytes = unit_row_bytes((int)dtype);
+        const uint32_t stages = (chunk_count + su - 1u) / su;
 #pragma unroll
         for (int r = 0; r < ROWS; ++r) {
             macc[r] = 0.0f;
 #pragma unroll
             for (int c = 0; c < 8; ++c) acc[r][c] = 0.0f;
         }
-        for (uint32_t s = 0; s < stages_per_item; ++s) {
-            const uint32_t job = item * stages_per_item + s;
-            const uint32_t slot = job % kGemvStages;
-            if (!mbar_wait(&bar[slot], (job / kGemvStages) & 1u)) { failed = true; break; }
-            const uint32_t u0 = s * kStageUnits;
-            const uint32_t cnt = min(kStageUnits, chunk_count - u0);
-            const uint8_t* stage = ring + slot * kStageBytes;
+        for (uint32_t s = 0; s < stages; ++s) {
+            if (!mbar_wait(&bar[slot], phase)) { failed = true; break; }
+            const uint32_t u0 = s * su;
+            const uint32_t cnt = min(su, chunk_count - u0);
+            const uint8_t* stage = ring + slot * kGemvStageBytes;
             for (uint32_t u = 0; u < cnt; ++u) {
                 const uint32_t lu = u0 + u;      // unit index inside the chunk
-                float* tbl = table + (lu & 1u) * kTable;
-                if constexpr (DTYPE == GF_Q4_K)
-                    unit_row_q4k<ROWS>(stage + u * kUnitRow, xs + lu * 256u, sx + lu * 8u, slice, slice / 32u,
+                float* tbl = table + (lu & 1u) * kGemvTableFloats;
+                if (dtype == GF_Q4_K)
+                    unit_row_q4k<ROWS>(stage + u * row_bytes, xs_scaled + lu * 256u, sx + lu * 8u, slice, slice / 32u,
                                        tbl, lane, acc, macc);
-                else if constexpr (DTYPE == GF_Q6_K)
-                    unit_row_q6k<ROWS>(stage + u * kUnitRow, xs + lu * 256u, slice, tbl, lane, acc);
+                else if (dtype == GF_Q6_K)
+                    unit_row_q6k<ROWS>(stage + u * row_bytes, xs_plain + lu * 256u, slice, tbl, lane, acc);
                 else
-                    unit_row_q80<ROWS>(stage + u * kUnitRow, xs + lu * 128u, slice, tbl, lane, acc);
+                    unit_row_q80<ROWS>(stage + u * row_bytes, xs_plain + lu * 128u, slice, tbl, lane, acc);
             }
             __syncwarp();   // every lane has finished reading this slot
-            if (lane == 0 && job + kGemvStages < jobs) issue(job + kGemvStages);
+            if (lane == 0) issue_next();
+            if (++slot == (uint32_t)kGemvStages) { slot = 0; phase ^= 1u; }
         }
         if (failed) break;
-        // Reduce the eight column sums across the warp and write this item's outputs.
-        const uint32_t tile = first_tile + item * stride;
+        // Reduce the eight column sums across the warp.
+        float totals[ROWS];
 #pragma unroll
         for (int r = 0; r < ROWS; ++r) {
             float total = reduce_columns8(acc[r], lane);
-            if constexpr (DTYPE == GF_Q4_K) {
+            if (dtype == GF_Q4_K) {
                 float m = macc[r];                         // lanes with equal (lane & 7) share a column
                 m += __shfl_xor_sync(0xffffffffu, m, 8);
                 m += __shfl_xor_sync(0xffffffffu, m, 16);
                 total -= __shfl_sync(0xffffffffu, m, column_of_lane(lane));
             }
-            const uint32_t column = tile * 8u + column_of_lane(lane);
-            if ((lane & 3u) == 0u && column < p.n)
-                p.out[((size_t)chunk * ROWS + r) * p.n + column] = total;
+            totals[r] = total;
+        }
+        const uint32_t local_tile = tile - mat.first_tile;
+        const uint32_t column = local_tile * 8u + column_of_lane(lane);
+        if (p.chunks == 1u) {
+#pragma unroll
+            for (int r = 0; r < ROWS; ++r)
+                if ((lane & 3u) == 0u && column < mat.n) mat.out[(size_t)r * mat.n + column] = totals[r];
+            continue;
+        }
+        // Split K: park this chunk's partial sums; the warp that arrives last for the tile adds
+        // all chunks in chunk order (so the result does not depend on arrival order).
+        const size_t width = (size_t)p.total_tiles * 8u;
+#pragma unroll
+        for (int r = 0; r < ROWS; ++r)
+            if ((lane & 3u) == 0u) p.partial[((size_t)chunk * ROWS + r) * width + (size_t)tile * 8u + column_of_lane(lane)] = totals[r];
+        __threadfence();
+        __syncwarp();
+        uint32_t arrived = 0;
+        if (lane == 0) arrived = atomicAdd(&p.counters[tile], 1u);
+        arrived = __shfl_sync(0xffffffffu, arrived, 0);
+        if (arrived == p.chunks - 1u) {
+            __threadfence();
+            const uint32_t col = lane & 7u, r = lane >> 3;
+            if (r < (uint32_t)ROWS) {
+                float sum = 0.0f;
+                for (uint32_t c = 0; c < p.chunks; ++c)
+                    sum += __ldcg(&p.partial[((size_t)c * ROWS + r) * width + (size_t)tile * 8u + col]);
+                const uint32_t out_column = local_tile * 8u + col;
+                if (out_column < mat.n) mat.out[(size_t)r * mat.n + out_column] = sum;
+            }
+            if (lane == 0) p.counters[tile] = 0u;
         }
     }
-    if (failed && lane == 0) atomicExch(p.error_flag, 1);
-}
-
-// Adds split-K partials in chunk order: y[r][n] = sum_c partial[c][r][n].
-static __global__ void __launch_bounds__(256) gemv_reduce_kernel(const float* __restrict__ partial, float* __restrict__ y,
-                                                          uint32_t chunks, uint32_t elements) {
-    pdl_wait();
-    const uint32_t i = blockIdx.x * blockDim.x + threadIdx.x;
-    if (i < elements) {
-        float sum = partial[i];
-        for (uint32_t c = 1; c < chunks; ++c) sum += partial[(size_t)c * elements + i];
-        y[i] = sum;
+    if (failed) {
+        // Give outstanding copies a bounded chance to land before the shared memory is released.
+        for (int s = 0; s < kGemvStages; ++s) mbar_wait(&bar[s], 0);
+        if (lane == 0) atomicExch(p.error_flag, 1);
     }
-    pdl_launch_dependents();
 }
 
 #endif  // __CUDACC__
 
-// Host-side plan: how a (dtype, rows, K, N) product is decomposed.
-struct GemvPlan {
-    uint32_t units, tiles, chunks, chunk_units, grid, smem;
+// Host-side description of one fused launch.
+struct GemvMatrixDesc { int dtype; const void* packed; float* out; uint64_t n; };
+struct GemvLaunch {
+    GemvMatrixDesc matrices[kGemvMaxMatrices];
+    uint32_t count = 1;
+    uint64_t k = 0;
+    uint32_t rows = 1;
+    uint32_t prologue = kProloguePlain;
+    const float *in = nullptr, *residual = nullptr, *gamma0 = nullptr, *gamma1 = nullptr;
+    float* residual_out = nullptr;
+    float eps = 1e-6f;
 };
-int gemv_plan(int dtype, uint32_t rows, uint64_t k, uint64_t n, GemvPlan& plan);
-int gemv_launch(int dtype, const void* packed, const float* x, float* y, uint32_t rows, uint64_t k, uint64_t n,
-                void* workspace, int* error_flag, cudaStream_t stream, bool programmatic);
+struct GemvPlan { uint32_t units, unit_elems, total_tiles, chunks, chunk_units, grid, smem, needs_scaled, needs_plain; };
+
+int gemv_plan(const GemvLaunch& launch, GemvPlan& plan);
+// Split-K scratch of one launch: `partial` bytes of sums, and one arrival counter per column tile.
+// Counters must be zero before a launch and are left zero by it; they must not share memory
+// with any launch's partial sums.
+size_t gemv_partial_bytes(const GemvLaunch& launch);
+size_t gemv_counter_bytes(const GemvLaunch& launch);
+int gemv_launch(const GemvLaunch& launch, uint32_t* counters, float* partial, size_t partial_bytes, int* error_flag,
+                cudaStream_t stream, bool programmatic);
 
 }  // namespace gf

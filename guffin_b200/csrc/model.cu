@@ -172,12 +172,27 @@ int Model::finalize() {
     GF_TRY(device_alloc(allocations_, &up_, (size_t)R * c.ffn));
     GF_TRY(device_alloc(allocations_, &gated_, (size_t)R * c.ffn));
     GF_TRY(device_alloc(allocations_, &logits_, (size_t)R * c.vocab));
-    size_t ws = 16;
-    auto grow = [&](const PackedMatrix& m) { ws = std::max(ws, gf_matmul_workspace_bytes(m.dtype, R, m.k, m.n)); };
-    for (const LayerWeights& w : layers_) { grow(w.q); grow(w.k); grow(w.v); grow(w.o); grow(w.gate); grow(w.up); grow(w.down); }
-    grow(has_head_ ? head_ : token_embd_);
+    // Split-K workspace: the largest any launch of the schedule needs, for every row count.
+    size_t ws = 256, counters = 256;
+    auto grow = [&](std::initializer_list<const PackedMatrix*> set) {
+        for (uint32_t rows = 1; rows <= R; ++rows) {
+            GemvLaunch launch;
+            launch.count = 0;
+            for (const PackedMatrix* m : set) {
+                launch.matrices[launch.count++] = GemvMatrixDesc{m->dtype, m->data, logits_, m->n};
+                launch.k = m->k;
+            }
+            launch.rows = rows;
+            ws = std::max(ws, gemv_partial_bytes(launch));
+            counters = std::max(counters, gemv_counter_bytes(launch));
+        }
+    };
+    for (const LayerWeights& w : layers_) { grow({&w.q, &w.k, &w.v}); grow({&w.o}); grow({&w.gate, &w.up}); grow({&w.down}); }
+    grow({has_head_ ? &head_ : &token_embd_});
     uint8_t* bytes = nullptr;
-    GF_TRY(device_alloc(allocations_, &bytes, ws)); matmul_ws_ = bytes;
+    GF_TRY(device_alloc(allocations_, &bytes, ws)); matmul_ws_ = bytes; matmul_ws_bytes_ = ws;
+    GF_TRY(device_alloc(allocations_, &bytes, counters)); matmul_counters_ = reinterpret_cast<uint32_t*>(bytes);
+    GF_CUDA(cudaMemsetAsync(matmul_counters_, 0, counters, stream_));   // arrival counters start (and stay) at zero
     GF_TRY(device_alloc(allocations_, &bytes, gf_attention_workspace_bytes(R, c.heads))); attention_ws_ = bytes;
     GF_TRY(device_alloc(allocations_, &bytes, candidates_workspace_bytes(R, c.vocab))); candidates_ws_ = bytes;
     GF_TRY(device_alloc(allocations_, &bytes, (size_t)R * gf_selection_request_bytes())); requests_dev_ = bytes;
@@ -208,27 +223,48 @@ int Model::reset() {
     return GF_OK;
 }
 
-int Model::matmul(const PackedMatrix& w, const float* x, float* y, uint32_t rows) {
+static GemvMatrixDesc desc(const PackedMatrix& w, float* out) { return GemvMatrixDesc{w.dtype, w.data, out, w.n}; }
+
+int Model::run_gemv(GemvLaunch& launch, uint32_t rows) {
+    launch.rows = rows;
+    launch.eps = config_.rms_eps;
     ++launches_;
-    return gemv_launch(w.dtype, w.data, x, y, rows, w.k, w.n, matmul_ws_, error_flag_, stream_, true);
+    return gemv_launch(launch, matmul_counters_, static_cast<float*>(matmul_ws_), matmul_ws_bytes_, error_flag_, stream_, true);
 }
 
 // One transformer pass: the operator order of encode_gemma_target_blocks
-// (gemma_target_runtime.cpp:28-219).
+// (gemma_target_runtime.cpp:28-219), with the small operators folded into the GEMV launches:
+//   QKV   <- prologue: [residual += norm(down; post_ffw)] ; norm(residual; attn_norm)
+//   rope/norm/store, attention
+//   O     <- plain
+//   gate,up <- prologue: residual2 = residual + norm(O; post_attention) ; norm(residual2; ffn_norm)
+//   down  <- prologue: gelu_tanh(gate) * up
+// The next layer's QKV (or the head) applies the post-FFW norm and residual of this layer.
 int Model::encode_blocks(uint32_t rows, uint32_t flags) {
     const gf_model_config& c = config_;
     const float embedding_scale = sqrtf((float)c.hidden);     // f32, not bf16-rounded (model.cpp:599-605)
     GF_TRY(launch_embedding(token_embd_.dtype, token_embd_.data, c.hidden, c.vocab, tokens_dev_, rows, embedding_scale,
                             residual_, status_dev_, stream_, false));
-    float* x = residual_;
-    float* x2 = post_attention_;
+    ++launches_;
+    float* x = residual_;          // residual stream entering a layer
+    float* x2 = post_attention_;   // residual stream after the attention branch
     for (uint32_t l = 0; l < c.layers; ++l) {
         const LayerWeights& w = layers_[l];
         const LayerCache& cache = caches_[l];
-        GF_TRY(launch_rms_norm(x, w.attn_norm, nullptr, normalized_, rows, c.hidden, c.rms_eps, stream_, true));
-        GF_TRY(matmul(w.q, normalized_, raw_q_, rows));
-        GF_TRY(matmul(w.k, normalized_, raw_k_, rows));
-        GF_TRY(matmul(w.v, normalized_, raw_v_, rows));
+        GemvLaunch qkv;
+        qkv.k = c.hidden;
+        const bool same_unit = unit_elements(w.q.dtype) == unit_elements(w.v.dtype);
+        qkv.matrices[0] = desc(w.q, raw_q_);
+        qkv.matrices[1] = desc(w.k, raw_k_);
+        qkv.matrices[2] = desc(w.v, raw_v_);
+        qkv.count = same_unit ? 3 : 2;
+        if (l == 0) { qkv.prologue = kPrologueNorm; qkv.in = x; qkv.gamma1 = w.attn_norm; }
+        else {
+            qkv.prologue = kPrologueAddNorm; qkv.in = projected_; qkv.residual = x2; qkv.gamma0 = layers_[l - 1].post_ffw_norm;
+            qkv.residual_out = x; qkv.gamma1 = w.attn_norm;
+        }
+        GF_TRY(run_gemv(qkv, rows));
+        if (!same_unit) return fail(GF_ERR_INVALID, "attention projections of one layer must share a block family");
         RopeStoreParams rp{raw_q_, raw_k_, raw_v_, c.uses_qk_norm ? w.q_norm : nullptr, c.uses_qk_norm ? w.k_norm : nullptr,
                            query_, cache.private_k, cache.private_v, state_dev_, status_dev_, rows, c.heads, c.kv_heads,
                            c.head_dim, c.rms_eps, cache.rope_base, cache.rope_scale, c.kv_f16};
@@ -242,20 +278,33 @@ int Model::encode_blocks(uint32_t rows, uint32_t flags) {
         ap.ring_mask = cache.ring_rows - 1u; ap.window = cache.window; ap.scale = c.attention_scale;
         ap.softcap = c.attn_softcap; ap.kv_f16 = c.kv_f16;
         GF_TRY(launch_attention(ap, stream_, true));
-        GF_TRY(matmul(w.o, attention_out_, projected_, rows));
-        GF_TRY(launch_rms_norm(projected_, w.post_attention_norm, x, x2, rows, c.hidden, c.rms_eps, stream_, true));
-        GF_TRY(launch_rms_norm(x2, w.ffn_norm, nullptr, normalized_, rows, c.hidden, c.rms_eps, stream_, true));
-        GF_TRY(matmul(w.gate, normalized_, gate_, rows));
-        GF_TRY(matmul(w.up, normalized_, up_, rows));
-        GF_TRY(launch_geglu(gate_, up_, gated_, (uint64_t)rows * c.ffn, stream_, true));
-        GF_TRY(matmul(w.down, gated_, projected_, rows));
-        GF_TRY(launch_rms_norm(projected_, w.post_ffw_norm, x2, x, rows, c.hidden, c.rms_eps, stream_, true));
-        launches_ += 8;
+        launches_ += 3;
+        GemvLaunch o;
+        o.k = (uint64_t)c.heads * c.head_dim;
+        o.matrices[0] = desc(w.o, projected_);
+        o.in = attention_out_;
+        GF_TRY(run_gemv(o, rows));
+        GemvLaunch gu;
+        gu.k = c.hidden;
+        gu.matrices[0] = desc(w.gate, gate_);
+        gu.matrices[1] = desc(w.up, up_);
+        gu.count = 2;
+        gu.prologue = kPrologueAddNorm; gu.in = projected_; gu.residual = x; gu.gamma0 = w.post_attention_norm;
+        gu.residual_out = x2; gu.gamma1 = w.ffn_norm;
+        GF_TRY(run_gemv(gu, rows));
+        GemvLaunch down;
+        down.k = c.ffn;
+        down.matrices[0] = desc(w.down, projected_);
+        down.prologue = kPrologueGeglu; down.in = gate_; down.residual = up_;
+        GF_TRY(run_gemv(down, rows));
     }
     if (flags & kForwardLogits) {
-        GF_TRY(launch_rms_norm(x, output_norm_, nullptr, normalized_, rows, c.hidden, c.rms_eps, stream_, true));
-        GF_TRY(matmul(has_head_ ? head_ : token_embd_, normalized_, logits_, rows));
-        ++launches_;
+        GemvLaunch head;
+        head.k = c.hidden;
+        head.matrices[0] = desc(has_head_ ? head_ : token_embd_, logits_);
+        head.prologue = kPrologueAddNorm; head.in = projected_; head.residual = x2;
+        head.gamma0 = layers_[c.layers - 1].post_ffw_norm; head.residual_out = x; head.gamma1 = output_norm_;
+        GF_TRY(run_gemv(head, rows));
     }
     return GF_OK;
 }
@@ -279,7 +328,7 @@ int Model::run_graph_or_encode(uint32_t rows, uint32_t flags) {
         GF_CUDA(inst);
     }
     GF_CUDA(cudaGraphLaunch(exec, stream_));
-    launches_ += config_.layers * 15u + 3u;
+    launches_ += config_.layers * 7u + 2u;
     return GF_OK;
 }
 
@@ -349,21 +398,25 @@ int Model::weight_sweep(uint32_t rows, uint32_t* out_launches, uint64_t* out_byt
     if (rows == 0 || rows > config_.row_capacity) return fail(GF_ERR_INVALID, "bad row count");
     uint32_t launches = 0;
     uint64_t bytes = 0;
-    auto run = [&](const PackedMatrix& w, const float* x, float* y) {
+    auto run = [&](std::initializer_list<std::pair<const PackedMatrix*, float*>> set, const float* x) {
+        GemvLaunch launch;
+        launch.count = 0;
+        for (const auto& entry : set) {
+            launch.matrices[launch.count++] = desc(*entry.first, entry.second);
+            launch.k = entry.first->k;
+            bytes += entry.first->native_bytes;
+        }
+        launch.in = x;
         ++launches;
-        bytes += w.native_bytes;
-        return gemv_launch(w.dtype, w.data, x, y, rows, w.k, w.n, matmul_ws_, error_flag_, stream_, true);
+        return run_gemv(launch, rows);
     };
     for (const LayerWeights& w : layers_) {
-        GF_TRY(run(w.q, normalized_, raw_q_));
-        GF_TRY(run(w.k, normalized_, raw_k_));
-        GF_TRY(run(w.v, normalized_, raw_v_));
-        GF_TRY(run(w.o, attention_out_, projected_));
-        GF_TRY(run(w.gate, normalized_, gate_));
-        GF_TRY(run(w.up, normalized_, up_));
-        GF_TRY(run(w.down, gated_, projected_));
+        GF_TRY(run({{&w.q, raw_q_}, {&w.k, raw_k_}, {&w.v, raw_v_}}, normalized_));
+        GF_TRY(run({{&w.o, projected_}}, attention_out_));
+        GF_TRY(run({{&w.gate, gate_}, {&w.up, up_}}, normalized_));
+        GF_TRY(run({{&w.down, projected_}}, gated_));
     }
-    GF_TRY(run(has_head_ ? head_ : token_embd_, normalized_, logits_));
+    GF_TRY(run({{has_head_ ? &head_ : &token_embd_, logits_}}, normalized_));
     if (out_launches) *out_launches = launches;
     if (out_bytes) *out_bytes = bytes;
     return GF_OK;

@@ -82,7 +82,7 @@ public:
 
 private:
     int encode_blocks(uint32_t rows, uint32_t flags);
-    int matmul(const PackedMatrix& w, const float* x, float* y, uint32_t rows);
+    int run_gemv(struct GemvLaunch& launch, uint32_t rows);
     int run_graph_or_encode(uint32_t rows, uint32_t flags);
     bool layer_is_local(uint32_t layer) const;
 
@@ -102,6 +102,8 @@ private:
     float *query_ = nullptr, *attention_out_ = nullptr, *projected_ = nullptr, *post_attention_ = nullptr;
     float *gate_ = nullptr, *up_ = nullptr, *gated_ = nullptr, *logits_ = nullptr;
     void *attention_ws_ = nullptr, *matmul_ws_ = nullptr, *candidates_ws_ = nullptr;
+    size_t matmul_ws_bytes_ = 0;
+    uint32_t* matmul_counters_ = nullptr;
     void *requests_dev_ = nullptr, *results_dev_ = nullptr;
     uint32_t *tokens_dev_ = nullptr, *state_dev_ = nullptr, *status_dev_ = nullptr;
     int* error_flag_ = nullptr;
