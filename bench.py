@@ -103,6 +103,19 @@ def prompt_tokens(vocab: int, rank: int) -> np.ndarray:
     return np.random.default_rng(SEEDS["prompt"] + rank).integers(0, vocab, CONTEXT).astype(np.uint32)
 
 
+def aggregate_streams(dist, tokens: float, tokens_e2e: float, device_ms: float, e2e_s: float, device=None):
+    """Whole-job figures of N independent streams: tokens add up, time is the slowest rank's.
+    `dist` is torch.distributed (any backend) or None for a single process."""
+    if dist is None:
+        return tokens, tokens_e2e, device_ms, e2e_s
+    import torch
+    totals = torch.tensor([tokens, tokens_e2e], dtype=torch.float64, device=device)
+    slowest = torch.tensor([device_ms, e2e_s], dtype=torch.float64, device=device)
+    dist.all_reduce(totals, op=dist.ReduceOp.SUM)
+    dist.all_reduce(slowest, op=dist.ReduceOp.MAX)
+    return (*totals.tolist(), *slowest.tolist())
+
+
 # ----------------------------------------------------------------------------------------- ours
 
 def run_ours(args) -> dict:
@@ -177,16 +190,8 @@ def run_ours(args) -> dict:
     launches = target.kernel_launches() + draft.kernel_launches() - launches_before
     status = target.status() | draft.status()
 
-    produced, produced_e2e = float(len(tokens)), float(len(tokens_e2e))
-    elapsed_ms, e2e_s = device_ms, e2e_wall
-    if dist is not None:
-        import torch
-        agg = torch.tensor([produced, produced_e2e], device="cuda", dtype=torch.float64)
-        slow = torch.tensor([device_ms, e2e_wall], device="cuda", dtype=torch.float64)
-        dist.all_reduce(agg, op=dist.ReduceOp.SUM)
-        dist.all_reduce(slow, op=dist.ReduceOp.MAX)
-        produced, produced_e2e = agg.tolist()
-        elapsed_ms, e2e_s = slow.tolist()
+    produced, produced_e2e, elapsed_ms, e2e_s = aggregate_streams(
+        dist, float(len(tokens)), float(len(tokens_e2e)), device_ms, e2e_wall, "cuda" if dist is not None else None)
     if rank != 0:
         return {}
 

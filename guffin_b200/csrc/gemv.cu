@@ -35,7 +35,9 @@ int gemv_plan(const GemvLaunch& launch, GemvPlan& plan) {
     const uint32_t limit = max_chunk_units(launch.rows, plan.unit_elems, variants, plan.needs_scaled != 0);
     if (limit == 0) return fail(GF_ERR_INVALID, "gf_matmul: no decomposition fits");
     const uint32_t slots = (uint32_t)sm_count() * 2u;      // two CTAs per SM
-    double best = -1.0;
+    // Critical path of a warp, in unit rows: rounds x (units per item + per-item overhead); the
+    // split-K hand-over costs about one more.  Ties go to fewer chunks.
+    double best = 1e30;
     plan.chunks = 0;
     for (uint32_t chunks = 1; chunks <= 64u && chunks <= plan.units && chunks <= slots; ++chunks) {
         const uint32_t chunk_units = (plan.units + chunks - 1u) / chunks;
@@ -44,11 +46,9 @@ int gemv_plan(const GemvLaunch& launch, GemvPlan& plan) {
         const uint32_t group_ctas = slots / chunks;
         const uint32_t group_warps = group_ctas * kGemvWarps;
         const uint32_t rounds = (plan.total_tiles + group_warps - 1u) / group_warps;
-        // Share of the machine's warp slots doing useful work; ties go to fewer chunks.
-        double efficiency = (double)plan.total_tiles / ((double)rounds * group_warps) * (double)(group_ctas * chunks) / slots;
-        efficiency -= 0.002 * chunks;
-        if (efficiency > best) {
-            best = efficiency;
+        const double cost = (double)rounds * ((double)chunk_units + 2.0 + (chunks > 1u ? 1.0 : 0.0));
+        if (cost < best - 1e-9) {
+            best = cost;
             plan.chunks = chunks;
             plan.chunk_units = chunk_units;
             plan.grid = group_ctas * chunks;

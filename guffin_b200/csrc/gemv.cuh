@@ -77,14 +77,104 @@ __device__ __forceinline__ float magic_to_float(uint32_t bits, float bias) {
     return __fsub_rn(__uint_as_float(bits), bias);
 }
 
+// ---- packed f32x2 arithmetic (sm_100): one instruction issues two independent f32 operations,
+// halving the issue slots of the conversion and multiply-add stream.  Each half rounds exactly
+// like the scalar instruction.
+typedef unsigned long long f32x2;
+// The "magic" exponent word 0x4B000000 (2^23) held in a register the compiler cannot fold: a
+// logic instruction encodes only one immediate, so (w & mask) | magic is a single LOP3 only when
+// the magic operand comes from a register.
+__device__ __forceinline__ uint32_t magic_register() {
+    uint32_t r;
+    asm("mov.u32 %0, 0x4B000000;" : "=r"(r));
+    return r;
+}
+__device__ __forceinline__ f32x2 pack2(uint32_t lo, uint32_t hi) {
+    f32x2 r;
+    asm("mov.b64 %0, {%1, %2};" : "=l"(r) : "r"(lo), "r"(hi));
+    return r;
+}
+__device__ __forceinline__ f32x2 pack2f(float lo, float hi) { return pack2(__float_as_uint(lo), __float_as_uint(hi)); }
+__device__ __forceinline__ float2 unpack2(f32x2 v) {
+    uint32_t lo, hi;
+    asm("mov.b64 {%0, %1}, %2;" : "=r"(lo), "=r"(hi) : "l"(v));
+    return make_float2(__uint_as_float(lo), __uint_as_float(hi));
+}
+__device__ __forceinline__ f32x2 add2(f32x2 a, f32x2 b) {
+    f32x2 r;
+    asm("add.rn.f32x2 %0, %1, %2;" : "=l"(r) : "l"(a), "l"(b));
+    return r;
+}
+__device__ __forceinline__ f32x2 mul2(f32x2 a, f32x2 b) {
+    f32x2 r;
+    asm("mul.rn.f32x2 %0, %1, %2;" : "=l"(r) : "l"(a), "l"(b));
+    return r;
+}
+__device__ __forceinline__ f32x2 fma2(f32x2 a, f32x2 b, f32x2 c) {
+    f32x2 r;
+    asm("fma.rn.f32x2 %0, %1, %2, %3;" : "=l"(r) : "l"(a), "l"(b), "l"(c));
+    return r;
+}
+
+// Two codes of one word become a pair of exact floats in one go: (w & mask) | magic for each half
+// (a single three-input logic instruction each, the magic word coming from a register), then
+// one packed add of -bias.  MASK_LO / MASK_HI select the code of the even / odd element.
+template <uint32_t MASK_LO, uint32_t MASK_HI>
+__device__ __forceinline__ f32x2 masked_pair(uint32_t w, uint32_t magic, f32x2 neg_bias) {
+    f32x2 r;
+    asm("{\n\t.reg .b32 lo, hi;\n\t.reg .b64 p;\n\t"
+        "lop3.b32 lo, %1, %2, %4, 0xEA;\n\t"
+        "lop3.b32 hi, %1, %3, %4, 0xEA;\n\t"
+        "mov.b64 p, {lo, hi};\n\t"
+        "add.rn.f32x2 %0, p, %5;\n\t}"
+        : "=l"(r) : "r"(w), "n"(MASK_LO), "n"(MASK_HI), "r"(magic), "l"(neg_bias));
+    return r;
+}
+// Bytes SEL and SEL+1 of `v` (each < 256) become a pair of exact floats minus the bias.
+template <uint32_t SEL>
+__device__ __forceinline__ f32x2 byte_pair(uint32_t v, uint32_t magic, f32x2 neg_bias) {
+    f32x2 r;
+    asm("{\n\t.reg .b32 lo, hi;\n\t.reg .b64 p;\n\t"
+        "prmt.b32 lo, %1, %2, %3;\n\t"
+        "prmt.b32 hi, %1, %2, %4;\n\t"
+        "mov.b64 p, {lo, hi};\n\t"
+        "add.rn.f32x2 %0, p, %5;\n\t}"
+        : "=l"(r) : "r"(v), "r"(magic), "n"(0x7540u + SEL), "n"(0x7541u + SEL), "l"(neg_bias));
+    return r;
+}
+
+// Sums four per-lane column values over the 16 lanes of a half warp; afterwards the lanes
+// with (lane & 3) == 0 hold the total of column half_column_of_lane(lane).
+__device__ __forceinline__ float reduce_columns4(float (&v)[4], uint32_t lane) {
+    const bool b8 = lane & 8u, b4 = lane & 4u;
+    float u[2];
+#pragma unroll
+    for (int i = 0; i < 2; ++i) {
+        const float keep = b8 ? v[i + 2] : v[i];
+        const float send = b8 ? v[i] : v[i + 2];
+        u[i] = keep + __shfl_xor_sync(0xffffffffu, send, 8);
+    }
+    const float keep = b4 ? u[1] : u[0];
+    const float send = b4 ? u[0] : u[1];
+    float w = keep + __shfl_xor_sync(0xffffffffu, send, 4);
+    w += __shfl_xor_sync(0xffffffffu, w, 2);
+    w += __shfl_xor_sync(0xffffffffu, w, 1);
+    return w;
+}
+__device__ __forceinline__ uint32_t half_column_of_lane(uint32_t lane) {
+    return (lane >> 4) * 4u + ((lane & 8u) ? 2u : 0u) + ((lane & 4u) ? 1u : 0u);
+}
+
 // ---- one unit row (8 columns x one K unit) of each format.  `row` points at the unit row in
 // shared memory, `xs` at the activation slice of this unit (row stride `xstride` floats),
-// `table` at this warp's scale table for the current parity.
+// `table` at this warp's scale table for the current parity.  Each half warp owns four of the
+// eight columns; a lane owns sixteen K positions and keeps their activations in registers as
+// f32x2 pairs.  acc[r][cc] is a pair of partial sums of row r, column half*4+cc.
 
 template <int ROWS>
 __device__ __forceinline__ void unit_row_q4k(const uint8_t* row, const float* xs, const float* sx,
                                              uint32_t xstride, uint32_t sxstride, float* table,
-                                             uint32_t lane, float (&acc)[ROWS][8], float (&macc)[ROWS]) {
+                                             uint32_t lane, f32x2 (&acc)[ROWS][4], float (&macc)[ROWS]) {
     // Phase A: lane (col, pair) decodes the two 6-bit scales and mins of groups 2*pair, 2*pair+1.
     {
         const uint32_t col = lane & 7u, pair = lane >> 3;
@@ -96,10 +186,9 @@ __device__ __forceinline__ void unit_row_q4k(const uint8_t* row, const float* xs
         const bool upper = pair >= 2u;
         const uint32_t sc = upper ? ((c & 0x0f0fu) | ((a >> 2) & 0x3030u)) : (a & 0x3f3fu);
         const uint32_t mn = upper ? (((c >> 4) & 0x0f0fu) | ((b >> 2) & 0x3030u)) : (b & 0x3f3fu);
-        float2 ds;
-        ds.x = __fmul_rn(d, (float)(sc & 0xffu));
-        ds.y = __fmul_rn(d, (float)(sc >> 8));
-        *reinterpret_cast<float2*>(table + (col * 4u + pair) * 2u) = ds;
+        const float ds0 = __fmul_rn(d, (float)(sc & 0xffu)), ds1 = __fmul_rn(d, (float)(sc >> 8));
+        // Each scale is stored twice so that Phase B reads it as a ready-made f32x2 pair.
+        *reinterpret_cast<float4*>(table + (col * 4u + pair) * 4u) = make_float4(ds0, ds0, ds1, ds1);
         const float m0 = __fmul_rn(dmin, (float)(mn & 0xffu)), m1 = __fmul_rn(dmin, (float)(mn >> 8));
 #pragma unroll
         for (int r = 0; r < ROWS; ++r) {
@@ -108,45 +197,46 @@ __device__ __forceinline__ void unit_row_q4k(const uint8_t* row, const float* xs
         }
     }
     __syncwarp();
-    // Phase B: lane (chunk c, word i) owns nibbles of elements 64c+4i+j (low) and 64c+32+4i+j (high).
-    const uint32_t c = lane >> 3, i = lane & 7u;
-    float xl[ROWS][4], xh[ROWS][4];
+    // Phase B: lane (half, chunk c, piece i) owns the nibbles of elements 64c+8i+j (low) and
+    // 64c+32+8i+j (high), j < 8, of the half's four columns.
+    const uint32_t half = lane >> 4, t = lane & 15u, c = t >> 2, i = t & 3u;
+    f32x2 xl[ROWS][4], xh[ROWS][4];
 #pragma unroll
     for (int r = 0; r < ROWS; ++r) {
-        const float4 lo = *reinterpret_cast<const float4*>(xs + r * xstride + c * 64u + i * 4u);
-        const float4 hi = *reinterpret_cast<const float4*>(xs + r * xstride + c * 64u + 32u + i * 4u);
-        xl[r][0] = lo.x; xl[r][1] = lo.y; xl[r][2] = lo.z; xl[r][3] = lo.w;
-        xh[r][0] = hi.x; xh[r][1] = hi.y; xh[r][2] = hi.z; xh[r][3] = hi.w;
+        const ulonglong2* lo = reinterpret_cast<const ulonglong2*>(xs + r * xstride + c * 64u + i * 8u);
+        const ulonglong2* hi = reinterpret_cast<const ulonglong2*>(xs + r * xstride + c * 64u + 32u + i * 8u);
+        const ulonglong2 l0 = lo[0], l1 = lo[1], h0 = hi[0], h1 = hi[1];
+        xl[r][0] = l0.x; xl[r][1] = l0.y; xl[r][2] = l1.x; xl[r][3] = l1.y;
+        xh[r][0] = h0.x; xh[r][1] = h0.y; xh[r][2] = h1.x; xh[r][3] = h1.y;
     }
-    const uint32_t* qs = reinterpret_cast<const uint32_t*>(row);
-    constexpr uint32_t kMagic = 0x4B000000u;   // 2^23: the nibble lands in the low mantissa bits
-    constexpr float kBias = 8388608.0f;
+    const uint2* qs = reinterpret_cast<const uint2*>(row);
+    const uint32_t magic = magic_register();
+    const f32x2 neg_bias = pack2f(-8388608.0f, -8388608.0f);
 #pragma unroll
-    for (int col = 0; col < 8; ++col) {
-        const uint32_t w = qs[col * 32 + lane];
-        const uint32_t w2 = w >> 16;
-        const float2 ds = *reinterpret_cast<const float2*>(table + (col * 4u + c) * 2u);
-        // Activations were pre-scaled by 2^-bitpos of their nibble, so q * 2^bitpos * x' = q * x exactly.
-        const float l0 = magic_to_float((w & 0x0000000fu) | kMagic, kBias);
-        const float l1 = magic_to_float((w & 0x00000f00u) | kMagic, kBias);
-        const float l2 = magic_to_float((w2 & 0x0000000fu) | kMagic, kBias);
-        const float l3 = magic_to_float((w2 & 0x00000f00u) | kMagic, kBias);
-        const float h0 = magic_to_float((w & 0x000000f0u) | kMagic, kBias);
-        const float h1 = magic_to_float((w & 0x0000f000u) | kMagic, kBias);
-        const float h2 = magic_to_float((w2 & 0x000000f0u) | kMagic, kBias);
-        const float h3 = magic_to_float((w2 & 0x0000f000u) | kMagic, kBias);
+    for (int cc = 0; cc < 4; ++cc) {
+        const uint32_t col = half * 4u + cc;
+        const uint2 w = qs[col * 16u + t];
+        const ulonglong2 ds = *reinterpret_cast<const ulonglong2*>(table + (col * 4u + c) * 4u);
+        const uint32_t w0 = w.x, w0h = w.x >> 16, w1 = w.y, w1h = w.y >> 16;
+        // Pair = (even element, odd element): bits 0-3 / 8-11 of a half word hold the low nibbles,
+        // bits 4-7 / 12-15 the high nibbles.  Activations were pre-scaled by 2^-bitpos of their
+        // nibble, so q * 2^bitpos * x' = q * x exactly.
+        const f32x2 qa0 = masked_pair<0x0000000fu, 0x00000f00u>(w0, magic, neg_bias), qb0 = masked_pair<0x000000f0u, 0x0000f000u>(w0, magic, neg_bias);
+        const f32x2 qa1 = masked_pair<0x0000000fu, 0x00000f00u>(w0h, magic, neg_bias), qb1 = masked_pair<0x000000f0u, 0x0000f000u>(w0h, magic, neg_bias);
+        const f32x2 qa2 = masked_pair<0x0000000fu, 0x00000f00u>(w1, magic, neg_bias), qb2 = masked_pair<0x000000f0u, 0x0000f000u>(w1, magic, neg_bias);
+        const f32x2 qa3 = masked_pair<0x0000000fu, 0x00000f00u>(w1h, magic, neg_bias), qb3 = masked_pair<0x000000f0u, 0x0000f000u>(w1h, magic, neg_bias);
 #pragma unroll
         for (int r = 0; r < ROWS; ++r) {
-            const float lo = fmaf(xl[r][3], l3, fmaf(xl[r][2], l2, fmaf(xl[r][1], l1, xl[r][0] * l0)));
-            const float hi = fmaf(xh[r][3], h3, fmaf(xh[r][2], h2, fmaf(xh[r][1], h1, xh[r][0] * h0)));
-            acc[r][col] = fmaf(ds.x, lo, fmaf(ds.y, hi, acc[r][col]));
+            const f32x2 lo = fma2(xl[r][3], qa3, fma2(xl[r][2], qa2, fma2(xl[r][1], qa1, mul2(xl[r][0], qa0))));
+            const f32x2 hi = fma2(xh[r][3], qb3, fma2(xh[r][2], qb2, fma2(xh[r][1], qb1, mul2(xh[r][0], qb0))));
+            acc[r][cc] = fma2(ds.x, lo, fma2(ds.y, hi, acc[r][cc]));
         }
     }
 }
 
 template <int ROWS>
 __device__ __forceinline__ void unit_row_q6k(const uint8_t* row, const float* xs, uint32_t xstride,
-                                             float* table, uint32_t lane, float (&acc)[ROWS][8]) {
+                                             float* table, uint32_t lane, f32x2 (&acc)[ROWS][4]) {
     {   // Phase A: lane (col, part) turns int8 sub-scales 4*part..4*part+3 into d*scale.
         const uint32_t col = lane & 7u, part = lane >> 3;
         const uint32_t s4 = *reinterpret_cast<const uint32_t*>(row + 1536u + col * 16u + part * 4u);
@@ -159,74 +249,82 @@ __device__ __forceinline__ void unit_row_q6k(const uint8_t* row, const float* xs
         }
     }
     __syncwarp();
-    // Phase B: lane (half h, plane p, word i): elements h*128+32p+4i+j (low nibble, high bits 2p)
-    // and h*128+32(p+2)+4i+j (high nibble, high bits 2p+4); each set lies in one 16-wide group.
-    const uint32_t h = lane >> 4, p = (lane >> 3) & 1u, i = lane & 7u;
-    float xa[ROWS][4], xb[ROWS][4];
+    // Phase B: lane (half, t = (h, p, i)): elements h*128+32p+8i+j (low nibble, high bits 2p) and
+    // h*128+32(p+2)+8i+j (high nibble, high bits 2p+4), j < 8; each set lies in one 16-wide group.
+    const uint32_t half = lane >> 4, t = lane & 15u, h = t >> 3, p = (t >> 2) & 1u, i = t & 3u;
+    f32x2 xa[ROWS][4], xb[ROWS][4];
 #pragma unroll
     for (int r = 0; r < ROWS; ++r) {
-        const float4 a = *reinterpret_cast<const float4*>(xs + r * xstride + h * 128u + p * 32u + i * 4u);
-        const float4 b = *reinterpret_cast<const float4*>(xs + r * xstride + h * 128u + p * 32u + 64u + i * 4u);
-        xa[r][0] = a.x; xa[r][1] = a.y; xa[r][2] = a.z; xa[r][3] = a.w;
-        xb[r][0] = b.x; xb[r][1] = b.y; xb[r][2] = b.z; xb[r][3] = b.w;
+        const ulonglong2* a = reinterpret_cast<const ulonglong2*>(xs + r * xstride + h * 128u + p * 32u + i * 8u);
+        const ulonglong2* b = reinterpret_cast<const ulonglong2*>(xs + r * xstride + h * 128u + p * 32u + 64u + i * 8u);
+        const ulonglong2 a0 = a[0], a1 = a[1], b0 = b[0], b1 = b[1];
+        xa[r][0] = a0.x; xa[r][1] = a0.y; xa[r][2] = a1.x; xa[r][3] = a1.y;
+        xb[r][0] = b0.x; xb[r][1] = b0.y; xb[r][2] = b1.x; xb[r][3] = b1.y;
     }
-    const uint32_t* ql = reinterpret_cast<const uint32_t*>(row);
-    const uint32_t* qh = reinterpret_cast<const uint32_t*>(row + 1024u);
-    constexpr uint32_t kMagic = 0x4B000000u;
-    constexpr float kBias = 8388608.0f + 32.0f;      // removes the magic exponent and the -32 offset
+    const uint2* ql = reinterpret_cast<const uint2*>(row);
+    const uint2* qh = reinterpret_cast<const uint2*>(row + 1024u);
+    const uint32_t kMagic = magic_register();
+    const f32x2 neg_bias = pack2f(-(8388608.0f + 32.0f), -(8388608.0f + 32.0f));   // magic exponent and the -32 offset
     const uint32_t shift = p * 2u;
 #pragma unroll
-    for (int col = 0; col < 8; ++col) {
-        const uint32_t wl = ql[col * 32 + h * 16u + p * 8u + i];
-        const uint32_t wh = qh[col * 16 + h * 8u + i] >> shift;
-        const uint32_t va = (wl & 0x0f0f0f0fu) | ((wh << 4) & 0x30303030u);
-        const uint32_t vb = ((wl >> 4) & 0x0f0f0f0fu) | (wh & 0x30303030u);
-        const float2 ds = *reinterpret_cast<const float2*>(table + col * 16u + ((h * 2u + p) * 2u + (i >> 2)) * 2u);
-        float qa[4], qb[4];
-#pragma unroll
-        for (int j = 0; j < 4; ++j) {
-            qa[j] = magic_to_float(__byte_perm(va, kMagic, 0x7540 + j), kBias);
-            qb[j] = magic_to_float(__byte_perm(vb, kMagic, 0x7540 + j), kBias);
-        }
+    for (int cc = 0; cc < 4; ++cc) {
+        const uint32_t col = half * 4u + cc;
+        const uint2 wl = ql[col * 16u + t];
+        const uint2 whr = qh[col * 8u + h * 4u + i];
+        const float2 ds = *reinterpret_cast<const float2*>(table + col * 16u + ((h * 2u + p) * 2u + (i >> 1)) * 2u);
+        const uint32_t wh0 = whr.x >> shift, wh1 = whr.y >> shift;
+        const uint32_t va0 = (wl.x & 0x0f0f0f0fu) | ((wh0 << 4) & 0x30303030u);
+        const uint32_t vb0 = ((wl.x >> 4) & 0x0f0f0f0fu) | (wh0 & 0x30303030u);
+        const uint32_t va1 = (wl.y & 0x0f0f0f0fu) | ((wh1 << 4) & 0x30303030u);
+        const uint32_t vb1 = ((wl.y >> 4) & 0x0f0f0f0fu) | (wh1 & 0x30303030u);
+        const f32x2 qa0 = byte_pair<0>(va0, kMagic, neg_bias), qa1 = byte_pair<2>(va0, kMagic, neg_bias);
+        const f32x2 qa2 = byte_pair<0>(va1, kMagic, neg_bias), qa3 = byte_pair<2>(va1, kMagic, neg_bias);
+        const f32x2 qb0 = byte_pair<0>(vb0, kMagic, neg_bias), qb1 = byte_pair<2>(vb0, kMagic, neg_bias);
+        const f32x2 qb2 = byte_pair<0>(vb1, kMagic, neg_bias), qb3 = byte_pair<2>(vb1, kMagic, neg_bias);
+        const f32x2 dsa = pack2f(ds.x, ds.x), dsb = pack2f(ds.y, ds.y);
 #pragma unroll
         for (int r = 0; r < ROWS; ++r) {
-            const float da = fmaf(xa[r][3], qa[3], fmaf(xa[r][2], qa[2], fmaf(xa[r][1], qa[1], xa[r][0] * qa[0])));
-            const float db = fmaf(xb[r][3], qb[3], fmaf(xb[r][2], qb[2], fmaf(xb[r][1], qb[1], xb[r][0] * qb[0])));
-            acc[r][col] = fmaf(ds.x, da, fmaf(ds.y, db, acc[r][col]));
+            const f32x2 da = fma2(xa[r][3], qa3, fma2(xa[r][2], qa2, fma2(xa[r][1], qa1, mul2(xa[r][0], qa0))));
+            const f32x2 db = fma2(xb[r][3], qb3, fma2(xb[r][2], qb2, fma2(xb[r][1], qb1, mul2(xb[r][0], qb0))));
+            acc[r][cc] = fma2(dsa, da, fma2(dsb, db, acc[r][cc]));
         }
     }
 }
 
 template <int ROWS>
 __device__ __forceinline__ void unit_row_q80(const uint8_t* row, const float* xs, uint32_t xstride,
-                                             float* table, uint32_t lane, float (&acc)[ROWS][8]) {
+                                             float* table, uint32_t lane, f32x2 (&acc)[ROWS][4]) {
     {   // Phase A: lane (col, block) widens the block's f16 scale.
         const uint32_t col = lane & 7u, block = lane >> 3;
         table[col * 4u + block] = __half2float(__ushort_as_half(
             *reinterpret_cast<const unsigned short*>(row + 1024u + col * 8u + block * 2u)));
     }
     __syncwarp();
-    const uint32_t block = lane >> 3;
-    float xv[ROWS][4];
+    // Phase B: lane (half, t) owns elements 8t..8t+7 (block t/4) of the half's four columns.
+    const uint32_t half = lane >> 4, t = lane & 15u, block = t >> 2;
+    f32x2 xv[ROWS][4];
 #pragma unroll
     for (int r = 0; r < ROWS; ++r) {
-        const float4 v = *reinterpret_cast<const float4*>(xs + r * xstride + lane * 4u);
-        xv[r][0] = v.x; xv[r][1] = v.y; xv[r][2] = v.z; xv[r][3] = v.w;
+        const ulonglong2* v = reinterpret_cast<const ulonglong2*>(xs + r * xstride + t * 8u);
+        const ulonglong2 v0 = v[0], v1 = v[1];
+        xv[r][0] = v0.x; xv[r][1] = v0.y; xv[r][2] = v1.x; xv[r][3] = v1.y;
     }
-    const uint32_t* q = reinterpret_cast<const uint32_t*>(row);
-    constexpr uint32_t kMagic = 0x4B000000u;
-    constexpr float kBias = 8388608.0f + 128.0f;     // int8 + 128 was made unsigned by flipping bit 7
+    const uint2* q = reinterpret_cast<const uint2*>(row);
+    const uint32_t kMagic = magic_register();
+    const f32x2 neg_bias = pack2f(-(8388608.0f + 128.0f), -(8388608.0f + 128.0f));   // int8 + 128 made unsigned by flipping bit 7
 #pragma unroll
-    for (int col = 0; col < 8; ++col) {
-        const uint32_t w = q[col * 32 + lane] ^ 0x80808080u;
+    for (int cc = 0; cc < 4; ++cc) {
+        const uint32_t col = half * 4u + cc;
+        const uint2 raw = q[col * 16u + t];
+        const uint32_t w0 = raw.x ^ 0x80808080u, w1 = raw.y ^ 0x80808080u;
         const float d = table[col * 4u + block];
-        float qv[4];
-#pragma unroll
-        for (int j = 0; j < 4; ++j) qv[j] = magic_to_float(__byte_perm(w, kMagic, 0x7540 + j), kBias);
+        const f32x2 q0 = byte_pair<0>(w0, kMagic, neg_bias), q1 = byte_pair<2>(w0, kMagic, neg_bias);
+        const f32x2 q2 = byte_pair<0>(w1, kMagic, neg_bias), q3 = byte_pair<2>(w1, kMagic, neg_bias);
+        const f32x2 dd = pack2f(d, d);
 #pragma unroll
         for (int r = 0; r < ROWS; ++r) {
-            const float dot = fmaf(xv[r][3], qv[3], fmaf(xv[r][2], qv[2], fmaf(xv[r][1], qv[1], xv[r][0] * qv[0])));
-            acc[r][col] = fmaf(d, dot, acc[r][col]);
+            const f32x2 dot = fma2(xv[r][3], q3, fma2(xv[r][2], q2, fma2(xv[r][1], q1, mul2(xv[r][0], q0))));
+            acc[r][cc] = fma2(dd, dot, acc[r][cc]);
         }
     }
 }
@@ -376,7 +474,7 @@ __global__ void __launch_bounds__(kGemvWarps * 32, 2) gemv_kernel(const __grid_c
     __syncthreads();
     pdl_launch_dependents();
 
-    float acc[ROWS][8];
+    f32x2 acc[ROWS][4];
     float macc[ROWS];
     bool failed = false;
     uint32_t slot = 0, phase = 0;
@@ -389,7 +487,7 @@ __global__ void __launch_bounds__(kGemvWarps * 32, 2) gemv_kernel(const __grid_c
         for (int r = 0; r < ROWS; ++r) {
             macc[r] = 0.0f;
 #pragma unroll
-            for (int c = 0; c < 8; ++c) acc[r][c] = 0.0f;
+            for (int c = 0; c < 4; ++c) acc[r][c] = 0ull;
         }
         for (uint32_t s = 0; s < stages; ++s) {
             if (!mbar_wait(&bar[slot], phase)) { failed = true; break; }
@@ -412,21 +510,25 @@ __global__ void __launch_bounds__(kGemvWarps * 32, 2) gemv_kernel(const __grid_c
             if (++slot == (uint32_t)kGemvStages) { slot = 0; phase ^= 1u; }
         }
         if (failed) break;
-        // Reduce the eight column sums across the warp.
+        // Reduce each half warp's four column sums; lanes with (lane & 3) == 0 hold the eight totals.
+        const uint32_t my_column = half_column_of_lane(lane);
         float totals[ROWS];
 #pragma unroll
         for (int r = 0; r < ROWS; ++r) {
-            float total = reduce_columns8(acc[r], lane);
+            float sums[4];
+#pragma unroll
+            for (int c = 0; c < 4; ++c) { const float2 v = unpack2(acc[r][c]); sums[c] = v.x + v.y; }
+            float total = reduce_columns4(sums, lane);
             if (dtype == GF_Q4_K) {
                 float m = macc[r];                         // lanes with equal (lane & 7) share a column
                 m += __shfl_xor_sync(0xffffffffu, m, 8);
                 m += __shfl_xor_sync(0xffffffffu, m, 16);
-                total -= __shfl_sync(0xffffffffu, m, column_of_lane(lane));
+                total -= __shfl_sync(0xffffffffu, m, my_column);
             }
             totals[r] = total;
         }
         const uint32_t local_tile = tile - mat.first_tile;
-        const uint32_t column = local_tile * 8u + column_of_lane(lane);
+        const uint32_t column = local_tile * 8u + my_column;
         if (p.chunks == 1u) {
 #pragma unroll
             for (int r = 0; r < ROWS; ++r)
@@ -438,7 +540,7 @@ __global__ void __launch_bounds__(kGemvWarps * 32, 2) gemv_kernel(const __grid_c
         const size_t width = (size_t)p.total_tiles * 8u;
 #pragma unroll
         for (int r = 0; r < ROWS; ++r)
-            if ((lane & 3u) == 0u) p.partial[((size_t)chunk * ROWS + r) * width + (size_t)tile * 8u + column_of_lane(lane)] = totals[r];
+            if ((lane & 3u) == 0u) p.partial[((size_t)chunk * ROWS + r) * width + (size_t)tile * 8u + my_column] = totals[r];
         __threadfence();
         __syncwarp();
         uint32_t arrived = 0;

@@ -12,11 +12,6 @@ size_t candidates_workspace_bytes(uint32_t rows, uint32_t vocab);
 int launch_candidates(const float* logits, uint32_t rows, uint32_t vocab, float softcap, const void* requests,
                       void* workspace, void* results, cudaStream_t stream, bool pdl);
 
-static __global__ void advance_position_kernel(uint32_t* state, uint32_t delta) {
-    pdl_wait();
-    if (threadIdx.x == 0) state[0] += delta;
-}
-
 static uint32_t next_pow2(uint32_t v) {
     uint32_t p = 1;
     while (p < v) p <<= 1;
@@ -158,6 +153,16 @@ int Model::finalize() {
         cache.ring_k = rk; cache.ring_v = rv; cache.private_k = pk; cache.private_v = pv;
         GF_CUDA(cudaMemsetAsync(rk, 0, (size_t)cache.ring_rows * kvw * element, stream_));
         GF_CUDA(cudaMemsetAsync(rv, 0, (size_t)cache.ring_rows * kvw * element, stream_));
+    }
+    {
+        std::vector<KvPublishLayer> table(c.layers);
+        for (uint32_t l = 0; l < c.layers; ++l)
+            table[l] = KvPublishLayer{static_cast<uint8_t*>(caches_[l].ring_k), static_cast<uint8_t*>(caches_[l].ring_v),
+                                      static_cast<const uint8_t*>(caches_[l].private_k), static_cast<const uint8_t*>(caches_[l].private_v),
+                                      caches_[l].ring_rows - 1u, (uint32_t)(kvw * element)};
+        GF_TRY(device_alloc(allocations_, &publish_layers_, c.layers));
+        GF_CUDA(cudaMemcpyAsync(publish_layers_, table.data(), sizeof(KvPublishLayer) * c.layers, cudaMemcpyHostToDevice, stream_));
+        GF_CUDA(cudaStreamSynchronize(stream_));
     }
     GF_TRY(device_alloc(allocations_, &residual_, (size_t)R * c.hidden));
     GF_TRY(device_alloc(allocations_, &normalized_, (size_t)R * c.hidden));
@@ -355,14 +360,8 @@ int Model::publish(uint32_t rows) {
     if (!finalized_) return fail(GF_ERR_STATE, "plan is not finalized");
     if (rows == 0 || rows > config_.row_capacity || rows > config_.context - position_)
         return fail(GF_ERR_INVALID, "cannot publish %u rows", rows);
-    const uint32_t kvw = config_.kv_heads * config_.head_dim;
-    for (uint32_t l = 0; l < config_.layers; ++l) {
-        const LayerCache& cache = caches_[l];
-        GF_TRY(launch_kv_scatter(cache.private_k, cache.private_v, cache.ring_k, cache.ring_v, state_dev_, rows, kvw,
-                                 cache.ring_rows - 1u, config_.kv_f16, stream_, false));
-    }
-    GF_TRY(launch_kernel(advance_position_kernel, dim3(1), dim3(32), 0, stream_, false, state_dev_, rows));
-    launches_ += config_.layers + 1u;
+    GF_TRY(launch_kv_publish(publish_layers_, config_.layers, state_dev_, rows, stream_));
+    launches_ += 2u;
     position_ += rows;
     return GF_OK;
 }

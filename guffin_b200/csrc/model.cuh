@@ -104,6 +104,7 @@ private:
     void *attention_ws_ = nullptr, *matmul_ws_ = nullptr, *candidates_ws_ = nullptr;
     size_t matmul_ws_bytes_ = 0;
     uint32_t* matmul_counters_ = nullptr;
+    KvPublishLayer* publish_layers_ = nullptr;
     void *requests_dev_ = nullptr, *results_dev_ = nullptr;
     uint32_t *tokens_dev_ = nullptr, *state_dev_ = nullptr, *status_dev_ = nullptr;
     int* error_flag_ = nullptr;

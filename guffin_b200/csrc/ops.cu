@@ -361,6 +361,35 @@ __global__ void __launch_bounds__(256) kv_scatter_kernel(const uint8_t* __restri
     }
 }
 
+// All layers at once: block (row, layer) copies that layer's private row into its ring; the last
+// block advances the committed position after every copy of the launch has been issued (the
+// position is only read by later launches).
+__global__ void __launch_bounds__(128) kv_publish_kernel(const KvPublishLayer* __restrict__ layers, uint32_t* base_position,
+                                                         uint32_t rows) {
+    pdl_wait();
+    const uint32_t row = blockIdx.x, layer = blockIdx.y;
+    const KvPublishLayer L = layers[layer];
+    const uint32_t base = *base_position;
+    const size_t dst = (size_t)((base + row) & L.ring_mask) * L.row_bytes, src = (size_t)row * L.row_bytes;
+    for (uint32_t b = threadIdx.x * 16u; b < L.row_bytes; b += blockDim.x * 16u) {
+        *reinterpret_cast<uint4*>(L.ring_k + dst + b) = *reinterpret_cast<const uint4*>(L.private_k + src + b);
+        *reinterpret_cast<uint4*>(L.ring_v + dst + b) = *reinterpret_cast<const uint4*>(L.private_v + src + b);
+    }
+}
+
+__global__ void advance_position_kernel(uint32_t* state, uint32_t delta) {
+    pdl_wait();
+    if (threadIdx.x == 0) state[0] += delta;
+}
+
+int launch_kv_publish(const KvPublishLayer* layers_dev, uint32_t layer_count, uint32_t* base_position, uint32_t rows,
+                      cudaStream_t stream) {
+    const int status = launch_kernel(kv_publish_kernel, dim3(rows, layer_count), dim3(128), 0, stream, false, layers_dev,
+                                     base_position, rows);
+    if (status != GF_OK) return status;
+    return launch_kernel(advance_position_kernel, dim3(1), dim3(32), 0, stream, false, base_position, rows);
+}
+
 // ------------------------------------------------------------------ launchers
 
 int launch_embedding(int dtype, const void* packed, uint32_t k, uint32_t vocab, const uint32_t* tokens, uint32_t rows,

@@ -47,6 +47,14 @@ struct AttentionParams {
     int kv_f16;
 };
 
+struct KvPublishLayer {          // one per layer, device resident
+    uint8_t *ring_k, *ring_v;
+    const uint8_t *private_k, *private_v;
+    uint32_t ring_mask, row_bytes;
+};
+int launch_kv_publish(const KvPublishLayer* layers_dev, uint32_t layer_count, uint32_t* base_position, uint32_t rows,
+                      cudaStream_t stream);
+
 int launch_embedding(int dtype, const void* packed, uint32_t k, uint32_t vocab, const uint32_t* tokens,
                      uint32_t rows, float scale, float* out, uint32_t* status, cudaStream_t stream, bool pdl);
 int launch_rms_norm(const float* x, const float* gamma, const float* residual, float* out, uint32_t rows,
