@@ -239,3 +239,76 @@ int gf_matmul_host(int dtype, const void* packed_dev, const float* x_host, float
 }
 
 }  // extern "C"
+
+// ------------------------------------------------------------------------------------------
+// gf_matmul_static: the same product with its split-K scratch in a fixed device array.
+//
+// Some callers may not allocate device memory at the moment they need a projection: a decode
+// loop that must not hit cudaMalloc's implicit device-wide synchronisation, a host process whose
+// HBM has been handed out completely to its own pools, or a plugin that is only ever given
+// the buffers it reads and writes.  For them the scratch the kernel needs (arrival counters
+// and per-chunk partial sums) and the error word live in this translation unit's static
+// device storage, which every GPU that loads the library holds until the process exits.
+namespace {
+
+constexpr size_t kStaticScratchBytes = 8u << 20;   // 8 MiB per GPU
+static __device__ __align__(256) unsigned char g_static_scratch[kStaticScratchBytes];
+static __device__ __align__(256) int g_static_error_flag[64];
+
+struct StaticScratch { unsigned char* scratch = nullptr; int* error_flag = nullptr; };
+
+// In host code the array names above are host-side stand-ins, not device addresses; the
+// device address comes from cudaGetSymbolAddress, once per device, with that device current.
+int static_scratch_for_current_device(StaticScratch& out) {
+    static StaticScratch per_device[64];
+    static std::mutex guard;
+    int device = 0;
+    GF_CUDA(cudaGetDevice(&device));
+    if (device < 0 || device >= 64) return fail(GF_ERR_INVALID, "gf_matmul_static: device index %d out of range", device);
+    std::lock_guard<std::mutex> lock(guard);
+    StaticScratch& slot = per_device[device];
+    if (!slot.scratch) {
+        void* scratch = nullptr;
+        void* flag = nullptr;
+        GF_CUDA(cudaGetSymbolAddress(&scratch, g_static_scratch));
+        GF_CUDA(cudaGetSymbolAddress(&flag, g_static_error_flag));
+        slot.scratch = static_cast<unsigned char*>(scratch);
+        slot.error_flag = static_cast<int*>(flag);
+    }
+    out = slot;
+    return GF_OK;
+}
+
+}  // namespace
+
+extern "C" {
+
+size_t gf_matmul_static_capacity(void) { return kStaticScratchBytes; }
+
+int gf_matmul_static(int dtype, const void* packed_dev, const float* x_dev, float* y_dev, uint32_t rows, uint64_t k,
+                     uint64_t n, void* stream) {
+    const GemvLaunch launch = single(dtype, packed_dev ? packed_dev : reinterpret_cast<const void*>(1), x_dev,
+                                     y_dev ? y_dev : reinterpret_cast<float*>(1), rows, k, n);
+    GemvPlan plan;
+    const int status = gemv_plan(launch, plan);
+    if (status != GF_OK) return status;
+    const size_t counters = gemv_counter_bytes(launch), partial = gemv_partial_bytes(launch);
+    if (counters + partial > kStaticScratchBytes)
+        return fail(GF_ERR_INVALID,
+                    "gf_matmul_static: this shape needs %zu bytes of split-K scratch but the built-in array holds %zu; "
+                    "use gf_matmul with a caller-provided workspace",
+                    counters + partial, (size_t)kStaticScratchBytes);
+    if (!packed_dev || !x_dev || !y_dev) return fail(GF_ERR_INVALID, "gf_matmul_static: null buffer");
+    StaticScratch device;
+    const int setup = static_scratch_for_current_device(device);
+    if (setup != GF_OK) return setup;
+    cudaStream_t s = as_stream(stream);
+    // The array keeps whatever the previous call left: the arrival counters and the error word
+    // must start at zero, the partial sums are fully overwritten before they are read.
+    if (counters) GF_CUDA(cudaMemsetAsync(device.scratch, 0, counters, s));
+    GF_CUDA(cudaMemsetAsync(device.error_flag, 0, sizeof(int), s));
+    return gemv_launch(launch, reinterpret_cast<uint32_t*>(device.scratch), reinterpret_cast<float*>(device.scratch + counters),
+                       partial, device.error_flag, s, false);
+}
+
+}  // extern "C"

@@ -71,6 +71,7 @@ def _declare(L: C.CDLL) -> None:
         "gf_matmul": [i32, vp, vp, vp, u32, u64, u64, vp, vp],
         "gf_matmul_check": [vp],
         "gf_matmul_host": [i32, vp, vp, vp, u32, u64, u64],
+        "gf_matmul_static": [i32, vp, vp, vp, u32, u64, u64, vp],
     }
     for name, args in sigs.items():
         fn = getattr(L, name)
@@ -80,6 +81,8 @@ def _declare(L: C.CDLL) -> None:
     L.gf_packed_weight_bytes.restype = sz
     L.gf_matmul_workspace_bytes.argtypes = [i32, u32, u64, u64]
     L.gf_matmul_workspace_bytes.restype = sz
+    L.gf_matmul_static_capacity.argtypes = []
+    L.gf_matmul_static_capacity.restype = sz
     _apply(L, SIGNATURES)
 
 

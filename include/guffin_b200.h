@@ -95,6 +95,20 @@ GF_API int gf_matmul(int dtype, const void* packed_dev, const float* x_dev, floa
  * up (GF_ERR_TIMEOUT); synchronises `stream`.  The analogue of reading the command buffer's
  * status after wait_until_completed (metal_command_context.mm:2316-2344). */
 GF_API int gf_matmul_check(void* stream);
+/* No counterpart in the reference.  gf_matmul for callers that cannot allocate device memory when
+ * they need a projection (a latency-critical loop that must avoid cudaMalloc's device-wide stall,
+ * a process whose HBM is already fully handed out to its own pools, a plugin that only receives
+ * its input and output buffers): the split-K scratch is a fixed array of
+ * gf_matmul_static_capacity() bytes (8 MiB) inside the library, held by every GPU that loads it.
+ * The caller passes only the weights, x and y.  Shapes whose scratch would not fit are rejected
+ * with GF_ERR_INVALID and a message naming both sizes.  No allocation is made, here or in
+ * anything this calls.  The first call on a device looks the array's device address up (with that
+ * device current); make that first call before starting any stream capture.  All calls on a
+ * device share the one array: the call zeroes the counters it needs, but two calls whose kernels
+ * can overlap on the GPU (different streams without ordering) race on it. */
+GF_API size_t gf_matmul_static_capacity(void);
+GF_API int gf_matmul_static(int dtype, const void* packed_dev, const float* x_dev, float* y_dev,
+                            uint32_t rows, uint64_t k, uint64_t n, void* stream);
 /* Same product from HOST buffers through an internal context: uploads x, runs, downloads y.
  * `packed_dev` stays device-resident (weights are uploaded once at load time). */
 GF_API int gf_matmul_host(int dtype, const void* packed_dev, const float* x_host, float* y_host,
