@@ -29,11 +29,51 @@ __host__ __device__ inline uint32_t block_elements(int dtype) { return dtype == 
 __host__ __device__ inline uint32_t block_bytes(int dtype) {
     return dtype == GF_Q8_0 ? 34u : dtype == GF_Q4_K ? 144u : 210u;
 }
-// The streaming layout groups 8 output columns over one K "unit": 256 elements for the
-// K-quants, 128 elements (four blocks) for Q8_0.
+// The streaming layout groups 16 output columns (two column tiles of 8) over one K "unit":
+// 256 elements for the K-quants, 128 elements (four blocks) for Q8_0.  One group is a "pair row".
 __host__ __device__ inline uint32_t unit_elements(int dtype) { return dtype == GF_Q8_0 ? 128u : 256u; }
-__host__ __device__ inline uint32_t unit_row_bytes(int dtype) {
-    return dtype == GF_Q8_0 ? 1088u : dtype == GF_Q4_K ? 1152u : 1680u;
+__host__ __device__ inline uint32_t unit_native_bytes(int dtype) {
+    return dtype == GF_Q8_0 ? 136u : dtype == GF_Q4_K ? 144u : 210u;
+}
+__host__ __device__ inline uint32_t pair_row_bytes(int dtype) { return 16u * unit_native_bytes(dtype); }
+
+// Where byte `native` (offset inside one column's native unit) of column `c16` of a group lives
+// inside the group's pair row.  The quantised codes are laid out in tensor-core fragment order:
+// lane (g, t) of a warp (g = lane / 4, t = lane % 4) feeds rows g (column g) and g + 8 (column
+// g + 8) of a 16 x 16 A operand whose sixteen K positions are sixteen consecutive elements,
+// lane t supplying elements 4t .. 4t+3, and it finds every word it needs for one loop body in
+// 16 consecutive bytes at lane * 16 of a 512-byte plane:
+//   Q4_K (2304 B): plane c (64-element chunk c)      = words {A.w0, A.w1, B.w0, B.w1}, A/B = column g / g+8,
+//                  w = which 16 of the chunk's 32 code bytes; then header[16][16] (d, dmin, scales)
+//   Q6_K (3360 B): per 128-element half h three planes: column g's ql words {s0 even, s0 odd, s1 even, s1 odd},
+//                  the same for column g+8, and qh words {A.s0, A.s1, B.s0, B.s1} (s = which 16 of 32 bytes,
+//                  even / odd = ql bytes 0-31 / 32-63 of the half); then scales[16][16], d[16][2]
+//   Q8_0 (2176 B): plane b (32-element block b)      = words {A.w0, A.w1, B.w0, B.w1}; then d[16][4][2]
+// Only 16-bit words move (all fields are 2-byte aligned in the native blocks), so the mapping is a
+// bijection and unpacking restores the native payload byte for byte.
+__host__ __device__ inline uint32_t packed_offset(int dtype, uint32_t c16, uint32_t native) {
+    const uint32_t g = c16 & 7u, tb = c16 >> 3;
+    if (dtype == GF_Q4_K) {
+        if (native < 16u) return 2048u + c16 * 16u + native;
+        const uint32_t o = native - 16u, word = o >> 2, c = word >> 3, w = (word >> 2) & 1u, t = word & 3u;
+        return c * 512u + (g * 4u + t) * 16u + (tb * 2u + w) * 4u + (o & 3u);
+    }
+    if (dtype == GF_Q6_K) {
+        if (native < 128u) {
+            const uint32_t word = native >> 2, h = word >> 4, odd = (word >> 3) & 1u, s = (word >> 2) & 1u, t = word & 3u;
+            return h * 1536u + tb * 512u + (g * 4u + t) * 16u + (2u * s + odd) * 4u + (native & 3u);
+        }
+        if (native < 192u) {
+            const uint32_t o = native - 128u, word = o >> 2, h = word >> 3, s = (word >> 2) & 1u, t = word & 3u;
+            return h * 1536u + 1024u + (g * 4u + t) * 16u + (tb * 2u + s) * 4u + (o & 3u);
+        }
+        if (native < 208u) return 3072u + c16 * 16u + (native - 192u);
+        return 3328u + c16 * 2u + (native - 208u);
+    }
+    const uint32_t b = native / 34u, o = native % 34u;
+    if (o < 2u) return 2048u + c16 * 8u + b * 2u + o;
+    const uint32_t q = o - 2u, word = q >> 2, w = word >> 2, t = word & 3u;
+    return b * 512u + (g * 4u + t) * 16u + (tb * 2u + w) * 4u + (q & 3u);
 }
 
 #ifdef __CUDACC__

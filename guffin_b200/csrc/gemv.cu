@@ -1,23 +1,24 @@
 // Host side of the streaming dequant-GEMV: decomposition plan, launch, C entry points.
 #include "gemv.cuh"
 
+#include <algorithm>
 #include <mutex>
 
 namespace gf {
 
-static uint32_t max_chunk_units(uint32_t rows, uint32_t unit_elems, uint32_t variants, bool sums) {
+static uint32_t max_chunk_units(uint32_t rows, uint32_t unit_elems, uint32_t slot_bytes, uint32_t table_bytes) {
     uint32_t best = 0;
-    for (uint32_t cu = 1; cu <= 16u; ++cu)
-        if (gemv_smem_layout(rows, cu, unit_elems, variants, sums).total <= kGemvSmemBudget) best = cu;
+    for (uint32_t cu = 1; cu <= 64u; ++cu)
+        if (gemv_smem_layout(rows, cu, unit_elems, slot_bytes, table_bytes).total <= kGemvSmemLimit) best = cu;
     return best;
 }
 
 int gemv_plan(const GemvLaunch& launch, GemvPlan& plan) {
     if (launch.count == 0 || launch.count > (uint32_t)kGemvMaxMatrices) return fail(GF_ERR_INVALID, "gf_matmul: 1..3 matrices per launch");
     if (launch.rows == 0 || launch.rows > GF_MAX_ROWS) return fail(GF_ERR_INVALID, "gf_matmul: rows=%u outside [1, %d]", launch.rows, GF_MAX_ROWS);
-    plan.needs_scaled = plan.needs_plain = 0;
-    plan.total_tiles = 0;
+    plan.total_pairs = 0;
     plan.unit_elems = 0;
+    plan.slot_bytes = plan.table_bytes = 0;
     for (uint32_t i = 0; i < launch.count; ++i) {
         const int dtype = launch.matrices[i].dtype;
         if (dtype != GF_Q8_0 && dtype != GF_Q4_K && dtype != GF_Q6_K) return fail(GF_ERR_INVALID, "gf_matmul: unsupported weight dtype %d", dtype);
@@ -25,17 +26,17 @@ int gemv_plan(const GemvLaunch& launch, GemvPlan& plan) {
         if (plan.unit_elems && plan.unit_elems != unit) return fail(GF_ERR_INVALID, "gf_matmul: Q8_0 and K-quant matrices cannot share a launch");
         plan.unit_elems = unit;
         if (launch.matrices[i].n == 0 || launch.matrices[i].n > (1ull << 28)) return fail(GF_ERR_INVALID, "gf_matmul: N must be positive");
-        plan.total_tiles += (uint32_t)((launch.matrices[i].n + 7u) / 8u);
-        if (dtype == GF_Q4_K) plan.needs_scaled = 1; else plan.needs_plain = 1;
+        plan.total_pairs += (uint32_t)((launch.matrices[i].n + 15u) / 16u);
+        plan.slot_bytes = std::max(plan.slot_bytes, pair_row_bytes(dtype));
+        plan.table_bytes = std::max(plan.table_bytes, gemv_table_bytes(dtype));
     }
     if (launch.k == 0 || launch.k % plan.unit_elems != 0 || launch.k > (1ull << 24))
         return fail(GF_ERR_INVALID, "gf_matmul: K=%llu must be a positive multiple of %u", (unsigned long long)launch.k, plan.unit_elems);
     plan.units = (uint32_t)(launch.k / plan.unit_elems);
-    const uint32_t variants = plan.needs_scaled + plan.needs_plain;
-    const uint32_t limit = max_chunk_units(launch.rows, plan.unit_elems, variants, plan.needs_scaled != 0);
+    const uint32_t limit = max_chunk_units(launch.rows, plan.unit_elems, plan.slot_bytes, plan.table_bytes);
     if (limit == 0) return fail(GF_ERR_INVALID, "gf_matmul: no decomposition fits");
-    const uint32_t slots = (uint32_t)sm_count() * 2u;      // two CTAs per SM
-    // Critical path of a warp, in unit rows: rounds x (units per item + per-item overhead); the
+    const uint32_t slots = (uint32_t)sm_count();           // one CTA per SM
+    // Critical path of a warp, in pair rows: rounds x (units per item + per-item overhead); the
     // split-K hand-over costs about one more.  Ties go to fewer chunks.
     double best = 1e30;
     plan.chunks = 0;
@@ -45,7 +46,7 @@ int gemv_plan(const GemvLaunch& launch, GemvPlan& plan) {
         if (chunk_units > limit) continue;
         const uint32_t group_ctas = slots / chunks;
         const uint32_t group_warps = group_ctas * kGemvWarps;
-        const uint32_t rounds = (plan.total_tiles + group_warps - 1u) / group_warps;
+        const uint32_t rounds = (plan.total_pairs + group_warps - 1u) / group_warps;
         const double cost = (double)rounds * ((double)chunk_units + 2.0 + (chunks > 1u ? 1.0 : 0.0));
         if (cost < best - 1e-9) {
             best = cost;
@@ -55,16 +56,16 @@ int gemv_plan(const GemvLaunch& launch, GemvPlan& plan) {
         }
     }
     if (plan.chunks == 0) return fail(GF_ERR_INVALID, "gf_matmul: no decomposition fits K=%llu rows=%u", (unsigned long long)launch.k, launch.rows);
-    plan.smem = gemv_smem_layout(launch.rows, plan.chunk_units, plan.unit_elems, variants, plan.needs_scaled != 0).total;
+    plan.smem = gemv_smem_layout(launch.rows, plan.chunk_units, plan.unit_elems, plan.slot_bytes, plan.table_bytes).total;
     return GF_OK;
 }
 
-static size_t counters_bytes(const GemvPlan& plan) { return ((size_t)plan.total_tiles * 4u + 255u) & ~(size_t)255u; }
+static size_t counters_bytes(const GemvPlan& plan) { return ((size_t)plan.total_pairs * 4u + 255u) & ~(size_t)255u; }
 
 size_t gemv_partial_bytes(const GemvLaunch& launch) {
     GemvPlan plan;
     if (gemv_plan(launch, plan) != GF_OK || plan.chunks == 1) return 0;
-    return (size_t)plan.chunks * launch.rows * plan.total_tiles * 8u * sizeof(float);
+    return (size_t)plan.chunks * launch.rows * plan.total_pairs * 16u * sizeof(float);
 }
 
 size_t gemv_counter_bytes(const GemvLaunch& launch) {
@@ -80,7 +81,7 @@ static int launch_instance(const GemvParams& p, const GemvPlan& plan, cudaStream
     cudaGetDevice(&device);
     cudaError_t attr_error = cudaSuccess;
     std::call_once(once[device & 63], [&] {
-        attr_error = cudaFuncSetAttribute(gemv_kernel<ROWS>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)kGemvSmemBudget);
+        attr_error = cudaFuncSetAttribute(gemv_kernel<ROWS>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)kGemvSmemLimit);
     });
     GF_CUDA(attr_error);
     cudaLaunchConfig_t config = {};
@@ -103,6 +104,10 @@ int gemv_launch(const GemvLaunch& launch, uint32_t* counters, float* partial, si
     const int status = gemv_plan(launch, plan);
     if (status != GF_OK) return status;
     if (!launch.in || !error_flag) return fail(GF_ERR_INVALID, "gf_matmul: null buffer");
+    // The activation prologue reads four floats at a time.
+    auto aligned = [](const void* ptr) { return (reinterpret_cast<uintptr_t>(ptr) & 15u) == 0u; };
+    if (!aligned(launch.in) || !aligned(launch.residual) || !aligned(launch.gamma0) || !aligned(launch.gamma1) || !aligned(launch.residual_out))
+        return fail(GF_ERR_INVALID, "gf_matmul: activation, residual and norm-weight pointers must be 16-byte aligned");
     if ((launch.prologue == kPrologueNorm && !launch.gamma1)
         || (launch.prologue == kPrologueAddNorm && (!launch.gamma0 || !launch.gamma1 || !launch.residual || !launch.residual_out))
         || (launch.prologue == kPrologueGeglu && !launch.residual) || launch.prologue > kPrologueGeglu)
@@ -115,27 +120,27 @@ int gemv_launch(const GemvLaunch& launch, uint32_t* counters, float* partial, si
         p.m[i].weight = static_cast<const uint8_t*>(d.packed);
         p.m[i].out = d.out;
         p.m[i].n = (uint32_t)d.n;
-        p.m[i].tiles = (uint32_t)((d.n + 7u) / 8u);
+        p.m[i].pairs = (uint32_t)((d.n + 15u) / 16u);
         p.m[i].dtype = (uint32_t)d.dtype;
-        p.m[i].first_tile = first;
-        first += p.m[i].tiles;
+        p.m[i].first_pair = first;
+        first += p.m[i].pairs;
     }
     p.matrices = launch.count;
-    p.total_tiles = plan.total_tiles;
+    p.total_pairs = plan.total_pairs;
     p.k = (uint32_t)launch.k;
     p.units = plan.units;
     p.unit_elems = plan.unit_elems;
     p.chunks = plan.chunks;
     p.chunk_units = plan.chunk_units;
-    p.needs_scaled = plan.needs_scaled;
-    p.needs_plain = plan.needs_plain;
+    p.slot_bytes = plan.slot_bytes;
+    p.table_bytes = plan.table_bytes;
     p.prologue = launch.prologue;
     p.in = launch.in; p.residual = launch.residual; p.gamma0 = launch.gamma0; p.gamma1 = launch.gamma1;
     p.residual_out = launch.residual_out;
     p.eps = launch.eps;
     p.error_flag = error_flag;
     if (plan.chunks > 1) {
-        const size_t need = (size_t)plan.chunks * launch.rows * plan.total_tiles * 8u * sizeof(float);
+        const size_t need = (size_t)plan.chunks * launch.rows * plan.total_pairs * 16u * sizeof(float);
         if (!counters || !partial || partial_bytes < need) return fail(GF_ERR_INVALID, "gf_matmul: this shape needs a %zu-byte split-K workspace", need);
         p.counters = counters;
         p.partial = partial;

@@ -12,35 +12,36 @@ namespace gf {
 // reference's rounding (quantization.cpp:457,517,590), then scales it (model.cpp:599-605).
 __device__ __forceinline__ float packed_element(int dtype, const uint8_t* packed, uint32_t units, uint32_t token,
                                                 uint32_t e) {
-    const uint32_t tile = token >> 3, c = token & 7u;
+    const uint32_t unit = unit_elements(dtype), c16 = token & 15u;
+    const uint8_t* base = packed + ((size_t)(token >> 4) * units + e / unit) * pair_row_bytes(dtype);
+    // Byte `o` of the column's native unit (bytes keep their place inside a moved 16-bit word).
+    auto byte_at = [&](uint32_t o) -> uint32_t { return base[packed_offset(dtype, c16, o & ~1u) + (o & 1u)]; };
+    auto half_at = [&](uint32_t o) -> float {
+        return __half2float(__ushort_as_half(*reinterpret_cast<const unsigned short*>(base + packed_offset(dtype, c16, o))));
+    };
+    const uint32_t i = e % unit;
     if (dtype == GF_Q6_K) {
-        const uint8_t* base = packed + ((size_t)tile * units + e / 256u) * 1680u;
-        const uint32_t i = e % 256u, half = i / 128u, w = i % 128u, lane = w % 32u, quarter = w / 32u;
-        const uint32_t lowbyte = base[c * 128u + half * 64u + (quarter % 2u) * 32u + lane];
+        const uint32_t half = i / 128u, w = i % 128u, lane = w % 32u, quarter = w / 32u;
+        const uint32_t lowbyte = byte_at(half * 64u + (quarter % 2u) * 32u + lane);
         const uint32_t low = quarter < 2u ? (lowbyte & 15u) : (lowbyte >> 4);
-        const uint32_t high = (base[1024u + c * 64u + half * 32u + lane] >> (quarter * 2u)) & 3u;
+        const uint32_t high = (byte_at(128u + half * 32u + lane) >> (quarter * 2u)) & 3u;
         const int q = (int)(low | (high << 4)) - 32;
-        const float d = __half2float(__ushort_as_half(*reinterpret_cast<const unsigned short*>(base + 1664u + c * 2u)));
-        const float s = (float)(int)(signed char)base[1536u + c * 16u + i / 16u];
-        return __fmul_rn(__fmul_rn(d, s), (float)q);
+        const float s = (float)(int)(signed char)byte_at(192u + i / 16u);
+        return __fmul_rn(__fmul_rn(half_at(208u), s), (float)q);
     }
     if (dtype == GF_Q8_0) {
-        const uint8_t* base = packed + ((size_t)tile * units + e / 128u) * 1088u;
-        const uint32_t i = e % 128u;
-        const float d = __half2float(__ushort_as_half(
-            *reinterpret_cast<const unsigned short*>(base + 1024u + c * 8u + (i / 32u) * 2u)));
-        return __fmul_rn(d, (float)(int)(signed char)base[c * 128u + i]);
+        const uint32_t block = i / 32u;
+        return __fmul_rn(half_at(block * 34u), (float)(int)(signed char)byte_at(block * 34u + 2u + i % 32u));
     }
-    const uint8_t* base = packed + ((size_t)tile * units + e / 256u) * 1152u;
-    const uint8_t* hdr = base + 1024u + c * 16u;
-    const uint32_t i = e % 256u, group = i / 32u, in64 = i % 64u;
-    const float d = __half2float(__ushort_as_half(*reinterpret_cast<const unsigned short*>(hdr)));
-    const float dmin = __half2float(__ushort_as_half(*reinterpret_cast<const unsigned short*>(hdr + 2)));
-    const uint8_t* s = hdr + 4;
+    const uint32_t group = i / 32u, in64 = i % 64u;
+    const float d = half_at(0u), dmin = half_at(2u);
     uint32_t sc, mn;
-    if (group < 4u) { sc = s[group] & 63u; mn = s[group + 4u] & 63u; }
-    else { sc = (s[group + 4u] & 15u) | ((s[group - 4u] >> 6) << 4); mn = (s[group + 4u] >> 4) | ((s[group] >> 6) << 4); }
-    const uint32_t byte = base[c * 128u + (i / 64u) * 32u + in64 % 32u];
+    if (group < 4u) { sc = byte_at(4u + group) & 63u; mn = byte_at(8u + group) & 63u; }
+    else {
+        sc = (byte_at(8u + group) & 15u) | ((byte_at(group) >> 6) << 4);
+        mn = (byte_at(8u + group) >> 4) | ((byte_at(4u + group) >> 6) << 4);
+    }
+    const uint32_t byte = byte_at(16u + (i / 64u) * 32u + in64 % 32u);
     const uint32_t q = in64 < 32u ? (byte & 15u) : (byte >> 4);
     return __fsub_rn(__fmul_rn(__fmul_rn(d, (float)sc), (float)q), __fmul_rn(dmin, (float)mn));
 }

@@ -1,13 +1,11 @@
 // Weight preparation and bit-exact dequantisation.
 //
-// Streaming layout ("columns8 units"): for column tile ct = n/8 and K unit u the group
-// [(ct * units + u) * unit_row_bytes, +unit_row_bytes) holds the native bytes of the eight
-// columns' blocks for that unit, split into planes so that a warp reads each plane with
-// conflict-free aligned shared-memory loads after one contiguous bulk copy:
-//   Q4_K (1152 B): qs[8][128] | header[8][16]  (header = d, dmin, 12 scale/min bytes)
-//   Q6_K (1680 B): ql[8][128] | qh[8][64] | scales[8][16] | d[8][2]
-//   Q8_0 (1088 B): q[8][4][32] | d[8][4][2]     (unit = four 32-element blocks)
-// Nothing is re-quantised: gf_unpack_weight restores the native payload byte for byte.
+// Streaming layout ("pair rows"): for column pair cp = n/16 and K unit u the group
+// [(cp * units + u) * pair_row_bytes, +pair_row_bytes) holds the native bytes of the sixteen
+// columns' blocks for that unit, permuted (16-bit words only) into the order the GEMV's lanes
+// consume them; packed_offset() in common.cuh is the map.  Nothing is re-quantised:
+// gf_unpack_weight restores the native payload byte for byte.  Columns beyond N inside the last
+// group are zero bytes.
 #include "common.cuh"
 
 namespace gf {
@@ -16,45 +14,29 @@ struct PackGeometry {
     int dtype;
     uint64_t units;        // K units per column
     uint64_t columns;      // N
-    uint64_t tiles;        // ceil(N / 8)
+    uint64_t pairs;        // ceil(N / 16)
     uint32_t unit_native;  // native bytes of one column's unit
-    uint32_t unit_row;     // packed bytes of eight columns' unit
+    uint32_t pair_row;     // packed bytes of sixteen columns' unit
 };
 
-// Maps a byte offset inside a packed unit row to (column-in-tile, byte offset in that
-// column's native unit).
-__host__ __device__ inline void packed_offset_to_native(int dtype, uint32_t off, uint32_t& c, uint32_t& native) {
-    if (dtype == GF_Q4_K) {
-        if (off < 1024u) { c = off / 128u; native = 16u + off % 128u; }
-        else { const uint32_t o = off - 1024u; c = o / 16u; native = o % 16u; }
-    } else if (dtype == GF_Q6_K) {
-        if (off < 1024u) { c = off / 128u; native = off % 128u; }
-        else if (off < 1536u) { const uint32_t o = off - 1024u; c = o / 64u; native = 128u + o % 64u; }
-        else if (off < 1664u) { const uint32_t o = off - 1536u; c = o / 16u; native = 192u + o % 16u; }
-        else { const uint32_t o = off - 1664u; c = o / 2u; native = 208u + o % 2u; }
-    } else {
-        if (off < 1024u) { c = off / 128u; const uint32_t r = off % 128u; native = (r / 32u) * 34u + 2u + r % 32u; }
-        else { const uint32_t o = off - 1024u; c = o / 8u; const uint32_t r = o % 8u; native = (r / 2u) * 34u + r % 2u; }
-    }
-}
-
-// One thread per packed 16-bit word (every plane boundary and native field is 2-byte aligned).
+// One thread per native 16-bit word of the (zero-extended) sixteen-column groups.
 template <bool kPack>
 __global__ void __launch_bounds__(256) repack_kernel(PackGeometry g, const uint16_t* __restrict__ src,
                                                      uint16_t* __restrict__ dst) {
-    const uint64_t words_per_row = g.unit_row / 2u;
-    const uint64_t total = g.tiles * g.units * words_per_row;
+    const uint64_t words_per_unit = g.unit_native / 2u;
+    const uint64_t total = g.pairs * g.units * 16u * words_per_unit;
     for (uint64_t w = blockIdx.x * (uint64_t)blockDim.x + threadIdx.x; w < total;
          w += (uint64_t)gridDim.x * blockDim.x) {
-        const uint64_t row = w / words_per_row;             // (ct, u)
-        const uint32_t off = (uint32_t)(w % words_per_row) * 2u;
-        const uint64_t ct = row / g.units, u = row % g.units;
-        uint32_t c, native;
-        packed_offset_to_native(g.dtype, off, c, native);
-        const uint64_t column = ct * 8u + c;
-        const uint64_t native_word = ((column * g.units + u) * g.unit_native + native) / 2u;
-        if (kPack) dst[w] = column < g.columns ? src[native_word] : (uint16_t)0;
-        else if (column < g.columns) dst[native_word] = src[w];
+        const uint32_t word = (uint32_t)(w % words_per_unit);
+        const uint64_t rest = w / words_per_unit;
+        const uint32_t c16 = (uint32_t)(rest % 16u);
+        const uint64_t row = rest / 16u;                     // (cp, u)
+        const uint64_t cp = row / g.units, u = row % g.units;
+        const uint64_t column = cp * 16u + c16;
+        const uint64_t packed_word = (row * g.pair_row + packed_offset(g.dtype, c16, word * 2u)) / 2u;
+        const uint64_t native_word = (column * g.units + u) * words_per_unit + word;
+        if (kPack) dst[packed_word] = column < g.columns ? src[native_word] : (uint16_t)0;
+        else if (column < g.columns) dst[native_word] = src[packed_word];
     }
 }
 
@@ -110,9 +92,9 @@ static int geometry(int dtype, uint64_t k, uint64_t n, PackGeometry& g) {
     g.dtype = dtype;
     g.units = k / unit;
     g.columns = n;
-    g.tiles = (n + 7u) / 8u;
-    g.unit_native = unit / block_elements(dtype) * block_bytes(dtype);
-    g.unit_row = unit_row_bytes(dtype);
+    g.pairs = (n + 15u) / 16u;
+    g.unit_native = unit_native_bytes(dtype);
+    g.pair_row = pair_row_bytes(dtype);
     return GF_OK;
 }
 
@@ -125,7 +107,7 @@ extern "C" {
 size_t gf_packed_weight_bytes(int dtype, uint64_t k, uint64_t n) {
     PackGeometry g;
     if (geometry(dtype, k, n, g) != GF_OK) return 0;
-    return (size_t)(g.tiles * g.units * g.unit_row);
+    return (size_t)(g.pairs * g.units * g.pair_row);
 }
 
 int gf_pack_weight(int dtype, const void* native_dev, uint64_t k, uint64_t n, void* packed_dev, void* stream) {

@@ -33,7 +33,8 @@ def test_packed_sizes_keep_native_byte_count():
     assert L.gf_packed_weight_bytes(lib.Q6_K, 15360, 3840) == 3840 * 60 * 210
     assert L.gf_packed_weight_bytes(lib.Q8_0, 640, 262144) == 262144 * 20 * 34
     # a ragged last tile is zero-padded to 8 columns
-    assert L.gf_packed_weight_bytes(lib.Q4_K, 256, 9) == 2 * 1152
+    assert L.gf_packed_weight_bytes(lib.Q4_K, 256, 9) == 2304           # one group of sixteen columns
+    assert L.gf_packed_weight_bytes(lib.Q4_K, 256, 17) == 2 * 2304
 
 
 def test_matmul_rejects_bad_arguments_without_a_gpu():

@@ -23,12 +23,12 @@ def test_pack_round_trip_is_lossless(gf, dtype, n):
     native = syn.make_weight(rng, dtype, k, n)
     weight = gf.PackedWeight(dtype, k, n, native)
     np.testing.assert_array_equal(weight.unpack(), native)
-    if n % 8:      # missing columns of the last tile are zero bytes
-        packed = weight.packed.download(np.uint8)
-        unit_row = {syn.Q4_K: 1152, syn.Q6_K: 1680, syn.Q8_0: 1088}[dtype]
-        last = packed.reshape(-1, unit_row)[-1]
-        plane = last[:1024].reshape(8, 128)
-        assert not plane[n % 8:].any()
+    if n % 16:     # missing columns of the last group of sixteen are zero bytes
+        padded = (n + 15) // 16 * 16
+        column_bytes = native.size // n
+        extended = np.concatenate([native, np.zeros((padded - n) * column_bytes, np.uint8)])
+        np.testing.assert_array_equal(weight.packed.download(np.uint8),
+                                      gf.PackedWeight(dtype, k, padded, extended).packed.download(np.uint8))
 
 
 @pytest.mark.parametrize("dtype", DTYPES)

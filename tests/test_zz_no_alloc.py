@@ -39,10 +39,11 @@ def test_static_scratch_matmul_matches_matmul_twice_in_a_row(gf, dtype, k, n, ro
 def test_static_scratch_rejects_shapes_beyond_its_capacity(gf):
     L = gf.load()
     assert L.gf_matmul_static_capacity() == 8 << 20
-    # Four rows of a 2048-wide, 2^20-column matrix must split K and would need ~50 MiB of partial
-    # sums.  The size check comes first, so no buffers are needed to see the refusal.
-    assert L.gf_matmul_workspace_bytes(syn.Q8_0, 4, 2048, 1 << 20) > L.gf_matmul_static_capacity()
-    status = L.gf_matmul_static(syn.Q8_0, None, None, None, 4, 2048, 1 << 20, None)
+    # Four rows over K = 65536 cannot keep their activations in one CTA's shared memory, so K must
+    # split, and 2^18 columns of partial sums per chunk exceed the array.  The size check comes
+    # first, so no buffers are needed to see the refusal.
+    assert L.gf_matmul_workspace_bytes(syn.Q8_0, 4, 1 << 16, 1 << 18) > L.gf_matmul_static_capacity()
+    status = L.gf_matmul_static(syn.Q8_0, None, None, None, 4, 1 << 16, 1 << 18, None)
     assert status == gf.GF_ERR_INVALID
     message = L.gf_last_error()
     assert b"scratch" in message and str(8 << 20).encode() in message
