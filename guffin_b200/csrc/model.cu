@@ -198,7 +198,8 @@ int Model::finalize() {
     GF_TRY(device_alloc(allocations_, &bytes, ws)); matmul_ws_ = bytes; matmul_ws_bytes_ = ws;
     GF_TRY(device_alloc(allocations_, &bytes, counters)); matmul_counters_ = reinterpret_cast<uint32_t*>(bytes);
     GF_CUDA(cudaMemsetAsync(matmul_counters_, 0, counters, stream_));   // arrival counters start (and stay) at zero
-    GF_TRY(device_alloc(allocations_, &bytes, gf_attention_workspace_bytes(R, c.heads))); attention_ws_ = bytes;
+    GF_TRY(device_alloc(allocations_, &bytes, attention_workspace_bytes(R, c.heads))); attention_ws_ = bytes;
+    GF_CUDA(cudaMemsetAsync(attention_counters(attention_ws_, R, c.heads), 0, (size_t)R * c.heads * sizeof(uint32_t), stream_));
     GF_TRY(device_alloc(allocations_, &bytes, candidates_workspace_bytes(R, c.vocab))); candidates_ws_ = bytes;
     GF_TRY(device_alloc(allocations_, &bytes, (size_t)R * gf_selection_request_bytes())); requests_dev_ = bytes;
     GF_TRY(device_alloc(allocations_, &bytes, (size_t)R * gf_candidate_result_bytes())); results_dev_ = bytes;
@@ -279,11 +280,12 @@ int Model::encode_blocks(uint32_t rows, uint32_t flags) {
         ap.private_v = cache.private_v; ap.out = attention_out_;
         ap.partial_out = static_cast<float*>(attention_ws_);
         ap.partial_ml = ap.partial_out + (size_t)c.row_capacity * c.heads * kMaxAttentionPartitions * 256u;
+        ap.counters = attention_counters(attention_ws_, c.row_capacity, c.heads);
         ap.base_position = state_dev_; ap.rows = rows; ap.heads = c.heads; ap.kv_heads = c.kv_heads; ap.head_dim = c.head_dim;
         ap.ring_mask = cache.ring_rows - 1u; ap.window = cache.window; ap.scale = c.attention_scale;
         ap.softcap = c.attn_softcap; ap.kv_f16 = c.kv_f16;
         GF_TRY(launch_attention(ap, stream_, true));
-        launches_ += 3;
+        launches_ += 2;
         GemvLaunch o;
         o.k = (uint64_t)c.heads * c.head_dim;
         o.matrices[0] = desc(w.o, projected_);

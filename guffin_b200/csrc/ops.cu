@@ -154,11 +154,22 @@ __global__ void __launch_bounds__(256) rope_store_kernel(RopeStoreParams p) {
 
 // ------------------------------------------------------------------ attention
 
-__device__ __forceinline__ void load8(const __half* p, float (&v)[8]) {
-    const uint4 raw = *reinterpret_cast<const uint4*>(p);
-    const __half2* h = reinterpret_cast<const __half2*>(&raw);
+// Eight consecutive cache elements of one lane: raw registers (so a load can be issued a whole
+// iteration before its use) and their widening to f32.
+template <typename KV> struct KvRaw;
+template <> struct KvRaw<__half> { uint4 v; };
+template <> struct KvRaw<float> { float4 a, b; };
+__device__ __forceinline__ void load_raw(const __half* p, KvRaw<__half>& r) { r.v = *reinterpret_cast<const uint4*>(p); }
+__device__ __forceinline__ void load_raw(const float* p, KvRaw<float>& r) {
+    r.a = *reinterpret_cast<const float4*>(p); r.b = *reinterpret_cast<const float4*>(p + 4);
+}
+__device__ __forceinline__ void widen(const KvRaw<__half>& r, float (&v)[8]) {
+    const __half2* h = reinterpret_cast<const __half2*>(&r.v);
 #pragma unroll
     for (int i = 0; i < 4; ++i) { const float2 f = __half22float2(h[i]); v[2 * i] = f.x; v[2 * i + 1] = f.y; }
+}
+__device__ __forceinline__ void widen(const KvRaw<float>& r, float (&v)[8]) {
+    v[0] = r.a.x; v[1] = r.a.y; v[2] = r.a.z; v[3] = r.a.w; v[4] = r.b.x; v[5] = r.b.y; v[6] = r.b.z; v[7] = r.b.w;
 }
 __device__ __forceinline__ void load8(const float* p, float (&v)[8]) {
     const float4 a = *reinterpret_cast<const float4*>(p), b = *reinterpret_cast<const float4*>(p + 4);
@@ -185,13 +196,16 @@ __device__ __forceinline__ AttentionWindow attention_window(uint32_t base, uint3
 }
 
 // Online-softmax GQA, head_dim 256: grid (kv_head, partition, row), four warps per block.  A warp
-// walks quads of cached rows; a lane owns eight of the 256 dimensions, so K and V rows are read
-// as one coalesced 512-byte (F16) or 1-KiB (F32) line per row, shared by the G query heads.
+// walks quads of cached rows, loading the next quad while it works on the current one; a lane
+// owns eight of the 256 dimensions, so K and V rows are read as one coalesced 512-byte (F16) or
+// 1-KiB (F32) line per row, shared by the G query heads.  The block that finishes last for a
+// (row, kv head) merges the partitions in partition order.
 template <typename KV, int G>
 __global__ void __launch_bounds__(128) attention_kernel(AttentionParams p) {
     __shared__ float scores[4][16];
     __shared__ float warp_m[4][G], warp_l[4][G];
     __shared__ float warp_acc[4][G][256];
+    __shared__ uint32_t arrival;
     pdl_wait();
     pdl_launch_dependents();
     const uint32_t kvh = blockIdx.x, part = blockIdx.y, row = blockIdx.z;
@@ -217,26 +231,37 @@ __global__ void __launch_bounds__(128) attention_kernel(AttentionParams p) {
 #pragma unroll
         for (int d = 0; d < 8; ++d) acc[g][d] = 0.0f;
     }
-    const uint32_t quads = (win.count + 3u) / 4u;
-    for (uint32_t quad = part * 4u + warp; quad < quads; quad += win.parts * 4u) {
-        float kf[4][8], vf[4][8];
-        bool valid[4];
+    const uint32_t quads = (win.count + 3u) / 4u, step = win.parts * 4u;
+    KvRaw<KV> kraw[4], vraw[4];
+    auto fetch = [&](uint32_t quad) {
 #pragma unroll
         for (int t = 0; t < 4; ++t) {
             const uint32_t token = quad * 4u + t;
-            valid[t] = token < win.count;
             const KV *kp, *vp;
             if (token < win.base_count) {
                 const size_t slot = ((size_t)((win.base_first + token) & p.ring_mask)) * kv_width + kvh * 256u + lane * 8u;
                 kp = ring_k + slot; vp = ring_v + slot;
             } else {
-                const uint32_t prow = valid[t] ? win.private_start + (token - win.base_count) : 0u;
+                const uint32_t prow = token < win.count ? win.private_start + (token - win.base_count) : 0u;
                 const size_t slot = (size_t)prow * kv_width + kvh * 256u + lane * 8u;
                 kp = priv_k + slot; vp = priv_v + slot;
             }
-            load8(kp, kf[t]);
-            load8(vp, vf[t]);
+            load_raw(kp, kraw[t]);
+            load_raw(vp, vraw[t]);
         }
+    };
+    uint32_t quad = part * 4u + warp;
+    if (quad < quads) fetch(quad);
+    for (; quad < quads; quad += step) {
+        float kf[4][8], vf[4][8];
+        bool valid[4];
+#pragma unroll
+        for (int t = 0; t < 4; ++t) {
+            valid[t] = quad * 4u + t < win.count;
+            widen(kraw[t], kf[t]);
+            widen(vraw[t], vf[t]);
+        }
+        if (quad + step < quads) fetch(quad + step);
         // Partial dot products (token t, head g) -> column t*G+g, reduced across the warp eight at a time.
         float s[4][G];
 #pragma unroll
@@ -313,25 +338,28 @@ __global__ void __launch_bounds__(128) attention_kernel(AttentionParams p) {
             if (d == 0) { p.partial_ml[slot * 2u] = mm; p.partial_ml[slot * 2u + 1u] = ll; }
         }
     }
-}
-
-// Merges the partitions of one (row, head) in partition order.
-__global__ void __launch_bounds__(256) attention_reduce_kernel(AttentionParams p) {
-    pdl_wait();
-    pdl_launch_dependents();
-    const uint32_t head = blockIdx.x, row = blockIdx.y, d = threadIdx.x;
-    const AttentionWindow win = attention_window(*p.base_position, row, p.window);
-    if (win.parts <= 1u) return;
-    const size_t base = ((size_t)row * p.heads + head) * kMaxAttentionPartitions;
-    float mm = -INFINITY;
-    for (uint32_t i = 0; i < win.parts; ++i) mm = fmaxf(mm, p.partial_ml[(base + i) * 2u]);
-    float a = 0.0f, ll = 0.0f;
-    for (uint32_t i = 0; i < win.parts; ++i) {
-        const float f = expf(p.partial_ml[(base + i) * 2u] - mm);
-        a = fmaf(p.partial_out[(base + i) * 256u + d], f, a);
-        ll = fmaf(p.partial_ml[(base + i) * 2u + 1u], f, ll);
+    if (win.parts == 1u) return;
+    // The block that arrives last for this (row, kv head) merges all partitions.
+    __threadfence();
+    __syncthreads();
+    if (threadIdx.x == 0) arrival = atomicAdd(&p.counters[row * p.kv_heads + kvh], 1u);
+    __syncthreads();
+    if (arrival != win.parts - 1u) return;
+    __threadfence();
+    for (uint32_t idx = threadIdx.x; idx < (uint32_t)G * 256u; idx += blockDim.x) {
+        const uint32_t head = kvh * G + idx / 256u, d = idx % 256u;
+        const size_t base = ((size_t)row * p.heads + head) * kMaxAttentionPartitions;
+        float mm = -INFINITY;
+        for (uint32_t i = 0; i < win.parts; ++i) mm = fmaxf(mm, __ldcg(&p.partial_ml[(base + i) * 2u]));
+        float a = 0.0f, ll = 0.0f;
+        for (uint32_t i = 0; i < win.parts; ++i) {
+            const float f = expf(__ldcg(&p.partial_ml[(base + i) * 2u]) - mm);
+            a = fmaf(__ldcg(&p.partial_out[(base + i) * 256u + d]), f, a);
+            ll = fmaf(__ldcg(&p.partial_ml[(base + i) * 2u + 1u]), f, ll);
+        }
+        p.out[((size_t)row * p.heads + head) * 256u + d] = a / ll;
     }
-    p.out[((size_t)row * p.heads + head) * 256u + d] = a / ll;
+    if (threadIdx.x == 0) p.counters[row * p.kv_heads + kvh] = 0u;
 }
 
 // ------------------------------------------------------------------ GeGLU, KV publication
@@ -420,8 +448,7 @@ static int launch_attention_typed(const AttentionParams& p, cudaStream_t stream,
     else if (group == 2u) status = launch_kernel(attention_kernel<KV, 2>, grid, dim3(128), 0, stream, pdl, p);
     else if (group == 4u) status = launch_kernel(attention_kernel<KV, 4>, grid, dim3(128), 0, stream, pdl, p);
     else return fail(GF_ERR_INVALID, "attention: query/KV head ratio %u unsupported (1, 2, 4)", group);
-    if (status != GF_OK) return status;
-    return launch_kernel(attention_reduce_kernel, dim3(p.heads, p.rows), dim3(256), 0, stream, pdl, p);
+    return status;
 }
 
 int launch_attention(const AttentionParams& p, cudaStream_t stream, bool pdl) {
@@ -487,7 +514,7 @@ int gf_qk_norm_rope_store(const float* raw_q_dev, const float* raw_k_dev, const 
 }
 
 size_t gf_attention_workspace_bytes(uint32_t rows, uint32_t heads) {
-    return (size_t)rows * heads * kMaxAttentionPartitions * (256u + 2u) * sizeof(float);
+    return attention_workspace_bytes(rows, heads);
 }
 
 int gf_attention(const float* q_dev, const void* ring_k_dev, const void* ring_v_dev, const void* private_k_dev,
@@ -502,6 +529,9 @@ int gf_attention(const float* q_dev, const void* ring_k_dev, const void* ring_v_
     p.out = out_dev;
     p.partial_out = static_cast<float*>(workspace_dev);
     p.partial_ml = p.partial_out + (size_t)rows * heads * kMaxAttentionPartitions * 256u;
+    p.counters = attention_counters(workspace_dev, rows, heads);
+    // The arrival counters must start at zero (a finished call leaves them zero again).
+    GF_CUDA(cudaMemsetAsync(p.counters, 0, (size_t)rows * heads * sizeof(uint32_t), as_stream(stream)));
     p.base_position = base_position_dev;
     p.rows = rows; p.heads = heads; p.kv_heads = kv_heads; p.head_dim = head_dim;
     p.ring_mask = ring_rows - 1u; p.window = window; p.scale = scale; p.softcap = softcap; p.kv_f16 = kv_f16;

@@ -8,7 +8,7 @@
 namespace gf {
 
 constexpr int kMaxAttentionPartitions = 32;   // verifier_max_partitions in the reference
-constexpr int kAttentionTokensPerPartition = 256;
+constexpr int kAttentionTokensPerPartition = 64;
 
 // Status bits shared with the reference's validation word
 // (metal_kernels.mm:2332,2357,2370,2484; metal_command_context.hpp:17).
@@ -39,6 +39,7 @@ struct AttentionParams {
     float* out;                // [rows][heads*hd]
     float* partial_out;        // [rows][heads][kMaxAttentionPartitions][hd]
     float* partial_ml;         // [rows][heads][kMaxAttentionPartitions][2]
+    uint32_t* counters;        // [rows][kv_heads] partition arrivals, zero between launches
     const uint32_t* base_position;
     uint32_t rows, heads, kv_heads, head_dim;
     uint32_t ring_mask;        // ring_rows - 1
@@ -46,6 +47,14 @@ struct AttentionParams {
     float scale, softcap;
     int kv_f16;
 };
+
+// Attention workspace: partial outputs, partial (max, sum) pairs, then the arrival counters.
+inline size_t attention_workspace_bytes(uint32_t rows, uint32_t heads) {
+    return (size_t)rows * heads * kMaxAttentionPartitions * (256u + 2u) * sizeof(float) + (size_t)rows * heads * sizeof(uint32_t);
+}
+inline uint32_t* attention_counters(void* workspace, uint32_t rows, uint32_t heads) {
+    return reinterpret_cast<uint32_t*>(static_cast<float*>(workspace) + (size_t)rows * heads * kMaxAttentionPartitions * (256u + 2u));
+}
 
 struct KvPublishLayer {          // one per layer, device resident
     uint8_t *ring_k, *ring_v;
