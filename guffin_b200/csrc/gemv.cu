@@ -6,10 +6,10 @@
 
 namespace gf {
 
-static uint32_t max_chunk_units(uint32_t rows, uint32_t unit_elems, uint32_t slot_bytes, uint32_t table_bytes) {
+static uint32_t max_chunk_units(uint32_t rows, uint32_t unit_elems, uint32_t slot_bytes) {
     uint32_t best = 0;
     for (uint32_t cu = 1; cu <= 64u; ++cu)
-        if (gemv_smem_layout(rows, cu, unit_elems, slot_bytes, table_bytes).total <= kGemvSmemLimit) best = cu;
+        if (gemv_smem_layout(rows, cu, unit_elems, slot_bytes).total <= kGemvSmemLimit) best = cu;
     return best;
 }
 
@@ -18,7 +18,7 @@ int gemv_plan(const GemvLaunch& launch, GemvPlan& plan) {
     if (launch.rows == 0 || launch.rows > GF_MAX_ROWS) return fail(GF_ERR_INVALID, "gf_matmul: rows=%u outside [1, %d]", launch.rows, GF_MAX_ROWS);
     plan.total_pairs = 0;
     plan.unit_elems = 0;
-    plan.slot_bytes = plan.table_bytes = 0;
+    plan.slot_bytes = 0;
     for (uint32_t i = 0; i < launch.count; ++i) {
         const int dtype = launch.matrices[i].dtype;
         if (dtype != GF_Q8_0 && dtype != GF_Q4_K && dtype != GF_Q6_K) return fail(GF_ERR_INVALID, "gf_matmul: unsupported weight dtype %d", dtype);
@@ -28,12 +28,11 @@ int gemv_plan(const GemvLaunch& launch, GemvPlan& plan) {
         if (launch.matrices[i].n == 0 || launch.matrices[i].n > (1ull << 28)) return fail(GF_ERR_INVALID, "gf_matmul: N must be positive");
         plan.total_pairs += (uint32_t)((launch.matrices[i].n + 15u) / 16u);
         plan.slot_bytes = std::max(plan.slot_bytes, pair_row_bytes(dtype));
-        plan.table_bytes = std::max(plan.table_bytes, gemv_table_bytes(dtype));
     }
     if (launch.k == 0 || launch.k % plan.unit_elems != 0 || launch.k > (1ull << 24))
         return fail(GF_ERR_INVALID, "gf_matmul: K=%llu must be a positive multiple of %u", (unsigned long long)launch.k, plan.unit_elems);
     plan.units = (uint32_t)(launch.k / plan.unit_elems);
-    const uint32_t limit = max_chunk_units(launch.rows, plan.unit_elems, plan.slot_bytes, plan.table_bytes);
+    const uint32_t limit = max_chunk_units(launch.rows, plan.unit_elems, plan.slot_bytes);
     if (limit == 0) return fail(GF_ERR_INVALID, "gf_matmul: no decomposition fits");
     const uint32_t slots = (uint32_t)sm_count();           // one CTA per SM
     // Critical path of a warp, in pair rows: rounds x (units per item + per-item overhead); the
@@ -56,7 +55,7 @@ int gemv_plan(const GemvLaunch& launch, GemvPlan& plan) {
         }
     }
     if (plan.chunks == 0) return fail(GF_ERR_INVALID, "gf_matmul: no decomposition fits K=%llu rows=%u", (unsigned long long)launch.k, launch.rows);
-    plan.smem = gemv_smem_layout(launch.rows, plan.chunk_units, plan.unit_elems, plan.slot_bytes, plan.table_bytes).total;
+    plan.smem = gemv_smem_layout(launch.rows, plan.chunk_units, plan.unit_elems, plan.slot_bytes).total;
     return GF_OK;
 }
 
@@ -133,7 +132,6 @@ int gemv_launch(const GemvLaunch& launch, uint32_t* counters, float* partial, si
     p.chunks = plan.chunks;
     p.chunk_units = plan.chunk_units;
     p.slot_bytes = plan.slot_bytes;
-    p.table_bytes = plan.table_bytes;
     p.prologue = launch.prologue;
     p.in = launch.in; p.residual = launch.residual; p.gamma0 = launch.gamma0; p.gamma1 = launch.gamma1;
     p.residual_out = launch.residual_out;

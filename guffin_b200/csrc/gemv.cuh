@@ -6,19 +6,20 @@
 // one-shot TMA bulk copies (cp.async.bulk + mbarrier), so no block-level synchronisation
 // happens while weights stream.
 //
-// Arithmetic: the quantised codes are integers below 256, so they are exact in bf16; a logic
-// instruction per two codes turns the packed nibbles into bf16 pairs in the register layout of
-// the A operand of mma.m16n8k16 (16 output columns x 16 K positions).  The B operand holds the
-// activations: every f32 activation is split exactly into three bf16 terms (8 + 8 + 8 mantissa
-// bits), which occupy three of the eight B columns, so one tensor-core instruction multiplies
-// 256 weights with the full-precision activations of up to two rows and accumulates in f32.
-// That removes the per-element conversion and multiply-add instructions that bound a
-// CUDA-core dequant-GEMV on issue slots rather than on HBM bandwidth.  Group scales are applied
-// to the accumulator of each scale group (two packed f32 multiply-adds per instruction group);
-// the constant offsets of the code encodings and the Q4_K minima reduce to one dot product per
-// column with the per-group activation sums, taken while the scales are decoded.
+// Arithmetic: the quantised codes are small integers, so the products run on the integer tensor
+// cores.  One logic instruction turns four packed nibbles into four u8 elements of the A operand
+// of mma.m16n8k32 (16 output columns x 32 K positions; Q8_0 bytes are the operand as they are).
+// The activations become block fixed point: every 256 consecutive elements of a row share a
+// power-of-two scale, each element is a 31-bit integer of that scale, and its four signed bytes
+// are four columns of the s8 B operand.  Integer accumulation is exact; the integer group scales
+// of Q4_K / Q6_K are applied with integer multiply-adds, and one conversion per 256-element block
+// (per 32-element block for Q8_0) brings the sum back to f32, where it meets the block's f16
+// scale and the activation scale.  The result differs from exact arithmetic by the 2^-30
+// quantisation of the activations and one f32 rounding per block, which is tighter than an f32
+// multiply-add chain.  The Q4_K minima and the Q6_K offset of 32 reduce to one dot product per
+// column with per-group activation sums, taken while the scales are decoded.
 //
-// Row r's arithmetic does not depend on how many rows are computed beside it (its three B
+// Row r's arithmetic does not depend on how many rows are computed beside it (its four B
 // columns are independent of the others), and partial sums of different K chunks are added in
 // chunk order, so results are reproducible and row-count invariant.
 #pragma once
@@ -30,6 +31,7 @@ namespace gf {
 constexpr int kGemvWarps = 16;       // warps per CTA; one CTA per SM
 constexpr int kGemvSlots = 3;        // ring depth per warp, one pair row per slot
 constexpr uint32_t kGemvSmemLimit = 226u * 1024u;    // dynamic part; the static arrays take the rest of the 227 KB
+constexpr uint32_t kGemvTableBytes = 256u;           // per warp: decoded scales of one pair row
 constexpr int kGemvMaxMatrices = 3;
 
 // How the activation rows are produced from global memory before the weights are applied.
@@ -51,7 +53,7 @@ struct GemvParams {
     uint32_t matrices, total_pairs;
     uint32_t k, units, unit_elems;
     uint32_t chunks, chunk_units;
-    uint32_t slot_bytes, table_bytes;     // ring slot size; scale table bytes per warp
+    uint32_t slot_bytes;                  // ring slot size
     uint32_t prologue;
     const float *in, *residual, *gamma0, *gamma1;
     float* residual_out;
@@ -61,28 +63,26 @@ struct GemvParams {
     int* error_flag;           // set to 1 when a bounded wait gives up
 };
 
-// Columns of the B operand kept per 16-element group: three bf16 terms per row, padded to a
-// power of two (one row) or to whole n-tiles of eight.
+// Columns of the B operand kept per 32-element group: four signed bytes per row, in whole n-tiles
+// of eight (one row uses half a tile).
 __host__ __device__ constexpr uint32_t gemv_fragment_columns(uint32_t rows) {
-    return rows == 1u ? 4u : ((3u * rows + 7u) / 8u) * 8u;
-}
-__host__ __device__ constexpr uint32_t gemv_table_bytes(int dtype) {   // per warp: 16 columns x groups x (a, a)
-    return dtype == GF_Q6_K ? 2048u : dtype == GF_Q4_K ? 1024u : 512u;
+    return rows == 1u ? 4u : ((4u * rows + 7u) / 8u) * 8u;
 }
 
 struct GemvSmemLayout {
-    uint32_t frag_bytes, sums_bytes, ring_bytes, table_bytes, total;
+    uint32_t frag_bytes, sums_bytes, scale_bytes, ring_bytes, table_bytes, total;
 };
 
 __host__ __device__ inline GemvSmemLayout gemv_smem_layout(uint32_t rows, uint32_t chunk_units, uint32_t unit_elems,
-                                                           uint32_t slot_bytes, uint32_t table_bytes) {
+                                                           uint32_t slot_bytes) {
     GemvSmemLayout s;
-    const uint32_t slice = chunk_units * unit_elems;
-    s.frag_bytes = slice * gemv_fragment_columns(rows) * 2u;
-    s.sums_bytes = rows * (slice / 16u) * 4u;
+    const uint32_t slice = chunk_units * unit_elems, padded = (slice + 255u) & ~255u;
+    s.frag_bytes = padded * gemv_fragment_columns(rows);     // 32 bytes per group per column
+    s.sums_bytes = rows * (padded / 16u) * 4u;
+    s.scale_bytes = ((rows * (padded / 256u) * 4u) + 15u) & ~15u;
     s.ring_bytes = (uint32_t)kGemvWarps * kGemvSlots * slot_bytes;
-    s.table_bytes = (uint32_t)kGemvWarps * table_bytes;
-    s.total = s.frag_bytes + s.sums_bytes + s.ring_bytes + s.table_bytes + kGemvWarps * kGemvSlots * 8u + 64u;
+    s.table_bytes = (uint32_t)kGemvWarps * kGemvTableBytes;
+    s.total = s.frag_bytes + s.sums_bytes + s.scale_bytes + s.ring_bytes + s.table_bytes + kGemvWarps * kGemvSlots * 8u + 64u;
     return s;
 }
 
@@ -102,11 +102,6 @@ __device__ __forceinline__ float2 unpack2(f32x2 v) {
     asm("mov.b64 {%0, %1}, %2;" : "=r"(lo), "=r"(hi) : "l"(v));
     return make_float2(__uint_as_float(lo), __uint_as_float(hi));
 }
-__device__ __forceinline__ f32x2 add2(f32x2 a, f32x2 b) {
-    f32x2 r;
-    asm("add.rn.f32x2 %0, %1, %2;" : "=l"(r) : "l"(a), "l"(b));
-    return r;
-}
 __device__ __forceinline__ f32x2 mul2(f32x2 a, f32x2 b) {
     f32x2 r;
     asm("mul.rn.f32x2 %0, %1, %2;" : "=l"(r) : "l"(a), "l"(b));
@@ -118,8 +113,7 @@ __device__ __forceinline__ f32x2 fma2(f32x2 a, f32x2 b, f32x2 c) {
     return r;
 }
 
-// A constant the compiler cannot fold into an immediate: a logic instruction encodes only one
-// immediate, so (w & mask) | magic is a single instruction only when the magic word is a register.
+// A constant the compiler cannot fold into an immediate (a logic instruction encodes only one).
 __device__ __forceinline__ uint32_t opaque_constant(uint32_t value) {
     uint32_t r;
     asm("mov.u32 %0, %1;" : "=r"(r) : "r"(value));
@@ -145,247 +139,225 @@ __device__ __forceinline__ f32x2 byte_pair(uint32_t v, uint32_t magic, f32x2 neg
         : "=l"(r) : "r"(v), "r"(magic), "n"(0x7540u + SEL), "n"(0x7541u + SEL), "l"(neg_bias));
     return r;
 }
-
-// D = A (16 x 16, bf16) * B (16 x 8, bf16) + C, f32 accumulation.  Lane (g, t): A registers are
-// (row g, k 2t..2t+1), (row g+8, same k), (row g, k 2t+8..2t+9), (row g+8, same k); B registers
-// are (k 2t..2t+1, column g), (k 2t+8..2t+9, column g); C/D are (row g, columns 2t..2t+1),
-// (row g+8, columns 2t..2t+1).
-__device__ __forceinline__ void mma_bf16(float (&d)[4], const uint32_t (&a)[4], uint32_t b0, uint32_t b1,
-                                         const float (&c)[4]) {
-    asm("mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0, %1, %2, %3}, {%4, %5, %6, %7}, {%8, %9}, {%10, %11, %12, %13};"
-        : "=f"(d[0]), "=f"(d[1]), "=f"(d[2]), "=f"(d[3])
-        : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b0), "r"(b1), "f"(c[0]), "f"(c[1]), "f"(c[2]), "f"(c[3]));
+// Byte K of v as an unsigned / sign-extended 32-bit integer: one byte-permute instruction.
+template <uint32_t K>
+__device__ __forceinline__ int byte_u(uint32_t v) { return (int)__byte_perm(v, 0u, 0x4440u + K); }
+template <uint32_t K>
+__device__ __forceinline__ int byte_s(uint32_t v) {
+    uint32_t r;
+    asm("prmt.b32 %0, %1, %2, %3;" : "=r"(r) : "r"(v), "r"(0u), "n"(((K | 8u) << 12) | ((K | 8u) << 8) | ((K | 8u) << 4) | K));
+    return (int)r;
 }
 
-// Nibble codes as bf16 pairs.  A code n sits in mantissa bits 3..6 of the bf16 word 0x4180
-// (16.0, whose mantissa step at those bits is 1), so the word reads 16 + n; the constant 16 per
-// element is removed through the activation sums.  Bytes (0, 2) of a 32-bit word give the pair
-// of elements (0, 2) and bytes (1, 3) the pair (1, 3), matching the activation fragments.
-constexpr uint32_t kNibbleMask = 0x00780078u;
-constexpr uint32_t kNibbleMagic = 0x41804180u;
-constexpr float kNibbleOffset = 16.0f;
-// a[0..3] for the low (HIGH = 0) or high (HIGH = 1) nibbles of word wa (column g) and wb (column g+8).
-template <int HIGH>
-__device__ __forceinline__ void nibble_fragment(uint32_t wa, uint32_t wb, uint32_t magic, uint32_t (&a)[4]) {
-    if (HIGH) {
-        a[0] = and_or<kNibbleMask>(wa >> 1, magic); a[1] = and_or<kNibbleMask>(wb >> 1, magic);
-        a[2] = and_or<kNibbleMask>(wa >> 9, magic); a[3] = and_or<kNibbleMask>(wb >> 9, magic);
-    } else {
-        a[0] = and_or<kNibbleMask>(wa << 3, magic); a[1] = and_or<kNibbleMask>(wb << 3, magic);
-        a[2] = and_or<kNibbleMask>(wa >> 5, magic); a[3] = and_or<kNibbleMask>(wb >> 5, magic);
-    }
+// Integer tensor-core products, s32 accumulation.  Lane (g, t), g = lane / 4, t = lane % 4.
+// k32: A registers are (row g, k 4t..4t+3), (row g+8, same k), (row g, k 16+4t..), (row g+8, same);
+// B registers are (k 4t..4t+3, column g), (k 16+4t.., column g).  k16: the first two A registers
+// and the first B register.  C/D are (row g, columns 2t, 2t+1), (row g+8, columns 2t, 2t+1).
+__device__ __forceinline__ void mma_u8s8_k32(int (&d)[4], const uint32_t (&a)[4], uint32_t b0, uint32_t b1, const int (&c)[4]) {
+    asm("mma.sync.aligned.m16n8k32.row.col.s32.u8.s8.s32 {%0, %1, %2, %3}, {%4, %5, %6, %7}, {%8, %9}, {%10, %11, %12, %13};"
+        : "=r"(d[0]), "=r"(d[1]), "=r"(d[2]), "=r"(d[3])
+        : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b0), "r"(b1), "r"(c[0]), "r"(c[1]), "r"(c[2]), "r"(c[3]));
+}
+__device__ __forceinline__ void mma_s8s8_k32(int (&d)[4], const uint32_t (&a)[4], uint32_t b0, uint32_t b1, const int (&c)[4]) {
+    asm("mma.sync.aligned.m16n8k32.row.col.s32.s8.s8.s32 {%0, %1, %2, %3}, {%4, %5, %6, %7}, {%8, %9}, {%10, %11, %12, %13};"
+        : "=r"(d[0]), "=r"(d[1]), "=r"(d[2]), "=r"(d[3])
+        : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b0), "r"(b1), "r"(c[0]), "r"(c[1]), "r"(c[2]), "r"(c[3]));
+}
+__device__ __forceinline__ void mma_u8s8_k16(int (&d)[4], uint32_t a0, uint32_t a1, uint32_t b0, const int (&c)[4]) {
+    asm("mma.sync.aligned.m16n8k16.row.col.s32.u8.s8.s32 {%0, %1, %2, %3}, {%4, %5}, {%6}, {%7, %8, %9, %10};"
+        : "=r"(d[0]), "=r"(d[1]), "=r"(d[2]), "=r"(d[3])
+        : "r"(a0), "r"(a1), "r"(b0), "r"(c[0]), "r"(c[1]), "r"(c[2]), "r"(c[3]));
+}
+
+// Per-lane context of the consumer loops.
+struct GemvLane {
+    uint32_t lane, g, t;
+    f32x2 digit_weight;       // (256^i0, 256^i1): weights of the two B columns this lane's C registers hold
+};
+
+// Adds the integer sums of one activation block to the f32 accumulators.  sums = (row g: columns
+// 2t, 2t+1; row g+8: the same); block_scale = the activation block's power of two for this lane's
+// row; dA / dB = the f16 block scales of output columns g / g + 8.
+__device__ __forceinline__ void fold_block(const int (&sums)[4], float block_scale, float dA, float dB,
+                                           const GemvLane& L, f32x2& accA, f32x2& accB) {
+    const f32x2 w = mul2(pack2f(block_scale, block_scale), L.digit_weight);
+    accA = fma2(mul2(pack2f(dA, dA), w), pack2f(__int2float_rn(sums[0]), __int2float_rn(sums[1])), accA);
+    accB = fma2(mul2(pack2f(dB, dB), w), pack2f(__int2float_rn(sums[2]), __int2float_rn(sums[3])), accB);
 }
 
 // ---- one pair row (16 columns x one K unit) of each format.  `row` points at the pair row in
-// shared memory, `frag` at this lane's activation fragments of the unit's first 32-element
-// group, `sums` at the unit's first per-16 activation sum of row 0, `table` at this warp's
-// scale table.  accA / accB are (columns 2t, 2t+1 of the B operand) for output column g / g + 8;
-// macc[r] collects this lane's share of the correction dot product of column (lane & 15).
-// FRAG_STRIDE = bytes between consecutive 32-element groups of fragments.
+// shared memory, `frag` at this lane's B registers of the unit's first 32-element group, `sums`
+// at the unit's first per-16 activation sum of row 0, `scales` at the unit's activation block
+// scale of this lane's row, `table` at this warp's scratch table.  accA / accB are (columns 2t,
+// 2t+1 of the B operand) for output column g / g + 8; macc[r] collects this lane's share of the
+// correction dot product of column (lane & 15).  FRAG_STRIDE = bytes between consecutive
+// 32-element groups of B registers; n-tile nt starts 256 bytes further.
 
 template <int ROWS, int NT, uint32_t FRAG_STRIDE>
 __device__ __forceinline__ void pair_row_q4k(const uint8_t* row, const uint8_t* frag, const float* sums,
-                                             uint32_t sums_stride, uint8_t* table, uint32_t lane,
-                                             f32x2 (&accA)[NT], f32x2 (&accB)[NT], float (&macc)[ROWS]) {
+                                             uint32_t sums_stride, const float* scales, uint8_t* table,
+                                             const GemvLane& L, f32x2 (&accA)[NT], f32x2 (&accB)[NT], float (&macc)[ROWS]) {
     // Phase A: lane (column, half) decodes the 6-bit scales and minima of groups 4*half .. 4*half+3.
     {
-        const uint32_t col = lane & 15u, hf = lane >> 4;
+        const uint32_t col = L.lane & 15u, hf = L.lane >> 4;
         const uint4 hdr = *reinterpret_cast<const uint4*>(row + 2048u + col * 16u);
-        const float d = __half2float(__ushort_as_half((unsigned short)(hdr.x & 0xffffu)));
         const float dmin = __half2float(__ushort_as_half((unsigned short)(hdr.x >> 16)));
         const uint32_t sc4 = hf ? ((hdr.w & 0x0f0f0f0fu) | ((hdr.y >> 2) & 0x30303030u)) : (hdr.y & 0x3f3f3f3fu);
         const uint32_t mn4 = hf ? (((hdr.w >> 4) & 0x0f0f0f0fu) | ((hdr.z >> 2) & 0x30303030u)) : (hdr.z & 0x3f3f3f3fu);
+        reinterpret_cast<uint32_t*>(table)[col * 2u + hf] = sc4;
         const uint32_t magic = opaque_constant(0x4B000000u);
         const f32x2 neg_bias = pack2f(-8388608.0f, -8388608.0f);
-        const f32x2 dd = pack2f(d, d), mm = pack2f(dmin, dmin);
-        const float2 a01 = unpack2(mul2(dd, byte_pair<0>(sc4, magic, neg_bias)));
-        const float2 a23 = unpack2(mul2(dd, byte_pair<2>(sc4, magic, neg_bias)));
+        const f32x2 mm = pack2f(dmin, dmin);
         const float2 m01 = unpack2(mul2(mm, byte_pair<0>(mn4, magic, neg_bias)));
         const float2 m23 = unpack2(mul2(mm, byte_pair<2>(mn4, magic, neg_bias)));
-        float4* dst = reinterpret_cast<float4*>(table + (col * 8u + hf * 4u) * 8u);
-        dst[0] = make_float4(a01.x, a01.x, a01.y, a01.y);
-        dst[1] = make_float4(a23.x, a23.x, a23.y, a23.y);
-        // Every code carries +16 and every element the group minimum: both multiply the group's
-        // activation sum.
-        const float b0 = fmaf(kNibbleOffset, a01.x, m01.x), b1 = fmaf(kNibbleOffset, a01.y, m01.y);
-        const float b2 = fmaf(kNibbleOffset, a23.x, m23.x), b3 = fmaf(kNibbleOffset, a23.y, m23.y);
 #pragma unroll
         for (int r = 0; r < ROWS; ++r) {
             const float4* s = reinterpret_cast<const float4*>(sums + r * sums_stride + hf * 8u);
             const float4 s0 = s[0], s1 = s[1];
-            macc[r] = fmaf(b0, s0.x + s0.y, macc[r]);
-            macc[r] = fmaf(b1, s0.z + s0.w, macc[r]);
-            macc[r] = fmaf(b2, s1.x + s1.y, macc[r]);
-            macc[r] = fmaf(b3, s1.z + s1.w, macc[r]);
+            macc[r] = fmaf(m01.x, s0.x + s0.y, macc[r]);
+            macc[r] = fmaf(m01.y, s0.z + s0.w, macc[r]);
+            macc[r] = fmaf(m23.x, s1.x + s1.y, macc[r]);
+            macc[r] = fmaf(m23.y, s1.z + s1.w, macc[r]);
         }
     }
     __syncwarp();
     // Phase B: chunk c = elements 64c .. 64c+63; its low nibbles are group 2c, its high nibbles 2c+1.
-    const uint32_t g = lane >> 2;
-    const uint32_t magic = opaque_constant(kNibbleMagic);
-    const float zero[4] = {0.0f, 0.0f, 0.0f, 0.0f};
+    const uint2 scA = *reinterpret_cast<const uint2*>(table + L.g * 8u);
+    const uint2 scB = *reinterpret_cast<const uint2*>(table + (L.g + 8u) * 8u);
+    const float dA = __half2float(__ushort_as_half(*reinterpret_cast<const unsigned short*>(row + 2048u + L.g * 16u)));
+    const float dB = __half2float(__ushort_as_half(*reinterpret_cast<const unsigned short*>(row + 2048u + (L.g + 8u) * 16u)));
+    const int zero[4] = {0, 0, 0, 0};
+    int total[NT][4];
+#pragma unroll
+    for (int nt = 0; nt < NT; ++nt)
+#pragma unroll
+        for (int i = 0; i < 4; ++i) total[nt][i] = 0;
 #pragma unroll
     for (int c = 0; c < 4; ++c) {
-        const uint4 w = *reinterpret_cast<const uint4*>(row + c * 512 + lane * 16u);
-        const ulonglong2 sA = *reinterpret_cast<const ulonglong2*>(table + (g * 8u + 2u * c) * 8u);
-        const ulonglong2 sB = *reinterpret_cast<const ulonglong2*>(table + ((g + 8u) * 8u + 2u * c) * 8u);
-        uint32_t lo0[4], lo1[4], hi0[4], hi1[4];
-        nibble_fragment<0>(w.x, w.z, magic, lo0);
-        nibble_fragment<0>(w.y, w.w, magic, lo1);
-        nibble_fragment<1>(w.x, w.z, magic, hi0);
-        nibble_fragment<1>(w.y, w.w, magic, hi1);
+        const uint4 w = *reinterpret_cast<const uint4*>(row + c * 512 + L.lane * 16u);
+        const uint32_t lo[4] = {w.x & 0x0f0f0f0fu, w.z & 0x0f0f0f0fu, w.y & 0x0f0f0f0fu, w.w & 0x0f0f0f0fu};
+        const uint32_t hi[4] = {(w.x >> 4) & 0x0f0f0f0fu, (w.z >> 4) & 0x0f0f0f0fu, (w.y >> 4) & 0x0f0f0f0fu, (w.w >> 4) & 0x0f0f0f0fu};
+        const uint32_t wordA = c < 2 ? scA.x : scA.y, wordB = c < 2 ? scB.x : scB.y;
+        const int sAl = (c & 1) ? byte_u<2>(wordA) : byte_u<0>(wordA), sAh = (c & 1) ? byte_u<3>(wordA) : byte_u<1>(wordA);
+        const int sBl = (c & 1) ? byte_u<2>(wordB) : byte_u<0>(wordB), sBh = (c & 1) ? byte_u<3>(wordB) : byte_u<1>(wordB);
 #pragma unroll
         for (int nt = 0; nt < NT; ++nt) {
-            const uint4 bl = *reinterpret_cast<const uint4*>(frag + (2 * c) * FRAG_STRIDE + nt * 512);
-            const uint4 bh = *reinterpret_cast<const uint4*>(frag + (2 * c + 1) * FRAG_STRIDE + nt * 512);
-            float cl[4], ch[4];
-            mma_bf16(cl, lo0, bl.x, bl.y, zero);
-            mma_bf16(ch, hi0, bh.x, bh.y, zero);
-            mma_bf16(cl, lo1, bl.z, bl.w, cl);
-            mma_bf16(ch, hi1, bh.z, bh.w, ch);
-            accA[nt] = fma2(sA.x, pack2f(cl[0], cl[1]), accA[nt]);
-            accB[nt] = fma2(sB.x, pack2f(cl[2], cl[3]), accB[nt]);
-            accA[nt] = fma2(sA.y, pack2f(ch[0], ch[1]), accA[nt]);
-            accB[nt] = fma2(sB.y, pack2f(ch[2], ch[3]), accB[nt]);
+            const uint2 bl = *reinterpret_cast<const uint2*>(frag + (2 * c) * FRAG_STRIDE + nt * 256);
+            const uint2 bh = *reinterpret_cast<const uint2*>(frag + (2 * c + 1) * FRAG_STRIDE + nt * 256);
+            int cl[4], ch[4];
+            mma_u8s8_k32(cl, lo, bl.x, bl.y, zero);
+            mma_u8s8_k32(ch, hi, bh.x, bh.y, zero);
+            total[nt][0] += sAl * cl[0] + sAh * ch[0];
+            total[nt][1] += sAl * cl[1] + sAh * ch[1];
+            total[nt][2] += sBl * cl[2] + sBh * ch[2];
+            total[nt][3] += sBl * cl[3] + sBh * ch[3];
         }
     }
+#pragma unroll
+    for (int nt = 0; nt < NT; ++nt) fold_block(total[nt], scales[nt], dA, dB, L, accA[nt], accB[nt]);
 }
 
-// Q6_K codes: low nibble from ql, two high bits from qh, placed in bits 0..5 of the bf16 word
-// 0x4300 (128.0, mantissa step 1), so the word reads 128 + code = 160 + q.
-constexpr float kQ6Offset = 160.0f;
-__device__ __forceinline__ uint32_t q6_pair(uint32_t ql_shifted, uint32_t qh_shifted, uint32_t magic) {
-    return and_or<0x000f000fu>(ql_shifted, and_or<0x00300030u>(qh_shifted, magic));
-}
-
+// Q6_K: code = ql nibble | two qh bits << 4 (0..63), value = code - 32; the offset goes through
+// the activation sums.
 template <int ROWS, int NT, uint32_t FRAG_STRIDE>
 __device__ __forceinline__ void pair_row_q6k(const uint8_t* row, const uint8_t* frag, const float* sums,
-                                             uint32_t sums_stride, uint8_t* table, uint32_t lane,
-                                             f32x2 (&accA)[NT], f32x2 (&accB)[NT], float (&macc)[ROWS]) {
-    {   // Phase A: lane (column, half) turns int8 sub-scales 8*half .. 8*half+7 into d*scale.
-        const uint32_t col = lane & 15u, hf = lane >> 4;
+                                             uint32_t sums_stride, const float* scales, uint8_t* table,
+                                             const GemvLane& L, f32x2 (&accA)[NT], f32x2 (&accB)[NT], float (&macc)[ROWS]) {
+    {   // Phase A: lane (column, half) accumulates d * scale_j * (sum of group j) for sub-scales 8*half .. 8*half+7.
+        const uint32_t col = L.lane & 15u, hf = L.lane >> 4;
         const uint2 s8 = *reinterpret_cast<const uint2*>(row + 3072u + col * 16u + hf * 8u);
         const float d = __half2float(__ushort_as_half(*reinterpret_cast<const unsigned short*>(row + 3328u + col * 2u)));
         const uint32_t magic = opaque_constant(0x4B000000u);
         const f32x2 neg_bias = pack2f(-(8388608.0f + 128.0f), -(8388608.0f + 128.0f));   // int8 made unsigned by flipping bit 7
         const f32x2 dd = pack2f(d, d);
         const uint32_t u0 = s8.x ^ 0x80808080u, u1 = s8.y ^ 0x80808080u;
-        float a[8];
-        { const float2 v = unpack2(mul2(dd, byte_pair<0>(u0, magic, neg_bias))); a[0] = v.x; a[1] = v.y; }
-        { const float2 v = unpack2(mul2(dd, byte_pair<2>(u0, magic, neg_bias))); a[2] = v.x; a[3] = v.y; }
-        { const float2 v = unpack2(mul2(dd, byte_pair<0>(u1, magic, neg_bias))); a[4] = v.x; a[5] = v.y; }
-        { const float2 v = unpack2(mul2(dd, byte_pair<2>(u1, magic, neg_bias))); a[6] = v.x; a[7] = v.y; }
-        float4* dst = reinterpret_cast<float4*>(table + (col * 16u + hf * 8u) * 8u);
-#pragma unroll
-        for (int j = 0; j < 4; ++j) dst[j] = make_float4(a[2 * j], a[2 * j], a[2 * j + 1], a[2 * j + 1]);
+        const float2 a01 = unpack2(mul2(dd, byte_pair<0>(u0, magic, neg_bias))), a23 = unpack2(mul2(dd, byte_pair<2>(u0, magic, neg_bias)));
+        const float2 a45 = unpack2(mul2(dd, byte_pair<0>(u1, magic, neg_bias))), a67 = unpack2(mul2(dd, byte_pair<2>(u1, magic, neg_bias)));
 #pragma unroll
         for (int r = 0; r < ROWS; ++r) {
             const float4* s = reinterpret_cast<const float4*>(sums + r * sums_stride + hf * 8u);
             const float4 s0 = s[0], s1 = s[1];
-            macc[r] = fmaf(a[0], s0.x, macc[r]); macc[r] = fmaf(a[1], s0.y, macc[r]);
-            macc[r] = fmaf(a[2], s0.z, macc[r]); macc[r] = fmaf(a[3], s0.w, macc[r]);
-            macc[r] = fmaf(a[4], s1.x, macc[r]); macc[r] = fmaf(a[5], s1.y, macc[r]);
-            macc[r] = fmaf(a[6], s1.z, macc[r]); macc[r] = fmaf(a[7], s1.w, macc[r]);
+            macc[r] = fmaf(a01.x, s0.x, macc[r]); macc[r] = fmaf(a01.y, s0.y, macc[r]);
+            macc[r] = fmaf(a23.x, s0.z, macc[r]); macc[r] = fmaf(a23.y, s0.w, macc[r]);
+            macc[r] = fmaf(a45.x, s1.x, macc[r]); macc[r] = fmaf(a45.y, s1.y, macc[r]);
+            macc[r] = fmaf(a67.x, s1.z, macc[r]); macc[r] = fmaf(a67.y, s1.w, macc[r]);
         }
     }
-    __syncwarp();
     // Phase B: half h = elements 128h .. 128h+127 = four quarters q of 32; 16-element group
     // (q, s) is scale group 8h + 2q + s.  ql byte l of the half serves quarters 0 (low nibble)
     // and 2 (high nibble), byte 32 + l quarters 1 and 3; qh byte l holds two bits per quarter.
-    const uint32_t g = lane >> 2;
-    const uint32_t magic = opaque_constant(0x43004300u);
-    const float zero[4] = {0.0f, 0.0f, 0.0f, 0.0f};
+    const uint4 scA = *reinterpret_cast<const uint4*>(row + 3072u + L.g * 16u);
+    const uint4 scB = *reinterpret_cast<const uint4*>(row + 3072u + (L.g + 8u) * 16u);
+    const float dA = __half2float(__ushort_as_half(*reinterpret_cast<const unsigned short*>(row + 3328u + L.g * 2u)));
+    const float dB = __half2float(__ushort_as_half(*reinterpret_cast<const unsigned short*>(row + 3328u + (L.g + 8u) * 2u)));
+    const int zero[4] = {0, 0, 0, 0};
+    int total[NT][4];
+#pragma unroll
+    for (int nt = 0; nt < NT; ++nt)
+#pragma unroll
+        for (int i = 0; i < 4; ++i) total[nt][i] = 0;
 #pragma unroll
     for (int h = 0; h < 2; ++h) {
-        const uint4 qa = *reinterpret_cast<const uint4*>(row + h * 1536 + lane * 16u);
-        const uint4 qb = *reinterpret_cast<const uint4*>(row + h * 1536 + 512 + lane * 16u);
-        const uint4 qh = *reinterpret_cast<const uint4*>(row + h * 1536 + 1024 + lane * 16u);
-        uint4 bf[NT][4];
-#pragma unroll
-        for (int nt = 0; nt < NT; ++nt)
-#pragma unroll
-            for (int q = 0; q < 4; ++q)
-                bf[nt][q] = *reinterpret_cast<const uint4*>(frag + (4 * h + q) * FRAG_STRIDE + nt * 512);
-        ulonglong2 sA[4], sB[4];
-#pragma unroll
-        for (int q = 0; q < 4; ++q) {
-            sA[q] = *reinterpret_cast<const ulonglong2*>(table + (g * 16u + 8u * h + 2u * q) * 8u);
-            sB[q] = *reinterpret_cast<const ulonglong2*>(table + ((g + 8u) * 16u + 8u * h + 2u * q) * 8u);
-        }
+        const uint4 qa = *reinterpret_cast<const uint4*>(row + h * 1536 + L.lane * 16u);
+        const uint4 qb = *reinterpret_cast<const uint4*>(row + h * 1536 + 512 + L.lane * 16u);
+        const uint4 qh = *reinterpret_cast<const uint4*>(row + h * 1536 + 1024 + L.lane * 16u);
+        const uint32_t lowA = h ? scA.z : scA.x, highA = h ? scA.w : scA.y;     // scale bytes 8h..8h+3, 8h+4..8h+7
+        const uint32_t lowB = h ? scB.z : scB.x, highB = h ? scB.w : scB.y;
 #pragma unroll
         for (int s = 0; s < 2; ++s) {
             const uint32_t ae = s ? qa.z : qa.x, ao = s ? qa.w : qa.y;
             const uint32_t be = s ? qb.z : qb.x, bo = s ? qb.w : qb.y;
             const uint32_t ha = s ? qh.y : qh.x, hb = s ? qh.w : qh.z;
-            uint32_t a[4][4];
-            a[0][0] = q6_pair(ae, ha << 4, magic);       a[0][1] = q6_pair(be, hb << 4, magic);
-            a[0][2] = q6_pair(ae >> 8, ha >> 4, magic);  a[0][3] = q6_pair(be >> 8, hb >> 4, magic);
-            a[1][0] = q6_pair(ao, ha << 2, magic);       a[1][1] = q6_pair(bo, hb << 2, magic);
-            a[1][2] = q6_pair(ao >> 8, ha >> 6, magic);  a[1][3] = q6_pair(bo >> 8, hb >> 6, magic);
-            a[2][0] = q6_pair(ae >> 4, ha, magic);       a[2][1] = q6_pair(be >> 4, hb, magic);
-            a[2][2] = q6_pair(ae >> 12, ha >> 8, magic); a[2][3] = q6_pair(be >> 12, hb >> 8, magic);
-            a[3][0] = q6_pair(ao >> 4, ha >> 2, magic);  a[3][1] = q6_pair(bo >> 4, hb >> 2, magic);
-            a[3][2] = q6_pair(ao >> 12, ha >> 10, magic); a[3][3] = q6_pair(bo >> 12, hb >> 10, magic);
+            uint32_t a[4][2];
+            a[0][0] = and_or<0x0f0f0f0fu>(ae, (ha << 4) & 0x30303030u);      a[0][1] = and_or<0x0f0f0f0fu>(be, (hb << 4) & 0x30303030u);
+            a[1][0] = and_or<0x0f0f0f0fu>(ao, (ha << 2) & 0x30303030u);      a[1][1] = and_or<0x0f0f0f0fu>(bo, (hb << 2) & 0x30303030u);
+            a[2][0] = and_or<0x0f0f0f0fu>(ae >> 4, ha & 0x30303030u);        a[2][1] = and_or<0x0f0f0f0fu>(be >> 4, hb & 0x30303030u);
+            a[3][0] = and_or<0x0f0f0f0fu>(ao >> 4, (ha >> 2) & 0x30303030u); a[3][1] = and_or<0x0f0f0f0fu>(bo >> 4, (hb >> 2) & 0x30303030u);
+            // Scale group 8h + 2q + s: byte 2q + s of the half's eight.
+            int sA[4], sB[4];
+            if (s == 0) {
+                sA[0] = byte_s<0>(lowA); sA[1] = byte_s<2>(lowA); sA[2] = byte_s<0>(highA); sA[3] = byte_s<2>(highA);
+                sB[0] = byte_s<0>(lowB); sB[1] = byte_s<2>(lowB); sB[2] = byte_s<0>(highB); sB[3] = byte_s<2>(highB);
+            } else {
+                sA[0] = byte_s<1>(lowA); sA[1] = byte_s<3>(lowA); sA[2] = byte_s<1>(highA); sA[3] = byte_s<3>(highA);
+                sB[0] = byte_s<1>(lowB); sB[1] = byte_s<3>(lowB); sB[2] = byte_s<1>(highB); sB[3] = byte_s<3>(highB);
+            }
 #pragma unroll
             for (int q = 0; q < 4; ++q)
 #pragma unroll
                 for (int nt = 0; nt < NT; ++nt) {
-                    float c[4];
-                    mma_bf16(c, a[q], s ? bf[nt][q].z : bf[nt][q].x, s ? bf[nt][q].w : bf[nt][q].y, zero);
-                    accA[nt] = fma2(s ? sA[q].y : sA[q].x, pack2f(c[0], c[1]), accA[nt]);
-                    accB[nt] = fma2(s ? sB[q].y : sB[q].x, pack2f(c[2], c[3]), accB[nt]);
+                    const uint32_t b = *reinterpret_cast<const uint32_t*>(frag + (4 * h + q) * FRAG_STRIDE + nt * 256 + s * 4);
+                    int c[4];
+                    mma_u8s8_k16(c, a[q][0], a[q][1], b, zero);
+                    total[nt][0] += sA[q] * c[0]; total[nt][1] += sA[q] * c[1];
+                    total[nt][2] += sB[q] * c[2]; total[nt][3] += sB[q] * c[3];
                 }
         }
     }
+#pragma unroll
+    for (int nt = 0; nt < NT; ++nt) fold_block(total[nt], scales[nt], dA, dB, L, accA[nt], accB[nt]);
 }
 
-// Q8_0: the byte with bit 7 flipped is v = q + 128 = 16 * hi + lo; both nibbles use the 16 + n
-// encoding, so (low product) + 16 * (high product) = sum (272 + v) x = sum (400 + q) x.
-constexpr float kQ80Offset = 400.0f;
-
+// Q8_0: the int8 codes are the A operand as stored; one f16 scale per 32-element block.
 template <int ROWS, int NT, uint32_t FRAG_STRIDE>
-__device__ __forceinline__ void pair_row_q80(const uint8_t* row, const uint8_t* frag, const float* sums,
-                                             uint32_t sums_stride, uint8_t* table, uint32_t lane,
-                                             f32x2 (&accA)[NT], f32x2 (&accB)[NT], float (&macc)[ROWS]) {
-    {   // Phase A: lane (column, half) widens the f16 scales of blocks 2*half, 2*half+1.
-        const uint32_t col = lane & 15u, hf = lane >> 4;
-        const uint32_t raw = *reinterpret_cast<const uint32_t*>(row + 2048u + col * 8u + hf * 4u);
-        const float d0 = __half2float(__ushort_as_half((unsigned short)(raw & 0xffffu)));
-        const float d1 = __half2float(__ushort_as_half((unsigned short)(raw >> 16)));
-        *reinterpret_cast<float4*>(table + (col * 4u + hf * 2u) * 8u) = make_float4(d0, d0, d1, d1);
-#pragma unroll
-        for (int r = 0; r < ROWS; ++r) {
-            const float4 s = *reinterpret_cast<const float4*>(sums + r * sums_stride + hf * 4u);
-            macc[r] = fmaf(d0, s.x + s.y, macc[r]);
-            macc[r] = fmaf(d1, s.z + s.w, macc[r]);
-        }
-    }
-    __syncwarp();
-    const uint32_t g = lane >> 2;
-    const uint32_t magic = opaque_constant(kNibbleMagic);
-    const float zero[4] = {0.0f, 0.0f, 0.0f, 0.0f};
-    const f32x2 sixteen = pack2f(16.0f, 16.0f);
+__device__ __forceinline__ void pair_row_q80(const uint8_t* row, const uint8_t* frag, const float* scales,
+                                             const GemvLane& L, f32x2 (&accA)[NT], f32x2 (&accB)[NT]) {
+    const uint2 dhA = *reinterpret_cast<const uint2*>(row + 2048u + L.g * 8u);          // four f16 block scales
+    const uint2 dhB = *reinterpret_cast<const uint2*>(row + 2048u + (L.g + 8u) * 8u);
+    const int zero[4] = {0, 0, 0, 0};
 #pragma unroll
     for (int b = 0; b < 4; ++b) {
-        uint4 w = *reinterpret_cast<const uint4*>(row + b * 512 + lane * 16u);
-        w.x ^= 0x80808080u; w.y ^= 0x80808080u; w.z ^= 0x80808080u; w.w ^= 0x80808080u;
-        const f32x2 dA = *reinterpret_cast<const f32x2*>(table + (g * 4u + b) * 8u);
-        const f32x2 dB = *reinterpret_cast<const f32x2*>(table + ((g + 8u) * 4u + b) * 8u);
-        uint32_t lo0[4], lo1[4], hi0[4], hi1[4];
-        nibble_fragment<0>(w.x, w.z, magic, lo0);
-        nibble_fragment<0>(w.y, w.w, magic, lo1);
-        nibble_fragment<1>(w.x, w.z, magic, hi0);
-        nibble_fragment<1>(w.y, w.w, magic, hi1);
+        const uint4 w = *reinterpret_cast<const uint4*>(row + b * 512 + L.lane * 16u);
+        const uint32_t a[4] = {w.x, w.z, w.y, w.w};
+        const uint32_t rawA = b < 2 ? dhA.x : dhA.y, rawB = b < 2 ? dhB.x : dhB.y;
+        const float dA = __half2float(__ushort_as_half((unsigned short)((b & 1) ? rawA >> 16 : rawA & 0xffffu)));
+        const float dB = __half2float(__ushort_as_half((unsigned short)((b & 1) ? rawB >> 16 : rawB & 0xffffu)));
 #pragma unroll
         for (int nt = 0; nt < NT; ++nt) {
-            const uint4 bq = *reinterpret_cast<const uint4*>(frag + b * FRAG_STRIDE + nt * 512);
-            float cl[4], ch[4];
-            mma_bf16(cl, lo0, bq.x, bq.y, zero);
-            mma_bf16(ch, hi0, bq.x, bq.y, zero);
-            mma_bf16(cl, lo1, bq.z, bq.w, cl);
-            mma_bf16(ch, hi1, bq.z, bq.w, ch);
-            accA[nt] = fma2(dA, fma2(sixteen, pack2f(ch[0], ch[1]), pack2f(cl[0], cl[1])), accA[nt]);
-            accB[nt] = fma2(dB, fma2(sixteen, pack2f(ch[2], ch[3]), pack2f(cl[2], cl[3])), accB[nt]);
+            const uint2 bq = *reinterpret_cast<const uint2*>(frag + b * FRAG_STRIDE + nt * 256);
+            int c[4];
+            mma_s8s8_k32(c, a, bq.x, bq.y, zero);
+            fold_block(c, scales[nt], dA, dB, L, accA[nt], accB[nt]);
         }
     }
 }
@@ -410,27 +382,29 @@ __device__ __forceinline__ float gemv_block_sum(float v, float* scratch) {
     return total;
 }
 
-// Exact split of two floats into three bf16 terms each: out[i] = (term i of a) | (term i of b) << 16.
-__device__ __forceinline__ void split_bf16x3(float a, float b, uint32_t (&out)[3]) {
-#pragma unroll
-    for (int i = 0; i < 3; ++i) {
-        uint32_t bits;
-        asm("cvt.rn.bf16x2.f32 %0, %1, %2;" : "=r"(bits) : "f"(b), "f"(a));   // first source -> upper half
-        out[i] = bits;
-        a = __fsub_rn(a, __uint_as_float(bits << 16));
-        b = __fsub_rn(b, __uint_as_float(bits & 0xffff0000u));
-    }
+// Four 32-bit integers whose bytes are signed base-256 digits become four words, word i holding
+// digit i of the four integers in order: a 4 x 4 byte transpose in eight byte-permutes.
+__device__ __forceinline__ void transpose_digits(const uint32_t (&w)[4], uint32_t (&digit)[4]) {
+    const uint32_t lo01 = __byte_perm(w[0], w[1], 0x5140u), lo23 = __byte_perm(w[2], w[3], 0x5140u);
+    const uint32_t hi01 = __byte_perm(w[0], w[1], 0x7362u), hi23 = __byte_perm(w[2], w[3], 0x7362u);
+    digit[0] = __byte_perm(lo01, lo23, 0x5410u); digit[1] = __byte_perm(lo01, lo23, 0x7632u);
+    digit[2] = __byte_perm(hi01, hi23, 0x5410u); digit[3] = __byte_perm(hi01, hi23, 0x7632u);
 }
 
-// Produces this CTA's K slice of the activation rows in shared memory as B-operand fragments:
-// for 32-element group G2, B column n and lane position t the 16 bytes at
-// ((G2 * NCP + n) * 4 + t) * 16 hold {(x0, x2), (x1, x3)} of elements 4t .. 4t+3 of the first
-// 16 elements and the same of the second 16, as bf16 pairs of term n % 3 of row n / 3.  Also the
-// f32 sum of every 16 consecutive elements.  The RMS norms of prologues 1 and 2 need the whole
-// row, so every CTA recomputes them from global memory (a few tens of KB out of L2).
+// Produces this CTA's K slice of the activation rows in shared memory as s8 B-operand registers.
+// A thread owns eight consecutive elements of a row, a warp 256: the warp's largest magnitude
+// fixes the block's power-of-two scale 2^(e-29), every element becomes round(x / scale), an
+// integer of at most 2^30, and adding 0x00808080 then flipping those bits makes its four bytes
+// signed base-256 digits.  For 32-element group G2, B column n = 4 * row + digit and lane
+// position t, the 8 bytes at ((G2 * NCP + n) * 4 + t) * 8 are the digit bytes of elements
+// 4t..4t+3 and 16+4t..16+4t+3 of the group.  Also written: the f32 sum of every 16 consecutive
+// elements, the block scales, and a per-row flag for non-finite inputs (whose row then yields
+// NaN).  The RMS norms of prologues 1 and 2 need the whole row, so every CTA recomputes them from
+// global memory (a few tens of KB out of L2).
 template <int ROWS>
-__device__ __forceinline__ void stage_activations(const GemvParams& p, uint32_t first, uint32_t count, uint32_t slice,
-                                                  uint8_t* frags, float* sums, float* scratch) {
+__device__ __forceinline__ void stage_activations(const GemvParams& p, uint32_t first, uint32_t count, uint32_t padded,
+                                                  uint8_t* frags, float* sums, float* block_scales, uint32_t* bad_rows,
+                                                  float* scratch) {
     constexpr uint32_t NCP = gemv_fragment_columns(ROWS);
     float inv0[ROWS], inv1[ROWS];
 #pragma unroll
@@ -467,72 +441,104 @@ __device__ __forceinline__ void stage_activations(const GemvParams& p, uint32_t 
             inv1[r] = __fdiv_rn(1.0f, __fsqrt_rn(__fadd_rn(__fdiv_rn(total2, (float)p.k), p.eps)));
         }
     }
-    const uint32_t quads = slice / 4u;      // a multiple of 32: whole warps stay together
-    for (uint32_t q = threadIdx.x; q < (uint32_t)ROWS * quads; q += blockDim.x) {
-        const uint32_t r = q / quads, o4 = q % quads, o = o4 * 4u;
-        float4 v = make_float4(0.0f, 0.0f, 0.0f, 0.0f);
+    const uint32_t pieces = padded / 8u;      // a multiple of 32: whole warps stay together
+    const uint32_t lane = threadIdx.x & 31u;
+    for (uint32_t q = threadIdx.x; q < (uint32_t)ROWS * pieces; q += blockDim.x) {
+        const uint32_t r = q / pieces, piece = q % pieces, o = piece * 8u;
+        float v[8];
+#pragma unroll
+        for (int i = 0; i < 8; ++i) v[i] = 0.0f;
         if (o < count) {
             const size_t gi = (size_t)r * p.k + first + o;
             const uint32_t c = first + o;
             float i0 = 1.0f, i1 = 1.0f;
 #pragma unroll
             for (int rr = 0; rr < ROWS; ++rr) if (rr == (int)r) { i0 = inv0[rr]; i1 = inv1[rr]; }
-            const float4 in = *reinterpret_cast<const float4*>(p.in + gi);
-            if (p.prologue == kProloguePlain) v = in;
-            else if (p.prologue == kPrologueNorm) {
-                const float4 gm = *reinterpret_cast<const float4*>(p.gamma1 + c);
-                v.x = __fmul_rn(__fmul_rn(in.x, i1), gm.x); v.y = __fmul_rn(__fmul_rn(in.y, i1), gm.y);
-                v.z = __fmul_rn(__fmul_rn(in.z, i1), gm.z); v.w = __fmul_rn(__fmul_rn(in.w, i1), gm.w);
-            } else if (p.prologue == kPrologueAddNorm) {
-                const float4 a = *reinterpret_cast<const float4*>(p.residual + gi);
-                const float4 g0 = *reinterpret_cast<const float4*>(p.gamma0 + c);
-                const float4 g1 = *reinterpret_cast<const float4*>(p.gamma1 + c);
-                v.x = __fmul_rn(__fmul_rn(__fadd_rn(a.x, __fmul_rn(__fmul_rn(in.x, i0), g0.x)), i1), g1.x);
-                v.y = __fmul_rn(__fmul_rn(__fadd_rn(a.y, __fmul_rn(__fmul_rn(in.y, i0), g0.y)), i1), g1.y);
-                v.z = __fmul_rn(__fmul_rn(__fadd_rn(a.z, __fmul_rn(__fmul_rn(in.z, i0), g0.z)), i1), g1.z);
-                v.w = __fmul_rn(__fmul_rn(__fadd_rn(a.w, __fmul_rn(__fmul_rn(in.w, i0), g0.w)), i1), g1.w);
-            } else {
-                const float4 up = *reinterpret_cast<const float4*>(p.residual + gi);
-                v.x = __fmul_rn(gelu_tanh_exact(in.x), up.x); v.y = __fmul_rn(gelu_tanh_exact(in.y), up.y);
-                v.z = __fmul_rn(gelu_tanh_exact(in.z), up.z); v.w = __fmul_rn(gelu_tanh_exact(in.w), up.w);
+#pragma unroll
+            for (int hq = 0; hq < 2; ++hq) {
+                const float4 in = *reinterpret_cast<const float4*>(p.in + gi + 4 * hq);
+                float4 out = in;
+                if (p.prologue == kPrologueNorm) {
+                    const float4 gm = *reinterpret_cast<const float4*>(p.gamma1 + c + 4 * hq);
+                    out.x = __fmul_rn(__fmul_rn(in.x, i1), gm.x); out.y = __fmul_rn(__fmul_rn(in.y, i1), gm.y);
+                    out.z = __fmul_rn(__fmul_rn(in.z, i1), gm.z); out.w = __fmul_rn(__fmul_rn(in.w, i1), gm.w);
+                } else if (p.prologue == kPrologueAddNorm) {
+                    const float4 a = *reinterpret_cast<const float4*>(p.residual + gi + 4 * hq);
+                    const float4 g0 = *reinterpret_cast<const float4*>(p.gamma0 + c + 4 * hq);
+                    const float4 g1 = *reinterpret_cast<const float4*>(p.gamma1 + c + 4 * hq);
+                    out.x = __fmul_rn(__fmul_rn(__fadd_rn(a.x, __fmul_rn(__fmul_rn(in.x, i0), g0.x)), i1), g1.x);
+                    out.y = __fmul_rn(__fmul_rn(__fadd_rn(a.y, __fmul_rn(__fmul_rn(in.y, i0), g0.y)), i1), g1.y);
+                    out.z = __fmul_rn(__fmul_rn(__fadd_rn(a.z, __fmul_rn(__fmul_rn(in.z, i0), g0.z)), i1), g1.z);
+                    out.w = __fmul_rn(__fmul_rn(__fadd_rn(a.w, __fmul_rn(__fmul_rn(in.w, i0), g0.w)), i1), g1.w);
+                } else if (p.prologue == kPrologueGeglu) {
+                    const float4 up = *reinterpret_cast<const float4*>(p.residual + gi + 4 * hq);
+                    out.x = __fmul_rn(gelu_tanh_exact(in.x), up.x); out.y = __fmul_rn(gelu_tanh_exact(in.y), up.y);
+                    out.z = __fmul_rn(gelu_tanh_exact(in.z), up.z); out.w = __fmul_rn(gelu_tanh_exact(in.w), up.w);
+                }
+                v[4 * hq] = out.x; v[4 * hq + 1] = out.y; v[4 * hq + 2] = out.z; v[4 * hq + 3] = out.w;
             }
         }
-        uint32_t b0[3], b1[3];
-        split_bf16x3(v.x, v.z, b0);
-        split_bf16x3(v.y, v.w, b1);
-        const uint32_t g2 = o4 >> 3, parity = (o4 >> 2) & 1u, t = o4 & 3u;
-        uint8_t* dst = frags + ((size_t)g2 * NCP * 4u + t) * 16u + parity * 8u;
+        // Largest magnitude of the warp's 256 elements, as a bit pattern (NaN and infinity sort on top).
+        uint32_t top = 0u;
 #pragma unroll
-        for (int i = 0; i < 3; ++i) *reinterpret_cast<uint2*>(dst + (3u * r + i) * 64u) = make_uint2(b0[i], b1[i]);
+        for (int i = 0; i < 8; ++i) top = max(top, __float_as_uint(v[i]) & 0x7fffffffu);
+#pragma unroll
+        for (int offset = 16; offset > 0; offset >>= 1) top = max(top, __shfl_xor_sync(0xffffffffu, top, offset));
+        uint32_t e = top >> 23;
+        if (e == 255u) { if (lane == 0u) atomicOr(bad_rows, 1u << r); e = 254u; }
+        e = max(e, 30u);
+        const float to_fixed = __uint_as_float((283u - e) << 23);           // 2^(156 - e): |x| < 2^(e-126) -> |x * to_fixed| < 2^30
+        if (lane == 0u) block_scales[r * (padded / 256u) + (piece >> 5)] = __uint_as_float((e - 29u) << 23);   // 2^(e - 156)
+        uint32_t words[8];
+#pragma unroll
+        for (int i = 0; i < 8; ++i) {
+            const int fixed = __float2int_rn(__fmul_rn(v[i], to_fixed));
+            words[i] = ((uint32_t)fixed + 0x00808080u) ^ 0x00808080u;
+        }
+        uint32_t d0[4], d1[4];
+        { const uint32_t a[4] = {words[0], words[1], words[2], words[3]}; transpose_digits(a, d0); }
+        { const uint32_t a[4] = {words[4], words[5], words[6], words[7]}; transpose_digits(a, d1); }
+        // Elements 8*piece .. +7: group G2 = piece / 4, sixteen-half (piece / 2) & 1, positions t = 2 * (piece & 1), +1.
+        const uint32_t g2 = piece >> 2, half = (piece >> 1) & 1u, t = (piece & 1u) * 2u;
+        uint8_t* dst = frags + ((size_t)g2 * NCP * 4u + t) * 8u + half * 4u;
+#pragma unroll
+        for (int i = 0; i < 4; ++i) {
+            *reinterpret_cast<uint32_t*>(dst + (4u * r + i) * 32u) = d0[i];
+            *reinterpret_cast<uint32_t*>(dst + (4u * r + i) * 32u + 8u) = d1[i];
+        }
         if (r == 0) {
 #pragma unroll
-            for (uint32_t n = 3u * ROWS; n < NCP; ++n) *reinterpret_cast<uint2*>(dst + n * 64u) = make_uint2(0u, 0u);
+            for (uint32_t n = 4u * ROWS; n < NCP; ++n) {
+                *reinterpret_cast<uint32_t*>(dst + n * 32u) = 0u;
+                *reinterpret_cast<uint32_t*>(dst + n * 32u + 8u) = 0u;
+            }
         }
-        float s = (v.x + v.y) + (v.z + v.w);
+        float s = ((v[0] + v[1]) + (v[2] + v[3])) + ((v[4] + v[5]) + (v[6] + v[7]));
         s += __shfl_xor_sync(0xffffffffu, s, 1);
-        s += __shfl_xor_sync(0xffffffffu, s, 2);
-        if (t == 0u) sums[r * (slice / 16u) + (o4 >> 2)] = s;
+        if ((lane & 1u) == 0u) sums[r * (padded / 16u) + (piece >> 1)] = s;
     }
 }
 
 template <int ROWS>
 __global__ void __launch_bounds__(kGemvWarps * 32, 1) gemv_kernel(const __grid_constant__ GemvParams p) {
-    constexpr int NT = (3 * ROWS + 7) / 8;
+    constexpr int NT = (4 * ROWS + 7) / 8;
     constexpr uint32_t NCP = gemv_fragment_columns(ROWS);
-    constexpr uint32_t FRAG_STRIDE = NCP * 64u;
+    constexpr uint32_t FRAG_STRIDE = NCP * 32u;
     extern __shared__ __align__(128) uint8_t smem[];
     __shared__ float scratch[kGemvWarps];
-    const GemvSmemLayout lay = gemv_smem_layout(ROWS, p.chunk_units, p.unit_elems, p.slot_bytes, p.table_bytes);
-    const uint32_t slice = p.chunk_units * p.unit_elems;
+    __shared__ uint32_t bad_rows;
+    const GemvSmemLayout lay = gemv_smem_layout(ROWS, p.chunk_units, p.unit_elems, p.slot_bytes);
+    const uint32_t slice = p.chunk_units * p.unit_elems, padded = (slice + 255u) & ~255u;
     uint8_t* frags = smem;
     float* sums = reinterpret_cast<float*>(smem + lay.frag_bytes);
-    uint8_t* ring_base = smem + lay.frag_bytes + lay.sums_bytes;
+    float* block_scales = reinterpret_cast<float*>(smem + lay.frag_bytes + lay.sums_bytes);
+    uint8_t* ring_base = smem + lay.frag_bytes + lay.sums_bytes + lay.scale_bytes;
     uint8_t* table_base = ring_base + lay.ring_bytes;
     uint64_t* bars = reinterpret_cast<uint64_t*>(table_base + lay.table_bytes);
 
     const uint32_t warp = threadIdx.x >> 5, lane = threadIdx.x & 31u;
     uint8_t* ring = ring_base + warp * (kGemvSlots * p.slot_bytes);
-    uint8_t* table = table_base + warp * p.table_bytes;
+    uint8_t* table = table_base + warp * kGemvTableBytes;
     uint64_t* bar = bars + warp * kGemvSlots;
 
     // This CTA's K chunk and this warp's sequence of column pairs (over all matrices).
@@ -551,11 +557,12 @@ __global__ void __launch_bounds__(kGemvWarps * 32, 1) gemv_kernel(const __grid_c
         return m;
     };
 
+    if (threadIdx.x == 0) bad_rows = 0u;
     if (lane == 0) {
         for (int s = 0; s < kGemvSlots; ++s) mbar_init(&bar[s], 1);
         fence_barrier_init();
     }
-    __syncwarp();
+    __syncthreads();
 
     // Producer cursor (lane 0): the next pair row to request, walking items then units.
     uint32_t prod_item = 0, prod_unit = 0, prod_slot = 0, prod_bytes = 0;
@@ -579,14 +586,21 @@ __global__ void __launch_bounds__(kGemvWarps * 32, 1) gemv_kernel(const __grid_c
         for (int j = 0; j < kGemvSlots; ++j) issue_next();
 
     pdl_wait();
-    stage_activations<ROWS>(p, first_unit * p.unit_elems, chunk_count * p.unit_elems, slice, frags, sums, scratch);
+    stage_activations<ROWS>(p, first_unit * p.unit_elems, chunk_count * p.unit_elems, padded, frags, sums, block_scales,
+                            &bad_rows, scratch);
     __syncthreads();
     pdl_launch_dependents();
 
-    const uint32_t g = lane >> 2, t = lane & 3u;
-    const uint8_t* my_frag = frags + ((g & (NCP - 1u)) * 4u + t) * 16u;
-    const uint32_t sums_stride = slice / 16u;
+    GemvLane L;
+    L.lane = lane; L.g = lane >> 2; L.t = lane & 3u;
+    // This lane's C registers hold B columns 2t, 2t+1 of every n-tile: digits (2t) % 4 and the next
+    // one of row (8 * nt + 2t) / 4.
+    L.digit_weight = (L.t & 1u) ? pack2f(65536.0f, 16777216.0f) : pack2f(1.0f, 256.0f);
+    const uint8_t* my_frag = frags + ((L.g & (NCP - 1u)) * 4u + L.t) * 8u;
+    const uint32_t sums_stride = padded / 16u, scales_stride = padded / 256u;
+    const uint32_t my_row[2] = {min(L.t >> 1, (uint32_t)ROWS - 1u), min(2u + (L.t >> 1), (uint32_t)ROWS - 1u)};
     const uint32_t quad_base = lane & ~3u;
+    const uint32_t bad = bad_rows;
 
     f32x2 accA[NT], accB[NT];
     float macc[ROWS];
@@ -603,46 +617,56 @@ __global__ void __launch_bounds__(kGemvWarps * 32, 1) gemv_kernel(const __grid_c
         for (uint32_t u = 0; u < chunk_count; ++u) {
             if (!mbar_wait(&bar[slot], phase)) { failed = true; break; }
             const uint8_t* row = ring + slot * p.slot_bytes;
-            if (dtype == GF_Q4_K)
+            if (dtype == GF_Q4_K) {
+                float scales[NT];
+#pragma unroll
+                for (int nt = 0; nt < NT; ++nt) scales[nt] = block_scales[my_row[nt] * scales_stride + u];
                 pair_row_q4k<ROWS, NT, FRAG_STRIDE>(row, my_frag + (size_t)u * 8u * FRAG_STRIDE, sums + u * 16u, sums_stride,
-                                                    table, lane, accA, accB, macc);
-            else if (dtype == GF_Q6_K)
+                                                    scales, table, L, accA, accB, macc);
+            } else if (dtype == GF_Q6_K) {
+                float scales[NT];
+#pragma unroll
+                for (int nt = 0; nt < NT; ++nt) scales[nt] = block_scales[my_row[nt] * scales_stride + u];
                 pair_row_q6k<ROWS, NT, FRAG_STRIDE>(row, my_frag + (size_t)u * 8u * FRAG_STRIDE, sums + u * 16u, sums_stride,
-                                                    table, lane, accA, accB, macc);
-            else
-                pair_row_q80<ROWS, NT, FRAG_STRIDE>(row, my_frag + (size_t)u * 4u * FRAG_STRIDE, sums + u * 8u, sums_stride,
-                                                    table, lane, accA, accB, macc);
+                                                    scales, table, L, accA, accB, macc);
+            } else {
+                float scales[NT];
+#pragma unroll
+                for (int nt = 0; nt < NT; ++nt) scales[nt] = block_scales[my_row[nt] * scales_stride + (u >> 1)];
+                pair_row_q80<ROWS, NT, FRAG_STRIDE>(row, my_frag + (size_t)u * 4u * FRAG_STRIDE, scales, L, accA, accB);
+            }
             __syncwarp();   // every lane has finished reading this slot and the scale table
             if (lane == 0) issue_next();
             if (++slot == (uint32_t)kGemvSlots) { slot = 0; phase ^= 1u; }
         }
         if (failed) break;
-        // Row r is the sum of B columns 3r, 3r+1, 3r+2 (held by quad lanes (n % 8) / 2 of n-tile
-        // n / 8), minus the correction dot product of its column.
-        const float offset = dtype == GF_Q4_K ? 1.0f : dtype == GF_Q6_K ? kQ6Offset : kQ80Offset;
+        // Row r is the sum of B columns 4r .. 4r+3 (digit 0 first; held by quad lanes (n % 8) / 2 of
+        // n-tile n / 8), minus the correction dot product of its column.
+        const float offset = dtype == GF_Q4_K ? 1.0f : dtype == GF_Q6_K ? 32.0f : 0.0f;
         float totalA[ROWS], totalB[ROWS];
 #pragma unroll
         for (int r = 0; r < ROWS; ++r) {
-            float partA[3], partB[3];
+            float partA[4], partB[4];
 #pragma unroll
-            for (int i = 0; i < 3; ++i) {
-                const int n = 3 * r + i, nt = n / 8, holder = (n % 8) / 2;
+            for (int i = 0; i < 4; ++i) {
+                const int n = 4 * r + i, nt = n / 8, holder = (n % 8) / 2;
                 const float2 a = unpack2(accA[nt]), b = unpack2(accB[nt]);
                 partA[i] = __shfl_sync(0xffffffffu, (n & 1) ? a.y : a.x, quad_base + holder);
                 partB[i] = __shfl_sync(0xffffffffu, (n & 1) ? b.y : b.x, quad_base + holder);
             }
             float m = macc[r];
             m += __shfl_xor_sync(0xffffffffu, m, 16);
-            const float mA = __shfl_sync(0xffffffffu, m, g), mB = __shfl_sync(0xffffffffu, m, g + 8u);
-            totalA[r] = __fsub_rn(__fadd_rn(__fadd_rn(partA[0], partA[1]), partA[2]), __fmul_rn(offset, mA));
-            totalB[r] = __fsub_rn(__fadd_rn(__fadd_rn(partB[0], partB[1]), partB[2]), __fmul_rn(offset, mB));
+            const float mA = __shfl_sync(0xffffffffu, m, L.g), mB = __shfl_sync(0xffffffffu, m, L.g + 8u);
+            totalA[r] = __fsub_rn(__fadd_rn(__fadd_rn(__fadd_rn(partA[0], partA[1]), partA[2]), partA[3]), __fmul_rn(offset, mA));
+            totalB[r] = __fsub_rn(__fadd_rn(__fadd_rn(__fadd_rn(partB[0], partB[1]), partB[2]), partB[3]), __fmul_rn(offset, mB));
+            if ((bad >> r) & 1u) totalA[r] = totalB[r] = __int_as_float(0x7fc00000);
         }
         const uint32_t local_pair = pair - mat.first_pair;
-        const uint32_t columnA = local_pair * 16u + g, columnB = columnA + 8u;
+        const uint32_t columnA = local_pair * 16u + L.g, columnB = columnA + 8u;
         if (p.chunks == 1u) {
 #pragma unroll
             for (int r = 0; r < ROWS; ++r)
-                if (t == (uint32_t)(r & 3)) {
+                if (L.t == (uint32_t)(r & 3)) {
                     if (columnA < mat.n) mat.out[(size_t)r * mat.n + columnA] = totalA[r];
                     if (columnB < mat.n) mat.out[(size_t)r * mat.n + columnB] = totalB[r];
                 }
@@ -653,10 +677,10 @@ __global__ void __launch_bounds__(kGemvWarps * 32, 1) gemv_kernel(const __grid_c
         const size_t width = (size_t)p.total_pairs * 16u;
 #pragma unroll
         for (int r = 0; r < ROWS; ++r)
-            if (t == (uint32_t)(r & 3)) {
+            if (L.t == (uint32_t)(r & 3)) {
                 float* dst = p.partial + ((size_t)chunk * ROWS + r) * width + (size_t)pair * 16u;
-                dst[g] = totalA[r];
-                dst[g + 8u] = totalB[r];
+                dst[L.g] = totalA[r];
+                dst[L.g + 8u] = totalB[r];
             }
         __threadfence();
         __syncwarp();
@@ -697,7 +721,7 @@ struct GemvLaunch {
     float* residual_out = nullptr;
     float eps = 1e-6f;
 };
-struct GemvPlan { uint32_t units, unit_elems, total_pairs, chunks, chunk_units, grid, smem, slot_bytes, table_bytes; };
+struct GemvPlan { uint32_t units, unit_elems, total_pairs, chunks, chunk_units, grid, smem, slot_bytes; };
 
 int gemv_plan(const GemvLaunch& launch, GemvPlan& plan);
 // Split-K scratch of one launch: `partial` bytes of sums, and one arrival counter per column pair.
