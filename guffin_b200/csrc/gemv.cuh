@@ -369,17 +369,40 @@ __device__ __forceinline__ float gelu_tanh_exact(float v) {
     return __fmul_rn(__fmul_rn(0.5f, v), __fadd_rn(1.0f, tanhf(inner)));
 }
 
-// Sum over the block of one value per thread; every thread gets the total (fixed order).
-__device__ __forceinline__ float gemv_block_sum(float v, float* scratch) {
-    v = warp_sum(v);
+// Sums over the block of ROWS values per thread; every thread gets the totals (fixed order).
+// `scratch` holds kGemvWarps * ROWS floats and must not be reused before the next block barrier.
+template <int ROWS>
+__device__ __forceinline__ void gemv_block_sums(float (&v)[ROWS], float* scratch) {
     const uint32_t warp = threadIdx.x >> 5, lane = threadIdx.x & 31u;
-    if (lane == 0) scratch[warp] = v;
-    __syncthreads();
-    float total = 0.0f;
 #pragma unroll
-    for (int w = 0; w < kGemvWarps; ++w) total += scratch[w];
+    for (int r = 0; r < ROWS; ++r) {
+        v[r] = warp_sum(v[r]);
+        if (lane == 0) scratch[warp * ROWS + r] = v[r];
+    }
     __syncthreads();
-    return total;
+#pragma unroll
+    for (int r = 0; r < ROWS; ++r) {
+        float total = 0.0f;
+#pragma unroll
+        for (int w = 0; w < kGemvWarps; ++w) total += scratch[w * ROWS + r];
+        v[r] = total;
+    }
+}
+__device__ __forceinline__ float rms_scale(float sum_of_squares, uint32_t k, float eps) {
+    return __fdiv_rn(1.0f, __fsqrt_rn(__fadd_rn(__fdiv_rn(sum_of_squares, (float)k), eps)));
+}
+__device__ __forceinline__ float sum_squares(const float (&v)[8], float sum) {
+#pragma unroll
+    for (int i = 0; i < 8; ++i) sum = fmaf(v[i], v[i], sum);
+    return sum;
+}
+__device__ __forceinline__ void load8f(const float* p, float (&v)[8]) {
+    const float4 a = *reinterpret_cast<const float4*>(p), b = *reinterpret_cast<const float4*>(p + 4);
+    v[0] = a.x; v[1] = a.y; v[2] = a.z; v[3] = a.w; v[4] = b.x; v[5] = b.y; v[6] = b.z; v[7] = b.w;
+}
+__device__ __forceinline__ void store8f(float* p, const float (&v)[8]) {
+    *reinterpret_cast<float4*>(p) = make_float4(v[0], v[1], v[2], v[3]);
+    *reinterpret_cast<float4*>(p + 4) = make_float4(v[4], v[5], v[6], v[7]);
 }
 
 // Four 32-bit integers whose bytes are signed base-256 digits become four words, word i holding
@@ -391,58 +414,166 @@ __device__ __forceinline__ void transpose_digits(const uint32_t (&w)[4], uint32_
     digit[2] = __byte_perm(hi01, hi23, 0x5410u); digit[3] = __byte_perm(hi01, hi23, 0x7632u);
 }
 
-// Produces this CTA's K slice of the activation rows in shared memory as s8 B-operand registers.
-// A thread owns eight consecutive elements of a row, a warp 256: the warp's largest magnitude
-// fixes the block's power-of-two scale 2^(e-29), every element becomes round(x / scale), an
-// integer of at most 2^30, and adding 0x00808080 then flipping those bits makes its four bytes
-// signed base-256 digits.  For 32-element group G2, B column n = 4 * row + digit and lane
-// position t, the 8 bytes at ((G2 * NCP + n) * 4 + t) * 8 are the digit bytes of elements
-// 4t..4t+3 and 16+4t..16+4t+3 of the group.  Also written: the f32 sum of every 16 consecutive
-// elements, the block scales, and a per-row flag for non-finite inputs (whose row then yields
-// NaN).  The RMS norms of prologues 1 and 2 need the whole row, so every CTA recomputes them from
-// global memory (a few tens of KB out of L2).
+// Where the staged activations live in shared memory.
+struct GemvStage {
+    uint8_t* frags;          // B registers
+    float* sums;             // [rows][padded / 16]
+    float* block_scales;     // [rows][padded / 256]
+    uint32_t* bad_rows;      // bit r: row r holds a non-finite activation
+    uint32_t padded;
+};
+
+// Turns eight consecutive activations of row r (slice piece `piece`, i.e. slice elements
+// 8 * piece .. +7) into B registers.  Must be called by whole warps whose lanes hold consecutive
+// pieces of one 256-element block: the warp's largest magnitude fixes the block's power-of-two
+// scale 2^(e-156), every element becomes round(x / scale), an integer of at most 2^30, and adding
+// 0x00808080 then flipping those bits makes its four bytes signed base-256 digits.  For
+// 32-element group G2, B column n = 4 * row + digit and lane position t, the 8 bytes at
+// ((G2 * NCP + n) * 4 + t) * 8 are the digit bytes of elements 4t..4t+3 and 16+4t..16+4t+3 of
+// the group.  Also written: the f32 sum of every 16 consecutive elements, the block scale, and
+// the row's flag when an input is not finite (the row then yields NaN).  `store` is false for
+// lanes whose piece lies outside the slice (they only take part in the warp exchanges).
 template <int ROWS>
-__device__ __forceinline__ void stage_activations(const GemvParams& p, uint32_t first, uint32_t count, uint32_t padded,
-                                                  uint8_t* frags, float* sums, float* block_scales, uint32_t* bad_rows,
-                                                  float* scratch) {
+__device__ __forceinline__ void quantize_piece(const GemvStage& st, uint32_t r, uint32_t piece, const float (&v)[8], bool store) {
     constexpr uint32_t NCP = gemv_fragment_columns(ROWS);
+    const uint32_t lane = threadIdx.x & 31u;
+    // Largest magnitude of the warp's 256 elements, as a bit pattern (NaN and infinity sort on top).
+    uint32_t top = 0u;
+#pragma unroll
+    for (int i = 0; i < 8; ++i) top = max(top, __float_as_uint(v[i]) & 0x7fffffffu);
+#pragma unroll
+    for (int offset = 16; offset > 0; offset >>= 1) top = max(top, __shfl_xor_sync(0xffffffffu, top, offset));
+    uint32_t e = top >> 23;
+    if (e == 255u) { if (lane == 0u) atomicOr(st.bad_rows, 1u << r); e = 254u; }
+    e = max(e, 30u);
+    const float to_fixed = __uint_as_float((283u - e) << 23);           // 2^(156 - e): |x| < 2^(e-126) -> |x * to_fixed| < 2^30
+    float s = ((v[0] + v[1]) + (v[2] + v[3])) + ((v[4] + v[5]) + (v[6] + v[7]));
+    s += __shfl_xor_sync(0xffffffffu, s, 1);
+    if (!store) return;
+    if (lane == 0u) st.block_scales[r * (st.padded / 256u) + (piece >> 5)] = __uint_as_float((e - 29u) << 23);   // 2^(e - 156)
+    if ((lane & 1u) == 0u) st.sums[r * (st.padded / 16u) + (piece >> 1)] = s;
+    uint32_t words[8];
+#pragma unroll
+    for (int i = 0; i < 8; ++i) {
+        const int fixed = __float2int_rn(__fmul_rn(v[i], to_fixed));
+        words[i] = ((uint32_t)fixed + 0x00808080u) ^ 0x00808080u;
+    }
+    uint32_t d0[4], d1[4];
+    { const uint32_t a[4] = {words[0], words[1], words[2], words[3]}; transpose_digits(a, d0); }
+    { const uint32_t a[4] = {words[4], words[5], words[6], words[7]}; transpose_digits(a, d1); }
+    // Elements 8*piece .. +7: group G2 = piece / 4, sixteen-half (piece / 2) & 1, positions t = 2 * (piece & 1), +1.
+    const uint32_t g2 = piece >> 2, half = (piece >> 1) & 1u, t = (piece & 1u) * 2u;
+    uint8_t* dst = st.frags + ((size_t)g2 * NCP * 4u + t) * 8u + half * 4u;
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+        *reinterpret_cast<uint32_t*>(dst + (4u * r + i) * 32u) = d0[i];
+        *reinterpret_cast<uint32_t*>(dst + (4u * r + i) * 32u + 8u) = d1[i];
+    }
+    if (r == 0) {
+#pragma unroll
+        for (uint32_t n = 4u * ROWS; n < NCP; ++n) {
+            *reinterpret_cast<uint32_t*>(dst + n * 32u) = 0u;
+            *reinterpret_cast<uint32_t*>(dst + n * 32u + 8u) = 0u;
+        }
+    }
+}
+
+// Produces this CTA's K slice [first, first + count) of the activation rows in shared memory.
+// The RMS norms of prologues 1 and 2 need the whole row, so every CTA recomputes them from global
+// memory (a few tens of KB out of L2).  When a row has at most one 8-element piece per thread
+// (K <= 8 * block size) and the slice starts on a 256-element boundary, everything a thread needs
+// is loaded once, up front, and kept in registers through both norms; otherwise the row is
+// re-read for each pass.
+template <int ROWS>
+__device__ __forceinline__ void stage_activations(const GemvParams& p, uint32_t first, uint32_t count,
+                                                  const GemvStage& st, float* scratch) {
+    const bool norms = p.prologue == kPrologueNorm || p.prologue == kPrologueAddNorm;
+    const uint32_t row_pieces = p.k / 8u;
+    if (norms && row_pieces <= blockDim.x && (first & 255u) == 0u) {
+        const uint32_t piece = threadIdx.x;
+        const bool live = piece < row_pieces;
+        const uint32_t o = piece * 8u;
+        float x[ROWS][8], res[ROWS][8], g0[8], g1[8];
+#pragma unroll
+        for (int i = 0; i < 8; ++i) { g0[i] = 0.0f; g1[i] = 0.0f; }
+#pragma unroll
+        for (int r = 0; r < ROWS; ++r)
+#pragma unroll
+            for (int i = 0; i < 8; ++i) { x[r][i] = 0.0f; res[r][i] = 0.0f; }
+        if (live) {
+#pragma unroll
+            for (int r = 0; r < ROWS; ++r) {
+                load8f(p.in + (size_t)r * p.k + o, x[r]);
+                if (p.prologue == kPrologueAddNorm) load8f(p.residual + (size_t)r * p.k + o, res[r]);
+            }
+            if (p.prologue == kPrologueAddNorm) load8f(p.gamma0 + o, g0);
+            load8f(p.gamma1 + o, g1);
+        }
+        float ss[ROWS];
+#pragma unroll
+        for (int r = 0; r < ROWS; ++r) ss[r] = sum_squares(x[r], 0.0f);
+        gemv_block_sums<ROWS>(ss, scratch);
+        if (p.prologue == kPrologueAddNorm) {
+#pragma unroll
+            for (int r = 0; r < ROWS; ++r) {
+                const float inv = rms_scale(ss[r], p.k, p.eps);
+#pragma unroll
+                for (int i = 0; i < 8; ++i) x[r][i] = __fadd_rn(res[r][i], __fmul_rn(__fmul_rn(x[r][i], inv), g0[i]));
+                if (blockIdx.x == 0 && live) store8f(p.residual_out + (size_t)r * p.k + o, x[r]);
+                ss[r] = sum_squares(x[r], 0.0f);
+            }
+            gemv_block_sums<ROWS>(ss, scratch + kGemvWarps * ROWS);
+        }
+        const bool inside = live && o >= first && o < first + count;
+#pragma unroll
+        for (int r = 0; r < ROWS; ++r) {
+            const float inv = rms_scale(ss[r], p.k, p.eps);
+            float v[8];
+#pragma unroll
+            for (int i = 0; i < 8; ++i) v[i] = __fmul_rn(__fmul_rn(x[r][i], inv), g1[i]);
+            quantize_piece<ROWS>(st, r, (o - first) / 8u, v, inside);
+        }
+        return;
+    }
     float inv0[ROWS], inv1[ROWS];
 #pragma unroll
     for (int r = 0; r < ROWS; ++r) { inv0[r] = 1.0f; inv1[r] = 1.0f; }
-    if (p.prologue == kPrologueNorm || p.prologue == kPrologueAddNorm) {
+    if (norms) {
+        float ss[ROWS];
 #pragma unroll
         for (int r = 0; r < ROWS; ++r) {
-            const float4* in = reinterpret_cast<const float4*>(p.in + (size_t)r * p.k);
-            float sum = 0.0f;
-            for (uint32_t c = threadIdx.x; c < p.k / 4u; c += blockDim.x) {
-                const float4 v = in[c];
-                sum = fmaf(v.x, v.x, sum); sum = fmaf(v.y, v.y, sum); sum = fmaf(v.z, v.z, sum); sum = fmaf(v.w, v.w, sum);
+            ss[r] = 0.0f;
+            for (uint32_t c = threadIdx.x; c < row_pieces; c += blockDim.x) {
+                float x[8];
+                load8f(p.in + (size_t)r * p.k + c * 8u, x);
+                ss[r] = sum_squares(x, ss[r]);
             }
-            const float total = gemv_block_sum(sum, scratch);
-            const float inv = __fdiv_rn(1.0f, __fsqrt_rn(__fadd_rn(__fdiv_rn(total, (float)p.k), p.eps)));
-            if (p.prologue == kPrologueNorm) { inv1[r] = inv; continue; }
-            inv0[r] = inv;
+        }
+        gemv_block_sums<ROWS>(ss, scratch);
+#pragma unroll
+        for (int r = 0; r < ROWS; ++r) (p.prologue == kPrologueNorm ? inv1[r] : inv0[r]) = rms_scale(ss[r], p.k, p.eps);
+        if (p.prologue == kPrologueAddNorm) {
             // r = residual + norm(in) * gamma0; its mean square feeds the second norm.
-            const float4* res = reinterpret_cast<const float4*>(p.residual + (size_t)r * p.k);
-            const float4* g0 = reinterpret_cast<const float4*>(p.gamma0);
-            float4* res_out = reinterpret_cast<float4*>(p.residual_out + (size_t)r * p.k);
-            float sum2 = 0.0f;
-            for (uint32_t c = threadIdx.x; c < p.k / 4u; c += blockDim.x) {
-                const float4 v = in[c], a = res[c], gm = g0[c];
-                float4 o;
-                o.x = __fadd_rn(a.x, __fmul_rn(__fmul_rn(v.x, inv), gm.x));
-                o.y = __fadd_rn(a.y, __fmul_rn(__fmul_rn(v.y, inv), gm.y));
-                o.z = __fadd_rn(a.z, __fmul_rn(__fmul_rn(v.z, inv), gm.z));
-                o.w = __fadd_rn(a.w, __fmul_rn(__fmul_rn(v.w, inv), gm.w));
-                sum2 = fmaf(o.x, o.x, sum2); sum2 = fmaf(o.y, o.y, sum2); sum2 = fmaf(o.z, o.z, sum2); sum2 = fmaf(o.w, o.w, sum2);
-                if (blockIdx.x == 0) res_out[c] = o;
+#pragma unroll
+            for (int r = 0; r < ROWS; ++r) {
+                ss[r] = 0.0f;
+                for (uint32_t c = threadIdx.x; c < row_pieces; c += blockDim.x) {
+                    float x[8], a[8], gm[8];
+                    load8f(p.in + (size_t)r * p.k + c * 8u, x);
+                    load8f(p.residual + (size_t)r * p.k + c * 8u, a);
+                    load8f(p.gamma0 + c * 8u, gm);
+#pragma unroll
+                    for (int i = 0; i < 8; ++i) x[i] = __fadd_rn(a[i], __fmul_rn(__fmul_rn(x[i], inv0[r]), gm[i]));
+                    ss[r] = sum_squares(x, ss[r]);
+                    if (blockIdx.x == 0) store8f(p.residual_out + (size_t)r * p.k + c * 8u, x);
+                }
             }
-            const float total2 = gemv_block_sum(sum2, scratch);
-            inv1[r] = __fdiv_rn(1.0f, __fsqrt_rn(__fadd_rn(__fdiv_rn(total2, (float)p.k), p.eps)));
+            gemv_block_sums<ROWS>(ss, scratch + kGemvWarps * ROWS);
+#pragma unroll
+            for (int r = 0; r < ROWS; ++r) inv1[r] = rms_scale(ss[r], p.k, p.eps);
         }
     }
-    const uint32_t pieces = padded / 8u;      // a multiple of 32: whole warps stay together
-    const uint32_t lane = threadIdx.x & 31u;
+    const uint32_t pieces = st.padded / 8u;      // a multiple of 32: whole warps stay together
     for (uint32_t q = threadIdx.x; q < (uint32_t)ROWS * pieces; q += blockDim.x) {
         const uint32_t r = q / pieces, piece = q % pieces, o = piece * 8u;
         float v[8];
@@ -454,68 +585,28 @@ __device__ __forceinline__ void stage_activations(const GemvParams& p, uint32_t 
             float i0 = 1.0f, i1 = 1.0f;
 #pragma unroll
             for (int rr = 0; rr < ROWS; ++rr) if (rr == (int)r) { i0 = inv0[rr]; i1 = inv1[rr]; }
+            load8f(p.in + gi, v);
+            if (p.prologue == kPrologueNorm) {
+                float gm[8];
+                load8f(p.gamma1 + c, gm);
 #pragma unroll
-            for (int hq = 0; hq < 2; ++hq) {
-                const float4 in = *reinterpret_cast<const float4*>(p.in + gi + 4 * hq);
-                float4 out = in;
-                if (p.prologue == kPrologueNorm) {
-                    const float4 gm = *reinterpret_cast<const float4*>(p.gamma1 + c + 4 * hq);
-                    out.x = __fmul_rn(__fmul_rn(in.x, i1), gm.x); out.y = __fmul_rn(__fmul_rn(in.y, i1), gm.y);
-                    out.z = __fmul_rn(__fmul_rn(in.z, i1), gm.z); out.w = __fmul_rn(__fmul_rn(in.w, i1), gm.w);
-                } else if (p.prologue == kPrologueAddNorm) {
-                    const float4 a = *reinterpret_cast<const float4*>(p.residual + gi + 4 * hq);
-                    const float4 g0 = *reinterpret_cast<const float4*>(p.gamma0 + c + 4 * hq);
-                    const float4 g1 = *reinterpret_cast<const float4*>(p.gamma1 + c + 4 * hq);
-                    out.x = __fmul_rn(__fmul_rn(__fadd_rn(a.x, __fmul_rn(__fmul_rn(in.x, i0), g0.x)), i1), g1.x);
-                    out.y = __fmul_rn(__fmul_rn(__fadd_rn(a.y, __fmul_rn(__fmul_rn(in.y, i0), g0.y)), i1), g1.y);
-                    out.z = __fmul_rn(__fmul_rn(__fadd_rn(a.z, __fmul_rn(__fmul_rn(in.z, i0), g0.z)), i1), g1.z);
-                    out.w = __fmul_rn(__fmul_rn(__fadd_rn(a.w, __fmul_rn(__fmul_rn(in.w, i0), g0.w)), i1), g1.w);
-                } else if (p.prologue == kPrologueGeglu) {
-                    const float4 up = *reinterpret_cast<const float4*>(p.residual + gi + 4 * hq);
-                    out.x = __fmul_rn(gelu_tanh_exact(in.x), up.x); out.y = __fmul_rn(gelu_tanh_exact(in.y), up.y);
-                    out.z = __fmul_rn(gelu_tanh_exact(in.z), up.z); out.w = __fmul_rn(gelu_tanh_exact(in.w), up.w);
-                }
-                v[4 * hq] = out.x; v[4 * hq + 1] = out.y; v[4 * hq + 2] = out.z; v[4 * hq + 3] = out.w;
+                for (int i = 0; i < 8; ++i) v[i] = __fmul_rn(__fmul_rn(v[i], i1), gm[i]);
+            } else if (p.prologue == kPrologueAddNorm) {
+                float a[8], gm0[8], gm1[8];
+                load8f(p.residual + gi, a);
+                load8f(p.gamma0 + c, gm0);
+                load8f(p.gamma1 + c, gm1);
+#pragma unroll
+                for (int i = 0; i < 8; ++i)
+                    v[i] = __fmul_rn(__fmul_rn(__fadd_rn(a[i], __fmul_rn(__fmul_rn(v[i], i0), gm0[i])), i1), gm1[i]);
+            } else if (p.prologue == kPrologueGeglu) {
+                float up[8];
+                load8f(p.residual + gi, up);
+#pragma unroll
+                for (int i = 0; i < 8; ++i) v[i] = __fmul_rn(gelu_tanh_exact(v[i]), up[i]);
             }
         }
-        // Largest magnitude of the warp's 256 elements, as a bit pattern (NaN and infinity sort on top).
-        uint32_t top = 0u;
-#pragma unroll
-        for (int i = 0; i < 8; ++i) top = max(top, __float_as_uint(v[i]) & 0x7fffffffu);
-#pragma unroll
-        for (int offset = 16; offset > 0; offset >>= 1) top = max(top, __shfl_xor_sync(0xffffffffu, top, offset));
-        uint32_t e = top >> 23;
-        if (e == 255u) { if (lane == 0u) atomicOr(bad_rows, 1u << r); e = 254u; }
-        e = max(e, 30u);
-        const float to_fixed = __uint_as_float((283u - e) << 23);           // 2^(156 - e): |x| < 2^(e-126) -> |x * to_fixed| < 2^30
-        if (lane == 0u) block_scales[r * (padded / 256u) + (piece >> 5)] = __uint_as_float((e - 29u) << 23);   // 2^(e - 156)
-        uint32_t words[8];
-#pragma unroll
-        for (int i = 0; i < 8; ++i) {
-            const int fixed = __float2int_rn(__fmul_rn(v[i], to_fixed));
-            words[i] = ((uint32_t)fixed + 0x00808080u) ^ 0x00808080u;
-        }
-        uint32_t d0[4], d1[4];
-        { const uint32_t a[4] = {words[0], words[1], words[2], words[3]}; transpose_digits(a, d0); }
-        { const uint32_t a[4] = {words[4], words[5], words[6], words[7]}; transpose_digits(a, d1); }
-        // Elements 8*piece .. +7: group G2 = piece / 4, sixteen-half (piece / 2) & 1, positions t = 2 * (piece & 1), +1.
-        const uint32_t g2 = piece >> 2, half = (piece >> 1) & 1u, t = (piece & 1u) * 2u;
-        uint8_t* dst = frags + ((size_t)g2 * NCP * 4u + t) * 8u + half * 4u;
-#pragma unroll
-        for (int i = 0; i < 4; ++i) {
-            *reinterpret_cast<uint32_t*>(dst + (4u * r + i) * 32u) = d0[i];
-            *reinterpret_cast<uint32_t*>(dst + (4u * r + i) * 32u + 8u) = d1[i];
-        }
-        if (r == 0) {
-#pragma unroll
-            for (uint32_t n = 4u * ROWS; n < NCP; ++n) {
-                *reinterpret_cast<uint32_t*>(dst + n * 32u) = 0u;
-                *reinterpret_cast<uint32_t*>(dst + n * 32u + 8u) = 0u;
-            }
-        }
-        float s = ((v[0] + v[1]) + (v[2] + v[3])) + ((v[4] + v[5]) + (v[6] + v[7]));
-        s += __shfl_xor_sync(0xffffffffu, s, 1);
-        if ((lane & 1u) == 0u) sums[r * (padded / 16u) + (piece >> 1)] = s;
+        quantize_piece<ROWS>(st, r, piece, v, true);
     }
 }
 
@@ -525,7 +616,7 @@ __global__ void __launch_bounds__(kGemvWarps * 32, 1) gemv_kernel(const __grid_c
     constexpr uint32_t NCP = gemv_fragment_columns(ROWS);
     constexpr uint32_t FRAG_STRIDE = NCP * 32u;
     extern __shared__ __align__(128) uint8_t smem[];
-    __shared__ float scratch[kGemvWarps];
+    __shared__ float scratch[2 * kGemvWarps * ROWS];
     __shared__ uint32_t bad_rows;
     const GemvSmemLayout lay = gemv_smem_layout(ROWS, p.chunk_units, p.unit_elems, p.slot_bytes);
     const uint32_t slice = p.chunk_units * p.unit_elems, padded = (slice + 255u) & ~255u;
@@ -586,8 +677,8 @@ __global__ void __launch_bounds__(kGemvWarps * 32, 1) gemv_kernel(const __grid_c
         for (int j = 0; j < kGemvSlots; ++j) issue_next();
 
     pdl_wait();
-    stage_activations<ROWS>(p, first_unit * p.unit_elems, chunk_count * p.unit_elems, padded, frags, sums, block_scales,
-                            &bad_rows, scratch);
+    const GemvStage stage{frags, sums, block_scales, &bad_rows, padded};
+    stage_activations<ROWS>(p, first_unit * p.unit_elems, chunk_count * p.unit_elems, stage, scratch);
     __syncthreads();
     pdl_launch_dependents();
 

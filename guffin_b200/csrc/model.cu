@@ -154,6 +154,20 @@ int Model::finalize() {
         GF_CUDA(cudaMemsetAsync(rk, 0, (size_t)cache.ring_rows * kvw * element, stream_));
         GF_CUDA(cudaMemsetAsync(rv, 0, (size_t)cache.ring_rows * kvw * element, stream_));
     }
+    {   // RoPE divisors, one table per distinct base (local and global layers).
+        double* tables[2] = {nullptr, nullptr};
+        const float bases[2] = {c.rope_base_local, c.rope_base_global};
+        for (int kind = 0; kind < 2; ++kind) {
+            if (kind == 1 && bases[1] == bases[0]) { tables[1] = tables[0]; break; }
+            std::vector<double> host(c.head_dim / 2u);
+            for (uint32_t i = 0; i < c.head_dim / 2u; ++i)
+                host[i] = std::pow((double)bases[kind], (double)(2u * i) / (double)c.head_dim);
+            GF_TRY(device_alloc(allocations_, &tables[kind], host.size()));
+            GF_CUDA(cudaMemcpyAsync(tables[kind], host.data(), host.size() * sizeof(double), cudaMemcpyHostToDevice, stream_));
+            GF_CUDA(cudaStreamSynchronize(stream_));
+        }
+        for (uint32_t l = 0; l < c.layers; ++l) caches_[l].rope_divisors = tables[layer_is_local(l) ? 0 : 1];
+    }
     {
         std::vector<KvPublishLayer> table(c.layers);
         for (uint32_t l = 0; l < c.layers; ++l)
@@ -272,7 +286,7 @@ int Model::encode_blocks(uint32_t rows, uint32_t flags) {
         GF_TRY(run_gemv(qkv, rows));
         if (!same_unit) return fail(GF_ERR_INVALID, "attention projections of one layer must share a block family");
         RopeStoreParams rp{raw_q_, raw_k_, raw_v_, c.uses_qk_norm ? w.q_norm : nullptr, c.uses_qk_norm ? w.k_norm : nullptr,
-                           query_, cache.private_k, cache.private_v, state_dev_, status_dev_, rows, c.heads, c.kv_heads,
+                           query_, cache.private_k, cache.private_v, state_dev_, status_dev_, cache.rope_divisors, rows, c.heads, c.kv_heads,
                            c.head_dim, c.rms_eps, cache.rope_base, cache.rope_scale, c.kv_f16};
         GF_TRY(launch_rope_store(rp, stream_, true));
         AttentionParams ap;

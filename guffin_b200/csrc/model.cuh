@@ -31,6 +31,7 @@ struct LayerCache {
     uint32_t ring_rows = 0;                           // power of two (gemma2_metal_plan.cpp:356-366)
     uint32_t window = 0;                              // 0 = global layer
     float rope_base = 0.0f, rope_scale = 1.0f;
+    const double* rope_divisors = nullptr;            // [head_dim / 2] rope_base^(2i / head_dim)
 };
 
 enum ForwardFlags : uint32_t {

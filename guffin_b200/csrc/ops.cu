@@ -122,11 +122,16 @@ __global__ void __launch_bounds__(256) rope_store_kernel(RopeStoreParams p) {
         second = __fmul_rn(__fmul_rn(second, inv), gamma[i + half]);
     }
     const uint32_t position = *p.base_position + row;
-    const double exponent = (double)(2u * i) / (double)p.head_dim;
-    const double angle = (double)position * (double)p.freq_scale / pow((double)p.freq_base, exponent);
-    double sd, cd;
-    sincos(angle, &sd, &cd);
-    const float c = (float)cd, s = (float)sd;
+    // Angle in double as the reference forms it (ops/rope.cpp:109-117); the divisor
+    // freq_base^(2i/d) comes from a table when the caller has one.  The angle is reduced to
+    // [-pi, pi] in double (two-term 2*pi), after which single-precision sine and cosine are
+    // within an ulp of the double ones rounded to f32.
+    const double divisor = p.divisors ? p.divisors[i] : pow((double)p.freq_base, (double)(2u * i) / (double)p.head_dim);
+    const double angle = (double)position * (double)p.freq_scale / divisor;
+    const double turns = rint(angle * 0.15915494309189535);
+    const double reduced = fma(-turns, 2.4492935982947064e-16, fma(-turns, 6.283185307179586, angle));
+    float s, c;
+    sincosf((float)reduced, &s, &c);
     const float r0 = __fsub_rn(__fmul_rn(first, c), __fmul_rn(second, s));
     const float r1 = __fadd_rn(__fmul_rn(first, s), __fmul_rn(second, c));
     if (is_query) {
@@ -509,7 +514,7 @@ int gf_qk_norm_rope_store(const float* raw_q_dev, const float* raw_k_dev, const 
         || !status_dev || rows == 0 || !(freq_base > 0.0f))
         return fail(GF_ERR_INVALID, "gf_qk_norm_rope_store: bad arguments");
     RopeStoreParams p{raw_q_dev, raw_k_dev, raw_v_dev, q_norm_dev, k_norm_dev, q_out_dev, private_k_dev, private_v_dev,
-                      base_position_dev, status_dev, rows, heads, kv_heads, head_dim, eps, freq_base, freq_scale, kv_f16};
+                      base_position_dev, status_dev, nullptr, rows, heads, kv_heads, head_dim, eps, freq_base, freq_scale, kv_f16};
     return launch_rope_store(p, as_stream(stream), false);
 }
 

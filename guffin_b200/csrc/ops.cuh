@@ -25,6 +25,7 @@ struct RopeStoreParams {
     void* private_v;
     const uint32_t* base_position;   // device scalar: position of row 0
     uint32_t* status;
+    const double* divisors;    // [hd / 2] freq_base^(2i / hd), or null to compute them in the kernel
     uint32_t rows, heads, kv_heads, head_dim;
     float eps, freq_base, freq_scale;
     int kv_f16;
