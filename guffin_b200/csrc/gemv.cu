@@ -2,6 +2,9 @@
 #include "gemv.cuh"
 
 #include <algorithm>
+#include <cstdio>
+#include <cstdlib>
+#include <cstring>
 #include <mutex>
 
 namespace gf {
@@ -52,6 +55,15 @@ int gemv_plan(const GemvLaunch& launch, GemvPlan& plan) {
             plan.chunks = chunks;
             plan.chunk_units = chunk_units;
             plan.grid = group_ctas * chunks;
+        }
+    }
+    if (const char* tune = getenv("GF_TUNE_CHUNKS")) {      // "units:pairs:chunks,..." (experiments only)
+        for (const char* q = tune; q && *q; q = strchr(q, ',') ? strchr(q, ',') + 1 : nullptr) {
+            unsigned u = 0, pr = 0, ch = 0;
+            if (sscanf(q, "%u:%u:%u", &u, &pr, &ch) == 3 && u == plan.units && pr == plan.total_pairs && ch >= 1 && ch <= plan.units) {
+                const uint32_t cu = (plan.units + ch - 1u) / ch;
+                if (cu <= limit && (ch - 1u) * cu < plan.units) { plan.chunks = ch; plan.chunk_units = cu; plan.grid = slots / ch * ch; }
+            }
         }
     }
     if (plan.chunks == 0) return fail(GF_ERR_INVALID, "gf_matmul: no decomposition fits K=%llu rows=%u", (unsigned long long)launch.k, launch.rows);
@@ -137,6 +149,27 @@ int gemv_launch(const GemvLaunch& launch, uint32_t* counters, float* partial, si
     p.residual_out = launch.residual_out;
     p.eps = launch.eps;
     p.error_flag = error_flag;
+    if (launch.next) {
+        GemvLaunch hint = *launch.next;
+        hint.rows = launch.rows;
+        GemvPlan next_plan;
+        if (gemv_plan(hint, next_plan) == GF_OK) {
+            uint32_t next_first = 0;
+            for (uint32_t i = 0; i < hint.count; ++i) {
+                p.next[i].weight = static_cast<const uint8_t*>(hint.matrices[i].packed);
+                p.next[i].dtype = (uint32_t)hint.matrices[i].dtype;
+                p.next[i].pairs = (uint32_t)((hint.matrices[i].n + 15u) / 16u);
+                p.next[i].first_pair = next_first;
+                next_first += p.next[i].pairs;
+            }
+            p.next_matrices = hint.count;
+            // Only the pairs of the next kernel's first round: what its warps request before anything else.
+            p.next_pairs = std::min(next_plan.total_pairs, next_plan.grid / next_plan.chunks * (uint32_t)kGemvWarps);
+            p.next_units = next_plan.units;
+            p.next_chunks = next_plan.chunks;
+            p.next_chunk_units = next_plan.chunk_units;
+        }
+    }
     if (plan.chunks > 1) {
         const size_t need = (size_t)plan.chunks * launch.rows * plan.total_pairs * 16u * sizeof(float);
         if (!counters || !partial || partial_bytes < need) return fail(GF_ERR_INVALID, "gf_matmul: this shape needs a %zu-byte split-K workspace", need);

@@ -31,7 +31,6 @@ namespace gf {
 constexpr int kGemvWarps = 16;       // warps per CTA; one CTA per SM
 constexpr int kGemvSlots = 3;        // ring depth per warp, one pair row per slot
 constexpr uint32_t kGemvSmemLimit = 226u * 1024u;    // dynamic part; the static arrays take the rest of the 227 KB
-constexpr uint32_t kGemvTableBytes = 256u;           // per warp: decoded scales of one pair row
 constexpr int kGemvMaxMatrices = 3;
 
 // How the activation rows are produced from global memory before the weights are applied.
@@ -58,6 +57,11 @@ struct GemvParams {
     const float *in, *residual, *gamma0, *gamma1;
     float* residual_out;
     float eps;
+    // The GEMV that runs next in the stream (if known): the pair rows its warps will ask for first
+    // are pulled into L2 by this kernel's warps as they run out of work, so the HBM stays busy
+    // across the kernel boundary.
+    GemvMatrix next[kGemvMaxMatrices];
+    uint32_t next_matrices, next_pairs, next_units, next_chunks, next_chunk_units;
     float* partial;            // [chunks][rows][total_pairs * 16] when chunks > 1
     uint32_t* counters;        // [total_pairs] arrival counts, zero between launches
     int* error_flag;           // set to 1 when a bounded wait gives up
@@ -70,7 +74,7 @@ __host__ __device__ constexpr uint32_t gemv_fragment_columns(uint32_t rows) {
 }
 
 struct GemvSmemLayout {
-    uint32_t frag_bytes, sums_bytes, scale_bytes, ring_bytes, table_bytes, total;
+    uint32_t frag_bytes, sums_bytes, scale_bytes, ring_bytes, total;
 };
 
 __host__ __device__ inline GemvSmemLayout gemv_smem_layout(uint32_t rows, uint32_t chunk_units, uint32_t unit_elems,
@@ -81,8 +85,7 @@ __host__ __device__ inline GemvSmemLayout gemv_smem_layout(uint32_t rows, uint32
     s.sums_bytes = rows * (padded / 16u) * 4u;
     s.scale_bytes = ((rows * (padded / 256u) * 4u) + 15u) & ~15u;
     s.ring_bytes = (uint32_t)kGemvWarps * kGemvSlots * slot_bytes;
-    s.table_bytes = (uint32_t)kGemvWarps * kGemvTableBytes;
-    s.total = s.frag_bytes + s.sums_bytes + s.scale_bytes + s.ring_bytes + s.table_bytes + kGemvWarps * kGemvSlots * 8u + 64u;
+    s.total = s.frag_bytes + s.sums_bytes + s.scale_bytes + s.ring_bytes + kGemvWarps * kGemvSlots * 8u + 64u;
     return s;
 }
 
@@ -188,44 +191,43 @@ __device__ __forceinline__ void fold_block(const int (&sums)[4], float block_sca
 // ---- one pair row (16 columns x one K unit) of each format.  `row` points at the pair row in
 // shared memory, `frag` at this lane's B registers of the unit's first 32-element group, `sums`
 // at the unit's first per-16 activation sum of row 0, `scales` at the unit's activation block
-// scale of this lane's row, `table` at this warp's scratch table.  accA / accB are (columns 2t,
-// 2t+1 of the B operand) for output column g / g + 8; macc[r] collects this lane's share of the
-// correction dot product of column (lane & 15).  FRAG_STRIDE = bytes between consecutive
-// 32-element groups of B registers; n-tile nt starts 256 bytes further.
+// scales of this lane's rows.  Everything a lane needs about its two output columns (g and g + 8)
+// it decodes itself from the pair row, so the warp never synchronises inside a pair row.
+// accA / accB are (columns 2t, 2t+1 of the B operand) for output column g / g + 8; maccA / maccB
+// collect this lane's share (a quarter of the scale groups) of the correction dot product of
+// those columns.  FRAG_STRIDE = bytes between consecutive 32-element groups of B registers;
+// n-tile nt starts 256 bytes further.
 
 template <int ROWS, int NT, uint32_t FRAG_STRIDE>
 __device__ __forceinline__ void pair_row_q4k(const uint8_t* row, const uint8_t* frag, const float* sums,
-                                             uint32_t sums_stride, const float* scales, uint8_t* table,
-                                             const GemvLane& L, f32x2 (&accA)[NT], f32x2 (&accB)[NT], float (&macc)[ROWS]) {
-    // Phase A: lane (column, half) decodes the 6-bit scales and minima of groups 4*half .. 4*half+3.
-    {
-        const uint32_t col = L.lane & 15u, hf = L.lane >> 4;
-        const uint4 hdr = *reinterpret_cast<const uint4*>(row + 2048u + col * 16u);
-        const float dmin = __half2float(__ushort_as_half((unsigned short)(hdr.x >> 16)));
-        const uint32_t sc4 = hf ? ((hdr.w & 0x0f0f0f0fu) | ((hdr.y >> 2) & 0x30303030u)) : (hdr.y & 0x3f3f3f3fu);
-        const uint32_t mn4 = hf ? (((hdr.w >> 4) & 0x0f0f0f0fu) | ((hdr.z >> 2) & 0x30303030u)) : (hdr.z & 0x3f3f3f3fu);
-        reinterpret_cast<uint32_t*>(table)[col * 2u + hf] = sc4;
+                                             uint32_t sums_stride, const float* scales, const GemvLane& L,
+                                             f32x2 (&accA)[NT], f32x2 (&accB)[NT], float (&maccA)[ROWS], float (&maccB)[ROWS]) {
+    // Headers of this lane's two columns: d, dmin and the twelve bytes of 6-bit scales and minima.
+    const uint4 hA = *reinterpret_cast<const uint4*>(row + 2048u + L.g * 16u);
+    const uint4 hB = *reinterpret_cast<const uint4*>(row + 2048u + (L.g + 8u) * 16u);
+    const uint32_t scA[2] = {hA.y & 0x3f3f3f3fu, (hA.w & 0x0f0f0f0fu) | ((hA.y >> 2) & 0x30303030u)};   // groups 0-3, 4-7
+    const uint32_t scB[2] = {hB.y & 0x3f3f3f3fu, (hB.w & 0x0f0f0f0fu) | ((hB.y >> 2) & 0x30303030u)};
+    {   // Minima of groups 2t, 2t+1 (this lane's share of the correction term) times the groups' activation sums.
+        const uint32_t mnA = L.t < 2u ? (hA.z & 0x3f3f3f3fu) : (((hA.w >> 4) & 0x0f0f0f0fu) | ((hA.z >> 2) & 0x30303030u));
+        const uint32_t mnB = L.t < 2u ? (hB.z & 0x3f3f3f3fu) : (((hB.w >> 4) & 0x0f0f0f0fu) | ((hB.z >> 2) & 0x30303030u));
+        const uint32_t shift = (L.t & 1u) * 16u;
         const uint32_t magic = opaque_constant(0x4B000000u);
         const f32x2 neg_bias = pack2f(-8388608.0f, -8388608.0f);
-        const f32x2 mm = pack2f(dmin, dmin);
-        const float2 m01 = unpack2(mul2(mm, byte_pair<0>(mn4, magic, neg_bias)));
-        const float2 m23 = unpack2(mul2(mm, byte_pair<2>(mn4, magic, neg_bias)));
+        const float dminA = __half2float(__ushort_as_half((unsigned short)(hA.x >> 16)));
+        const float dminB = __half2float(__ushort_as_half((unsigned short)(hB.x >> 16)));
+        const float2 mA = unpack2(mul2(pack2f(dminA, dminA), byte_pair<0>(mnA >> shift, magic, neg_bias)));
+        const float2 mB = unpack2(mul2(pack2f(dminB, dminB), byte_pair<0>(mnB >> shift, magic, neg_bias)));
 #pragma unroll
         for (int r = 0; r < ROWS; ++r) {
-            const float4* s = reinterpret_cast<const float4*>(sums + r * sums_stride + hf * 8u);
-            const float4 s0 = s[0], s1 = s[1];
-            macc[r] = fmaf(m01.x, s0.x + s0.y, macc[r]);
-            macc[r] = fmaf(m01.y, s0.z + s0.w, macc[r]);
-            macc[r] = fmaf(m23.x, s1.x + s1.y, macc[r]);
-            macc[r] = fmaf(m23.y, s1.z + s1.w, macc[r]);
+            const float4 sm = *reinterpret_cast<const float4*>(sums + r * sums_stride + L.t * 4u);
+            const float x0 = sm.x + sm.y, x1 = sm.z + sm.w;
+            maccA[r] = fmaf(mA.y, x1, fmaf(mA.x, x0, maccA[r]));
+            maccB[r] = fmaf(mB.y, x1, fmaf(mB.x, x0, maccB[r]));
         }
     }
-    __syncwarp();
-    // Phase B: chunk c = elements 64c .. 64c+63; its low nibbles are group 2c, its high nibbles 2c+1.
-    const uint2 scA = *reinterpret_cast<const uint2*>(table + L.g * 8u);
-    const uint2 scB = *reinterpret_cast<const uint2*>(table + (L.g + 8u) * 8u);
-    const float dA = __half2float(__ushort_as_half(*reinterpret_cast<const unsigned short*>(row + 2048u + L.g * 16u)));
-    const float dB = __half2float(__ushort_as_half(*reinterpret_cast<const unsigned short*>(row + 2048u + (L.g + 8u) * 16u)));
+    const float dA = __half2float(__ushort_as_half((unsigned short)(hA.x & 0xffffu)));
+    const float dB = __half2float(__ushort_as_half((unsigned short)(hB.x & 0xffffu)));
+    // Chunk c = elements 64c .. 64c+63; its low nibbles are group 2c, its high nibbles 2c+1.
     const int zero[4] = {0, 0, 0, 0};
     int total[NT][4];
 #pragma unroll
@@ -237,7 +239,7 @@ __device__ __forceinline__ void pair_row_q4k(const uint8_t* row, const uint8_t* 
         const uint4 w = *reinterpret_cast<const uint4*>(row + c * 512 + L.lane * 16u);
         const uint32_t lo[4] = {w.x & 0x0f0f0f0fu, w.z & 0x0f0f0f0fu, w.y & 0x0f0f0f0fu, w.w & 0x0f0f0f0fu};
         const uint32_t hi[4] = {(w.x >> 4) & 0x0f0f0f0fu, (w.z >> 4) & 0x0f0f0f0fu, (w.y >> 4) & 0x0f0f0f0fu, (w.w >> 4) & 0x0f0f0f0fu};
-        const uint32_t wordA = c < 2 ? scA.x : scA.y, wordB = c < 2 ? scB.x : scB.y;
+        const uint32_t wordA = scA[c >> 1], wordB = scB[c >> 1];
         const int sAl = (c & 1) ? byte_u<2>(wordA) : byte_u<0>(wordA), sAh = (c & 1) ? byte_u<3>(wordA) : byte_u<1>(wordA);
         const int sBl = (c & 1) ? byte_u<2>(wordB) : byte_u<0>(wordB), sBh = (c & 1) ? byte_u<3>(wordB) : byte_u<1>(wordB);
 #pragma unroll
@@ -261,35 +263,33 @@ __device__ __forceinline__ void pair_row_q4k(const uint8_t* row, const uint8_t* 
 // the activation sums.
 template <int ROWS, int NT, uint32_t FRAG_STRIDE>
 __device__ __forceinline__ void pair_row_q6k(const uint8_t* row, const uint8_t* frag, const float* sums,
-                                             uint32_t sums_stride, const float* scales, uint8_t* table,
-                                             const GemvLane& L, f32x2 (&accA)[NT], f32x2 (&accB)[NT], float (&macc)[ROWS]) {
-    {   // Phase A: lane (column, half) accumulates d * scale_j * (sum of group j) for sub-scales 8*half .. 8*half+7.
-        const uint32_t col = L.lane & 15u, hf = L.lane >> 4;
-        const uint2 s8 = *reinterpret_cast<const uint2*>(row + 3072u + col * 16u + hf * 8u);
-        const float d = __half2float(__ushort_as_half(*reinterpret_cast<const unsigned short*>(row + 3328u + col * 2u)));
-        const uint32_t magic = opaque_constant(0x4B000000u);
-        const f32x2 neg_bias = pack2f(-(8388608.0f + 128.0f), -(8388608.0f + 128.0f));   // int8 made unsigned by flipping bit 7
-        const f32x2 dd = pack2f(d, d);
-        const uint32_t u0 = s8.x ^ 0x80808080u, u1 = s8.y ^ 0x80808080u;
-        const float2 a01 = unpack2(mul2(dd, byte_pair<0>(u0, magic, neg_bias))), a23 = unpack2(mul2(dd, byte_pair<2>(u0, magic, neg_bias)));
-        const float2 a45 = unpack2(mul2(dd, byte_pair<0>(u1, magic, neg_bias))), a67 = unpack2(mul2(dd, byte_pair<2>(u1, magic, neg_bias)));
-#pragma unroll
-        for (int r = 0; r < ROWS; ++r) {
-            const float4* s = reinterpret_cast<const float4*>(sums + r * sums_stride + hf * 8u);
-            const float4 s0 = s[0], s1 = s[1];
-            macc[r] = fmaf(a01.x, s0.x, macc[r]); macc[r] = fmaf(a01.y, s0.y, macc[r]);
-            macc[r] = fmaf(a23.x, s0.z, macc[r]); macc[r] = fmaf(a23.y, s0.w, macc[r]);
-            macc[r] = fmaf(a45.x, s1.x, macc[r]); macc[r] = fmaf(a45.y, s1.y, macc[r]);
-            macc[r] = fmaf(a67.x, s1.z, macc[r]); macc[r] = fmaf(a67.y, s1.w, macc[r]);
-        }
-    }
-    // Phase B: half h = elements 128h .. 128h+127 = four quarters q of 32; 16-element group
-    // (q, s) is scale group 8h + 2q + s.  ql byte l of the half serves quarters 0 (low nibble)
-    // and 2 (high nibble), byte 32 + l quarters 1 and 3; qh byte l holds two bits per quarter.
+                                             uint32_t sums_stride, const float* scales, const GemvLane& L,
+                                             f32x2 (&accA)[NT], f32x2 (&accB)[NT], float (&maccA)[ROWS], float (&maccB)[ROWS]) {
+    // The sixteen int8 sub-scales and the f16 scale of this lane's two columns.
     const uint4 scA = *reinterpret_cast<const uint4*>(row + 3072u + L.g * 16u);
     const uint4 scB = *reinterpret_cast<const uint4*>(row + 3072u + (L.g + 8u) * 16u);
     const float dA = __half2float(__ushort_as_half(*reinterpret_cast<const unsigned short*>(row + 3328u + L.g * 2u)));
     const float dB = __half2float(__ushort_as_half(*reinterpret_cast<const unsigned short*>(row + 3328u + (L.g + 8u) * 2u)));
+    {   // This lane's share of the correction term: d * scale_j * (sum of group j) for groups 4t .. 4t+3.
+        const uint32_t wA = L.t == 0u ? scA.x : L.t == 1u ? scA.y : L.t == 2u ? scA.z : scA.w;
+        const uint32_t wB = L.t == 0u ? scB.x : L.t == 1u ? scB.y : L.t == 2u ? scB.z : scB.w;
+        const uint32_t magic = opaque_constant(0x4B000000u);
+        const f32x2 neg_bias = pack2f(-(8388608.0f + 128.0f), -(8388608.0f + 128.0f));   // int8 made unsigned by flipping bit 7
+        const f32x2 ddA = pack2f(dA, dA), ddB = pack2f(dB, dB);
+        const float2 a01 = unpack2(mul2(ddA, byte_pair<0>(wA ^ 0x80808080u, magic, neg_bias)));
+        const float2 a23 = unpack2(mul2(ddA, byte_pair<2>(wA ^ 0x80808080u, magic, neg_bias)));
+        const float2 b01 = unpack2(mul2(ddB, byte_pair<0>(wB ^ 0x80808080u, magic, neg_bias)));
+        const float2 b23 = unpack2(mul2(ddB, byte_pair<2>(wB ^ 0x80808080u, magic, neg_bias)));
+#pragma unroll
+        for (int r = 0; r < ROWS; ++r) {
+            const float4 sm = *reinterpret_cast<const float4*>(sums + r * sums_stride + L.t * 4u);
+            maccA[r] = fmaf(a23.y, sm.w, fmaf(a23.x, sm.z, fmaf(a01.y, sm.y, fmaf(a01.x, sm.x, maccA[r]))));
+            maccB[r] = fmaf(b23.y, sm.w, fmaf(b23.x, sm.z, fmaf(b01.y, sm.y, fmaf(b01.x, sm.x, maccB[r]))));
+        }
+    }
+    // Half h = elements 128h .. 128h+127 = four quarters q of 32; 16-element group (q, s) is scale
+    // group 8h + 2q + s.  ql byte l of the half serves quarters 0 (low nibble) and 2 (high nibble),
+    // byte 32 + l quarters 1 and 3; qh byte l holds two bits per quarter.
     const int zero[4] = {0, 0, 0, 0};
     int total[NT][4];
 #pragma unroll
@@ -624,12 +624,10 @@ __global__ void __launch_bounds__(kGemvWarps * 32, 1) gemv_kernel(const __grid_c
     float* sums = reinterpret_cast<float*>(smem + lay.frag_bytes);
     float* block_scales = reinterpret_cast<float*>(smem + lay.frag_bytes + lay.sums_bytes);
     uint8_t* ring_base = smem + lay.frag_bytes + lay.sums_bytes + lay.scale_bytes;
-    uint8_t* table_base = ring_base + lay.ring_bytes;
-    uint64_t* bars = reinterpret_cast<uint64_t*>(table_base + lay.table_bytes);
+    uint64_t* bars = reinterpret_cast<uint64_t*>(ring_base + lay.ring_bytes);
 
     const uint32_t warp = threadIdx.x >> 5, lane = threadIdx.x & 31u;
     uint8_t* ring = ring_base + warp * (kGemvSlots * p.slot_bytes);
-    uint8_t* table = table_base + warp * kGemvTableBytes;
     uint64_t* bar = bars + warp * kGemvSlots;
 
     // This CTA's K chunk and this warp's sequence of column pairs (over all matrices).
@@ -694,7 +692,7 @@ __global__ void __launch_bounds__(kGemvWarps * 32, 1) gemv_kernel(const __grid_c
     const uint32_t bad = bad_rows;
 
     f32x2 accA[NT], accB[NT];
-    float macc[ROWS];
+    float maccA[ROWS], maccB[ROWS];
     bool failed = false;
     uint32_t slot = 0, phase = 0;
     for (uint32_t item = 0; item < my_items && !failed; ++item) {
@@ -704,7 +702,7 @@ __global__ void __launch_bounds__(kGemvWarps * 32, 1) gemv_kernel(const __grid_c
 #pragma unroll
         for (int nt = 0; nt < NT; ++nt) { accA[nt] = 0ull; accB[nt] = 0ull; }
 #pragma unroll
-        for (int r = 0; r < ROWS; ++r) macc[r] = 0.0f;
+        for (int r = 0; r < ROWS; ++r) { maccA[r] = 0.0f; maccB[r] = 0.0f; }
         for (uint32_t u = 0; u < chunk_count; ++u) {
             if (!mbar_wait(&bar[slot], phase)) { failed = true; break; }
             const uint8_t* row = ring + slot * p.slot_bytes;
@@ -713,20 +711,20 @@ __global__ void __launch_bounds__(kGemvWarps * 32, 1) gemv_kernel(const __grid_c
 #pragma unroll
                 for (int nt = 0; nt < NT; ++nt) scales[nt] = block_scales[my_row[nt] * scales_stride + u];
                 pair_row_q4k<ROWS, NT, FRAG_STRIDE>(row, my_frag + (size_t)u * 8u * FRAG_STRIDE, sums + u * 16u, sums_stride,
-                                                    scales, table, L, accA, accB, macc);
+                                                    scales, L, accA, accB, maccA, maccB);
             } else if (dtype == GF_Q6_K) {
                 float scales[NT];
 #pragma unroll
                 for (int nt = 0; nt < NT; ++nt) scales[nt] = block_scales[my_row[nt] * scales_stride + u];
                 pair_row_q6k<ROWS, NT, FRAG_STRIDE>(row, my_frag + (size_t)u * 8u * FRAG_STRIDE, sums + u * 16u, sums_stride,
-                                                    scales, table, L, accA, accB, macc);
+                                                    scales, L, accA, accB, maccA, maccB);
             } else {
                 float scales[NT];
 #pragma unroll
                 for (int nt = 0; nt < NT; ++nt) scales[nt] = block_scales[my_row[nt] * scales_stride + (u >> 1)];
                 pair_row_q80<ROWS, NT, FRAG_STRIDE>(row, my_frag + (size_t)u * 4u * FRAG_STRIDE, scales, L, accA, accB);
             }
-            __syncwarp();   // every lane has finished reading this slot and the scale table
+            __syncwarp();   // every lane has finished reading this slot
             if (lane == 0) issue_next();
             if (++slot == (uint32_t)kGemvSlots) { slot = 0; phase ^= 1u; }
         }
@@ -745,9 +743,9 @@ __global__ void __launch_bounds__(kGemvWarps * 32, 1) gemv_kernel(const __grid_c
                 partA[i] = __shfl_sync(0xffffffffu, (n & 1) ? a.y : a.x, quad_base + holder);
                 partB[i] = __shfl_sync(0xffffffffu, (n & 1) ? b.y : b.x, quad_base + holder);
             }
-            float m = macc[r];
-            m += __shfl_xor_sync(0xffffffffu, m, 16);
-            const float mA = __shfl_sync(0xffffffffu, m, L.g), mB = __shfl_sync(0xffffffffu, m, L.g + 8u);
+            float mA = maccA[r], mB = maccB[r];      // quad lanes hold the shares of different groups
+            mA += __shfl_xor_sync(0xffffffffu, mA, 1); mB += __shfl_xor_sync(0xffffffffu, mB, 1);
+            mA += __shfl_xor_sync(0xffffffffu, mA, 2); mB += __shfl_xor_sync(0xffffffffu, mB, 2);
             totalA[r] = __fsub_rn(__fadd_rn(__fadd_rn(__fadd_rn(partA[0], partA[1]), partA[2]), partA[3]), __fmul_rn(offset, mA));
             totalB[r] = __fsub_rn(__fadd_rn(__fadd_rn(__fadd_rn(partB[0], partB[1]), partB[2]), partB[3]), __fmul_rn(offset, mB));
             if ((bad >> r) & 1u) totalA[r] = totalB[r] = __int_as_float(0x7fc00000);
@@ -791,6 +789,19 @@ __global__ void __launch_bounds__(kGemvWarps * 32, 1) gemv_kernel(const __grid_c
             if (lane == 0) p.counters[pair] = 0u;
         }
     }
+    if (!failed && lane == 0 && p.next_matrices != 0u) {
+        const uint32_t total = p.next_pairs * p.next_chunks;
+        for (uint32_t idx = blockIdx.x * kGemvWarps + warp; idx < total; idx += gridDim.x * kGemvWarps) {
+            const uint32_t pair = idx / p.next_chunks, c = idx % p.next_chunks;
+            uint32_t m = 0;
+            if (p.next_matrices > 1u && pair >= p.next[1].first_pair) m = 1;
+            if (p.next_matrices > 2u && pair >= p.next[2].first_pair) m = 2;
+            const GemvMatrix& mat = p.next[m];
+            const uint32_t bytes = pair_row_bytes((int)mat.dtype), first = c * p.next_chunk_units;
+            const uint32_t count = min((uint32_t)kGemvSlots, min(p.next_chunk_units, p.next_units - first));
+            l2_prefetch(mat.weight + ((size_t)(pair - mat.first_pair) * p.next_units + first) * bytes, count * bytes);
+        }
+    }
     if (failed) {
         // Give outstanding copies a bounded chance to land before the shared memory is released.
         for (int s = 0; s < kGemvSlots; ++s) mbar_wait(&bar[s], 0);
@@ -811,6 +822,7 @@ struct GemvLaunch {
     const float *in = nullptr, *residual = nullptr, *gamma0 = nullptr, *gamma1 = nullptr;
     float* residual_out = nullptr;
     float eps = 1e-6f;
+    const GemvLaunch* next = nullptr;   // the GEMV launched next in the same stream, if known (weights only are read)
 };
 struct GemvPlan { uint32_t units, unit_elems, total_pairs, chunks, chunk_units, grid, smem, slot_bytes; };
 

@@ -268,23 +268,38 @@ int Model::encode_blocks(uint32_t rows, uint32_t flags) {
     ++launches_;
     float* x = residual_;          // residual stream entering a layer
     float* x2 = post_attention_;   // residual stream after the attention branch
+    // Weight sets of the launches, so that each launch can name the one that follows it.
+    auto qkv_weights = [&](uint32_t l) {
+        const LayerWeights& w = layers_[l];
+        GemvLaunch g;
+        g.k = c.hidden;
+        g.matrices[0] = desc(w.q, raw_q_); g.matrices[1] = desc(w.k, raw_k_); g.matrices[2] = desc(w.v, raw_v_);
+        g.count = unit_elements(w.q.dtype) == unit_elements(w.v.dtype) ? 3 : 2;
+        return g;
+    };
+    auto o_weights = [&](uint32_t l) { GemvLaunch g; g.k = (uint64_t)c.heads * c.head_dim; g.matrices[0] = desc(layers_[l].o, projected_); return g; };
+    auto gate_up_weights = [&](uint32_t l) {
+        GemvLaunch g;
+        g.k = c.hidden;
+        g.matrices[0] = desc(layers_[l].gate, gate_); g.matrices[1] = desc(layers_[l].up, up_);
+        g.count = 2;
+        return g;
+    };
+    auto down_weights = [&](uint32_t l) { GemvLaunch g; g.k = c.ffn; g.matrices[0] = desc(layers_[l].down, projected_); return g; };
+    auto head_weights = [&]() { GemvLaunch g; g.k = c.hidden; g.matrices[0] = desc(has_head_ ? head_ : token_embd_, logits_); return g; };
     for (uint32_t l = 0; l < c.layers; ++l) {
         const LayerWeights& w = layers_[l];
         const LayerCache& cache = caches_[l];
-        GemvLaunch qkv;
-        qkv.k = c.hidden;
-        const bool same_unit = unit_elements(w.q.dtype) == unit_elements(w.v.dtype);
-        qkv.matrices[0] = desc(w.q, raw_q_);
-        qkv.matrices[1] = desc(w.k, raw_k_);
-        qkv.matrices[2] = desc(w.v, raw_v_);
-        qkv.count = same_unit ? 3 : 2;
+        GemvLaunch qkv = qkv_weights(l);
+        if (qkv.count != 3) return fail(GF_ERR_INVALID, "attention projections of one layer must share a block family");
         if (l == 0) { qkv.prologue = kPrologueNorm; qkv.in = x; qkv.gamma1 = w.attn_norm; }
         else {
             qkv.prologue = kPrologueAddNorm; qkv.in = projected_; qkv.residual = x2; qkv.gamma0 = layers_[l - 1].post_ffw_norm;
             qkv.residual_out = x; qkv.gamma1 = w.attn_norm;
         }
+        GemvLaunch o = o_weights(l);
+        qkv.next = &o;
         GF_TRY(run_gemv(qkv, rows));
-        if (!same_unit) return fail(GF_ERR_INVALID, "attention projections of one layer must share a block family");
         RopeStoreParams rp{raw_q_, raw_k_, raw_v_, c.uses_qk_norm ? w.q_norm : nullptr, c.uses_qk_norm ? w.k_norm : nullptr,
                            query_, cache.private_k, cache.private_v, state_dev_, status_dev_, cache.rope_divisors, rows, c.heads, c.kv_heads,
                            c.head_dim, c.rms_eps, cache.rope_base, cache.rope_scale, c.kv_f16};
@@ -300,29 +315,24 @@ int Model::encode_blocks(uint32_t rows, uint32_t flags) {
         ap.softcap = c.attn_softcap; ap.kv_f16 = c.kv_f16;
         GF_TRY(launch_attention(ap, stream_, true));
         launches_ += 2;
-        GemvLaunch o;
-        o.k = (uint64_t)c.heads * c.head_dim;
-        o.matrices[0] = desc(w.o, projected_);
         o.in = attention_out_;
+        GemvLaunch gu = gate_up_weights(l);
+        o.next = &gu;
         GF_TRY(run_gemv(o, rows));
-        GemvLaunch gu;
-        gu.k = c.hidden;
-        gu.matrices[0] = desc(w.gate, gate_);
-        gu.matrices[1] = desc(w.up, up_);
-        gu.count = 2;
         gu.prologue = kPrologueAddNorm; gu.in = projected_; gu.residual = x; gu.gamma0 = w.post_attention_norm;
         gu.residual_out = x2; gu.gamma1 = w.ffn_norm;
+        GemvLaunch down = down_weights(l);
+        gu.next = &down;
         GF_TRY(run_gemv(gu, rows));
-        GemvLaunch down;
-        down.k = c.ffn;
-        down.matrices[0] = desc(w.down, projected_);
         down.prologue = kPrologueGeglu; down.in = gate_; down.residual = up_;
+        GemvLaunch after;
+        const bool has_after = l + 1u < c.layers || (flags & kForwardLogits);
+        if (l + 1u < c.layers) after = qkv_weights(l + 1u); else after = head_weights();
+        if (has_after) down.next = &after;
         GF_TRY(run_gemv(down, rows));
     }
     if (flags & kForwardLogits) {
-        GemvLaunch head;
-        head.k = c.hidden;
-        head.matrices[0] = desc(has_head_ ? head_ : token_embd_, logits_);
+        GemvLaunch head = head_weights();
         head.prologue = kPrologueAddNorm; head.in = projected_; head.residual = x2;
         head.gamma0 = layers_[c.layers - 1].post_ffw_norm; head.residual_out = x; head.gamma1 = output_norm_;
         GF_TRY(run_gemv(head, rows));
@@ -413,7 +423,8 @@ int Model::weight_sweep(uint32_t rows, uint32_t* out_launches, uint64_t* out_byt
     if (rows == 0 || rows > config_.row_capacity) return fail(GF_ERR_INVALID, "bad row count");
     uint32_t launches = 0;
     uint64_t bytes = 0;
-    auto run = [&](std::initializer_list<std::pair<const PackedMatrix*, float*>> set, const float* x) {
+    std::vector<GemvLaunch> sequence;
+    auto add = [&](std::initializer_list<std::pair<const PackedMatrix*, float*>> set, const float* x) {
         GemvLaunch launch;
         launch.count = 0;
         for (const auto& entry : set) {
@@ -422,16 +433,20 @@ int Model::weight_sweep(uint32_t rows, uint32_t* out_launches, uint64_t* out_byt
             bytes += entry.first->native_bytes;
         }
         launch.in = x;
-        ++launches;
-        return run_gemv(launch, rows);
+        sequence.push_back(launch);
     };
     for (const LayerWeights& w : layers_) {
-        GF_TRY(run({{&w.q, raw_q_}, {&w.k, raw_k_}, {&w.v, raw_v_}}, normalized_));
-        GF_TRY(run({{&w.o, projected_}}, attention_out_));
-        GF_TRY(run({{&w.gate, gate_}, {&w.up, up_}}, normalized_));
-        GF_TRY(run({{&w.down, projected_}}, gated_));
+        add({{&w.q, raw_q_}, {&w.k, raw_k_}, {&w.v, raw_v_}}, normalized_);
+        add({{&w.o, projected_}}, attention_out_);
+        add({{&w.gate, gate_}, {&w.up, up_}}, normalized_);
+        add({{&w.down, projected_}}, gated_);
     }
-    GF_TRY(run({{has_head_ ? &head_ : &token_embd_, logits_}}, normalized_));
+    add({{has_head_ ? &head_ : &token_embd_, logits_}}, normalized_);
+    for (size_t i = 0; i < sequence.size(); ++i) {
+        if (i + 1 < sequence.size()) sequence[i].next = &sequence[i + 1];
+        ++launches;
+        GF_TRY(run_gemv(sequence[i], rows));
+    }
     if (out_launches) *out_launches = launches;
     if (out_bytes) *out_bytes = bytes;
     return GF_OK;

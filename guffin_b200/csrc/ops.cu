@@ -3,6 +3,7 @@
 #include "ops.cuh"
 
 #include <cmath>
+#include <cstdlib>
 
 namespace gf {
 
@@ -186,7 +187,7 @@ struct AttentionWindow { uint32_t base_first, base_count, private_start, private
 // Which cached rows a verify/decode row sees: the committed ring rows inside its window, then
 // the private rows of its ancestors, itself included (gemma_target_runtime.cpp:256-268,
 // target_verifier.cpp:186-202).  The sliding window includes the row itself.
-__device__ __forceinline__ AttentionWindow attention_window(uint32_t base, uint32_t row, uint32_t window) {
+__device__ __forceinline__ AttentionWindow attention_window(uint32_t base, uint32_t row, uint32_t window, uint32_t tokens_per_part) {
     AttentionWindow w;
     const uint32_t position = base + row;
     const uint32_t window_start = (window != 0u && position + 1u > window) ? position + 1u - window : 0u;
@@ -196,7 +197,7 @@ __device__ __forceinline__ AttentionWindow attention_window(uint32_t base, uint3
     w.private_count = row + 1u - w.private_start;
     w.count = w.base_count + w.private_count;
     w.parts = min((uint32_t)kMaxAttentionPartitions,
-                  (w.count + kAttentionTokensPerPartition - 1u) / kAttentionTokensPerPartition);
+                  (w.count + tokens_per_part - 1u) / tokens_per_part);
     return w;
 }
 
@@ -215,7 +216,7 @@ __global__ void __launch_bounds__(128) attention_kernel(AttentionParams p) {
     pdl_launch_dependents();
     const uint32_t kvh = blockIdx.x, part = blockIdx.y, row = blockIdx.z;
     const uint32_t warp = threadIdx.x >> 5, lane = threadIdx.x & 31u;
-    const AttentionWindow win = attention_window(*p.base_position, row, p.window);
+    const AttentionWindow win = attention_window(*p.base_position, row, p.window, p.tokens_per_part);
     if (part >= win.parts) return;
     const uint32_t kv_width = p.kv_heads * 256u;
     const KV* ring_k = static_cast<const KV*>(p.ring_k);
@@ -456,7 +457,10 @@ static int launch_attention_typed(const AttentionParams& p, cudaStream_t stream,
     return status;
 }
 
-int launch_attention(const AttentionParams& p, cudaStream_t stream, bool pdl) {
+int launch_attention(const AttentionParams& params, cudaStream_t stream, bool pdl) {
+    AttentionParams p = params;
+    static const uint32_t tuned = getenv("GF_TUNE_ATTN_TOKENS") ? (uint32_t)atoi(getenv("GF_TUNE_ATTN_TOKENS")) : 0u;
+    p.tokens_per_part = tuned ? tuned : (uint32_t)kAttentionTokensPerPartition;
     if (p.head_dim != 256u) return fail(GF_ERR_INVALID, "attention: head_dim must be 256 (got %u)", p.head_dim);
     if (p.heads % p.kv_heads) return fail(GF_ERR_INVALID, "attention: heads %u not a multiple of kv heads %u", p.heads, p.kv_heads);
     return p.kv_f16 ? launch_attention_typed<__half>(p, stream, pdl) : launch_attention_typed<float>(p, stream, pdl);

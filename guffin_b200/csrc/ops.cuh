@@ -45,6 +45,7 @@ struct AttentionParams {
     uint32_t rows, heads, kv_heads, head_dim;
     uint32_t ring_mask;        // ring_rows - 1
     uint32_t window;           // 0 = global layer
+    uint32_t tokens_per_part;  // set by launch_attention
     float scale, softcap;
     int kv_f16;
 };
