@@ -113,10 +113,6 @@ __device__ __forceinline__ void bulk_load(void* dst, const void* src, uint32_t b
         "cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];"
         ::"r"(smem_u32(dst)), "l"(src), "r"(bytes), "r"(smem_u32(bar)) : "memory");
 }
-// Hint: pull [src, src + bytes) into L2 (16-byte aligned address and size); nothing waits on it.
-__device__ __forceinline__ void l2_prefetch(const void* src, uint32_t bytes) {
-    asm volatile("cp.async.bulk.prefetch.L2.global [%0], %1;" ::"l"(src), "r"(bytes) : "memory");
-}
 // Programmatic dependent launch: let the next kernel in the stream start its prologue, and
 // wait for everything the previous kernel wrote.
 __device__ __forceinline__ void pdl_launch_dependents() {

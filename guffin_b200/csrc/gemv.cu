@@ -149,27 +149,6 @@ int gemv_launch(const GemvLaunch& launch, uint32_t* counters, float* partial, si
     p.residual_out = launch.residual_out;
     p.eps = launch.eps;
     p.error_flag = error_flag;
-    if (launch.next) {
-        GemvLaunch hint = *launch.next;
-        hint.rows = launch.rows;
-        GemvPlan next_plan;
-        if (gemv_plan(hint, next_plan) == GF_OK) {
-            uint32_t next_first = 0;
-            for (uint32_t i = 0; i < hint.count; ++i) {
-                p.next[i].weight = static_cast<const uint8_t*>(hint.matrices[i].packed);
-                p.next[i].dtype = (uint32_t)hint.matrices[i].dtype;
-                p.next[i].pairs = (uint32_t)((hint.matrices[i].n + 15u) / 16u);
-                p.next[i].first_pair = next_first;
-                next_first += p.next[i].pairs;
-            }
-            p.next_matrices = hint.count;
-            // Only the pairs of the next kernel's first round: what its warps request before anything else.
-            p.next_pairs = std::min(next_plan.total_pairs, next_plan.grid / next_plan.chunks * (uint32_t)kGemvWarps);
-            p.next_units = next_plan.units;
-            p.next_chunks = next_plan.chunks;
-            p.next_chunk_units = next_plan.chunk_units;
-        }
-    }
     if (plan.chunks > 1) {
         const size_t need = (size_t)plan.chunks * launch.rows * plan.total_pairs * 16u * sizeof(float);
         if (!counters || !partial || partial_bytes < need) return fail(GF_ERR_INVALID, "gf_matmul: this shape needs a %zu-byte split-K workspace", need);

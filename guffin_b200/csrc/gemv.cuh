@@ -57,11 +57,6 @@ struct GemvParams {
     const float *in, *residual, *gamma0, *gamma1;
     float* residual_out;
     float eps;
-    // The GEMV that runs next in the stream (if known): the pair rows its warps will ask for first
-    // are pulled into L2 by this kernel's warps as they run out of work, so the HBM stays busy
-    // across the kernel boundary.
-    GemvMatrix next[kGemvMaxMatrices];
-    uint32_t next_matrices, next_pairs, next_units, next_chunks, next_chunk_units;
     float* partial;            // [chunks][rows][total_pairs * 16] when chunks > 1
     uint32_t* counters;        // [total_pairs] arrival counts, zero between launches
     int* error_flag;           // set to 1 when a bounded wait gives up
@@ -789,19 +784,6 @@ __global__ void __launch_bounds__(kGemvWarps * 32, 1) gemv_kernel(const __grid_c
             if (lane == 0) p.counters[pair] = 0u;
         }
     }
-    if (!failed && lane == 0 && p.next_matrices != 0u) {
-        const uint32_t total = p.next_pairs * p.next_chunks;
-        for (uint32_t idx = blockIdx.x * kGemvWarps + warp; idx < total; idx += gridDim.x * kGemvWarps) {
-            const uint32_t pair = idx / p.next_chunks, c = idx % p.next_chunks;
-            uint32_t m = 0;
-            if (p.next_matrices > 1u && pair >= p.next[1].first_pair) m = 1;
-            if (p.next_matrices > 2u && pair >= p.next[2].first_pair) m = 2;
-            const GemvMatrix& mat = p.next[m];
-            const uint32_t bytes = pair_row_bytes((int)mat.dtype), first = c * p.next_chunk_units;
-            const uint32_t count = min((uint32_t)kGemvSlots, min(p.next_chunk_units, p.next_units - first));
-            l2_prefetch(mat.weight + ((size_t)(pair - mat.first_pair) * p.next_units + first) * bytes, count * bytes);
-        }
-    }
     if (failed) {
         // Give outstanding copies a bounded chance to land before the shared memory is released.
         for (int s = 0; s < kGemvSlots; ++s) mbar_wait(&bar[s], 0);
@@ -822,7 +804,6 @@ struct GemvLaunch {
     const float *in = nullptr, *residual = nullptr, *gamma0 = nullptr, *gamma1 = nullptr;
     float* residual_out = nullptr;
     float eps = 1e-6f;
-    const GemvLaunch* next = nullptr;   // the GEMV launched next in the same stream, if known (weights only are read)
 };
 struct GemvPlan { uint32_t units, unit_elems, total_pairs, chunks, chunk_units, grid, smem, slot_bytes; };
 

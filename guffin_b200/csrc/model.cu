@@ -268,7 +268,7 @@ int Model::encode_blocks(uint32_t rows, uint32_t flags) {
     ++launches_;
     float* x = residual_;          // residual stream entering a layer
     float* x2 = post_attention_;   // residual stream after the attention branch
-    // Weight sets of the launches, so that each launch can name the one that follows it.
+    // Weight sets of the launches.
     auto qkv_weights = [&](uint32_t l) {
         const LayerWeights& w = layers_[l];
         GemvLaunch g;
@@ -298,7 +298,6 @@ int Model::encode_blocks(uint32_t rows, uint32_t flags) {
             qkv.residual_out = x; qkv.gamma1 = w.attn_norm;
         }
         GemvLaunch o = o_weights(l);
-        qkv.next = &o;
         GF_TRY(run_gemv(qkv, rows));
         RopeStoreParams rp{raw_q_, raw_k_, raw_v_, c.uses_qk_norm ? w.q_norm : nullptr, c.uses_qk_norm ? w.k_norm : nullptr,
                            query_, cache.private_k, cache.private_v, state_dev_, status_dev_, cache.rope_divisors, rows, c.heads, c.kv_heads,
@@ -317,18 +316,12 @@ int Model::encode_blocks(uint32_t rows, uint32_t flags) {
         launches_ += 2;
         o.in = attention_out_;
         GemvLaunch gu = gate_up_weights(l);
-        o.next = &gu;
         GF_TRY(run_gemv(o, rows));
         gu.prologue = kPrologueAddNorm; gu.in = projected_; gu.residual = x; gu.gamma0 = w.post_attention_norm;
         gu.residual_out = x2; gu.gamma1 = w.ffn_norm;
         GemvLaunch down = down_weights(l);
-        gu.next = &down;
         GF_TRY(run_gemv(gu, rows));
         down.prologue = kPrologueGeglu; down.in = gate_; down.residual = up_;
-        GemvLaunch after;
-        const bool has_after = l + 1u < c.layers || (flags & kForwardLogits);
-        if (l + 1u < c.layers) after = qkv_weights(l + 1u); else after = head_weights();
-        if (has_after) down.next = &after;
         GF_TRY(run_gemv(down, rows));
     }
     if (flags & kForwardLogits) {
@@ -443,7 +436,6 @@ int Model::weight_sweep(uint32_t rows, uint32_t* out_launches, uint64_t* out_byt
     }
     add({{has_head_ ? &head_ : &token_embd_, logits_}}, normalized_);
     for (size_t i = 0; i < sequence.size(); ++i) {
-        if (i + 1 < sequence.size()) sequence[i].next = &sequence[i + 1];
         ++launches;
         GF_TRY(run_gemv(sequence[i], rows));
     }
