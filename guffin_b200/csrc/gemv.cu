@@ -2,9 +2,6 @@
 #include "gemv.cuh"
 
 #include <algorithm>
-#include <cstdio>
-#include <cstdlib>
-#include <cstring>
 #include <mutex>
 
 namespace gf {
@@ -55,15 +52,6 @@ int gemv_plan(const GemvLaunch& launch, GemvPlan& plan) {
             plan.chunks = chunks;
             plan.chunk_units = chunk_units;
             plan.grid = group_ctas * chunks;
-        }
-    }
-    if (const char* tune = getenv("GF_TUNE_CHUNKS")) {      // "units:pairs:chunks,..." (experiments only)
-        for (const char* q = tune; q && *q; q = strchr(q, ',') ? strchr(q, ',') + 1 : nullptr) {
-            unsigned u = 0, pr = 0, ch = 0;
-            if (sscanf(q, "%u:%u:%u", &u, &pr, &ch) == 3 && u == plan.units && pr == plan.total_pairs && ch >= 1 && ch <= plan.units) {
-                const uint32_t cu = (plan.units + ch - 1u) / ch;
-                if (cu <= limit && (ch - 1u) * cu < plan.units) { plan.chunks = ch; plan.chunk_units = cu; plan.grid = slots / ch * ch; }
-            }
         }
     }
     if (plan.chunks == 0) return fail(GF_ERR_INVALID, "gf_matmul: no decomposition fits K=%llu rows=%u", (unsigned long long)launch.k, launch.rows);

@@ -3,7 +3,6 @@
 #include "ops.cuh"
 
 #include <cmath>
-#include <cstdlib>
 
 namespace gf {
 
@@ -201,16 +200,16 @@ __device__ __forceinline__ AttentionWindow attention_window(uint32_t base, uint3
     return w;
 }
 
-// Online-softmax GQA, head_dim 256: grid (kv_head, partition, row), four warps per block.  A warp
+// Online-softmax GQA, head_dim 256: grid (kv_head, partition, row), kAttentionWarps warps per block.  A warp
 // walks quads of cached rows, loading the next quad while it works on the current one; a lane
 // owns eight of the 256 dimensions, so K and V rows are read as one coalesced 512-byte (F16) or
 // 1-KiB (F32) line per row, shared by the G query heads.  The block that finishes last for a
 // (row, kv head) merges the partitions in partition order.
 template <typename KV, int G>
-__global__ void __launch_bounds__(128) attention_kernel(AttentionParams p) {
-    __shared__ float scores[4][16];
-    __shared__ float warp_m[4][G], warp_l[4][G];
-    __shared__ float warp_acc[4][G][256];
+__global__ void __launch_bounds__(kAttentionWarps * 32) attention_kernel(AttentionParams p) {
+    __shared__ float scores[kAttentionWarps][16];
+    __shared__ float warp_m[kAttentionWarps][G], warp_l[kAttentionWarps][G];
+    __shared__ float warp_acc[kAttentionWarps][G][256];
     __shared__ uint32_t arrival;
     pdl_wait();
     pdl_launch_dependents();
@@ -237,7 +236,7 @@ __global__ void __launch_bounds__(128) attention_kernel(AttentionParams p) {
 #pragma unroll
         for (int d = 0; d < 8; ++d) acc[g][d] = 0.0f;
     }
-    const uint32_t quads = (win.count + 3u) / 4u, step = win.parts * 4u;
+    const uint32_t quads = (win.count + 3u) / 4u, step = win.parts * kAttentionWarps;
     KvRaw<KV> kraw[4], vraw[4];
     auto fetch = [&](uint32_t quad) {
 #pragma unroll
@@ -256,7 +255,7 @@ __global__ void __launch_bounds__(128) attention_kernel(AttentionParams p) {
             load_raw(vp, vraw[t]);
         }
     };
-    uint32_t quad = part * 4u + warp;
+    uint32_t quad = part * kAttentionWarps + warp;
     if (quad < quads) fetch(quad);
     for (; quad < quads; quad += step) {
         float kf[4][8], vf[4][8];
@@ -316,7 +315,7 @@ __global__ void __launch_bounds__(128) attention_kernel(AttentionParams p) {
             m[g] = m_new;
         }
     }
-    // Combine the four warps in warp order.
+    // Combine the warps in warp order.
 #pragma unroll
     for (int g = 0; g < G; ++g) {
         if (lane == 0) { warp_m[warp][g] = m[g]; warp_l[warp][g] = l[g]; }
@@ -327,9 +326,9 @@ __global__ void __launch_bounds__(128) attention_kernel(AttentionParams p) {
     for (uint32_t idx = threadIdx.x; idx < (uint32_t)G * 256u; idx += blockDim.x) {
         const uint32_t g = idx / 256u, d = idx % 256u;
         float mm = -INFINITY;
-        for (int w = 0; w < 4; ++w) mm = fmaxf(mm, warp_m[w][g]);
+        for (int w = 0; w < kAttentionWarps; ++w) mm = fmaxf(mm, warp_m[w][g]);
         float a = 0.0f, ll = 0.0f;
-        for (int w = 0; w < 4; ++w) {
+        for (int w = 0; w < kAttentionWarps; ++w) {
             if (warp_l[w][g] == 0.0f) continue;
             const float f = expf(warp_m[w][g] - mm);
             a = fmaf(warp_acc[w][g][d], f, a);
@@ -450,17 +449,18 @@ static int launch_attention_typed(const AttentionParams& p, cudaStream_t stream,
     const dim3 grid(p.kv_heads, kMaxAttentionPartitions, p.rows);
     const uint32_t group = p.heads / p.kv_heads;
     int status;
-    if (group == 1u) status = launch_kernel(attention_kernel<KV, 1>, grid, dim3(128), 0, stream, pdl, p);
-    else if (group == 2u) status = launch_kernel(attention_kernel<KV, 2>, grid, dim3(128), 0, stream, pdl, p);
-    else if (group == 4u) status = launch_kernel(attention_kernel<KV, 4>, grid, dim3(128), 0, stream, pdl, p);
+    if (group == 1u) status = launch_kernel(attention_kernel<KV, 1>, grid, dim3(kAttentionWarps * 32), 0, stream, pdl, p);
+    else if (group == 2u) status = launch_kernel(attention_kernel<KV, 2>, grid, dim3(kAttentionWarps * 32), 0, stream, pdl, p);
+    else if (group == 4u) status = launch_kernel(attention_kernel<KV, 4>, grid, dim3(kAttentionWarps * 32), 0, stream, pdl, p);
     else return fail(GF_ERR_INVALID, "attention: query/KV head ratio %u unsupported (1, 2, 4)", group);
     return status;
 }
 
 int launch_attention(const AttentionParams& params, cudaStream_t stream, bool pdl) {
     AttentionParams p = params;
-    static const uint32_t tuned = getenv("GF_TUNE_ATTN_TOKENS") ? (uint32_t)atoi(getenv("GF_TUNE_ATTN_TOKENS")) : 0u;
-    p.tokens_per_part = tuned ? tuned : (uint32_t)kAttentionTokensPerPartition;
+    // Few (kv head, row) pairs leave SMs idle unless the keys are cut finer; with many of them
+    // fewer, longer partitions save merge work.
+    p.tokens_per_part = p.kv_heads * p.rows >= 8u ? 2u * kAttentionTokensPerPartition : (uint32_t)kAttentionTokensPerPartition;
     if (p.head_dim != 256u) return fail(GF_ERR_INVALID, "attention: head_dim must be 256 (got %u)", p.head_dim);
     if (p.heads % p.kv_heads) return fail(GF_ERR_INVALID, "attention: heads %u not a multiple of kv heads %u", p.heads, p.kv_heads);
     return p.kv_f16 ? launch_attention_typed<__half>(p, stream, pdl) : launch_attention_typed<float>(p, stream, pdl);

@@ -9,6 +9,7 @@ namespace gf {
 
 constexpr int kMaxAttentionPartitions = 32;   // verifier_max_partitions in the reference
 constexpr int kAttentionTokensPerPartition = 64;
+constexpr int kAttentionWarps = 8;
 
 // Status bits shared with the reference's validation word
 // (metal_kernels.mm:2332,2357,2370,2484; metal_command_context.hpp:17).
