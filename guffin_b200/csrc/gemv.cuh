@@ -372,19 +372,24 @@ __device__ __forceinline__ void gemv_block_sums(float (&v)[ROWS], float* scratch
 #pragma unroll
     for (int r = 0; r < ROWS; ++r) {
         v[r] = warp_sum(v[r]);
-        if (lane == 0) scratch[warp * ROWS + r] = v[r];
+        if (lane == 0) scratch[r * kGemvWarps + warp] = v[r];
     }
     __syncthreads();
+    // Every warp adds the kGemvWarps partial sums of each row the same way: lane w holds warp w's.
 #pragma unroll
     for (int r = 0; r < ROWS; ++r) {
-        float total = 0.0f;
+        float part = lane < (uint32_t)kGemvWarps ? scratch[r * kGemvWarps + lane] : 0.0f;
 #pragma unroll
-        for (int w = 0; w < kGemvWarps; ++w) total += scratch[w * ROWS + r];
-        v[r] = total;
+        for (int offset = 8; offset > 0; offset >>= 1) part += __shfl_xor_sync(0xffffffffu, part, offset);
+        v[r] = __shfl_sync(0xffffffffu, part, 0);
     }
 }
+// 1 / sqrt(mean square + eps): hardware reciprocal square root plus one Newton step (about one ulp;
+// the exact divide and square root sequences cost more than the rest of the prologue).
 __device__ __forceinline__ float rms_scale(float sum_of_squares, uint32_t k, float eps) {
-    return __fdiv_rn(1.0f, __fsqrt_rn(__fadd_rn(__fdiv_rn(sum_of_squares, (float)k), eps)));
+    const float a = fmaf(sum_of_squares, 1.0f / (float)k, eps);
+    const float y = rsqrtf(a);
+    return y * fmaf(-0.5f * a, y * y, 1.5f);
 }
 __device__ __forceinline__ float sum_squares(const float (&v)[8], float sum) {
 #pragma unroll
