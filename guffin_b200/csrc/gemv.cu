@@ -6,6 +6,9 @@
 
 namespace gf {
 
+// The kernel is compiled for 1, 2, 3, 4 and 8 rows; 5 to 7 rows run the eight-row instance.
+static uint32_t instance_rows(uint32_t rows) { return rows <= 4u ? rows : 8u; }
+
 static uint32_t max_chunk_units(uint32_t rows, uint32_t unit_elems, uint32_t slot_bytes) {
     uint32_t best = 0;
     for (uint32_t cu = 1; cu <= 64u; ++cu)
@@ -32,7 +35,7 @@ int gemv_plan(const GemvLaunch& launch, GemvPlan& plan) {
     if (launch.k == 0 || launch.k % plan.unit_elems != 0 || launch.k > (1ull << 24))
         return fail(GF_ERR_INVALID, "gf_matmul: K=%llu must be a positive multiple of %u", (unsigned long long)launch.k, plan.unit_elems);
     plan.units = (uint32_t)(launch.k / plan.unit_elems);
-    const uint32_t limit = max_chunk_units(launch.rows, plan.unit_elems, plan.slot_bytes);
+    const uint32_t limit = max_chunk_units(instance_rows(launch.rows), plan.unit_elems, plan.slot_bytes);
     if (limit == 0) return fail(GF_ERR_INVALID, "gf_matmul: no decomposition fits");
     const uint32_t slots = (uint32_t)sm_count();           // one CTA per SM
     // Critical path of a warp, in pair rows: rounds x (units per item + per-item overhead); the
@@ -55,7 +58,7 @@ int gemv_plan(const GemvLaunch& launch, GemvPlan& plan) {
         }
     }
     if (plan.chunks == 0) return fail(GF_ERR_INVALID, "gf_matmul: no decomposition fits K=%llu rows=%u", (unsigned long long)launch.k, launch.rows);
-    plan.smem = gemv_smem_layout(launch.rows, plan.chunk_units, plan.unit_elems, plan.slot_bytes).total;
+    plan.smem = gemv_smem_layout(instance_rows(launch.rows), plan.chunk_units, plan.unit_elems, plan.slot_bytes).total;
     return GF_OK;
 }
 
@@ -64,7 +67,7 @@ static size_t counters_bytes(const GemvPlan& plan) { return ((size_t)plan.total_
 size_t gemv_partial_bytes(const GemvLaunch& launch) {
     GemvPlan plan;
     if (gemv_plan(launch, plan) != GF_OK || plan.chunks == 1) return 0;
-    return (size_t)plan.chunks * launch.rows * plan.total_pairs * 16u * sizeof(float);
+    return (size_t)plan.chunks * instance_rows(launch.rows) * plan.total_pairs * 16u * sizeof(float);
 }
 
 size_t gemv_counter_bytes(const GemvLaunch& launch) {
@@ -129,6 +132,7 @@ int gemv_launch(const GemvLaunch& launch, uint32_t* counters, float* partial, si
     p.k = (uint32_t)launch.k;
     p.units = plan.units;
     p.unit_elems = plan.unit_elems;
+    p.active_rows = launch.rows;
     p.chunks = plan.chunks;
     p.chunk_units = plan.chunk_units;
     p.slot_bytes = plan.slot_bytes;
@@ -138,7 +142,7 @@ int gemv_launch(const GemvLaunch& launch, uint32_t* counters, float* partial, si
     p.eps = launch.eps;
     p.error_flag = error_flag;
     if (plan.chunks > 1) {
-        const size_t need = (size_t)plan.chunks * launch.rows * plan.total_pairs * 16u * sizeof(float);
+        const size_t need = (size_t)plan.chunks * instance_rows(launch.rows) * plan.total_pairs * 16u * sizeof(float);
         if (!counters || !partial || partial_bytes < need) return fail(GF_ERR_INVALID, "gf_matmul: this shape needs a %zu-byte split-K workspace", need);
         p.counters = counters;
         p.partial = partial;
@@ -147,7 +151,8 @@ int gemv_launch(const GemvLaunch& launch, uint32_t* counters, float* partial, si
         case 1: return launch_instance<1>(p, plan, stream, programmatic);
         case 2: return launch_instance<2>(p, plan, stream, programmatic);
         case 3: return launch_instance<3>(p, plan, stream, programmatic);
-        default: return launch_instance<4>(p, plan, stream, programmatic);
+        case 4: return launch_instance<4>(p, plan, stream, programmatic);
+        default: return launch_instance<8>(p, plan, stream, programmatic);      // 5..8 rows: the eight-row instance
     }
 }
 

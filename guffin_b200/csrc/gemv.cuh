@@ -30,7 +30,7 @@ namespace gf {
 
 constexpr int kGemvWarps = 16;       // warps per CTA; one CTA per SM
 constexpr int kGemvSlots = 3;        // ring depth per warp, one pair row per slot
-constexpr uint32_t kGemvSmemLimit = 226u * 1024u;    // dynamic part; the static arrays take the rest of the 227 KB
+constexpr uint32_t kGemvSmemLimit = 225u * 1024u;    // dynamic part; the static arrays take the rest of the 227 KB
 constexpr int kGemvMaxMatrices = 3;
 
 // How the activation rows are produced from global memory before the weights are applied.
@@ -51,6 +51,7 @@ struct GemvParams {
     GemvMatrix m[kGemvMaxMatrices];
     uint32_t matrices, total_pairs;
     uint32_t k, units, unit_elems;
+    uint32_t active_rows;                 // rows that exist; the kernel instance may be compiled for more
     uint32_t chunks, chunk_units;
     uint32_t slot_bytes;                  // ring slot size
     uint32_t prologue;
@@ -489,7 +490,7 @@ __device__ __forceinline__ void stage_activations(const GemvParams& p, uint32_t 
                                                   const GemvStage& st, float* scratch) {
     const bool norms = p.prologue == kPrologueNorm || p.prologue == kPrologueAddNorm;
     const uint32_t row_pieces = p.k / 8u;
-    if (norms && row_pieces <= blockDim.x && (first & 255u) == 0u) {
+    if (ROWS <= 4 && norms && row_pieces <= blockDim.x && (first & 255u) == 0u) {
         const uint32_t piece = threadIdx.x;
         const bool live = piece < row_pieces;
         const uint32_t o = piece * 8u;
@@ -503,6 +504,7 @@ __device__ __forceinline__ void stage_activations(const GemvParams& p, uint32_t 
         if (live) {
 #pragma unroll
             for (int r = 0; r < ROWS; ++r) {
+                if ((uint32_t)r >= p.active_rows) continue;
                 load8f(p.in + (size_t)r * p.k + o, x[r]);
                 if (p.prologue == kPrologueAddNorm) load8f(p.residual + (size_t)r * p.k + o, res[r]);
             }
@@ -519,7 +521,7 @@ __device__ __forceinline__ void stage_activations(const GemvParams& p, uint32_t 
                 const float inv = rms_scale(ss[r], p.k, p.eps);
 #pragma unroll
                 for (int i = 0; i < 8; ++i) x[r][i] = __fadd_rn(res[r][i], __fmul_rn(__fmul_rn(x[r][i], inv), g0[i]));
-                if (blockIdx.x == 0 && live) store8f(p.residual_out + (size_t)r * p.k + o, x[r]);
+                if (blockIdx.x == 0 && live && (uint32_t)r < p.active_rows) store8f(p.residual_out + (size_t)r * p.k + o, x[r]);
                 ss[r] = sum_squares(x[r], 0.0f);
             }
             gemv_block_sums<ROWS>(ss, scratch + kGemvWarps * ROWS);
@@ -543,7 +545,7 @@ __device__ __forceinline__ void stage_activations(const GemvParams& p, uint32_t 
 #pragma unroll
         for (int r = 0; r < ROWS; ++r) {
             ss[r] = 0.0f;
-            for (uint32_t c = threadIdx.x; c < row_pieces; c += blockDim.x) {
+            for (uint32_t c = threadIdx.x; c < row_pieces && (uint32_t)r < p.active_rows; c += blockDim.x) {
                 float x[8];
                 load8f(p.in + (size_t)r * p.k + c * 8u, x);
                 ss[r] = sum_squares(x, ss[r]);
@@ -557,7 +559,7 @@ __device__ __forceinline__ void stage_activations(const GemvParams& p, uint32_t 
 #pragma unroll
             for (int r = 0; r < ROWS; ++r) {
                 ss[r] = 0.0f;
-                for (uint32_t c = threadIdx.x; c < row_pieces; c += blockDim.x) {
+                for (uint32_t c = threadIdx.x; c < row_pieces && (uint32_t)r < p.active_rows; c += blockDim.x) {
                     float x[8], a[8], gm[8];
                     load8f(p.in + (size_t)r * p.k + c * 8u, x);
                     load8f(p.residual + (size_t)r * p.k + c * 8u, a);
@@ -579,7 +581,7 @@ __device__ __forceinline__ void stage_activations(const GemvParams& p, uint32_t 
         float v[8];
 #pragma unroll
         for (int i = 0; i < 8; ++i) v[i] = 0.0f;
-        if (o < count) {
+        if (o < count && r < p.active_rows) {
             const size_t gi = (size_t)r * p.k + first + o;
             const uint32_t c = first + o;
             float i0 = 1.0f, i1 = 1.0f;
@@ -687,7 +689,9 @@ __global__ void __launch_bounds__(kGemvWarps * 32, 1) gemv_kernel(const __grid_c
     L.digit_weight = (L.t & 1u) ? pack2f(65536.0f, 16777216.0f) : pack2f(1.0f, 256.0f);
     const uint8_t* my_frag = frags + ((L.g & (NCP - 1u)) * 4u + L.t) * 8u;
     const uint32_t sums_stride = padded / 16u, scales_stride = padded / 256u;
-    const uint32_t my_row[2] = {min(L.t >> 1, (uint32_t)ROWS - 1u), min(2u + (L.t >> 1), (uint32_t)ROWS - 1u)};
+    uint32_t my_row[NT];      // the activation row whose digits this lane's C registers of n-tile nt hold
+#pragma unroll
+    for (int nt = 0; nt < NT; ++nt) my_row[nt] = min(2u * nt + (L.t >> 1), (uint32_t)ROWS - 1u);
     const uint32_t quad_base = lane & ~3u;
     const uint32_t bad = bad_rows;
 
@@ -755,7 +759,7 @@ __global__ void __launch_bounds__(kGemvWarps * 32, 1) gemv_kernel(const __grid_c
         if (p.chunks == 1u) {
 #pragma unroll
             for (int r = 0; r < ROWS; ++r)
-                if (L.t == (uint32_t)(r & 3)) {
+                if (L.t == (uint32_t)(r & 3) && (uint32_t)r < p.active_rows) {
                     if (columnA < mat.n) mat.out[(size_t)r * mat.n + columnA] = totalA[r];
                     if (columnB < mat.n) mat.out[(size_t)r * mat.n + columnB] = totalB[r];
                 }
@@ -784,7 +788,7 @@ __global__ void __launch_bounds__(kGemvWarps * 32, 1) gemv_kernel(const __grid_c
                 for (uint32_t c = 0; c < p.chunks; ++c)
                     sum += __ldcg(&p.partial[((size_t)c * ROWS + r) * width + (size_t)pair * 16u + col]);
                 const uint32_t out_column = local_pair * 16u + col;
-                if (out_column < mat.n) mat.out[(size_t)r * mat.n + out_column] = sum;
+                if (out_column < mat.n && r < p.active_rows) mat.out[(size_t)r * mat.n + out_column] = sum;
             }
             if (lane == 0) p.counters[pair] = 0u;
         }

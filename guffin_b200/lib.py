@@ -14,7 +14,7 @@ LIB_PATH = os.path.join(HERE, "libguffin_b200.so")
 HEADER_PATH = os.path.join(HERE, "..", "include", "guffin_b200.h")
 
 Q8_0, Q4_K, Q6_K = 8, 12, 14
-MAX_ROWS = 4
+MAX_ROWS = 8
 
 GF_OK, GF_ERR_INVALID, GF_ERR_STATE, GF_ERR_CUDA, GF_ERR_UNAVAILABLE, GF_ERR_NUMERIC, GF_ERR_TIMEOUT = 0, -1, -2, -3, -4, -5, -6
 

@@ -87,7 +87,7 @@ GF_API int gf_dequantize(int dtype, const void* native_dev, uint64_t block_count
  * result is identical whether computed alone or beside other rows.
  * `workspace_dev` holds split-K partial sums (gf_matmul_workspace_bytes); it may be NULL when
  * that size is 0. ---- */
-#define GF_MAX_ROWS 4
+#define GF_MAX_ROWS 8
 GF_API size_t gf_matmul_workspace_bytes(int dtype, uint32_t rows, uint64_t k, uint64_t n);
 GF_API int gf_matmul(int dtype, const void* packed_dev, const float* x_dev, float* y_dev,
                      uint32_t rows, uint64_t k, uint64_t n, void* workspace_dev, void* stream);

@@ -65,7 +65,7 @@ SHAPES = {
 
 
 @pytest.mark.parametrize("dtype", DTYPES)
-@pytest.mark.parametrize("rows", [1, 2, 3, 4])
+@pytest.mark.parametrize("rows", [1, 2, 3, 4, 6, 8])
 def test_matmul_matches_oracle(gf, oracle, dtype, rows):
     for k, n in SHAPES[dtype]:
         rng = np.random.default_rng(k * 31 + n * 7 + rows)
@@ -91,11 +91,12 @@ def test_rows_are_count_invariant(gf, dtype, k, n):
     rng = np.random.default_rng(99)
     native = syn.make_weight(rng, dtype, k, n)
     weight = gf.PackedWeight(dtype, k, n, native)
-    x = rng.standard_normal((4, k)).astype(np.float32)
+    x = rng.standard_normal((8, k)).astype(np.float32)
     together = gf.matmul(weight, x)
-    for rows in (1, 2, 3):
+    for rows in (1, 2, 3, 4, 5, 7):
         np.testing.assert_array_equal(gf.matmul(weight, x[:rows]), together[:rows])
     np.testing.assert_array_equal(gf.matmul(weight, x[2:3]), together[2:3])
+    np.testing.assert_array_equal(gf.matmul(weight, x[6:8]), together[6:8])
     np.testing.assert_array_equal(gf.matmul_host(weight, x[:2]), together[:2])
 
 

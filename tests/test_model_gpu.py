@@ -292,6 +292,32 @@ def test_decode_verify_and_rollback_match_oracle(gf, gm, oracle, geometry, seed)
     np.testing.assert_array_equal(model.logits(0), two)
 
 
+@pytest.mark.parametrize("geometry,seed", [("tiny-target", 41), ("tiny-draft", 42)])
+def test_eight_row_prefill_equals_two_row_prefill(gf, gm, oracle, geometry, seed):
+    """Prompt ingestion in passes of eight rows (the batched prefill path) leaves the same cache and
+    gives the same next-token logits as passes of two rows, and both agree with the oracle
+    (run_gemma3_resident_prefill chunks rows the same way, gemma_target_runtime.cpp:420-455)."""
+    wide, config, weights = _gpu_model(gm, geometry, seed, context=96, rows=8)
+    narrow, _, _ = _gpu_model(gm, geometry, seed, context=96, rows=2)
+    ref = OracleModel(oracle, config, weights, context=96)
+    tokens = np.random.default_rng(seed).integers(0, config["vocab"], 45).astype(np.uint32)
+    wide.prefill(tokens[:43])                     # five passes of eight and one of three
+    narrow.prefill(tokens[:43])
+    for t in tokens[:43]:
+        last = ref.append(t)
+    assert wide.position == narrow.position == 43
+    assert rel_l2(wide.logits(2), last) < 2e-4                 # 43 = 5 * 8 + 3: the last row of the last pass
+    assert rel_l2(wide.logits(2), narrow.logits(0)) < 1e-5
+    # Decoding on from both caches gives the same floats up to summation order in attention.
+    wide.forward(tokens[43:45], logits=True)
+    narrow.forward(tokens[43:45], logits=True)
+    want0 = ref.append(tokens[43]); want1 = ref.append(tokens[44])
+    for row, want in ((0, want0), (1, want1)):
+        assert rel_l2(wide.logits(row), want) < 2e-4
+        assert rel_l2(wide.logits(row), narrow.logits(row)) < 1e-5
+    assert wide.status() == 0 and narrow.status() == 0
+
+
 def test_graph_replay_equals_direct_launches(gf, gm):
     model, config, _ = _gpu_model(gm, "tiny-target", 31, context=64)
     direct, _, _ = _gpu_model(gm, "tiny-target", 31, context=64)
