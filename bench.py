@@ -33,6 +33,7 @@ sys.path.insert(0, ROOT)
 CONTEXT = 2048
 TARGET, DRAFT = "gemma3-12b", "gemma3-270m"
 ACCEPT_P = 0.7
+PREFILL_ROWS = 8          # rows per prompt-ingestion pass (verification passes stay two rows wide)
 # dram__bytes_read.sum + dram__bytes_write.sum over the weight bytes of one captured GEMV launch
 # (profiles/gemv_kernel_q4k_k3840_n65536_rows2.md).
 TRAFFIC_PER_ALGORITHMIC_BYTE = 148.46 / 141.56
@@ -137,8 +138,8 @@ def run_ours(args) -> dict:
 
     t0 = time.time()
     tc, dc = syn.model_config(TARGET), syn.model_config(DRAFT)
-    target = gm.Model(tc, syn.iter_model_weights(TARGET, SEEDS["target"]), context, 2)
-    draft = gm.Model(dc, syn.iter_model_weights(DRAFT, SEEDS["draft"]), context, 2)
+    target = gm.Model(tc, syn.iter_model_weights(TARGET, SEEDS["target"]), context, PREFILL_ROWS)
+    draft = gm.Model(dc, syn.iter_model_weights(DRAFT, SEEDS["draft"]), context, PREFILL_ROWS)
     load_s = time.time() - t0
     options = ge.H1Options(ge.sampler_options(0.7, 40, 0.95, 0.05, 1.0, seed=SEEDS["sampler"] + rank), 1, 1, ACCEPT_P,
                            SEEDS["schedule"] + rank, 0)
