@@ -141,6 +141,17 @@ int gemv_launch(const GemvLaunch& launch, uint32_t* counters, float* partial, si
     p.residual_out = launch.residual_out;
     p.eps = launch.eps;
     p.error_flag = error_flag;
+    if (launch.heads.rotation) {
+        const GemvLaunch::Heads& h = launch.heads;
+        if (launch.count != 3 || !h.q_out || !h.private_k || !h.private_v || !h.base_position || !h.status || !h.head_counters
+            || launch.matrices[0].n % 256u || launch.matrices[1].n % 256u || launch.matrices[2].n != launch.matrices[1].n)
+            return fail(GF_ERR_INVALID, "gf_matmul: the head epilogue needs Q, K and V matrices of 256-column heads and its buffers");
+        p.heads.q_norm = h.q_norm; p.heads.k_norm = h.k_norm; p.heads.q_out = h.q_out;
+        p.heads.private_k = h.private_k; p.heads.private_v = h.private_v; p.heads.rotation = h.rotation;
+        p.heads.base_position = h.base_position; p.heads.status = h.status; p.heads.head_counters = h.head_counters;
+        p.heads.enabled = 1u; p.heads.table_rows = h.table_rows; p.heads.kv_f16 = h.kv_f16 ? 1u : 0u;
+        p.heads.eps = launch.eps;
+    }
     if (plan.chunks > 1) {
         const size_t need = (size_t)plan.chunks * instance_rows(launch.rows) * plan.total_pairs * 16u * sizeof(float);
         if (!counters || !partial || partial_bytes < need) return fail(GF_ERR_INVALID, "gf_matmul: this shape needs a %zu-byte split-K workspace", need);

@@ -58,6 +58,20 @@ struct GemvParams {
     const float *in, *residual, *gamma0, *gamma1;
     float* residual_out;
     float eps;
+    // Optional head epilogue of a fused Q/K/V launch (matrix 0 = Q, 1 = K, 2 = V, 256 columns per
+    // head): the warp that completes a head's last column pair applies the per-head RMSNorm and
+    // the NEOX rotation and writes the rotated query (f32) or the private K/V row of the cache.
+    struct HeadEpilogue {
+        const float *q_norm, *k_norm;        // [256] or null
+        float* q_out;                        // [rows][heads * 256]
+        void *private_k, *private_v;         // [rows][kv_heads * 256] in the cache type
+        const float2* rotation;              // [table_rows][128] (cos, sin) of position * scale / base^(2i/256)
+        const uint32_t* base_position;
+        uint32_t* status;
+        uint32_t* head_counters;             // [heads + 2 * kv_heads], zero between launches
+        uint32_t enabled, table_rows, kv_f16;
+        float eps;
+    } heads;
     float* partial;            // [chunks][rows][total_pairs * 16] when chunks > 1
     uint32_t* counters;        // [total_pairs] arrival counts, zero between launches
     int* error_flag;           // set to 1 when a bounded wait gives up
@@ -612,6 +626,97 @@ __device__ __forceinline__ void stage_activations(const GemvParams& p, uint32_t 
     }
 }
 
+// Status bit of a non-finite binary16 K/V value (the reference's validation word, metal_kernels.mm:2484).
+constexpr uint32_t kGemvStatusKvNonFinite = 8u;
+
+// One finished head (256 output columns starting at `column0` of matrix `which`: 0 = Q, 1 = K,
+// 2 = V) of every active row: RMSNorm with the head's weights, NEOX rotation by the tabulated
+// (cos, sin) of the row's position, and the store the block schedule wants -- rotated queries in
+// f32, K and V rounded to the cache type in the private rows.  Lane l owns elements 4l..4l+3 and
+// 128+4l..128+4l+3, i.e. four rotation pairs.  The caller has made the head's values visible
+// (fence after the last arrival).
+template <int ROWS>
+__device__ __forceinline__ void finish_head(const GemvParams& p, const GemvMatrix& mat, uint32_t which, uint32_t head, uint32_t lane) {
+    const GemvParams::HeadEpilogue& e = p.heads;
+    const uint32_t base = *e.base_position;
+    const float* gamma = which == 0u ? e.q_norm : which == 1u ? e.k_norm : nullptr;
+    for (uint32_t r = 0; r < p.active_rows && r < (uint32_t)ROWS; ++r) {
+        const float* src = mat.out + (size_t)r * mat.n + head * 256u;
+        const float4 a = __ldcg(reinterpret_cast<const float4*>(src + 4u * lane));
+        const float4 b = __ldcg(reinterpret_cast<const float4*>(src + 128u + 4u * lane));
+        float first[4] = {a.x, a.y, a.z, a.w}, second[4] = {b.x, b.y, b.z, b.w};
+        if (which != 2u) {
+            if (gamma) {
+                float sum = 0.0f;
+#pragma unroll
+                for (int j = 0; j < 4; ++j) sum = fmaf(first[j], first[j], fmaf(second[j], second[j], sum));
+                sum = warp_sum(sum);
+                const float inv = __fdiv_rn(1.0f, __fsqrt_rn(__fadd_rn(__fdiv_rn(sum, 256.0f), e.eps)));
+                const float4 ga = *reinterpret_cast<const float4*>(gamma + 4u * lane);
+                const float4 gb = *reinterpret_cast<const float4*>(gamma + 128u + 4u * lane);
+                const float g0[4] = {ga.x, ga.y, ga.z, ga.w}, g1[4] = {gb.x, gb.y, gb.z, gb.w};
+#pragma unroll
+                for (int j = 0; j < 4; ++j) {
+                    first[j] = __fmul_rn(__fmul_rn(first[j], inv), g0[j]);
+                    second[j] = __fmul_rn(__fmul_rn(second[j], inv), g1[j]);
+                }
+            }
+            const float4* rot = reinterpret_cast<const float4*>(e.rotation + (size_t)(base + r) * 128u + 4u * lane);
+            const float4 r01 = rot[0], r23 = rot[1];            // (cos, sin) of pairs 4l, 4l+1 and 4l+2, 4l+3
+            const float cs[4] = {r01.x, r01.z, r23.x, r23.z}, sn[4] = {r01.y, r01.w, r23.y, r23.w};
+#pragma unroll
+            for (int j = 0; j < 4; ++j) {
+                const float r0 = __fsub_rn(__fmul_rn(first[j], cs[j]), __fmul_rn(second[j], sn[j]));
+                const float r1 = __fadd_rn(__fmul_rn(first[j], sn[j]), __fmul_rn(second[j], cs[j]));
+                first[j] = r0; second[j] = r1;
+            }
+        }
+        if (which == 0u) {
+            float* dst = e.q_out + (size_t)r * mat.n + head * 256u;
+            *reinterpret_cast<float4*>(dst + 4u * lane) = make_float4(first[0], first[1], first[2], first[3]);
+            *reinterpret_cast<float4*>(dst + 128u + 4u * lane) = make_float4(second[0], second[1], second[2], second[3]);
+            continue;
+        }
+        const size_t o = (size_t)r * mat.n + head * 256u;
+        if (e.kv_f16) {
+            __half* dst = static_cast<__half*>(which == 1u ? e.private_k : e.private_v) + o;
+            __half2 lo[2], hi[2];
+            bool finite = true;
+#pragma unroll
+            for (int j = 0; j < 2; ++j) {
+                lo[j] = __halves2half2(__float2half_rn(first[2 * j]), __float2half_rn(first[2 * j + 1]));
+                hi[j] = __halves2half2(__float2half_rn(second[2 * j]), __float2half_rn(second[2 * j + 1]));
+                const float2 fl = __half22float2(lo[j]), fh = __half22float2(hi[j]);
+                finite &= isfinite(fl.x) && isfinite(fl.y) && isfinite(fh.x) && isfinite(fh.y);
+            }
+            *reinterpret_cast<uint2*>(dst + 4u * lane) = make_uint2(*reinterpret_cast<uint32_t*>(&lo[0]), *reinterpret_cast<uint32_t*>(&lo[1]));
+            *reinterpret_cast<uint2*>(dst + 128u + 4u * lane) = make_uint2(*reinterpret_cast<uint32_t*>(&hi[0]), *reinterpret_cast<uint32_t*>(&hi[1]));
+            if (!finite) atomicOr(e.status, kGemvStatusKvNonFinite);
+        } else {
+            float* dst = static_cast<float*>(which == 1u ? e.private_k : e.private_v) + o;
+            *reinterpret_cast<float4*>(dst + 4u * lane) = make_float4(first[0], first[1], first[2], first[3]);
+            *reinterpret_cast<float4*>(dst + 128u + 4u * lane) = make_float4(second[0], second[1], second[2], second[3]);
+        }
+    }
+}
+
+// Counts a finished column pair of a fused Q/K/V launch; the warp that completes a head (16 pairs)
+// finishes it.  The pair's outputs must already be written by this warp.
+template <int ROWS>
+__device__ __forceinline__ void head_pair_done(const GemvParams& p, const GemvMatrix& mat, uint32_t which, uint32_t local_pair, uint32_t lane) {
+    const uint32_t head = local_pair >> 4;
+    const uint32_t slot = (which == 0u ? 0u : which == 1u ? p.m[0].n / 256u : p.m[0].n / 256u + p.m[1].n / 256u) + head;
+    __threadfence();
+    __syncwarp();
+    uint32_t arrived = 0;
+    if (lane == 0) arrived = atomicAdd(&p.heads.head_counters[slot], 1u);
+    arrived = __shfl_sync(0xffffffffu, arrived, 0);
+    if (arrived != 15u) return;
+    __threadfence();
+    finish_head<ROWS>(p, mat, which, head, lane);
+    if (lane == 0) p.heads.head_counters[slot] = 0u;
+}
+
 template <int ROWS>
 __global__ void __launch_bounds__(kGemvWarps * 32, 1) gemv_kernel(const __grid_constant__ GemvParams p) {
     constexpr int NT = (4 * ROWS + 7) / 8;
@@ -763,6 +868,7 @@ __global__ void __launch_bounds__(kGemvWarps * 32, 1) gemv_kernel(const __grid_c
                     if (columnA < mat.n) mat.out[(size_t)r * mat.n + columnA] = totalA[r];
                     if (columnB < mat.n) mat.out[(size_t)r * mat.n + columnB] = totalB[r];
                 }
+            if (p.heads.enabled) head_pair_done<ROWS>(p, mat, matrix_of(pair), local_pair, lane);
             continue;
         }
         // Split K: park this chunk's partial sums; the warp that arrives last for the pair adds
@@ -791,6 +897,7 @@ __global__ void __launch_bounds__(kGemvWarps * 32, 1) gemv_kernel(const __grid_c
                 if (out_column < mat.n && r < p.active_rows) mat.out[(size_t)r * mat.n + out_column] = sum;
             }
             if (lane == 0) p.counters[pair] = 0u;
+            if (p.heads.enabled) head_pair_done<ROWS>(p, mat, matrix_of(pair), local_pair, lane);
         }
     }
     if (failed) {
@@ -813,6 +920,18 @@ struct GemvLaunch {
     const float *in = nullptr, *residual = nullptr, *gamma0 = nullptr, *gamma1 = nullptr;
     float* residual_out = nullptr;
     float eps = 1e-6f;
+    // Head epilogue of a fused Q/K/V launch (see GemvParams::HeadEpilogue); off when rotation is null.
+    struct Heads {
+        const float *q_norm = nullptr, *k_norm = nullptr;
+        float* q_out = nullptr;
+        void *private_k = nullptr, *private_v = nullptr;
+        const float2* rotation = nullptr;
+        const uint32_t* base_position = nullptr;
+        uint32_t* status = nullptr;
+        uint32_t* head_counters = nullptr;
+        uint32_t table_rows = 0;
+        int kv_f16 = 0;
+    } heads;
 };
 struct GemvPlan { uint32_t units, unit_elems, total_pairs, chunks, chunk_units, grid, smem, slot_bytes; };
 

@@ -167,6 +167,31 @@ int Model::finalize() {
             GF_CUDA(cudaStreamSynchronize(stream_));
         }
         for (uint32_t l = 0; l < c.layers; ++l) caches_[l].rope_divisors = tables[layer_is_local(l) ? 0 : 1];
+        // (cos, sin) of every position the plan can reach, formed on the host exactly as the
+        // reference forms them: double angle = position * scale / base^(2i/d), then rounded to f32
+        // (ops/rope.cpp:109-117).  256-wide heads only (the fused Q/K/V epilogue's layout).
+        if (c.head_dim == 256u) {
+            float2* rotations[2] = {nullptr, nullptr};
+            const float scales[2] = {c.rope_scale_local, c.rope_scale_global};
+            const uint32_t table_rows = c.context + GF_MAX_ROWS;
+            for (int kind = 0; kind < 2; ++kind) {
+                if (kind == 1 && bases[1] == bases[0] && scales[1] == scales[0]) { rotations[1] = rotations[0]; break; }
+                std::vector<float2> host((size_t)table_rows * 128u);
+                for (uint32_t i = 0; i < 128u; ++i) {
+                    const double divisor = std::pow((double)bases[kind], (double)(2u * i) / 256.0);
+                    for (uint32_t position = 0; position < table_rows; ++position) {
+                        const double angle = (double)position * (double)scales[kind] / divisor;
+                        host[(size_t)position * 128u + i] = make_float2((float)std::cos(angle), (float)std::sin(angle));
+                    }
+                }
+                GF_TRY(device_alloc(allocations_, &rotations[kind], host.size()));
+                GF_CUDA(cudaMemcpyAsync(rotations[kind], host.data(), host.size() * sizeof(float2), cudaMemcpyHostToDevice, stream_));
+                GF_CUDA(cudaStreamSynchronize(stream_));
+            }
+            for (uint32_t l = 0; l < c.layers; ++l) caches_[l].rope_rotation = rotations[layer_is_local(l) ? 0 : 1];
+            GF_TRY(device_alloc(allocations_, &head_counters_, c.heads + 2u * c.kv_heads));
+            GF_CUDA(cudaMemsetAsync(head_counters_, 0, (c.heads + 2u * c.kv_heads) * sizeof(uint32_t), stream_));
+        }
     }
     {
         std::vector<KvPublishLayer> table(c.layers);
@@ -298,11 +323,21 @@ int Model::encode_blocks(uint32_t rows, uint32_t flags) {
             qkv.residual_out = x; qkv.gamma1 = w.attn_norm;
         }
         GemvLaunch o = o_weights(l);
+        const bool fused_heads = cache.rope_rotation != nullptr;
+        if (fused_heads) {      // per-head norm, RoPE and the private K/V store ride on the Q/K/V launch
+            qkv.heads.q_norm = c.uses_qk_norm ? w.q_norm : nullptr; qkv.heads.k_norm = c.uses_qk_norm ? w.k_norm : nullptr;
+            qkv.heads.q_out = query_; qkv.heads.private_k = cache.private_k; qkv.heads.private_v = cache.private_v;
+            qkv.heads.rotation = cache.rope_rotation; qkv.heads.base_position = state_dev_; qkv.heads.status = status_dev_;
+            qkv.heads.head_counters = head_counters_; qkv.heads.table_rows = c.context + GF_MAX_ROWS; qkv.heads.kv_f16 = c.kv_f16;
+        }
         GF_TRY(run_gemv(qkv, rows));
-        RopeStoreParams rp{raw_q_, raw_k_, raw_v_, c.uses_qk_norm ? w.q_norm : nullptr, c.uses_qk_norm ? w.k_norm : nullptr,
-                           query_, cache.private_k, cache.private_v, state_dev_, status_dev_, cache.rope_divisors, rows, c.heads, c.kv_heads,
-                           c.head_dim, c.rms_eps, cache.rope_base, cache.rope_scale, c.kv_f16};
-        GF_TRY(launch_rope_store(rp, stream_, true));
+        if (!fused_heads) {
+            RopeStoreParams rp{raw_q_, raw_k_, raw_v_, c.uses_qk_norm ? w.q_norm : nullptr, c.uses_qk_norm ? w.k_norm : nullptr,
+                               query_, cache.private_k, cache.private_v, state_dev_, status_dev_, cache.rope_divisors, rows, c.heads, c.kv_heads,
+                               c.head_dim, c.rms_eps, cache.rope_base, cache.rope_scale, c.kv_f16};
+            GF_TRY(launch_rope_store(rp, stream_, true));
+            launches_ += 1;
+        }
         AttentionParams ap;
         ap.q = query_; ap.ring_k = cache.ring_k; ap.ring_v = cache.ring_v; ap.private_k = cache.private_k;
         ap.private_v = cache.private_v; ap.out = attention_out_;
@@ -313,7 +348,7 @@ int Model::encode_blocks(uint32_t rows, uint32_t flags) {
         ap.ring_mask = cache.ring_rows - 1u; ap.window = cache.window; ap.scale = c.attention_scale;
         ap.softcap = c.attn_softcap; ap.kv_f16 = c.kv_f16;
         GF_TRY(launch_attention(ap, stream_, true));
-        launches_ += 2;
+        launches_ += 1;
         o.in = attention_out_;
         GemvLaunch gu = gate_up_weights(l);
         GF_TRY(run_gemv(o, rows));

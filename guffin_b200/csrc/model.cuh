@@ -32,6 +32,7 @@ struct LayerCache {
     uint32_t window = 0;                              // 0 = global layer
     float rope_base = 0.0f, rope_scale = 1.0f;
     const double* rope_divisors = nullptr;            // [head_dim / 2] rope_base^(2i / head_dim)
+    const float2* rope_rotation = nullptr;            // [context + GF_MAX_ROWS][head_dim / 2] (cos, sin) per position
 };
 
 enum ForwardFlags : uint32_t {
@@ -106,6 +107,7 @@ private:
     size_t matmul_ws_bytes_ = 0;
     uint32_t* matmul_counters_ = nullptr;
     KvPublishLayer* publish_layers_ = nullptr;
+    uint32_t* head_counters_ = nullptr;
     void *requests_dev_ = nullptr, *results_dev_ = nullptr;
     uint32_t *tokens_dev_ = nullptr, *state_dev_ = nullptr, *status_dev_ = nullptr;
     int* error_flag_ = nullptr;
