@@ -317,7 +317,11 @@ def main():
                 "sample": f"2 H1 cycles (1 drafter row + 2 target rows each) after 1 warm-up at context <= 8 tokens, oracle port "
                           f"of the reference's scalar CPU GEMV split over {threads} threads, {1 + ACCEPT_P:.1f} tokens per cycle"}
     if result:
-        print(json.dumps(result))
+        print(json.dumps(result), flush=True)
+    if "torch.distributed" in sys.modules:
+        import torch.distributed as dist
+        if dist.is_available() and dist.is_initialized():
+            dist.destroy_process_group()
 
 
 if __name__ == "__main__":
