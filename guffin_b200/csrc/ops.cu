@@ -351,18 +351,39 @@ __global__ void __launch_bounds__(kAttentionWarps * 32) attention_kernel(Attenti
     __syncthreads();
     if (arrival != win.parts - 1u) return;
     __threadfence();
+    // Weights of the partitions first (one thread per (head, partition), all loads in flight at
+    // once), then every thread sums its outputs over the partitions with the loads unrolled.
+    float* weight = &warp_acc[0][0][0];                 // [G][kMaxAttentionPartitions] factor, then [G] total
+    for (uint32_t idx = threadIdx.x; idx < (uint32_t)G * 32u; idx += blockDim.x) {
+        const uint32_t g = idx >> 5, lane_part = idx & 31u;
+        const size_t slot = ((size_t)row * p.heads + kvh * G + g) * kMaxAttentionPartitions + lane_part;
+        const bool live = lane_part < win.parts;
+        const float pm = live ? __ldcg(&p.partial_ml[slot * 2u]) : -INFINITY;
+        const float pl = live ? __ldcg(&p.partial_ml[slot * 2u + 1u]) : 0.0f;
+        float mm = pm;
+#pragma unroll
+        for (int offset = 16; offset > 0; offset >>= 1) mm = fmaxf(mm, __shfl_xor_sync(0xffffffffu, mm, offset));
+        const float f = live ? expf(pm - mm) : 0.0f;
+        weight[g * kMaxAttentionPartitions + lane_part] = f;
+        // Sum of l_i * f_i in partition order: a shuffle scan would reorder it, so lane 0 adds.
+        float ll = 0.0f;
+        for (uint32_t i = 0; i < win.parts; ++i)
+            ll = fmaf(__shfl_sync(0xffffffffu, pl, i), __shfl_sync(0xffffffffu, f, i), ll);
+        if (lane_part == 0u) weight[G * kMaxAttentionPartitions + g] = ll;
+    }
+    __syncthreads();
     for (uint32_t idx = threadIdx.x; idx < (uint32_t)G * 256u; idx += blockDim.x) {
-        const uint32_t head = kvh * G + idx / 256u, d = idx % 256u;
+        const uint32_t g = idx / 256u, d = idx % 256u, head = kvh * G + g;
         const size_t base = ((size_t)row * p.heads + head) * kMaxAttentionPartitions;
-        float mm = -INFINITY;
-        for (uint32_t i = 0; i < win.parts; ++i) mm = fmaxf(mm, __ldcg(&p.partial_ml[(base + i) * 2u]));
-        float a = 0.0f, ll = 0.0f;
-        for (uint32_t i = 0; i < win.parts; ++i) {
-            const float f = expf(__ldcg(&p.partial_ml[(base + i) * 2u]) - mm);
-            a = fmaf(__ldcg(&p.partial_out[(base + i) * 256u + d]), f, a);
-            ll = fmaf(__ldcg(&p.partial_ml[(base + i) * 2u + 1u]), f, ll);
+        float a = 0.0f;
+        for (uint32_t i0 = 0; i0 < win.parts; i0 += 8u) {
+            float v[8];
+#pragma unroll
+            for (int j = 0; j < 8; ++j) v[j] = i0 + j < win.parts ? __ldcg(&p.partial_out[(base + i0 + j) * 256u + d]) : 0.0f;
+#pragma unroll
+            for (int j = 0; j < 8; ++j) a = fmaf(v[j], weight[g * kMaxAttentionPartitions + ((i0 + j) & 31u)], a);
         }
-        p.out[((size_t)row * p.heads + head) * 256u + d] = a / ll;
+        p.out[((size_t)row * p.heads + head) * 256u + d] = a / weight[G * kMaxAttentionPartitions + g];
     }
     if (threadIdx.x == 0) p.counters[row * p.kv_heads + kvh] = 0u;
 }
