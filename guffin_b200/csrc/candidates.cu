@@ -56,6 +56,25 @@ __device__ __forceinline__ void bitonic_sort(uint64_t* keys) {
     __syncthreads();
 }
 
+// Ascending bitonic sort of the first n keys (n a power of two <= kTile) by the first n / 2 threads.
+__device__ __forceinline__ void bitonic_sort_prefix(uint64_t* keys, uint32_t n) {
+    for (uint32_t width = 2; width <= n; width <<= 1) {
+        for (uint32_t stride = width >> 1; stride > 0; stride >>= 1) {
+            __syncthreads();
+            const uint32_t t = threadIdx.x;
+            if (t < n / 2u) {
+                const uint32_t lo = 2u * t - (t & (stride - 1u));
+                const uint32_t hi = lo + stride;
+                const bool ascending = (lo & width) == 0u;
+                const uint64_t a = keys[lo], b = keys[hi];
+                if ((a > b) == ascending) { keys[lo] = b; keys[hi] = a; }
+            }
+        }
+    }
+    __syncthreads();
+}
+__device__ __forceinline__ uint32_t next_pow2_u32(uint32_t v) { return v <= 1u ? 1u : 1u << (32 - __clz(v - 1u)); }
+
 __global__ void __launch_bounds__(1024) candidate_tile_kernel(const float* __restrict__ logits, uint32_t vocab,
                                                               float softcap, const SelectionRequest* __restrict__ requests,
                                                               uint64_t* __restrict__ runs, CandidateResult* results) {
@@ -95,17 +114,49 @@ __global__ void __launch_bounds__(1024) candidate_merge_kernel(const float* __re
         if (threadIdx.x == 0) atomicOr(&results[row].status, kStatusBadRequest);
     }
     const uint32_t total = tiles * retain;            // run entries, flattened tile-major
-    const uint32_t fresh = kTile - retain;            // new entries admitted per round
-    for (uint32_t i = threadIdx.x; i < retain; i += blockDim.x) keys[i] = kPadKey;
-    for (uint32_t first = 0; first < total || first == 0; first += fresh) {
+    __shared__ uint32_t survivors;
+    bool merged = false;
+    if (retain > 0u && tiles >= retain && tiles <= kTile) {
+        // The `retain`-th best of the tiles' best keys bounds the answer from below: at least
+        // `retain` keys (those heads) are that good, so nothing worse can be in the result.
+        // Usually only about two `retain` run entries pass, and one small sort finishes the job.
+        const uint32_t heads = next_pow2_u32(tiles);
+        for (uint32_t i = threadIdx.x; i < heads; i += blockDim.x)
+            keys[i] = i < tiles ? runs[((size_t)row * tiles + i) * kMaxRetain] : kPadKey;
+        if (threadIdx.x == 0) survivors = 0u;
+        bitonic_sort_prefix(keys, heads);
+        const uint64_t bound = keys[retain - 1u];
         __syncthreads();
-        for (uint32_t i = threadIdx.x; i < fresh; i += blockDim.x) {
-            const uint32_t flat = first + i;
-            uint64_t key = kPadKey;
-            if (flat < total) key = runs[((size_t)row * tiles + flat / retain) * kMaxRetain + flat % retain];
-            keys[retain + i] = key;
+        for (uint32_t flat = threadIdx.x; flat < total; flat += blockDim.x) {
+            const uint64_t key = runs[((size_t)row * tiles + flat / retain) * kMaxRetain + flat % retain];
+            if (key <= bound) {
+                const uint32_t slot = atomicAdd(&survivors, 1u);
+                if (slot < kTile) keys[slot] = key;
+            }
         }
-        bitonic_sort(keys);
+        __syncthreads();
+        const uint32_t count = survivors;
+        if (count <= kTile) {
+            const uint32_t padded = next_pow2_u32(max(count, retain));
+            for (uint32_t i = count + threadIdx.x; i < padded; i += blockDim.x) keys[i] = kPadKey;
+            bitonic_sort_prefix(keys, padded);
+            merged = true;
+        }
+        __syncthreads();
+    }
+    if (!merged) {
+        const uint32_t fresh = kTile - retain;            // new entries admitted per round
+        for (uint32_t i = threadIdx.x; i < retain; i += blockDim.x) keys[i] = kPadKey;
+        for (uint32_t first = 0; first < total || first == 0; first += fresh) {
+            __syncthreads();
+            for (uint32_t i = threadIdx.x; i < fresh; i += blockDim.x) {
+                const uint32_t flat = first + i;
+                uint64_t key = kPadKey;
+                if (flat < total) key = runs[((size_t)row * tiles + flat / retain) * kMaxRetain + flat % retain];
+                keys[retain + i] = key;
+            }
+            bitonic_sort(keys);
+        }
     }
     CandidateResult& result = results[row];
     for (uint32_t i = threadIdx.x; i < retain; i += blockDim.x) {
