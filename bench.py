@@ -170,6 +170,7 @@ def run_ours(args) -> dict:
         end.synchronize()
         wall = time.perf_counter() - wall0
         device_ms = start.elapsed_ms(end)
+        launches = target.kernel_launches() + draft.kernel_launches() - launches_before    # of the device-timed loop only
         # Same loop once more for the end-to-end figure: host wall clock around the public call,
         # which uploads the root token and selection requests and reads back candidates and the
         # drafter's receipt every cycle.
@@ -191,7 +192,6 @@ def run_ours(args) -> dict:
     barrier()
     stats = engine.stats()
     cycles = stats.cycles + stats.ordinary_steps - stats_before.cycles - stats_before.ordinary_steps
-    launches = target.kernel_launches() + draft.kernel_launches() - launches_before
     status = target.status() | draft.status()
 
     produced, produced_e2e, elapsed_ms, e2e_s = aggregate_streams(
