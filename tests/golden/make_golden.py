@@ -1,7 +1,8 @@
 #!/usr/bin/env python3
 """Generates the committed golden fixtures from the REFERENCE's own code.
 
-Run in a checkout where the reference tree is available (default /root/reference) and
+Run where the reference tree is available (its location comes from the GF_REFERENCE environment
+variable) and
 oracle/_ref has been built (`make -C oracle ref`):
 
     python tests/golden/make_golden.py
