@@ -30,8 +30,11 @@ int gemv_plan(const GemvLaunch& launch, GemvPlan& plan) {
         plan.unit_elems = unit;
         if (launch.matrices[i].n == 0 || launch.matrices[i].n > (1ull << 28)) return fail(GF_ERR_INVALID, "gf_matmul: N must be positive");
         plan.total_pairs += (uint32_t)((launch.matrices[i].n + 15u) / 16u);
-        plan.slot_bytes = std::max(plan.slot_bytes, pair_row_bytes(dtype));
+        plan.slot_bytes = std::max(plan.slot_bytes, pair_row_bytes(dtype));     // one pair row; scaled below
     }
+    // Two pair rows per slot (one copy, one wait for both) unless a Q6_K row makes that too large.
+    plan.slot_units = plan.slot_bytes <= 2304u ? 2u : 1u;
+    plan.slot_bytes *= plan.slot_units;
     if (launch.k == 0 || launch.k % plan.unit_elems != 0 || launch.k > (1ull << 24))
         return fail(GF_ERR_INVALID, "gf_matmul: K=%llu must be a positive multiple of %u", (unsigned long long)launch.k, plan.unit_elems);
     plan.units = (uint32_t)(launch.k / plan.unit_elems);
@@ -136,6 +139,7 @@ int gemv_launch(const GemvLaunch& launch, uint32_t* counters, float* partial, si
     p.chunks = plan.chunks;
     p.chunk_units = plan.chunk_units;
     p.slot_bytes = plan.slot_bytes;
+    p.slot_units = plan.slot_units;
     p.prologue = launch.prologue;
     p.in = launch.in; p.residual = launch.residual; p.gamma0 = launch.gamma0; p.gamma1 = launch.gamma1;
     p.residual_out = launch.residual_out;

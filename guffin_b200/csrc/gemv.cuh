@@ -29,7 +29,7 @@
 namespace gf {
 
 constexpr int kGemvWarps = 16;       // warps per CTA; one CTA per SM
-constexpr int kGemvSlots = 3;        // ring depth per warp, one pair row per slot
+constexpr int kGemvSlots = 2;        // ring depth per warp; a slot holds `slot_units` consecutive pair rows of an item
 constexpr uint32_t kGemvSmemLimit = 225u * 1024u;    // dynamic part; the static arrays take the rest of the 227 KB
 constexpr int kGemvMaxMatrices = 3;
 
@@ -53,7 +53,7 @@ struct GemvParams {
     uint32_t k, units, unit_elems;
     uint32_t active_rows;                 // rows that exist; the kernel instance may be compiled for more
     uint32_t chunks, chunk_units;
-    uint32_t slot_bytes;                  // ring slot size
+    uint32_t slot_bytes, slot_units;      // ring slot size; pair rows (K units) copied and consumed per slot
     uint32_t prologue;
     const float *in, *residual, *gamma0, *gamma1;
     float* residual_out;
@@ -760,7 +760,7 @@ __global__ void __launch_bounds__(kGemvWarps * 32, 1) gemv_kernel(const __grid_c
     }
     __syncthreads();
 
-    // Producer cursor (lane 0): the next pair row to request, walking items then units.
+    // Producer cursor (lane 0): the next slot-full of pair rows to request, walking items then units.
     uint32_t prod_item = 0, prod_unit = 0, prod_slot = 0, prod_bytes = 0;
     const uint8_t* prod_src = nullptr;
     auto issue_next = [&]() {   // lane 0 only
@@ -771,11 +771,13 @@ __global__ void __launch_bounds__(kGemvWarps * 32, 1) gemv_kernel(const __grid_c
             prod_bytes = pair_row_bytes((int)mat.dtype);
             prod_src = mat.weight + ((size_t)(pair - mat.first_pair) * p.units + first_unit) * prod_bytes;
         }
-        mbar_expect_tx(&bar[prod_slot], prod_bytes);
-        bulk_load(ring + prod_slot * p.slot_bytes, prod_src, prod_bytes, &bar[prod_slot]);
-        prod_src += prod_bytes;
+        const uint32_t count = min(p.slot_units, chunk_count - prod_unit), bytes = count * prod_bytes;
+        mbar_expect_tx(&bar[prod_slot], bytes);
+        bulk_load(ring + prod_slot * p.slot_bytes, prod_src, bytes, &bar[prod_slot]);
+        prod_src += bytes;
         prod_slot = prod_slot + 1u == (uint32_t)kGemvSlots ? 0u : prod_slot + 1u;
-        if (++prod_unit == chunk_count) { prod_unit = 0; ++prod_item; }
+        prod_unit += count;
+        if (prod_unit == chunk_count) { prod_unit = 0; ++prod_item; }
     };
     // Weights do not depend on the previous kernel: start streaming before waiting for it.
     if (lane == 0)
@@ -812,26 +814,29 @@ __global__ void __launch_bounds__(kGemvWarps * 32, 1) gemv_kernel(const __grid_c
         for (int nt = 0; nt < NT; ++nt) { accA[nt] = 0ull; accB[nt] = 0ull; }
 #pragma unroll
         for (int r = 0; r < ROWS; ++r) { maccA[r] = 0.0f; maccB[r] = 0.0f; }
-        for (uint32_t u = 0; u < chunk_count; ++u) {
+        const uint32_t row_bytes = pair_row_bytes((int)dtype);
+        for (uint32_t u0 = 0; u0 < chunk_count; u0 += p.slot_units) {
             if (!mbar_wait(&bar[slot], phase)) { failed = true; break; }
-            const uint8_t* row = ring + slot * p.slot_bytes;
-            if (dtype == GF_Q4_K) {
+            const uint32_t count = min(p.slot_units, chunk_count - u0);
+            for (uint32_t j = 0; j < count; ++j) {
+                const uint32_t u = u0 + j;
+                const uint8_t* row = ring + slot * p.slot_bytes + j * row_bytes;
                 float scales[NT];
+                if (dtype == GF_Q4_K) {
 #pragma unroll
-                for (int nt = 0; nt < NT; ++nt) scales[nt] = block_scales[my_row[nt] * scales_stride + u];
-                pair_row_q4k<ROWS, NT, FRAG_STRIDE>(row, my_frag + (size_t)u * 8u * FRAG_STRIDE, sums + u * 16u, sums_stride,
-                                                    scales, L, accA, accB, maccA, maccB);
-            } else if (dtype == GF_Q6_K) {
-                float scales[NT];
+                    for (int nt = 0; nt < NT; ++nt) scales[nt] = block_scales[my_row[nt] * scales_stride + u];
+                    pair_row_q4k<ROWS, NT, FRAG_STRIDE>(row, my_frag + (size_t)u * 8u * FRAG_STRIDE, sums + u * 16u, sums_stride,
+                                                        scales, L, accA, accB, maccA, maccB);
+                } else if (dtype == GF_Q6_K) {
 #pragma unroll
-                for (int nt = 0; nt < NT; ++nt) scales[nt] = block_scales[my_row[nt] * scales_stride + u];
-                pair_row_q6k<ROWS, NT, FRAG_STRIDE>(row, my_frag + (size_t)u * 8u * FRAG_STRIDE, sums + u * 16u, sums_stride,
-                                                    scales, L, accA, accB, maccA, maccB);
-            } else {
-                float scales[NT];
+                    for (int nt = 0; nt < NT; ++nt) scales[nt] = block_scales[my_row[nt] * scales_stride + u];
+                    pair_row_q6k<ROWS, NT, FRAG_STRIDE>(row, my_frag + (size_t)u * 8u * FRAG_STRIDE, sums + u * 16u, sums_stride,
+                                                        scales, L, accA, accB, maccA, maccB);
+                } else {
 #pragma unroll
-                for (int nt = 0; nt < NT; ++nt) scales[nt] = block_scales[my_row[nt] * scales_stride + (u >> 1)];
-                pair_row_q80<ROWS, NT, FRAG_STRIDE>(row, my_frag + (size_t)u * 4u * FRAG_STRIDE, scales, L, accA, accB);
+                    for (int nt = 0; nt < NT; ++nt) scales[nt] = block_scales[my_row[nt] * scales_stride + (u >> 1)];
+                    pair_row_q80<ROWS, NT, FRAG_STRIDE>(row, my_frag + (size_t)u * 4u * FRAG_STRIDE, scales, L, accA, accB);
+                }
             }
             __syncwarp();   // every lane has finished reading this slot
             if (lane == 0) issue_next();
@@ -933,7 +938,7 @@ struct GemvLaunch {
         int kv_f16 = 0;
     } heads;
 };
-struct GemvPlan { uint32_t units, unit_elems, total_pairs, chunks, chunk_units, grid, smem, slot_bytes; };
+struct GemvPlan { uint32_t units, unit_elems, total_pairs, chunks, chunk_units, grid, smem, slot_bytes, slot_units; };
 
 int gemv_plan(const GemvLaunch& launch, GemvPlan& plan);
 // Split-K scratch of one launch: `partial` bytes of sums, and one arrival counter per column pair.
