@@ -170,7 +170,7 @@ int Model::finalize() {
         // (cos, sin) of every position the plan can reach, formed on the host exactly as the
         // reference forms them: double angle = position * scale / base^(2i/d), then rounded to f32
         // (ops/rope.cpp:109-117).  256-wide heads only (the fused Q/K/V epilogue's layout).
-        if (c.head_dim == 256u) {
+        if (c.head_dim == 256u && c.context <= 65536u) {     // 1 KB per position and table; longer contexts rotate in rope_store_kernel
             float2* rotations[2] = {nullptr, nullptr};
             const float scales[2] = {c.rope_scale_local, c.rope_scale_global};
             const uint32_t table_rows = c.context + GF_MAX_ROWS;

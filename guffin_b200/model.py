@@ -53,6 +53,7 @@ lib.register({
     "gf_model_destroy": (i32, [vp]),
     "gf_model_set_matrix": (i32, [vp, i32, u32, i32, vp, u64, u64]),
     "gf_model_set_vector": (i32, [vp, i32, u32, vp, u32]),
+    "gf_model_load_gguf": (i32, [vp, C.c_char_p, vp]),
     "gf_model_finalize": (i32, [vp]),
     "gf_model_reset": (i32, [vp]),
     "gf_model_position": (i32, [vp, C.POINTER(u32)]),
@@ -102,16 +103,27 @@ def selection_request(retain: int, history=()) -> SelectionRequest:
 
 class Model:
     """A resident Gemma plan on the current device.  `weights` is the dict produced by
-    guffin_b200.synthetic.make_model_weights (GGUF tensor names), or any iterable of
-    (name, value) pairs such as synthetic.iter_model_weights."""
+    guffin_b200.synthetic.make_model_weights (GGUF tensor names), any iterable of
+    (name, value) pairs such as synthetic.iter_model_weights, or the path of a GGUF file."""
 
-    def __init__(self, config: dict, weights: dict, context: int, row_capacity: int = 2):
+    def __init__(self, config: dict, weights, context: int, row_capacity: int = 2):
         self.L = load()
         self.config = dict(config)
         self.cfg = make_config(config, context, row_capacity)
         handle = vp()
         check(self.L.gf_model_create(C.byref(self.cfg), C.byref(handle)))
         self.handle = handle.value
+        if isinstance(weights, (str, bytes)) or hasattr(weights, "__fspath__"):     # a GGUF file
+            import os
+            bound = u32()
+            try:
+                check(self.L.gf_model_load_gguf(self.handle, os.fsencode(weights), C.byref(bound)))
+                check(self.L.gf_model_finalize(self.handle))
+            except Exception:
+                self.close()
+                raise
+            self.bound_tensors = bound.value
+            return
         for name, value in (weights.items() if hasattr(weights, "items") else weights):
             parts = name.split(".")
             layer, short = (int(parts[1]), parts[2]) if parts[0] == "blk" else (0, parts[0])

@@ -207,6 +207,12 @@ GF_API int gf_model_set_matrix(gf_model* model, int kind, uint32_t layer, int dt
                                const void* native_host, uint64_t k, uint64_t n);
 GF_API int gf_model_set_vector(gf_model* model, int kind, uint32_t layer, const float* values_host,
                                uint32_t count);
+/* Binds every tensor of a GGUF v2/v3 file that the block schedule knows (llama.cpp tensor names,
+ * F32 vectors and Q8_0 / Q4_K / Q6_K matrices) through the two calls above: the path's share of
+ * read_file_backed_gguf_model (model_format/gguf_reader.hpp:85) and of the WeightMaterializer.
+ * The geometry still comes from gf_model_config; *out_bound_tensors (optional) counts the
+ * tensors taken.  Call gf_model_finalize afterwards. */
+GF_API int gf_model_load_gguf(gf_model* model, const char* path, uint32_t* out_bound_tensors);
 /* Checks every tensor is bound and allocates KV rings, private rows and scratch
  * (allocate_kv_cache, gemma2_metal_plan.cpp:514-537). */
 GF_API int gf_model_finalize(gf_model* model);

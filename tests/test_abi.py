@@ -43,3 +43,11 @@ def test_matmul_rejects_bad_arguments_without_a_gpu():
     assert L.gf_matmul_workspace_bytes(7, 1, 3840, 15360) == 0             # unknown dtype
     assert L.gf_matmul(lib.Q4_K, None, None, None, 0, 3840, 15360, None, None) == lib.GF_ERR_INVALID
     assert L.gf_matmul(lib.Q4_K, None, None, None, 1, 100, 15360, None, None) == lib.GF_ERR_INVALID
+
+
+def test_gguf_loader_rejects_missing_arguments_without_a_gpu(tmp_path):
+    L = lib.load()
+    L.gf_model_load_gguf.argtypes = [ctypes.c_void_p, ctypes.c_char_p, ctypes.c_void_p]
+    L.gf_model_load_gguf.restype = ctypes.c_int
+    assert L.gf_model_load_gguf(None, str(tmp_path / "absent.gguf").encode(), None) == lib.GF_ERR_INVALID
+    assert b"null argument" in L.gf_last_error()

@@ -100,6 +100,22 @@ def test_rows_are_count_invariant(gf, dtype, k, n):
     np.testing.assert_array_equal(gf.matmul_host(weight, x[:2]), together[:2])
 
 
+@pytest.mark.parametrize("dtype,k,n", [(syn.Q4_K, 3840, 64), (syn.Q6_K, 768, 40), (syn.Q8_0, 640, 48)])
+def test_non_finite_activation_poisons_its_row_only(gf, dtype, k, n):
+    """An infinity or NaN among the activations of a row makes that row's outputs NaN (the f32
+    reference propagates them through the dot product); the other row is untouched."""
+    rng = np.random.default_rng(5)
+    weight = gf.PackedWeight(dtype, k, n, syn.make_weight(rng, dtype, k, n))
+    x = rng.standard_normal((2, k)).astype(np.float32)
+    clean = gf.matmul(weight, x)
+    for bad in (np.inf, np.nan):
+        poisoned = x.copy()
+        poisoned[1, k // 3] = bad
+        y = gf.matmul(weight, poisoned)
+        np.testing.assert_array_equal(y[0], clean[0])
+        assert np.isnan(y[1]).all()
+
+
 def test_q4k_scale_min_cancellation(gf, oracle):
     """Large d*scale*q against large dmin*min: the adversarial case of
     tests/tensor/gemma3_metal_tests.cpp:1291-1365."""

@@ -318,6 +318,70 @@ def test_eight_row_prefill_equals_two_row_prefill(gf, gm, oracle, geometry, seed
     assert wide.status() == 0 and narrow.status() == 0
 
 
+def _write_gguf(path, weights, alignment=64):
+    """A GGUF v3 file with a metadata section of every value kind and the tensors of `weights`."""
+    import struct
+
+    def string(text):
+        raw = text.encode()
+        return struct.pack("<Q", len(raw)) + raw
+
+    metadata = [
+        string("general.architecture") + struct.pack("<I", 8) + string("gemma3"),
+        string("general.alignment") + struct.pack("<II", 4, alignment),
+        string("gemma3.attention.layer_norm_rms_epsilon") + struct.pack("<If", 6, 1e-6),
+        string("tokenizer.ggml.tokens") + struct.pack("<IIQ", 9, 8, 3) + string("a") + string("bc") + string(""),
+        string("tokenizer.ggml.scores") + struct.pack("<IIQ", 9, 6, 4) + struct.pack("<4f", 0, 1, 2, 3),
+        string("some.flag") + struct.pack("<IB", 7, 1),
+        string("some.count") + struct.pack("<IQ", 10, 1 << 40),
+    ]
+    tensors = [("rope_freqs.weight", (4,), 0, np.zeros(4, np.float32).tobytes())]      # a tensor the path ignores
+    for name, value in weights.items():
+        if isinstance(value, tuple):
+            dtype, k, n, data = value
+            tensors.append((name, (k, n), dtype, np.ascontiguousarray(data).tobytes()))
+        else:
+            tensors.append((name, (value.size,), 0, np.ascontiguousarray(value, np.float32).tobytes()))
+    head = b"GGUF" + struct.pack("<IQQ", 3, len(tensors), len(metadata)) + b"".join(metadata)
+    offset, payload = 0, []
+    for name, dims, ggml_type, data in tensors:
+        head += string(name) + struct.pack("<I", len(dims)) + b"".join(struct.pack("<Q", d) for d in dims)
+        head += struct.pack("<IQ", ggml_type, offset)
+        pad = (-len(data)) % alignment
+        payload.append(data + b"\0" * pad)
+        offset += len(data) + pad
+    head += b"\0" * ((-len(head)) % alignment)
+    with open(path, "wb") as f:
+        f.write(head)
+        for chunk in payload:
+            f.write(chunk)
+
+
+@pytest.mark.parametrize("geometry,seed", [("tiny-target", 61), ("tiny-gemma2", 62)])
+def test_gguf_file_loads_like_the_tensor_dictionary(gf, gm, tmp_path, geometry, seed):
+    """gf_model_load_gguf binds the same tensors as tensor-by-tensor set_matrix / set_vector calls:
+    identical logits, metadata of every kind skipped, unknown tensors ignored, damage refused."""
+    config = syn.model_config(geometry)
+    weights = syn.make_model_weights(geometry, seed)
+    path = tmp_path / "model.gguf"
+    _write_gguf(path, weights)
+    from_file = gm.Model(config, path, 64, 2)
+    from_dict = gm.Model(config, weights, 64, 2)
+    assert from_file.bound_tensors == len(weights)
+    tokens = np.random.default_rng(seed).integers(0, config["vocab"], 6).astype(np.uint32)
+    for model in (from_file, from_dict):
+        model.prefill(tokens)
+    np.testing.assert_array_equal(from_file.logits(1), from_dict.logits(1))
+    # A truncated file and a wrong magic are refused with GF_ERR_INVALID before anything is bound.
+    raw = path.read_bytes()
+    (tmp_path / "cut.gguf").write_bytes(raw[:len(raw) // 2])
+    (tmp_path / "magic.gguf").write_bytes(b"GGML" + raw[4:])
+    for bad in ("cut.gguf", "magic.gguf", "absent.gguf"):
+        with pytest.raises(gf.GuffinError) as error:
+            gm.Model(config, tmp_path / bad, 64, 2)
+        assert error.value.status == gf.GF_ERR_INVALID
+
+
 def test_graph_replay_equals_direct_launches(gf, gm):
     model, config, _ = _gpu_model(gm, "tiny-target", 31, context=64)
     direct, _, _ = _gpu_model(gm, "tiny-target", 31, context=64)
