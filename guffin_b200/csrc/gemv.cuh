@@ -456,8 +456,7 @@ __device__ __forceinline__ void quantize_piece(const GemvStage& st, uint32_t r, 
     uint32_t top = 0u;
 #pragma unroll
     for (int i = 0; i < 8; ++i) top = max(top, __float_as_uint(v[i]) & 0x7fffffffu);
-#pragma unroll
-    for (int offset = 16; offset > 0; offset >>= 1) top = max(top, __shfl_xor_sync(0xffffffffu, top, offset));
+    top = __reduce_max_sync(0xffffffffu, top);         // one warp-wide integer reduction instruction
     uint32_t e = top >> 23;
     if (e == 255u) { if (lane == 0u) atomicOr(st.bad_rows, 1u << r); e = 254u; }
     e = max(e, 30u);
