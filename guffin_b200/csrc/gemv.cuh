@@ -82,6 +82,10 @@ struct GemvParams {
 __host__ __device__ constexpr uint32_t gemv_fragment_columns(uint32_t rows) {
     return rows == 1u ? 4u : ((4u * rows + 7u) / 8u) * 8u;
 }
+// Bytes between the B registers of consecutive 32-element groups: 32 per column plus 32 of padding,
+// so that the lanes of a warp that quantise eight consecutive groups at once store to different
+// banks (without it the groups are a multiple of 128 bytes apart and collide eight ways).
+__host__ __device__ constexpr uint32_t gemv_fragment_stride(uint32_t rows) { return gemv_fragment_columns(rows) * 32u + 32u; }
 
 struct GemvSmemLayout {
     uint32_t frag_bytes, sums_bytes, scale_bytes, ring_bytes, total;
@@ -91,7 +95,7 @@ __host__ __device__ inline GemvSmemLayout gemv_smem_layout(uint32_t rows, uint32
                                                            uint32_t slot_bytes) {
     GemvSmemLayout s;
     const uint32_t slice = chunk_units * unit_elems, padded = (slice + 255u) & ~255u;
-    s.frag_bytes = padded * gemv_fragment_columns(rows);     // 32 bytes per group per column
+    s.frag_bytes = (padded / 32u) * gemv_fragment_stride(rows);
     s.sums_bytes = rows * (padded / 16u) * 4u;
     s.scale_bytes = ((rows * (padded / 256u) * 4u) + 15u) & ~15u;
     s.ring_bytes = (uint32_t)kGemvWarps * kGemvSlots * slot_bytes;
@@ -444,7 +448,7 @@ struct GemvStage {
 // scale 2^(e-156), every element becomes round(x / scale), an integer of at most 2^30, and adding
 // 0x00808080 then flipping those bits makes its four bytes signed base-256 digits.  For
 // 32-element group G2, B column n = 4 * row + digit and lane position t, the 8 bytes at
-// ((G2 * NCP + n) * 4 + t) * 8 are the digit bytes of elements 4t..4t+3 and 16+4t..16+4t+3 of
+// G2 * gemv_fragment_stride + (n * 4 + t) * 8 are the digit bytes of elements 4t..4t+3 and 16+4t..16+4t+3 of
 // the group.  Also written: the f32 sum of every 16 consecutive elements, the block scale, and
 // the row's flag when an input is not finite (the row then yields NaN).  `store` is false for
 // lanes whose piece lies outside the slice (they only take part in the warp exchanges).
@@ -477,7 +481,7 @@ __device__ __forceinline__ void quantize_piece(const GemvStage& st, uint32_t r, 
     { const uint32_t a[4] = {words[4], words[5], words[6], words[7]}; transpose_digits(a, d1); }
     // Elements 8*piece .. +7: group G2 = piece / 4, sixteen-half (piece / 2) & 1, positions t = 2 * (piece & 1), +1.
     const uint32_t g2 = piece >> 2, half = (piece >> 1) & 1u, t = (piece & 1u) * 2u;
-    uint8_t* dst = st.frags + ((size_t)g2 * NCP * 4u + t) * 8u + half * 4u;
+    uint8_t* dst = st.frags + (size_t)g2 * gemv_fragment_stride(ROWS) + t * 8u + half * 4u;
 #pragma unroll
     for (int i = 0; i < 4; ++i) {
         *reinterpret_cast<uint32_t*>(dst + (4u * r + i) * 32u) = d0[i];
@@ -720,7 +724,7 @@ template <int ROWS>
 __global__ void __launch_bounds__(kGemvWarps * 32, 1) gemv_kernel(const __grid_constant__ GemvParams p) {
     constexpr int NT = (4 * ROWS + 7) / 8;
     constexpr uint32_t NCP = gemv_fragment_columns(ROWS);
-    constexpr uint32_t FRAG_STRIDE = NCP * 32u;
+    constexpr uint32_t FRAG_STRIDE = gemv_fragment_stride(ROWS);
     extern __shared__ __align__(128) uint8_t smem[];
     __shared__ float scratch[2 * kGemvWarps * ROWS];
     __shared__ uint32_t bad_rows;
