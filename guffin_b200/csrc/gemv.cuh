@@ -520,12 +520,16 @@ __device__ __forceinline__ void stage_activations(const GemvParams& p, uint32_t 
             for (int i = 0; i < 8; ++i) { x[r][i] = 0.0f; res[r][i] = 0.0f; }
         if (live) {
 #pragma unroll
-            for (int r = 0; r < ROWS; ++r) {
-                if ((uint32_t)r >= p.active_rows) continue;
-                load8f(p.in + (size_t)r * p.k + o, x[r]);
-                if (p.prologue == kPrologueAddNorm) load8f(p.residual + (size_t)r * p.k + o, res[r]);
+            // What the first reduction needs goes first.
+#pragma unroll
+            for (int r = 0; r < ROWS; ++r)
+                if ((uint32_t)r < p.active_rows) load8f(p.in + (size_t)r * p.k + o, x[r]);
+            if (p.prologue == kPrologueAddNorm) {
+                load8f(p.gamma0 + o, g0);
+#pragma unroll
+                for (int r = 0; r < ROWS; ++r)
+                    if ((uint32_t)r < p.active_rows) load8f(p.residual + (size_t)r * p.k + o, res[r]);
             }
-            if (p.prologue == kPrologueAddNorm) load8f(p.gamma0 + o, g0);
             load8f(p.gamma1 + o, g1);
         }
         float ss[ROWS];
@@ -538,7 +542,8 @@ __device__ __forceinline__ void stage_activations(const GemvParams& p, uint32_t 
                 const float inv = rms_scale(ss[r], p.k, p.eps);
 #pragma unroll
                 for (int i = 0; i < 8; ++i) x[r][i] = __fadd_rn(res[r][i], __fmul_rn(__fmul_rn(x[r][i], inv), g0[i]));
-                if (blockIdx.x == 0 && live && (uint32_t)r < p.active_rows) store8f(p.residual_out + (size_t)r * p.k + o, x[r]);
+                // Every block holds the whole row: each writes the pieces that fall to it, so none straggles.
+                if (live && piece % gridDim.x == blockIdx.x && (uint32_t)r < p.active_rows) store8f(p.residual_out + (size_t)r * p.k + o, x[r]);
                 ss[r] = sum_squares(x[r], 0.0f);
             }
             gemv_block_sums<ROWS>(ss, scratch + kGemvWarps * ROWS);
@@ -584,7 +589,7 @@ __device__ __forceinline__ void stage_activations(const GemvParams& p, uint32_t 
 #pragma unroll
                     for (int i = 0; i < 8; ++i) x[i] = __fadd_rn(a[i], __fmul_rn(__fmul_rn(x[i], inv0[r]), gm[i]));
                     ss[r] = sum_squares(x, ss[r]);
-                    if (blockIdx.x == 0) store8f(p.residual_out + (size_t)r * p.k + c * 8u, x);
+                    if (c % gridDim.x == blockIdx.x) store8f(p.residual_out + (size_t)r * p.k + c * 8u, x);
                 }
             }
             gemv_block_sums<ROWS>(ss, scratch + kGemvWarps * ROWS);
