@@ -236,6 +236,7 @@ int Model::finalize() {
     uint8_t* bytes = nullptr;
     GF_TRY(device_alloc(allocations_, &bytes, ws)); matmul_ws_ = bytes; matmul_ws_bytes_ = ws;
     GF_TRY(device_alloc(allocations_, &bytes, counters)); matmul_counters_ = reinterpret_cast<uint32_t*>(bytes);
+    matmul_counters_bytes_ = counters;
     GF_CUDA(cudaMemsetAsync(matmul_counters_, 0, counters, stream_));   // arrival counters start (and stay) at zero
     GF_TRY(device_alloc(allocations_, &bytes, attention_workspace_bytes(R, c.heads))); attention_ws_ = bytes;
     GF_CUDA(cudaMemsetAsync(attention_counters(attention_ws_, R, c.heads), 0, (size_t)R * c.heads * sizeof(uint32_t), stream_));
@@ -263,6 +264,13 @@ int Model::reset() {
     if (!finalized_) return fail(GF_ERR_STATE, "plan is not finalized");
     GF_CUDA(cudaMemsetAsync(state_dev_, 0, 32, stream_));
     GF_CUDA(cudaMemsetAsync(status_dev_, 0, 16, stream_));
+    // A pass that was cut short (a bounded wait gave up) can leave arrival counters half way:
+    // every kernel that counts arrivals expects zero.
+    GF_CUDA(cudaMemsetAsync(error_flag_, 0, 16, stream_));
+    if (matmul_counters_bytes_) GF_CUDA(cudaMemsetAsync(matmul_counters_, 0, matmul_counters_bytes_, stream_));
+    GF_CUDA(cudaMemsetAsync(attention_counters(attention_ws_, config_.row_capacity, config_.heads), 0,
+                            (size_t)config_.row_capacity * config_.heads * sizeof(uint32_t), stream_));
+    if (head_counters_) GF_CUDA(cudaMemsetAsync(head_counters_, 0, (config_.heads + 2u * config_.kv_heads) * sizeof(uint32_t), stream_));
     position_ = 0;
     poisoned_ = false;
     return GF_OK;

@@ -106,6 +106,7 @@ private:
     void *attention_ws_ = nullptr, *matmul_ws_ = nullptr, *candidates_ws_ = nullptr;
     size_t matmul_ws_bytes_ = 0;
     uint32_t* matmul_counters_ = nullptr;
+    size_t matmul_counters_bytes_ = 0;
     KvPublishLayer* publish_layers_ = nullptr;
     uint32_t* head_counters_ = nullptr;
     void *requests_dev_ = nullptr, *results_dev_ = nullptr;
