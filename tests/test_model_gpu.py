@@ -382,6 +382,19 @@ def test_gguf_file_loads_like_the_tensor_dictionary(gf, gm, tmp_path, geometry, 
         assert error.value.status == gf.GF_ERR_INVALID
 
 
+def test_reset_returns_the_plan_to_its_first_token(gf, gm):
+    """gf_model_reset forgets the committed positions: the same prompt gives the same floats again."""
+    model, config, _ = _gpu_model(gm, "tiny-target", 71, context=64)
+    tokens = np.random.default_rng(71).integers(0, config["vocab"], 9).astype(np.uint32)
+    model.prefill(tokens)
+    first = model.logits(0).copy()
+    model.forward(tokens[:2], logits=True)          # leave an unpublished pass behind
+    model.reset()
+    assert model.position == 0 and model.status() == 0
+    model.prefill(tokens)
+    np.testing.assert_array_equal(model.logits(0), first)
+
+
 def test_graph_replay_equals_direct_launches(gf, gm):
     model, config, _ = _gpu_model(gm, "tiny-target", 31, context=64)
     direct, _, _ = _gpu_model(gm, "tiny-target", 31, context=64)
