@@ -211,8 +211,10 @@ __global__ void __launch_bounds__(kAttentionWarps * 32) attention_kernel(Attenti
     __shared__ float warp_m[kAttentionWarps][G], warp_l[kAttentionWarps][G];
     __shared__ float warp_acc[kAttentionWarps][G][256];
     __shared__ uint32_t arrival;
-    pdl_wait();
-    pdl_launch_dependents();
+    // The committed position and the ring rows were written by launches that completed before
+    // the launch ahead of this one began its work, so they are read ahead of the dependency wait:
+    // the first ring rows are then in flight while that launch drains.  The query and the private
+    // rows come from it and are read after the wait.
     const uint32_t kvh = blockIdx.x, part = blockIdx.y, row = blockIdx.z;
     const uint32_t warp = threadIdx.x >> 5, lane = threadIdx.x & 31u;
     const AttentionWindow win = attention_window(*p.base_position, row, p.window, p.tokens_per_part);
@@ -223,12 +225,6 @@ __global__ void __launch_bounds__(kAttentionWarps * 32) attention_kernel(Attenti
     const KV* priv_k = static_cast<const KV*>(p.private_k);
     const KV* priv_v = static_cast<const KV*>(p.private_v);
 
-    float q[G][8];
-#pragma unroll
-    for (int g = 0; g < G; ++g) {
-        const float* qp = p.q + ((size_t)row * p.heads + kvh * G + g) * 256u + lane * 8u;
-        load8(qp, q[g]);
-    }
     float m[G], l[G], acc[G][8];
 #pragma unroll
     for (int g = 0; g < G; ++g) {
@@ -256,7 +252,17 @@ __global__ void __launch_bounds__(kAttentionWarps * 32) attention_kernel(Attenti
         }
     };
     uint32_t quad = part * kAttentionWarps + warp;
-    if (quad < quads) fetch(quad);
+    const bool early = quad * 4u + 3u < win.base_count;
+    if (early) fetch(quad);
+    pdl_wait();
+    pdl_launch_dependents();
+    float q[G][8];
+#pragma unroll
+    for (int g = 0; g < G; ++g) {
+        const float* qp = p.q + ((size_t)row * p.heads + kvh * G + g) * 256u + lane * 8u;
+        load8(qp, q[g]);
+    }
+    if (!early && quad < quads) fetch(quad);
     for (; quad < quads; quad += step) {
         float kf[4][8], vf[4][8];
         bool valid[4];
