@@ -181,70 +181,88 @@ __device__ __forceinline__ void load8(const float* p, float (&v)[8]) {
     v[0] = a.x; v[1] = a.y; v[2] = a.z; v[3] = a.w; v[4] = b.x; v[5] = b.y; v[6] = b.z; v[7] = b.w;
 }
 
-struct AttentionWindow { uint32_t base_first, base_count, private_start, private_count, count, parts; };
+// The cached positions a group of consecutive verify/decode rows reads: the union of the rows'
+// key ranges.  Row r (position base + r) sees the positions from its window start (the sliding
+// window includes the row itself) up to its own; positions below the committed base live in the
+// ring, the rest are the private rows of the pass   (gemma_target_runtime.cpp:256-268,
+// target_verifier.cpp:186-202).  Consecutive rows' ranges overlap in all but one position at
+// each end, so one walk over the union serves the whole group with a per-row mask.
+struct AttentionSpan { uint32_t base, first, count, parts; };
 
-// Which cached rows a verify/decode row sees: the committed ring rows inside its window, then
-// the private rows of its ancestors, itself included (gemma_target_runtime.cpp:256-268,
-// target_verifier.cpp:186-202).  The sliding window includes the row itself.
-__device__ __forceinline__ AttentionWindow attention_window(uint32_t base, uint32_t row, uint32_t window, uint32_t tokens_per_part) {
-    AttentionWindow w;
-    const uint32_t position = base + row;
-    const uint32_t window_start = (window != 0u && position + 1u > window) ? position + 1u - window : 0u;
-    w.base_first = min(base, window_start);
-    w.base_count = base - w.base_first;
-    w.private_start = window_start > base ? window_start - base : 0u;
-    w.private_count = row + 1u - w.private_start;
-    w.count = w.base_count + w.private_count;
-    w.parts = min((uint32_t)kMaxAttentionPartitions,
-                  (w.count + tokens_per_part - 1u) / tokens_per_part);
-    return w;
+__device__ __forceinline__ uint32_t attention_window_start(uint32_t position, uint32_t window) {
+    return (window != 0u && position + 1u > window) ? position + 1u - window : 0u;
 }
 
-// Online-softmax GQA, head_dim 256: grid (kv_head, partition, row), kAttentionWarps warps per block.  A warp
-// walks quads of cached rows, loading the next quad while it works on the current one; a lane
-// owns eight of the 256 dimensions, so K and V rows are read as one coalesced 512-byte (F16) or
-// 1-KiB (F32) line per row, shared by the G query heads.  The block that finishes last for a
-// (row, kv head) merges the partitions in partition order.
-template <typename KV, int G>
+__device__ __forceinline__ AttentionSpan attention_span(uint32_t base, uint32_t first_row, uint32_t row_count, uint32_t window,
+                                                        uint32_t target_parts) {
+    AttentionSpan s;
+    s.base = base;
+    s.first = attention_window_start(base + first_row, window);
+    s.count = base + first_row + row_count - s.first;
+    // As many partitions as the launch has room for, none shorter than the minimum length, each a
+    // whole number of block iterations (kAttentionWarps quads).
+    uint32_t tokens = (s.count + target_parts - 1u) / target_parts;
+    tokens = max((uint32_t)kAttentionTokensPerPartition, (tokens + 4u * kAttentionWarps - 1u) / (4u * kAttentionWarps) * (4u * kAttentionWarps));
+    s.parts = min((uint32_t)kMaxAttentionPartitions, (s.count + tokens - 1u) / tokens);
+    return s;
+}
+
+// Online-softmax GQA, head_dim 256: grid (kv_head, partition, row group), kAttentionWarps warps per
+// block.  A block serves R consecutive rows and the G query heads of one KV head: Q = G * R query
+// vectors against one walk over the cached rows.  A warp walks quads of cached rows, loading the
+// next quad while it works on the current one; a lane owns eight of the 256 dimensions, so K and
+// V rows are read as one coalesced 512-byte (F16) or 1-KiB (F32) line per row.  The block that
+// finishes last for a (row group, kv head) merges the partitions in partition order.
+template <typename KV, int G, int R>
 __global__ void __launch_bounds__(kAttentionWarps * 32) attention_kernel(AttentionParams p) {
+    constexpr int Q = G * R;
+    static_assert(4 * Q <= 16, "scores hold sixteen (token, query) columns");
     __shared__ float scores[kAttentionWarps][16];
-    __shared__ float warp_m[kAttentionWarps][G], warp_l[kAttentionWarps][G];
-    __shared__ float warp_acc[kAttentionWarps][G][256];
+    __shared__ float warp_m[kAttentionWarps][Q], warp_l[kAttentionWarps][Q];
+    __shared__ float warp_acc[kAttentionWarps][Q][256];
     __shared__ uint32_t arrival;
     // The committed position and the ring rows were written by launches that completed before
     // the launch ahead of this one began its work, so they are read ahead of the dependency wait:
-    // the first ring rows are then in flight while that launch drains.  The query and the private
+    // the first ring rows are then in flight while that launch drains.  The queries and the private
     // rows come from it and are read after the wait.
-    const uint32_t kvh = blockIdx.x, part = blockIdx.y, row = blockIdx.z;
+    const uint32_t kvh = blockIdx.x, part = blockIdx.y, first_row = blockIdx.z * R;
     const uint32_t warp = threadIdx.x >> 5, lane = threadIdx.x & 31u;
-    const AttentionWindow win = attention_window(*p.base_position, row, p.window, p.tokens_per_part);
-    if (part >= win.parts) return;
+    const uint32_t live_rows = min((uint32_t)R, p.rows - first_row);
+    const AttentionSpan span = attention_span(*p.base_position, first_row, live_rows, p.window, p.target_parts);
+    if (part >= span.parts) return;
     const uint32_t kv_width = p.kv_heads * 256u;
     const KV* ring_k = static_cast<const KV*>(p.ring_k);
     const KV* ring_v = static_cast<const KV*>(p.ring_v);
     const KV* priv_k = static_cast<const KV*>(p.private_k);
     const KV* priv_v = static_cast<const KV*>(p.private_v);
 
-    float m[G], l[G], acc[G][8];
+    // Row r of the group sees positions [low[r], high[r]]; rows past the launch see none.
+    uint32_t low[R], high[R];
 #pragma unroll
-    for (int g = 0; g < G; ++g) {
-        m[g] = -INFINITY; l[g] = 0.0f;
-#pragma unroll
-        for (int d = 0; d < 8; ++d) acc[g][d] = 0.0f;
+    for (int r = 0; r < R; ++r) {
+        const uint32_t position = span.base + first_row + r;
+        low[r] = (uint32_t)r < live_rows ? attention_window_start(position, p.window) : 1u;
+        high[r] = (uint32_t)r < live_rows ? position : 0u;
     }
-    const uint32_t quads = (win.count + 3u) / 4u, step = win.parts * kAttentionWarps;
+    float m[Q], l[Q], acc[Q][8];
+#pragma unroll
+    for (int qi = 0; qi < Q; ++qi) {
+        m[qi] = -INFINITY; l[qi] = 0.0f;
+#pragma unroll
+        for (int d = 0; d < 8; ++d) acc[qi][d] = 0.0f;
+    }
+    const uint32_t quads = (span.count + 3u) / 4u, step = span.parts * kAttentionWarps;
     KvRaw<KV> kraw[4], vraw[4];
     auto fetch = [&](uint32_t quad) {
 #pragma unroll
         for (int t = 0; t < 4; ++t) {
-            const uint32_t token = quad * 4u + t;
+            const uint32_t position = span.first + min(quad * 4u + t, span.count - 1u);
             const KV *kp, *vp;
-            if (token < win.base_count) {
-                const size_t slot = ((size_t)((win.base_first + token) & p.ring_mask)) * kv_width + kvh * 256u + lane * 8u;
+            if (position < span.base) {
+                const size_t slot = ((size_t)(position & p.ring_mask)) * kv_width + kvh * 256u + lane * 8u;
                 kp = ring_k + slot; vp = ring_v + slot;
             } else {
-                const uint32_t prow = token < win.count ? win.private_start + (token - win.base_count) : 0u;
-                const size_t slot = (size_t)prow * kv_width + kvh * 256u + lane * 8u;
+                const size_t slot = (size_t)(position - span.base) * kv_width + kvh * 256u + lane * 8u;
                 kp = priv_k + slot; vp = priv_v + slot;
             }
             load_raw(kp, kraw[t]);
@@ -252,39 +270,39 @@ __global__ void __launch_bounds__(kAttentionWarps * 32) attention_kernel(Attenti
         }
     };
     uint32_t quad = part * kAttentionWarps + warp;
-    const bool early = quad * 4u + 3u < win.base_count;
+    const bool early = span.first + quad * 4u + 3u < span.base;
     if (early) fetch(quad);
     pdl_wait();
     pdl_launch_dependents();
-    float q[G][8];
+    float q[Q][8];
 #pragma unroll
-    for (int g = 0; g < G; ++g) {
-        const float* qp = p.q + ((size_t)row * p.heads + kvh * G + g) * 256u + lane * 8u;
-        load8(qp, q[g]);
+    for (int qi = 0; qi < Q; ++qi) {
+        const uint32_t row = min(first_row + qi / G, p.rows - 1u);
+        const float* qp = p.q + ((size_t)row * p.heads + kvh * G + qi % G) * 256u + lane * 8u;
+        load8(qp, q[qi]);
     }
     if (!early && quad < quads) fetch(quad);
     for (; quad < quads; quad += step) {
         float kf[4][8], vf[4][8];
-        bool valid[4];
+        uint32_t position[4];
 #pragma unroll
         for (int t = 0; t < 4; ++t) {
-            valid[t] = quad * 4u + t < win.count;
+            position[t] = span.first + quad * 4u + t;      // past the span: above every row's own position
             widen(kraw[t], kf[t]);
             widen(vraw[t], vf[t]);
         }
         if (quad + step < quads) fetch(quad + step);
-        // Partial dot products (token t, head g) -> column t*G+g, reduced across the warp eight at a time.
-        float s[4][G];
+        // Partial dot products (token t, query qi) -> column t*Q+qi, reduced across the warp eight at a time.
 #pragma unroll
-        for (int half = 0; half < (4 * G + 7) / 8; ++half) {
+        for (int half = 0; half < (4 * Q + 7) / 8; ++half) {
             float cols[8];
 #pragma unroll
             for (int cidx = 0; cidx < 8; ++cidx) {
-                const int flat = half * 8 + cidx, t = flat / G, g = flat % G;
+                const int flat = half * 8 + cidx, t = flat / Q, qi = flat % Q;
                 float dot = 0.0f;
-                if (flat < 4 * G) {
+                if (flat < 4 * Q) {
 #pragma unroll
-                    for (int d = 0; d < 8; ++d) dot = fmaf(q[g][d], kf[t][d], dot);
+                    for (int d = 0; d < 8; ++d) dot = fmaf(q[qi][d], kf[t][d], dot);
                 }
                 cols[cidx] = dot;
             }
@@ -292,56 +310,59 @@ __global__ void __launch_bounds__(kAttentionWarps * 32) attention_kernel(Attenti
             if ((lane & 3u) == 0u) scores[warp][half * 8 + column_of_lane(lane)] = total;
         }
         __syncwarp();
+        float s[4][Q];
+        bool visible[4][R];
 #pragma unroll
         for (int t = 0; t < 4; ++t)
 #pragma unroll
-            for (int g = 0; g < G; ++g) {
-                float v = scores[warp][t * G + g] * p.scale;
+            for (int qi = 0; qi < Q; ++qi) {
+                float v = scores[warp][t * Q + qi] * p.scale;
                 if (p.softcap > 0.0f) v = tanhf(v / p.softcap) * p.softcap;
-                s[t][g] = valid[t] ? v : -INFINITY;
+                visible[t][qi / G] = position[t] >= low[qi / G] && position[t] <= high[qi / G];
+                s[t][qi] = visible[t][qi / G] ? v : -INFINITY;
             }
         __syncwarp();
 #pragma unroll
-        for (int g = 0; g < G; ++g) {
-            float m_new = m[g];
+        for (int qi = 0; qi < Q; ++qi) {
+            float m_new = m[qi];
 #pragma unroll
-            for (int t = 0; t < 4; ++t) m_new = fmaxf(m_new, s[t][g]);
-            const float corr = m[g] == -INFINITY ? 0.0f : expf(m[g] - m_new);
+            for (int t = 0; t < 4; ++t) m_new = fmaxf(m_new, s[t][qi]);
+            const float corr = m[qi] == -INFINITY ? 0.0f : expf(m[qi] - m_new);
             float pr[4];
 #pragma unroll
-            for (int t = 0; t < 4; ++t) pr[t] = valid[t] ? expf(s[t][g] - m_new) : 0.0f;
-            l[g] = l[g] * corr + ((pr[0] + pr[1]) + (pr[2] + pr[3]));
+            for (int t = 0; t < 4; ++t) pr[t] = visible[t][qi / G] ? expf(s[t][qi] - m_new) : 0.0f;
+            l[qi] = l[qi] * corr + ((pr[0] + pr[1]) + (pr[2] + pr[3]));
 #pragma unroll
             for (int d = 0; d < 8; ++d) {
-                float a = acc[g][d] * corr;
+                float a = acc[qi][d] * corr;
 #pragma unroll
                 for (int t = 0; t < 4; ++t) a = fmaf(pr[t], vf[t][d], a);
-                acc[g][d] = a;
+                acc[qi][d] = a;
             }
-            m[g] = m_new;
+            m[qi] = m_new;
         }
     }
     // Combine the warps in warp order.
 #pragma unroll
-    for (int g = 0; g < G; ++g) {
-        if (lane == 0) { warp_m[warp][g] = m[g]; warp_l[warp][g] = l[g]; }
+    for (int qi = 0; qi < Q; ++qi) {
+        if (lane == 0) { warp_m[warp][qi] = m[qi]; warp_l[warp][qi] = l[qi]; }
 #pragma unroll
-        for (int d = 0; d < 8; ++d) warp_acc[warp][g][lane * 8 + d] = acc[g][d];
+        for (int d = 0; d < 8; ++d) warp_acc[warp][qi][lane * 8 + d] = acc[qi][d];
     }
     __syncthreads();
-    for (uint32_t idx = threadIdx.x; idx < (uint32_t)G * 256u; idx += blockDim.x) {
-        const uint32_t g = idx / 256u, d = idx % 256u;
+    for (uint32_t idx = threadIdx.x; idx < live_rows * (uint32_t)G * 256u; idx += blockDim.x) {
+        const uint32_t qi = idx / 256u, d = idx % 256u;
         float mm = -INFINITY;
-        for (int w = 0; w < kAttentionWarps; ++w) mm = fmaxf(mm, warp_m[w][g]);
+        for (int w = 0; w < kAttentionWarps; ++w) mm = fmaxf(mm, warp_m[w][qi]);
         float a = 0.0f, ll = 0.0f;
         for (int w = 0; w < kAttentionWarps; ++w) {
-            if (warp_l[w][g] == 0.0f) continue;
-            const float f = expf(warp_m[w][g] - mm);
-            a = fmaf(warp_acc[w][g][d], f, a);
-            ll = fmaf(warp_l[w][g], f, ll);
+            if (warp_l[w][qi] == 0.0f) continue;
+            const float f = expf(warp_m[w][qi] - mm);
+            a = fmaf(warp_acc[w][qi][d], f, a);
+            ll = fmaf(warp_l[w][qi], f, ll);
         }
-        const uint32_t head = kvh * G + g;
-        if (win.parts == 1u) {
+        const uint32_t row = first_row + qi / G, head = kvh * G + qi % G;
+        if (span.parts == 1u) {
             p.out[((size_t)row * p.heads + head) * 256u + d] = a / ll;
         } else {
             const size_t slot = ((size_t)row * p.heads + head) * kMaxAttentionPartitions + part;
@@ -349,49 +370,69 @@ __global__ void __launch_bounds__(kAttentionWarps * 32) attention_kernel(Attenti
             if (d == 0) { p.partial_ml[slot * 2u] = mm; p.partial_ml[slot * 2u + 1u] = ll; }
         }
     }
-    if (win.parts == 1u) return;
-    // The block that arrives last for this (row, kv head) merges all partitions.
+    if (span.parts == 1u) return;
+    // The block that arrives last for this (row group, kv head) merges all partitions.
     __threadfence();
     __syncthreads();
-    if (threadIdx.x == 0) arrival = atomicAdd(&p.counters[row * p.kv_heads + kvh], 1u);
+    if (threadIdx.x == 0) arrival = atomicAdd(&p.counters[blockIdx.z * p.kv_heads + kvh], 1u);
     __syncthreads();
-    if (arrival != win.parts - 1u) return;
+    if (arrival != span.parts - 1u) return;
     __threadfence();
-    // Weights of the partitions first (one thread per (head, partition), all loads in flight at
-    // once), then every thread sums its outputs over the partitions with the loads unrolled.
-    float* weight = &warp_acc[0][0][0];                 // [G][kMaxAttentionPartitions] factor, then [G] total
-    for (uint32_t idx = threadIdx.x; idx < (uint32_t)G * 32u; idx += blockDim.x) {
-        const uint32_t g = idx >> 5, lane_part = idx & 31u;
-        const size_t slot = ((size_t)row * p.heads + kvh * G + g) * kMaxAttentionPartitions + lane_part;
-        const bool live = lane_part < win.parts;
+    // A thread merges four consecutive dimensions of one query: its partial outputs of the first
+    // sixteen partitions are requested at once, ahead of the partition weights (one warp per
+    // query), so the two round trips to L2 overlap.  A partition in which a row saw no position
+    // carries (-inf, 0) and weighs nothing.
+    constexpr uint32_t kChunk = 16;
+    const uint32_t item = threadIdx.x, item_q = item / 64u, item_d = (item % 64u) * 4u;
+    const bool item_live = item_q < live_rows * (uint32_t)G;
+    const uint32_t item_row = first_row + item_q / G, item_head = kvh * G + item_q % G;
+    const float* item_src = p.partial_out + ((size_t)item_row * p.heads + item_head) * kMaxAttentionPartitions * 256u + item_d;
+    float4 v[kChunk];
+#pragma unroll
+    for (uint32_t j = 0; j < kChunk; ++j)
+        v[j] = item_live && j < span.parts ? __ldcg(reinterpret_cast<const float4*>(item_src + (size_t)j * 256u)) : make_float4(0.0f, 0.0f, 0.0f, 0.0f);
+    float* weight = &warp_acc[0][0][0];                 // [Q][kMaxAttentionPartitions] factor, then [Q] total
+    for (uint32_t idx = threadIdx.x; idx < live_rows * (uint32_t)G * 32u; idx += blockDim.x) {
+        const uint32_t qi = idx >> 5, lane_part = idx & 31u;
+        const uint32_t row = first_row + qi / G, head = kvh * G + qi % G;
+        const size_t slot = ((size_t)row * p.heads + head) * kMaxAttentionPartitions + lane_part;
+        const bool live = lane_part < span.parts;
         const float pm = live ? __ldcg(&p.partial_ml[slot * 2u]) : -INFINITY;
         const float pl = live ? __ldcg(&p.partial_ml[slot * 2u + 1u]) : 0.0f;
         float mm = pm;
 #pragma unroll
         for (int offset = 16; offset > 0; offset >>= 1) mm = fmaxf(mm, __shfl_xor_sync(0xffffffffu, mm, offset));
-        const float f = live ? expf(pm - mm) : 0.0f;
-        weight[g * kMaxAttentionPartitions + lane_part] = f;
-        // Sum of l_i * f_i in partition order: a shuffle scan would reorder it, so lane 0 adds.
-        float ll = 0.0f;
-        for (uint32_t i = 0; i < win.parts; ++i)
-            ll = fmaf(__shfl_sync(0xffffffffu, pl, i), __shfl_sync(0xffffffffu, f, i), ll);
-        if (lane_part == 0u) weight[G * kMaxAttentionPartitions + g] = ll;
+        const float f = live && pl != 0.0f ? expf(pm - mm) : 0.0f;
+        weight[qi * kMaxAttentionPartitions + lane_part] = f;
+        // Sum of l_i * f_i over the partitions in a fixed butterfly order (the same on every lane).
+        const float ll = warp_sum(pl * f);
+        if (lane_part == 0u) weight[Q * kMaxAttentionPartitions + qi] = ll;
     }
     __syncthreads();
-    for (uint32_t idx = threadIdx.x; idx < (uint32_t)G * 256u; idx += blockDim.x) {
-        const uint32_t g = idx / 256u, d = idx % 256u, head = kvh * G + g;
-        const size_t base = ((size_t)row * p.heads + head) * kMaxAttentionPartitions;
-        float a = 0.0f;
-        for (uint32_t i0 = 0; i0 < win.parts; i0 += 8u) {
-            float v[8];
+    if (item_live) {
+        float4 a = make_float4(0.0f, 0.0f, 0.0f, 0.0f);
+        const float* w = weight + item_q * kMaxAttentionPartitions;
 #pragma unroll
-            for (int j = 0; j < 8; ++j) v[j] = i0 + j < win.parts ? __ldcg(&p.partial_out[(base + i0 + j) * 256u + d]) : 0.0f;
-#pragma unroll
-            for (int j = 0; j < 8; ++j) a = fmaf(v[j], weight[g * kMaxAttentionPartitions + ((i0 + j) & 31u)], a);
+        for (uint32_t j = 0; j < kChunk; ++j) {
+            a.x = fmaf(v[j].x, w[j], a.x); a.y = fmaf(v[j].y, w[j], a.y);
+            a.z = fmaf(v[j].z, w[j], a.z); a.w = fmaf(v[j].w, w[j], a.w);
         }
-        p.out[((size_t)row * p.heads + head) * 256u + d] = a / weight[G * kMaxAttentionPartitions + g];
+        if (span.parts > kChunk) {
+#pragma unroll
+            for (uint32_t j = 0; j < kChunk; ++j)
+                v[j] = kChunk + j < span.parts ? __ldcg(reinterpret_cast<const float4*>(item_src + (size_t)(kChunk + j) * 256u))
+                                               : make_float4(0.0f, 0.0f, 0.0f, 0.0f);
+#pragma unroll
+            for (uint32_t j = 0; j < kChunk; ++j) {
+                a.x = fmaf(v[j].x, w[kChunk + j], a.x); a.y = fmaf(v[j].y, w[kChunk + j], a.y);
+                a.z = fmaf(v[j].z, w[kChunk + j], a.z); a.w = fmaf(v[j].w, w[kChunk + j], a.w);
+            }
+        }
+        const float total = weight[Q * kMaxAttentionPartitions + item_q];
+        *reinterpret_cast<float4*>(p.out + ((size_t)item_row * p.heads + item_head) * 256u + item_d) =
+            make_float4(a.x / total, a.y / total, a.z / total, a.w / total);
     }
-    if (threadIdx.x == 0) p.counters[row * p.kv_heads + kvh] = 0u;
+    if (threadIdx.x == 0) p.counters[blockIdx.z * p.kv_heads + kvh] = 0u;
 }
 
 // ------------------------------------------------------------------ GeGLU, KV publication
@@ -471,23 +512,35 @@ int launch_rope_store(const RopeStoreParams& p, cudaStream_t stream, bool pdl) {
     return launch_kernel(rope_store_kernel, dim3(p.heads + p.kv_heads, p.rows), dim3(p.head_dim / 2u), 0, stream, pdl, p);
 }
 
-template <typename KV>
-static int launch_attention_typed(const AttentionParams& p, cudaStream_t stream, bool pdl) {
-    const dim3 grid(p.kv_heads, kMaxAttentionPartitions, p.rows);
-    const uint32_t group = p.heads / p.kv_heads;
-    int status;
-    if (group == 1u) status = launch_kernel(attention_kernel<KV, 1>, grid, dim3(kAttentionWarps * 32), 0, stream, pdl, p);
-    else if (group == 2u) status = launch_kernel(attention_kernel<KV, 2>, grid, dim3(kAttentionWarps * 32), 0, stream, pdl, p);
-    else if (group == 4u) status = launch_kernel(attention_kernel<KV, 4>, grid, dim3(kAttentionWarps * 32), 0, stream, pdl, p);
-    else return fail(GF_ERR_INVALID, "attention: query/KV head ratio %u unsupported (1, 2, 4)", group);
-    return status;
+template <typename KV, int G, int R>
+static int launch_attention_instance(const AttentionParams& params, cudaStream_t stream, bool pdl) {
+    AttentionParams p = params;
+    const uint32_t groups = (p.rows + R - 1u) / R;
+    // About one block per SM: (kv head, row group) pairs times partitions.
+    const uint32_t per_pair = (uint32_t)sm_count() / (p.kv_heads * groups);
+    p.target_parts = per_pair < 1u ? 1u : per_pair > (uint32_t)kMaxAttentionPartitions ? (uint32_t)kMaxAttentionPartitions : per_pair;
+    return launch_kernel(attention_kernel<KV, G, R>, dim3(p.kv_heads, p.target_parts, groups), dim3(kAttentionWarps * 32), 0,
+                         stream, pdl, p);
 }
 
-int launch_attention(const AttentionParams& params, cudaStream_t stream, bool pdl) {
-    AttentionParams p = params;
-    // Few (kv head, row) pairs leave SMs idle unless the keys are cut finer; with many of them
-    // fewer, longer partitions save merge work.
-    p.tokens_per_part = p.kv_heads * p.rows >= 8u ? 2u * kAttentionTokensPerPartition : (uint32_t)kAttentionTokensPerPartition;
+// Rows are served in groups of R with G * R <= 4 query vectors per block.
+template <typename KV>
+static int launch_attention_typed(const AttentionParams& p, cudaStream_t stream, bool pdl) {
+    const uint32_t group = p.heads / p.kv_heads;
+    if (group == 1u) {
+        if (p.rows >= 3u) return launch_attention_instance<KV, 1, 4>(p, stream, pdl);
+        if (p.rows == 2u) return launch_attention_instance<KV, 1, 2>(p, stream, pdl);
+        return launch_attention_instance<KV, 1, 1>(p, stream, pdl);
+    }
+    if (group == 2u) {
+        if (p.rows >= 2u) return launch_attention_instance<KV, 2, 2>(p, stream, pdl);
+        return launch_attention_instance<KV, 2, 1>(p, stream, pdl);
+    }
+    if (group == 4u) return launch_attention_instance<KV, 4, 1>(p, stream, pdl);
+    return fail(GF_ERR_INVALID, "attention: query/KV head ratio %u unsupported (1, 2, 4)", group);
+}
+
+int launch_attention(const AttentionParams& p, cudaStream_t stream, bool pdl) {
     if (p.head_dim != 256u) return fail(GF_ERR_INVALID, "attention: head_dim must be 256 (got %u)", p.head_dim);
     if (p.heads % p.kv_heads) return fail(GF_ERR_INVALID, "attention: heads %u not a multiple of kv heads %u", p.heads, p.kv_heads);
     return p.kv_f16 ? launch_attention_typed<__half>(p, stream, pdl) : launch_attention_typed<float>(p, stream, pdl);

@@ -41,12 +41,12 @@ struct AttentionParams {
     float* out;                // [rows][heads*hd]
     float* partial_out;        // [rows][heads][kMaxAttentionPartitions][hd]
     float* partial_ml;         // [rows][heads][kMaxAttentionPartitions][2]
-    uint32_t* counters;        // [rows][kv_heads] partition arrivals, zero between launches
+    uint32_t* counters;        // [row groups][kv_heads] partition arrivals, zero between launches
     const uint32_t* base_position;
     uint32_t rows, heads, kv_heads, head_dim;
     uint32_t ring_mask;        // ring_rows - 1
     uint32_t window;           // 0 = global layer
-    uint32_t tokens_per_part;  // set by launch_attention
+    uint32_t target_parts;     // partitions the launch has room for per (kv head, row group); set by launch_attention
     float scale, softcap;
     int kv_f16;
 };

@@ -142,6 +142,14 @@ def test_attention_global_local_and_ring_wrap(gf, gm, oracle, kv_f16):
     # first tokens of a sequence, drafter head ratio 4:1, Gemma 2 score softcap
     _attention_case(gf, oracle, base=0, rows=1, window=8, ring_rows=16, heads=4, kv_heads=1, kv_f16=kv_f16, softcap=50.0, seed=4)
     _attention_case(gf, oracle, base=3, rows=3, window=0, ring_rows=16, heads=4, kv_heads=1, kv_f16=kv_f16, softcap=50.0, seed=5)
+    # rows served in groups: an odd row count (the last group has one live row), groups of four
+    # (head ratio 1), eight rows (prefill), and a window edge that falls inside a group
+    _attention_case(gf, oracle, base=300, rows=3, window=0, ring_rows=512, heads=4, kv_heads=2, kv_f16=kv_f16, softcap=0.0, seed=6)
+    _attention_case(gf, oracle, base=90, rows=5, window=64, ring_rows=128, heads=2, kv_heads=2, kv_f16=kv_f16, softcap=0.0, seed=7)
+    _attention_case(gf, oracle, base=200, rows=8, window=128, ring_rows=256, heads=4, kv_heads=2, kv_f16=kv_f16, softcap=0.0, seed=8)
+    _attention_case(gf, oracle, base=1, rows=2, window=2, ring_rows=4, heads=4, kv_heads=2, kv_f16=kv_f16, softcap=0.0, seed=9)
+    # a context long enough that every partition walks several block iterations
+    _attention_case(gf, oracle, base=5000, rows=2, window=0, ring_rows=8192, heads=16, kv_heads=8, kv_f16=kv_f16, softcap=0.0, seed=10)
 
 
 def test_attention_matches_reference_fixture(gf, gm):
