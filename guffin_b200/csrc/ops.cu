@@ -378,19 +378,27 @@ __global__ void __launch_bounds__(kAttentionWarps * 32) attention_kernel(Attenti
     __syncthreads();
     if (arrival != span.parts - 1u) return;
     __threadfence();
-    // A thread merges four consecutive dimensions of one query: its partial outputs of the first
-    // sixteen partitions are requested at once, ahead of the partition weights (one warp per
-    // query), so the two round trips to L2 overlap.  A partition in which a row saw no position
-    // carries (-inf, 0) and weighs nothing.
+    // A thread merges four consecutive dimensions of one query at a time (item = query * 64 +
+    // dimension / 4): the partial outputs of the first sixteen partitions of its first item are
+    // requested at once, ahead of the partition weights (one warp per query), so the two round
+    // trips to L2 overlap.  A partition in which a row saw no position carries (-inf, 0) and weighs
+    // nothing.
     constexpr uint32_t kChunk = 16;
-    const uint32_t item = threadIdx.x, item_q = item / 64u, item_d = (item % 64u) * 4u;
-    const bool item_live = item_q < live_rows * (uint32_t)G;
-    const uint32_t item_row = first_row + item_q / G, item_head = kvh * G + item_q % G;
-    const float* item_src = p.partial_out + ((size_t)item_row * p.heads + item_head) * kMaxAttentionPartitions * 256u + item_d;
+    const uint32_t items = live_rows * (uint32_t)G * 64u;
+    auto item_offset = [&](uint32_t item) -> size_t {      // of (row, head, dimension) in p.out; partials are 32 times as wide
+        const uint32_t qi = item / 64u;
+        return ((size_t)(first_row + qi / G) * p.heads + kvh * G + qi % G) * 256u + (item % 64u) * 4u;
+    };
     float4 v[kChunk];
+    auto load_chunk = [&](uint32_t item, uint32_t first_part) {
+        const size_t o = item_offset(item);
+        const float* src = p.partial_out + (o & ~(size_t)255u) * kMaxAttentionPartitions + (o & 255u);
 #pragma unroll
-    for (uint32_t j = 0; j < kChunk; ++j)
-        v[j] = item_live && j < span.parts ? __ldcg(reinterpret_cast<const float4*>(item_src + (size_t)j * 256u)) : make_float4(0.0f, 0.0f, 0.0f, 0.0f);
+        for (uint32_t j = 0; j < kChunk; ++j)
+            v[j] = first_part + j < span.parts ? __ldcg(reinterpret_cast<const float4*>(src + (size_t)(first_part + j) * 256u))
+                                               : make_float4(0.0f, 0.0f, 0.0f, 0.0f);
+    };
+    if (threadIdx.x < items) load_chunk(threadIdx.x, 0u);
     float* weight = &warp_acc[0][0][0];                 // [Q][kMaxAttentionPartitions] factor, then [Q] total
     for (uint32_t idx = threadIdx.x; idx < live_rows * (uint32_t)G * 32u; idx += blockDim.x) {
         const uint32_t qi = idx >> 5, lane_part = idx & 31u;
@@ -409,28 +417,21 @@ __global__ void __launch_bounds__(kAttentionWarps * 32) attention_kernel(Attenti
         if (lane_part == 0u) weight[Q * kMaxAttentionPartitions + qi] = ll;
     }
     __syncthreads();
-    if (item_live) {
+    for (uint32_t item = threadIdx.x; item < items; item += blockDim.x) {
+        const uint32_t qi = item / 64u;
+        const float* w = weight + qi * kMaxAttentionPartitions;
         float4 a = make_float4(0.0f, 0.0f, 0.0f, 0.0f);
-        const float* w = weight + item_q * kMaxAttentionPartitions;
-#pragma unroll
-        for (uint32_t j = 0; j < kChunk; ++j) {
-            a.x = fmaf(v[j].x, w[j], a.x); a.y = fmaf(v[j].y, w[j], a.y);
-            a.z = fmaf(v[j].z, w[j], a.z); a.w = fmaf(v[j].w, w[j], a.w);
-        }
-        if (span.parts > kChunk) {
-#pragma unroll
-            for (uint32_t j = 0; j < kChunk; ++j)
-                v[j] = kChunk + j < span.parts ? __ldcg(reinterpret_cast<const float4*>(item_src + (size_t)(kChunk + j) * 256u))
-                                               : make_float4(0.0f, 0.0f, 0.0f, 0.0f);
+        for (uint32_t first_part = 0; first_part < span.parts; first_part += kChunk) {
+            if (item != threadIdx.x || first_part != 0u) load_chunk(item, first_part);
 #pragma unroll
             for (uint32_t j = 0; j < kChunk; ++j) {
-                a.x = fmaf(v[j].x, w[kChunk + j], a.x); a.y = fmaf(v[j].y, w[kChunk + j], a.y);
-                a.z = fmaf(v[j].z, w[kChunk + j], a.z); a.w = fmaf(v[j].w, w[kChunk + j], a.w);
+                const float f = w[(first_part + j) & 31u];
+                a.x = fmaf(v[j].x, f, a.x); a.y = fmaf(v[j].y, f, a.y);
+                a.z = fmaf(v[j].z, f, a.z); a.w = fmaf(v[j].w, f, a.w);
             }
         }
-        const float total = weight[Q * kMaxAttentionPartitions + item_q];
-        *reinterpret_cast<float4*>(p.out + ((size_t)item_row * p.heads + item_head) * 256u + item_d) =
-            make_float4(a.x / total, a.y / total, a.z / total, a.w / total);
+        const float total = weight[Q * kMaxAttentionPartitions + qi];
+        *reinterpret_cast<float4*>(p.out + item_offset(item)) = make_float4(a.x / total, a.y / total, a.z / total, a.w / total);
     }
     if (threadIdx.x == 0) p.counters[blockIdx.z * p.kv_heads + kvh] = 0u;
 }
@@ -517,25 +518,23 @@ static int launch_attention_instance(const AttentionParams& params, cudaStream_t
     AttentionParams p = params;
     const uint32_t groups = (p.rows + R - 1u) / R;
     // About one block per SM: (kv head, row group) pairs times partitions.
-    const uint32_t per_pair = (uint32_t)sm_count() / (p.kv_heads * groups);
+    const uint32_t per_pair = (uint32_t)sm_count() * kAttentionBlocksPerSm / (p.kv_heads * groups);
     p.target_parts = per_pair < 1u ? 1u : per_pair > (uint32_t)kMaxAttentionPartitions ? (uint32_t)kMaxAttentionPartitions : per_pair;
     return launch_kernel(attention_kernel<KV, G, R>, dim3(p.kv_heads, p.target_parts, groups), dim3(kAttentionWarps * 32), 0,
                          stream, pdl, p);
 }
 
-// Rows are served in groups of R with G * R <= 4 query vectors per block.
+// Two query vectors per block where the head ratio allows it: measured on the 12B verify pass, four
+// (both rows of a pair of heads in one block) halve the blocks but double each warp's serial work
+// and came out 1 % slower per cycle.
 template <typename KV>
 static int launch_attention_typed(const AttentionParams& p, cudaStream_t stream, bool pdl) {
     const uint32_t group = p.heads / p.kv_heads;
     if (group == 1u) {
-        if (p.rows >= 3u) return launch_attention_instance<KV, 1, 4>(p, stream, pdl);
-        if (p.rows == 2u) return launch_attention_instance<KV, 1, 2>(p, stream, pdl);
+        if (p.rows >= 2u) return launch_attention_instance<KV, 1, 2>(p, stream, pdl);
         return launch_attention_instance<KV, 1, 1>(p, stream, pdl);
     }
-    if (group == 2u) {
-        if (p.rows >= 2u) return launch_attention_instance<KV, 2, 2>(p, stream, pdl);
-        return launch_attention_instance<KV, 2, 1>(p, stream, pdl);
-    }
+    if (group == 2u) return launch_attention_instance<KV, 2, 1>(p, stream, pdl);
     if (group == 4u) return launch_attention_instance<KV, 4, 1>(p, stream, pdl);
     return fail(GF_ERR_INVALID, "attention: query/KV head ratio %u unsupported (1, 2, 4)", group);
 }

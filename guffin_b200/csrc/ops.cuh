@@ -8,8 +8,9 @@
 namespace gf {
 
 constexpr int kMaxAttentionPartitions = 32;   // verifier_max_partitions in the reference
-constexpr int kAttentionTokensPerPartition = 64;
+constexpr int kAttentionTokensPerPartition = 32;
 constexpr int kAttentionWarps = 8;
+constexpr int kAttentionBlocksPerSm = 1;      // registers keep one 8-warp block per SM; 4-warp blocks at 2 or 3 per SM measured no faster
 
 // Status bits shared with the reference's validation word
 // (metal_kernels.mm:2332,2357,2370,2484; metal_command_context.hpp:17).
