@@ -194,17 +194,113 @@ __device__ __forceinline__ uint32_t attention_window_start(uint32_t position, ui
 }
 
 __device__ __forceinline__ AttentionSpan attention_span(uint32_t base, uint32_t first_row, uint32_t row_count, uint32_t window,
-                                                        uint32_t target_parts) {
+                                                        uint32_t target_parts, uint32_t granule, uint32_t min_tokens) {
     AttentionSpan s;
     s.base = base;
     s.first = attention_window_start(base + first_row, window);
     s.count = base + first_row + row_count - s.first;
     // As many partitions as the launch has room for, none shorter than the minimum length, each a
-    // whole number of block iterations (kAttentionWarps quads).
+    // whole number of block iterations (`granule` cached rows).
     uint32_t tokens = (s.count + target_parts - 1u) / target_parts;
-    tokens = max((uint32_t)kAttentionTokensPerPartition, (tokens + 4u * kAttentionWarps - 1u) / (4u * kAttentionWarps) * (4u * kAttentionWarps));
+    tokens = max(min_tokens, (tokens + granule - 1u) / granule * granule);
     s.parts = min((uint32_t)kMaxAttentionPartitions, (s.count + tokens - 1u) / tokens);
     return s;
+}
+
+// What follows the walk over the cache, for a block of W warps that has left each warp's running
+// maximum, sum and unnormalised output of its Q = G * R query vectors in shared memory: the warps
+// are combined in warp order; with one partition that is the result, otherwise it is parked and the
+// block that arrives last for the (row group, kv head) merges the partitions.
+template <int G, int R, int W>
+__device__ __forceinline__ void attention_finish(const AttentionParams& p, const AttentionSpan& span, uint32_t kvh, uint32_t part,
+                                                 uint32_t first_row, uint32_t live_rows, float (&warp_m)[W][G * R],
+                                                 float (&warp_l)[W][G * R], float (&warp_acc)[W][G * R][256], uint32_t& arrival) {
+    constexpr int Q = G * R;
+    __syncthreads();
+    for (uint32_t idx = threadIdx.x; idx < live_rows * (uint32_t)G * 256u; idx += blockDim.x) {
+        const uint32_t qi = idx / 256u, d = idx % 256u;
+        float mm = -INFINITY;
+        for (int w = 0; w < W; ++w) mm = fmaxf(mm, warp_m[w][qi]);
+        float a = 0.0f, ll = 0.0f;
+        for (int w = 0; w < W; ++w) {
+            if (warp_l[w][qi] == 0.0f) continue;
+            const float f = expf(warp_m[w][qi] - mm);
+            a = fmaf(warp_acc[w][qi][d], f, a);
+            ll = fmaf(warp_l[w][qi], f, ll);
+        }
+        const uint32_t row = first_row + qi / G, head = kvh * G + qi % G;
+        if (span.parts == 1u) {
+            p.out[((size_t)row * p.heads + head) * 256u + d] = a / ll;
+        } else {
+            const size_t slot = ((size_t)row * p.heads + head) * kMaxAttentionPartitions + part;
+            p.partial_out[slot * 256u + d] = a;
+            if (d == 0) { p.partial_ml[slot * 2u] = mm; p.partial_ml[slot * 2u + 1u] = ll; }
+        }
+    }
+    if (span.parts == 1u) return;
+    // The block that arrives last for this (row group, kv head) merges all partitions.
+    __threadfence();
+    __syncthreads();
+    if (threadIdx.x == 0) arrival = atomicAdd(&p.counters[blockIdx.z * p.kv_heads + kvh], 1u);
+    __syncthreads();
+    if (arrival != span.parts - 1u) return;
+    __threadfence();
+    // A thread merges four consecutive dimensions of one query at a time (item = query * 64 +
+    // dimension / 4): the partial outputs of all partitions of its first item are requested at
+    // once, ahead of the partition weights (one warp per query), so the two round trips to L2
+    // overlap.  A partition in which a row saw no position carries (-inf, 0) and weighs
+    // nothing.
+    constexpr uint32_t kChunk = kMaxAttentionPartitions;
+    const uint32_t items = live_rows * (uint32_t)G * 64u;
+    auto item_offset = [&](uint32_t item) -> size_t {      // of (row, head, dimension) in p.out; partials are 32 times as wide
+        const uint32_t qi = item / 64u;
+        return ((size_t)(first_row + qi / G) * p.heads + kvh * G + qi % G) * 256u + (item % 64u) * 4u;
+    };
+    float4 v[kChunk];
+    auto load_chunk = [&](uint32_t item, uint32_t first_part) {
+        const size_t o = item_offset(item);
+        const float* src = p.partial_out + (o & ~(size_t)255u) * kMaxAttentionPartitions + (o & 255u);
+#pragma unroll
+        for (uint32_t j = 0; j < kChunk; ++j)
+            v[j] = first_part + j < span.parts ? __ldcg(reinterpret_cast<const float4*>(src + (size_t)(first_part + j) * 256u))
+                                               : make_float4(0.0f, 0.0f, 0.0f, 0.0f);
+    };
+    if (threadIdx.x < items) load_chunk(threadIdx.x, 0u);
+    float* weight = &warp_acc[0][0][0];                 // [Q][kMaxAttentionPartitions] factor, then [Q] total
+    for (uint32_t idx = threadIdx.x; idx < live_rows * (uint32_t)G * 32u; idx += blockDim.x) {
+        const uint32_t qi = idx >> 5, lane_part = idx & 31u;
+        const uint32_t row = first_row + qi / G, head = kvh * G + qi % G;
+        const size_t slot = ((size_t)row * p.heads + head) * kMaxAttentionPartitions + lane_part;
+        const bool live = lane_part < span.parts;
+        const float pm = live ? __ldcg(&p.partial_ml[slot * 2u]) : -INFINITY;
+        const float pl = live ? __ldcg(&p.partial_ml[slot * 2u + 1u]) : 0.0f;
+        float mm = pm;
+#pragma unroll
+        for (int offset = 16; offset > 0; offset >>= 1) mm = fmaxf(mm, __shfl_xor_sync(0xffffffffu, mm, offset));
+        const float f = live && pl != 0.0f ? expf(pm - mm) : 0.0f;
+        weight[qi * kMaxAttentionPartitions + lane_part] = f;
+        // Sum of l_i * f_i over the partitions in a fixed butterfly order (the same on every lane).
+        const float ll = warp_sum(pl * f);
+        if (lane_part == 0u) weight[Q * kMaxAttentionPartitions + qi] = ll;
+    }
+    __syncthreads();
+    for (uint32_t item = threadIdx.x; item < items; item += blockDim.x) {
+        const uint32_t qi = item / 64u;
+        const float* w = weight + qi * kMaxAttentionPartitions;
+        float4 a = make_float4(0.0f, 0.0f, 0.0f, 0.0f);
+        for (uint32_t first_part = 0; first_part < span.parts; first_part += kChunk) {
+            if (item != threadIdx.x || first_part != 0u) load_chunk(item, first_part);
+#pragma unroll
+            for (uint32_t j = 0; j < kChunk; ++j) {
+                const float f = w[(first_part + j) & 31u];
+                a.x = fmaf(v[j].x, f, a.x); a.y = fmaf(v[j].y, f, a.y);
+                a.z = fmaf(v[j].z, f, a.z); a.w = fmaf(v[j].w, f, a.w);
+            }
+        }
+        const float total = weight[Q * kMaxAttentionPartitions + qi];
+        *reinterpret_cast<float4*>(p.out + item_offset(item)) = make_float4(a.x / total, a.y / total, a.z / total, a.w / total);
+    }
+    if (threadIdx.x == 0) p.counters[blockIdx.z * p.kv_heads + kvh] = 0u;
 }
 
 // Online-softmax GQA, head_dim 256: grid (kv_head, partition, row group), kAttentionWarps warps per
@@ -228,7 +324,8 @@ __global__ void __launch_bounds__(kAttentionWarps * 32) attention_kernel(Attenti
     const uint32_t kvh = blockIdx.x, part = blockIdx.y, first_row = blockIdx.z * R;
     const uint32_t warp = threadIdx.x >> 5, lane = threadIdx.x & 31u;
     const uint32_t live_rows = min((uint32_t)R, p.rows - first_row);
-    const AttentionSpan span = attention_span(*p.base_position, first_row, live_rows, p.window, p.target_parts);
+    const AttentionSpan span = attention_span(*p.base_position, first_row, live_rows, p.window, p.target_parts,
+                                               4u * kAttentionWarps, kAttentionTokensPerPartition);
     if (part >= span.parts) return;
     const uint32_t kv_width = p.kv_heads * 256u;
     const KV* ring_k = static_cast<const KV*>(p.ring_k);
@@ -349,91 +446,198 @@ __global__ void __launch_bounds__(kAttentionWarps * 32) attention_kernel(Attenti
 #pragma unroll
         for (int d = 0; d < 8; ++d) warp_acc[warp][qi][lane * 8 + d] = acc[qi][d];
     }
-    __syncthreads();
-    for (uint32_t idx = threadIdx.x; idx < live_rows * (uint32_t)G * 256u; idx += blockDim.x) {
-        const uint32_t qi = idx / 256u, d = idx % 256u;
-        float mm = -INFINITY;
-        for (int w = 0; w < kAttentionWarps; ++w) mm = fmaxf(mm, warp_m[w][qi]);
-        float a = 0.0f, ll = 0.0f;
-        for (int w = 0; w < kAttentionWarps; ++w) {
-            if (warp_l[w][qi] == 0.0f) continue;
-            const float f = expf(warp_m[w][qi] - mm);
-            a = fmaf(warp_acc[w][qi][d], f, a);
-            ll = fmaf(warp_l[w][qi], f, ll);
-        }
-        const uint32_t row = first_row + qi / G, head = kvh * G + qi % G;
-        if (span.parts == 1u) {
-            p.out[((size_t)row * p.heads + head) * 256u + d] = a / ll;
-        } else {
-            const size_t slot = ((size_t)row * p.heads + head) * kMaxAttentionPartitions + part;
-            p.partial_out[slot * 256u + d] = a;
-            if (d == 0) { p.partial_ml[slot * 2u] = mm; p.partial_ml[slot * 2u + 1u] = ll; }
-        }
-    }
-    if (span.parts == 1u) return;
-    // The block that arrives last for this (row group, kv head) merges all partitions.
-    __threadfence();
-    __syncthreads();
-    if (threadIdx.x == 0) arrival = atomicAdd(&p.counters[blockIdx.z * p.kv_heads + kvh], 1u);
-    __syncthreads();
-    if (arrival != span.parts - 1u) return;
-    __threadfence();
-    // A thread merges four consecutive dimensions of one query at a time (item = query * 64 +
-    // dimension / 4): the partial outputs of the first sixteen partitions of its first item are
-    // requested at once, ahead of the partition weights (one warp per query), so the two round
-    // trips to L2 overlap.  A partition in which a row saw no position carries (-inf, 0) and weighs
-    // nothing.
-    constexpr uint32_t kChunk = 16;
-    const uint32_t items = live_rows * (uint32_t)G * 64u;
-    auto item_offset = [&](uint32_t item) -> size_t {      // of (row, head, dimension) in p.out; partials are 32 times as wide
-        const uint32_t qi = item / 64u;
-        return ((size_t)(first_row + qi / G) * p.heads + kvh * G + qi % G) * 256u + (item % 64u) * 4u;
+    attention_finish<G, R, kAttentionWarps>(p, span, kvh, part, first_row, live_rows, warp_m, warp_l, warp_acc, arrival);
+}
+
+// ---- attention over a binary16 cache on the tensor cores
+//
+// D (16 x 8, f32) += A (16 x 16, f16, row-major) * B (16 x 8, f16, column-major), one warp.  With
+// g = lane / 4 and t = lane % 4, a lane holds A rows g (a[0], a[2]) and g + 8 (a[1], a[3]), columns
+// 2t, 2t+1 (a[0], a[1]) and 2t+8, 2t+9 (a[2], a[3]); B rows 2t, 2t+1 (b0) and 2t+8, 2t+9 (b1) of
+// column g; D rows g (d[0], d[1]) and g + 8 (d[2], d[3]), columns 2t and 2t+1.
+__device__ __forceinline__ void mma_f16_k16(float (&d)[4], uint32_t a0, uint32_t a1, uint32_t a2, uint32_t a3, uint32_t b0, uint32_t b1) {
+    asm volatile("mma.sync.aligned.m16n8k16.row.col.f32.f16.f16.f32 {%0, %1, %2, %3}, {%4, %5, %6, %7}, {%8, %9}, {%0, %1, %2, %3};"
+                 : "+f"(d[0]), "+f"(d[1]), "+f"(d[2]), "+f"(d[3])
+                 : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1));
+}
+// An f32 value as the sum of two binary16 values (exact to about 2^-22 of its magnitude).
+__device__ __forceinline__ void split_f16(float x, __half& hi, __half& lo) {
+    hi = __float2half_rn(x);
+    lo = __float2half_rn(x - __half2float(hi));
+}
+__device__ __forceinline__ uint32_t pack_halves(__half a, __half b) {
+    const __half2 h = __halves2half2(a, b);
+    return *reinterpret_cast<const uint32_t*>(&h);
+}
+__device__ __forceinline__ uint32_t word_of(const uint4& v, int i) { return i == 0 ? v.x : i == 1 ? v.y : i == 2 ? v.z : v.w; }
+
+constexpr int kAttentionMmaWarps = 8;
+
+// The same online-softmax GQA as attention_kernel for a binary16 cache, with both contractions on
+// the tensor cores.  A warp takes tiles of sixteen cached rows.  The Q <= 4 query vectors become
+// eight B columns, column 2q the binary16 rounding of (scale * query q) and column 2q + 1 the
+// rounding of what that left over, so the two columns' products add up to the f32 score; the
+// softmax weights are split the same way for the second contraction.  The cache rows are the A
+// operands as they lie in memory: the contraction index of a product may be permuted freely as long
+// as both operands agree, so a lane reads whole 16-byte pieces -- for the scores, dimensions
+// 32c + 8t .. +7 of rows g and g + 8 serve k-steps 2c and 2c + 1; for the outputs, dimensions
+// 64J + 8g .. +7 of rows 2t, 2t+1, 2t+8, 2t+9 are paired across rows by byte permutes and serve the
+// four output tiles of group J, whose rows g / g + 8 stand for dimensions 64J + 8g + j / + 4 + j.
+// A lane ends up with dimensions 64J + 8g .. +7 (J = 0..3) of query t.
+template <int G, int R>
+__global__ void __launch_bounds__(kAttentionMmaWarps * 32) attention_mma_kernel(AttentionParams p) {
+    constexpr int Q = G * R, W = kAttentionMmaWarps;
+    static_assert(Q <= 4, "eight B columns hold four split query vectors");
+    __shared__ float warp_m[W][Q], warp_l[W][Q];
+    __shared__ float warp_acc[W][Q][256];
+    __shared__ uint2 q_frag[16][32];            // B registers of k-step ks, per lane
+    __shared__ uint32_t arrival;
+    // As in attention_kernel: the committed position and ring rows are read ahead of the dependency
+    // wait, the queries and the private rows after it.
+    const uint32_t kvh = blockIdx.x, part = blockIdx.y, first_row = blockIdx.z * R;
+    const uint32_t warp = threadIdx.x >> 5, lane = threadIdx.x & 31u, g = lane >> 2, t = lane & 3u;
+    const uint32_t live_rows = min((uint32_t)R, p.rows - first_row), live_q = live_rows * G;
+    const AttentionSpan span = attention_span(*p.base_position, first_row, live_rows, p.window, p.target_parts, 16u * W, 16u * W);
+    if (part >= span.parts) return;
+    const uint32_t kv_width = p.kv_heads * 256u;
+    const __half* ring_k = static_cast<const __half*>(p.ring_k);
+    const __half* ring_v = static_cast<const __half*>(p.ring_v);
+    const __half* priv_k = static_cast<const __half*>(p.private_k);
+    const __half* priv_v = static_cast<const __half*>(p.private_v);
+
+    // This lane's query t belongs to row t / G of the group and sees positions [low, high].
+    const bool my_live = t < live_q;
+    const uint32_t my_position = span.base + first_row + t / G;
+    const uint32_t low = my_live ? attention_window_start(my_position, p.window) : 1u, high = my_live ? my_position : 0u;
+
+    auto row_of = [&](uint32_t token, const __half* ring, const __half* priv) -> const __half* {
+        const uint32_t position = span.first + min(token, span.count - 1u);
+        return position < span.base ? ring + (size_t)(position & p.ring_mask) * kv_width + kvh * 256u
+                                    : priv + (size_t)(position - span.base) * kv_width + kvh * 256u;
     };
-    float4 v[kChunk];
-    auto load_chunk = [&](uint32_t item, uint32_t first_part) {
-        const size_t o = item_offset(item);
-        const float* src = p.partial_out + (o & ~(size_t)255u) * kMaxAttentionPartitions + (o & 255u);
+    uint4 kraw[2][8], vraw[4][4];
+    auto fetch_k = [&](uint32_t tile) {
 #pragma unroll
-        for (uint32_t j = 0; j < kChunk; ++j)
-            v[j] = first_part + j < span.parts ? __ldcg(reinterpret_cast<const float4*>(src + (size_t)(first_part + j) * 256u))
-                                               : make_float4(0.0f, 0.0f, 0.0f, 0.0f);
+        for (int h = 0; h < 2; ++h) {
+            const __half* src = row_of(tile * 16u + g + 8u * h, ring_k, priv_k) + 8u * t;
+#pragma unroll
+            for (int c = 0; c < 8; ++c) kraw[h][c] = *reinterpret_cast<const uint4*>(src + 32 * c);
+        }
     };
-    if (threadIdx.x < items) load_chunk(threadIdx.x, 0u);
-    float* weight = &warp_acc[0][0][0];                 // [Q][kMaxAttentionPartitions] factor, then [Q] total
-    for (uint32_t idx = threadIdx.x; idx < live_rows * (uint32_t)G * 32u; idx += blockDim.x) {
-        const uint32_t qi = idx >> 5, lane_part = idx & 31u;
-        const uint32_t row = first_row + qi / G, head = kvh * G + qi % G;
-        const size_t slot = ((size_t)row * p.heads + head) * kMaxAttentionPartitions + lane_part;
-        const bool live = lane_part < span.parts;
-        const float pm = live ? __ldcg(&p.partial_ml[slot * 2u]) : -INFINITY;
-        const float pl = live ? __ldcg(&p.partial_ml[slot * 2u + 1u]) : 0.0f;
-        float mm = pm;
+    auto fetch_v = [&](uint32_t tile) {
 #pragma unroll
-        for (int offset = 16; offset > 0; offset >>= 1) mm = fmaxf(mm, __shfl_xor_sync(0xffffffffu, mm, offset));
-        const float f = live && pl != 0.0f ? expf(pm - mm) : 0.0f;
-        weight[qi * kMaxAttentionPartitions + lane_part] = f;
-        // Sum of l_i * f_i over the partitions in a fixed butterfly order (the same on every lane).
-        const float ll = warp_sum(pl * f);
-        if (lane_part == 0u) weight[Q * kMaxAttentionPartitions + qi] = ll;
-    }
-    __syncthreads();
-    for (uint32_t item = threadIdx.x; item < items; item += blockDim.x) {
-        const uint32_t qi = item / 64u;
-        const float* w = weight + qi * kMaxAttentionPartitions;
-        float4 a = make_float4(0.0f, 0.0f, 0.0f, 0.0f);
-        for (uint32_t first_part = 0; first_part < span.parts; first_part += kChunk) {
-            if (item != threadIdx.x || first_part != 0u) load_chunk(item, first_part);
+        for (int u = 0; u < 4; ++u) {
+            const __half* src = row_of(tile * 16u + 2u * t + (u & 1) + 8u * (u >> 1), ring_v, priv_v) + 8u * g;
 #pragma unroll
-            for (uint32_t j = 0; j < kChunk; ++j) {
-                const float f = w[(first_part + j) & 31u];
-                a.x = fmaf(v[j].x, f, a.x); a.y = fmaf(v[j].y, f, a.y);
-                a.z = fmaf(v[j].z, f, a.z); a.w = fmaf(v[j].w, f, a.w);
+            for (int J = 0; J < 4; ++J) vraw[u][J] = *reinterpret_cast<const uint4*>(src + 64 * J);
+        }
+    };
+    const uint32_t tiles = (span.count + 15u) / 16u, step = span.parts * W;
+    uint32_t tile = part * W + warp;
+    const bool early = span.first + tile * 16u + 15u < span.base;
+    if (early) { fetch_k(tile); fetch_v(tile); }
+    pdl_wait();
+    pdl_launch_dependents();
+    // B registers of the scores: lane (g, t) holds, of column g (query g / 2, rounding or left-over),
+    // dimensions 32c + 8t + 4e .. +3 for k-step 2c + e.  Warp w prepares chunks c = w, w + W, ...
+    {
+        const uint32_t qv = g >> 1;
+        for (uint32_t c = warp; c < 8u; c += W) {
+            float x[8];
+#pragma unroll
+            for (int i = 0; i < 8; ++i) x[i] = 0.0f;
+            if (qv < live_q) load8(p.q + ((size_t)(first_row + qv / G) * p.heads + kvh * G + qv % G) * 256u + 32u * c + 8u * t, x);
+            uint32_t w[4];
+#pragma unroll
+            for (int k = 0; k < 4; ++k) {
+                __half h0, l0, h1, l1;
+                split_f16(x[2 * k] * p.scale, h0, l0);
+                split_f16(x[2 * k + 1] * p.scale, h1, l1);
+                w[k] = (g & 1u) ? pack_halves(l0, l1) : pack_halves(h0, h1);
             }
+            q_frag[2u * c][lane] = make_uint2(w[0], w[1]);
+            q_frag[2u * c + 1u][lane] = make_uint2(w[2], w[3]);
         }
-        const float total = weight[Q * kMaxAttentionPartitions + qi];
-        *reinterpret_cast<float4*>(p.out + item_offset(item)) = make_float4(a.x / total, a.y / total, a.z / total, a.w / total);
     }
-    if (threadIdx.x == 0) p.counters[blockIdx.z * p.kv_heads + kvh] = 0u;
+    __syncthreads();
+    if (!early && tile < tiles) { fetch_k(tile); fetch_v(tile); }
+
+    float m_run = -INFINITY, l_run = 0.0f;      // of query t, over this lane's rows g and g + 8 of every tile
+    float acc[16][4];
+#pragma unroll
+    for (int i = 0; i < 16; ++i) { acc[i][0] = 0.0f; acc[i][1] = 0.0f; acc[i][2] = 0.0f; acc[i][3] = 0.0f; }
+    for (; tile < tiles; tile += step) {
+        float s4[4] = {0.0f, 0.0f, 0.0f, 0.0f};
+#pragma unroll
+        for (int c = 0; c < 8; ++c)
+#pragma unroll
+            for (int e = 0; e < 2; ++e) {
+                const uint2 b = q_frag[2 * c + e][lane];
+                mma_f16_k16(s4, word_of(kraw[0][c], 2 * e), word_of(kraw[1][c], 2 * e), word_of(kraw[0][c], 2 * e + 1),
+                            word_of(kraw[1][c], 2 * e + 1), b.x, b.y);
+            }
+        const bool more = tile + step < tiles;
+        if (more) fetch_k(tile + step);
+        // Scores of rows g and g + 8 against query t: rounding column plus left-over column.
+        float s0 = s4[0] + s4[1], s1 = s4[2] + s4[3];
+        if (p.softcap > 0.0f) { s0 = tanhf(s0 / p.softcap) * p.softcap; s1 = tanhf(s1 / p.softcap) * p.softcap; }
+        const uint32_t position0 = span.first + tile * 16u + g, position1 = position0 + 8u;
+        const bool visible0 = position0 >= low && position0 <= high, visible1 = position1 >= low && position1 <= high;
+        float m_new = fmaxf(visible0 ? s0 : -INFINITY, visible1 ? s1 : -INFINITY);
+        m_new = fmaxf(m_new, __shfl_xor_sync(0xffffffffu, m_new, 4));
+        m_new = fmaxf(m_new, __shfl_xor_sync(0xffffffffu, m_new, 8));
+        m_new = fmaxf(m_new, __shfl_xor_sync(0xffffffffu, m_new, 16));
+        m_new = fmaxf(m_new, m_run);
+        const float corr = m_run == -INFINITY ? 0.0f : expf(m_run - m_new);
+        const float p0 = visible0 ? expf(s0 - m_new) : 0.0f, p1 = visible1 ? expf(s1 - m_new) : 0.0f;
+        l_run = l_run * corr + (p0 + p1);
+        m_run = m_new;
+        if (!__all_sync(0xffffffffu, corr == 1.0f)) {
+#pragma unroll
+            for (int i = 0; i < 16; ++i) { acc[i][0] *= corr; acc[i][1] *= corr; acc[i][2] *= corr; acc[i][3] *= corr; }
+        }
+        // B registers of the outputs: lane (g, t) needs, of column g (query g / 2, rounding or
+        // left-over of the weight), rows 2t, 2t+1, 2t+8, 2t+9; row r < 8 of query q is p0 of lane
+        // 4r + q, row r + 8 its p1.
+        __half h0, l0, h1, l1;
+        split_f16(p0, h0, l0);
+        split_f16(p1, h1, l1);
+        const uint32_t rounded = pack_halves(h0, h1), left_over = pack_halves(l0, l1);
+        const uint32_t source = 8u * t + (g >> 1);
+        const uint32_t ra = __shfl_sync(0xffffffffu, rounded, source), la = __shfl_sync(0xffffffffu, left_over, source);
+        const uint32_t rb = __shfl_sync(0xffffffffu, rounded, source + 4u), lb = __shfl_sync(0xffffffffu, left_over, source + 4u);
+        const uint32_t xa = (g & 1u) ? la : ra, xb = (g & 1u) ? lb : rb;
+        const uint32_t b0 = __byte_perm(xa, xb, 0x5410u), b1 = __byte_perm(xa, xb, 0x7632u);
+#pragma unroll
+        for (int J = 0; J < 4; ++J)
+#pragma unroll
+            for (int j = 0; j < 4; ++j) {
+                const uint32_t sel = (j & 1) ? 0x7632u : 0x5410u;
+                const int wi = j >> 1;
+                mma_f16_k16(acc[J * 4 + j],
+                            __byte_perm(word_of(vraw[0][J], wi), word_of(vraw[1][J], wi), sel),
+                            __byte_perm(word_of(vraw[0][J], 2 + wi), word_of(vraw[1][J], 2 + wi), sel),
+                            __byte_perm(word_of(vraw[2][J], wi), word_of(vraw[3][J], wi), sel),
+                            __byte_perm(word_of(vraw[2][J], 2 + wi), word_of(vraw[3][J], 2 + wi), sel), b0, b1);
+            }
+        if (more) fetch_v(tile + step);
+    }
+    // Sum of the weights over the eight row pairs; then the warp's state goes to shared memory.
+    l_run += __shfl_xor_sync(0xffffffffu, l_run, 4);
+    l_run += __shfl_xor_sync(0xffffffffu, l_run, 8);
+    l_run += __shfl_xor_sync(0xffffffffu, l_run, 16);
+    if (my_live) {
+        if (g == 0u) { warp_m[warp][t] = m_run; warp_l[warp][t] = l_run; }
+#pragma unroll
+        for (int J = 0; J < 4; ++J) {
+            float* dst = &warp_acc[warp][t][64 * J + 8 * g];
+            *reinterpret_cast<float4*>(dst) = make_float4(acc[J * 4][0] + acc[J * 4][1], acc[J * 4 + 1][0] + acc[J * 4 + 1][1],
+                                                          acc[J * 4 + 2][0] + acc[J * 4 + 2][1], acc[J * 4 + 3][0] + acc[J * 4 + 3][1]);
+            *reinterpret_cast<float4*>(dst + 4) = make_float4(acc[J * 4][2] + acc[J * 4][3], acc[J * 4 + 1][2] + acc[J * 4 + 1][3],
+                                                              acc[J * 4 + 2][2] + acc[J * 4 + 2][3], acc[J * 4 + 3][2] + acc[J * 4 + 3][3]);
+        }
+    }
+    attention_finish<G, R, W>(p, span, kvh, part, first_row, live_rows, warp_m, warp_l, warp_acc, arrival);
 }
 
 // ------------------------------------------------------------------ GeGLU, KV publication
@@ -513,36 +717,64 @@ int launch_rope_store(const RopeStoreParams& p, cudaStream_t stream, bool pdl) {
     return launch_kernel(rope_store_kernel, dim3(p.heads + p.kv_heads, p.rows), dim3(p.head_dim / 2u), 0, stream, pdl, p);
 }
 
+static uint32_t attention_target_parts(const AttentionParams& p, uint32_t groups, uint32_t blocks_per_sm) {
+    // About one wave of blocks: (kv head, row group) pairs times partitions.
+    const uint32_t per_pair = (uint32_t)sm_count() * blocks_per_sm / (p.kv_heads * groups);
+    return per_pair < 1u ? 1u : per_pair > (uint32_t)kMaxAttentionPartitions ? (uint32_t)kMaxAttentionPartitions : per_pair;
+}
+
 template <typename KV, int G, int R>
 static int launch_attention_instance(const AttentionParams& params, cudaStream_t stream, bool pdl) {
     AttentionParams p = params;
     const uint32_t groups = (p.rows + R - 1u) / R;
-    // About one block per SM: (kv head, row group) pairs times partitions.
-    const uint32_t per_pair = (uint32_t)sm_count() * kAttentionBlocksPerSm / (p.kv_heads * groups);
-    p.target_parts = per_pair < 1u ? 1u : per_pair > (uint32_t)kMaxAttentionPartitions ? (uint32_t)kMaxAttentionPartitions : per_pair;
+    p.target_parts = attention_target_parts(p, groups, kAttentionBlocksPerSm);
     return launch_kernel(attention_kernel<KV, G, R>, dim3(p.kv_heads, p.target_parts, groups), dim3(kAttentionWarps * 32), 0,
                          stream, pdl, p);
 }
 
-// Two query vectors per block where the head ratio allows it: measured on the 12B verify pass, four
-// (both rows of a pair of heads in one block) halve the blocks but double each warp's serial work
-// and came out 1 % slower per cycle.
-template <typename KV>
-static int launch_attention_typed(const AttentionParams& p, cudaStream_t stream, bool pdl) {
+template <int G, int R>
+static int launch_attention_mma_instance(const AttentionParams& params, cudaStream_t stream, bool pdl) {
+    AttentionParams p = params;
+    const uint32_t groups = (p.rows + R - 1u) / R;
+    p.target_parts = attention_target_parts(p, groups, 1u);
+    return launch_kernel(attention_mma_kernel<G, R>, dim3(p.kv_heads, p.target_parts, groups), dim3(kAttentionMmaWarps * 32), 0,
+                         stream, pdl, p);
+}
+
+// F32 cache.  Two query vectors per block where the head ratio allows it: measured on the 12B
+// verify pass, four (both rows of a pair of heads in one block) halve the blocks but double each
+// warp's serial work and came out 1 % slower per cycle.
+static int launch_attention_f32(const AttentionParams& p, cudaStream_t stream, bool pdl) {
     const uint32_t group = p.heads / p.kv_heads;
     if (group == 1u) {
-        if (p.rows >= 2u) return launch_attention_instance<KV, 1, 2>(p, stream, pdl);
-        return launch_attention_instance<KV, 1, 1>(p, stream, pdl);
+        if (p.rows >= 2u) return launch_attention_instance<float, 1, 2>(p, stream, pdl);
+        return launch_attention_instance<float, 1, 1>(p, stream, pdl);
     }
-    if (group == 2u) return launch_attention_instance<KV, 2, 1>(p, stream, pdl);
-    if (group == 4u) return launch_attention_instance<KV, 4, 1>(p, stream, pdl);
+    if (group == 2u) return launch_attention_instance<float, 2, 1>(p, stream, pdl);
+    if (group == 4u) return launch_attention_instance<float, 4, 1>(p, stream, pdl);
+    return fail(GF_ERR_INVALID, "attention: query/KV head ratio %u unsupported (1, 2, 4)", group);
+}
+
+// Binary16 cache: the tensor-core kernel, with as many rows per block as four query vectors allow.
+static int launch_attention_f16(const AttentionParams& p, cudaStream_t stream, bool pdl) {
+    const uint32_t group = p.heads / p.kv_heads;
+    if (group == 1u) {
+        if (p.rows >= 3u) return launch_attention_mma_instance<1, 4>(p, stream, pdl);
+        if (p.rows == 2u) return launch_attention_mma_instance<1, 2>(p, stream, pdl);
+        return launch_attention_mma_instance<1, 1>(p, stream, pdl);
+    }
+    if (group == 2u) {
+        if (p.rows >= 2u) return launch_attention_mma_instance<2, 2>(p, stream, pdl);
+        return launch_attention_mma_instance<2, 1>(p, stream, pdl);
+    }
+    if (group == 4u) return launch_attention_mma_instance<4, 1>(p, stream, pdl);
     return fail(GF_ERR_INVALID, "attention: query/KV head ratio %u unsupported (1, 2, 4)", group);
 }
 
 int launch_attention(const AttentionParams& p, cudaStream_t stream, bool pdl) {
     if (p.head_dim != 256u) return fail(GF_ERR_INVALID, "attention: head_dim must be 256 (got %u)", p.head_dim);
     if (p.heads % p.kv_heads) return fail(GF_ERR_INVALID, "attention: heads %u not a multiple of kv heads %u", p.heads, p.kv_heads);
-    return p.kv_f16 ? launch_attention_typed<__half>(p, stream, pdl) : launch_attention_typed<float>(p, stream, pdl);
+    return p.kv_f16 ? launch_attention_f16(p, stream, pdl) : launch_attention_f32(p, stream, pdl);
 }
 
 int launch_geglu(const float* gate, const float* up, float* out, uint64_t count, cudaStream_t stream, bool pdl) {
