@@ -38,6 +38,8 @@ enum GemvPrologue : uint32_t {
     kProloguePlain = 0,      // xs = in
     kPrologueNorm = 1,       // xs = rmsnorm(in; gamma1)
     kPrologueAddNorm = 2,    // r = residual + rmsnorm(in; gamma0) -> residual_out;  xs = rmsnorm(r; gamma1)
+                             // (`residual` is read before the dependency wait: a launch that directly follows its
+                             //  writer under programmatic dependent launch must not be given it)
     kPrologueGeglu = 3,      // xs = gelu_tanh(in) * residual
 };
 
@@ -496,41 +498,70 @@ __device__ __forceinline__ void quantize_piece(const GemvStage& st, uint32_t r, 
     }
 }
 
+// What the register-resident prologue can read before the launch ahead has finished: the norm
+// weights, and for the residual prologue the residual rows, which were written two or more
+// launches back (the block schedule never lets the launch directly ahead write them).
+template <int ROWS>
+struct GemvEarly {
+    float res[ROWS][8], g0[8], g1[8];
+    bool cached;
+};
+
+// Whether the prologue keeps a row in registers: the norms of prologues 1 and 2 with at most one
+// 8-element piece per thread (K <= 8 * block size) and a slice that starts on a 256-element boundary.
+template <int ROWS>
+__device__ __forceinline__ bool gemv_prologue_cached(const GemvParams& p, uint32_t first) {
+    const bool norms = p.prologue == kPrologueNorm || p.prologue == kPrologueAddNorm;
+    return ROWS <= 4 && norms && p.k / 8u <= blockDim.x && (first & 255u) == 0u;
+}
+
+template <int ROWS>
+__device__ __forceinline__ void stage_early(const GemvParams& p, uint32_t first, GemvEarly<ROWS>& early) {
+    early.cached = gemv_prologue_cached<ROWS>(p, first);
+    if (!early.cached) return;
+    const uint32_t piece = threadIdx.x, o = piece * 8u;
+#pragma unroll
+    for (int i = 0; i < 8; ++i) { early.g0[i] = 0.0f; early.g1[i] = 0.0f; }
+#pragma unroll
+    for (int r = 0; r < ROWS; ++r)
+#pragma unroll
+        for (int i = 0; i < 8; ++i) early.res[r][i] = 0.0f;
+    if (piece >= p.k / 8u) return;
+    if (p.prologue == kPrologueAddNorm) {
+        load8f(p.gamma0 + o, early.g0);
+#pragma unroll
+        for (int r = 0; r < ROWS; ++r)
+            if ((uint32_t)r < p.active_rows) load8f(p.residual + (size_t)r * p.k + o, early.res[r]);
+    }
+    load8f(p.gamma1 + o, early.g1);
+}
+
 // Produces this CTA's K slice [first, first + count) of the activation rows in shared memory.
 // The RMS norms of prologues 1 and 2 need the whole row, so every CTA recomputes them from global
-// memory (a few tens of KB out of L2).  When a row has at most one 8-element piece per thread
-// (K <= 8 * block size) and the slice starts on a 256-element boundary, everything a thread needs
-// is loaded once, up front, and kept in registers through both norms; otherwise the row is
-// re-read for each pass.
+// memory (a few tens of KB out of L2).  In the register-resident case everything a thread needs
+// of the launch ahead's output is loaded once and kept in registers through both norms (the rest
+// came in with stage_early); otherwise the row is re-read for each pass.
 template <int ROWS>
 __device__ __forceinline__ void stage_activations(const GemvParams& p, uint32_t first, uint32_t count,
-                                                  const GemvStage& st, float* scratch) {
+                                                  const GemvStage& st, float* scratch, GemvEarly<ROWS>& early) {
     const bool norms = p.prologue == kPrologueNorm || p.prologue == kPrologueAddNorm;
     const uint32_t row_pieces = p.k / 8u;
-    if (ROWS <= 4 && norms && row_pieces <= blockDim.x && (first & 255u) == 0u) {
+    if (early.cached) {
         const uint32_t piece = threadIdx.x;
         const bool live = piece < row_pieces;
         const uint32_t o = piece * 8u;
-        float x[ROWS][8], res[ROWS][8], g0[8], g1[8];
-#pragma unroll
-        for (int i = 0; i < 8; ++i) { g0[i] = 0.0f; g1[i] = 0.0f; }
+        float x[ROWS][8];
+        float (&res)[ROWS][8] = early.res;
+        float (&g0)[8] = early.g0;
+        float (&g1)[8] = early.g1;
 #pragma unroll
         for (int r = 0; r < ROWS; ++r)
 #pragma unroll
-            for (int i = 0; i < 8; ++i) { x[r][i] = 0.0f; res[r][i] = 0.0f; }
+            for (int i = 0; i < 8; ++i) x[r][i] = 0.0f;
         if (live) {
-#pragma unroll
-            // What the first reduction needs goes first.
 #pragma unroll
             for (int r = 0; r < ROWS; ++r)
                 if ((uint32_t)r < p.active_rows) load8f(p.in + (size_t)r * p.k + o, x[r]);
-            if (p.prologue == kPrologueAddNorm) {
-                load8f(p.gamma0 + o, g0);
-#pragma unroll
-                for (int r = 0; r < ROWS; ++r)
-                    if ((uint32_t)r < p.active_rows) load8f(p.residual + (size_t)r * p.k + o, res[r]);
-            }
-            load8f(p.gamma1 + o, g1);
         }
         float ss[ROWS];
 #pragma unroll
@@ -791,9 +822,12 @@ __global__ void __launch_bounds__(kGemvWarps * 32, 1) gemv_kernel(const __grid_c
     if (lane == 0)
         for (int j = 0; j < kGemvSlots; ++j) issue_next();
 
+    GemvEarly<ROWS> early_inputs;
+    stage_early<ROWS>(p, first_unit * p.unit_elems, early_inputs);
+
     pdl_wait();
     const GemvStage stage{frags, sums, block_scales, &bad_rows, padded};
-    stage_activations<ROWS>(p, first_unit * p.unit_elems, chunk_count * p.unit_elems, stage, scratch);
+    stage_activations<ROWS>(p, first_unit * p.unit_elems, chunk_count * p.unit_elems, stage, scratch, early_inputs);
     __syncthreads();
     pdl_launch_dependents();
 
