@@ -42,7 +42,8 @@ int gemv_plan(const GemvLaunch& launch, GemvPlan& plan) {
     if (limit == 0) return fail(GF_ERR_INVALID, "gf_matmul: no decomposition fits");
     const uint32_t slots = (uint32_t)sm_count();           // one CTA per SM
     // Critical path of a warp, in pair rows: rounds x (units per item + per-item overhead); the
-    // split-K hand-over costs about one more.  Ties go to fewer chunks.
+    // split-K hand-over (fence, arrival count, re-read of the partial sums) costs about four more.
+    // Ties go to fewer chunks.
     double best = 1e30;
     plan.chunks = 0;
     for (uint32_t chunks = 1; chunks <= 64u && chunks <= plan.units && chunks <= slots; ++chunks) {
@@ -52,7 +53,7 @@ int gemv_plan(const GemvLaunch& launch, GemvPlan& plan) {
         const uint32_t group_ctas = slots / chunks;
         const uint32_t group_warps = group_ctas * kGemvWarps;
         const uint32_t rounds = (plan.total_pairs + group_warps - 1u) / group_warps;
-        const double cost = (double)rounds * ((double)chunk_units + 2.0 + (chunks > 1u ? 1.0 : 0.0));
+        const double cost = (double)rounds * ((double)chunk_units + 2.0) + (chunks > 1u ? 4.0 : 0.0);
         if (cost < best - 1e-9) {
             best = cost;
             plan.chunks = chunks;
