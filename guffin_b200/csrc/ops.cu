@@ -216,25 +216,35 @@ __device__ __forceinline__ void attention_finish(const AttentionParams& p, const
                                                  uint32_t first_row, uint32_t live_rows, float (&warp_m)[W][G * R],
                                                  float (&warp_l)[W][G * R], float (&warp_acc)[W][G * R][256], uint32_t& arrival) {
     constexpr int Q = G * R;
+    __shared__ float factor[W][Q], block_m[Q], block_l[Q];
+    __syncthreads();
+    // Each warp's weight in the block's result, once per (warp, query): warp 0, lane = query.
+    if (threadIdx.x < live_rows * (uint32_t)G) {
+        const uint32_t qi = threadIdx.x;
+        float mm = -INFINITY;
+        for (int w = 0; w < W; ++w) mm = fmaxf(mm, warp_m[w][qi]);
+        float ll = 0.0f;
+        for (int w = 0; w < W; ++w) {
+            const float f = warp_l[w][qi] == 0.0f ? 0.0f : expf(warp_m[w][qi] - mm);
+            factor[w][qi] = f;
+            ll = fmaf(warp_l[w][qi], f, ll);
+        }
+        block_m[qi] = mm;
+        block_l[qi] = ll;
+    }
     __syncthreads();
     for (uint32_t idx = threadIdx.x; idx < live_rows * (uint32_t)G * 256u; idx += blockDim.x) {
         const uint32_t qi = idx / 256u, d = idx % 256u;
-        float mm = -INFINITY;
-        for (int w = 0; w < W; ++w) mm = fmaxf(mm, warp_m[w][qi]);
-        float a = 0.0f, ll = 0.0f;
-        for (int w = 0; w < W; ++w) {
-            if (warp_l[w][qi] == 0.0f) continue;
-            const float f = expf(warp_m[w][qi] - mm);
-            a = fmaf(warp_acc[w][qi][d], f, a);
-            ll = fmaf(warp_l[w][qi], f, ll);
-        }
+        float a = 0.0f;
+#pragma unroll
+        for (int w = 0; w < W; ++w) a = fmaf(warp_acc[w][qi][d], factor[w][qi], a);
         const uint32_t row = first_row + qi / G, head = kvh * G + qi % G;
         if (span.parts == 1u) {
-            p.out[((size_t)row * p.heads + head) * 256u + d] = a / ll;
+            p.out[((size_t)row * p.heads + head) * 256u + d] = a / block_l[qi];
         } else {
             const size_t slot = ((size_t)row * p.heads + head) * kMaxAttentionPartitions + part;
             p.partial_out[slot * 256u + d] = a;
-            if (d == 0) { p.partial_ml[slot * 2u] = mm; p.partial_ml[slot * 2u + 1u] = ll; }
+            if (d == 0) { p.partial_ml[slot * 2u] = block_m[qi]; p.partial_ml[slot * 2u + 1u] = block_l[qi]; }
         }
     }
     if (span.parts == 1u) return;
@@ -567,15 +577,18 @@ __global__ void __launch_bounds__(kAttentionMmaWarps * 32) attention_mma_kernel(
 #pragma unroll
     for (int i = 0; i < 16; ++i) { acc[i][0] = 0.0f; acc[i][1] = 0.0f; acc[i][2] = 0.0f; acc[i][3] = 0.0f; }
     for (; tile < tiles; tile += step) {
-        float s4[4] = {0.0f, 0.0f, 0.0f, 0.0f};
+        // Two accumulators (even and odd k-steps) halve the chain of dependent products.
+        float s4[4] = {0.0f, 0.0f, 0.0f, 0.0f}, s4odd[4] = {0.0f, 0.0f, 0.0f, 0.0f};
 #pragma unroll
         for (int c = 0; c < 8; ++c)
 #pragma unroll
             for (int e = 0; e < 2; ++e) {
                 const uint2 b = q_frag[2 * c + e][lane];
-                mma_f16_k16(s4, word_of(kraw[0][c], 2 * e), word_of(kraw[1][c], 2 * e), word_of(kraw[0][c], 2 * e + 1),
+                mma_f16_k16(e ? s4odd : s4, word_of(kraw[0][c], 2 * e), word_of(kraw[1][c], 2 * e), word_of(kraw[0][c], 2 * e + 1),
                             word_of(kraw[1][c], 2 * e + 1), b.x, b.y);
             }
+#pragma unroll
+        for (int i = 0; i < 4; ++i) s4[i] += s4odd[i];
         const bool more = tile + step < tiles;
         if (more) fetch_k(tile + step);
         // Scores of rows g and g + 8 against query t: rounding column plus left-over column.
