@@ -360,15 +360,18 @@ __global__ void __launch_bounds__(kAttentionWarps * 32) attention_kernel(Attenti
     }
     const uint32_t quads = (span.count + 3u) / 4u, step = span.parts * kAttentionWarps;
     KvRaw<KV> kraw[4], vraw[4];
-    auto fetch = [&](uint32_t quad) {
+    // `which`: 0 = every row of the quad, 1 = only rows in the ring, 2 = only private rows.
+    auto fetch = [&](uint32_t quad, int which) {
 #pragma unroll
         for (int t = 0; t < 4; ++t) {
             const uint32_t position = span.first + min(quad * 4u + t, span.count - 1u);
             const KV *kp, *vp;
             if (position < span.base) {
+                if (which == 2) continue;
                 const size_t slot = ((size_t)(position & p.ring_mask)) * kv_width + kvh * 256u + lane * 8u;
                 kp = ring_k + slot; vp = ring_v + slot;
             } else {
+                if (which == 1) continue;
                 const size_t slot = (size_t)(position - span.base) * kv_width + kvh * 256u + lane * 8u;
                 kp = priv_k + slot; vp = priv_v + slot;
             }
@@ -377,8 +380,7 @@ __global__ void __launch_bounds__(kAttentionWarps * 32) attention_kernel(Attenti
         }
     };
     uint32_t quad = part * kAttentionWarps + warp;
-    const bool early = span.first + quad * 4u + 3u < span.base;
-    if (early) fetch(quad);
+    if (quad < quads) fetch(quad, 1);
     pdl_wait();
     pdl_launch_dependents();
     float q[Q][8];
@@ -388,7 +390,7 @@ __global__ void __launch_bounds__(kAttentionWarps * 32) attention_kernel(Attenti
         const float* qp = p.q + ((size_t)row * p.heads + kvh * G + qi % G) * 256u + lane * 8u;
         load8(qp, q[qi]);
     }
-    if (!early && quad < quads) fetch(quad);
+    if (quad < quads) fetch(quad, 2);
     for (; quad < quads; quad += step) {
         float kf[4][8], vf[4][8];
         uint32_t position[4];
@@ -398,7 +400,7 @@ __global__ void __launch_bounds__(kAttentionWarps * 32) attention_kernel(Attenti
             widen(kraw[t], kf[t]);
             widen(vraw[t], vf[t]);
         }
-        if (quad + step < quads) fetch(quad + step);
+        if (quad + step < quads) fetch(quad + step, 0);
         // Partial dot products (token t, query qi) -> column t*Q+qi, reduced across the warp eight at a time.
 #pragma unroll
         for (int half = 0; half < (4 * Q + 7) / 8; ++half) {
@@ -520,32 +522,35 @@ __global__ void __launch_bounds__(kAttentionMmaWarps * 32) attention_mma_kernel(
     const uint32_t my_position = span.base + first_row + t / G;
     const uint32_t low = my_live ? attention_window_start(my_position, p.window) : 1u, high = my_live ? my_position : 0u;
 
-    auto row_of = [&](uint32_t token, const __half* ring, const __half* priv) -> const __half* {
+    // A cached row's address, or null when `which` (0 = every row, 1 = only rows in the ring, 2 =
+    // only private rows) leaves it out.
+    auto row_of = [&](uint32_t token, const __half* ring, const __half* priv, int which) -> const __half* {
         const uint32_t position = span.first + min(token, span.count - 1u);
-        return position < span.base ? ring + (size_t)(position & p.ring_mask) * kv_width + kvh * 256u
-                                    : priv + (size_t)(position - span.base) * kv_width + kvh * 256u;
+        if (position < span.base) return which == 2 ? nullptr : ring + (size_t)(position & p.ring_mask) * kv_width + kvh * 256u;
+        return which == 1 ? nullptr : priv + (size_t)(position - span.base) * kv_width + kvh * 256u;
     };
     uint4 kraw[2][8], vraw[4][4];
-    auto fetch_k = [&](uint32_t tile) {
+    auto fetch_k = [&](uint32_t tile, int which) {
 #pragma unroll
         for (int h = 0; h < 2; ++h) {
-            const __half* src = row_of(tile * 16u + g + 8u * h, ring_k, priv_k) + 8u * t;
+            const __half* src = row_of(tile * 16u + g + 8u * h, ring_k, priv_k, which);
+            if (!src) continue;
 #pragma unroll
-            for (int c = 0; c < 8; ++c) kraw[h][c] = *reinterpret_cast<const uint4*>(src + 32 * c);
+            for (int c = 0; c < 8; ++c) kraw[h][c] = *reinterpret_cast<const uint4*>(src + 8u * t + 32 * c);
         }
     };
-    auto fetch_v = [&](uint32_t tile) {
+    auto fetch_v = [&](uint32_t tile, int which) {
 #pragma unroll
         for (int u = 0; u < 4; ++u) {
-            const __half* src = row_of(tile * 16u + 2u * t + (u & 1) + 8u * (u >> 1), ring_v, priv_v) + 8u * g;
+            const __half* src = row_of(tile * 16u + 2u * t + (u & 1) + 8u * (u >> 1), ring_v, priv_v, which);
+            if (!src) continue;
 #pragma unroll
-            for (int J = 0; J < 4; ++J) vraw[u][J] = *reinterpret_cast<const uint4*>(src + 64 * J);
+            for (int J = 0; J < 4; ++J) vraw[u][J] = *reinterpret_cast<const uint4*>(src + 8u * g + 64 * J);
         }
     };
     const uint32_t tiles = (span.count + 15u) / 16u, step = span.parts * W;
     uint32_t tile = part * W + warp;
-    const bool early = span.first + tile * 16u + 15u < span.base;
-    if (early) { fetch_k(tile); fetch_v(tile); }
+    if (tile < tiles) { fetch_k(tile, 1); fetch_v(tile, 1); }
     pdl_wait();
     pdl_launch_dependents();
     // B registers of the scores: lane (g, t) holds, of column g (query g / 2, rounding or left-over),
@@ -570,7 +575,7 @@ __global__ void __launch_bounds__(kAttentionMmaWarps * 32) attention_mma_kernel(
         }
     }
     __syncthreads();
-    if (!early && tile < tiles) { fetch_k(tile); fetch_v(tile); }
+    if (tile < tiles) { fetch_k(tile, 2); fetch_v(tile, 2); }
 
     float m_run = -INFINITY, l_run = 0.0f;      // of query t, over this lane's rows g and g + 8 of every tile
     float acc[16][4];
@@ -590,7 +595,7 @@ __global__ void __launch_bounds__(kAttentionMmaWarps * 32) attention_mma_kernel(
 #pragma unroll
         for (int i = 0; i < 4; ++i) s4[i] += s4odd[i];
         const bool more = tile + step < tiles;
-        if (more) fetch_k(tile + step);
+        if (more) fetch_k(tile + step, 0);
         // Scores of rows g and g + 8 against query t: rounding column plus left-over column.
         float s0 = s4[0] + s4[1], s1 = s4[2] + s4[3];
         if (p.softcap > 0.0f) { s0 = tanhf(s0 / p.softcap) * p.softcap; s1 = tanhf(s1 / p.softcap) * p.softcap; }
@@ -633,7 +638,7 @@ __global__ void __launch_bounds__(kAttentionMmaWarps * 32) attention_mma_kernel(
                             __byte_perm(word_of(vraw[2][J], wi), word_of(vraw[3][J], wi), sel),
                             __byte_perm(word_of(vraw[2][J], 2 + wi), word_of(vraw[3][J], 2 + wi), sel), b0, b1);
             }
-        if (more) fetch_v(tile + step);
+        if (more) fetch_v(tile + step, 0);
     }
     // Sum of the weights over the eight row pairs; then the warp's state goes to shared memory.
     l_run += __shfl_xor_sync(0xffffffffu, l_run, 4);
