@@ -862,6 +862,11 @@ int gf_attention(const float* q_dev, const void* ring_k_dev, const void* ring_v_
     if (!q_dev || !ring_k_dev || !ring_v_dev || !private_k_dev || !private_v_dev || !out_dev || !workspace_dev
         || !base_position_dev || rows == 0 || rows > GF_MAX_ROWS || ring_rows == 0 || (ring_rows & (ring_rows - 1u)))
         return fail(GF_ERR_INVALID, "gf_attention: bad arguments (ring rows must be a power of two)");
+    // Queries, cache rows, outputs and partial results move as 16-byte vectors.
+    const uintptr_t pointers = reinterpret_cast<uintptr_t>(q_dev) | reinterpret_cast<uintptr_t>(ring_k_dev) | reinterpret_cast<uintptr_t>(ring_v_dev)
+        | reinterpret_cast<uintptr_t>(private_k_dev) | reinterpret_cast<uintptr_t>(private_v_dev) | reinterpret_cast<uintptr_t>(out_dev)
+        | reinterpret_cast<uintptr_t>(workspace_dev);
+    if (pointers & 15u) return fail(GF_ERR_INVALID, "gf_attention: device pointers must be 16-byte aligned");
     AttentionParams p;
     p.q = q_dev; p.ring_k = ring_k_dev; p.ring_v = ring_v_dev; p.private_k = private_k_dev; p.private_v = private_v_dev;
     p.out = out_dev;

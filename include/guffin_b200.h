@@ -144,7 +144,8 @@ GF_API int gf_qk_norm_rope_store(const float* raw_q_dev, const float* raw_k_dev,
 /* encode_verifier_attention (metal_command_context.hpp:245-268; kernels
  * metal_kernels.mm:3070-3382): grouped-query attention of rows 0..rows-1 at positions base+row
  * over the committed ring rows inside each row's window followed by the private rows of its
- * chain ancestors, itself included.  window = 0 means a global layer.  head_dim must be 256. */
+ * chain ancestors, itself included.  window = 0 means a global layer.  head_dim must be 256;
+ * every device pointer must be 16-byte aligned. */
 GF_API size_t gf_attention_workspace_bytes(uint32_t rows, uint32_t heads);
 GF_API int gf_attention(const float* q_dev, const void* ring_k_dev, const void* ring_v_dev,
                         const void* private_k_dev, const void* private_v_dev, float* out_dev,

@@ -152,6 +152,20 @@ def test_attention_global_local_and_ring_wrap(gf, gm, oracle, kv_f16):
     _attention_case(gf, oracle, base=5000, rows=2, window=0, ring_rows=8192, heads=16, kv_heads=8, kv_f16=kv_f16, softcap=0.0, seed=10)
 
 
+def test_attention_rejects_unaligned_pointers(gf, gm):
+    """The kernels move 16-byte vectors; a pointer off that boundary is an argument error, not a launch."""
+    L = gf.load()
+    q = dev(gf, np.zeros((1, 4 * 256 + 4), np.float32))
+    ring = [dev(gf, np.zeros((16, 512), np.float32)) for _ in range(2)]
+    private = [dev(gf, np.zeros((1, 512), np.float32)) for _ in range(2)]
+    out = gf.DeviceBuffer(4 * 256 * 4)
+    ws = gf.DeviceBuffer(L.gf_attention_workspace_bytes(1, 4))
+    pos = dev(gf, np.array([3], np.uint32))
+    with pytest.raises(gf.GuffinError):
+        gf.check(L.gf_attention(q.ptr + 4, ring[0].ptr, ring[1].ptr, private[0].ptr, private[1].ptr, out.ptr, ws.ptr, pos.ptr,
+                                1, 4, 2, 256, 16, 0, 0.0625, 0.0, 0, None))
+
+
 def test_attention_matches_reference_fixture(gf, gm):
     """The reference's causal_grouped_attention_* + softmax composition, stored by make_golden."""
     want, d = np.load(golden.HERE / "ref_ops.npz"), golden.ops_inputs()
