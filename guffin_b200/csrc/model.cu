@@ -543,12 +543,15 @@ int Model::status_word(uint32_t* out) {
 }
 
 size_t Model::kv_bytes_per_pass(uint32_t rows) const {
-    // Cached rows one pass reads: every committed row inside each layer's window, K and V.
+    // Cached rows one pass has to read: every committed row inside each layer's window, K and V,
+    // once -- the rows of a pass look at the same cache (the reference counts it the same way,
+    // docs/archive/DEVELOPMENT_HISTORY.md: 8 global x context + 40 local x window rows of 8 KB).
+    if (rows == 0) return 0;
     const size_t row_bytes = (size_t)config_.kv_heads * config_.head_dim * (config_.kv_f16 ? 2 : 4) * 2;
     size_t total = 0;
     for (const LayerCache& cache : caches_) {
         const uint32_t seen = cache.window ? std::min(position_, cache.window) : position_;
-        total += (size_t)seen * row_bytes * rows;
+        total += (size_t)seen * row_bytes;
     }
     return total;
 }

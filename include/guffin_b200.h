@@ -248,6 +248,8 @@ GF_API void* gf_model_stream(gf_model* model);
 GF_API uint32_t* gf_model_tokens_dev(gf_model* model);
 GF_API float* gf_model_logits_dev(gf_model* model);
 GF_API size_t gf_model_weight_bytes(const gf_model* model, int native);
+/* K and V bytes one pass has to read at the current position: the committed rows inside every
+ * layer's window, once (the rows of a pass share the cache); 0 for rows = 0. */
 GF_API size_t gf_model_kv_bytes_per_pass(const gf_model* model, uint32_t rows);
 GF_API uint32_t gf_model_kernel_launches(const gf_model* model);
 GF_API int gf_model_use_graph(gf_model* model, int enable);
