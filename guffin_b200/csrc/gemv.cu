@@ -50,6 +50,7 @@ int gemv_plan(const GemvLaunch& launch, GemvPlan& plan) {
         const uint32_t chunk_units = (plan.units + chunks - 1u) / chunks;
         if ((chunks - 1u) * chunk_units >= plan.units) continue;          // an empty last chunk
         if (chunk_units > limit) continue;
+        if (launch.prologue == kPrologueMerge && (chunk_units * plan.unit_elems) % 256u) continue;   // slices start on head boundaries
         const uint32_t group_ctas = slots / chunks;
         const uint32_t group_warps = group_ctas * kGemvWarps;
         const uint32_t rounds = (plan.total_pairs + group_warps - 1u) / group_warps;
@@ -116,7 +117,8 @@ int gemv_launch(const GemvLaunch& launch, uint32_t* counters, float* partial, si
         return fail(GF_ERR_INVALID, "gf_matmul: activation, residual and norm-weight pointers must be 16-byte aligned");
     if ((launch.prologue == kPrologueNorm && !launch.gamma1)
         || (launch.prologue == kPrologueAddNorm && (!launch.gamma0 || !launch.gamma1 || !launch.residual || !launch.residual_out))
-        || (launch.prologue == kPrologueGeglu && !launch.residual) || launch.prologue > kPrologueGeglu)
+        || (launch.prologue == kPrologueGeglu && !launch.residual)
+        || (launch.prologue == kPrologueMerge && (!launch.residual || launch.k % 256u)) || launch.prologue > kPrologueMerge)
         return fail(GF_ERR_INVALID, "gf_matmul: prologue operands missing");
     GemvParams p = {};
     uint32_t first = 0;

@@ -41,6 +41,8 @@ enum GemvPrologue : uint32_t {
                              // (`residual` is read before the dependency wait: a launch that directly follows its
                              //  writer under programmatic dependent launch must not be given it)
     kPrologueGeglu = 3,      // xs = gelu_tanh(in) * residual
+    kPrologueMerge = 4,      // xs = the attention output merged from partition results: `in` holds [row][head][32][256]
+                             // unnormalised outputs, `residual` the (maximum, sum) pair of every slot (empty: sum 0)
 };
 
 struct GemvMatrix {
@@ -536,6 +538,42 @@ __device__ __forceinline__ void stage_early(const GemvParams& p, uint32_t first,
     load8f(p.gamma1 + o, early.g1);
 }
 
+// Prologue kPrologueMerge for one 256-element block (one attention head) of row r: lane l first
+// weighs partition l from its (maximum, sum) pair, then merges its own eight dimensions over the
+// partitions that hold data, eight partitions' loads in flight at a time.  Whole warps only.
+__device__ __forceinline__ void merge_head_piece(const GemvParams& p, uint32_t r, uint32_t element, float (&v)[8]) {
+    const uint32_t lane = threadIdx.x & 31u, heads = p.k / 256u, head = element / 256u, d = element % 256u;
+    const size_t slot0 = ((size_t)r * heads + head) * 32u;
+    const float2 ml = __ldcg(reinterpret_cast<const float2*>(p.residual + (slot0 + lane) * 2u));
+    float top = ml.x;
+#pragma unroll
+    for (int offset = 16; offset > 0; offset >>= 1) top = fmaxf(top, __shfl_xor_sync(0xffffffffu, top, offset));
+    const float weight = ml.y != 0.0f ? expf(ml.x - top) : 0.0f;
+    const float total = warp_sum(ml.y * weight);
+    const uint32_t filled = __ballot_sync(0xffffffffu, ml.y != 0.0f);
+    const float* src = p.in + slot0 * 256u + d;
+    float a[8];
+#pragma unroll
+    for (int i = 0; i < 8; ++i) a[i] = 0.0f;
+    for (uint32_t base = 0; base < 32u && (filled >> base) != 0u; base += 8u) {
+        float4 lo[8], hi[8];
+#pragma unroll
+        for (uint32_t j = 0; j < 8u; ++j) {
+            const bool has = (filled >> (base + j)) & 1u;
+            lo[j] = has ? __ldcg(reinterpret_cast<const float4*>(src + (size_t)(base + j) * 256u)) : make_float4(0.0f, 0.0f, 0.0f, 0.0f);
+            hi[j] = has ? __ldcg(reinterpret_cast<const float4*>(src + (size_t)(base + j) * 256u + 4u)) : make_float4(0.0f, 0.0f, 0.0f, 0.0f);
+        }
+#pragma unroll
+        for (uint32_t j = 0; j < 8u; ++j) {
+            const float f = __shfl_sync(0xffffffffu, weight, base + j);
+            a[0] = fmaf(lo[j].x, f, a[0]); a[1] = fmaf(lo[j].y, f, a[1]); a[2] = fmaf(lo[j].z, f, a[2]); a[3] = fmaf(lo[j].w, f, a[3]);
+            a[4] = fmaf(hi[j].x, f, a[4]); a[5] = fmaf(hi[j].y, f, a[5]); a[6] = fmaf(hi[j].z, f, a[6]); a[7] = fmaf(hi[j].w, f, a[7]);
+        }
+    }
+#pragma unroll
+    for (int i = 0; i < 8; ++i) v[i] = a[i] / total;
+}
+
 // Produces this CTA's K slice [first, first + count) of the activation rows in shared memory.
 // The RMS norms of prologues 1 and 2 need the whole row, so every CTA recomputes them from global
 // memory (a few tens of KB out of L2).  In the register-resident case everything a thread needs
@@ -634,7 +672,10 @@ __device__ __forceinline__ void stage_activations(const GemvParams& p, uint32_t 
         float v[8];
 #pragma unroll
         for (int i = 0; i < 8; ++i) v[i] = 0.0f;
-        if (o < count && r < p.active_rows) {
+        if (p.prologue == kPrologueMerge) {
+            // A warp holds one 256-element block of one row (slices start on head boundaries).
+            if ((o & ~255u) < count && r < p.active_rows) merge_head_piece(p, r, first + o, v);
+        } else if (o < count && r < p.active_rows) {
             const size_t gi = (size_t)r * p.k + first + o;
             const uint32_t c = first + o;
             float i0 = 1.0f, i1 = 1.0f;

@@ -218,10 +218,11 @@ int Model::finalize() {
     GF_TRY(device_alloc(allocations_, &logits_, (size_t)R * c.vocab));
     // Split-K workspace: the largest any launch of the schedule needs, for every row count.
     size_t ws = 256, counters = 256;
-    auto grow = [&](std::initializer_list<const PackedMatrix*> set) {
+    auto grow = [&](std::initializer_list<const PackedMatrix*> set, uint32_t prologue = kProloguePlain) {
         for (uint32_t rows = 1; rows <= R; ++rows) {
             GemvLaunch launch;
             launch.count = 0;
+            launch.prologue = prologue;              // the merge prologue narrows the planner's choice of K chunks
             for (const PackedMatrix* m : set) {
                 launch.matrices[launch.count++] = GemvMatrixDesc{m->dtype, m->data, logits_, m->n};
                 launch.k = m->k;
@@ -231,7 +232,7 @@ int Model::finalize() {
             counters = std::max(counters, gemv_counter_bytes(launch));
         }
     };
-    for (const LayerWeights& w : layers_) { grow({&w.q, &w.k, &w.v}); grow({&w.o}); grow({&w.gate, &w.up}); grow({&w.down}); }
+    for (const LayerWeights& w : layers_) { grow({&w.q, &w.k, &w.v}); grow({&w.o}); grow({&w.o}, kPrologueMerge); grow({&w.gate, &w.up}); grow({&w.down}); }
     grow({has_head_ ? &head_ : &token_embd_});
     uint8_t* bytes = nullptr;
     GF_TRY(device_alloc(allocations_, &bytes, ws)); matmul_ws_ = bytes; matmul_ws_bytes_ = ws;
@@ -289,7 +290,7 @@ int Model::run_gemv(GemvLaunch& launch, uint32_t rows) {
 // (gemma_target_runtime.cpp:28-219), with the small operators folded into the GEMV launches:
 //   QKV   <- prologue: [residual += norm(down; post_ffw)] ; norm(residual; attn_norm)
 //   rope/norm/store, attention
-//   O     <- plain
+//   O     <- prologue: merge of the attention partitions
 //   gate,up <- prologue: residual2 = residual + norm(O; post_attention) ; norm(residual2; ffn_norm)
 //   down  <- prologue: gelu_tanh(gate) * up
 // The next layer's QKV (or the head) applies the post-FFW norm and residual of this layer.
@@ -355,9 +356,10 @@ int Model::encode_blocks(uint32_t rows, uint32_t flags) {
         ap.base_position = state_dev_; ap.rows = rows; ap.heads = c.heads; ap.kv_heads = c.kv_heads; ap.head_dim = c.head_dim;
         ap.ring_mask = cache.ring_rows - 1u; ap.window = cache.window; ap.scale = c.attention_scale;
         ap.softcap = c.attn_softcap; ap.kv_f16 = c.kv_f16;
+        ap.defer_merge = 1u;                 // the O projection's prologue merges the partitions
         GF_TRY(launch_attention(ap, stream_, true));
         launches_ += 1;
-        o.in = attention_out_;
+        o.prologue = kPrologueMerge; o.in = ap.partial_out; o.residual = ap.partial_ml;
         GemvLaunch gu = gate_up_weights(l);
         GF_TRY(run_gemv(o, rows));
         gu.prologue = kPrologueAddNorm; gu.in = projected_; gu.residual = x; gu.gamma0 = w.post_attention_norm;

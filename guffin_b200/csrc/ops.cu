@@ -239,13 +239,25 @@ __device__ __forceinline__ void attention_finish(const AttentionParams& p, const
 #pragma unroll
         for (int w = 0; w < W; ++w) a = fmaf(warp_acc[w][qi][d], factor[w][qi], a);
         const uint32_t row = first_row + qi / G, head = kvh * G + qi % G;
-        if (span.parts == 1u) {
+        if (span.parts == 1u && !p.defer_merge) {
             p.out[((size_t)row * p.heads + head) * 256u + d] = a / block_l[qi];
         } else {
             const size_t slot = ((size_t)row * p.heads + head) * kMaxAttentionPartitions + part;
             p.partial_out[slot * 256u + d] = a;
             if (d == 0) { p.partial_ml[slot * 2u] = block_m[qi]; p.partial_ml[slot * 2u + 1u] = block_l[qi]; }
         }
+    }
+    if (p.defer_merge) {
+        // The consumer merges; it looks at all slots, so partition 0 marks the unused ones empty.
+        if (part == 0u)
+            for (uint32_t idx = threadIdx.x; idx < live_rows * (uint32_t)G * 32u; idx += blockDim.x) {
+                const uint32_t qi = idx >> 5, lane_part = idx & 31u;
+                if (lane_part < span.parts) continue;
+                const size_t slot = ((size_t)(first_row + qi / G) * p.heads + kvh * G + qi % G) * kMaxAttentionPartitions + lane_part;
+                p.partial_ml[slot * 2u] = -INFINITY;
+                p.partial_ml[slot * 2u + 1u] = 0.0f;
+            }
+        return;
     }
     if (span.parts == 1u) return;
     // The block that arrives last for this (row group, kv head) merges all partitions.

@@ -50,6 +50,10 @@ struct AttentionParams {
     uint32_t target_parts;     // partitions the launch has room for per (kv head, row group); set by launch_attention
     float scale, softcap;
     int kv_f16;
+    // 0: the block that arrives last merges the partitions into `out`.  1: every block parks its
+    // partial result and the consumer merges (the GEMV prologue kPrologueMerge); partition slots
+    // the launch did not fill are marked empty, `out` and `counters` are not touched.
+    uint32_t defer_merge = 0;
 };
 
 // Attention workspace: partial outputs, partial (max, sum) pairs, then the arrival counters.
