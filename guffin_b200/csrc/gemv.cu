@@ -63,7 +63,42 @@ int gemv_plan(const GemvLaunch& launch, GemvPlan& plan) {
         }
     }
     if (plan.chunks == 0) return fail(GF_ERR_INVALID, "gf_matmul: no decomposition fits K=%llu rows=%u", (unsigned long long)launch.k, launch.rows);
-    plan.smem = gemv_smem_layout(instance_rows(launch.rows), plan.chunk_units, plan.unit_elems, plan.slot_bytes).total;
+    plan.intra = 1;
+    plan.staged_units = plan.chunk_units;
+    // K split over the warps of one CTA instead: the partial sums then meet in shared memory, which
+    // costs about half a pair row, but every CTA stages the whole activation row, so it must fit beside
+    // the ring.  Not with the partition-merge prologue, whose cost grows with the staged slice.  Whether
+    // K is split this way, and where, is decided for the four-row instance, so that every row count
+    // adds the same partial sums in the same order: an instance too large for it (eight rows) takes
+    // the same chunks across CTAs.
+    const bool whole_row_fits = gemv_smem_layout(4u, plan.units, plan.unit_elems, plan.slot_bytes, true).total <= kGemvSmemLimit;
+    if (whole_row_fits && launch.prologue != kPrologueMerge) {
+        uint32_t inside_best = 0, units_best = 0;
+        for (uint32_t inside = 2; inside <= (uint32_t)kGemvWarps && inside <= plan.units; inside *= 2u) {
+            const uint32_t chunk_units = (plan.units + inside - 1u) / inside;
+            if ((inside - 1u) * chunk_units >= plan.units) continue;
+            const uint32_t pair_slots = (uint32_t)kGemvWarps / inside;
+            const uint32_t rounds = (plan.total_pairs + slots * pair_slots - 1u) / (slots * pair_slots);
+            const double cost = (double)rounds * ((double)chunk_units + 2.0) + 0.5;
+            if (cost < best - 1e-9) { best = cost; inside_best = inside; units_best = chunk_units; }
+        }
+        if (inside_best != 0u) {
+            const uint32_t pair_slots = (uint32_t)kGemvWarps / inside_best;
+            if (instance_rows(launch.rows) <= 4u) {
+                plan.chunks = 1;
+                plan.intra = inside_best;
+                plan.chunk_units = units_best;
+                plan.staged_units = plan.units;
+                plan.grid = std::min(slots, (plan.total_pairs + pair_slots - 1u) / pair_slots);
+            } else if (units_best <= limit && inside_best <= slots) {
+                plan.chunks = inside_best;
+                plan.chunk_units = units_best;
+                plan.staged_units = units_best;
+                plan.grid = slots / inside_best * inside_best;
+            }
+        }
+    }
+    plan.smem = gemv_smem_layout(instance_rows(launch.rows), plan.staged_units, plan.unit_elems, plan.slot_bytes, plan.intra > 1u).total;
     return GF_OK;
 }
 
@@ -141,6 +176,8 @@ int gemv_launch(const GemvLaunch& launch, uint32_t* counters, float* partial, si
     p.active_rows = launch.rows;
     p.chunks = plan.chunks;
     p.chunk_units = plan.chunk_units;
+    p.intra = plan.intra;
+    p.staged_units = plan.staged_units;
     p.slot_bytes = plan.slot_bytes;
     p.slot_units = plan.slot_units;
     p.prologue = launch.prologue;

@@ -56,7 +56,9 @@ struct GemvParams {
     uint32_t matrices, total_pairs;
     uint32_t k, units, unit_elems;
     uint32_t active_rows;                 // rows that exist; the kernel instance may be compiled for more
-    uint32_t chunks, chunk_units;
+    uint32_t chunks, chunk_units;         // K chunks spread over CTAs (hand-over through L2), K units per chunk
+    uint32_t intra, staged_units;         // K chunks spread over the warps of one CTA (1 = none; hand-over in shared
+                                          // memory, `chunks` is then 1); K units of the activation slice a CTA stages
     uint32_t slot_bytes, slot_units;      // ring slot size; pair rows (K units) copied and consumed per slot
     uint32_t prologue;
     const float *in, *residual, *gamma0, *gamma1;
@@ -94,16 +96,19 @@ __host__ __device__ constexpr uint32_t gemv_fragment_stride(uint32_t rows) { ret
 struct GemvSmemLayout {
     uint32_t frag_bytes, sums_bytes, scale_bytes, ring_bytes, total;
 };
+// Shared-memory meeting place of the warps that split K inside a CTA: [warp][row][16 columns] f32.
+__host__ __device__ constexpr uint32_t gemv_meeting_bytes(uint32_t rows) { return (uint32_t)kGemvWarps * rows * 16u * 4u; }
 
 __host__ __device__ inline GemvSmemLayout gemv_smem_layout(uint32_t rows, uint32_t chunk_units, uint32_t unit_elems,
-                                                           uint32_t slot_bytes) {
+                                                           uint32_t slot_bytes, bool meeting = false) {
     GemvSmemLayout s;
     const uint32_t slice = chunk_units * unit_elems, padded = (slice + 255u) & ~255u;
     s.frag_bytes = (padded / 32u) * gemv_fragment_stride(rows);
     s.sums_bytes = rows * (padded / 16u) * 4u;
     s.scale_bytes = ((rows * (padded / 256u) * 4u) + 15u) & ~15u;
     s.ring_bytes = (uint32_t)kGemvWarps * kGemvSlots * slot_bytes;
-    s.total = s.frag_bytes + s.sums_bytes + s.scale_bytes + s.ring_bytes + kGemvWarps * kGemvSlots * 8u + 64u;
+    s.total = s.frag_bytes + s.sums_bytes + s.scale_bytes + s.ring_bytes + kGemvWarps * kGemvSlots * 8u + 64u
+              + (meeting ? gemv_meeting_bytes(rows) : 0u);
     return s;
 }
 
@@ -805,25 +810,31 @@ __global__ void __launch_bounds__(kGemvWarps * 32, 1) gemv_kernel(const __grid_c
     extern __shared__ __align__(128) uint8_t smem[];
     __shared__ float scratch[2 * kGemvWarps * ROWS];
     __shared__ uint32_t bad_rows;
-    const GemvSmemLayout lay = gemv_smem_layout(ROWS, p.chunk_units, p.unit_elems, p.slot_bytes);
-    const uint32_t slice = p.chunk_units * p.unit_elems, padded = (slice + 255u) & ~255u;
+    const bool intra = p.intra > 1u;
+    const GemvSmemLayout lay = gemv_smem_layout(ROWS, p.staged_units, p.unit_elems, p.slot_bytes);
+    const uint32_t slice = p.staged_units * p.unit_elems, padded = (slice + 255u) & ~255u;
     uint8_t* frags = smem;
     float* sums = reinterpret_cast<float*>(smem + lay.frag_bytes);
     float* block_scales = reinterpret_cast<float*>(smem + lay.frag_bytes + lay.sums_bytes);
     uint8_t* ring_base = smem + lay.frag_bytes + lay.sums_bytes + lay.scale_bytes;
     uint64_t* bars = reinterpret_cast<uint64_t*>(ring_base + lay.ring_bytes);
+    float* meeting = reinterpret_cast<float*>(bars + kGemvWarps * kGemvSlots);      // only laid out when K is split inside the CTA
 
     const uint32_t warp = threadIdx.x >> 5, lane = threadIdx.x & 31u;
     uint8_t* ring = ring_base + warp * (kGemvSlots * p.slot_bytes);
     uint64_t* bar = bars + warp * kGemvSlots;
 
     // This CTA's K chunk and this warp's sequence of column pairs (over all matrices).
-    const uint32_t chunk = blockIdx.x % p.chunks;
-    const uint32_t group_ctas = gridDim.x / p.chunks;
+    // With K split inside the CTA, warp w takes K chunk w % intra of the column pairs of slot w / intra.
+    const uint32_t chunk = intra ? warp % p.intra : blockIdx.x % p.chunks;
+    const uint32_t group_ctas = intra ? gridDim.x : gridDim.x / p.chunks;
     const uint32_t first_unit = chunk * p.chunk_units;
     const uint32_t chunk_count = min(p.chunk_units, p.units - first_unit);
-    const uint32_t stride = group_ctas * kGemvWarps;
-    const uint32_t first_pair = (blockIdx.x / p.chunks) * kGemvWarps + warp;
+    const uint32_t pair_slots = intra ? (uint32_t)kGemvWarps / p.intra : (uint32_t)kGemvWarps;
+    const uint32_t pair_slot = intra ? warp / p.intra : warp;
+    const uint32_t stride = group_ctas * pair_slots;
+    const uint32_t first_pair = (intra ? blockIdx.x : blockIdx.x / p.chunks) * pair_slots + pair_slot;
+    const uint32_t unit_base = intra ? first_unit : 0u;          // of this warp's chunk inside the staged slice
     const uint32_t my_items = first_pair < p.total_pairs ? (p.total_pairs - first_pair + stride - 1u) / stride : 0u;
 
     auto matrix_of = [&](uint32_t pair) -> uint32_t {
@@ -864,11 +875,11 @@ __global__ void __launch_bounds__(kGemvWarps * 32, 1) gemv_kernel(const __grid_c
         for (int j = 0; j < kGemvSlots; ++j) issue_next();
 
     GemvEarly<ROWS> early_inputs;
-    stage_early<ROWS>(p, first_unit * p.unit_elems, early_inputs);
+    stage_early<ROWS>(p, intra ? 0u : first_unit * p.unit_elems, early_inputs);
 
     pdl_wait();
     const GemvStage stage{frags, sums, block_scales, &bad_rows, padded};
-    stage_activations<ROWS>(p, first_unit * p.unit_elems, chunk_count * p.unit_elems, stage, scratch, early_inputs);
+    stage_activations<ROWS>(p, intra ? 0u : first_unit * p.unit_elems, intra ? p.k : chunk_count * p.unit_elems, stage, scratch, early_inputs);
     __syncthreads();
     pdl_launch_dependents();
 
@@ -889,7 +900,7 @@ __global__ void __launch_bounds__(kGemvWarps * 32, 1) gemv_kernel(const __grid_c
     float maccA[ROWS], maccB[ROWS];
     bool failed = false;
     uint32_t slot = 0, phase = 0;
-    for (uint32_t item = 0; item < my_items && !failed; ++item) {
+    for (uint32_t item = 0; item < my_items && (!failed || intra); ++item) {
         const uint32_t pair = first_pair + item * stride;
         const GemvMatrix& mat = p.m[matrix_of(pair)];
         const uint32_t dtype = mat.dtype;
@@ -898,11 +909,11 @@ __global__ void __launch_bounds__(kGemvWarps * 32, 1) gemv_kernel(const __grid_c
 #pragma unroll
         for (int r = 0; r < ROWS; ++r) { maccA[r] = 0.0f; maccB[r] = 0.0f; }
         const uint32_t row_bytes = pair_row_bytes((int)dtype);
-        for (uint32_t u0 = 0; u0 < chunk_count; u0 += p.slot_units) {
+        for (uint32_t u0 = 0; u0 < chunk_count && !failed; u0 += p.slot_units) {
             if (!mbar_wait(&bar[slot], phase)) { failed = true; break; }
             const uint32_t count = min(p.slot_units, chunk_count - u0);
             for (uint32_t j = 0; j < count; ++j) {
-                const uint32_t u = u0 + j;
+                const uint32_t u = unit_base + u0 + j;
                 const uint8_t* row = ring + slot * p.slot_bytes + j * row_bytes;
                 float scales[NT];
                 if (dtype == GF_Q4_K) {
@@ -925,7 +936,7 @@ __global__ void __launch_bounds__(kGemvWarps * 32, 1) gemv_kernel(const __grid_c
             if (lane == 0) issue_next();
             if (++slot == (uint32_t)kGemvSlots) { slot = 0; phase ^= 1u; }
         }
-        if (failed) break;
+        if (failed && !intra) break;      // inside a CTA the other chunks' warps wait at the meeting barrier
         // Row r is the sum of B columns 4r .. 4r+3 (digit 0 first; held by quad lanes (n % 8) / 2 of
         // n-tile n / 8), minus the correction dot product of its column.
         const float offset = dtype == GF_Q4_K ? 1.0f : dtype == GF_Q6_K ? 32.0f : 0.0f;
@@ -949,6 +960,30 @@ __global__ void __launch_bounds__(kGemvWarps * 32, 1) gemv_kernel(const __grid_c
         }
         const uint32_t local_pair = pair - mat.first_pair;
         const uint32_t columnA = local_pair * 16u + L.g, columnB = columnA + 8u;
+        if (intra) {
+            // K split inside the CTA: the chunks' partial sums meet in shared memory; the warp of chunk 0
+            // adds them in chunk order and carries on as if it had computed the whole column pair.
+            float* mine = meeting + (size_t)warp * ROWS * 16u;
+#pragma unroll
+            for (int r = 0; r < ROWS; ++r)
+                if (L.t == (uint32_t)(r & 3)) { mine[r * 16 + L.g] = totalA[r]; mine[r * 16 + L.g + 8u] = totalB[r]; }
+            asm volatile("bar.sync %0, %1;" ::"r"(1u + pair_slot), "r"(p.intra * 32u) : "memory");
+            if (chunk == 0u) {
+#pragma unroll
+                for (int r = 0; r < ROWS; ++r)
+                    if (L.t == (uint32_t)(r & 3)) {
+                        float a = 0.0f, b = 0.0f;
+                        for (uint32_t c = 0; c < p.intra; ++c) {
+                            const float* theirs = meeting + (size_t)(warp + c) * ROWS * 16u;
+                            a += theirs[r * 16 + L.g];
+                            b += theirs[r * 16 + L.g + 8u];
+                        }
+                        totalA[r] = a; totalB[r] = b;
+                    }
+            }
+            asm volatile("bar.sync %0, %1;" ::"r"(1u + pair_slot), "r"(p.intra * 32u) : "memory");   // the meeting place is free again
+            if (chunk != 0u) continue;
+        }
         if (p.chunks == 1u) {
 #pragma unroll
             for (int r = 0; r < ROWS; ++r)
@@ -1021,7 +1056,7 @@ struct GemvLaunch {
         int kv_f16 = 0;
     } heads;
 };
-struct GemvPlan { uint32_t units, unit_elems, total_pairs, chunks, chunk_units, grid, smem, slot_bytes, slot_units; };
+struct GemvPlan { uint32_t units, unit_elems, total_pairs, chunks, chunk_units, grid, smem, slot_bytes, slot_units, intra, staged_units; };
 
 int gemv_plan(const GemvLaunch& launch, GemvPlan& plan);
 // Split-K scratch of one launch: `partial` bytes of sums, and one arrival counter per column pair.
