@@ -725,10 +725,23 @@ __device__ __forceinline__ void finish_head(const GemvParams& p, const GemvMatri
     const GemvParams::HeadEpilogue& e = p.heads;
     const uint32_t base = *e.base_position;
     const float* gamma = which == 0u ? e.q_norm : which == 1u ? e.k_norm : nullptr;
-    for (uint32_t r = 0; r < p.active_rows && r < (uint32_t)ROWS; ++r) {
-        const float* src = mat.out + (size_t)r * mat.n + head * 256u;
-        const float4 a = __ldcg(reinterpret_cast<const float4*>(src + 4u * lane));
-        const float4 b = __ldcg(reinterpret_cast<const float4*>(src + 128u + 4u * lane));
+    // The finished values of the first two rows are requested together (the verify pass has two).
+    const uint32_t rows = min(p.active_rows, (uint32_t)ROWS);
+    float4 early_a[2], early_b[2];
+#pragma unroll
+    for (uint32_t i = 0; i < 2u; ++i) {
+        const float* src = mat.out + (size_t)min(i, rows - 1u) * mat.n + head * 256u;
+        early_a[i] = __ldcg(reinterpret_cast<const float4*>(src + 4u * lane));
+        early_b[i] = __ldcg(reinterpret_cast<const float4*>(src + 128u + 4u * lane));
+    }
+    for (uint32_t r = 0; r < rows; ++r) {
+        float4 a, b;
+        if (r < 2u) { a = r == 0u ? early_a[0] : early_a[1]; b = r == 0u ? early_b[0] : early_b[1]; }
+        else {
+            const float* src = mat.out + (size_t)r * mat.n + head * 256u;
+            a = __ldcg(reinterpret_cast<const float4*>(src + 4u * lane));
+            b = __ldcg(reinterpret_cast<const float4*>(src + 128u + 4u * lane));
+        }
         float first[4] = {a.x, a.y, a.z, a.w}, second[4] = {b.x, b.y, b.z, b.w};
         if (which != 2u) {
             if (gamma) {
