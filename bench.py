@@ -4,16 +4,24 @@ decode (one drafted token, two-row verification, lossless acceptance), on synthe
 weights of those geometries.
 
     python bench.py [--gpus N] [--steps K] [--warmup W] [--impl ours|reference]
+    python bench.py --case matmul <dtype 8|12|14> <K> <N> <rows> [launches]
+    python bench.py --case attention <cached rows> <rows> <heads> <kv_heads> <window> <kv_f16 0|1> [launches]
 
 A "step" is one H1 cycle: drafter proposal -> two-row target pass -> candidate selection ->
 host acceptance -> publish / rollback.  Accept/reject control flow follows a seeded Bernoulli(0.7)
 schedule (random weights give no natural draft agreement) while the real acceptance law runs on
-the real logits and proposal law every cycle.  Each rank decodes its own independent stream
-(data parallel, no collective); the reported value is all ranks' tokens over the slowest
-rank's device time.
+the real logits and proposal law every cycle; tokens per cycle (1 + accepted) is therefore an
+assumption of the workload, `ms_per_step` is the measured quantity.  The device-timed loop and the
+end-to-end loop replay the same scheduled outcomes.  Each rank decodes its own independent stream
+(data parallel, no collective); the reported value is all ranks' tokens over the slowest rank's
+device time.
 
-`--impl reference` times the reference's CPU path for the same cycle (the CPU oracle's
-restatement of its scalar GEMV / block schedule, all host cores) on a bounded sample.
+`--impl reference` times the reference's own CPU matmul (its compiled sources, one call per
+column slice on every host core) on a bounded sample of the same cycle and scales it by
+multiply-add count; where the compiled reference is absent it times the CPU restatement instead.
+
+`--case` runs one small single-kernel case a few times through the C ABI: the command to put
+under a profiler.
 """
 from __future__ import annotations
 
@@ -35,9 +43,9 @@ TARGET, DRAFT = "gemma3-12b", "gemma3-270m"
 ACCEPT_P = 0.7
 PREFILL_ROWS = 8          # rows per prompt-ingestion pass (verification passes stay two rows wide)
 # dram__bytes_read.sum + dram__bytes_write.sum over the weight bytes of one captured GEMV launch
-# (profiles/gemv_kernel_q4k_k3840_n65536_rows2.md).
+# (profiles/weight_stream_kernel_q4k_k3840_n65536_rows2.md).
 TRAFFIC_PER_ALGORITHMIC_BYTE = (141.66 + 3.65) / 141.56
-SEEDS = dict(target=1201, draft=2701, prompt=31, sampler=41, schedule=7)
+SEEDS = dict(target=1201, draft=2701, prompt=31, sampler=41, schedule=7, shapes=17)
 
 
 def load_peaks():
@@ -122,6 +130,71 @@ def aggregate_streams(dist, tokens: float, tokens_e2e: float, device_ms: float, 
 
 # ----------------------------------------------------------------------------------------- ours
 
+L2_BYTES = 126 << 20
+# configs[0] and configs[1] of the workload list: single dequant-GEMV shapes, one and two rows.
+SHAPES = [("q4k_ffn_gate_15360x3840", 12, 3840, 15360), ("q6k_ffn_down_3840x15360", 14, 15360, 3840),
+          ("q80_drafter_2048x640", 8, 640, 2048), ("q80_drafter_640x2048", 8, 2048, 640),
+          ("q80_head_262144x640", 8, 640, 262144)]
+
+
+def shape_rooflines(lib, syn, peak: float) -> list:
+    """GB/s of weight bytes for each single-matrix shape at one and two rows: "isolated" = one
+    product per submission (median of 20, events around each), "sustained" = 40 products back to
+    back between one event pair.  Successive products read different copies of the matrix, more
+    of them than fit in L2, so every byte comes from HBM."""
+    L = lib.load()
+    rng = np.random.default_rng(SEEDS["shapes"])
+    out = []
+    for name, dtype, k, n in SHAPES:
+        native = syn.make_weight(rng, dtype, k, n)
+        first = lib.PackedWeight(dtype, k, n, native)
+        copies = max(2, -(-2 * L2_BYTES // first.nbytes) + 1)
+        pool = lib.DeviceBuffer(copies * first.nbytes)
+        for c in range(copies):
+            lib.check(L.gf_copy(pool.ptr + c * first.nbytes, first.packed.ptr, first.nbytes, None))
+        first.packed.free()
+        nbytes = syn.weight_bytes(dtype, k, n)
+        entry = {"shape": name, "weight_bytes": nbytes, "copies": copies}
+        for rows in (1, 2):
+            x = lib.DeviceBuffer.from_numpy(rng.standard_normal((rows, k)).astype(np.float32))
+            y = lib.DeviceBuffer(rows * n * 4)
+            ws_bytes = L.gf_matmul_workspace_bytes(dtype, rows, k, n)
+            ws = lib.DeviceBuffer(ws_bytes) if ws_bytes else None
+
+            def run(i):
+                lib.check(L.gf_matmul(dtype, pool.ptr + (i % copies) * first.nbytes, x.ptr, y.ptr, rows, k, n,
+                                      ws.ptr if ws else None, None))
+            for i in range(copies + 3):
+                run(i)
+            lib.check(L.gf_stream_synchronize(None))
+            isolated = []
+            for i in range(20):
+                e0, e1 = lib.Event(), lib.Event()
+                e0.record(None)
+                run(i)
+                e1.record(None)
+                e1.synchronize()
+                isolated.append(e0.elapsed_ms(e1))
+            e0, e1 = lib.Event(), lib.Event()
+            e0.record(None)
+            for i in range(40):
+                run(i)
+            e1.record(None)
+            e1.synchronize()
+            sustained = e0.elapsed_ms(e1) / 40
+            lib.check(L.gf_matmul_check(None))
+            iso = float(np.median(isolated))
+            entry[f"rows{rows}"] = {"isolated_us": iso * 1e3, "isolated_gbs": nbytes / iso / 1e6,
+                                    "sustained_us": sustained * 1e3, "sustained_gbs": nbytes / sustained / 1e6,
+                                    "sustained_frac": nbytes / sustained / 1e6 / peak}
+            for b in (x, y, ws):
+                if b:
+                    b.free()
+        pool.free()
+        out.append(entry)
+    return out
+
+
 def run_ours(args) -> dict:
     from guffin_b200 import engine as ge, lib, model as gm, synthetic as syn
     world, rank, local = distributed()
@@ -155,11 +228,17 @@ def run_ours(args) -> dict:
         if dist is not None:
             dist.barrier()
 
+    def launches_now():
+        return target.kernel_launches() + draft.kernel_launches() + int(engine.stats().sampler_launches)
+
     # ---- warm-up, then K cycles timed on the device (events on the target's stream; the drafter's
-    # work is ordered into it every cycle), bracketed by barrier + synchronise.
+    # work is ordered into it every cycle), bracketed by barrier + synchronise.  Both measured loops
+    # restart the accept schedule from the same seed, so they see the same outcomes.
     engine.generate_steps(warmup)
     barrier()
-    launches_before = target.kernel_launches() + draft.kernel_launches()
+    loop_seed = 1000 + SEEDS["schedule"] + rank
+    engine.reseed_schedule(loop_seed)
+    launches_before = launches_now()
     stats_before = engine.stats()
     start, end = lib.Event(), lib.Event()
     with ClockSampler(local) as clocks:
@@ -170,11 +249,13 @@ def run_ours(args) -> dict:
         end.synchronize()
         wall = time.perf_counter() - wall0
         device_ms = start.elapsed_ms(end)
-        launches = target.kernel_launches() + draft.kernel_launches() - launches_before    # of the device-timed loop only
+        launches = launches_now() - launches_before          # kernels of the device-timed loop only, counted as launched
+        stats_loop = engine.stats()
         # Same loop once more for the end-to-end figure: host wall clock around the public call,
         # which uploads the root token and selection requests and reads back candidates and the
         # drafter's receipt every cycle.
         barrier()
+        engine.reseed_schedule(loop_seed)
         e2e0 = time.perf_counter()
         tokens_e2e = engine.generate_steps(steps)
         target.synchronize()
@@ -190,9 +271,11 @@ def run_ours(args) -> dict:
             if i >= 2:
                 sweep_ms.append(s0.elapsed_ms(s1))
     barrier()
-    stats = engine.stats()
-    cycles = stats.cycles + stats.ordinary_steps - stats_before.cycles - stats_before.ordinary_steps
+    cycles = stats_loop.cycles + stats_loop.ordinary_steps - stats_before.cycles - stats_before.ordinary_steps
+    accepted = int(stats_loop.accepted - stats_before.accepted)
     status = target.status() | draft.status()
+    weight_bytes = target.weight_bytes(True) + draft.weight_bytes(True)
+    kv_bytes = target.kv_bytes_per_pass(2)
 
     produced, produced_e2e, elapsed_ms, e2e_s = aggregate_streams(
         dist, float(len(tokens)), float(len(tokens_e2e)), device_ms, e2e_wall, "cuda" if dist is not None else None)
@@ -202,8 +285,6 @@ def run_ours(args) -> dict:
     peak, peak_kind = load_peaks()
     sweep = float(np.mean(sweep_ms))
     achieved = sweep_bytes / (sweep * 1e-3) / 1e9
-    weight_bytes = target.weight_bytes(True) + draft.weight_bytes(True)
-    kv_bytes = target.kv_bytes_per_pass(2)
     result = {
         "metric": "Gemma3-12B Q4_K_M+270M H1 decode tok/s per GPU; dequant-GEMV HBM GB/s vs 8 TB/s",
         "value": produced / (elapsed_ms * 1e-3),            # whole job: every rank's stream
@@ -218,77 +299,221 @@ def run_ours(args) -> dict:
                                "top-p 0.95 min-p 0.05, 2-row verification, seeded Bernoulli(0.7) accept schedule",
                    "streams_per_gpu": 1, "parallelism": f"independent streams x{world} (no collective)",
                    "l2_policy": "inputs larger than L2: every pass streams 7.3 GB of distinct weights",
-                   "tokens_per_cycle_rank0": (len(tokens) + len(tokens_e2e)) / max(cycles, 1),
-                   "accepted": int(stats.accepted - stats_before.accepted), "cycles": int(cycles),
-                   "law_agreements": int(stats.law_agreements), "load_s": round(load_s, 1), "prefill_s": round(prefill_s, 1),
+                   "assumed_accept_probability": ACCEPT_P,
+                   "tokens_per_cycle_rank0": len(tokens) / max(cycles, 1),
+                   "cycles_per_s_per_gpu": steps / (elapsed_ms * 1e-3),
+                   "accepted": accepted, "cycles": int(cycles),
+                   "law_agreements": int(stats_loop.law_agreements - stats_before.law_agreements),
+                   "load_s": round(load_s, 1), "prefill_s": round(prefill_s, 2),
                    "status_word": int(status)},
         "e2e": {"value": produced_e2e / e2e_s, "unit": "tok/s",
                 "h2d_bytes_per_step": 4 + 2 * 264, "d2h_bytes_per_step": 2 * 3080 + 3096,
-                "wall_s_first_loop": wall},
+                "ms_per_step": e2e_s * 1e3 / steps, "wall_s_first_loop": wall},
         "gpu_launches": int(launches),
         "roofline": {"bound": "hbm", "achieved": achieved, "peak": peak, "unit": "GB/s", "frac": achieved / peak,
                      "peak_source": f"of {peak_kind}",
                      # DRAM bytes per launch: the read+write bytes ncu counted on one launch of the same kernel
                      # (Q4_K, K = 3840, N = 65536, two rows: 145.31 MB for 141.56 MB of weights), scaled by bytes.
                      "traffic": TRAFFIC_PER_ALGORITHMIC_BYTE * sweep_bytes / sweep_launches,
-                     "kernel": "gemv_kernel (Q4_K/Q6_K, rows=2): one verify pass's weight GEMVs run alone",
+                     "kernel": "weight_stream_kernel (Q4_K/Q6_K, rows=2): one verify pass's weight products run alone",
                      "bytes_per_launch": sweep_bytes / sweep_launches, "launches": sweep_launches,
                      "avg_launch_us": sweep * 1e3 / sweep_launches,
                      "cycle_bytes": weight_bytes + kv_bytes,
                      "cycle_frac": (weight_bytes + kv_bytes) / (elapsed_ms / steps * 1e-3) / 1e9 / peak},
         "clocks": clocks.summary(),
     }
+    if world == 1 and not args.no_shapes:
+        result["roofline"]["per_shape"] = shape_rooflines(lib, syn, peak)
+    if world == 1 and not args.no_cpu_baseline:
+        result["cpu_baseline"], result["parity"] = cpu_baseline_with_parity(target)
     return result
 
 
 # ----------------------------------------------------------------------------------------- CPU arm
 
-def cpu_cycle_time(threads: int, cycles: int, warmup: int):
-    """Times the reference CPU path for one H1 cycle: one drafter row and two target rows through
-    the oracle's restatement of the scalar dequant-GEMV block schedule (context of a few tokens:
-    a full 2048-token CPU prefill would take over an hour; attention is a negligible share)."""
+def cpu_port_cycles(threads: int, cycles: int, warmup: int, gpu_target=None):
+    """Times the CPU restatement of the reference's path for whole H1 cycles: one drafter row and two
+    target rows through its scalar dequant-GEMV block schedule, the second target row dropped again
+    (a rejected draft), at a context of a few tokens (a 2048-token CPU prefill would take over an
+    hour; attention is a negligible share).  With `gpu_target` the same two rows run on the GPU plan
+    from a reset cache and the logits of both sides are compared."""
     from guffin_b200 import synthetic as syn
     from oracle.pyoracle import Oracle, OracleModel, build
     build(reference=False)
     oracle = Oracle()
     oracle.set_threads(threads)
     tc, dc = syn.model_config(TARGET), syn.model_config(DRAFT)
-    target = OracleModel(oracle, tc, syn.make_model_weights(TARGET, SEEDS["target"]), context=2 * (cycles + warmup) + 4)
-    draft = OracleModel(oracle, dc, syn.make_model_weights(DRAFT, SEEDS["draft"]), context=2 * (cycles + warmup) + 4)
+    total = cycles + warmup
+    target = OracleModel(oracle, tc, syn.make_model_weights(TARGET, SEEDS["target"]), context=total + 4)
+    draft = OracleModel(oracle, dc, syn.make_model_weights(DRAFT, SEEDS["draft"]), context=total + 4)
     tokens = prompt_tokens(tc["vocab"], 0)
-    times = []
-    for i in range(cycles + warmup):
+    if gpu_target is not None:
+        gpu_target.reset()
+    times, errors = [], []
+    for i in range(total):
         t0 = time.perf_counter()
-        draft.append(tokens[2 * i], want_logits=True)
-        target.append(tokens[2 * i], want_logits=True)
-        target.append(tokens[2 * i + 1], want_logits=True)
-        if i % 3 == 0:
-            target.truncate(target.position - 1)            # a rejected draft row is dropped
+        draft.append(tokens[i], want_logits=True)
+        want = [target.append(tokens[i], want_logits=True), target.append(tokens[i + 1], want_logits=True)]
+        target.truncate(i + 1)                                # the rejected draft row is dropped
         times.append(time.perf_counter() - t0)
-    return times[warmup:]
+        if gpu_target is not None:
+            gpu_target.forward(tokens[i:i + 2], logits=True)
+            for row in range(2):
+                got = gpu_target.logits(row)
+                errors.append(float(np.linalg.norm(got - want[row]) / np.linalg.norm(want[row])))
+            gpu_target.publish(1)
+    return times[warmup:], errors
+
+
+def cpu_baseline_with_parity(gpu_target):
+    threads = os.cpu_count() or 1
+    times, errors = cpu_port_cycles(threads, 2, 2, gpu_target)
+    per_cycle = float(np.mean(times))
+    baseline = {"value": (1.0 + ACCEPT_P) / per_cycle, "unit": "tok/s", "cores": threads, "kind": "port",
+                "ms_per_step": per_cycle * 1e3,
+                "sample": f"{len(times)} H1 cycles (1 drafter row + 2 target rows each) after 2 warm-up cycles at context <= "
+                          f"{len(times) + 4} tokens, CPU restatement of the reference's scalar dequant-GEMV block schedule "
+                          f"split over {threads} threads by output column, {1 + ACCEPT_P:.1f} tokens per cycle assumed"}
+    parity = {"rel_l2": max(errors), "rows": len(errors), "what": "12B two-row verify logits, GPU plan against the CPU "
+              "restatement on the same tokens from an empty cache"}
+    return baseline, parity
+
+
+def reference_layer_sample(threads: int, steps: int, warmup: int):
+    """Times the reference's own backends::cpu::matmul_f32_quantized_gguf_weight (compiled from its
+    sources into oracle/_ref) on the seven projections of two 12B layers at two rows -- one layer
+    whose attn_v / ffn_down are Q6_K and one all-Q4_K, the two kinds a Q4_K_M file holds in equal
+    number -- each matrix cut into column slices, one call per slice, `threads` calls in flight."""
+    from concurrent.futures import ThreadPoolExecutor
+    from guffin_b200 import synthetic as syn
+    from oracle.pyoracle import Reference, build, BLOCK_BYTES, BLOCK_ELEMENTS
+    build(reference=False)
+    ref = Reference()
+    config = syn.model_config(TARGET)
+    rng = np.random.default_rng(SEEDS["target"])
+    jobs, elements = [], 0
+    for q6 in (True, False):
+        for name, (k, n) in syn.matrix_shapes(config).items():
+            dtype = syn.Q6_K if q6 and name in ("attn_v", "ffn_down") else syn.Q4_K
+            weight = syn.make_weight(rng, dtype, k, n)
+            x = rng.standard_normal((2, k)).astype(np.float32)
+            column_bytes = (k // BLOCK_ELEMENTS[dtype]) * BLOCK_BYTES[dtype]
+            slices = min(n, 4 * threads)
+            for s in range(slices):
+                begin, end = n * s // slices, n * (s + 1) // slices
+                jobs.append((dtype, x, weight[begin * column_bytes:end * column_bytes], k, end - begin,
+                             np.empty((2, end - begin), np.float32)))
+            elements += 2 * k * n
+
+    def run(job):
+        dtype, x, weight, k, n, out = job
+        assert ref.lib.ref_matmul_quantized(dtype, x, weight, 2, k, n, out) == 0
+
+    times = []
+    with ThreadPoolExecutor(threads) as pool:
+        for i in range(steps + warmup):
+            t0 = time.perf_counter()
+            list(pool.map(run, jobs))
+            times.append(time.perf_counter() - t0)
+    return times[warmup:], elements
+
+
+def cycle_multiply_adds() -> float:
+    """Weight elements times rows of one H1 cycle: two target rows, and the drafter's 1 + 0.7 rows
+    (the pending token of an accepted cycle rides along)."""
+    from guffin_b200 import synthetic as syn
+
+    def elements(name):
+        config = syn.model_config(name)
+        body = sum(k * n for k, n in syn.matrix_shapes(config).values()) * config["layers"]
+        return body + config["hidden"] * config["vocab"]
+    return 2.0 * elements(TARGET) + (1.0 + ACCEPT_P) * elements(DRAFT)
 
 
 def run_reference(args) -> dict:
+    from oracle.pyoracle import Reference
     world, rank, _ = distributed()
     if rank != 0:
         return {}
     threads = os.cpu_count() or 1
-    # A CPU cycle takes seconds: time at most six of them so that any --steps ends within minutes.
-    times = cpu_cycle_time(threads, max(1, min(args.steps, 6)), max(1, min(args.warmup, 1)))
-    per_cycle = float(np.mean(times))
+    steps, warmup = max(1, args.steps), max(2, args.warmup)
+    if Reference.available():
+        # A step is the bounded sample; the cycle time follows from it by multiply-add count.
+        steps = min(steps, 8)
+        times, sample_elements = reference_layer_sample(threads, steps, warmup)
+        scale = cycle_multiply_adds() / sample_elements
+        per_cycle = float(np.mean(times)) * scale
+        kind = "reference"
+        sample = (f"{len(times)} timed samples after {warmup} warm-up: the reference's matmul_f32_quantized_gguf_weight (its own "
+                  f"sources, compiled) on the 7 projections of two 12B layers at 2 rows ({sample_elements / 2e6:.0f} M weights), "
+                  f"column slices on {threads} threads, {np.mean(times):.2f} s per sample; scaled x{scale:.1f} by multiply-add count "
+                  f"to one H1 cycle (2 target rows + {1 + ACCEPT_P:.1f} drafter rows; attention, norms and sampling left out), "
+                  f"{1 + ACCEPT_P:.1f} tokens per cycle assumed")
+    else:
+        steps = min(steps, 6)
+        times, _ = cpu_port_cycles(threads, steps, warmup)
+        per_cycle = float(np.mean(times))
+        kind = "port"
+        sample = (f"{len(times)} H1 cycles (1 drafter row + 2 target rows each) after {warmup} warm-up cycles at context <= "
+                  f"{len(times) + warmup + 4} tokens, CPU restatement of the reference's scalar dequant-GEMV (the compiled reference "
+                  f"is not present), {threads} threads, {1 + ACCEPT_P:.1f} tokens per cycle assumed")
     value = (1.0 + ACCEPT_P) / per_cycle
-    sample = (f"{len(times)} H1 cycles (1 drafter row + 2 target rows each) at context <= {2 * len(times) + 4} tokens, "
-              f"oracle port of the reference's scalar CPU GEMV, {threads} threads, {1 + ACCEPT_P:.1f} tokens per cycle")
     return {
         "impl": "reference",
         "metric": "Gemma3-12B Q4_K_M+270M H1 decode tok/s per GPU; dequant-GEMV HBM GB/s vs 8 TB/s",
-        "value": value, "unit": "tok/s", "n_gpus": world, "steps": args.steps, "warmup": args.warmup,
+        "value": value, "unit": "tok/s", "n_gpus": world, "steps": len(times), "warmup": warmup,
         "ms_per_step": per_cycle * 1e3, "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
         "dtype": "u4/u6/u8 blocks -> f32", "data": "synthetic",
-        "config": {"workload": "configs[3]: Gemma-3-12B Q4_K_M + 270M Q8_0 drafter, H1 (CPU sample, see cpu_baseline.sample)"},
-        "cpu_baseline": {"value": value, "unit": "tok/s", "cores": threads, "kind": "port", "sample": sample},
+        "config": {"workload": "configs[3]: Gemma-3-12B Q4_K_M + 270M Q8_0 drafter, H1 (CPU sample, see cpu_baseline.sample)",
+                   "steps_requested": args.steps, "sample_s": float(np.mean(times))},
+        "cpu_baseline": {"value": value, "unit": "tok/s", "cores": threads, "kind": kind, "sample": sample},
         "e2e": {"value": value, "unit": "tok/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
     }
+
+
+# ----------------------------------------------------------------------------------------- single-kernel cases
+
+def run_case(argv) -> int:
+    """One small single-kernel case, a few launches through the C ABI (for a profiler)."""
+    from guffin_b200 import lib, model, synthetic as syn  # noqa: F401  (model declares the operator signatures)
+    L = lib.load()
+    rng = np.random.default_rng(0)
+    kind, numbers = argv[0], [int(a) for a in argv[1:]]
+    if kind == "matmul":
+        dtype, k, n, rows = numbers[:4]
+        launches = numbers[4] if len(numbers) > 4 else 3
+        weight = lib.PackedWeight(dtype, k, n, syn.make_weight(rng, dtype, k, n))
+        x = lib.DeviceBuffer.from_numpy(rng.standard_normal((rows, k)).astype(np.float32))
+        y = lib.DeviceBuffer(rows * n * 4)
+        ws_bytes = L.gf_matmul_workspace_bytes(dtype, rows, k, n)
+        ws = lib.DeviceBuffer(ws_bytes) if ws_bytes else None
+        for _ in range(launches):
+            lib.check(L.gf_matmul(dtype, weight.packed.ptr, x.ptr, y.ptr, rows, k, n, ws.ptr if ws else None, None))
+        lib.check(L.gf_matmul_check(None))
+        print(f"ok: {launches} gf_matmul launches, dtype={dtype} K={k} N={n} rows={rows} ({weight.nbytes / 1e6:.1f} MB of weights)")
+        return 0
+    if kind == "attention":
+        base, rows, heads, kv_heads, window, kv_f16 = numbers[:6]
+        launches = numbers[6] if len(numbers) > 6 else 3
+        ring_rows = 1 << max(1, int(np.ceil(np.log2(base + rows))))
+        kv_dtype = np.float16 if kv_f16 else np.float32
+        q = rng.standard_normal((rows, heads * 256)).astype(np.float32)
+        arrays = [q] + [rng.standard_normal((ring_rows, kv_heads * 256)).astype(kv_dtype) for _ in range(2)] \
+            + [rng.standard_normal((rows, kv_heads * 256)).astype(kv_dtype) for _ in range(2)]
+        buffers = [lib.DeviceBuffer.from_numpy(a) for a in arrays]
+        out = lib.DeviceBuffer(q.nbytes)
+        workspace = lib.DeviceBuffer(L.gf_attention_workspace_bytes(rows, heads))
+        position = lib.DeviceBuffer.from_numpy(np.array([base], np.uint32))
+        for _ in range(launches):
+            lib.check(L.gf_attention(buffers[0].ptr, buffers[1].ptr, buffers[2].ptr, buffers[3].ptr, buffers[4].ptr, out.ptr,
+                                     workspace.ptr, position.ptr, rows, heads, kv_heads, 256, ring_rows, window,
+                                     1.0 / 16.0, 0.0, kv_f16, None))
+        result = out.download(np.float32)
+        print(f"ok: {launches} gf_attention launches, base={base} rows={rows} heads={heads}/{kv_heads} window={window}, "
+              f"|out| = {float(np.abs(result).mean()):.4f}")
+        return 0
+    print(f"unknown case {kind!r}", file=sys.stderr)
+    return 2
 
 
 def main():
@@ -297,25 +522,20 @@ def main():
     parser.add_argument("--steps", type=int, default=None)
     parser.add_argument("--warmup", type=int, default=None)
     parser.add_argument("--impl", choices=("ours", "reference"), default="ours")
-    parser.add_argument("--no-cpu-baseline", action="store_true", help="skip the CPU baseline leg of the default arm")
+    parser.add_argument("--no-cpu-baseline", action="store_true", help="skip the CPU baseline / parity leg of the default arm")
+    parser.add_argument("--no-shapes", action="store_true", help="skip the per-shape GB/s table of the default arm")
+    parser.add_argument("--case", nargs="+", default=None, help="run one single-kernel case instead of the benchmark")
     args = parser.parse_args()
+    if args.case:
+        sys.exit(run_case(args.case))
     if args.impl == "reference":
         args.steps = 3 if args.steps is None else args.steps
-        args.warmup = 1 if args.warmup is None else args.warmup
+        args.warmup = 2 if args.warmup is None else args.warmup
         result = run_reference(args)
     else:
         args.steps = 200 if args.steps is None else args.steps
         args.warmup = 10 if args.warmup is None else args.warmup
         result = run_ours(args)
-        world, rank, _ = distributed()
-        if result and world == 1 and not args.no_cpu_baseline:
-            threads = os.cpu_count() or 1
-            times = cpu_cycle_time(threads, 2, 1)
-            per_cycle = float(np.mean(times))
-            result["cpu_baseline"] = {
-                "value": (1.0 + ACCEPT_P) / per_cycle, "unit": "tok/s", "cores": threads, "kind": "port",
-                "sample": f"2 H1 cycles (1 drafter row + 2 target rows each) after 1 warm-up at context <= 8 tokens, oracle port "
-                          f"of the reference's scalar CPU GEMV split over {threads} threads, {1 + ACCEPT_P:.1f} tokens per cycle"}
     if result:
         print(json.dumps(result), flush=True)
     if "torch.distributed" in sys.modules:

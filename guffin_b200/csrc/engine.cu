@@ -97,6 +97,7 @@ public:
         stats_ = gf_h1_stats();
         records_.clear();
         pending_ = false;
+        draft_exhausted_ = false;
         GF_TRY(target_.prefill(tokens, count));
         if (draft_ && options_.speculative) {
             // The drafter ingests the same prompt; its last logits are not needed.
@@ -129,7 +130,7 @@ public:
             ++steps;
             const uint32_t room = target_.config().context - target_.position();
             if (room < 2) break;                                            // context exhausted
-            const bool spec = options_.speculative && max_tokens - produced >= 2 && room >= 3
+            const bool spec = options_.speculative && !draft_exhausted_ && max_tokens - produced >= 2 && room >= 3
                 && draft_->config().context - draft_->position() >= 3;
             if (spec) {
                 uint32_t tokens[2];
@@ -148,6 +149,7 @@ public:
     }
 
     const gf_h1_stats& stats() const { return stats_; }
+    void reseed_schedule(uint64_t seed) { schedule_.seed(seed); }
     const std::vector<gf_h1_cycle_record>& records() const { return records_; }
 
 private:
@@ -175,13 +177,19 @@ private:
         const SelectionRequestRow row = to_request(request);
         GF_TRY(target_.select(&row, 1));
         GF_TRY(target_.publish(1));
-        if (draft_ && options_.speculative) {           // keep the drafter's timeline in step
+        if (draft_ && options_.speculative && !draft_exhausted_) {           // keep the drafter's timeline in step
             uint32_t tokens[2];
             uint32_t rows = 0;
             if (pending_) tokens[rows++] = pending_token_;
             tokens[rows++] = r;
-            GF_TRY(draft_->forward(tokens, rows, 0));
-            GF_TRY(draft_->publish(rows));
+            if (draft_->config().context - draft_->position() < rows) {
+                // The drafter's context is full before the target's: decoding goes on without it
+                // (generate() no longer speculates once fewer than three drafter rows remain).
+                draft_exhausted_ = true;
+            } else {
+                GF_TRY(draft_->forward(tokens, rows, 0));
+                GF_TRY(draft_->publish(rows));
+            }
             pending_ = false;
         }
         GF_TRY(target_.read_candidates(results_host_, 1));
@@ -211,6 +219,7 @@ private:
                                    draft_->config().vocab, so.temperature, so.top_k, so.top_p, so.min_p,
                                    so.repetition_penalty, draft_history.tokens.data(), draft_history.count, word, draft_ws_,
                                    receipt_dev_, target_.tokens_dev() + 1, nullptr, draft_->stream()));
+        stats_.sampler_launches += 3;
         GF_CUDA(cudaMemcpyAsync(receipt_host_, receipt_dev_, sizeof(DraftReceiptRow), cudaMemcpyDeviceToHost, draft_->stream()));
         GF_CUDA(cudaEventRecord(draft_done_, draft_->stream()));
         // --- target: verify rows [r, x] in one pass; x never visits the host on this path.
@@ -328,7 +337,7 @@ private:
     DraftReceiptRow* receipt_host_ = nullptr;
     cudaEvent_t draft_done_ = nullptr;
     uint32_t root_ = 0, pending_token_ = 0;
-    bool has_root_ = false, pending_ = false, first_emitted_ = false;
+    bool has_root_ = false, pending_ = false, first_emitted_ = false, draft_exhausted_ = false;
 };
 
 }  // namespace gf
@@ -418,6 +427,11 @@ int gf_h1_generate_steps(gf_h1* e, uint32_t steps, uint32_t max_tokens, uint32_t
 int gf_h1_stats_read(const gf_h1* e, gf_h1_stats* out_stats) {
     if (!e || !out_stats) return fail(GF_ERR_INVALID, "null argument");
     *out_stats = e->impl.stats();
+    return GF_OK;
+}
+int gf_h1_reseed_schedule(gf_h1* e, uint64_t seed) {
+    if (!e) return fail(GF_ERR_INVALID, "null engine");
+    e->impl.reseed_schedule(seed);
     return GF_OK;
 }
 uint32_t gf_h1_cycle_record_count(const gf_h1* e) { return e ? (uint32_t)e->impl.records().size() : 0; }

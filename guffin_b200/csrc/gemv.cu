@@ -117,13 +117,13 @@ size_t gemv_counter_bytes(const GemvLaunch& launch) {
 }
 
 template <int ROWS>
-static int launch_instance(const GemvParams& p, const GemvPlan& plan, cudaStream_t stream, bool programmatic) {
+static int launch_instance(const WeightStreamParams& p, const GemvPlan& plan, cudaStream_t stream, bool programmatic) {
     static std::once_flag once[64];
     int device = 0;
     cudaGetDevice(&device);
     cudaError_t attr_error = cudaSuccess;
     std::call_once(once[device & 63], [&] {
-        attr_error = cudaFuncSetAttribute(gemv_kernel<ROWS>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)kGemvSmemLimit);
+        attr_error = cudaFuncSetAttribute(weight_stream_kernel<ROWS>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)kGemvSmemLimit);
     });
     GF_CUDA(attr_error);
     cudaLaunchConfig_t config = {};
@@ -136,7 +136,7 @@ static int launch_instance(const GemvParams& p, const GemvPlan& plan, cudaStream
     attribute.val.programmaticStreamSerializationAllowed = 1;
     config.attrs = &attribute;
     config.numAttrs = programmatic ? 1 : 0;
-    GF_CUDA(cudaLaunchKernelEx(&config, gemv_kernel<ROWS>, p));
+    GF_CUDA(cudaLaunchKernelEx(&config, weight_stream_kernel<ROWS>, p));
     return GF_OK;
 }
 
@@ -155,7 +155,7 @@ int gemv_launch(const GemvLaunch& launch, uint32_t* counters, float* partial, si
         || (launch.prologue == kPrologueGeglu && !launch.residual)
         || (launch.prologue == kPrologueMerge && (!launch.residual || launch.k % 256u)) || launch.prologue > kPrologueMerge)
         return fail(GF_ERR_INVALID, "gf_matmul: prologue operands missing");
-    GemvParams p = {};
+    WeightStreamParams p = {};
     uint32_t first = 0;
     for (uint32_t i = 0; i < launch.count; ++i) {
         const GemvMatrixDesc& d = launch.matrices[i];
@@ -366,12 +366,29 @@ int gf_matmul_static(int dtype, const void* packed_dev, const float* x_dev, floa
     const int setup = static_scratch_for_current_device(device);
     if (setup != GF_OK) return setup;
     cudaStream_t s = as_stream(stream);
-    // The array keeps whatever the previous call left: the arrival counters and the error word
-    // must start at zero, the partial sums are fully overwritten before they are read.
+    // The array keeps whatever the previous call left: the arrival counters must start at zero,
+    // the partial sums are fully overwritten before they are read.  The error word is NOT cleared
+    // here: a wait that gave up in an earlier call stays visible until gf_matmul_static_check reads it.
     if (counters) GF_CUDA(cudaMemsetAsync(device.scratch, 0, counters, s));
-    GF_CUDA(cudaMemsetAsync(device.error_flag, 0, sizeof(int), s));
     return gemv_launch(launch, reinterpret_cast<uint32_t*>(device.scratch), reinterpret_cast<float*>(device.scratch + counters),
                        partial, device.error_flag, s, false);
+}
+
+int gf_matmul_static_check(void* stream) {
+    StaticScratch device;
+    const int setup = static_scratch_for_current_device(device);
+    if (setup != GF_OK) return setup;
+    cudaStream_t s = as_stream(stream);
+    int value = 0;
+    // The word lives in the library's static device storage: read through its symbol address, nothing is allocated.
+    GF_CUDA(cudaMemcpyAsync(&value, device.error_flag, sizeof(int), cudaMemcpyDeviceToHost, s));
+    GF_CUDA(cudaStreamSynchronize(s));
+    if (value != 0) {
+        GF_CUDA(cudaMemsetAsync(device.error_flag, 0, sizeof(int), s));
+        // A call that was cut short leaves its arrival counters half way; the next call zeroes the ones it uses.
+        return fail(GF_ERR_TIMEOUT, "gf_matmul_static: a weight-streaming wait gave up (bounded mbarrier wait); y is incomplete");
+    }
+    return GF_OK;
 }
 
 }  // extern "C"

@@ -51,7 +51,7 @@ struct GemvMatrix {
     uint32_t n, pairs, dtype, first_pair;
 };
 
-struct GemvParams {
+struct WeightStreamParams {
     GemvMatrix m[kGemvMaxMatrices];
     uint32_t matrices, total_pairs;
     uint32_t k, units, unit_elems;
@@ -517,13 +517,13 @@ struct GemvEarly {
 // Whether the prologue keeps a row in registers: the norms of prologues 1 and 2 with at most one
 // 8-element piece per thread (K <= 8 * block size) and a slice that starts on a 256-element boundary.
 template <int ROWS>
-__device__ __forceinline__ bool gemv_prologue_cached(const GemvParams& p, uint32_t first) {
+__device__ __forceinline__ bool gemv_prologue_cached(const WeightStreamParams& p, uint32_t first) {
     const bool norms = p.prologue == kPrologueNorm || p.prologue == kPrologueAddNorm;
     return ROWS <= 4 && norms && p.k / 8u <= blockDim.x && (first & 255u) == 0u;
 }
 
 template <int ROWS>
-__device__ __forceinline__ void stage_early(const GemvParams& p, uint32_t first, GemvEarly<ROWS>& early) {
+__device__ __forceinline__ void stage_early(const WeightStreamParams& p, uint32_t first, GemvEarly<ROWS>& early) {
     early.cached = gemv_prologue_cached<ROWS>(p, first);
     if (!early.cached) return;
     const uint32_t piece = threadIdx.x, o = piece * 8u;
@@ -546,7 +546,7 @@ __device__ __forceinline__ void stage_early(const GemvParams& p, uint32_t first,
 // Prologue kPrologueMerge for one 256-element block (one attention head) of row r: lane l first
 // weighs partition l from its (maximum, sum) pair, then merges its own eight dimensions over the
 // partitions that hold data, eight partitions' loads in flight at a time.  Whole warps only.
-__device__ __forceinline__ void merge_head_piece(const GemvParams& p, uint32_t r, uint32_t element, float (&v)[8]) {
+__device__ __forceinline__ void merge_head_piece(const WeightStreamParams& p, uint32_t r, uint32_t element, float (&v)[8]) {
     const uint32_t lane = threadIdx.x & 31u, heads = p.k / 256u, head = element / 256u, d = element % 256u;
     const size_t slot0 = ((size_t)r * heads + head) * 32u;
     const float2 ml = __ldcg(reinterpret_cast<const float2*>(p.residual + (slot0 + lane) * 2u));
@@ -585,7 +585,7 @@ __device__ __forceinline__ void merge_head_piece(const GemvParams& p, uint32_t r
 // of the launch ahead's output is loaded once and kept in registers through both norms (the rest
 // came in with stage_early); otherwise the row is re-read for each pass.
 template <int ROWS>
-__device__ __forceinline__ void stage_activations(const GemvParams& p, uint32_t first, uint32_t count,
+__device__ __forceinline__ void stage_activations(const WeightStreamParams& p, uint32_t first, uint32_t count,
                                                   const GemvStage& st, float* scratch, GemvEarly<ROWS>& early) {
     const bool norms = p.prologue == kPrologueNorm || p.prologue == kPrologueAddNorm;
     const uint32_t row_pieces = p.k / 8u;
@@ -713,6 +713,8 @@ __device__ __forceinline__ void stage_activations(const GemvParams& p, uint32_t 
 
 // Status bit of a non-finite binary16 K/V value (the reference's validation word, metal_kernels.mm:2484).
 constexpr uint32_t kGemvStatusKvNonFinite = 8u;
+// Status bit of a pass whose committed position plus row lies beyond the tabulated rotations.
+constexpr uint32_t kGemvStatusBadPosition = 16u;
 
 // One finished head (256 output columns starting at `column0` of matrix `which`: 0 = Q, 1 = K,
 // 2 = V) of every active row: RMSNorm with the head's weights, NEOX rotation by the tabulated
@@ -721,8 +723,8 @@ constexpr uint32_t kGemvStatusKvNonFinite = 8u;
 // 128+4l..128+4l+3, i.e. four rotation pairs.  The caller has made the head's values visible
 // (fence after the last arrival).
 template <int ROWS>
-__device__ __forceinline__ void finish_head(const GemvParams& p, const GemvMatrix& mat, uint32_t which, uint32_t head, uint32_t lane) {
-    const GemvParams::HeadEpilogue& e = p.heads;
+__device__ __forceinline__ void finish_head(const WeightStreamParams& p, const GemvMatrix& mat, uint32_t which, uint32_t head, uint32_t lane) {
+    const WeightStreamParams::HeadEpilogue& e = p.heads;
     const uint32_t base = *e.base_position;
     const float* gamma = which == 0u ? e.q_norm : which == 1u ? e.k_norm : nullptr;
     // The finished values of the first two rows are requested together (the verify pass has two).
@@ -759,7 +761,10 @@ __device__ __forceinline__ void finish_head(const GemvParams& p, const GemvMatri
                     second[j] = __fmul_rn(__fmul_rn(second[j], inv), g1[j]);
                 }
             }
-            const float4* rot = reinterpret_cast<const float4*>(e.rotation + (size_t)(base + r) * 128u + 4u * lane);
+            // A position past the rotation table (the device position word drifted from the host's) is reported, not read.
+            uint32_t table_row = base + r;
+            if (table_row >= e.table_rows) { if (lane == 0) atomicOr(e.status, kGemvStatusBadPosition); table_row = e.table_rows - 1u; }
+            const float4* rot = reinterpret_cast<const float4*>(e.rotation + (size_t)table_row * 128u + 4u * lane);
             const float4 r01 = rot[0], r23 = rot[1];            // (cos, sin) of pairs 4l, 4l+1 and 4l+2, 4l+3
             const float cs[4] = {r01.x, r01.z, r23.x, r23.z}, sn[4] = {r01.y, r01.w, r23.y, r23.w};
 #pragma unroll
@@ -801,7 +806,7 @@ __device__ __forceinline__ void finish_head(const GemvParams& p, const GemvMatri
 // Counts a finished column pair of a fused Q/K/V launch; the warp that completes a head (16 pairs)
 // finishes it.  The pair's outputs must already be written by this warp.
 template <int ROWS>
-__device__ __forceinline__ void head_pair_done(const GemvParams& p, const GemvMatrix& mat, uint32_t which, uint32_t local_pair, uint32_t lane) {
+__device__ __forceinline__ void head_pair_done(const WeightStreamParams& p, const GemvMatrix& mat, uint32_t which, uint32_t local_pair, uint32_t lane) {
     const uint32_t head = local_pair >> 4;
     const uint32_t slot = (which == 0u ? 0u : which == 1u ? p.m[0].n / 256u : p.m[0].n / 256u + p.m[1].n / 256u) + head;
     __threadfence();
@@ -816,7 +821,7 @@ __device__ __forceinline__ void head_pair_done(const GemvParams& p, const GemvMa
 }
 
 template <int ROWS>
-__global__ void __launch_bounds__(kGemvWarps * 32, 1) gemv_kernel(const __grid_constant__ GemvParams p) {
+__global__ void __launch_bounds__(kGemvWarps * 32, 1) weight_stream_kernel(const __grid_constant__ WeightStreamParams p) {
     constexpr int NT = (4 * ROWS + 7) / 8;
     constexpr uint32_t NCP = gemv_fragment_columns(ROWS);
     constexpr uint32_t FRAG_STRIDE = gemv_fragment_stride(ROWS);
@@ -1056,7 +1061,7 @@ struct GemvLaunch {
     const float *in = nullptr, *residual = nullptr, *gamma0 = nullptr, *gamma1 = nullptr;
     float* residual_out = nullptr;
     float eps = 1e-6f;
-    // Head epilogue of a fused Q/K/V launch (see GemvParams::HeadEpilogue); off when rotation is null.
+    // Head epilogue of a fused Q/K/V launch (see WeightStreamParams::HeadEpilogue); off when rotation is null.
     struct Heads {
         const float *q_norm = nullptr, *k_norm = nullptr;
         float* q_out = nullptr;

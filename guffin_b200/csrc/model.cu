@@ -389,6 +389,7 @@ int Model::run_graph_or_encode(uint32_t rows, uint32_t flags) {
         GF_CUDA(cudaStreamBeginCapture(stream_, cudaStreamCaptureModeThreadLocal));
         const int status = encode_blocks(rows, flags);
         const cudaError_t end = cudaStreamEndCapture(stream_, &graph);
+        graph_launches_[rows][with_logits] = launches_ - before;      // kernels recorded into this graph, counted as encoded
         launches_ = before;
         if (status != GF_OK) { if (graph) cudaGraphDestroy(graph); return status; }
         GF_CUDA(end);
@@ -397,7 +398,7 @@ int Model::run_graph_or_encode(uint32_t rows, uint32_t flags) {
         GF_CUDA(inst);
     }
     GF_CUDA(cudaGraphLaunch(exec, stream_));
-    launches_ += config_.layers * 7u + 2u;
+    launches_ += graph_launches_[rows][with_logits];
     return GF_OK;
 }
 
@@ -527,6 +528,38 @@ int Model::read_logits(uint32_t row, float* host) {
     return synchronize();
 }
 
+int Model::read_kv(uint32_t layer, uint32_t first_position, uint32_t count, float* k_host, float* v_host) {
+    if (!finalized_) return fail(GF_ERR_STATE, "plan is not finalized");
+    if (layer >= config_.layers || !k_host || !v_host || count == 0) return fail(GF_ERR_INVALID, "bad K/V readback");
+    const LayerCache& cache = caches_[layer];
+    if (first_position + count > position_ || position_ - first_position > cache.ring_rows)
+        return fail(GF_ERR_INVALID, "K/V rows [%u, %u) are not all committed and still inside layer %u's ring", first_position,
+                    first_position + count, layer);
+    const size_t kvw = (size_t)config_.kv_heads * config_.head_dim, element = config_.kv_f16 ? 2 : 4;
+    std::vector<uint8_t> raw[2];
+    const void* rings[2] = {cache.ring_k, cache.ring_v};
+    for (int which = 0; which < 2; ++which) {
+        raw[which].resize((size_t)count * kvw * element);
+        uint32_t done = 0;
+        while (done < count) {                       // at most two contiguous runs of ring slots
+            const uint32_t slot = (first_position + done) & (cache.ring_rows - 1u);
+            const uint32_t run = std::min(count - done, cache.ring_rows - slot);
+            GF_CUDA(cudaMemcpyAsync(raw[which].data() + (size_t)done * kvw * element,
+                                    static_cast<const uint8_t*>(rings[which]) + (size_t)slot * kvw * element,
+                                    (size_t)run * kvw * element, cudaMemcpyDeviceToHost, stream_));
+            done += run;
+        }
+    }
+    GF_TRY(synchronize());
+    float* outs[2] = {k_host, v_host};
+    for (int which = 0; which < 2; ++which) {
+        if (!config_.kv_f16) { std::memcpy(outs[which], raw[which].data(), raw[which].size()); continue; }
+        const __half* src = reinterpret_cast<const __half*>(raw[which].data());
+        for (size_t i = 0; i < (size_t)count * kvw; ++i) outs[which][i] = __half2float(src[i]);
+    }
+    return GF_OK;
+}
+
 int Model::synchronize() {
     const cudaError_t error = cudaStreamSynchronize(stream_);
     if (error != cudaSuccess) { poisoned_ = true; return check_cuda(error, "stream synchronize"); }
@@ -541,6 +574,7 @@ int Model::status_word(uint32_t* out) {
     if (out) *out = host[0];
     if (host[1] != 0) { poisoned_ = true; return fail(GF_ERR_TIMEOUT, "a weight-streaming wait gave up"); }
     if (host[0] & kStatusKvNonFinite) { poisoned_ = true; return fail(GF_ERR_NUMERIC, "non-finite F16 K/V (status %u)", host[0]); }
+    if (host[0] & kStatusBadPosition) { poisoned_ = true; return fail(GF_ERR_STATE, "a pass ran beyond the tabulated positions (status %u)", host[0]); }
     return GF_OK;
 }
 
@@ -604,6 +638,9 @@ int gf_model_read_candidates(gf_model* m, void* results_host, uint32_t rows) {
 }
 int gf_model_read_logits(gf_model* m, uint32_t row, float* logits_host) {
     return m ? m->impl.read_logits(row, logits_host) : fail(GF_ERR_INVALID, "null model");
+}
+int gf_model_read_kv(gf_model* m, uint32_t layer, uint32_t first_position, uint32_t count, float* k_host, float* v_host) {
+    return m ? m->impl.read_kv(layer, first_position, count, k_host, v_host) : fail(GF_ERR_INVALID, "null model");
 }
 int gf_model_synchronize(gf_model* m) { return m ? m->impl.synchronize() : fail(GF_ERR_INVALID, "null model"); }
 int gf_model_status(gf_model* m, uint32_t* out_status) { return m ? m->impl.status_word(out_status) : fail(GF_ERR_INVALID, "null model"); }

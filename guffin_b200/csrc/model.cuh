@@ -57,6 +57,7 @@ public:
     int select(const void* requests_host, uint32_t rows);
     int read_candidates(void* results_host, uint32_t rows);
     int read_logits(uint32_t row, float* host);
+    int read_kv(uint32_t layer, uint32_t first_position, uint32_t count, float* k_host, float* v_host);
     int synchronize();
     int status_word(uint32_t* out);
     int prefill(const uint32_t* tokens_host, uint32_t count);
@@ -117,6 +118,7 @@ private:
     uint32_t position_ = 0;
     uint32_t launches_ = 0;
     cudaGraphExec_t graphs_[GF_MAX_ROWS + 1][2] = {};
+    uint32_t graph_launches_[GF_MAX_ROWS + 1][2] = {};      // kernel nodes of each recorded graph
     cudaEvent_t tokens_copied_ = nullptr, requests_copied_ = nullptr;
 };
 

@@ -14,7 +14,7 @@ constexpr int kAttentionBlocksPerSm = 1;      // registers keep one 8-warp block
 
 // Status bits shared with the reference's validation word
 // (metal_kernels.mm:2332,2357,2370,2484; metal_command_context.hpp:17).
-enum : uint32_t { kStatusBadToken = 1u, kStatusBadRequest = 2u, kStatusBadHistory = 4u, kStatusKvNonFinite = 8u };
+enum : uint32_t { kStatusBadToken = 1u, kStatusBadRequest = 2u, kStatusBadHistory = 4u, kStatusKvNonFinite = 8u, kStatusBadPosition = 16u };
 
 struct RopeStoreParams {
     const float* raw_q;        // [rows][heads*hd]

@@ -13,31 +13,31 @@ static bool better(const TokenLogit& a, const TokenLogit& b) {
 }
 
 int validate_options(const SamplerOptions& o) {
-    if (!std::isfinite(o.temperature) || o.temperature < 0.0f) return fail(GF_ERR_INVALID, "sampling temperature must be finite and nonnegative");
-    if (o.top_k == 0 || o.top_k > kSamplerMaxTopK) return fail(GF_ERR_INVALID, "sampling top_k must be in [1, 256]");
-    if (!std::isfinite(o.top_p) || o.top_p <= 0.0f || o.top_p > 1.0f) return fail(GF_ERR_INVALID, "sampling top_p must be in (0, 1]");
-    if (!std::isfinite(o.min_p) || o.min_p < 0.0f || o.min_p > 1.0f) return fail(GF_ERR_INVALID, "sampling min_p must be in [0, 1]");
-    if (!std::isfinite(o.repetition_penalty) || o.repetition_penalty <= 0.0f) return fail(GF_ERR_INVALID, "sampling repetition_penalty must be finite and positive");
-    if (o.repetition_window > kSamplerMaxWindow) return fail(GF_ERR_INVALID, "sampling repetition_window must be at most 64");
+    if (!std::isfinite(o.temperature) || o.temperature < 0.0f) return fail(GF_ERR_INVALID, "sampler options: temperature %g is negative or not finite", (double)o.temperature);
+    if (o.top_k == 0 || o.top_k > kSamplerMaxTopK) return fail(GF_ERR_INVALID, "sampler options: top_k outside 1..256");
+    if (!std::isfinite(o.top_p) || o.top_p <= 0.0f || o.top_p > 1.0f) return fail(GF_ERR_INVALID, "sampler options: top_p outside (0, 1]");
+    if (!std::isfinite(o.min_p) || o.min_p < 0.0f || o.min_p > 1.0f) return fail(GF_ERR_INVALID, "sampler options: min_p outside [0, 1]");
+    if (!std::isfinite(o.repetition_penalty) || o.repetition_penalty <= 0.0f) return fail(GF_ERR_INVALID, "sampler options: repetition_penalty must be a positive finite number");
+    if (o.repetition_window > kSamplerMaxWindow) return fail(GF_ERR_INVALID, "sampler options: repetition_window above 64");
     return GF_OK;
 }
 
 int prepare_distribution(const TokenLogit* compact, uint32_t count, const SamplerOptions& options,
                          const SelectionHistory& request, TokenDistribution& out) {
     if (!compact || count == 0 || count > kSamplerMaxCandidates)
-        return fail(GF_ERR_INVALID, "compact sampling candidates must contain between 1 and 384 entries");
+        return fail(GF_ERR_INVALID, "candidate list: expected 1..384 (token, logit) pairs");
     if (request.top_k == 0 || request.top_k > options.top_k || request.count > kSamplerMaxWindow)
-        return fail(GF_ERR_INVALID, "sampling distribution request is invalid");
+        return fail(GF_ERR_INVALID, "candidate list: the selection request that produced it is malformed");
     std::array<TokenLogit, kSamplerMaxCandidates> pool;
     uint32_t n = 0;
     for (uint32_t i = 0; i < count; ++i) {
-        if (!std::isfinite(compact[i].logit)) return fail(GF_ERR_INVALID, "compact sampling candidate logits must be finite");
+        if (!std::isfinite(compact[i].logit)) return fail(GF_ERR_INVALID, "candidate list: a logit is NaN or infinite");
         uint32_t j = 0;
         while (j < n && pool[j].token != compact[i].token) ++j;
         if (j == n) pool[n++] = compact[i];
-        else if (pool[j].logit != compact[i].logit) return fail(GF_ERR_INVALID, "duplicate compact sampling candidates have different logits");
+        else if (pool[j].logit != compact[i].logit) return fail(GF_ERR_INVALID, "candidate list: one token appears twice with two logits");
     }
-    if (n < request.top_k) return fail(GF_ERR_INVALID, "compact sampling candidate set is smaller than top_k");
+    if (n < request.top_k) return fail(GF_ERR_INVALID, "candidate list: fewer pairs than the requested top_k");
     for (uint32_t i = 0; i < n; ++i) {
         const uint32_t* end = request.tokens.data() + request.count;
         if (std::find(request.tokens.data(), end, pool[i].token) != end)
@@ -73,7 +73,7 @@ int prepare_distribution(const TokenLogit* compact, uint32_t count, const Sample
         weights[i] = std::exp(static_cast<double>(pool[i].logit - top) / static_cast<double>(options.temperature));
         normalization += weights[i];
     }
-    if (!std::isfinite(normalization) || normalization <= 0.0) return fail(GF_ERR_NUMERIC, "sampling distribution normalization is invalid");
+    if (!std::isfinite(normalization) || normalization <= 0.0) return fail(GF_ERR_NUMERIC, "target law: the weights do not sum to a positive finite number");
     out.count = n;
     out.total_weight = normalization;
     for (uint32_t i = 0; i < n; ++i) out.values[i] = {pool[i].token, weights[i] / normalization, weights[i]};
@@ -83,11 +83,11 @@ int prepare_distribution(const TokenLogit* compact, uint32_t count, const Sample
 // Compensated (Neumaier) sum of the sampling weights: the normaliser both laws divide by.
 static int compensated_total(const TokenDistribution& d, double& total_out) {
     if (d.count == 0 || d.count > kSamplerMaxTopK || !std::isfinite(d.total_weight) || d.total_weight <= 0.0)
-        return fail(GF_ERR_INVALID, "prepared probability distribution is invalid");
+        return fail(GF_ERR_INVALID, "target law: empty or oversized support");
     double total = 0.0, correction = 0.0;
     for (uint32_t i = 0; i < d.count; ++i) {
         const double w = d.values[i].weight;
-        if (!std::isfinite(w) || w < 0.0) return fail(GF_ERR_INVALID, "prepared weights must be finite and nonnegative");
+        if (!std::isfinite(w) || w < 0.0) return fail(GF_ERR_INVALID, "target law: a weight is negative or not finite");
         const double sum = total + w;
         correction += total >= w ? (total - sum) + w : (w - sum) + total;
         total = sum;
@@ -95,7 +95,7 @@ static int compensated_total(const TokenDistribution& d, double& total_out) {
     total += correction;
     const double tolerance = static_cast<double>(d.count) * std::numeric_limits<double>::epsilon() * total;
     if (!std::isfinite(total) || total <= 0.0 || std::abs(total - d.total_weight) > tolerance)
-        return fail(GF_ERR_INVALID, "prepared probability normalization disagrees with its support");
+        return fail(GF_ERR_INVALID, "target law: stored total differs from the sum of its weights");
     total_out = total;
     return GF_OK;
 }
@@ -107,21 +107,21 @@ int prepare_speculative(const GatheredDraft& draft, const TokenDistribution& tar
     if (status != GF_OK) return status;
     if (draft.proposal_mass == 0 || draft.proposal_mass > kDraftMassTotal
         || draft.proposal_cdf_begin > kDraftMassTotal - draft.proposal_mass || draft.count != target.count)
-        return fail(GF_ERR_INVALID, "gathered draft proposal or support is invalid");
+        return fail(GF_ERR_INVALID, "draft law: proposal or support size out of range");
     uint64_t gathered = 0;
     bool proposal_in_target = false;
     for (uint32_t i = 0; i < target.count; ++i) {
         if (draft.target_mass[i] > kDraftMassTotal - gathered)
-            return fail(GF_ERR_INVALID, "gathered draft masses do not cover the exact target support");
+            return fail(GF_ERR_INVALID, "draft law: gathered on a support other than the target's");
         gathered += draft.target_mass[i];
         if (target.values[i].token == draft.proposal) {
             proposal_in_target = true;
             if (draft.target_mass[i] != draft.proposal_mass)
-                return fail(GF_ERR_INVALID, "gathered proposal mass disagrees with its selected bin");
+                return fail(GF_ERR_INVALID, "draft law: the proposal's mass and its gathered entry differ");
         }
     }
     if (!proposal_in_target && draft.proposal_mass > kDraftMassTotal - gathered)
-        return fail(GF_ERR_INVALID, "gathered draft and proposal masses exceed the full proposal law");
+        return fail(GF_ERR_INVALID, "draft law: masses add up to more than 2^32");
     // a = min(1, p(x) / q(x)); residual proportional to max(p - q, 0) on the target support,
     // q taken as it is (never renormalised).
     const double two32 = static_cast<double>(kDraftMassTotal);
@@ -139,7 +139,7 @@ int prepare_speculative(const GatheredDraft& draft, const TokenDistribution& tar
     if (residual.count != 0) {
         for (uint32_t i = 0; i < residual.count; ++i) residual.values[i].probability = residual.values[i].weight / residual.total_weight;
     } else if (acceptance < 1.0) {
-        return fail(GF_ERR_NUMERIC, "speculative rejection has no representable residual probability mass");
+        return fail(GF_ERR_NUMERIC, "acceptance: a rejection is possible but the residual law is empty");
     }
     return GF_OK;
 }
@@ -218,7 +218,7 @@ int Sampler::sample_speculative(const GatheredDraft& draft, const TokenLogit* ca
     std::mt19937_64 proposal_cursor = proposal_rng_;
     const uint64_t word = proposal_cursor() >> 32;
     if (word < draft.proposal_cdf_begin || word - draft.proposal_cdf_begin >= draft.proposal_mass)
-        return fail(GF_ERR_INVALID, "gathered proposal does not match its checkpoint-owned random word");
+        return fail(GF_ERR_INVALID, "acceptance: the proposal word falls outside the proposal's CDF interval");
     std::mt19937_64 target_cursor = rng_;
     uint32_t draws = 0;
     double accept_draw = 0.0, residual_draw = 0.0;
@@ -231,7 +231,7 @@ int Sampler::sample_speculative(const GatheredDraft& draft, const TokenLogit* ca
     if (accept_draw < acceptance) {
         out = {draft.proposal, true, draws};
     } else {
-        if (residual.count == 0) return fail(GF_ERR_NUMERIC, "rejection without a residual distribution");
+        if (residual.count == 0) return fail(GF_ERR_NUMERIC, "acceptance: rejected with an empty residual law");
         double checked = 0.0;
         status = compensated_total(residual, checked);
         if (status != GF_OK) return status;

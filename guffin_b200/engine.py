@@ -38,7 +38,7 @@ class H1Options(C.Structure):
 
 class H1Stats(C.Structure):
     _fields_ = [(n, u64) for n in ("cycles", "accepted", "rejected", "ordinary_steps", "fallback_cycles",
-                                   "emitted_tokens", "law_agreements")]
+                                   "emitted_tokens", "law_agreements", "sampler_launches")]
 
 
 class CycleRecord(C.Structure):
@@ -69,6 +69,7 @@ lib.register({
     "gf_h1_generate": (i32, [vp, u32, vp, C.POINTER(u32)]),
     "gf_h1_generate_steps": (i32, [vp, u32, u32, vp, C.POINTER(u32)]),
     "gf_h1_stats_read": (i32, [vp, C.POINTER(H1Stats)]),
+    "gf_h1_reseed_schedule": (i32, [vp, u64]),
     "gf_h1_cycle_record_read": (i32, [vp, u32, C.POINTER(CycleRecord)]),
     "gf_h1_cycle_record_count": (u32, [vp]),
 })
@@ -188,6 +189,9 @@ class H1:
         stats = H1Stats()
         check(self.L.gf_h1_stats_read(self.handle, C.byref(stats)))
         return stats
+
+    def reseed_schedule(self, seed: int) -> None:
+        check(self.L.gf_h1_reseed_schedule(self.handle, seed))
 
     def records(self):
         out = []

@@ -72,6 +72,7 @@ def _declare(L: C.CDLL) -> None:
         "gf_matmul_check": [vp],
         "gf_matmul_host": [i32, vp, vp, vp, u32, u64, u64],
         "gf_matmul_static": [i32, vp, vp, vp, u32, u64, u64, vp],
+        "gf_matmul_static_check": [vp],
     }
     for name, args in sigs.items():
         fn = getattr(L, name)

@@ -64,6 +64,7 @@ lib.register({
     "gf_model_select": (i32, [vp, vp, u32]),
     "gf_model_read_candidates": (i32, [vp, vp, u32]),
     "gf_model_read_logits": (i32, [vp, u32, vp]),
+    "gf_model_read_kv": (i32, [vp, u32, u32, u32, vp, vp]),
     "gf_model_synchronize": (i32, [vp]),
     "gf_model_status": (i32, [vp, C.POINTER(u32)]),
     "gf_model_stream": (vp, [vp]),
@@ -166,6 +167,13 @@ class Model:
         out = np.empty(self.cfg.vocab, np.float32)
         check(self.L.gf_model_read_logits(self.handle, row, out.ctypes.data))
         return out
+
+    def read_kv(self, layer: int, first: int, count: int):
+        """Committed K and V rows [first, first + count) of one layer as f32 arrays [count, kv_width]."""
+        width = self.cfg.kv_heads * self.cfg.head_dim
+        k, v = np.empty((count, width), np.float32), np.empty((count, width), np.float32)
+        check(self.L.gf_model_read_kv(self.handle, layer, first, count, k.ctypes.data, v.ctypes.data))
+        return k, v
 
     def select(self, requests) -> list:
         rows = len(requests)

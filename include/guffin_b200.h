@@ -84,7 +84,11 @@ GF_API int gf_dequantize(int dtype, const void* native_dev, uint64_t block_count
  * (metal_command_context.hpp:94-101; kernels metal_kernels.mm:551-986) and the CPU reference
  * matmul_f32_quantized_gguf_weight (cpu_backend.cpp:301-323).
  * y[m, n] = sum_k x[m, k] * deq(W)[n, k], rows m <= GF_MAX_ROWS, f32 accumulate.  Each row's
- * result is identical whether computed alone or beside other rows.
+ * result is bit-identical whether computed alone or beside other rows, for row counts 1 to 4
+ * (the decode and verification widths, gemma3_metal_tests.cpp:1223-1256 tests M = 1, 2, 3) and,
+ * separately, for row counts 5 to 8: the eight-row instance has less shared memory for its
+ * activation slice, so for very wide matrices it may split K differently and then add the same
+ * products in another order (differences of a few f32 ulps between the two groups).
  * `workspace_dev` holds split-K partial sums (gf_matmul_workspace_bytes); it may be NULL when
  * that size is 0. ---- */
 #define GF_MAX_ROWS 8
@@ -105,10 +109,16 @@ GF_API int gf_matmul_check(void* stream);
  * anything this calls.  The first call on a device looks the array's device address up (with that
  * device current); make that first call before starting any stream capture.  All calls on a
  * device share the one array: the call zeroes the counters it needs, but two calls whose kernels
- * can overlap on the GPU (different streams without ordering) race on it. */
+ * can overlap on the GPU (different streams without ordering) race on it.
+ * Failures on the device: a bounded wait that gives up sets an error word that also lives in the
+ * library's static storage (gf_matmul_check does not see it).  gf_matmul_static_check(stream)
+ * synchronises the stream, reads that word without allocating, returns GF_ERR_TIMEOUT and clears
+ * it when it is set (y of the failed call is incomplete), GF_OK otherwise.  The word is never
+ * cleared by gf_matmul_static itself, so an unread failure survives later calls. */
 GF_API size_t gf_matmul_static_capacity(void);
 GF_API int gf_matmul_static(int dtype, const void* packed_dev, const float* x_dev, float* y_dev,
                             uint32_t rows, uint64_t k, uint64_t n, void* stream);
+GF_API int gf_matmul_static_check(void* stream);
 /* Same product from HOST buffers through an internal context: uploads x, runs, downloads y.
  * `packed_dev` stays device-resident (weights are uploaded once at load time). */
 GF_API int gf_matmul_host(int dtype, const void* packed_dev, const float* x_host, float* y_host,
@@ -240,9 +250,16 @@ GF_API int gf_model_truncate(gf_model* model, uint32_t position);
 GF_API int gf_model_select(gf_model* model, const void* requests_host, uint32_t rows);
 GF_API int gf_model_read_candidates(gf_model* model, void* results_host, uint32_t rows);
 GF_API int gf_model_read_logits(gf_model* model, uint32_t row, float* logits_host);
+/* Committed K and V rows of one layer, positions [first_position, first_position + count), widened
+ * to f32: `count` x kv_heads*head_dim values each.  Synchronises.  The rows must still be inside
+ * the layer's ring (copy_tensor_from_backend on the plan's cache buffers, backend_buffer.hpp:47-68;
+ * the reference's runtime tests read the caches the same way, gemma3_target_runtime_tests.cpp:255-308). */
+GF_API int gf_model_read_kv(gf_model* model, uint32_t layer, uint32_t first_position, uint32_t count,
+                            float* k_host, float* v_host);
 GF_API int gf_model_synchronize(gf_model* model);
 /* Synchronises and returns the validation word (bit 1 bad token id, bit 2 bad request,
- * bit 8 non-finite F16 K/V; read_verifier_status) and GF_ERR_TIMEOUT / GF_ERR_NUMERIC. */
+ * bit 8 non-finite F16 K/V, bit 16 a position beyond the bound context; read_verifier_status)
+ * and GF_ERR_TIMEOUT / GF_ERR_NUMERIC / GF_ERR_STATE. */
 GF_API int gf_model_status(gf_model* model, uint32_t* out_status);
 GF_API void* gf_model_stream(gf_model* model);
 GF_API uint32_t* gf_model_tokens_dev(gf_model* model);
@@ -327,6 +344,8 @@ typedef struct gf_h1_options {
 typedef struct gf_h1_stats {
     uint64_t cycles, accepted, rejected, ordinary_steps, fallback_cycles, emitted_tokens;
     uint64_t law_agreements;             /* cycles whose real decision equals the forced one (forced mode) */
+    uint64_t sampler_launches;           /* kernels of the drafter's device sampler (three per proposal); the plans count
+                                            their own in gf_model_kernel_launches */
 } gf_h1_stats;
 typedef struct gf_h1_cycle_record {      /* inputs and result of one real acceptance test */
     uint32_t root, proposal, word, candidate_count;
@@ -349,6 +368,9 @@ GF_API int gf_h1_generate(gf_h1* engine, uint32_t max_tokens, uint32_t* out_toke
 GF_API int gf_h1_generate_steps(gf_h1* engine, uint32_t steps, uint32_t max_tokens, uint32_t* out_tokens,
                                 uint32_t* out_count);
 GF_API int gf_h1_stats_read(const gf_h1* engine, gf_h1_stats* out_stats);
+/* Restarts the forced accept/reject schedule (options.forced_schedule) from `seed`, so that two
+ * measured loops see the same sequence of scheduled outcomes.  Benchmark control only. */
+GF_API int gf_h1_reseed_schedule(gf_h1* engine, uint64_t seed);
 GF_API int gf_h1_cycle_record_read(const gf_h1* engine, uint32_t index, gf_h1_cycle_record* out_record);
 GF_API uint32_t gf_h1_cycle_record_count(const gf_h1* engine);
 

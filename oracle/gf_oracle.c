@@ -722,6 +722,17 @@ const float* gfo_model_value(const gfo_model* m, uint32_t layer, uint32_t positi
     return m->values[layer] + (size_t)position * m->c.kv_heads * m->c.head_dim;
 }
 
+/* Overwrites cached rows [first, first + count) of one layer and, with `position`, moves the
+ * model's position: lets a test continue from a cache computed elsewhere (a long prefix the
+ * scalar path would take hours to build) and check only the rows it appends itself. */
+void gfo_model_set_kv(gfo_model* m, uint32_t layer, uint32_t first, uint32_t count, const float* keys, const float* values) {
+    const size_t kvw = (size_t)m->c.kv_heads * m->c.head_dim;
+    if (layer >= m->c.layers || first + count > m->context) return;
+    memcpy(m->keys[layer] + (size_t)first * kvw, keys, (size_t)count * kvw * sizeof(float));
+    memcpy(m->values[layer] + (size_t)first * kvw, values, (size_t)count * kvw * sizeof(float));
+}
+void gfo_model_seek(gfo_model* m, uint32_t position) { if (position <= m->context) m->position = position; }
+
 static int layer_is_local(const gfo_model_config* c, uint32_t layer) {
     if (c->sliding_pattern == 6) return (layer + 1u) % 6u != 0u;
     if (c->sliding_pattern == 2) return layer % 2u == 0u;

@@ -160,6 +160,8 @@ uint32_t gfo_model_position(const gfo_model* model);
  * final_hidden may be NULL. */
 void gfo_model_append(gfo_model* model, uint32_t token, float* logits, float* final_hidden);
 void gfo_model_truncate(gfo_model* model, uint32_t position);
+void gfo_model_set_kv(gfo_model* model, uint32_t layer, uint32_t first, uint32_t count, const float* keys, const float* values);
+void gfo_model_seek(gfo_model* model, uint32_t position);
 /* Logical cache row (after rounding), [kv_heads*head_dim] floats. */
 const float* gfo_model_key(const gfo_model* model, uint32_t layer, uint32_t position);
 const float* gfo_model_value(const gfo_model* model, uint32_t layer, uint32_t position);

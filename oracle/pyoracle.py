@@ -27,6 +27,11 @@ TOKEN_LOGIT = np.dtype([("token", np.uint32), ("logit", np.float32)])
 PROB = np.dtype([("token", np.uint32), ("pad", np.uint32), ("probability", np.float64), ("weight", np.float64)])
 
 
+def reference_root() -> str:
+    """Where the reference project is checked out: $GF_REFERENCE, else `reference` beside this repository."""
+    return os.environ.get("GF_REFERENCE") or os.path.join(os.path.dirname(os.path.dirname(HERE)), "reference")
+
+
 def build(reference: bool = True) -> None:
     """Compile liboracle.so and, when the reference tree is present, _ref/libguffin_ref.so."""
     subprocess.run(["make", "-s", "-C", HERE, "oracle"], check=True)
@@ -130,6 +135,10 @@ class Oracle:
         L.gfo_model_destroy.argtypes = [C.c_void_p]
         L.gfo_model_reset.argtypes = [C.c_void_p]
         L.gfo_model_truncate.argtypes = [C.c_void_p, C.c_uint32]
+        L.gfo_model_set_kv.argtypes = [C.c_void_p, C.c_uint32, C.c_uint32, C.c_uint32, _f32p, _f32p]
+        L.gfo_model_set_kv.restype = None
+        L.gfo_model_seek.argtypes = [C.c_void_p, C.c_uint32]
+        L.gfo_model_seek.restype = None
         L.gfo_model_position.restype = C.c_uint32
         L.gfo_model_position.argtypes = [C.c_void_p]
         L.gfo_model_append.argtypes = [C.c_void_p, C.c_uint32, C.c_void_p, C.c_void_p]
@@ -328,6 +337,14 @@ class OracleModel:
 
     def reset(self):
         self.oracle.lib.gfo_model_reset(self.handle)
+
+    def set_kv(self, layer, first, keys, values):
+        """Overwrites cached rows [first, first + len(keys)) of one layer (f32 [rows, kv_width])."""
+        keys, values = np.ascontiguousarray(keys, np.float32), np.ascontiguousarray(values, np.float32)
+        self.oracle.lib.gfo_model_set_kv(self.handle, layer, first, keys.shape[0], keys, values)
+
+    def seek(self, position):
+        self.oracle.lib.gfo_model_seek(self.handle, position)
 
     @property
     def position(self):

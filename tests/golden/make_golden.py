@@ -33,7 +33,7 @@ import numpy as np
 HERE = Path(__file__).resolve().parent
 ROOT = HERE.parent.parent
 sys.path.insert(0, str(ROOT))
-REFERENCE = Path(os.environ.get("GF_REFERENCE", "/root/reference"))
+REFERENCE = Path(os.environ.get("GF_REFERENCE") or Path(__file__).resolve().parents[3] / "reference")
 
 from guffin_b200 import synthetic as syn  # noqa: E402
 from oracle.pyoracle import Reference, SamplerOptions, TOKEN_LOGIT  # noqa: E402

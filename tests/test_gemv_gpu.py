@@ -100,6 +100,25 @@ def test_rows_are_count_invariant(gf, dtype, k, n):
     np.testing.assert_array_equal(gf.matmul_host(weight, x[:2]), together[:2])
 
 
+@pytest.mark.parametrize("dtype,k,n", [(syn.Q4_K, 3840, 65536), (syn.Q6_K, 3840, 32768)])
+def test_rows_are_count_invariant_on_wide_matrices(gf, dtype, k, n):
+    """At widths where the chunk limit of the planner binds: row counts 1 to 4 (decode and
+    verification) give bit-identical rows, and so do 5 to 8 among themselves; the eight-row
+    instance stages a smaller activation slice, may therefore split K differently, and then
+    differs from the narrow instances by rounding only."""
+    rng = np.random.default_rng(7)
+    weight = gf.PackedWeight(dtype, k, n, syn.make_weight(rng, dtype, k, n))
+    x = rng.standard_normal((8, k)).astype(np.float32)
+    narrow = gf.matmul(weight, x[:4])
+    for rows in (1, 2, 3):
+        np.testing.assert_array_equal(gf.matmul(weight, x[:rows]), narrow[:rows])
+    wide = gf.matmul(weight, x)
+    for rows in (5, 6, 7):
+        np.testing.assert_array_equal(gf.matmul(weight, x[:rows]), wide[:rows])
+    assert rel_l2(wide[:4], narrow) < 1e-6
+    weight.packed.free()
+
+
 @pytest.mark.parametrize("dtype,k,n", [(syn.Q4_K, 3840, 64), (syn.Q6_K, 768, 40), (syn.Q8_0, 640, 48)])
 def test_non_finite_activation_poisons_its_row_only(gf, dtype, k, n):
     """An infinity or NaN among the activations of a row makes that row's outputs NaN (the f32

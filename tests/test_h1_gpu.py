@@ -120,6 +120,27 @@ def test_h1_greedy_is_lossless(gf, ge, gm):
     assert target.status() == 0 and draft.status() == 0
 
 
+def test_h1_continues_without_the_drafter_when_its_context_fills_first(gf, ge, gm):
+    """A drafter bound to a shorter context than its target stops proposing when it is full;
+    generation then goes on as ordinary decoding and, greedy, still equals the plain run."""
+    prompt = np.random.default_rng(2).integers(0, 2048, 24).astype(np.uint32)
+    tc = syn.model_config("tiny-target")
+    tw = syn.make_model_weights("tiny-target", 51)
+    dc = dict(tc, kv_f16=0, rope_scale_global=1.0)
+    dw = dict(tw)
+    dw["output_norm.weight"] = (tw["output_norm.weight"] * 0.8).astype(np.float32)
+    target, draft = gm.Model(tc, tw, 128, 2), gm.Model(dc, dw, 40, 2)
+    spec = ge.H1(target, draft, _options(ge, 0.0, 5))
+    spec.prefill(prompt)
+    speculative = spec.generate(80)
+    stats = spec.stats()
+    plain = ge.H1(gm.Model(tc, tw, 128, 2), None, _options(ge, 0.0, 5, speculative=0))
+    plain.prefill(prompt)
+    np.testing.assert_array_equal(speculative, plain.generate(80))
+    assert len(speculative) == 80 and stats.cycles > 0 and stats.ordinary_steps > 30
+    assert draft.position <= 40 and target.status() == 0
+
+
 @pytest.mark.parametrize("penalty", [1.0, 1.2])
 def test_h1_acceptance_decisions_match_oracle(gf, ge, gm, oracle, penalty):
     """Every accept/reject decision and corrected token of a sampled run, replayed through the
