@@ -214,6 +214,9 @@ def run_ours(args) -> dict:
     target = gm.Model(tc, syn.iter_model_weights(TARGET, SEEDS["target"]), context, PREFILL_ROWS)
     draft = gm.Model(dc, syn.iter_model_weights(DRAFT, SEEDS["draft"]), context, PREFILL_ROWS)
     load_s = time.time() - t0
+    if args.schedule is not None:
+        target.use_pass_kernel(args.schedule)
+        draft.use_pass_kernel(args.schedule)
     options = ge.H1Options(ge.sampler_options(0.7, 40, 0.95, 0.05, 1.0, seed=SEEDS["sampler"] + rank), 1, 1, ACCEPT_P,
                            SEEDS["schedule"] + rank, 0)
     engine = ge.H1(target, draft, options)
@@ -297,6 +300,8 @@ def run_ours(args) -> dict:
         "data": "synthetic",
         "config": {"workload": "configs[3]: Gemma-3-12B Q4_K_M + 270M Q8_0 drafter, H1, context 2048, T=0.7 top-k 40 "
                                "top-p 0.95 min-p 0.05, 2-row verification, seeded Bernoulli(0.7) accept schedule",
+                   "schedule": {None: "decode pass kernel (default)", 0: "kernel per operator", 1: "decode pass kernel",
+                                2: "decode pass kernel, attention launched separately"}[args.schedule],
                    "streams_per_gpu": 1, "parallelism": f"independent streams x{world} (no collective)",
                    "l2_policy": "inputs larger than L2: every pass streams 7.3 GB of distinct weights",
                    "assumed_accept_probability": ACCEPT_P,
@@ -524,6 +529,9 @@ def main():
     parser.add_argument("--impl", choices=("ours", "reference"), default="ours")
     parser.add_argument("--no-cpu-baseline", action="store_true", help="skip the CPU baseline / parity leg of the default arm")
     parser.add_argument("--no-shapes", action="store_true", help="skip the per-shape GB/s table of the default arm")
+    parser.add_argument("--schedule", type=int, choices=(0, 1, 2), default=None,
+                        help="0: one kernel per operator (CUDA graph); 1: persistent decode pass kernel (default); "
+                             "2: pass kernel with attention launched separately")
     parser.add_argument("--case", nargs="+", default=None, help="run one single-kernel case instead of the benchmark")
     args = parser.parse_args()
     if args.case:

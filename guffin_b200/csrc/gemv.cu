@@ -140,9 +140,8 @@ static int launch_instance(const WeightStreamParams& p, const GemvPlan& plan, cu
     return GF_OK;
 }
 
-int gemv_launch(const GemvLaunch& launch, uint32_t* counters, float* partial, size_t partial_bytes, int* error_flag,
-                cudaStream_t stream, bool programmatic) {
-    GemvPlan plan;
+int gemv_prepare(const GemvLaunch& launch, uint32_t* counters, float* partial, size_t partial_bytes, int* error_flag,
+                 WeightStreamParams& p, GemvPlan& plan) {
     const int status = gemv_plan(launch, plan);
     if (status != GF_OK) return status;
     if (!launch.in || !error_flag) return fail(GF_ERR_INVALID, "gf_matmul: null buffer");
@@ -155,7 +154,7 @@ int gemv_launch(const GemvLaunch& launch, uint32_t* counters, float* partial, si
         || (launch.prologue == kPrologueGeglu && !launch.residual)
         || (launch.prologue == kPrologueMerge && (!launch.residual || launch.k % 256u)) || launch.prologue > kPrologueMerge)
         return fail(GF_ERR_INVALID, "gf_matmul: prologue operands missing");
-    WeightStreamParams p = {};
+    p = WeightStreamParams{};
     uint32_t first = 0;
     for (uint32_t i = 0; i < launch.count; ++i) {
         const GemvMatrixDesc& d = launch.matrices[i];
@@ -180,6 +179,7 @@ int gemv_launch(const GemvLaunch& launch, uint32_t* counters, float* partial, si
     p.staged_units = plan.staged_units;
     p.slot_bytes = plan.slot_bytes;
     p.slot_units = plan.slot_units;
+    p.grid = plan.grid;
     p.prologue = launch.prologue;
     p.in = launch.in; p.residual = launch.residual; p.gamma0 = launch.gamma0; p.gamma1 = launch.gamma1;
     p.residual_out = launch.residual_out;
@@ -202,6 +202,15 @@ int gemv_launch(const GemvLaunch& launch, uint32_t* counters, float* partial, si
         p.counters = counters;
         p.partial = partial;
     }
+    return GF_OK;
+}
+
+int gemv_launch(const GemvLaunch& launch, uint32_t* counters, float* partial, size_t partial_bytes, int* error_flag,
+                cudaStream_t stream, bool programmatic) {
+    WeightStreamParams p;
+    GemvPlan plan;
+    const int status = gemv_prepare(launch, counters, partial, partial_bytes, error_flag, p, plan);
+    if (status != GF_OK) return status;
     switch (launch.rows) {
         case 1: return launch_instance<1>(p, plan, stream, programmatic);
         case 2: return launch_instance<2>(p, plan, stream, programmatic);

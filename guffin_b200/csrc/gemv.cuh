@@ -60,6 +60,7 @@ struct WeightStreamParams {
     uint32_t intra, staged_units;         // K chunks spread over the warps of one CTA (1 = none; hand-over in shared
                                           // memory, `chunks` is then 1); K units of the activation slice a CTA stages
     uint32_t slot_bytes, slot_units;      // ring slot size; pair rows (K units) copied and consumed per slot
+    uint32_t grid;                        // CTAs that take part (the launch's grid; a pass kernel's CTAs beyond it idle)
     uint32_t prologue;
     const float *in, *residual, *gamma0, *gamma1;
     float* residual_out;
@@ -94,11 +95,17 @@ __host__ __device__ constexpr uint32_t gemv_fragment_columns(uint32_t rows) {
 __host__ __device__ constexpr uint32_t gemv_fragment_stride(uint32_t rows) { return gemv_fragment_columns(rows) * 32u + 32u; }
 
 struct GemvSmemLayout {
-    uint32_t frag_bytes, sums_bytes, scale_bytes, ring_bytes, total;
+    uint32_t frag_bytes, sums_bytes, scale_bytes, ring_bytes, staging_bytes, total;
 };
 // Shared-memory meeting place of the warps that split K inside a CTA: [warp][row][16 columns] f32.
 __host__ __device__ constexpr uint32_t gemv_meeting_bytes(uint32_t rows) { return (uint32_t)kGemvWarps * rows * 16u * 4u; }
+// Ring, its barriers and the per-warp cursor records (the size of WeightCursor, checked where it is defined).
+constexpr uint32_t kGemvCursorBytes = 96u;
+__host__ __device__ constexpr uint32_t gemv_ring_bytes(uint32_t slot_bytes) {
+    return (uint32_t)kGemvWarps * kGemvSlots * slot_bytes + (uint32_t)kGemvWarps * kGemvSlots * 8u + (uint32_t)kGemvWarps * kGemvCursorBytes;
+}
 
+// [ring | barriers | cursors | fragments | sums | scales | meeting]
 __host__ __device__ inline GemvSmemLayout gemv_smem_layout(uint32_t rows, uint32_t chunk_units, uint32_t unit_elems,
                                                            uint32_t slot_bytes, bool meeting = false) {
     GemvSmemLayout s;
@@ -106,9 +113,9 @@ __host__ __device__ inline GemvSmemLayout gemv_smem_layout(uint32_t rows, uint32
     s.frag_bytes = (padded / 32u) * gemv_fragment_stride(rows);
     s.sums_bytes = rows * (padded / 16u) * 4u;
     s.scale_bytes = ((rows * (padded / 256u) * 4u) + 15u) & ~15u;
-    s.ring_bytes = (uint32_t)kGemvWarps * kGemvSlots * slot_bytes;
-    s.total = s.frag_bytes + s.sums_bytes + s.scale_bytes + s.ring_bytes + kGemvWarps * kGemvSlots * 8u + 64u
-              + (meeting ? gemv_meeting_bytes(rows) : 0u);
+    s.ring_bytes = gemv_ring_bytes(slot_bytes);
+    s.staging_bytes = s.frag_bytes + s.sums_bytes + s.scale_bytes + (meeting ? gemv_meeting_bytes(rows) : 0u);
+    s.total = s.ring_bytes + s.staging_bytes + 64u;
     return s;
 }
 
@@ -428,6 +435,12 @@ __device__ __forceinline__ void load8f(const float* p, float (&v)[8]) {
     const float4 a = *reinterpret_cast<const float4*>(p), b = *reinterpret_cast<const float4*>(p + 4);
     v[0] = a.x; v[1] = a.y; v[2] = a.z; v[3] = a.w; v[4] = b.x; v[5] = b.y; v[6] = b.z; v[7] = b.w;
 }
+// Activations written by other CTAs (of the launch ahead, or of an earlier phase of the same pass
+// kernel, whose stale copy may still sit in this SM's L1): read from L2.
+__device__ __forceinline__ void load8f_cg(const float* p, float (&v)[8]) {
+    const float4 a = __ldcg(reinterpret_cast<const float4*>(p)), b = __ldcg(reinterpret_cast<const float4*>(p + 4));
+    v[0] = a.x; v[1] = a.y; v[2] = a.z; v[3] = a.w; v[4] = b.x; v[5] = b.y; v[6] = b.z; v[7] = b.w;
+}
 __device__ __forceinline__ void store8f(float* p, const float (&v)[8]) {
     *reinterpret_cast<float4*>(p) = make_float4(v[0], v[1], v[2], v[3]);
     *reinterpret_cast<float4*>(p + 4) = make_float4(v[4], v[5], v[6], v[7]);
@@ -538,7 +551,7 @@ __device__ __forceinline__ void stage_early(const WeightStreamParams& p, uint32_
         load8f(p.gamma0 + o, early.g0);
 #pragma unroll
         for (int r = 0; r < ROWS; ++r)
-            if ((uint32_t)r < p.active_rows) load8f(p.residual + (size_t)r * p.k + o, early.res[r]);
+            if ((uint32_t)r < p.active_rows) load8f_cg(p.residual + (size_t)r * p.k + o, early.res[r]);
     }
     load8f(p.gamma1 + o, early.g1);
 }
@@ -604,7 +617,7 @@ __device__ __forceinline__ void stage_activations(const WeightStreamParams& p, u
         if (live) {
 #pragma unroll
             for (int r = 0; r < ROWS; ++r)
-                if ((uint32_t)r < p.active_rows) load8f(p.in + (size_t)r * p.k + o, x[r]);
+                if ((uint32_t)r < p.active_rows) load8f_cg(p.in + (size_t)r * p.k + o, x[r]);
         }
         float ss[ROWS];
 #pragma unroll
@@ -617,7 +630,7 @@ __device__ __forceinline__ void stage_activations(const WeightStreamParams& p, u
 #pragma unroll
                 for (int i = 0; i < 8; ++i) x[r][i] = __fadd_rn(res[r][i], __fmul_rn(__fmul_rn(x[r][i], inv), g0[i]));
                 // Every block holds the whole row: each writes the pieces that fall to it, so none straggles.
-                if (live && piece % gridDim.x == blockIdx.x && (uint32_t)r < p.active_rows) store8f(p.residual_out + (size_t)r * p.k + o, x[r]);
+                if (live && piece % p.grid == blockIdx.x && (uint32_t)r < p.active_rows) store8f(p.residual_out + (size_t)r * p.k + o, x[r]);
                 ss[r] = sum_squares(x[r], 0.0f);
             }
             gemv_block_sums<ROWS>(ss, scratch + kGemvWarps * ROWS);
@@ -643,7 +656,7 @@ __device__ __forceinline__ void stage_activations(const WeightStreamParams& p, u
             ss[r] = 0.0f;
             for (uint32_t c = threadIdx.x; c < row_pieces && (uint32_t)r < p.active_rows; c += blockDim.x) {
                 float x[8];
-                load8f(p.in + (size_t)r * p.k + c * 8u, x);
+                load8f_cg(p.in + (size_t)r * p.k + c * 8u, x);
                 ss[r] = sum_squares(x, ss[r]);
             }
         }
@@ -657,13 +670,13 @@ __device__ __forceinline__ void stage_activations(const WeightStreamParams& p, u
                 ss[r] = 0.0f;
                 for (uint32_t c = threadIdx.x; c < row_pieces && (uint32_t)r < p.active_rows; c += blockDim.x) {
                     float x[8], a[8], gm[8];
-                    load8f(p.in + (size_t)r * p.k + c * 8u, x);
-                    load8f(p.residual + (size_t)r * p.k + c * 8u, a);
+                    load8f_cg(p.in + (size_t)r * p.k + c * 8u, x);
+                    load8f_cg(p.residual + (size_t)r * p.k + c * 8u, a);
                     load8f(p.gamma0 + c * 8u, gm);
 #pragma unroll
                     for (int i = 0; i < 8; ++i) x[i] = __fadd_rn(a[i], __fmul_rn(__fmul_rn(x[i], inv0[r]), gm[i]));
                     ss[r] = sum_squares(x, ss[r]);
-                    if (c % gridDim.x == blockIdx.x) store8f(p.residual_out + (size_t)r * p.k + c * 8u, x);
+                    if (c % p.grid == blockIdx.x) store8f(p.residual_out + (size_t)r * p.k + c * 8u, x);
                 }
             }
             gemv_block_sums<ROWS>(ss, scratch + kGemvWarps * ROWS);
@@ -686,7 +699,7 @@ __device__ __forceinline__ void stage_activations(const WeightStreamParams& p, u
             float i0 = 1.0f, i1 = 1.0f;
 #pragma unroll
             for (int rr = 0; rr < ROWS; ++rr) if (rr == (int)r) { i0 = inv0[rr]; i1 = inv1[rr]; }
-            load8f(p.in + gi, v);
+            load8f_cg(p.in + gi, v);
             if (p.prologue == kPrologueNorm) {
                 float gm[8];
                 load8f(p.gamma1 + c, gm);
@@ -694,7 +707,7 @@ __device__ __forceinline__ void stage_activations(const WeightStreamParams& p, u
                 for (int i = 0; i < 8; ++i) v[i] = __fmul_rn(__fmul_rn(v[i], i1), gm[i]);
             } else if (p.prologue == kPrologueAddNorm) {
                 float a[8], gm0[8], gm1[8];
-                load8f(p.residual + gi, a);
+                load8f_cg(p.residual + gi, a);
                 load8f(p.gamma0 + c, gm0);
                 load8f(p.gamma1 + c, gm1);
 #pragma unroll
@@ -702,7 +715,7 @@ __device__ __forceinline__ void stage_activations(const WeightStreamParams& p, u
                     v[i] = __fmul_rn(__fmul_rn(__fadd_rn(a[i], __fmul_rn(__fmul_rn(v[i], i0), gm0[i])), i1), gm1[i]);
             } else if (p.prologue == kPrologueGeglu) {
                 float up[8];
-                load8f(p.residual + gi, up);
+                load8f_cg(p.residual + gi, up);
 #pragma unroll
                 for (int i = 0; i < 8; ++i) v[i] = __fmul_rn(gelu_tanh_exact(v[i]), up[i]);
             }
@@ -820,86 +833,174 @@ __device__ __forceinline__ void head_pair_done(const WeightStreamParams& p, cons
     if (lane == 0) p.heads.head_counters[slot] = 0u;
 }
 
-template <int ROWS>
-__global__ void __launch_bounds__(kGemvWarps * 32, 1) weight_stream_kernel(const __grid_constant__ WeightStreamParams p) {
+// ---- the weight ring of a warp and the cursor that fills it --------------------------------
+//
+// Issue number k of a warp uses slot k % kGemvSlots and barrier parity (k / kGemvSlots) % 2.  The
+// cursor (lane 0) walks the warp's items in the order the consumer meets them; inside a pass kernel
+// it carries on into the next phase's items as soon as the current phase's are all requested, so
+// weights of the next matrix arrive while the CTA waits for that phase's activations.
+
+// One warp's share of a launch (or of a phase of a pass kernel).
+struct WarpShare {
+    uint32_t chunk, first_unit, chunk_count, pair_slot, stride, first_pair, unit_base, my_items;
+};
+__device__ __forceinline__ WarpShare warp_share(const WeightStreamParams& p, uint32_t block, uint32_t warp) {
+    WarpShare w;
+    const bool intra = p.intra > 1u;
+    // With K split inside the CTA, warp w takes K chunk w % intra of the column pairs of slot w / intra.
+    w.chunk = intra ? warp % p.intra : block % p.chunks;
+    const uint32_t group_ctas = intra ? p.grid : p.grid / p.chunks;
+    w.first_unit = w.chunk * p.chunk_units;
+    w.chunk_count = min(p.chunk_units, p.units - w.first_unit);
+    const uint32_t pair_slots = intra ? (uint32_t)kGemvWarps / p.intra : (uint32_t)kGemvWarps;
+    w.pair_slot = intra ? warp / p.intra : warp;
+    w.stride = group_ctas * pair_slots;
+    w.first_pair = (intra ? block : block / p.chunks) * pair_slots + w.pair_slot;
+    w.unit_base = intra ? w.first_unit : 0u;          // of this warp's chunk inside the staged slice
+    w.my_items = (block < p.grid && w.first_pair < p.total_pairs) ? (p.total_pairs - w.first_pair + w.stride - 1u) / w.stride : 0u;
+    return w;
+}
+__device__ __forceinline__ uint32_t matrix_of_pair(const WeightStreamParams& p, uint32_t pair) {
+    uint32_t m = 0;
+    if (p.matrices > 1u && pair >= p.m[1].first_pair) m = 1;
+    if (p.matrices > 2u && pair >= p.m[2].first_pair) m = 2;
+    return m;
+}
+
+// Ring slot of a pass kernel: two Q4_K / Q8_0 pair rows or one Q6_K pair row.
+constexpr uint32_t kPassSlotBytes = 4608u;
+
+// Cursor state, one per warp in shared memory (only lane 0 touches it).
+struct WeightCursor {
+    const WeightStreamParams* phase;     // the launch / phase the cursor is in; null when nothing is left
+    const WeightStreamParams* last;      // last phase of the pass kernel's table (== phase for a single launch)
+    uint32_t phase_stride;               // bytes between consecutive table entries
+    uint32_t item, unit;                 // next item of the phase, next unit inside it
+    uint32_t issued;                     // copies requested so far
+    WarpShare share;                     // of `phase`
+    const uint8_t* src;
+    uint32_t row_bytes, slot_units;
+};
+
+struct WeightRing {
+    uint8_t* slots;          // this warp's kGemvSlots slots
+    uint64_t* bars;          // and their barriers
+    uint32_t slot_bytes;
+    WeightCursor* cursor;
+    uint32_t consumed;       // copies consumed so far (the same in every lane)
+};
+
+// Pair rows one slot carries for a matrix of `dtype`.
+template <bool PASS>
+__device__ __forceinline__ uint32_t ring_slot_units(const WeightStreamParams& p, uint32_t dtype) {
+    return PASS ? (dtype == (uint32_t)GF_Q6_K ? 1u : 2u) : p.slot_units;
+}
+
+// A table entry holds the parameters of a streaming phase when its first word is kPhaseStream.
+constexpr uint32_t kPhaseStream = 1u;
+__device__ __forceinline__ const WeightStreamParams* phase_stream_params(const uint8_t* entry) {
+    return reinterpret_cast<const WeightStreamParams*>(entry + 16u);
+}
+
+// Requests the next slot-full of pair rows (lane 0 only).
+template <bool PASS>
+__device__ __forceinline__ void ring_issue(WeightRing& ring, uint32_t block, uint32_t warp) {
+    WeightCursor& c = *ring.cursor;
+    while (true) {
+        if (c.phase == nullptr) return;
+        if (c.item < c.share.my_items) break;
+        if (!PASS || c.phase == c.last) { c.phase = nullptr; return; }
+        // On to the next streaming phase of the table.
+        const uint8_t* entry = reinterpret_cast<const uint8_t*>(c.phase) - 16u;
+        const uint8_t* last_entry = reinterpret_cast<const uint8_t*>(c.last) - 16u;
+        const WeightStreamParams* next = nullptr;
+        while (entry != last_entry) {
+            entry += c.phase_stride;
+            if (*reinterpret_cast<const uint32_t*>(entry) == kPhaseStream) { next = phase_stream_params(entry); break; }
+        }
+        c.phase = next;
+        if (next == nullptr) return;
+        c.share = warp_share(*next, block, warp);
+        c.item = 0; c.unit = 0;
+    }
+    const WeightStreamParams& p = *c.phase;
+    if (c.unit == 0u) {
+        const uint32_t pair = c.share.first_pair + c.item * c.share.stride;
+        const GemvMatrix& mat = p.m[matrix_of_pair(p, pair)];
+        c.row_bytes = pair_row_bytes((int)mat.dtype);
+        c.slot_units = ring_slot_units<PASS>(p, mat.dtype);
+        c.src = mat.weight + ((size_t)(pair - mat.first_pair) * p.units + c.share.first_unit) * c.row_bytes;
+    }
+    const uint32_t count = min(c.slot_units, c.share.chunk_count - c.unit), bytes = count * c.row_bytes;
+    const uint32_t slot = c.issued % (uint32_t)kGemvSlots;
+    mbar_expect_tx(&ring.bars[slot], bytes);
+    bulk_load(ring.slots + slot * ring.slot_bytes, c.src, bytes, &ring.bars[slot]);
+    c.src += bytes;
+    ++c.issued;
+    c.unit += count;
+    if (c.unit == c.share.chunk_count) { c.unit = 0; ++c.item; }
+}
+
+// Gives outstanding copies a bounded chance to land before the shared memory is released (lane 0).
+__device__ __forceinline__ void ring_drain(WeightRing& ring) {
+    const uint32_t issued = ring.cursor->issued;
+    for (uint32_t k = ring.consumed; k < issued; ++k)
+        mbar_wait(&ring.bars[k % (uint32_t)kGemvSlots], (k / (uint32_t)kGemvSlots) & 1u);
+}
+
+// Shared-memory carve-up of a streaming phase: [ring | barriers | cursors | fragments | sums | scales | meeting].
+struct StreamSmem {
+    uint8_t* ring; uint64_t* bars; WeightCursor* cursors; uint8_t* staging;
+};
+static_assert(sizeof(WeightCursor) <= kGemvCursorBytes, "cursor record outgrew its shared-memory slot");
+__host__ __device__ constexpr uint32_t stream_smem_fixed(uint32_t slot_bytes) { return gemv_ring_bytes(slot_bytes); }
+__device__ __forceinline__ StreamSmem stream_smem(uint8_t* smem, uint32_t slot_bytes) {
+    StreamSmem s;
+    s.ring = smem;
+    s.bars = reinterpret_cast<uint64_t*>(smem + (uint32_t)kGemvWarps * kGemvSlots * slot_bytes);
+    s.cursors = reinterpret_cast<WeightCursor*>(s.bars + kGemvWarps * kGemvSlots);     // kGemvCursorBytes apart
+    s.staging = smem + stream_smem_fixed(slot_bytes);
+    return s;
+}
+
+// One streaming launch, or one streaming phase of a pass kernel (PASS): stages this CTA's slice of the
+// activation rows once `dependency()` says the producer's outputs are visible, then every warp walks
+// its items.  `dependency` is called by every thread of the CTA exactly once and returns false when
+// the wait gave up; `scratch` holds 2 * kGemvWarps * ROWS floats, `bad_rows` one word.  Returns false
+// when a bounded wait gave up somewhere in this CTA (the error word is set by the caller).
+template <int ROWS, bool PASS, typename Dependency>
+__device__ __forceinline__ bool stream_phase(const WeightStreamParams& p, const StreamSmem& sm, WeightRing& ring,
+                                             float* scratch, uint32_t* bad_rows, Dependency&& dependency) {
     constexpr int NT = (4 * ROWS + 7) / 8;
     constexpr uint32_t NCP = gemv_fragment_columns(ROWS);
     constexpr uint32_t FRAG_STRIDE = gemv_fragment_stride(ROWS);
-    extern __shared__ __align__(128) uint8_t smem[];
-    __shared__ float scratch[2 * kGemvWarps * ROWS];
-    __shared__ uint32_t bad_rows;
     const bool intra = p.intra > 1u;
-    const GemvSmemLayout lay = gemv_smem_layout(ROWS, p.staged_units, p.unit_elems, p.slot_bytes);
+    const GemvSmemLayout lay = gemv_smem_layout(ROWS, p.staged_units, p.unit_elems, ring.slot_bytes);
     const uint32_t slice = p.staged_units * p.unit_elems, padded = (slice + 255u) & ~255u;
-    uint8_t* frags = smem;
-    float* sums = reinterpret_cast<float*>(smem + lay.frag_bytes);
-    float* block_scales = reinterpret_cast<float*>(smem + lay.frag_bytes + lay.sums_bytes);
-    uint8_t* ring_base = smem + lay.frag_bytes + lay.sums_bytes + lay.scale_bytes;
-    uint64_t* bars = reinterpret_cast<uint64_t*>(ring_base + lay.ring_bytes);
-    float* meeting = reinterpret_cast<float*>(bars + kGemvWarps * kGemvSlots);      // only laid out when K is split inside the CTA
+    uint8_t* frags = sm.staging;
+    float* sums = reinterpret_cast<float*>(sm.staging + lay.frag_bytes);
+    float* block_scales = reinterpret_cast<float*>(sm.staging + lay.frag_bytes + lay.sums_bytes);
+    float* meeting = reinterpret_cast<float*>(sm.staging + lay.frag_bytes + lay.sums_bytes + lay.scale_bytes);   // only laid out when K is split inside the CTA
 
     const uint32_t warp = threadIdx.x >> 5, lane = threadIdx.x & 31u;
-    uint8_t* ring = ring_base + warp * (kGemvSlots * p.slot_bytes);
-    uint64_t* bar = bars + warp * kGemvSlots;
+    const bool member = blockIdx.x < p.grid;            // a pass kernel's CTAs beyond the phase's grid only keep the barriers company
+    const WarpShare w = warp_share(p, blockIdx.x, warp);
+    const uint32_t chunk = w.chunk, first_unit = w.first_unit, chunk_count = w.chunk_count, pair_slot = w.pair_slot;
+    const uint32_t stride = w.stride, first_pair = w.first_pair, unit_base = w.unit_base, my_items = w.my_items;
 
-    // This CTA's K chunk and this warp's sequence of column pairs (over all matrices).
-    // With K split inside the CTA, warp w takes K chunk w % intra of the column pairs of slot w / intra.
-    const uint32_t chunk = intra ? warp % p.intra : blockIdx.x % p.chunks;
-    const uint32_t group_ctas = intra ? gridDim.x : gridDim.x / p.chunks;
-    const uint32_t first_unit = chunk * p.chunk_units;
-    const uint32_t chunk_count = min(p.chunk_units, p.units - first_unit);
-    const uint32_t pair_slots = intra ? (uint32_t)kGemvWarps / p.intra : (uint32_t)kGemvWarps;
-    const uint32_t pair_slot = intra ? warp / p.intra : warp;
-    const uint32_t stride = group_ctas * pair_slots;
-    const uint32_t first_pair = (intra ? blockIdx.x : blockIdx.x / p.chunks) * pair_slots + pair_slot;
-    const uint32_t unit_base = intra ? first_unit : 0u;          // of this warp's chunk inside the staged slice
-    const uint32_t my_items = first_pair < p.total_pairs ? (p.total_pairs - first_pair + stride - 1u) / stride : 0u;
+    if (threadIdx.x == 0) *bad_rows = 0u;
+    GemvEarly<ROWS> early_inputs;
+    early_inputs.cached = false;
+    if (member) stage_early<ROWS>(p, intra ? 0u : first_unit * p.unit_elems, early_inputs);
 
-    auto matrix_of = [&](uint32_t pair) -> uint32_t {
-        uint32_t m = 0;
-        if (p.matrices > 1u && pair >= p.m[1].first_pair) m = 1;
-        if (p.matrices > 2u && pair >= p.m[2].first_pair) m = 2;
-        return m;
-    };
-
-    if (threadIdx.x == 0) bad_rows = 0u;
-    if (lane == 0) {
-        for (int s = 0; s < kGemvSlots; ++s) mbar_init(&bar[s], 1);
-        fence_barrier_init();
+    if (!dependency()) return false;
+    if (member) {
+        const GemvStage stage{frags, sums, block_scales, bad_rows, padded};
+        stage_activations<ROWS>(p, intra ? 0u : first_unit * p.unit_elems, intra ? p.k : chunk_count * p.unit_elems, stage, scratch, early_inputs);
     }
     __syncthreads();
-
-    // Producer cursor (lane 0): the next slot-full of pair rows to request, walking items then units.
-    uint32_t prod_item = 0, prod_unit = 0, prod_slot = 0, prod_bytes = 0;
-    const uint8_t* prod_src = nullptr;
-    auto issue_next = [&]() {   // lane 0 only
-        if (prod_item >= my_items) return;
-        if (prod_unit == 0u) {
-            const uint32_t pair = first_pair + prod_item * stride;
-            const GemvMatrix& mat = p.m[matrix_of(pair)];
-            prod_bytes = pair_row_bytes((int)mat.dtype);
-            prod_src = mat.weight + ((size_t)(pair - mat.first_pair) * p.units + first_unit) * prod_bytes;
-        }
-        const uint32_t count = min(p.slot_units, chunk_count - prod_unit), bytes = count * prod_bytes;
-        mbar_expect_tx(&bar[prod_slot], bytes);
-        bulk_load(ring + prod_slot * p.slot_bytes, prod_src, bytes, &bar[prod_slot]);
-        prod_src += bytes;
-        prod_slot = prod_slot + 1u == (uint32_t)kGemvSlots ? 0u : prod_slot + 1u;
-        prod_unit += count;
-        if (prod_unit == chunk_count) { prod_unit = 0; ++prod_item; }
-    };
-    // Weights do not depend on the previous kernel: start streaming before waiting for it.
-    if (lane == 0)
-        for (int j = 0; j < kGemvSlots; ++j) issue_next();
-
-    GemvEarly<ROWS> early_inputs;
-    stage_early<ROWS>(p, intra ? 0u : first_unit * p.unit_elems, early_inputs);
-
-    pdl_wait();
-    const GemvStage stage{frags, sums, block_scales, &bad_rows, padded};
-    stage_activations<ROWS>(p, intra ? 0u : first_unit * p.unit_elems, intra ? p.k : chunk_count * p.unit_elems, stage, scratch, early_inputs);
-    __syncthreads();
-    pdl_launch_dependents();
+    if (!PASS) pdl_launch_dependents();
+    if (!member) return true;
 
     GemvLane L;
     L.lane = lane; L.g = lane >> 2; L.t = lane & 3u;
@@ -912,27 +1013,29 @@ __global__ void __launch_bounds__(kGemvWarps * 32, 1) weight_stream_kernel(const
 #pragma unroll
     for (int nt = 0; nt < NT; ++nt) my_row[nt] = min(2u * nt + (L.t >> 1), (uint32_t)ROWS - 1u);
     const uint32_t quad_base = lane & ~3u;
-    const uint32_t bad = bad_rows;
+    const uint32_t bad = *bad_rows;
 
     f32x2 accA[NT], accB[NT];
     float maccA[ROWS], maccB[ROWS];
     bool failed = false;
-    uint32_t slot = 0, phase = 0;
     for (uint32_t item = 0; item < my_items && (!failed || intra); ++item) {
         const uint32_t pair = first_pair + item * stride;
-        const GemvMatrix& mat = p.m[matrix_of(pair)];
+        const uint32_t which = matrix_of_pair(p, pair);
+        const GemvMatrix& mat = p.m[which];
         const uint32_t dtype = mat.dtype;
 #pragma unroll
         for (int nt = 0; nt < NT; ++nt) { accA[nt] = 0ull; accB[nt] = 0ull; }
 #pragma unroll
         for (int r = 0; r < ROWS; ++r) { maccA[r] = 0.0f; maccB[r] = 0.0f; }
         const uint32_t row_bytes = pair_row_bytes((int)dtype);
-        for (uint32_t u0 = 0; u0 < chunk_count && !failed; u0 += p.slot_units) {
-            if (!mbar_wait(&bar[slot], phase)) { failed = true; break; }
-            const uint32_t count = min(p.slot_units, chunk_count - u0);
+        const uint32_t slot_units = ring_slot_units<PASS>(p, dtype);
+        for (uint32_t u0 = 0; u0 < chunk_count && !failed; u0 += slot_units) {
+            const uint32_t slot = ring.consumed % (uint32_t)kGemvSlots;
+            if (!mbar_wait(&ring.bars[slot], (ring.consumed / (uint32_t)kGemvSlots) & 1u)) { failed = true; break; }
+            const uint32_t count = min(slot_units, chunk_count - u0);
             for (uint32_t j = 0; j < count; ++j) {
                 const uint32_t u = unit_base + u0 + j;
-                const uint8_t* row = ring + slot * p.slot_bytes + j * row_bytes;
+                const uint8_t* row = ring.slots + slot * ring.slot_bytes + j * row_bytes;
                 float scales[NT];
                 if (dtype == GF_Q4_K) {
 #pragma unroll
@@ -951,8 +1054,8 @@ __global__ void __launch_bounds__(kGemvWarps * 32, 1) weight_stream_kernel(const
                 }
             }
             __syncwarp();   // every lane has finished reading this slot
-            if (lane == 0) issue_next();
-            if (++slot == (uint32_t)kGemvSlots) { slot = 0; phase ^= 1u; }
+            ++ring.consumed;
+            if (lane == 0) ring_issue<PASS>(ring, blockIdx.x, warp);
         }
         if (failed && !intra) break;      // inside a CTA the other chunks' warps wait at the meeting barrier
         // Row r is the sum of B columns 4r .. 4r+3 (digit 0 first; held by quad lanes (n % 8) / 2 of
@@ -1009,7 +1112,7 @@ __global__ void __launch_bounds__(kGemvWarps * 32, 1) weight_stream_kernel(const
                     if (columnA < mat.n) mat.out[(size_t)r * mat.n + columnA] = totalA[r];
                     if (columnB < mat.n) mat.out[(size_t)r * mat.n + columnB] = totalB[r];
                 }
-            if (p.heads.enabled) head_pair_done<ROWS>(p, mat, matrix_of(pair), local_pair, lane);
+            if (p.heads.enabled) head_pair_done<ROWS>(p, mat, which, local_pair, lane);
             continue;
         }
         // Split K: park this chunk's partial sums; the warp that arrives last for the pair adds
@@ -1038,13 +1141,49 @@ __global__ void __launch_bounds__(kGemvWarps * 32, 1) weight_stream_kernel(const
                 if (out_column < mat.n && r < p.active_rows) mat.out[(size_t)r * mat.n + out_column] = sum;
             }
             if (lane == 0) p.counters[pair] = 0u;
-            if (p.heads.enabled) head_pair_done<ROWS>(p, mat, matrix_of(pair), local_pair, lane);
+            if (p.heads.enabled) head_pair_done<ROWS>(p, mat, which, local_pair, lane);
         }
     }
-    if (failed) {
-        // Give outstanding copies a bounded chance to land before the shared memory is released.
-        for (int s = 0; s < kGemvSlots; ++s) mbar_wait(&bar[s], 0);
-        if (lane == 0) atomicExch(p.error_flag, 1);
+    return !failed;
+}
+
+// Sets up this warp's ring over the CTA's shared memory: barriers initialised, cursor at the first
+// item of `first` (a single launch: last == first).  Ends with a block barrier.
+template <bool PASS>
+__device__ __forceinline__ WeightRing ring_open(const StreamSmem& sm, uint32_t slot_bytes, const WeightStreamParams* first,
+                                                const WeightStreamParams* last, uint32_t phase_stride) {
+    const uint32_t warp = threadIdx.x >> 5, lane = threadIdx.x & 31u;
+    WeightRing ring;
+    ring.slots = sm.ring + warp * (kGemvSlots * slot_bytes);
+    ring.bars = sm.bars + warp * kGemvSlots;
+    ring.slot_bytes = slot_bytes;
+    ring.cursor = sm.cursors + warp;
+    ring.consumed = 0;
+    if (lane == 0) {
+        for (int s = 0; s < kGemvSlots; ++s) mbar_init(&ring.bars[s], 1);
+        fence_barrier_init();
+        WeightCursor& c = *ring.cursor;
+        c.phase = first; c.last = last; c.phase_stride = phase_stride;
+        c.item = 0; c.unit = 0; c.issued = 0;
+        if (first != nullptr) c.share = warp_share(*first, blockIdx.x, warp);
+    }
+    __syncthreads();
+    // Weights do not depend on anything computed on the device: start streaming at once.
+    if (lane == 0)
+        for (int j = 0; j < kGemvSlots; ++j) ring_issue<PASS>(ring, blockIdx.x, warp);
+    return ring;
+}
+
+template <int ROWS>
+__global__ void __launch_bounds__(kGemvWarps * 32, 1) weight_stream_kernel(const __grid_constant__ WeightStreamParams p) {
+    extern __shared__ __align__(128) uint8_t smem[];
+    __shared__ float scratch[2 * kGemvWarps * ROWS];
+    __shared__ uint32_t bad_rows;
+    const StreamSmem sm = stream_smem(smem, p.slot_bytes);
+    WeightRing ring = ring_open<false>(sm, p.slot_bytes, &p, &p, 0u);
+    const bool ok = stream_phase<ROWS, false>(p, sm, ring, scratch, &bad_rows, [] { pdl_wait(); return true; });
+    if (!ok) {
+        if ((threadIdx.x & 31u) == 0u) { ring_drain(ring); atomicExch(p.error_flag, 1); }
     }
 }
 
@@ -1084,5 +1223,8 @@ size_t gemv_partial_bytes(const GemvLaunch& launch);
 size_t gemv_counter_bytes(const GemvLaunch& launch);
 int gemv_launch(const GemvLaunch& launch, uint32_t* counters, float* partial, size_t partial_bytes, int* error_flag,
                 cudaStream_t stream, bool programmatic);
+// The kernel parameters and decomposition gemv_launch would use, without launching (the phases of a pass kernel).
+int gemv_prepare(const GemvLaunch& launch, uint32_t* counters, float* partial, size_t partial_bytes, int* error_flag,
+                 WeightStreamParams& params, GemvPlan& plan);
 
 }  // namespace gf

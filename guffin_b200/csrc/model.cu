@@ -27,6 +27,7 @@ Model::~Model() {
     for (auto& per_rows : graphs_)
         for (auto& graph : per_rows)
             if (graph) cudaGraphExecDestroy(graph);
+    invalidate_passes();
     for (void* p : allocations_) cudaFree(p);
     if (tokens_copied_) cudaEventDestroy(tokens_copied_);
     if (requests_copied_) cudaEventDestroy(requests_copied_);
@@ -248,6 +249,8 @@ int Model::finalize() {
     GF_TRY(device_alloc(allocations_, &state_dev_, 8));
     GF_TRY(device_alloc(allocations_, &status_dev_, 4));
     GF_TRY(device_alloc(allocations_, &error_flag_, 4));
+    GF_TRY(device_alloc(allocations_, &pass_arrived_, 4));
+    GF_CUDA(cudaMemsetAsync(pass_arrived_, 0, 16, stream_));
     GF_CUDA(cudaMemsetAsync(state_dev_, 0, 32, stream_));
     GF_CUDA(cudaMemsetAsync(status_dev_, 0, 16, stream_));
     GF_CUDA(cudaMemsetAsync(error_flag_, 0, 16, stream_));
@@ -268,6 +271,7 @@ int Model::reset() {
     // A pass that was cut short (a bounded wait gave up) can leave arrival counters half way:
     // every kernel that counts arrivals expects zero.
     GF_CUDA(cudaMemsetAsync(error_flag_, 0, 16, stream_));
+    GF_CUDA(cudaMemsetAsync(pass_arrived_, 0, 16, stream_));       // a pass kernel that gave up leaves its barrier count behind
     if (matmul_counters_bytes_) GF_CUDA(cudaMemsetAsync(matmul_counters_, 0, matmul_counters_bytes_, stream_));
     GF_CUDA(cudaMemsetAsync(attention_counters(attention_ws_, config_.row_capacity, config_.heads), 0,
                             (size_t)config_.row_capacity * config_.heads * sizeof(uint32_t), stream_));
@@ -282,8 +286,136 @@ static GemvMatrixDesc desc(const PackedMatrix& w, float* out) { return GemvMatri
 int Model::run_gemv(GemvLaunch& launch, uint32_t rows) {
     launch.rows = rows;
     launch.eps = config_.rms_eps;
+    if (recording_) {
+        PassPhase phase {};
+        GemvPlan plan;
+        GF_TRY(gemv_prepare(launch, matmul_counters_, static_cast<float*>(matmul_ws_), matmul_ws_bytes_, error_flag_, phase.stream, plan));
+        phase.kind = kPhaseStream;
+        recording_->push_back(phase);
+        recording_breaks_.push_back(pending_break_);
+        pending_break_ = -1;
+        return GF_OK;
+    }
     ++launches_;
     return gemv_launch(launch, matmul_counters_, static_cast<float*>(matmul_ws_), matmul_ws_bytes_, error_flag_, stream_, true);
+}
+
+int Model::emit_embedding(uint32_t rows, float scale) {
+    const gf_model_config& c = config_;
+    if (recording_) {
+        PassPhase phase {};
+        phase.kind = kPhaseEmbedding;
+        phase.embedding = EmbeddingPhase{token_embd_.data, tokens_dev_, residual_, status_dev_, token_embd_.dtype, c.hidden, c.vocab, rows, scale};
+        recording_->push_back(phase);
+        recording_breaks_.push_back(pending_break_);
+        pending_break_ = -1;
+        return GF_OK;
+    }
+    ++launches_;
+    return launch_embedding(token_embd_.dtype, token_embd_.data, c.hidden, c.vocab, tokens_dev_, rows, scale, residual_, status_dev_, stream_, false);
+}
+
+int Model::emit_attention(const AttentionParams& params) {
+    if (recording_) {
+        AttentionParams ap = params;
+        uint32_t group = 0, rows_per_block = 0, parts = 0;
+        if (pass_mode_ == 1 && pending_break_ < 0 && pass_attention_supported(ap, ap.rows, group, rows_per_block, parts)) {
+            PassPhase phase {};
+            phase.kind = kPhaseAttention;
+            phase.attention_group = group;
+            phase.attention_rows = rows_per_block;
+            ap.target_parts = parts;
+            phase.attention = ap;
+            recording_->push_back(phase);
+            recording_breaks_.push_back(-1);
+            return GF_OK;
+        }
+        if (pending_break_ >= 0) { recording_failed_ = true; return GF_OK; }      // two launches in a row: not a shape this schedule produces
+        recording_pass_->attention_launches.push_back(ap);      // a launch of its own between two segments
+        pending_break_ = (int)recording_pass_->attention_launches.size() - 1;
+        return GF_OK;
+    }
+    ++launches_;
+    return launch_attention(params, stream_, true);
+}
+
+void Model::invalidate_passes() {
+    auto drop = [](RecordedPass& pass) {
+        if (pass.table_dev) cudaFree(pass.table_dev);
+        pass = RecordedPass();
+    };
+    for (auto& per_rows : passes_)
+        for (auto& pass : per_rows) drop(pass);
+    for (auto& pass : sweeps_) drop(pass);
+}
+
+// Records the launches of a pass (or of the weight sweep) as a phase table and cuts it into
+// pass-kernel launches wherever an attention launch of its own has to run in between.
+int Model::record_pass(uint32_t rows, uint32_t flags, bool sweep, RecordedPass& out) {
+    std::vector<PassPhase> phases;
+    out = RecordedPass();
+    out.ready = true;
+    recording_ = &phases;
+    recording_pass_ = &out;
+    recording_breaks_.clear();
+    recording_failed_ = false;
+    pending_break_ = -1;
+    const uint32_t before = launches_;
+    uint64_t bytes = 0;
+    const int status = sweep ? encode_sweep(rows, nullptr, &bytes) : encode_blocks(rows, flags);
+    launches_ = before;
+    recording_ = nullptr;
+    recording_pass_ = nullptr;
+    if (status != GF_OK) return status;
+    out.weight_bytes = bytes;
+    if (recording_failed_ || pending_break_ >= 0 || phases.empty()) return GF_OK;       // not usable: the caller keeps the other schedule
+    out.smem_bytes = pass_smem_bytes(phases.data(), (uint32_t)phases.size(), rows);
+    if (out.smem_bytes == 0) return GF_OK;
+    // Segments: a new one starts at every phase that an attention launch precedes.
+    PassSegment segment{0, 0, ~0u, ~0u, -1};
+    for (uint32_t i = 0; i < phases.size(); ++i) {
+        if (recording_breaks_[i] >= 0) {
+            if (segment.count == 0) return GF_OK;          // a pass does not begin with an attention launch
+            segment.attention = recording_breaks_[i];
+            out.segments.push_back(segment);
+            segment = PassSegment{i, 0, ~0u, ~0u, -1};
+        }
+        if (phases[i].kind == kPhaseStream) {
+            if (segment.first_stream == ~0u) segment.first_stream = segment.count;
+            segment.last_stream = segment.count;
+        }
+        ++segment.count;
+    }
+    out.segments.push_back(segment);
+    void* table = nullptr;
+    GF_CUDA(cudaMalloc(&table, phases.size() * sizeof(PassPhase)));
+    out.table_dev = static_cast<PassPhase*>(table);
+    GF_CUDA(cudaMemcpyAsync(out.table_dev, phases.data(), phases.size() * sizeof(PassPhase), cudaMemcpyHostToDevice, stream_));
+    GF_CUDA(cudaStreamSynchronize(stream_));       // `phases` is pageable and goes out of scope
+    out.phases = (uint32_t)phases.size();
+    out.usable = true;
+    return GF_OK;
+}
+
+int Model::run_recorded(const RecordedPass& pass, uint32_t rows) {
+    for (const PassSegment& segment : pass.segments) {
+        PassLaunch launch;
+        launch.table_dev = pass.table_dev;
+        launch.first = segment.first; launch.count = segment.count;
+        launch.first_stream = segment.first_stream; launch.last_stream = segment.last_stream;
+        launch.rows = rows;
+        launch.smem_bytes = pass.smem_bytes;
+        launch.arrived_dev = pass_arrived_;
+        launch.error_flag = error_flag_;
+        launch.poll_limit = pass_poll_limit_;
+        GF_TRY(launch_pass(launch, stream_));
+        ++launches_;
+        if (segment.attention >= 0) {
+            GF_TRY(launch_attention(pass.attention_launches[(size_t)segment.attention], stream_, true));
+            ++launches_;
+        }
+    }
+    return GF_OK;
 }
 
 // One transformer pass: the operator order of encode_gemma_target_blocks
@@ -297,9 +429,7 @@ int Model::run_gemv(GemvLaunch& launch, uint32_t rows) {
 int Model::encode_blocks(uint32_t rows, uint32_t flags) {
     const gf_model_config& c = config_;
     const float embedding_scale = sqrtf((float)c.hidden);     // f32, not bf16-rounded (model.cpp:599-605)
-    GF_TRY(launch_embedding(token_embd_.dtype, token_embd_.data, c.hidden, c.vocab, tokens_dev_, rows, embedding_scale,
-                            residual_, status_dev_, stream_, false));
-    ++launches_;
+    GF_TRY(emit_embedding(rows, embedding_scale));
     float* x = residual_;          // residual stream entering a layer
     float* x2 = post_attention_;   // residual stream after the attention branch
     // Weight sets of the launches.
@@ -340,6 +470,7 @@ int Model::encode_blocks(uint32_t rows, uint32_t flags) {
             qkv.heads.head_counters = head_counters_; qkv.heads.table_rows = c.context + GF_MAX_ROWS; qkv.heads.kv_f16 = c.kv_f16;
         }
         GF_TRY(run_gemv(qkv, rows));
+        if (!fused_heads && recording_) { recording_failed_ = true; return GF_OK; }      // the separate rotation kernel has no phase
         if (!fused_heads) {
             RopeStoreParams rp{raw_q_, raw_k_, raw_v_, c.uses_qk_norm ? w.q_norm : nullptr, c.uses_qk_norm ? w.k_norm : nullptr,
                                query_, cache.private_k, cache.private_v, state_dev_, status_dev_, cache.rope_divisors, rows, c.heads, c.kv_heads,
@@ -357,8 +488,7 @@ int Model::encode_blocks(uint32_t rows, uint32_t flags) {
         ap.ring_mask = cache.ring_rows - 1u; ap.window = cache.window; ap.scale = c.attention_scale;
         ap.softcap = c.attn_softcap; ap.kv_f16 = c.kv_f16;
         ap.defer_merge = 1u;                 // the O projection's prologue merges the partitions
-        GF_TRY(launch_attention(ap, stream_, true));
-        launches_ += 1;
+        GF_TRY(emit_attention(ap));
         o.prologue = kPrologueMerge; o.in = ap.partial_out; o.residual = ap.partial_ml;
         GemvLaunch gu = gate_up_weights(l);
         GF_TRY(run_gemv(o, rows));
@@ -380,6 +510,11 @@ int Model::encode_blocks(uint32_t rows, uint32_t flags) {
 
 int Model::run_graph_or_encode(uint32_t rows, uint32_t flags) {
     const int with_logits = (flags & kForwardLogits) ? 1 : 0;
+    if (pass_mode_ != 0 && rows <= kPassMaxRows) {
+        RecordedPass& pass = passes_[rows][with_logits];
+        if (!pass.ready) GF_TRY(record_pass(rows, flags, false, pass));
+        if (pass.usable) return run_recorded(pass, rows);
+    }
     if (!use_graph_) return encode_blocks(rows, flags);
     cudaGraphExec_t& exec = graphs_[rows][with_logits];
     if (!exec) {
@@ -460,6 +595,19 @@ int Model::prefill(const uint32_t* tokens_host, uint32_t count) {
 int Model::weight_sweep(uint32_t rows, uint32_t* out_launches, uint64_t* out_bytes) {
     if (!finalized_) return fail(GF_ERR_STATE, "plan is not finalized");
     if (rows == 0 || rows > config_.row_capacity) return fail(GF_ERR_INVALID, "bad row count");
+    if (pass_mode_ != 0 && rows <= kPassMaxRows) {
+        RecordedPass& pass = sweeps_[rows];
+        if (!pass.ready) GF_TRY(record_pass(rows, 0, true, pass));
+        if (pass.usable) {
+            if (out_launches) *out_launches = (uint32_t)pass.segments.size();
+            if (out_bytes) *out_bytes = pass.weight_bytes;
+            return run_recorded(pass, rows);
+        }
+    }
+    return encode_sweep(rows, out_launches, out_bytes);
+}
+
+int Model::encode_sweep(uint32_t rows, uint32_t* out_launches, uint64_t* out_bytes) {
     uint32_t launches = 0;
     uint64_t bytes = 0;
     std::vector<GemvLaunch> sequence;
@@ -658,6 +806,11 @@ int gf_model_weight_sweep(gf_model* m, uint32_t rows, uint32_t* out_launches, ui
 int gf_model_use_graph(gf_model* m, int enable) {
     if (!m) return fail(GF_ERR_INVALID, "null model");
     m->impl.set_use_graph(enable != 0);
+    return GF_OK;
+}
+int gf_model_use_pass_kernel(gf_model* m, int mode) {
+    if (!m || mode < 0 || mode > 2) return fail(GF_ERR_INVALID, "gf_model_use_pass_kernel: mode must be 0, 1 or 2");
+    m->impl.set_pass_mode(mode);
     return GF_OK;
 }
 

@@ -5,6 +5,7 @@
 
 #include "common.cuh"
 #include "ops.cuh"
+#include "pass.cuh"
 
 #include <string>
 #include <vector>
@@ -77,6 +78,10 @@ public:
     size_t kv_bytes_per_pass(uint32_t rows) const;
     uint32_t kernel_launches() const { return launches_; }
     void set_use_graph(bool on) { use_graph_ = on; }
+    // 0: kernel-per-matrix schedule only.  1: passes of one or two rows run as the decode pass kernel
+    // (attention inside it where it has an instance, as launches of its own between segments otherwise).
+    // 2: as 1, but attention always as launches of its own.
+    void set_pass_mode(int mode) { if (mode != pass_mode_) invalidate_passes(); pass_mode_ = mode; }
 
     // Enqueues the selection for rows whose requests already sit in requests_dev().
     int select_device(uint32_t rows);
@@ -84,9 +89,28 @@ public:
     int set_device_token(uint32_t row, uint32_t token);
 
 private:
+    // A recorded pass: the phase table on the device and the launches that walk it.  A segment is one
+    // pass-kernel launch over phases [first, first + count); `attention` >= 0 names the attention launch
+    // that follows it (an index into `attention_launches`).
+    struct PassSegment { uint32_t first, count, first_stream, last_stream; int attention; };
+    struct RecordedPass {
+        bool ready = false, usable = false;
+        PassPhase* table_dev = nullptr;
+        uint32_t smem_bytes = 0, phases = 0;
+        uint64_t weight_bytes = 0;               // of a recorded weight sweep
+        std::vector<PassSegment> segments;
+        std::vector<AttentionParams> attention_launches;
+    };
+
     int encode_blocks(uint32_t rows, uint32_t flags);
     int run_gemv(struct GemvLaunch& launch, uint32_t rows);
+    int emit_embedding(uint32_t rows, float scale);
+    int emit_attention(const AttentionParams& params);
     int run_graph_or_encode(uint32_t rows, uint32_t flags);
+    int record_pass(uint32_t rows, uint32_t flags, bool sweep, RecordedPass& out);
+    int finish_recording(uint32_t rows, RecordedPass& out);
+    int run_recorded(const RecordedPass& pass, uint32_t rows);
+    int encode_sweep(uint32_t rows, uint32_t* out_launches, uint64_t* out_bytes);
     bool layer_is_local(uint32_t layer) const;
 
     gf_model_config config_;
@@ -119,6 +143,18 @@ private:
     uint32_t launches_ = 0;
     cudaGraphExec_t graphs_[GF_MAX_ROWS + 1][2] = {};
     uint32_t graph_launches_[GF_MAX_ROWS + 1][2] = {};      // kernel nodes of each recorded graph
+    // Decode pass kernel: recorded tables per (rows, logits), one for the weight sweep per rows.
+    int pass_mode_ = 1, recorded_mode_ = -1;
+    RecordedPass passes_[kPassMaxRows + 1][2], sweeps_[kPassMaxRows + 1];
+    uint32_t* pass_arrived_ = nullptr;
+    uint32_t pass_poll_limit_ = kPassDefaultPollLimit;
+    // While a pass is being recorded, the emitters append phases here instead of launching.
+    std::vector<PassPhase>* recording_ = nullptr;
+    std::vector<int> recording_breaks_;                      // per recorded phase: attention launch that precedes it, or -1
+    RecordedPass* recording_pass_ = nullptr;
+    bool recording_failed_ = false;
+    int pending_break_ = -1;
+    void invalidate_passes();
     cudaEvent_t tokens_copied_ = nullptr, requests_copied_ = nullptr;
 };
 

@@ -74,6 +74,7 @@ lib.register({
     "gf_model_kv_bytes_per_pass": (sz, [vp, u32]),
     "gf_model_kernel_launches": (u32, [vp]),
     "gf_model_use_graph": (i32, [vp, i32]),
+    "gf_model_use_pass_kernel": (i32, [vp, i32]),
     "gf_model_weight_sweep": (i32, [vp, u32, C.POINTER(u32), C.POINTER(u64)]),
 })
 
@@ -198,6 +199,10 @@ class Model:
 
     def use_graph(self, enable: bool) -> None:
         check(self.L.gf_model_use_graph(self.handle, int(enable)))
+
+    def use_pass_kernel(self, mode: int) -> None:
+        """0: one kernel per operator; 1: the persistent decode pass kernel; 2: that, attention launched separately."""
+        check(self.L.gf_model_use_pass_kernel(self.handle, int(mode)))
 
     @property
     def stream(self):

@@ -420,12 +420,51 @@ def test_reset_returns_the_plan_to_its_first_token(gf, gm):
 def test_graph_replay_equals_direct_launches(gf, gm):
     model, config, _ = _gpu_model(gm, "tiny-target", 31, context=64)
     direct, _, _ = _gpu_model(gm, "tiny-target", 31, context=64)
+    model.use_pass_kernel(0); direct.use_pass_kernel(0)       # the kernel-per-operator schedule, replayed and launched directly
     direct.use_graph(False)
     tokens = np.random.default_rng(3).integers(0, config["vocab"], 12).astype(np.uint32)
     for i in range(0, 12, 2):
         model.forward(tokens[i:i + 2]); direct.forward(tokens[i:i + 2])
         np.testing.assert_array_equal(model.logits(1), direct.logits(1))
         model.publish(2); direct.publish(2)
+
+
+@pytest.mark.parametrize("geometry,seed", [("tiny-target", 71), ("tiny-draft", 72), ("tiny-gemma2", 73)])
+def test_decode_pass_kernel_equals_kernel_per_operator_schedule(gf, gm, geometry, seed):
+    """The persistent decode pass kernel (attention inside it, mode 1; attention as launches between
+    its segments, mode 2) gives bit-identical logits and K/V rows to the kernel-per-operator
+    schedule (mode 0): same decomposition, same order of every sum.  One- and two-row passes, a
+    rollback, and enough tokens for the sliding layers' rings to wrap."""
+    config = syn.model_config(geometry)
+    weights = syn.make_model_weights(geometry, seed)
+    tokens = np.random.default_rng(seed).integers(0, config["vocab"], 80).astype(np.uint32)
+    outputs = []
+    for mode in (0, 1, 2):
+        model = gm.Model(config, weights, 96, 2)
+        model.use_pass_kernel(mode)
+        logits, position, step = [], 0, 0
+        while position + 2 <= 60:
+            rows = 1 if step % 3 == 2 else 2
+            model.forward(tokens[position:position + rows], logits=True)
+            logits.append(model.logits(rows - 1).copy())
+            keep = 1 if (rows == 2 and step % 4 == 1) else rows          # a rejected second row now and then
+            model.publish(keep)
+            position += keep
+            step += 1
+        model.forward(tokens[position:position + 2], logits=False)        # a pass without the head
+        model.publish(2)
+        model.forward(tokens[position + 2:position + 3], logits=True)
+        logits.append(model.logits(0).copy())
+        kv = [model.read_kv(layer, model.position - 8, 8) for layer in range(config["layers"])]
+        assert model.status() == 0
+        outputs.append((logits, kv))
+        model.close()
+    for mode in (1, 2):
+        for got, want in zip(outputs[mode][0], outputs[0][0]):
+            np.testing.assert_array_equal(got, want)
+        for (gk, gv), (wk, wv) in zip(outputs[mode][1], outputs[0][1]):
+            np.testing.assert_array_equal(gk, wk)
+            np.testing.assert_array_equal(gv, wv)
 
 
 def test_model_argument_errors(gf, gm):
