@@ -870,24 +870,28 @@ __device__ __forceinline__ uint32_t matrix_of_pair(const WeightStreamParams& p, 
 // Ring slot of a pass kernel: two Q4_K / Q8_0 pair rows or one Q6_K pair row.
 constexpr uint32_t kPassSlotBytes = 4608u;
 
-// Cursor state, one per warp in shared memory (only lane 0 touches it).
+// The cursor's phase-level state, one record per warp in shared memory (only lane 0 touches it, and only
+// when it starts a new item): which launch / phase the cursor is in and this warp's share of it.
 struct WeightCursor {
-    const WeightStreamParams* phase;     // the launch / phase the cursor is in; null when nothing is left
-    const WeightStreamParams* last;      // last phase of the pass kernel's table (== phase for a single launch)
+    const WeightStreamParams* phase;     // null when nothing is left
+    const WeightStreamParams* last;      // last streaming phase of the pass kernel's table (== phase for a single launch)
     uint32_t phase_stride;               // bytes between consecutive table entries
-    uint32_t item, unit;                 // next item of the phase, next unit inside it
-    uint32_t issued;                     // copies requested so far
-    WarpShare share;                     // of `phase`
-    const uint8_t* src;
-    uint32_t row_bytes, slot_units;
+    uint32_t items_left;                 // items of `phase` not yet started
+    uint32_t next_pair;                  // column pair of the next item
+    uint32_t stride, first_unit, chunk_count;      // of this warp's share of `phase`
 };
 
+// A warp's ring: the slots, and the cursor's per-copy state in registers (meaningful in lane 0).
 struct WeightRing {
     uint8_t* slots;          // this warp's kGemvSlots slots
     uint64_t* bars;          // and their barriers
-    uint32_t slot_bytes;
     WeightCursor* cursor;
+    uint32_t slot_bytes;
     uint32_t consumed;       // copies consumed so far (the same in every lane)
+    uint32_t issued;         // copies requested so far
+    const uint8_t* src;      // next bytes of the item being requested
+    uint32_t units_left;     // K units of that item not yet requested (0: start the next item)
+    uint32_t row_bytes, slot_units;
 };
 
 // Pair rows one slot carries for a matrix of `dtype`.
@@ -902,14 +906,21 @@ __device__ __forceinline__ const WeightStreamParams* phase_stream_params(const u
     return reinterpret_cast<const WeightStreamParams*>(entry + 16u);
 }
 
-// Requests the next slot-full of pair rows (lane 0 only).
+__device__ __forceinline__ void cursor_enter(WeightCursor& c, const WeightStreamParams* phase, uint32_t block, uint32_t warp) {
+    c.phase = phase;
+    if (phase == nullptr) { c.items_left = 0; return; }
+    const WarpShare w = warp_share(*phase, block, warp);
+    c.items_left = w.my_items; c.next_pair = w.first_pair; c.stride = w.stride;
+    c.first_unit = w.first_unit; c.chunk_count = w.chunk_count;
+}
+
+// Starts the next item (lane 0 only): false when no item is left in this launch / pass.
 template <bool PASS>
-__device__ __forceinline__ void ring_issue(WeightRing& ring, uint32_t block, uint32_t warp) {
+__device__ __forceinline__ bool ring_next_item(WeightRing& ring, uint32_t block, uint32_t warp) {
     WeightCursor& c = *ring.cursor;
-    while (true) {
-        if (c.phase == nullptr) return;
-        if (c.item < c.share.my_items) break;
-        if (!PASS || c.phase == c.last) { c.phase = nullptr; return; }
+    while (c.items_left == 0u) {
+        if (c.phase == nullptr) return false;
+        if (!PASS || c.phase == c.last) { c.phase = nullptr; return false; }
         // On to the next streaming phase of the table.
         const uint8_t* entry = reinterpret_cast<const uint8_t*>(c.phase) - 16u;
         const uint8_t* last_entry = reinterpret_cast<const uint8_t*>(c.last) - 16u;
@@ -918,33 +929,36 @@ __device__ __forceinline__ void ring_issue(WeightRing& ring, uint32_t block, uin
             entry += c.phase_stride;
             if (*reinterpret_cast<const uint32_t*>(entry) == kPhaseStream) { next = phase_stream_params(entry); break; }
         }
-        c.phase = next;
-        if (next == nullptr) return;
-        c.share = warp_share(*next, block, warp);
-        c.item = 0; c.unit = 0;
+        cursor_enter(c, next, block, warp);
     }
     const WeightStreamParams& p = *c.phase;
-    if (c.unit == 0u) {
-        const uint32_t pair = c.share.first_pair + c.item * c.share.stride;
-        const GemvMatrix& mat = p.m[matrix_of_pair(p, pair)];
-        c.row_bytes = pair_row_bytes((int)mat.dtype);
-        c.slot_units = ring_slot_units<PASS>(p, mat.dtype);
-        c.src = mat.weight + ((size_t)(pair - mat.first_pair) * p.units + c.share.first_unit) * c.row_bytes;
-    }
-    const uint32_t count = min(c.slot_units, c.share.chunk_count - c.unit), bytes = count * c.row_bytes;
-    const uint32_t slot = c.issued % (uint32_t)kGemvSlots;
+    const uint32_t pair = c.next_pair;
+    c.next_pair += c.stride;
+    --c.items_left;
+    const GemvMatrix& mat = p.m[matrix_of_pair(p, pair)];
+    ring.row_bytes = pair_row_bytes((int)mat.dtype);
+    ring.slot_units = ring_slot_units<PASS>(p, mat.dtype);
+    ring.src = mat.weight + ((size_t)(pair - mat.first_pair) * p.units + c.first_unit) * ring.row_bytes;
+    ring.units_left = c.chunk_count;
+    return true;
+}
+
+// Requests the next slot-full of pair rows (lane 0 only).
+template <bool PASS>
+__device__ __forceinline__ void ring_issue(WeightRing& ring, uint32_t block, uint32_t warp) {
+    if (ring.units_left == 0u && !ring_next_item<PASS>(ring, block, warp)) return;
+    const uint32_t count = min(ring.slot_units, ring.units_left), bytes = count * ring.row_bytes;
+    const uint32_t slot = ring.issued % (uint32_t)kGemvSlots;
     mbar_expect_tx(&ring.bars[slot], bytes);
-    bulk_load(ring.slots + slot * ring.slot_bytes, c.src, bytes, &ring.bars[slot]);
-    c.src += bytes;
-    ++c.issued;
-    c.unit += count;
-    if (c.unit == c.share.chunk_count) { c.unit = 0; ++c.item; }
+    bulk_load(ring.slots + slot * ring.slot_bytes, ring.src, bytes, &ring.bars[slot]);
+    ring.src += bytes;
+    ++ring.issued;
+    ring.units_left -= count;
 }
 
 // Gives outstanding copies a bounded chance to land before the shared memory is released (lane 0).
 __device__ __forceinline__ void ring_drain(WeightRing& ring) {
-    const uint32_t issued = ring.cursor->issued;
-    for (uint32_t k = ring.consumed; k < issued; ++k)
+    for (uint32_t k = ring.consumed; k < ring.issued; ++k)
         mbar_wait(&ring.bars[k % (uint32_t)kGemvSlots], (k / (uint32_t)kGemvSlots) & 1u);
 }
 
@@ -969,8 +983,16 @@ __device__ __forceinline__ StreamSmem stream_smem(uint8_t* smem, uint32_t slot_b
 // the wait gave up; `scratch` holds 2 * kGemvWarps * ROWS floats, `bad_rows` one word.  Returns false
 // when a bounded wait gave up somewhere in this CTA (the error word is set by the caller).
 template <int ROWS, bool PASS, typename Dependency>
-__device__ __forceinline__ bool stream_phase(const WeightStreamParams& p, const StreamSmem& sm, WeightRing& ring,
+__device__ __forceinline__ bool stream_phase(const WeightStreamParams& p, const StreamSmem& sm, WeightRing& ring_state,
                                              float* scratch, uint32_t* bad_rows, Dependency&& dependency) {
+    // The ring is worked on in registers and handed back at the end (a pass kernel calls this through a
+    // function boundary, where the caller's copy lives in local memory).
+    struct RingScope {
+        WeightRing& home; WeightRing ring;
+        __device__ explicit RingScope(WeightRing& h) : home(h), ring(h) {}
+        __device__ ~RingScope() { home = ring; }
+    } scope(ring_state);
+    WeightRing& ring = scope.ring;
     constexpr int NT = (4 * ROWS + 7) / 8;
     constexpr uint32_t NCP = gemv_fragment_columns(ROWS);
     constexpr uint32_t FRAG_STRIDE = gemv_fragment_stride(ROWS);
@@ -1158,14 +1180,14 @@ __device__ __forceinline__ WeightRing ring_open(const StreamSmem& sm, uint32_t s
     ring.bars = sm.bars + warp * kGemvSlots;
     ring.slot_bytes = slot_bytes;
     ring.cursor = sm.cursors + warp;
-    ring.consumed = 0;
+    ring.consumed = 0; ring.issued = 0;
+    ring.src = nullptr; ring.units_left = 0; ring.row_bytes = 0; ring.slot_units = 1;
     if (lane == 0) {
         for (int s = 0; s < kGemvSlots; ++s) mbar_init(&ring.bars[s], 1);
         fence_barrier_init();
         WeightCursor& c = *ring.cursor;
-        c.phase = first; c.last = last; c.phase_stride = phase_stride;
-        c.item = 0; c.unit = 0; c.issued = 0;
-        if (first != nullptr) c.share = warp_share(*first, blockIdx.x, warp);
+        c.last = last; c.phase_stride = phase_stride;
+        cursor_enter(c, first, blockIdx.x, warp);
     }
     __syncthreads();
     // Weights do not depend on anything computed on the device: start streaming at once.

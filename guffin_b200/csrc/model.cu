@@ -271,7 +271,8 @@ int Model::reset() {
     // A pass that was cut short (a bounded wait gave up) can leave arrival counters half way:
     // every kernel that counts arrivals expects zero.
     GF_CUDA(cudaMemsetAsync(error_flag_, 0, 16, stream_));
-    GF_CUDA(cudaMemsetAsync(pass_arrived_, 0, 16, stream_));       // a pass kernel that gave up leaves its barrier count behind
+    GF_CUDA(cudaMemsetAsync(pass_arrived_, 0, 16, stream_));       // a pass kernel that gave up leaves its barrier count short
+    pass_arrivals_ = 0;
     if (matmul_counters_bytes_) GF_CUDA(cudaMemsetAsync(matmul_counters_, 0, matmul_counters_bytes_, stream_));
     GF_CUDA(cudaMemsetAsync(attention_counters(attention_ws_, config_.row_capacity, config_.heads), 0,
                             (size_t)config_.row_capacity * config_.heads * sizeof(uint32_t), stream_));
@@ -406,6 +407,8 @@ int Model::run_recorded(const RecordedPass& pass, uint32_t rows) {
         launch.rows = rows;
         launch.smem_bytes = pass.smem_bytes;
         launch.arrived_dev = pass_arrived_;
+        launch.base = pass_arrivals_;
+        pass_arrivals_ += (segment.count - 1u) * (uint32_t)sm_count();      // one arrival per CTA and barrier
         launch.error_flag = error_flag_;
         launch.poll_limit = pass_poll_limit_;
         GF_TRY(launch_pass(launch, stream_));

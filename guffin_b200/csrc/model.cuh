@@ -147,6 +147,7 @@ private:
     int pass_mode_ = 1, recorded_mode_ = -1;
     RecordedPass passes_[kPassMaxRows + 1][2], sweeps_[kPassMaxRows + 1];
     uint32_t* pass_arrived_ = nullptr;
+    uint32_t pass_arrivals_ = 0;                             // value of *pass_arrived_ once every launch so far has finished
     uint32_t pass_poll_limit_ = kPassDefaultPollLimit;
     // While a pass is being recorded, the emitters append phases here instead of launching.
     std::vector<PassPhase>* recording_ = nullptr;

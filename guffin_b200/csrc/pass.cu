@@ -11,9 +11,12 @@ namespace gf {
 
 static_assert(offsetof(PassPhase, stream) == 16, "phase_stream_params() expects the streaming parameters at byte 16");
 
-// ---- grid-wide barrier: one monotone counter per launch.  Barrier b (between phase b and b + 1 of the
-// launch) is passed once the counter has reached (b + 1) * gridDim.x.  Thread 0 polls; the block
-// barrier hands the outcome to the other threads (the scheme of a cooperative grid sync, with a limit).
+// ---- grid-wide barrier: one counter that only ever grows.  A launch is told the value the counter has
+// when it starts (`base`: every earlier launch's arrivals, which the host can count because every CTA
+// arrives exactly once per barrier); barrier b of the launch, between its phases b and b + 1, is passed
+// once the counter has reached base + (b + 1) * gridDim.x.  Comparisons are modulo 2^32.  Thread 0
+// polls; the block barrier hands the outcome to the other threads (the scheme of a cooperative grid
+// sync, with a limit on the polls).
 __device__ __forceinline__ uint32_t load_acquire(const uint32_t* p) {
     uint32_t v;
     asm volatile("ld.acquire.gpu.global.u32 %0, [%1];" : "=r"(v) : "l"(p) : "memory");
@@ -25,7 +28,7 @@ __device__ __forceinline__ bool grid_wait(const uint32_t* arrived, uint32_t targ
     if (threadIdx.x == 0) {
         uint32_t ok = 0;
         for (uint32_t spin = 0; spin < poll_limit; ++spin) {
-            if (load_acquire(arrived) >= target) { ok = 1; break; }
+            if ((int32_t)(load_acquire(arrived) - target) >= 0) { ok = 1; break; }
             if ((spin & 31u) == 31u && *reinterpret_cast<const volatile int*>(error_flag) != 0) break;   // another CTA gave up
         }
         *outcome = ok;
@@ -34,10 +37,10 @@ __device__ __forceinline__ bool grid_wait(const uint32_t* arrived, uint32_t targ
     return *outcome != 0;
 }
 
-// All of this CTA's writes of the phase are ordered before its arrival.
-__device__ __forceinline__ uint32_t grid_arrive(uint32_t* arrived) {
-    __threadfence();
-    return atomicAdd(arrived, 1u);
+// Arrival of a CTA whose threads have all passed a block barrier: the release orders every write of
+// the CTA's phase before the count; nothing is waited for.
+__device__ __forceinline__ void grid_arrive(uint32_t* arrived) {
+    asm volatile("red.release.gpu.global.add.u32 [%0], 1;" ::"l"(arrived) : "memory");
 }
 
 // The 16 warps of the CTA as one attention block (two warps per tile of cached rows).
@@ -87,29 +90,43 @@ __device__ __noinline__ bool stream_phase_call(const WeightStreamParams& p, cons
     return stream_phase<ROWS, true>(p, sm, ring, scratch, bad_rows, dependency);
 }
 
+// 16-byte asynchronous global -> shared copy (the next phase's table entry travels while this phase runs).
+__device__ __forceinline__ void copy_async_16(void* dst_smem, const void* src) {
+    asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(smem_u32(dst_smem)), "l"(src) : "memory");
+}
+__device__ __forceinline__ void copy_async_wait() { asm volatile("cp.async.wait_all;" ::: "memory"); }
+
+constexpr uint32_t kPhaseChunks = (uint32_t)(sizeof(PassPhase) / 16u);
+static_assert(sizeof(PassPhase) % 16u == 0, "table entries are copied 16 bytes at a time");
+
 template <int ROWS>
 __global__ void __launch_bounds__(kGemvWarps * 32, 1) decode_pass_kernel(const PassPhase* __restrict__ table, uint32_t count,
                                                                          uint32_t first_stream, uint32_t last_stream,
-                                                                         uint32_t* arrived, int* error_flag, uint32_t poll_limit) {
+                                                                         uint32_t* arrived, uint32_t base, int* error_flag,
+                                                                         uint32_t poll_limit) {
     extern __shared__ __align__(128) uint8_t smem[];
     __shared__ float scratch[2 * kGemvWarps * ROWS];
     __shared__ uint32_t bad_rows, wait_outcome;
+    // The running phase's parameters are read from shared memory (two entries: the current one and the
+    // next one on its way); only the ring's cursor, which runs ahead, reads the table itself.
+    __shared__ __align__(16) uint8_t entries[2][sizeof(PassPhase)];
+    if (threadIdx.x < kPhaseChunks) copy_async_16(entries[0] + threadIdx.x * 16u, reinterpret_cast<const uint8_t*>(table) + threadIdx.x * 16u);
+    copy_async_wait();
     const StreamSmem sm = stream_smem(smem, kPassSlotBytes);
     // The ring's cursor starts at the first streaming phase of the launch and ends with the last one.
     const bool streams = first_stream < count;
     WeightRing ring = ring_open<true>(sm, kPassSlotBytes, streams ? &table[first_stream].stream : nullptr,
-                                      streams ? &table[last_stream].stream : nullptr, (uint32_t)sizeof(PassPhase));
+                                      streams ? &table[last_stream].stream : nullptr, (uint32_t)sizeof(PassPhase));   // ends with a block barrier
 
     bool ok = true;
     for (uint32_t ph = 0; ph < count; ++ph) {
-        const PassPhase& phase = table[ph];
-        // The next entry's cache lines are requested now, so that its first read is not a trip to HBM.
-        if (ph + 1u < count && threadIdx.x < (sizeof(PassPhase) + 127u) / 128u)
-            asm volatile("prefetch.global.L2 [%0];" ::"l"(reinterpret_cast<const uint8_t*>(&table[ph + 1u]) + threadIdx.x * 128u));
+        const PassPhase& phase = *reinterpret_cast<const PassPhase*>(entries[ph & 1u]);
+        if (ph + 1u < count && threadIdx.x < kPhaseChunks)
+            copy_async_16(entries[(ph + 1u) & 1u] + threadIdx.x * 16u, reinterpret_cast<const uint8_t*>(&table[ph + 1u]) + threadIdx.x * 16u);
         // What phase ph reads was written before barrier ph - 1; the launch's first phase follows stream order.
         auto dependency = [&]() -> bool {
             if (ph == 0u) return true;
-            return grid_wait(arrived, ph * gridDim.x, error_flag, poll_limit, &wait_outcome);
+            return grid_wait(arrived, base + ph * gridDim.x, error_flag, poll_limit, &wait_outcome);
         };
         if (phase.kind == kPhaseStream) {
             ok = stream_phase_call<ROWS>(phase.stream, sm, ring, scratch, &bad_rows, dependency);
@@ -123,14 +140,11 @@ __global__ void __launch_bounds__(kGemvWarps * 32, 1) decode_pass_kernel(const P
                                blockIdx.x * blockDim.x + threadIdx.x, gridDim.x * blockDim.x);
             }
         }
-        // The CTA agrees on the outcome, then arrives: after the last phase too, so that the CTA that
-        // arrives last of all knows every poll of this launch is over and puts the counter back to zero.
+        copy_async_wait();            // this thread's piece of the next entry has landed; the barrier below publishes it
+        // The CTA agrees on the outcome, then arrives (the last phase needs no barrier behind it).
         ok = __syncthreads_or(ok ? 0 : 1) == 0;
         if (!ok) break;
-        if (threadIdx.x == 0) {
-            const uint32_t before = grid_arrive(arrived);
-            if (before + 1u == count * gridDim.x) atomicExch(arrived, 0u);
-        }
+        if (threadIdx.x == 0 && ph + 1u < count) grid_arrive(arrived);
     }
     if (!ok) {
         if (threadIdx.x == 0) atomicExch(error_flag, 1);          // first, so that the other CTAs stop polling at once
@@ -196,7 +210,8 @@ static int launch_pass_instance(const PassLaunch& launch, cudaStream_t stream) {
     config.attrs = &attribute;
     config.numAttrs = 1;
     GF_CUDA(cudaLaunchKernelEx(&config, decode_pass_kernel<ROWS>, launch.table_dev + launch.first, launch.count,
-                               launch.first_stream, launch.last_stream, launch.arrived_dev, launch.error_flag, launch.poll_limit));
+                               launch.first_stream, launch.last_stream, launch.arrived_dev, launch.base, launch.error_flag,
+                               launch.poll_limit));
     return GF_OK;
 }
 

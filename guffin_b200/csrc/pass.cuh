@@ -48,7 +48,8 @@ struct PassLaunch {
     uint32_t first_stream = ~0u, last_stream = ~0u;   // first and last streaming phase among them, counted from `first` (~0: none)
     uint32_t rows = 1;                      // 1 or 2: the kernel instance
     uint32_t smem_bytes = 0;                // pass_smem_bytes of the table
-    uint32_t* arrived_dev = nullptr;        // barrier word, zero between launches
+    uint32_t* arrived_dev = nullptr;        // barrier counter: only ever grows, by (count - 1) * SM count per launch
+    uint32_t base = 0;                      // its value when this launch starts (the host keeps count; modulo 2^32)
     int* error_flag = nullptr;
     uint32_t poll_limit = kPassDefaultPollLimit;
 };
