@@ -870,18 +870,17 @@ __device__ __forceinline__ uint32_t matrix_of_pair(const WeightStreamParams& p, 
 // Ring slot of a pass kernel: two Q4_K / Q8_0 pair rows or one Q6_K pair row.
 constexpr uint32_t kPassSlotBytes = 4608u;
 
-// The cursor's phase-level state, one record per warp in shared memory (only lane 0 touches it, and only
-// when it starts a new item): which launch / phase the cursor is in and this warp's share of it.
+// The cursor's phase-level state inside a pass kernel, one record per warp in shared memory (only lane 0
+// touches it, and only when it starts a new item): which phase the cursor is in and this warp's share
+// of it.  A single launch needs none of it: its parameters and the warp's share are at hand.
 struct WeightCursor {
     const WeightStreamParams* phase;     // null when nothing is left
-    const WeightStreamParams* last;      // last streaming phase of the pass kernel's table (== phase for a single launch)
+    const WeightStreamParams* last;      // last streaming phase of the pass kernel's table
     uint32_t phase_stride;               // bytes between consecutive table entries
-    uint32_t items_left;                 // items of `phase` not yet started
-    uint32_t next_pair;                  // column pair of the next item
     uint32_t stride, first_unit, chunk_count;      // of this warp's share of `phase`
 };
 
-// A warp's ring: the slots, and the cursor's per-copy state in registers (meaningful in lane 0).
+// A warp's ring: the slots, and the cursor's state in registers (meaningful in lane 0).
 struct WeightRing {
     uint8_t* slots;          // this warp's kGemvSlots slots
     uint64_t* bars;          // and their barriers
@@ -892,6 +891,8 @@ struct WeightRing {
     const uint8_t* src;      // next bytes of the item being requested
     uint32_t units_left;     // K units of that item not yet requested (0: start the next item)
     uint32_t row_bytes, slot_units;
+    uint32_t items_left;     // items of the cursor's launch / phase not yet started
+    uint32_t next_pair;      // column pair of the next item
 };
 
 // Pair rows one slot carries for a matrix of `dtype`.
@@ -906,47 +907,55 @@ __device__ __forceinline__ const WeightStreamParams* phase_stream_params(const u
     return reinterpret_cast<const WeightStreamParams*>(entry + 16u);
 }
 
-__device__ __forceinline__ void cursor_enter(WeightCursor& c, const WeightStreamParams* phase, uint32_t block, uint32_t warp) {
+__device__ __forceinline__ void cursor_enter(WeightRing& ring, const WeightStreamParams* phase, uint32_t block, uint32_t warp) {
+    WeightCursor& c = *ring.cursor;
     c.phase = phase;
-    if (phase == nullptr) { c.items_left = 0; return; }
+    if (phase == nullptr) { ring.items_left = 0; return; }
     const WarpShare w = warp_share(*phase, block, warp);
-    c.items_left = w.my_items; c.next_pair = w.first_pair; c.stride = w.stride;
-    c.first_unit = w.first_unit; c.chunk_count = w.chunk_count;
+    ring.items_left = w.my_items; ring.next_pair = w.first_pair;
+    c.stride = w.stride; c.first_unit = w.first_unit; c.chunk_count = w.chunk_count;
 }
 
-// Starts the next item (lane 0 only): false when no item is left in this launch / pass.
+// Points the cursor at the warp's next item of launch / phase `p` (lane 0 only).
 template <bool PASS>
-__device__ __forceinline__ bool ring_next_item(WeightRing& ring, uint32_t block, uint32_t warp) {
-    WeightCursor& c = *ring.cursor;
-    while (c.items_left == 0u) {
-        if (c.phase == nullptr) return false;
-        if (!PASS || c.phase == c.last) { c.phase = nullptr; return false; }
-        // On to the next streaming phase of the table.
-        const uint8_t* entry = reinterpret_cast<const uint8_t*>(c.phase) - 16u;
-        const uint8_t* last_entry = reinterpret_cast<const uint8_t*>(c.last) - 16u;
-        const WeightStreamParams* next = nullptr;
-        while (entry != last_entry) {
-            entry += c.phase_stride;
-            if (*reinterpret_cast<const uint32_t*>(entry) == kPhaseStream) { next = phase_stream_params(entry); break; }
-        }
-        cursor_enter(c, next, block, warp);
-    }
-    const WeightStreamParams& p = *c.phase;
-    const uint32_t pair = c.next_pair;
-    c.next_pair += c.stride;
-    --c.items_left;
+__device__ __forceinline__ void ring_take_item(WeightRing& ring, const WeightStreamParams& p, uint32_t stride, uint32_t first_unit,
+                                               uint32_t chunk_count) {
+    const uint32_t pair = ring.next_pair;
+    ring.next_pair += stride;
+    --ring.items_left;
     const GemvMatrix& mat = p.m[matrix_of_pair(p, pair)];
     ring.row_bytes = pair_row_bytes((int)mat.dtype);
     ring.slot_units = ring_slot_units<PASS>(p, mat.dtype);
-    ring.src = mat.weight + ((size_t)(pair - mat.first_pair) * p.units + c.first_unit) * ring.row_bytes;
-    ring.units_left = c.chunk_count;
-    return true;
+    ring.src = mat.weight + ((size_t)(pair - mat.first_pair) * p.units + first_unit) * ring.row_bytes;
+    ring.units_left = chunk_count;
 }
 
-// Requests the next slot-full of pair rows (lane 0 only).
+// Requests the next slot-full of pair rows (lane 0 only).  `p` and `w` are the launch's parameters and
+// the warp's share of it; a pass kernel's cursor uses its own record instead, since it may be a phase ahead.
 template <bool PASS>
-__device__ __forceinline__ void ring_issue(WeightRing& ring, uint32_t block, uint32_t warp) {
-    if (ring.units_left == 0u && !ring_next_item<PASS>(ring, block, warp)) return;
+__device__ __forceinline__ void ring_issue(WeightRing& ring, const WeightStreamParams& p, const WarpShare& w, uint32_t block, uint32_t warp) {
+    if (ring.units_left == 0u) {
+        if (!PASS) {
+            if (ring.items_left == 0u) return;
+            ring_take_item<false>(ring, p, w.stride, w.first_unit, w.chunk_count);
+        } else {
+            WeightCursor& c = *ring.cursor;
+            while (ring.items_left == 0u) {
+                if (c.phase == nullptr) return;
+                if (c.phase == c.last) { c.phase = nullptr; return; }
+                // On to the next streaming phase of the table.
+                const uint8_t* entry = reinterpret_cast<const uint8_t*>(c.phase) - 16u;
+                const uint8_t* last_entry = reinterpret_cast<const uint8_t*>(c.last) - 16u;
+                const WeightStreamParams* next = nullptr;
+                while (entry != last_entry) {
+                    entry += c.phase_stride;
+                    if (*reinterpret_cast<const uint32_t*>(entry) == kPhaseStream) { next = phase_stream_params(entry); break; }
+                }
+                cursor_enter(ring, next, block, warp);
+            }
+            ring_take_item<true>(ring, *c.phase, c.stride, c.first_unit, c.chunk_count);
+        }
+    }
     const uint32_t count = min(ring.slot_units, ring.units_left), bytes = count * ring.row_bytes;
     const uint32_t slot = ring.issued % (uint32_t)kGemvSlots;
     mbar_expect_tx(&ring.bars[slot], bytes);
@@ -1077,7 +1086,7 @@ __device__ __forceinline__ bool stream_phase(const WeightStreamParams& p, const 
             }
             __syncwarp();   // every lane has finished reading this slot
             ++ring.consumed;
-            if (lane == 0) ring_issue<PASS>(ring, blockIdx.x, warp);
+            if (lane == 0) ring_issue<PASS>(ring, p, w, blockIdx.x, warp);
         }
         if (failed && !intra) break;      // inside a CTA the other chunks' warps wait at the meeting barrier
         // Row r is the sum of B columns 4r .. 4r+3 (digit 0 first; held by quad lanes (n % 8) / 2 of
@@ -1169,8 +1178,9 @@ __device__ __forceinline__ bool stream_phase(const WeightStreamParams& p, const 
     return !failed;
 }
 
-// Sets up this warp's ring over the CTA's shared memory: barriers initialised, cursor at the first
-// item of `first` (a single launch: last == first).  Ends with a block barrier.
+// Sets up this warp's ring over the CTA's shared memory: barriers initialised, the cursor at the warp's
+// first item of `first` (a single launch: last == first, and the cursor lives in registers alone), the
+// first copies requested.  Contains a block barrier.
 template <bool PASS>
 __device__ __forceinline__ WeightRing ring_open(const StreamSmem& sm, uint32_t slot_bytes, const WeightStreamParams* first,
                                                 const WeightStreamParams* last, uint32_t phase_stride) {
@@ -1182,17 +1192,25 @@ __device__ __forceinline__ WeightRing ring_open(const StreamSmem& sm, uint32_t s
     ring.cursor = sm.cursors + warp;
     ring.consumed = 0; ring.issued = 0;
     ring.src = nullptr; ring.units_left = 0; ring.row_bytes = 0; ring.slot_units = 1;
+    ring.items_left = 0; ring.next_pair = 0;
+    WarpShare w = {};
+    if (!PASS) {
+        w = warp_share(*first, blockIdx.x, warp);
+        ring.items_left = w.my_items; ring.next_pair = w.first_pair;
+    }
     if (lane == 0) {
         for (int s = 0; s < kGemvSlots; ++s) mbar_init(&ring.bars[s], 1);
         fence_barrier_init();
-        WeightCursor& c = *ring.cursor;
-        c.last = last; c.phase_stride = phase_stride;
-        cursor_enter(c, first, blockIdx.x, warp);
+        if (PASS) {
+            WeightCursor& c = *ring.cursor;
+            c.last = last; c.phase_stride = phase_stride;
+            cursor_enter(ring, first, blockIdx.x, warp);
+        }
     }
     __syncthreads();
     // Weights do not depend on anything computed on the device: start streaming at once.
-    if (lane == 0)
-        for (int j = 0; j < kGemvSlots; ++j) ring_issue<PASS>(ring, blockIdx.x, warp);
+    if (lane == 0 && first != nullptr)
+        for (int j = 0; j < kGemvSlots; ++j) ring_issue<PASS>(ring, *first, w, blockIdx.x, warp);
     return ring;
 }
 

@@ -144,7 +144,7 @@ private:
     cudaGraphExec_t graphs_[GF_MAX_ROWS + 1][2] = {};
     uint32_t graph_launches_[GF_MAX_ROWS + 1][2] = {};      // kernel nodes of each recorded graph
     // Decode pass kernel: recorded tables per (rows, logits), one for the weight sweep per rows.
-    int pass_mode_ = 1, recorded_mode_ = -1;
+    int pass_mode_ = 0, recorded_mode_ = -1;
     RecordedPass passes_[kPassMaxRows + 1][2], sweeps_[kPassMaxRows + 1];
     uint32_t* pass_arrived_ = nullptr;
     uint32_t pass_arrivals_ = 0;                             // value of *pass_arrived_ once every launch so far has finished

@@ -1,0 +1,65 @@
+// Prompt ingestion as a dense contraction on the fifth-generation tensor cores (tcgen05 + TMEM).
+//
+// A chunk of up to 128 prompt rows goes through each projection as ONE GEMM
+//     C[128, N] = A[128, K] (bf16 activations) x deq(W)[N, K]^T (bf16, dequantised in shared memory)
+// so the quantised weights are read once per 128 rows instead of once per row pair
+// (run_gemma3_resident_prefill, src/engine/gemma_target_runtime.cpp:420-455; the reference's matrix
+// kernel is gemma3_matmul_f32_kquant_matrix_impl, metal_kernels.mm:1031-1199).
+//
+// Operands in shared memory use the tensor core's K-major layout without swizzle: a "core matrix" is
+// 8 rows x 16 bytes (8 bf16 along K) stored as 128 contiguous bytes; inside a block of 64 K elements
+// the core matrices of one 8-row group lie 128 bytes apart along K and the row groups 1024 bytes apart.
+// The activations are kept in global memory already in that order ("tile-major": one 16-KB block per
+// 64 K elements holding all 128 rows), so a CTA fetches a block with one bulk copy.
+#pragma once
+
+#include "common.cuh"
+
+namespace gf {
+
+constexpr uint32_t kPrefillRows = 128;          // rows of one chunk = M of the tensor-core instruction
+constexpr uint32_t kPrefillTile = 128;          // output columns per CTA
+constexpr uint32_t kPrefillBlockK = 64;         // K elements per shared-memory stage
+constexpr uint32_t kPrefillThreads = 256;
+constexpr uint32_t kPrefillBlockBytes = kPrefillRows * kPrefillBlockK * 2u;      // one tile-major activation block
+
+// Byte offset of element (row, k) in a tile-major bf16 activation buffer.
+__host__ __device__ inline size_t tile_major_offset(uint32_t row, uint32_t k) {
+    return (size_t)(k / kPrefillBlockK) * kPrefillBlockBytes + (row / 8u) * 1024u + ((k % kPrefillBlockK) / 8u) * 128u
+           + (row % 8u) * 16u + (k % 8u) * 2u;
+}
+inline size_t tile_major_bytes(uint64_t k) { return (size_t)((k + kPrefillBlockK - 1u) / kPrefillBlockK) * kPrefillBlockBytes; }
+
+struct PrefillMatrix {
+    const uint8_t* weight;      // streaming layout (the same bytes the decode kernels read)
+    float* out;                 // [128][n] f32
+    uint32_t n, dtype, first_tile;
+};
+
+struct PrefillGemmParams {
+    PrefillMatrix m[3];
+    uint32_t matrices, tiles;   // tiles over all matrices (n / kPrefillTile each)
+    uint32_t k, units, unit_elems;
+    const uint8_t* a;           // tile-major bf16 activations, `k` wide
+    int* error_flag;
+};
+
+struct PrefillGemmLaunch {
+    struct Matrix { int dtype; const void* packed; float* out; uint64_t n; } matrices[3];
+    uint32_t count = 1;
+    uint64_t k = 0;
+    const void* a = nullptr;
+};
+int launch_prefill_gemm(const PrefillGemmLaunch& launch, int* error_flag, cudaStream_t stream);
+
+// Elementwise steps between the GEMMs, each writing the next GEMM's tile-major bf16 operand.
+// mode 0: a = rmsnorm(x; gamma1)
+// mode 1: r = residual + rmsnorm(x; gamma0) -> residual_out;  a = rmsnorm(r; gamma1)     (gamma1 null: only residual_out)
+int launch_prefill_norm(const float* x, const float* residual, const float* gamma0, const float* gamma1, float* residual_out,
+                        void* a_out, uint32_t rows, uint32_t k, float eps, int mode, cudaStream_t stream);
+// a = gelu_tanh(gate) * up
+int launch_prefill_geglu(const float* gate, const float* up, void* a_out, uint32_t rows, uint32_t k, cudaStream_t stream);
+// a = x (f32 rows of width k)
+int launch_prefill_pack(const float* x, void* a_out, uint32_t rows, uint32_t k, cudaStream_t stream);
+
+}  // namespace gf

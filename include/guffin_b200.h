@@ -270,13 +270,15 @@ GF_API size_t gf_model_weight_bytes(const gf_model* model, int native);
 GF_API size_t gf_model_kv_bytes_per_pass(const gf_model* model, uint32_t rows);
 GF_API uint32_t gf_model_kernel_launches(const gf_model* model);
 GF_API int gf_model_use_graph(gf_model* model, int enable);
-/* How passes of one or two rows (decode, drafting, verification) are scheduled.  mode 1 (default): one
+/* How passes of one or two rows (decode, drafting, verification) are scheduled.  mode 0 (default): one
+ * kernel per operator with programmatic dependent launch, replayed as a CUDA graph.  mode 1: one
  * persistent "decode pass" kernel, one CTA per SM, walks the whole block schedule of
  * encode_gemma_target_blocks (gemma_target_runtime.cpp:13-221) with grid-wide barriers between its
  * operators and keeps streaming the next matrix's weights while it waits; attention runs inside it for
  * a binary16 cache and as launches of its own between kernel segments otherwise.  mode 2: as 1 with
- * attention always as launches of its own.  mode 0: one kernel per operator, replayed as a CUDA graph.
- * All modes compute bit-identical results.  Wider passes (prompt ingestion) always use mode 0. */
+ * attention always as launches of its own.  All modes compute bit-identical results; mode 0 measured
+ * fastest on B200 (a grid barrier costs more than a dependent-launch boundary).  Wider passes (prompt
+ * ingestion) never use the pass kernel. */
 GF_API int gf_model_use_pass_kernel(gf_model* model, int mode);
 /* Enqueues exactly the weight-streaming GEMVs of one `rows`-row pass (every projection of every
  * layer and the output head, in schedule order) and nothing else: the measurement the

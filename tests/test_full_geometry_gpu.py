@@ -67,7 +67,14 @@ def test_270m_greedy_256_after_512_token_prompt(gf, ge, gm, all_cores):
     print(f"270M greedy-256: worst oracle margin {worst:.3e}, {disagreements} steps chose a tie within tolerance")
     # One more row on both sides: full logits agree, not only the argmax.
     model.forward([int(tokens[-1])], logits=True)
-    assert rel_l2(model.logits(0), logits) < 1e-3
+    plain = model.logits(0).copy()
+    assert rel_l2(plain, logits) < 1e-3
+    # The same row through the persistent decode pass kernel (its attention stays a launch of its own for an
+    # f32 cache): bit-identical at this geometry too.
+    model.use_pass_kernel(1)
+    model.forward([int(tokens[-1])], logits=True)
+    np.testing.assert_array_equal(model.logits(0), plain)
+    assert model.status() == 0
 
 
 def _assert_same_candidates(model, gm, got_logits, want_logits, retain=40):
@@ -133,8 +140,15 @@ def test_12b_two_row_verification_matches_oracle_at_short_and_long_context(gf, g
     want = [ref.append(tokens[base]), ref.append(tokens[base + 1])]
     long_errors = [rel_l2(model.logits(row), want[row]) for row in range(2)]
     assert max(long_errors) < 1e-3
+    plain = [model.logits(row).copy() for row in range(2)]
     for row in range(2):
-        _assert_same_candidates(model, gm, model.logits(row), want[row])
+        _assert_same_candidates(model, gm, plain[row], want[row])
+    # The same two rows through the persistent decode pass kernel (attention inside it, several partitions,
+    # the 1024-row window): bit-identical to the kernel-per-operator schedule at this geometry.
+    model.use_pass_kernel(1)
+    model.forward(tokens[base:base + 2], logits=True)
+    for row in range(2):
+        np.testing.assert_array_equal(model.logits(row), plain[row])
     assert model.status() == 0
     print(f"12B verify parity: rel-L2 short context {max(errors):.2e}, at position {base} {max(long_errors):.2e}")
 
