@@ -211,44 +211,45 @@ __global__ void __launch_bounds__(kPrefillThreads, 1) prefill_gemm_kernel(const 
     };
     if (tid == 0) request_weights(0);
 
+    // A wait that gives up is agreed on by the whole CTA at the next block barrier, so that every thread
+    // leaves the loops at the same place.
     bool failed = false;
     uint32_t step = 0;                                 // stages used so far
     for (uint32_t unit = 0; unit < p.units && !failed; ++unit) {
-        if (!mbar_wait(&weight_bar[unit & 1u], (unit >> 1) & 1u)) { failed = true; break; }
+        bool bad = !mbar_wait(&weight_bar[unit & 1u], (unit >> 1) & 1u);
         // The other weight buffer was last read while unit - 1 was dequantised, which ended with a block barrier.
-        if (tid == 0 && unit + 1u < p.units) request_weights(unit + 1u);
+        if (tid == 0 && !bad && unit + 1u < p.units) request_weights(unit + 1u);
         const uint8_t* pair_row = smem + kOffW + (unit & 1u) * kWeightBufBytes + warp * row_bytes;
         for (uint32_t sub = 0; sub < subs; ++sub, ++step) {
             const uint32_t stage = step % kStages, use = step / kStages;
             // The stage's previous tensor-core reads must be over before it is overwritten.
-            if (use > 0u && !mbar_wait(&mma_bar[stage], (use - 1u) & 1u)) { failed = true; break; }
+            if (!bad && use > 0u && !mbar_wait(&mma_bar[stage], (use - 1u) & 1u)) bad = true;
             uint8_t* a_stage = smem + kOffA + stage * kAStageBytes;
             uint8_t* b_stage = smem + kOffB + stage * kBStageBytes;
-            if (tid == 0) {
-                mbar_expect_tx(&a_bar[stage], kAStageBytes);
-                bulk_load(a_stage, p.a + (size_t)(unit * subs + sub) * kPrefillBlockBytes, kAStageBytes, &a_bar[stage]);
-            }
-            if (dtype == GF_Q4_K) dequant_q4k(pair_row, sub, lane, warp * 16u, b_stage);
-            else if (dtype == GF_Q6_K) dequant_q6k(pair_row, sub, lane, warp * 16u, b_stage);
-            else dequant_q80(pair_row, sub, lane, warp * 16u, b_stage);
-            fence_async_smem();
-            __syncthreads();
-            if (tid == 0) {
-                if (!mbar_wait(&a_bar[stage], use & 1u)) { failed = true; }
-                else {
-                    tc_fence_after_sync();
-                    const uint32_t a_address = smem_u32(a_stage), b_address = smem_u32(b_stage);
-#pragma unroll
-                    for (uint32_t kk = 0; kk < kPrefillBlockK / 16u; ++kk)
-                        mma_bf16(tmem, operand_descriptor(a_address + kk * 256u), operand_descriptor(b_address + kk * 256u),
-                                 (step | kk) != 0u ? 1u : 0u);
-                    mma_commit(&mma_bar[stage]);
+            if (!bad) {
+                if (tid == 0) {
+                    mbar_expect_tx(&a_bar[stage], kAStageBytes);
+                    bulk_load(a_stage, p.a + (size_t)(unit * subs + sub) * kPrefillBlockBytes, kAStageBytes, &a_bar[stage]);
                 }
+                if (dtype == GF_Q4_K) dequant_q4k(pair_row, sub, lane, warp * 16u, b_stage);
+                else if (dtype == GF_Q6_K) dequant_q6k(pair_row, sub, lane, warp * 16u, b_stage);
+                else dequant_q80(pair_row, sub, lane, warp * 16u, b_stage);
+                fence_async_smem();
+                if (tid == 0 && !mbar_wait(&a_bar[stage], use & 1u)) bad = true;
+            }
+            failed = __syncthreads_or(bad ? 1 : 0) != 0;
+            if (failed) break;
+            if (tid == 0) {
+                tc_fence_after_sync();
+                const uint32_t a_address = smem_u32(a_stage), b_address = smem_u32(b_stage);
+#pragma unroll
+                for (uint32_t kk = 0; kk < kPrefillBlockK / 16u; ++kk)
+                    mma_bf16(tmem, operand_descriptor(a_address + kk * 256u), operand_descriptor(b_address + kk * 256u),
+                             (step | kk) != 0u ? 1u : 0u);
+                mma_commit(&mma_bar[stage]);
             }
         }
     }
-    // Thread 0's failure must reach everybody, and everybody's reaches thread 0.
-    failed = __syncthreads_or(failed ? 1 : 0) != 0;
     if (!failed) {
         if (tid == 0) mma_commit(done_bar);
         if (!mbar_wait(done_bar, 0u)) failed = true;
@@ -269,8 +270,6 @@ __global__ void __launch_bounds__(kPrefillThreads, 1) prefill_gemm_kernel(const 
         }
         tc_fence_before_sync();
     } else if (tid == 0) {
-        // Give copies in flight a bounded chance to land before the shared memory goes away.
-        mbar_wait(&weight_bar[0], 0u);
         atomicExch(p.error_flag, 1);
     }
     __syncthreads();
@@ -406,3 +405,46 @@ int launch_prefill_pack(const float* x, void* a_out, uint32_t rows, uint32_t k, 
 }
 
 }  // namespace gf
+
+using namespace gf;
+
+extern "C" {
+
+size_t gf_prefill_workspace_bytes(uint64_t k) { return tile_major_bytes(k); }
+
+int gf_prefill_matmul(int dtype, const void* packed_dev, const float* x_dev, float* y_dev, uint32_t rows, uint64_t k, uint64_t n,
+                      void* workspace_dev, void* stream) {
+    if (!packed_dev || !x_dev || !y_dev || !workspace_dev || rows == 0 || rows > kPrefillRows)
+        return fail(GF_ERR_INVALID, "gf_prefill_matmul: null buffer or rows outside [1, %u]", kPrefillRows);
+    if ((reinterpret_cast<uintptr_t>(y_dev) | reinterpret_cast<uintptr_t>(workspace_dev)) & 15u)
+        return fail(GF_ERR_INVALID, "gf_prefill_matmul: y and the workspace must be 16-byte aligned");
+    static int* flags[64] = {nullptr};
+    int device = 0;
+    GF_CUDA(cudaGetDevice(&device));
+    device &= 63;
+    if (!flags[device]) {
+        GF_CUDA(cudaMalloc(&flags[device], sizeof(int)));
+        GF_CUDA(cudaMemset(flags[device], 0, sizeof(int)));
+    }
+    cudaStream_t s = as_stream(stream);
+    const int status = launch_prefill_pack(x_dev, workspace_dev, rows, (uint32_t)k, s);
+    if (status != GF_OK) return status;
+    PrefillGemmLaunch launch;
+    launch.matrices[0] = {dtype, packed_dev, y_dev, n};
+    launch.count = 1;
+    launch.k = k;
+    launch.a = workspace_dev;
+    const int launched = launch_prefill_gemm(launch, flags[device], s);
+    if (launched != GF_OK) return launched;
+    int value = 0;
+    GF_CUDA(cudaMemcpyAsync(&value, flags[device], sizeof(int), cudaMemcpyDeviceToHost, s));
+    GF_CUDA(cudaStreamSynchronize(s));
+    if (value != 0) {
+        cudaMemsetAsync(flags[device], 0, sizeof(int), s);
+        return fail(GF_ERR_TIMEOUT, "gf_prefill_matmul: a bounded wait gave up");
+    }
+    return GF_OK;
+}
+
+}  // extern "C"
+

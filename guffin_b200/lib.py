@@ -73,6 +73,7 @@ def _declare(L: C.CDLL) -> None:
         "gf_matmul_host": [i32, vp, vp, vp, u32, u64, u64],
         "gf_matmul_static": [i32, vp, vp, vp, u32, u64, u64, vp],
         "gf_matmul_static_check": [vp],
+        "gf_prefill_matmul": [i32, vp, vp, vp, u32, u64, u64, vp, vp],
     }
     for name, args in sigs.items():
         fn = getattr(L, name)
@@ -82,6 +83,8 @@ def _declare(L: C.CDLL) -> None:
     L.gf_packed_weight_bytes.restype = sz
     L.gf_matmul_workspace_bytes.argtypes = [i32, u32, u64, u64]
     L.gf_matmul_workspace_bytes.restype = sz
+    L.gf_prefill_workspace_bytes.argtypes = [u64]
+    L.gf_prefill_workspace_bytes.restype = sz
     L.gf_matmul_static_capacity.argtypes = []
     L.gf_matmul_static_capacity.restype = sz
     _apply(L, SIGNATURES)
@@ -240,6 +243,21 @@ def matmul(weight: PackedWeight, x: np.ndarray) -> np.ndarray:
     for b in (xd, yd, ws):
         if b:
             b.free()
+    return y
+
+
+def prefill_matmul(weight: PackedWeight, x: np.ndarray) -> np.ndarray:
+    """y = x @ deq(W)^T for up to 128 rows on the tensor cores (bf16 operands, f32 accumulation)."""
+    L = load()
+    x = np.ascontiguousarray(x, np.float32).reshape(-1, weight.k)
+    rows = x.shape[0]
+    xd = DeviceBuffer.from_numpy(x)
+    yd = DeviceBuffer(128 * weight.n * 4)
+    ws = DeviceBuffer(L.gf_prefill_workspace_bytes(weight.k))
+    check(L.gf_prefill_matmul(weight.dtype, weight.packed.ptr, xd.ptr, yd.ptr, rows, weight.k, weight.n, ws.ptr, None))
+    y = yd.download(np.float32).reshape(128, weight.n)
+    for b in (xd, yd, ws):
+        b.free()
     return y
 
 

@@ -119,6 +119,18 @@ GF_API size_t gf_matmul_static_capacity(void);
 GF_API int gf_matmul_static(int dtype, const void* packed_dev, const float* x_dev, float* y_dev,
                             uint32_t rows, uint64_t k, uint64_t n, void* stream);
 GF_API int gf_matmul_static_check(void* stream);
+/* The same product for up to 128 rows at once as a dense contraction on the tensor cores: bf16
+ * activations, weights dequantised to bf16 in shared memory, f32 accumulation (tcgen05 / TMEM).  The
+ * prompt-ingestion shape of encode_verifier_matmul with allow_prefill_matrix
+ * (metal_command_context.hpp:94-101; MSL gemma3_matmul_f32_kquant_matrix_impl, metal_kernels.mm:1031-1199;
+ * the reference's Gemma 2 path uses half operands the same way, gemma2_runtime.cpp:893-1170).
+ * y_dev holds 128 rows of n floats (rows beyond `rows` are written as zeros); n must be a multiple of 128,
+ * k of 256 (128 for Q8_0); workspace_dev holds gf_prefill_workspace_bytes(k) bytes (the activations in the
+ * tensor core's operand order).  Synchronises the stream and returns GF_ERR_TIMEOUT if a bounded wait
+ * gave up.  Differs from gf_matmul by the bf16 rounding of both operands (about 4e-3 relative L2). */
+GF_API size_t gf_prefill_workspace_bytes(uint64_t k);
+GF_API int gf_prefill_matmul(int dtype, const void* packed_dev, const float* x_dev, float* y_dev,
+                             uint32_t rows, uint64_t k, uint64_t n, void* workspace_dev, void* stream);
 /* Same product from HOST buffers through an internal context: uploads x, runs, downloads y.
  * `packed_dev` stays device-resident (weights are uploaded once at load time). */
 GF_API int gf_matmul_host(int dtype, const void* packed_dev, const float* x_host, float* y_host,
