@@ -99,19 +99,10 @@ public:
         pending_ = false;
         draft_exhausted_ = false;
         GF_TRY(target_.prefill(tokens, count));
-        if (draft_ && options_.speculative) {
-            // The drafter ingests the same prompt; its last logits are not needed.
-            uint32_t done = 0;
-            while (done < count) {
-                const uint32_t rows = std::min(draft_->config().row_capacity, count - done);
-                GF_TRY(draft_->forward(tokens + done, rows, 0));
-                GF_TRY(draft_->publish(rows));
-                done += rows;
-            }
-        }
+        if (draft_ && options_.speculative) GF_TRY(draft_->prefill(tokens, count));      // the drafter ingests the same prompt
         sampler_.observe(tokens, count);
         // First token: ordinary sample from the prompt's last row.
-        const uint32_t last_row = (count - 1u) % target_.config().row_capacity;
+        const uint32_t last_row = target_.prefill_logits_row();
         const SelectionHistory request = sampler_.request_after(nullptr, 0);
         GF_TRY(select_and_read(request, last_row));
         GF_TRY(sampler_.sample(results_host_[0].candidates, results_host_[0].count, request, root_));

@@ -441,6 +441,12 @@ __device__ __forceinline__ void load8f_cg(const float* p, float (&v)[8]) {
     const float4 a = __ldcg(reinterpret_cast<const float4*>(p)), b = __ldcg(reinterpret_cast<const float4*>(p + 4));
     v[0] = a.x; v[1] = a.y; v[2] = a.z; v[3] = a.w; v[4] = b.x; v[5] = b.y; v[6] = b.z; v[7] = b.w;
 }
+// Activations of a launch of its own come through L1 like any other load (nothing on this SM can hold an
+// older copy: L1 starts empty with the launch); a phase of a pass kernel reads them from L2.
+template <bool FROM_L2>
+__device__ __forceinline__ void load8f_act(const float* p, float (&v)[8]) {
+    if (FROM_L2) load8f_cg(p, v); else load8f(p, v);
+}
 __device__ __forceinline__ void store8f(float* p, const float (&v)[8]) {
     *reinterpret_cast<float4*>(p) = make_float4(v[0], v[1], v[2], v[3]);
     *reinterpret_cast<float4*>(p + 4) = make_float4(v[4], v[5], v[6], v[7]);
@@ -535,7 +541,7 @@ __device__ __forceinline__ bool gemv_prologue_cached(const WeightStreamParams& p
     return ROWS <= 4 && norms && p.k / 8u <= blockDim.x && (first & 255u) == 0u;
 }
 
-template <int ROWS>
+template <int ROWS, bool PASS>
 __device__ __forceinline__ void stage_early(const WeightStreamParams& p, uint32_t first, GemvEarly<ROWS>& early) {
     early.cached = gemv_prologue_cached<ROWS>(p, first);
     if (!early.cached) return;
@@ -551,7 +557,7 @@ __device__ __forceinline__ void stage_early(const WeightStreamParams& p, uint32_
         load8f(p.gamma0 + o, early.g0);
 #pragma unroll
         for (int r = 0; r < ROWS; ++r)
-            if ((uint32_t)r < p.active_rows) load8f_cg(p.residual + (size_t)r * p.k + o, early.res[r]);
+            if ((uint32_t)r < p.active_rows) load8f_act<PASS>(p.residual + (size_t)r * p.k + o, early.res[r]);
     }
     load8f(p.gamma1 + o, early.g1);
 }
@@ -597,7 +603,7 @@ __device__ __forceinline__ void merge_head_piece(const WeightStreamParams& p, ui
 // memory (a few tens of KB out of L2).  In the register-resident case everything a thread needs
 // of the launch ahead's output is loaded once and kept in registers through both norms (the rest
 // came in with stage_early); otherwise the row is re-read for each pass.
-template <int ROWS>
+template <int ROWS, bool PASS>
 __device__ __forceinline__ void stage_activations(const WeightStreamParams& p, uint32_t first, uint32_t count,
                                                   const GemvStage& st, float* scratch, GemvEarly<ROWS>& early) {
     const bool norms = p.prologue == kPrologueNorm || p.prologue == kPrologueAddNorm;
@@ -617,7 +623,7 @@ __device__ __forceinline__ void stage_activations(const WeightStreamParams& p, u
         if (live) {
 #pragma unroll
             for (int r = 0; r < ROWS; ++r)
-                if ((uint32_t)r < p.active_rows) load8f_cg(p.in + (size_t)r * p.k + o, x[r]);
+                if ((uint32_t)r < p.active_rows) load8f_act<PASS>(p.in + (size_t)r * p.k + o, x[r]);
         }
         float ss[ROWS];
 #pragma unroll
@@ -656,7 +662,7 @@ __device__ __forceinline__ void stage_activations(const WeightStreamParams& p, u
             ss[r] = 0.0f;
             for (uint32_t c = threadIdx.x; c < row_pieces && (uint32_t)r < p.active_rows; c += blockDim.x) {
                 float x[8];
-                load8f_cg(p.in + (size_t)r * p.k + c * 8u, x);
+                load8f_act<PASS>(p.in + (size_t)r * p.k + c * 8u, x);
                 ss[r] = sum_squares(x, ss[r]);
             }
         }
@@ -670,8 +676,8 @@ __device__ __forceinline__ void stage_activations(const WeightStreamParams& p, u
                 ss[r] = 0.0f;
                 for (uint32_t c = threadIdx.x; c < row_pieces && (uint32_t)r < p.active_rows; c += blockDim.x) {
                     float x[8], a[8], gm[8];
-                    load8f_cg(p.in + (size_t)r * p.k + c * 8u, x);
-                    load8f_cg(p.residual + (size_t)r * p.k + c * 8u, a);
+                    load8f_act<PASS>(p.in + (size_t)r * p.k + c * 8u, x);
+                    load8f_act<PASS>(p.residual + (size_t)r * p.k + c * 8u, a);
                     load8f(p.gamma0 + c * 8u, gm);
 #pragma unroll
                     for (int i = 0; i < 8; ++i) x[i] = __fadd_rn(a[i], __fmul_rn(__fmul_rn(x[i], inv0[r]), gm[i]));
@@ -699,7 +705,7 @@ __device__ __forceinline__ void stage_activations(const WeightStreamParams& p, u
             float i0 = 1.0f, i1 = 1.0f;
 #pragma unroll
             for (int rr = 0; rr < ROWS; ++rr) if (rr == (int)r) { i0 = inv0[rr]; i1 = inv1[rr]; }
-            load8f_cg(p.in + gi, v);
+            load8f_act<PASS>(p.in + gi, v);
             if (p.prologue == kPrologueNorm) {
                 float gm[8];
                 load8f(p.gamma1 + c, gm);
@@ -707,7 +713,7 @@ __device__ __forceinline__ void stage_activations(const WeightStreamParams& p, u
                 for (int i = 0; i < 8; ++i) v[i] = __fmul_rn(__fmul_rn(v[i], i1), gm[i]);
             } else if (p.prologue == kPrologueAddNorm) {
                 float a[8], gm0[8], gm1[8];
-                load8f_cg(p.residual + gi, a);
+                load8f_act<PASS>(p.residual + gi, a);
                 load8f(p.gamma0 + c, gm0);
                 load8f(p.gamma1 + c, gm1);
 #pragma unroll
@@ -715,7 +721,7 @@ __device__ __forceinline__ void stage_activations(const WeightStreamParams& p, u
                     v[i] = __fmul_rn(__fmul_rn(__fadd_rn(a[i], __fmul_rn(__fmul_rn(v[i], i0), gm0[i])), i1), gm1[i]);
             } else if (p.prologue == kPrologueGeglu) {
                 float up[8];
-                load8f_cg(p.residual + gi, up);
+                load8f_act<PASS>(p.residual + gi, up);
 #pragma unroll
                 for (int i = 0; i < 8; ++i) v[i] = __fmul_rn(gelu_tanh_exact(v[i]), up[i]);
             }
@@ -989,7 +995,8 @@ __device__ __forceinline__ StreamSmem stream_smem(uint8_t* smem, uint32_t slot_b
 // One streaming launch, or one streaming phase of a pass kernel (PASS): stages this CTA's slice of the
 // activation rows once `dependency()` says the producer's outputs are visible, then every warp walks
 // its items.  `dependency` is called by every thread of the CTA exactly once and returns false when
-// the wait gave up; `scratch` holds 2 * kGemvWarps * ROWS floats, `bad_rows` one word.  Returns false
+// the wait gave up; `scratch` holds 2 * kGemvWarps * ROWS floats, `bad_rows` one word that the caller has
+// zeroed ahead of a block barrier.  Returns false
 // when a bounded wait gave up somewhere in this CTA (the error word is set by the caller).
 template <int ROWS, bool PASS, typename Dependency>
 __device__ __forceinline__ bool stream_phase(const WeightStreamParams& p, const StreamSmem& sm, WeightRing& ring_state,
@@ -1019,15 +1026,14 @@ __device__ __forceinline__ bool stream_phase(const WeightStreamParams& p, const 
     const uint32_t chunk = w.chunk, first_unit = w.first_unit, chunk_count = w.chunk_count, pair_slot = w.pair_slot;
     const uint32_t stride = w.stride, first_pair = w.first_pair, unit_base = w.unit_base, my_items = w.my_items;
 
-    if (threadIdx.x == 0) *bad_rows = 0u;
     GemvEarly<ROWS> early_inputs;
     early_inputs.cached = false;
-    if (member) stage_early<ROWS>(p, intra ? 0u : first_unit * p.unit_elems, early_inputs);
+    if (member) stage_early<ROWS, PASS>(p, intra ? 0u : first_unit * p.unit_elems, early_inputs);
 
     if (!dependency()) return false;
     if (member) {
         const GemvStage stage{frags, sums, block_scales, bad_rows, padded};
-        stage_activations<ROWS>(p, intra ? 0u : first_unit * p.unit_elems, intra ? p.k : chunk_count * p.unit_elems, stage, scratch, early_inputs);
+        stage_activations<ROWS, PASS>(p, intra ? 0u : first_unit * p.unit_elems, intra ? p.k : chunk_count * p.unit_elems, stage, scratch, early_inputs);
     }
     __syncthreads();
     if (!PASS) pdl_launch_dependents();
@@ -1220,6 +1226,7 @@ __global__ void __launch_bounds__(kGemvWarps * 32, 1) weight_stream_kernel(const
     __shared__ float scratch[2 * kGemvWarps * ROWS];
     __shared__ uint32_t bad_rows;
     const StreamSmem sm = stream_smem(smem, p.slot_bytes);
+    if (threadIdx.x == 0) bad_rows = 0u;
     WeightRing ring = ring_open<false>(sm, p.slot_bytes, &p, &p, 0u);
     const bool ok = stream_phase<ROWS, false>(p, sm, ring, scratch, &bad_rows, [] { pdl_wait(); return true; });
     if (!ok) {

@@ -582,16 +582,154 @@ int Model::truncate(uint32_t position) {
     return GF_OK;
 }
 
+// Prompts with at least this many rows ahead of their last token take the tensor-core path.
+constexpr uint32_t kTensorPrefillMinRows = 64;
+
 int Model::prefill(const uint32_t* tokens_host, uint32_t count) {
     if (!tokens_host || count == 0) return fail(GF_ERR_INVALID, "empty prompt");
+    if (!finalized_) return fail(GF_ERR_STATE, "plan is not finalized");
     uint32_t done = 0;
+    if (tensor_prefill_ && count - 1u >= kTensorPrefillMinRows) {
+        // All rows but the last as 128-row chunks through the tensor cores (K/V only: no chunk needs
+        // logits, so the last layer stops after its K/V rows, gemma_target_runtime.cpp:59-61,125); the
+        // last prompt token then runs as an ordinary one-row pass, which yields the logits.
+        if (position_ > config_.context || count > config_.context - position_)
+            return fail(GF_ERR_INVALID, "prompt exceeds the bound context (%u + %u > %u)", position_, count, config_.context);
+        for (uint32_t i = 0; i < count; ++i)
+            if (tokens_host[i] >= config_.vocab) return fail(GF_ERR_INVALID, "token id %u outside the vocabulary", tokens_host[i]);
+        GF_TRY(ensure_prefill_arena());
+        while (done < count - 1u) {
+            const uint32_t rows = std::min(prefill_.chunk_rows, count - 1u - done);
+            GF_TRY(prefill_chunk(tokens_host + done, rows));
+            done += rows;
+        }
+        GF_TRY(forward(tokens_host + done, 1, kForwardLogits));
+        GF_TRY(publish(1));
+        prefill_logits_row_ = 0;
+        return GF_OK;
+    }
     while (done < count) {
         const uint32_t rows = std::min(config_.row_capacity, count - done);
         const bool last = done + rows == count;
         GF_TRY(forward(tokens_host + done, rows, last ? kForwardLogits : 0u));
         GF_TRY(publish(rows));
+        prefill_logits_row_ = rows - 1u;
         done += rows;
     }
+    return GF_OK;
+}
+
+int Model::ensure_prefill_arena() {
+    if (prefill_.ready) return GF_OK;
+    const gf_model_config& c = config_;
+    const uint32_t qw = c.heads * c.head_dim, kvw = c.kv_heads * c.head_dim, R = kPrefillRows;
+    if (qw % kPrefillTile || kvw % kPrefillTile || c.hidden % kPrefillTile || c.ffn % kPrefillTile)
+        return fail(GF_ERR_INVALID, "tensor-core prefill needs projection widths that are multiples of %u", kPrefillTile);
+    PrefillArena& a = prefill_;
+    // A chunk must not publish two rows into one ring slot.
+    a.chunk_rows = R;
+    for (const LayerCache& cache : caches_) a.chunk_rows = std::min(a.chunk_rows, cache.ring_rows);
+    uint8_t* bytes = nullptr;
+    GF_TRY(device_alloc(allocations_, &bytes, tile_major_bytes(c.hidden))); a.a_hidden = bytes;
+    GF_TRY(device_alloc(allocations_, &bytes, tile_major_bytes(qw))); a.a_q = bytes;
+    GF_TRY(device_alloc(allocations_, &bytes, tile_major_bytes(c.ffn))); a.a_ffn = bytes;
+    GF_TRY(device_alloc(allocations_, &a.residual, (size_t)R * c.hidden));
+    GF_TRY(device_alloc(allocations_, &a.residual2, (size_t)R * c.hidden));
+    GF_TRY(device_alloc(allocations_, &a.raw_q, (size_t)R * qw));
+    GF_TRY(device_alloc(allocations_, &a.raw_k, (size_t)R * kvw));
+    GF_TRY(device_alloc(allocations_, &a.raw_v, (size_t)R * kvw));
+    GF_TRY(device_alloc(allocations_, &a.query, (size_t)R * qw));
+    GF_TRY(device_alloc(allocations_, &a.attention_out, (size_t)R * qw));
+    GF_TRY(device_alloc(allocations_, &a.projected, (size_t)R * c.hidden));
+    GF_TRY(device_alloc(allocations_, &a.gate, (size_t)R * c.ffn));
+    GF_TRY(device_alloc(allocations_, &a.up, (size_t)R * c.ffn));
+    GF_TRY(device_alloc(allocations_, &a.tokens, R));
+    const size_t element = c.kv_f16 ? 2 : 4;
+    std::vector<KvPublishLayer> table(c.layers);
+    a.private_k.resize(c.layers); a.private_v.resize(c.layers);
+    for (uint32_t l = 0; l < c.layers; ++l) {
+        uint8_t *pk, *pv;
+        GF_TRY(device_alloc(allocations_, &pk, (size_t)R * kvw * element));
+        GF_TRY(device_alloc(allocations_, &pv, (size_t)R * kvw * element));
+        a.private_k[l] = pk; a.private_v[l] = pv;
+        table[l] = KvPublishLayer{static_cast<uint8_t*>(caches_[l].ring_k), static_cast<uint8_t*>(caches_[l].ring_v), pk, pv,
+                                  caches_[l].ring_rows - 1u, (uint32_t)(kvw * element)};
+    }
+    GF_TRY(device_alloc(allocations_, &a.publish_layers, c.layers));
+    GF_CUDA(cudaMemcpyAsync(a.publish_layers, table.data(), sizeof(KvPublishLayer) * c.layers, cudaMemcpyHostToDevice, stream_));
+    GF_TRY(device_alloc(allocations_, &bytes, attention_workspace_bytes(R, c.heads))); a.attention_ws = bytes;
+    GF_CUDA(cudaMemsetAsync(attention_counters(a.attention_ws, R, c.heads), 0, (size_t)R * c.heads * sizeof(uint32_t), stream_));
+    GF_CUDA(cudaStreamSynchronize(stream_));       // `table` is pageable and goes out of scope
+    a.ready = true;
+    return GF_OK;
+}
+
+// One chunk of up to 128 prompt rows: every projection is one tensor-core GEMM over all rows of the
+// chunk; norms, GeGLU and the attention output go through small kernels that write the next GEMM's bf16
+// operand; RoPE / K/V store and attention reuse the row kernels.  The rows are published at the end.
+int Model::prefill_chunk(const uint32_t* tokens_host, uint32_t rows) {
+    const gf_model_config& c = config_;
+    PrefillArena& a = prefill_;
+    const uint32_t qw = c.heads * c.head_dim;
+    GF_CUDA(cudaMemcpyAsync(a.tokens, tokens_host, rows * sizeof(uint32_t), cudaMemcpyHostToDevice, stream_));
+    GF_TRY(launch_embedding(token_embd_.dtype, token_embd_.data, c.hidden, c.vocab, a.tokens, rows, sqrtf((float)c.hidden), a.residual,
+                            status_dev_, stream_, false));
+    launches_ += 1;
+    auto gemm = [&](std::initializer_list<std::pair<const PackedMatrix*, float*>> set, const void* operand, uint64_t k) -> int {
+        PrefillGemmLaunch launch;
+        launch.count = 0;
+        for (const auto& entry : set) launch.matrices[launch.count++] = {entry.first->dtype, entry.first->data, entry.second, entry.first->n};
+        launch.k = k;
+        launch.a = operand;
+        ++launches_;
+        return launch_prefill_gemm(launch, error_flag_, stream_);
+    };
+    for (uint32_t l = 0; l < c.layers; ++l) {
+        const LayerWeights& w = layers_[l];
+        const LayerCache& cache = caches_[l];
+        if (l == 0) GF_TRY(launch_prefill_norm(a.residual, nullptr, nullptr, w.attn_norm, nullptr, a.a_hidden, rows, c.hidden, c.rms_eps, 0, stream_));
+        else GF_TRY(launch_prefill_norm(a.projected, a.residual2, layers_[l - 1].post_ffw_norm, w.attn_norm, a.residual, a.a_hidden, rows,
+                                        c.hidden, c.rms_eps, 1, stream_));
+        if (unit_elements(w.q.dtype) == unit_elements(w.v.dtype)) {
+            GF_TRY(gemm({{&w.q, a.raw_q}, {&w.k, a.raw_k}, {&w.v, a.raw_v}}, a.a_hidden, c.hidden));
+        } else {
+            GF_TRY(gemm({{&w.q, a.raw_q}, {&w.k, a.raw_k}}, a.a_hidden, c.hidden));
+            GF_TRY(gemm({{&w.v, a.raw_v}}, a.a_hidden, c.hidden));
+        }
+        RopeStoreParams rp{a.raw_q, a.raw_k, a.raw_v, c.uses_qk_norm ? w.q_norm : nullptr, c.uses_qk_norm ? w.k_norm : nullptr, a.query,
+                           a.private_k[l], a.private_v[l], state_dev_, status_dev_, cache.rope_divisors, rows, c.heads, c.kv_heads,
+                           c.head_dim, c.rms_eps, cache.rope_base, cache.rope_scale, c.kv_f16};
+        GF_TRY(launch_rope_store(rp, stream_, false));
+        launches_ += 2;
+        if (l + 1u == c.layers) break;          // nothing downstream of the last layer's K/V is needed
+        AttentionParams ap;
+        ap.q = a.query; ap.ring_k = cache.ring_k; ap.ring_v = cache.ring_v; ap.private_k = a.private_k[l]; ap.private_v = a.private_v[l];
+        ap.out = a.attention_out;
+        ap.partial_out = static_cast<float*>(a.attention_ws);
+        ap.partial_ml = ap.partial_out + (size_t)kPrefillRows * c.heads * kMaxAttentionPartitions * 256u;
+        ap.counters = attention_counters(a.attention_ws, kPrefillRows, c.heads);
+        ap.base_position = state_dev_; ap.rows = rows; ap.heads = c.heads; ap.kv_heads = c.kv_heads; ap.head_dim = c.head_dim;
+        ap.ring_mask = cache.ring_rows - 1u; ap.window = cache.window; ap.scale = c.attention_scale;
+        ap.softcap = c.attn_softcap; ap.kv_f16 = c.kv_f16;
+        ap.defer_merge = 0u;
+        GF_TRY(launch_attention(ap, stream_, false));
+        GF_TRY(launch_prefill_pack(a.attention_out, a.a_q, rows, qw, stream_));
+        GF_TRY(gemm({{&w.o, a.projected}}, a.a_q, qw));
+        GF_TRY(launch_prefill_norm(a.projected, a.residual, w.post_attention_norm, w.ffn_norm, a.residual2, a.a_hidden, rows, c.hidden,
+                                   c.rms_eps, 1, stream_));
+        if (unit_elements(w.gate.dtype) == unit_elements(w.up.dtype)) {
+            GF_TRY(gemm({{&w.gate, a.gate}, {&w.up, a.up}}, a.a_hidden, c.hidden));
+        } else {
+            GF_TRY(gemm({{&w.gate, a.gate}}, a.a_hidden, c.hidden));
+            GF_TRY(gemm({{&w.up, a.up}}, a.a_hidden, c.hidden));
+        }
+        GF_TRY(launch_prefill_geglu(a.gate, a.up, a.a_ffn, rows, c.ffn, stream_));
+        GF_TRY(gemm({{&w.down, a.projected}}, a.a_ffn, c.ffn));
+        launches_ += 5;
+    }
+    GF_TRY(launch_kv_publish(a.publish_layers, c.layers, state_dev_, rows, stream_));
+    launches_ += 2;
+    position_ += rows;
     return GF_OK;
 }
 
@@ -811,6 +949,12 @@ int gf_model_use_graph(gf_model* m, int enable) {
     m->impl.set_use_graph(enable != 0);
     return GF_OK;
 }
+int gf_model_use_tensor_prefill(gf_model* m, int enable) {
+    if (!m) return fail(GF_ERR_INVALID, "null model");
+    m->impl.set_tensor_prefill(enable != 0);
+    return GF_OK;
+}
+uint32_t gf_model_prefill_logits_row(const gf_model* m) { return m ? m->impl.prefill_logits_row() : 0; }
 int gf_model_use_pass_kernel(gf_model* m, int mode) {
     if (!m || mode < 0 || mode > 2) return fail(GF_ERR_INVALID, "gf_model_use_pass_kernel: mode must be 0, 1 or 2");
     m->impl.set_pass_mode(mode);

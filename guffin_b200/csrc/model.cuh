@@ -6,6 +6,7 @@
 #include "common.cuh"
 #include "ops.cuh"
 #include "pass.cuh"
+#include "prefill.cuh"
 
 #include <string>
 #include <vector>
@@ -78,6 +79,11 @@ public:
     size_t kv_bytes_per_pass(uint32_t rows) const;
     uint32_t kernel_launches() const { return launches_; }
     void set_use_graph(bool on) { use_graph_ = on; }
+    // Prompts longer than kTensorPrefillMinRows go through the 128-row tensor-core path (bf16 operands)
+    // unless this is switched off; shorter ones, and every prompt then, through the exact row path.
+    void set_tensor_prefill(bool on) { tensor_prefill_ = on; }
+    // Row of the logits buffer that holds the last prompt token's logits after prefill().
+    uint32_t prefill_logits_row() const { return prefill_logits_row_; }
     // 0: kernel-per-matrix schedule only.  1: passes of one or two rows run as the decode pass kernel
     // (attention inside it where it has an instance, as launches of its own between segments otherwise).
     // 2: as 1, but attention always as launches of its own.
@@ -112,6 +118,23 @@ private:
     int run_recorded(const RecordedPass& pass, uint32_t rows);
     int encode_sweep(uint32_t rows, uint32_t* out_launches, uint64_t* out_bytes);
     bool layer_is_local(uint32_t layer) const;
+    int ensure_prefill_arena();
+    int prefill_chunk(const uint32_t* tokens_host, uint32_t rows);
+
+    // Buffers of the 128-row prompt path, allocated when a long prompt first arrives.
+    struct PrefillArena {
+        bool ready = false;
+        uint32_t chunk_rows = 0;
+        void *a_hidden = nullptr, *a_q = nullptr, *a_ffn = nullptr;            // tile-major bf16 operands
+        float *residual = nullptr, *residual2 = nullptr, *raw_q = nullptr, *raw_k = nullptr, *raw_v = nullptr;
+        float *query = nullptr, *attention_out = nullptr, *projected = nullptr, *gate = nullptr, *up = nullptr;
+        std::vector<void*> private_k, private_v;                               // per layer [128][kv width]
+        KvPublishLayer* publish_layers = nullptr;
+        void* attention_ws = nullptr;
+        uint32_t* tokens = nullptr;
+    } prefill_;
+    bool tensor_prefill_ = true;
+    uint32_t prefill_logits_row_ = 0;
 
     gf_model_config config_;
     bool finalized_ = false, use_graph_ = true, poisoned_ = false;

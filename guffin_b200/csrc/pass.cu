@@ -113,6 +113,7 @@ __global__ void __launch_bounds__(kGemvWarps * 32, 1) decode_pass_kernel(const P
     if (threadIdx.x < kPhaseChunks) copy_async_16(entries[0] + threadIdx.x * 16u, reinterpret_cast<const uint8_t*>(table) + threadIdx.x * 16u);
     copy_async_wait();
     const StreamSmem sm = stream_smem(smem, kPassSlotBytes);
+    if (threadIdx.x == 0) bad_rows = 0u;
     // The ring's cursor starts at the first streaming phase of the launch and ends with the last one.
     const bool streams = first_stream < count;
     WeightRing ring = ring_open<true>(sm, kPassSlotBytes, streams ? &table[first_stream].stream : nullptr,
@@ -144,6 +145,7 @@ __global__ void __launch_bounds__(kGemvWarps * 32, 1) decode_pass_kernel(const P
         // The CTA agrees on the outcome, then arrives (the last phase needs no barrier behind it).
         ok = __syncthreads_or(ok ? 0 : 1) == 0;
         if (!ok) break;
+        if (threadIdx.x == 0) bad_rows = 0u;          // for the next streaming phase; ordered by its dependency barrier
         if (threadIdx.x == 0 && ph + 1u < count) grid_arrive(arrived);
     }
     if (!ok) {

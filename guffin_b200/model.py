@@ -75,6 +75,8 @@ lib.register({
     "gf_model_kernel_launches": (u32, [vp]),
     "gf_model_use_graph": (i32, [vp, i32]),
     "gf_model_use_pass_kernel": (i32, [vp, i32]),
+    "gf_model_use_tensor_prefill": (i32, [vp, i32]),
+    "gf_model_prefill_logits_row": (u32, [vp]),
     "gf_model_weight_sweep": (i32, [vp, u32, C.POINTER(u32), C.POINTER(u64)]),
 })
 
@@ -199,6 +201,14 @@ class Model:
 
     def use_graph(self, enable: bool) -> None:
         check(self.L.gf_model_use_graph(self.handle, int(enable)))
+
+    def use_tensor_prefill(self, enable: bool) -> None:
+        """Long prompts through the 128-row bf16 tensor-core path (default) or the exact row path."""
+        check(self.L.gf_model_use_tensor_prefill(self.handle, int(enable)))
+
+    @property
+    def prefill_logits_row(self) -> int:
+        return self.L.gf_model_prefill_logits_row(self.handle)
 
     def use_pass_kernel(self, mode: int) -> None:
         """0: one kernel per operator; 1: the persistent decode pass kernel; 2: that, attention launched separately."""

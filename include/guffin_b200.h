@@ -256,6 +256,15 @@ GF_API int gf_model_publish(gf_model* model, uint32_t rows);
  * gemma_target_runtime.cpp:420); logits are produced for the last token only. */
 GF_API int gf_model_prefill(gf_model* model, const uint32_t* tokens_host, uint32_t count);
 GF_API int gf_model_truncate(gf_model* model, uint32_t position);
+/* gf_model_prefill ingests prompts of 65 tokens or more in chunks of up to 128 rows, every projection of
+ * a chunk as one bf16 tensor-core GEMM (run_gemma3_resident_prefill's 128-row chunks,
+ * gemma_target_runtime.cpp:420-455; the last layer of a chunk stops after its K/V rows, :59-61,125), and
+ * the last prompt token as an ordinary one-row pass.  K/V rows and logits then differ from the exact row
+ * path by the bf16 rounding of activations and weights (about 1e-2 relative L2 on logits).
+ * gf_model_use_tensor_prefill(model, 0) keeps every prompt on the exact row path.
+ * gf_model_prefill_logits_row: the row of the logits buffer that holds the last prompt token's logits. */
+GF_API int gf_model_use_tensor_prefill(gf_model* model, int enable);
+GF_API uint32_t gf_model_prefill_logits_row(const gf_model* model);
 /* Candidate selection over the last pass's logits; requests_host holds `rows` request rows
  * (gf_selection_request_bytes each).  gf_model_read_candidates synchronises and copies
  * `rows` result rows (gf_candidate_result_bytes each) (read_target_token_candidates). */

@@ -46,6 +46,7 @@ def test_270m_greedy_256_after_512_token_prompt(gf, ge, gm, all_cores):
     config = syn.model_config("gemma3-270m")
     weights = syn.make_model_weights("gemma3-270m", 2701)
     model = gm.Model(config, weights, 512 + 256 + 8, 2)
+    model.use_tensor_prefill(False)      # this test pins greedy tokens to 2e-4 of the oracle: the prompt takes the exact row path
     options = ge.H1Options(ge.sampler_options(0.0, seed=1), 0, 0, 0.7, 7, 0)
     engine = ge.H1(model, None, options)
     prompt = np.random.default_rng(31).integers(0, config["vocab"], 512).astype(np.uint32)
@@ -75,6 +76,18 @@ def test_270m_greedy_256_after_512_token_prompt(gf, ge, gm, all_cores):
     model.forward([int(tokens[-1])], logits=True)
     np.testing.assert_array_equal(model.logits(0), plain)
     assert model.status() == 0
+    # The same prompt through the tensor-core prefill (Q8_0 weights, f32 cache): first-token logits within
+    # the bf16 tolerance of the oracle's.
+    model.use_pass_kernel(0)
+    model.use_tensor_prefill(True)
+    model.reset()
+    model.prefill(prompt)
+    ref.reset()
+    for token in prompt[:-1]:
+        ref.append(token, want_logits=False)
+    error = rel_l2(model.logits(model.prefill_logits_row), ref.append(prompt[-1]))
+    print(f"270M tensor prefill of 512 tokens: first-token logits rel-L2 {error:.2e}")
+    assert error < 3e-2 and model.status() == 0
 
 
 def _assert_same_candidates(model, gm, got_logits, want_logits, retain=40):
@@ -101,6 +114,7 @@ def test_12b_two_row_verification_matches_oracle_at_short_and_long_context(gf, g
     weights = syn.make_model_weights("gemma3-12b", 1201)
     context = 1152
     model = gm.Model(config, weights, context, 8)
+    model.use_tensor_prefill(False)      # parts (a) and (b) pin the exact row path; part (c) turns the tensor path on
     ref = OracleModel(oracle, config, weights, context=context)
     tokens = np.random.default_rng(31).integers(0, config["vocab"], 1120).astype(np.uint32)
 
@@ -150,5 +164,15 @@ def test_12b_two_row_verification_matches_oracle_at_short_and_long_context(gf, g
     for row in range(2):
         np.testing.assert_array_equal(model.logits(row), plain[row])
     assert model.status() == 0
+    # (c) The same 1101-token prefix through the tensor-core prefill (128-row bf16 GEMMs): the last token's
+    # logits against the exact path's, within the stated bf16 tolerance.
+    model.use_pass_kernel(0)
+    model.use_tensor_prefill(True)
+    model.reset()
+    model.prefill(tokens[:base + 1])
+    assert model.position == base + 1
+    error = rel_l2(model.logits(model.prefill_logits_row), plain[0])
+    print(f"12B tensor prefill of {base + 1} tokens: last-token logits rel-L2 {error:.2e} against the exact row path")
+    assert error < 3e-2 and model.status() == 0
     print(f"12B verify parity: rel-L2 short context {max(errors):.2e}, at position {base} {max(long_errors):.2e}")
 
