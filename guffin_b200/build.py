@@ -17,24 +17,31 @@ def sources() -> list[str]:
     return sorted(os.path.join(CSRC, f) for f in os.listdir(CSRC) if f.endswith((".cu", ".cpp")))
 
 
-def stale() -> bool:
-    if not os.path.exists(LIB):
+TESTING_LIB = os.path.join(HERE, "libguffin_b200_testing.so")
+
+
+def stale(lib: str = LIB) -> bool:
+    if not os.path.exists(lib):
         return True
-    built = os.path.getmtime(LIB)
+    built = os.path.getmtime(lib)
     deps = [os.path.join(CSRC, f) for f in os.listdir(CSRC)] + [os.path.join(HERE, "..", "include", "guffin_b200.h")]
     return any(os.path.getmtime(d) > built for d in deps)
 
 
-def build(force: bool = False, verbose: bool = False) -> str:
-    if not force and not stale():
-        return LIB
+def build(force: bool = False, verbose: bool = False, testing: bool = False) -> str:
+    """Compiles every source and links the library.  `testing` builds the variant with the host-side
+    fault seam (-DGF_TESTING, libguffin_b200_testing.so) that only the give-up tests load."""
+    lib = TESTING_LIB if testing else LIB
+    if not force and not stale(lib):
+        return lib
     objects = []
-    os.makedirs(os.path.join(HERE, "build"), exist_ok=True)
+    out_dir = os.path.join(HERE, "build", "testing" if testing else "")
+    os.makedirs(out_dir, exist_ok=True)
     procs = []
     for src in sources():
-        obj = os.path.join(HERE, "build", os.path.basename(src) + ".o")
+        obj = os.path.join(out_dir, os.path.basename(src) + ".o")
         objects.append(obj)
-        cmd = [NVCC, *FLAGS, "-x", "cu", "-c", src, "-o", obj]
+        cmd = [NVCC, *FLAGS, *(["-DGF_TESTING"] if testing else []), "-x", "cu", "-c", src, "-o", obj]
         procs.append((src, subprocess.Popen(cmd, stdout=subprocess.PIPE, stderr=subprocess.STDOUT, text=True)))
     for src, proc in procs:
         out, _ = proc.communicate()
@@ -42,11 +49,12 @@ def build(force: bool = False, verbose: bool = False) -> str:
             sys.stderr.write(out)
         if proc.returncode != 0:
             raise RuntimeError(f"nvcc failed on {src}")
-        with open(os.path.join(HERE, "build", os.path.basename(src) + ".ptxas.txt"), "w") as f:
+        with open(os.path.join(out_dir, os.path.basename(src) + ".ptxas.txt"), "w") as f:
             f.write(out)
-    subprocess.run([NVCC, "-shared", "-o", LIB, *objects, "-lcudart"], check=True)
-    return LIB
+    subprocess.run([NVCC, "-shared", "-o", lib, *objects, "-lcudart"], check=True)
+    return lib
 
 
 if __name__ == "__main__":
     print(build(force="--force" in sys.argv, verbose="-v" in sys.argv))
+    print(build(force="--force" in sys.argv, verbose="-v" in sys.argv, testing=True))

@@ -22,6 +22,17 @@ int check_cuda(cudaError_t error, const char* what);
 
 inline cudaStream_t as_stream(void* stream) { return static_cast<cudaStream_t>(stream); }
 
+#ifdef GF_TESTING
+// Host-side fault seam of the testing build (never compiled into the shipped library; the reference keeps
+// its seams behind LOCAL_GGUF_ENGINE_TESTING the same way, tests/support/target_verifier_test_hooks.cpp).
+// A one-shot request that the next prepared launch consumes.  kind 1: a weight-streaming launch overstates
+// the byte count its first copy expects by 16 and gives up after `limit` polls -- every copy still lands,
+// the wait runs out, nothing faults.  kind 2: one CTA of the next decode pass kernel leaves out one barrier
+// arrival and every CTA's poll gives up after `limit` reads.
+struct TestingFault { int kind = 0; uint32_t limit = 0; };
+TestingFault& testing_fault();
+#endif
+
 int sm_count();
 
 // ---- block geometry (GGUF type ids: 8 = Q8_0, 12 = Q4_K, 14 = Q6_K)
@@ -101,8 +112,9 @@ __device__ __forceinline__ bool mbar_try_wait(uint64_t* bar, uint32_t parity) {
     return done != 0;
 }
 // Bounded wait: gives up after a fixed number of polls so a lost copy can never hang the GPU.
-__device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity) {
-    for (uint32_t spin = 0; spin < (1u << 24); ++spin)
+constexpr uint32_t kMbarWaitLimit = 1u << 24;
+__device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity, uint32_t limit = kMbarWaitLimit) {
+    for (uint32_t spin = 0; spin < limit; ++spin)
         if (mbar_try_wait(bar, parity)) return true;
     return false;
 }

@@ -180,6 +180,15 @@ int gemv_prepare(const GemvLaunch& launch, uint32_t* counters, float* partial, s
     p.slot_bytes = plan.slot_bytes;
     p.slot_units = plan.slot_units;
     p.grid = plan.grid;
+    p.wait_limit = kMbarWaitLimit;
+    p.overstate = 0;
+#ifdef GF_TESTING
+    if (testing_fault().kind == 1) {
+        p.wait_limit = testing_fault().limit;
+        p.overstate = 16;
+        testing_fault().kind = 0;
+    }
+#endif
     p.prologue = launch.prologue;
     p.in = launch.in; p.residual = launch.residual; p.gamma0 = launch.gamma0; p.gamma1 = launch.gamma1;
     p.residual_out = launch.residual_out;

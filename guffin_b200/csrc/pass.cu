@@ -103,7 +103,7 @@ template <int ROWS>
 __global__ void __launch_bounds__(kGemvWarps * 32, 1) decode_pass_kernel(const PassPhase* __restrict__ table, uint32_t count,
                                                                          uint32_t first_stream, uint32_t last_stream,
                                                                          uint32_t* arrived, uint32_t base, int* error_flag,
-                                                                         uint32_t poll_limit) {
+                                                                         uint32_t poll_limit, uint32_t skip_arrival) {
     extern __shared__ __align__(128) uint8_t smem[];
     __shared__ float scratch[2 * kGemvWarps * ROWS];
     __shared__ uint32_t bad_rows, wait_outcome;
@@ -146,7 +146,7 @@ __global__ void __launch_bounds__(kGemvWarps * 32, 1) decode_pass_kernel(const P
         ok = __syncthreads_or(ok ? 0 : 1) == 0;
         if (!ok) break;
         if (threadIdx.x == 0) bad_rows = 0u;          // for the next streaming phase; ordered by its dependency barrier
-        if (threadIdx.x == 0 && ph + 1u < count) grid_arrive(arrived);
+        if (threadIdx.x == 0 && ph + 1u < count && !(blockIdx.x == 0u && ph == skip_arrival)) grid_arrive(arrived);
     }
     if (!ok) {
         if (threadIdx.x == 0) atomicExch(error_flag, 1);          // first, so that the other CTAs stop polling at once
@@ -213,7 +213,7 @@ static int launch_pass_instance(const PassLaunch& launch, cudaStream_t stream) {
     config.numAttrs = 1;
     GF_CUDA(cudaLaunchKernelEx(&config, decode_pass_kernel<ROWS>, launch.table_dev + launch.first, launch.count,
                                launch.first_stream, launch.last_stream, launch.arrived_dev, launch.base, launch.error_flag,
-                               launch.poll_limit));
+                               launch.poll_limit, launch.skip_arrival));
     return GF_OK;
 }
 
@@ -235,7 +235,17 @@ int launch_pass(const PassLaunch& launch, cudaStream_t stream) {
     std::lock_guard<std::mutex> lock(order.guard);
     if (!order.last) GF_CUDA(cudaEventCreateWithFlags(&order.last, cudaEventDisableTiming));
     if (order.any) GF_CUDA(cudaStreamWaitEvent(stream, order.last, 0));       // a no-op behind a launch on the same stream
+#ifdef GF_TESTING
+    PassLaunch armed = launch;
+    if (testing_fault().kind == 2) {
+        armed.poll_limit = testing_fault().limit;
+        armed.skip_arrival = 1;
+        testing_fault().kind = 0;
+    }
+    const int status = armed.rows == 1 ? launch_pass_instance<1>(armed, stream) : launch_pass_instance<2>(armed, stream);
+#else
     const int status = launch.rows == 1 ? launch_pass_instance<1>(launch, stream) : launch_pass_instance<2>(launch, stream);
+#endif
     if (status != GF_OK) return status;
     GF_CUDA(cudaEventRecord(order.last, stream));
     order.any = true;

@@ -31,7 +31,7 @@ struct EmbeddingPhase {
     float scale;
 };
 
-struct PassPhase {
+struct alignas(16) PassPhase {
     uint32_t kind;
     uint32_t attention_group, attention_rows;     // query heads per KV head and rows per block of an attention phase
     uint32_t reserved;
@@ -52,6 +52,7 @@ struct PassLaunch {
     uint32_t base = 0;                      // its value when this launch starts (the host keeps count; modulo 2^32)
     int* error_flag = nullptr;
     uint32_t poll_limit = kPassDefaultPollLimit;
+    uint32_t skip_arrival = ~0u;            // phase after which CTA 0 leaves out its arrival (~0: never; a testing build's fault seam)
 };
 
 // Rows a pass kernel instance exists for.

@@ -145,3 +145,20 @@ int gf_event_elapsed_ms(void* start, void* end, float* out_ms) {
 }
 
 }  // extern "C"
+
+#ifdef GF_TESTING
+namespace gf {
+TestingFault& testing_fault() {
+    static TestingFault fault;
+    return fault;
+}
+}  // namespace gf
+
+// Testing build only (absent from include/guffin_b200.h): arms the one-shot fault described in common.cuh.
+extern "C" GF_API int gf_testing_arm_fault(int kind, uint32_t limit) {
+    if (kind < 0 || kind > 2 || (kind != 0 && limit == 0)) return gf::fail(GF_ERR_INVALID, "gf_testing_arm_fault: bad request");
+    gf::testing_fault().kind = kind;
+    gf::testing_fault().limit = limit;
+    return GF_OK;
+}
+#endif
