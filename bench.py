@@ -6,6 +6,7 @@ weights of those geometries.
     python bench.py [--gpus N] [--steps K] [--warmup W] [--impl ours|reference]
     python bench.py --case matmul <dtype 8|12|14> <K> <N> <rows> [launches]
     python bench.py --case attention <cached rows> <rows> <heads> <kv_heads> <window> <kv_f16 0|1> [launches]
+    python bench.py --case prefill <12b|270m> <tokens> [tensor path 0|1]
 
 A "step" is one H1 cycle: drafter proposal -> two-row target pass -> candidate selection ->
 host acceptance -> publish / rollback.  Accept/reject control flow follows a seeded Bernoulli(0.7)
@@ -220,10 +221,16 @@ def run_ours(args) -> dict:
     options = ge.H1Options(ge.sampler_options(0.7, 40, 0.95, 0.05, 1.0, seed=SEEDS["sampler"] + rank), 1, 1, ACCEPT_P,
                            SEEDS["schedule"] + rank, 0)
     engine = ge.H1(target, draft, options)
-    t0 = time.time()
-    engine.prefill(prompt_tokens(tc["vocab"], rank))
-    target.synchronize()
-    prefill_s = time.time() - t0
+    # Prompt ingestion of both plans, twice: the first call also allocates the 128-row arena and loads
+    # the kernels, the second is what a session pays per prompt.
+    prefill_times = []
+    for _ in range(2):
+        t0 = time.time()
+        engine.prefill(prompt_tokens(tc["vocab"], rank))
+        target.synchronize()
+        draft.synchronize()
+        prefill_times.append(time.time() - t0)
+    prefill_first_s, prefill_s = prefill_times
 
     def barrier():
         target.synchronize()
@@ -309,7 +316,8 @@ def run_ours(args) -> dict:
                    "cycles_per_s_per_gpu": steps / (elapsed_ms * 1e-3),
                    "accepted": accepted, "cycles": int(cycles),
                    "law_agreements": int(stats_loop.law_agreements - stats_before.law_agreements),
-                   "load_s": round(load_s, 1), "prefill_s": round(prefill_s, 2),
+                   "load_s": round(load_s, 1), "prefill_s": round(prefill_s, 3), "prefill_first_call_s": round(prefill_first_s, 3),
+                   "prefill_tok_s": round(CONTEXT / prefill_s, 1),
                    "status_word": int(status)},
         "e2e": {"value": produced_e2e / e2e_s, "unit": "tok/s",
                 "h2d_bytes_per_step": 4 + 2 * 264, "d2h_bytes_per_step": 2 * 3080 + 3096,
@@ -483,7 +491,8 @@ def run_case(argv) -> int:
     from guffin_b200 import lib, model, synthetic as syn  # noqa: F401  (model declares the operator signatures)
     L = lib.load()
     rng = np.random.default_rng(0)
-    kind, numbers = argv[0], [int(a) for a in argv[1:]]
+    kind = argv[0]
+    numbers = [int(a) for a in argv[1:]] if kind != "prefill" else []
     if kind == "matmul":
         dtype, k, n, rows = numbers[:4]
         launches = numbers[4] if len(numbers) > 4 else 3
@@ -516,6 +525,26 @@ def run_case(argv) -> int:
         result = out.download(np.float32)
         print(f"ok: {launches} gf_attention launches, base={base} rows={rows} heads={heads}/{kv_heads} window={window}, "
               f"|out| = {float(np.abs(result).mean()):.4f}")
+        return 0
+    if kind == "prefill":
+        # prefill <12b|270m> <tokens> [tensor 0|1]: prompt ingestion alone on one synthetic model.
+        name = {"12b": TARGET, "270m": DRAFT}[argv[1]]
+        count = int(argv[2])
+        tensor = int(argv[3]) if len(argv) > 3 else 1
+        from guffin_b200 import model as gm
+        config = syn.model_config(name)
+        plan = gm.Model(config, syn.iter_model_weights(name, SEEDS["target"]), count + 16, PREFILL_ROWS)
+        plan.use_tensor_prefill(bool(tensor))
+        tokens = prompt_tokens(config["vocab"], 0)[:count]
+        times = []
+        for _ in range(2):
+            plan.reset()
+            plan.synchronize()
+            t0 = time.perf_counter()
+            plan.prefill(tokens)
+            plan.synchronize()
+            times.append(time.perf_counter() - t0)
+        print(f"ok: {name} prefill of {count} tokens, tensor path {tensor}: {times[-1] * 1e3:.1f} ms ({count / times[-1]:.0f} tok/s), status {plan.status()}")
         return 0
     print(f"unknown case {kind!r}", file=sys.stderr)
     return 2

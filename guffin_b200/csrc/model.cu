@@ -640,7 +640,7 @@ int Model::ensure_prefill_arena() {
     GF_TRY(device_alloc(allocations_, &a.raw_v, (size_t)R * kvw));
     GF_TRY(device_alloc(allocations_, &a.query, (size_t)R * qw));
     GF_TRY(device_alloc(allocations_, &a.attention_out, (size_t)R * qw));
-    GF_TRY(device_alloc(allocations_, &a.projected, (size_t)R * c.hidden));
+    GF_TRY(device_alloc(allocations_, &a.projected, (size_t)kPrefillMaxSplits * R * c.hidden));      // K-split partial results
     GF_TRY(device_alloc(allocations_, &a.gate, (size_t)R * c.ffn));
     GF_TRY(device_alloc(allocations_, &a.up, (size_t)R * c.ffn));
     GF_TRY(device_alloc(allocations_, &a.tokens, R));
@@ -675,20 +675,22 @@ int Model::prefill_chunk(const uint32_t* tokens_host, uint32_t rows) {
     GF_TRY(launch_embedding(token_embd_.dtype, token_embd_.data, c.hidden, c.vocab, a.tokens, rows, sqrtf((float)c.hidden), a.residual,
                             status_dev_, stream_, false));
     launches_ += 1;
-    auto gemm = [&](std::initializer_list<std::pair<const PackedMatrix*, float*>> set, const void* operand, uint64_t k) -> int {
+    auto gemm = [&](std::initializer_list<std::pair<const PackedMatrix*, float*>> set, const void* operand, uint64_t k, uint32_t splits = 1) -> int {
         PrefillGemmLaunch launch;
         launch.count = 0;
+        launch.splits = splits;
         for (const auto& entry : set) launch.matrices[launch.count++] = {entry.first->dtype, entry.first->data, entry.second, entry.first->n};
         launch.k = k;
         launch.a = operand;
         ++launches_;
         return launch_prefill_gemm(launch, error_flag_, stream_);
     };
+    uint32_t down_splits = 1;          // of the previous layer's down projection
     for (uint32_t l = 0; l < c.layers; ++l) {
         const LayerWeights& w = layers_[l];
         const LayerCache& cache = caches_[l];
-        if (l == 0) GF_TRY(launch_prefill_norm(a.residual, nullptr, nullptr, w.attn_norm, nullptr, a.a_hidden, rows, c.hidden, c.rms_eps, 0, stream_));
-        else GF_TRY(launch_prefill_norm(a.projected, a.residual2, layers_[l - 1].post_ffw_norm, w.attn_norm, a.residual, a.a_hidden, rows,
+        if (l == 0) GF_TRY(launch_prefill_norm(a.residual, 1, nullptr, nullptr, w.attn_norm, nullptr, a.a_hidden, rows, c.hidden, c.rms_eps, 0, stream_));
+        else GF_TRY(launch_prefill_norm(a.projected, down_splits, a.residual2, layers_[l - 1].post_ffw_norm, w.attn_norm, a.residual, a.a_hidden, rows,
                                         c.hidden, c.rms_eps, 1, stream_));
         if (unit_elements(w.q.dtype) == unit_elements(w.v.dtype)) {
             GF_TRY(gemm({{&w.q, a.raw_q}, {&w.k, a.raw_k}, {&w.v, a.raw_v}}, a.a_hidden, c.hidden));
@@ -714,8 +716,9 @@ int Model::prefill_chunk(const uint32_t* tokens_host, uint32_t rows) {
         ap.defer_merge = 0u;
         GF_TRY(launch_attention(ap, stream_, false));
         GF_TRY(launch_prefill_pack(a.attention_out, a.a_q, rows, qw, stream_));
-        GF_TRY(gemm({{&w.o, a.projected}}, a.a_q, qw));
-        GF_TRY(launch_prefill_norm(a.projected, a.residual, w.post_attention_norm, w.ffn_norm, a.residual2, a.a_hidden, rows, c.hidden,
+        const uint32_t o_splits = prefill_gemm_splits(w.o.n, w.o.k, w.o.dtype);
+        GF_TRY(gemm({{&w.o, a.projected}}, a.a_q, qw, o_splits));
+        GF_TRY(launch_prefill_norm(a.projected, o_splits, a.residual, w.post_attention_norm, w.ffn_norm, a.residual2, a.a_hidden, rows, c.hidden,
                                    c.rms_eps, 1, stream_));
         if (unit_elements(w.gate.dtype) == unit_elements(w.up.dtype)) {
             GF_TRY(gemm({{&w.gate, a.gate}, {&w.up, a.up}}, a.a_hidden, c.hidden));
@@ -724,7 +727,8 @@ int Model::prefill_chunk(const uint32_t* tokens_host, uint32_t rows) {
             GF_TRY(gemm({{&w.up, a.up}}, a.a_hidden, c.hidden));
         }
         GF_TRY(launch_prefill_geglu(a.gate, a.up, a.a_ffn, rows, c.ffn, stream_));
-        GF_TRY(gemm({{&w.down, a.projected}}, a.a_ffn, c.ffn));
+        down_splits = prefill_gemm_splits(w.down.n, w.down.k, w.down.dtype);
+        GF_TRY(gemm({{&w.down, a.projected}}, a.a_ffn, c.ffn, down_splits));
         launches_ += 5;
     }
     GF_TRY(launch_kv_publish(a.publish_layers, c.layers, state_dev_, rows, stream_));

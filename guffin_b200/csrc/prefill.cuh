@@ -20,7 +20,7 @@ namespace gf {
 constexpr uint32_t kPrefillRows = 128;          // rows of one chunk = M of the tensor-core instruction
 constexpr uint32_t kPrefillTile = 128;          // output columns per CTA
 constexpr uint32_t kPrefillBlockK = 64;         // K elements per shared-memory stage
-constexpr uint32_t kPrefillThreads = 256;
+constexpr uint32_t kPrefillThreads = 544;          // sixteen dequantising warps and the warp that issues copies and products
 constexpr uint32_t kPrefillBlockBytes = kPrefillRows * kPrefillBlockK * 2u;      // one tile-major activation block
 
 // Byte offset of element (row, k) in a tile-major bf16 activation buffer.
@@ -49,14 +49,19 @@ struct PrefillGemmLaunch {
     uint32_t count = 1;
     uint64_t k = 0;
     const void* a = nullptr;
+    uint32_t splits = 1;       // K is cut into this many parts; part s writes [128][n] floats at out + s * 128 * n
 };
+constexpr uint32_t kPrefillMaxSplits = 4;
 int launch_prefill_gemm(const PrefillGemmLaunch& launch, int* error_flag, cudaStream_t stream);
+// K splits that give a single [K, n] matrix about one wave of CTAs (1 for wide outputs).
+uint32_t prefill_gemm_splits(uint64_t n, uint64_t k, int dtype);
 
 // Elementwise steps between the GEMMs, each writing the next GEMM's tile-major bf16 operand.
 // mode 0: a = rmsnorm(x; gamma1)
 // mode 1: r = residual + rmsnorm(x; gamma0) -> residual_out;  a = rmsnorm(r; gamma1)     (gamma1 null: only residual_out)
-int launch_prefill_norm(const float* x, const float* residual, const float* gamma0, const float* gamma1, float* residual_out,
-                        void* a_out, uint32_t rows, uint32_t k, float eps, int mode, cudaStream_t stream);
+// x is the sum, in split order, of `splits` partial results laid [split][128][k].
+int launch_prefill_norm(const float* x, uint32_t splits, const float* residual, const float* gamma0, const float* gamma1,
+                        float* residual_out, void* a_out, uint32_t rows, uint32_t k, float eps, int mode, cudaStream_t stream);
 // a = gelu_tanh(gate) * up
 int launch_prefill_geglu(const float* gate, const float* up, void* a_out, uint32_t rows, uint32_t k, cudaStream_t stream);
 // a = x (f32 rows of width k)
