@@ -7,6 +7,8 @@ weights of those geometries.
     python bench.py --case matmul <dtype 8|12|14> <K> <N> <rows> [launches]
     python bench.py --case attention <cached rows> <rows> <heads> <kv_heads> <window> <kv_f16 0|1> [launches]
     python bench.py --case prefill <12b|270m> <tokens> [tensor path 0|1]
+    python bench.py --case prefill_matmul <dtype 8|12|14> <K> <N> <rows> [launches]
+    python bench.py --case prefill_attention <cached rows> <rows> <heads> <kv_heads> <window> [launches]
 
 A "step" is one H1 cycle: drafter proposal -> two-row target pass -> candidate selection ->
 host acceptance -> publish / rollback.  Accept/reject control flow follows a seeded Bernoulli(0.7)
@@ -524,6 +526,34 @@ def run_case(argv) -> int:
                                      1.0 / 16.0, 0.0, kv_f16, None))
         result = out.download(np.float32)
         print(f"ok: {launches} gf_attention launches, base={base} rows={rows} heads={heads}/{kv_heads} window={window}, "
+              f"|out| = {float(np.abs(result).mean()):.4f}")
+        return 0
+    if kind == "prefill_matmul":
+        dtype, k, n, rows = numbers[:4]
+        launches = numbers[4] if len(numbers) > 4 else 3
+        weight = lib.PackedWeight(dtype, k, n, syn.make_weight(rng, dtype, k, n))
+        x = lib.DeviceBuffer.from_numpy(rng.standard_normal((rows, k)).astype(np.float32))
+        y = lib.DeviceBuffer(128 * n * 4)
+        ws = lib.DeviceBuffer(L.gf_prefill_workspace_bytes(k))
+        for _ in range(launches):
+            lib.check(L.gf_prefill_matmul(dtype, weight.packed.ptr, x.ptr, y.ptr, rows, k, n, ws.ptr, None))
+        print(f"ok: {launches} gf_prefill_matmul launches, dtype={dtype} K={k} N={n} rows={rows} ({weight.nbytes / 1e6:.1f} MB of weights)")
+        return 0
+    if kind == "prefill_attention":
+        base, rows, heads, kv_heads, window = numbers[:5]
+        launches = numbers[5] if len(numbers) > 5 else 3
+        ring_rows = 1 << max(1, int(np.ceil(np.log2(max(base, 2)))))
+        q = rng.standard_normal((rows, heads * 256)).astype(np.float32)
+        arrays = [q] + [rng.standard_normal((ring_rows, kv_heads * 256)).astype(np.float16) for _ in range(2)] \
+            + [rng.standard_normal((rows, kv_heads * 256)).astype(np.float16) for _ in range(2)]
+        buffers = [lib.DeviceBuffer.from_numpy(a) for a in arrays]
+        out = lib.DeviceBuffer(q.nbytes)
+        position = lib.DeviceBuffer.from_numpy(np.array([base], np.uint32))
+        for _ in range(launches):
+            lib.check(L.gf_prefill_attention(buffers[0].ptr, buffers[1].ptr, buffers[2].ptr, buffers[3].ptr, buffers[4].ptr, out.ptr,
+                                             position.ptr, rows, heads, kv_heads, 256, ring_rows, window, 1.0 / 16.0, 0.0, None))
+        result = out.download(np.float32)
+        print(f"ok: {launches} gf_prefill_attention launches, base={base} rows={rows} heads={heads}/{kv_heads} window={window}, "
               f"|out| = {float(np.abs(result).mean()):.4f}")
         return 0
     if kind == "prefill":

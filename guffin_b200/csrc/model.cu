@@ -635,14 +635,14 @@ int Model::ensure_prefill_arena() {
     GF_TRY(device_alloc(allocations_, &bytes, tile_major_bytes(c.ffn))); a.a_ffn = bytes;
     GF_TRY(device_alloc(allocations_, &a.residual, (size_t)R * c.hidden));
     GF_TRY(device_alloc(allocations_, &a.residual2, (size_t)R * c.hidden));
-    GF_TRY(device_alloc(allocations_, &a.raw_q, (size_t)R * qw));
-    GF_TRY(device_alloc(allocations_, &a.raw_k, (size_t)R * kvw));
-    GF_TRY(device_alloc(allocations_, &a.raw_v, (size_t)R * kvw));
+    GF_TRY(device_alloc(allocations_, &a.raw_q, (size_t)kPrefillMaxSplits * R * qw));           // K-split partial results
+    GF_TRY(device_alloc(allocations_, &a.raw_k, (size_t)kPrefillMaxSplits * R * kvw));
+    GF_TRY(device_alloc(allocations_, &a.raw_v, (size_t)kPrefillMaxSplits * R * kvw));
     GF_TRY(device_alloc(allocations_, &a.query, (size_t)R * qw));
     GF_TRY(device_alloc(allocations_, &a.attention_out, (size_t)R * qw));
     GF_TRY(device_alloc(allocations_, &a.projected, (size_t)kPrefillMaxSplits * R * c.hidden));      // K-split partial results
-    GF_TRY(device_alloc(allocations_, &a.gate, (size_t)R * c.ffn));
-    GF_TRY(device_alloc(allocations_, &a.up, (size_t)R * c.ffn));
+    GF_TRY(device_alloc(allocations_, &a.gate, (size_t)kPrefillMaxSplits * R * c.ffn));
+    GF_TRY(device_alloc(allocations_, &a.up, (size_t)kPrefillMaxSplits * R * c.ffn));
     GF_TRY(device_alloc(allocations_, &a.tokens, R));
     const size_t element = c.kv_f16 ? 2 : 4;
     std::vector<KvPublishLayer> table(c.layers);
@@ -693,7 +693,11 @@ int Model::prefill_chunk(const uint32_t* tokens_host, uint32_t rows) {
         else GF_TRY(launch_prefill_norm(a.projected, down_splits, a.residual2, layers_[l - 1].post_ffw_norm, w.attn_norm, a.residual, a.a_hidden, rows,
                                         c.hidden, c.rms_eps, 1, stream_));
         if (unit_elements(w.q.dtype) == unit_elements(w.v.dtype)) {
-            GF_TRY(gemm({{&w.q, a.raw_q}, {&w.k, a.raw_k}, {&w.v, a.raw_v}}, a.a_hidden, c.hidden));
+            const uint32_t splits = prefill_gemm_splits(w.q.n + w.k.n + w.v.n, c.hidden, w.q.dtype);
+            GF_TRY(gemm({{&w.q, a.raw_q}, {&w.k, a.raw_k}, {&w.v, a.raw_v}}, a.a_hidden, c.hidden, splits));
+            float* parts[3] = {a.raw_q, a.raw_k, a.raw_v};
+            const uint64_t widths[3] = {w.q.n, w.k.n, w.v.n};
+            GF_TRY(launch_prefill_reduce(parts, widths, 3, splits, rows, stream_));
         } else {
             GF_TRY(gemm({{&w.q, a.raw_q}, {&w.k, a.raw_k}}, a.a_hidden, c.hidden));
             GF_TRY(gemm({{&w.v, a.raw_v}}, a.a_hidden, c.hidden));
@@ -714,19 +718,22 @@ int Model::prefill_chunk(const uint32_t* tokens_host, uint32_t rows) {
         ap.ring_mask = cache.ring_rows - 1u; ap.window = cache.window; ap.scale = c.attention_scale;
         ap.softcap = c.attn_softcap; ap.kv_f16 = c.kv_f16;
         ap.defer_merge = 0u;
-        GF_TRY(launch_attention(ap, stream_, false));
+        if (prefill_attention_supported(ap)) GF_TRY(launch_prefill_attention(ap, stream_));
+        else GF_TRY(launch_attention(ap, stream_, false));
         GF_TRY(launch_prefill_pack(a.attention_out, a.a_q, rows, qw, stream_));
         const uint32_t o_splits = prefill_gemm_splits(w.o.n, w.o.k, w.o.dtype);
         GF_TRY(gemm({{&w.o, a.projected}}, a.a_q, qw, o_splits));
         GF_TRY(launch_prefill_norm(a.projected, o_splits, a.residual, w.post_attention_norm, w.ffn_norm, a.residual2, a.a_hidden, rows, c.hidden,
                                    c.rms_eps, 1, stream_));
+        uint32_t ffn_splits = 1;
         if (unit_elements(w.gate.dtype) == unit_elements(w.up.dtype)) {
-            GF_TRY(gemm({{&w.gate, a.gate}, {&w.up, a.up}}, a.a_hidden, c.hidden));
+            ffn_splits = prefill_gemm_splits(w.gate.n + w.up.n, c.hidden, w.gate.dtype);
+            GF_TRY(gemm({{&w.gate, a.gate}, {&w.up, a.up}}, a.a_hidden, c.hidden, ffn_splits));
         } else {
             GF_TRY(gemm({{&w.gate, a.gate}}, a.a_hidden, c.hidden));
             GF_TRY(gemm({{&w.up, a.up}}, a.a_hidden, c.hidden));
         }
-        GF_TRY(launch_prefill_geglu(a.gate, a.up, a.a_ffn, rows, c.ffn, stream_));
+        GF_TRY(launch_prefill_geglu(a.gate, a.up, ffn_splits, a.a_ffn, rows, c.ffn, stream_));
         down_splits = prefill_gemm_splits(w.down.n, w.down.k, w.down.dtype);
         GF_TRY(gemm({{&w.down, a.projected}}, a.a_ffn, c.ffn, down_splits));
         launches_ += 5;

@@ -408,16 +408,27 @@ __global__ void __launch_bounds__(256) prefill_norm_kernel(const float* __restri
     }
 }
 
-// Grid (128 rows, pieces / 256).
-__global__ void __launch_bounds__(256) prefill_geglu_kernel(const float* __restrict__ gate, const float* __restrict__ up,
+// Eight values of row `row` starting at element `at`, summed over `splits` partial results laid [split][128][k].
+__device__ __forceinline__ void load8_summed(const float* x, uint32_t splits, uint32_t row, uint32_t k, uint32_t at, float (&v)[8]) {
+    load8(x + (size_t)row * k + at, v);
+    for (uint32_t split = 1; split < splits; ++split) {
+        float more[8];
+        load8(x + ((size_t)split * kPrefillRows + row) * k + at, more);
+#pragma unroll
+        for (int i = 0; i < 8; ++i) v[i] += more[i];
+    }
+}
+
+// Grid (128 rows, pieces / 256).  gate and up are sums of `splits` partial results.
+__global__ void __launch_bounds__(256) prefill_geglu_kernel(const float* __restrict__ gate, const float* __restrict__ up, uint32_t splits,
                                                             uint8_t* __restrict__ a_out, uint32_t rows, uint32_t k) {
     const uint32_t row = blockIdx.x, piece = blockIdx.y * blockDim.x + threadIdx.x;
     if (piece >= k / 8u) return;
     float out[8] = {0.0f, 0.0f, 0.0f, 0.0f, 0.0f, 0.0f, 0.0f, 0.0f};
     if (row < rows) {
         float g[8], u[8];
-        load8(gate + (size_t)row * k + piece * 8u, g);
-        load8(up + (size_t)row * k + piece * 8u, u);
+        load8_summed(gate, splits, row, k, piece * 8u, g);
+        load8_summed(up, splits, row, k, piece * 8u, u);
 #pragma unroll
         for (int i = 0; i < 8; ++i) {
             const float v = g[i];
@@ -428,12 +439,250 @@ __global__ void __launch_bounds__(256) prefill_geglu_kernel(const float* __restr
     store_a8(a_out, row, piece * 8u, out);
 }
 
+// In-place sum of K-split partial results, for up to three matrices: x[0][row][:] += x[1..][row][:].
+struct ReduceSet { float* x[3]; uint32_t n[3]; uint32_t count, splits; };
+__global__ void __launch_bounds__(256) prefill_reduce_kernel(ReduceSet set, uint32_t rows) {
+    const uint32_t row = blockIdx.x;
+    if (row >= rows) return;
+    for (uint32_t m = 0; m < set.count; ++m) {
+        const uint32_t n = set.n[m];
+        for (uint32_t piece = blockIdx.y * blockDim.x + threadIdx.x; piece < n / 8u; piece += gridDim.y * blockDim.x) {
+            float v[8];
+            load8_summed(set.x[m], set.splits, row, n, piece * 8u, v);
+            float* dst = set.x[m] + (size_t)row * n + piece * 8u;
+            *reinterpret_cast<float4*>(dst) = make_float4(v[0], v[1], v[2], v[3]);
+            *reinterpret_cast<float4*>(dst + 4) = make_float4(v[4], v[5], v[6], v[7]);
+        }
+    }
+}
+
 __global__ void __launch_bounds__(256) prefill_pack_kernel(const float* __restrict__ x, uint8_t* __restrict__ a_out, uint32_t rows, uint32_t k) {
     const uint32_t row = blockIdx.x, piece = blockIdx.y * blockDim.x + threadIdx.x;
     if (piece >= k / 8u) return;
     float out[8] = {0.0f, 0.0f, 0.0f, 0.0f, 0.0f, 0.0f, 0.0f, 0.0f};
     if (row < rows) load8(x + (size_t)row * k + piece * 8u, out);
     store_a8(a_out, row, piece * 8u, out);
+}
+
+// ---- attention of a prompt chunk over a binary16 cache ------------------------------------------------
+//
+// Online-softmax GQA for up to 128 rows at once, both contractions on the tensor cores
+// (mma.sync.m16n8k16, f16 operands, f32 accumulation), operands straight from global memory in 16-byte
+// pieces -- no shared memory.  The sixteen rows of an MMA tile are (prompt row, query head) pairs of one KV
+// head: 16 / G prompt rows x G heads.  A block is four pairs of warps on the same sixteen queries.  The pairs
+// take the tiles of sixteen cached rows in turn (pair q the tiles q, q + 4, ...) and are merged at the end
+// through shared memory; inside a pair both warps compute the scores of a tile and each accumulates one half
+// of the 256 output dimensions.
+// The contraction index of a product may be permuted as long as both operands agree, so a lane reads
+// whole 16-byte pieces: for the scores, dimensions 32c + 8t .. +7 of its query rows and of cached row g
+// serve k-steps 2c and 2c + 1; for the outputs, dimensions 8g .. 8g + 7 (of each group of 64) of cached
+// rows 2t, 2t+1, 2t+8, 2t+9 are paired across rows by byte permutes, and column g of output tile j of the
+// group stands for dimension 8g + j.  (flash prefill attention of the reference: metal_kernels.mm:2596-2798.)
+
+__device__ __forceinline__ void mma_f16(float (&d)[4], uint32_t a0, uint32_t a1, uint32_t a2, uint32_t a3, uint32_t b0, uint32_t b1) {
+    asm volatile("mma.sync.aligned.m16n8k16.row.col.f32.f16.f16.f32 {%0, %1, %2, %3}, {%4, %5, %6, %7}, {%8, %9}, {%0, %1, %2, %3};"
+                 : "+f"(d[0]), "+f"(d[1]), "+f"(d[2]), "+f"(d[3])
+                 : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1));
+}
+__device__ __forceinline__ uint32_t half_pair(float lo, float hi) {
+    const __half2 h = __floats2half2_rn(lo, hi);
+    return *reinterpret_cast<const uint32_t*>(&h);
+}
+__device__ __forceinline__ uint32_t word_at(const uint4& v, int i) { return i == 0 ? v.x : i == 1 ? v.y : i == 2 ? v.z : v.w; }
+
+constexpr uint32_t kAttentionPairs = 4;                   // warp pairs of a block, each on every fourth tile of cached rows
+
+template <int G>
+__global__ void __launch_bounds__(64 * kAttentionPairs) prefill_attention_kernel(AttentionParams p) {
+    constexpr uint32_t kRows = 16u / G;                   // prompt rows per block
+    __shared__ float merge_m[kAttentionPairs][16], merge_l[kAttentionPairs][16];
+    __shared__ float merge_acc[2][2][64][32];             // [slot][half][accumulator word][lane]
+    const uint32_t kvh = blockIdx.x, first_row = blockIdx.y * kRows;
+    const uint32_t warp = threadIdx.x >> 5, half = warp & 1u, pair = warp >> 1;
+    const uint32_t lane = threadIdx.x & 31u, g = lane >> 2, t = lane & 3u;
+    const uint32_t base = *p.base_position;
+    const uint32_t kv_width = p.kv_heads * 256u;
+    const __half* ring_k = static_cast<const __half*>(p.ring_k);
+    const __half* ring_v = static_cast<const __half*>(p.ring_v);
+    const __half* priv_k = static_cast<const __half*>(p.private_k);
+    const __half* priv_v = static_cast<const __half*>(p.private_v);
+
+    // This lane's two query rows of the tile (m = g and g + 8): prompt row and head, and what they may see.
+    uint32_t low[2], high[2];
+    bool live[2];
+    const float* query[2];
+#pragma unroll
+    for (int i = 0; i < 2; ++i) {
+        const uint32_t m = g + 8u * i, row = first_row + m / G, head = kvh * G + m % G;
+        live[i] = row < p.rows;
+        const uint32_t position = base + row;
+        low[i] = live[i] ? ((p.window != 0u && position + 1u > p.window) ? position + 1u - p.window : 0u) : 1u;
+        high[i] = live[i] ? position : 0u;
+        query[i] = p.q + ((size_t)min(row, p.rows - 1u) * p.heads + head) * 256u;
+    }
+    // A registers of the scores: qa[c][i] = dimensions 32c + 8t .. +7 of query row i, scaled, as four f16 pairs.
+    uint4 qa[8][2];
+#pragma unroll
+    for (int c = 0; c < 8; ++c)
+#pragma unroll
+        for (int i = 0; i < 2; ++i) {
+            const float4 x = *reinterpret_cast<const float4*>(query[i] + 32 * c + 8 * t);
+            const float4 y = *reinterpret_cast<const float4*>(query[i] + 32 * c + 8 * t + 4);
+            qa[c][i] = live[i] ? make_uint4(half_pair(x.x * p.scale, x.y * p.scale), half_pair(x.z * p.scale, x.w * p.scale),
+                                            half_pair(y.x * p.scale, y.y * p.scale), half_pair(y.z * p.scale, y.w * p.scale))
+                               : make_uint4(0u, 0u, 0u, 0u);
+        }
+    float acc[16][4];                                     // output tiles (J, j) of this warp's two groups of 64 dimensions
+#pragma unroll
+    for (int i = 0; i < 16; ++i) { acc[i][0] = 0.0f; acc[i][1] = 0.0f; acc[i][2] = 0.0f; acc[i][3] = 0.0f; }
+    float m_run[2] = {-INFINITY, -INFINITY}, l_run[2] = {0.0f, 0.0f};
+
+    // Cached rows the block's queries can see: from the first row's window start to the last row itself.
+    const uint32_t last_row = min(first_row + kRows, p.rows) - 1u;
+    const uint32_t first_position = (p.window != 0u && base + first_row + 1u > p.window) ? base + first_row + 1u - p.window : 0u;
+    const uint32_t end_position = base + last_row + 1u;
+    auto row_pointer = [&](uint32_t position, const __half* ring, const __half* priv) -> const __half* {
+        position = min(position, end_position - 1u);
+        return position < base ? ring + (size_t)(position & p.ring_mask) * kv_width + kvh * 256u
+                               : priv + (size_t)(position - base) * kv_width + kvh * 256u;
+    };
+    for (uint32_t tile = first_position + 16u * pair; tile < end_position; tile += 16u * kAttentionPairs) {
+        // Scores of sixteen cached rows: two n-tiles of eight.
+        float s[2][4];
+#pragma unroll
+        for (int n = 0; n < 2; ++n) {
+            s[n][0] = 0.0f; s[n][1] = 0.0f; s[n][2] = 0.0f; s[n][3] = 0.0f;
+            const __half* key = row_pointer(tile + 8u * n + g, ring_k, priv_k);
+#pragma unroll
+            for (int c = 0; c < 8; ++c) {
+                const uint4 kb = __ldcg(reinterpret_cast<const uint4*>(key + 32 * c + 8 * t));
+                mma_f16(s[n], qa[c][0].x, qa[c][1].x, qa[c][0].y, qa[c][1].y, kb.x, kb.y);
+                mma_f16(s[n], qa[c][0].z, qa[c][1].z, qa[c][0].w, qa[c][1].w, kb.z, kb.w);
+            }
+        }
+        // s[n] = (row g: keys 2t, 2t+1), (row g + 8: keys 2t, 2t+1) of n-tile n.
+        float m_new[2] = {m_run[0], m_run[1]};
+        bool visible[2][2][2];
+#pragma unroll
+        for (int n = 0; n < 2; ++n)
+#pragma unroll
+            for (int i = 0; i < 2; ++i)
+#pragma unroll
+                for (int e = 0; e < 2; ++e) {
+                    const uint32_t position = tile + 8u * n + 2u * t + e;
+                    float& v = s[n][2 * i + e];
+                    if (p.softcap > 0.0f) v = tanhf(v / p.softcap) * p.softcap;
+                    visible[n][i][e] = position >= low[i] && position <= high[i];
+                    if (visible[n][i][e]) m_new[i] = fmaxf(m_new[i], v);
+                }
+        uint32_t pa[2][2];                                // A registers of the outputs: [n-tile][row i] = weights of keys 2t, 2t+1
+#pragma unroll
+        for (int i = 0; i < 2; ++i) {
+            m_new[i] = fmaxf(m_new[i], __shfl_xor_sync(0xffffffffu, m_new[i], 1));
+            m_new[i] = fmaxf(m_new[i], __shfl_xor_sync(0xffffffffu, m_new[i], 2));
+            const float corr = m_run[i] == -INFINITY ? 0.0f : expf(m_run[i] - m_new[i]);
+            float sum = 0.0f;
+#pragma unroll
+            for (int n = 0; n < 2; ++n) {
+                const float w0 = visible[n][i][0] ? expf(s[n][2 * i] - m_new[i]) : 0.0f;
+                const float w1 = visible[n][i][1] ? expf(s[n][2 * i + 1] - m_new[i]) : 0.0f;
+                sum += w0 + w1;
+                pa[n][i] = half_pair(w0, w1);
+            }
+            l_run[i] = l_run[i] * corr + sum;
+            m_run[i] = m_new[i];
+#pragma unroll
+            for (int o = 0; o < 16; ++o) { acc[o][2 * i] *= corr; acc[o][2 * i + 1] *= corr; }
+        }
+        // Outputs: this warp's half of the dimensions, J = 2 * half, 2 * half + 1.
+        const __half* value[4];
+#pragma unroll
+        for (int u = 0; u < 4; ++u) value[u] = row_pointer(tile + 2u * t + (u & 1) + 8u * (u >> 1), ring_v, priv_v);
+#pragma unroll
+        for (int jj = 0; jj < 2; ++jj) {
+            const uint32_t J = 2u * half + jj;
+            uint4 vr[4];
+#pragma unroll
+            for (int u = 0; u < 4; ++u) vr[u] = __ldcg(reinterpret_cast<const uint4*>(value[u] + 64u * J + 8u * g));
+#pragma unroll
+            for (int j = 0; j < 8; ++j) {
+                const uint32_t sel = (j & 1) ? 0x7632u : 0x5410u;
+                const uint32_t b0 = __byte_perm(word_at(vr[0], j >> 1), word_at(vr[1], j >> 1), sel);
+                const uint32_t b1 = __byte_perm(word_at(vr[2], j >> 1), word_at(vr[3], j >> 1), sel);
+                mma_f16(acc[jj * 8 + j], pa[0][0], pa[0][1], pa[1][0], pa[1][1], b0, b1);
+            }
+        }
+    }
+    // l over the four lanes that share a row.
+#pragma unroll
+    for (int i = 0; i < 2; ++i) {
+        l_run[i] += __shfl_xor_sync(0xffffffffu, l_run[i], 1);
+        l_run[i] += __shfl_xor_sync(0xffffffffu, l_run[i], 2);
+    }
+    // Merge of the pairs: every pair rescales its sums to the common maximum and the common denominator, then
+    // pairs 2 and 3 hand their sums to pairs 0 and 1, and pair 1 hands the result to pair 0.
+    if (half == 0u && t == 0u) {
+#pragma unroll
+        for (int i = 0; i < 2; ++i) { merge_m[pair][g + 8 * i] = m_run[i]; merge_l[pair][g + 8 * i] = l_run[i]; }
+    }
+    __syncthreads();
+#pragma unroll
+    for (int i = 0; i < 2; ++i) {
+        float top = -INFINITY;
+#pragma unroll
+        for (uint32_t q = 0; q < kAttentionPairs; ++q) top = fmaxf(top, merge_m[q][g + 8 * i]);
+        float denominator = 0.0f;
+#pragma unroll
+        for (uint32_t q = 0; q < kAttentionPairs; ++q) {
+            const float mq = merge_m[q][g + 8 * i];
+            if (mq != -INFINITY) denominator += merge_l[q][g + 8 * i] * expf(mq - top);
+        }
+        const float factor = (m_run[i] == -INFINITY || denominator == 0.0f) ? 0.0f : expf(m_run[i] - top) / denominator;
+#pragma unroll
+        for (int o = 0; o < 16; ++o) { acc[o][2 * i] *= factor; acc[o][2 * i + 1] *= factor; }
+    }
+    if (pair >= 2u) {
+#pragma unroll
+        for (int o = 0; o < 16; ++o)
+#pragma unroll
+            for (int e = 0; e < 4; ++e) merge_acc[pair - 2u][half][o * 4 + e][lane] = acc[o][e];
+    }
+    __syncthreads();
+    if (pair < 2u) {
+#pragma unroll
+        for (int o = 0; o < 16; ++o)
+#pragma unroll
+            for (int e = 0; e < 4; ++e) acc[o][e] += merge_acc[pair][half][o * 4 + e][lane];
+    }
+    __syncthreads();
+    if (pair == 1u) {
+#pragma unroll
+        for (int o = 0; o < 16; ++o)
+#pragma unroll
+            for (int e = 0; e < 4; ++e) merge_acc[0][half][o * 4 + e][lane] = acc[o][e];
+    }
+    __syncthreads();
+    if (pair != 0u) return;
+#pragma unroll
+    for (int o = 0; o < 16; ++o)
+#pragma unroll
+        for (int e = 0; e < 4; ++e) acc[o][e] += merge_acc[0][half][o * 4 + e][lane];
+#pragma unroll
+    for (int i = 0; i < 2; ++i) {
+        if (!live[i]) continue;
+        const uint32_t m = g + 8u * i, row = first_row + m / G, head = kvh * G + m % G;
+        float* out = p.out + ((size_t)row * p.heads + head) * 256u;
+        const float inv = 1.0f;
+#pragma unroll
+        for (int jj = 0; jj < 2; ++jj)
+#pragma unroll
+            for (int j = 0; j < 8; ++j) {
+                // Columns 2t and 2t + 1 of output tile (J, j) stand for dimensions 64J + 8 * (2t) + j and 64J + 8 * (2t + 1) + j.
+                const uint32_t J = 2u * half + jj;
+                out[64u * J + 16u * t + j] = acc[jj * 8 + j][2 * i] * inv;
+                out[64u * J + 16u * t + 8u + j] = acc[jj * 8 + j][2 * i + 1] * inv;
+            }
+    }
 }
 
 }  // namespace
@@ -474,11 +723,18 @@ int launch_prefill_gemm(const PrefillGemmLaunch& launch, int* error_flag, cudaSt
 }
 
 uint32_t prefill_gemm_splits(uint64_t n, uint64_t k, int dtype) {
-    // A narrow output leaves most SMs without a tile: cut K so that about one wave of CTAs runs.
-    const uint32_t tiles = (uint32_t)(n / kPrefillTile), units = (uint32_t)(k / unit_elements(dtype));
-    uint32_t splits = tiles ? (uint32_t)sm_count() / tiles : 1u;
-    splits = splits < 1u ? 1u : splits > kPrefillMaxSplits ? kPrefillMaxSplits : splits;
-    return splits > units ? units : splits;
+    // CTAs run one per SM, wave after wave: a launch costs ceil(tiles * splits / SMs) waves of 1 / splits of the
+    // whole K each.  Take the split with the least time; ties go to fewer splits.
+    const uint32_t tiles = (uint32_t)(n / kPrefillTile), units = (uint32_t)(k / unit_elements(dtype)), sms = (uint32_t)sm_count();
+    if (tiles >= sms) return 1;         // every SM already has a tile: more CTAs only add partial results
+    uint32_t best = 1;
+    double best_cost = 1e30;
+    for (uint32_t splits = 1; splits <= kPrefillMaxSplits && splits <= units; ++splits) {
+        const uint32_t waves = (tiles * splits + sms - 1u) / sms;
+        const double cost = (double)waves * ((double)((units + splits - 1u) / splits) + 0.5);      // half a unit of set-up and epilogue per CTA
+        if (cost < best_cost - 1e-9) { best_cost = cost; best = splits; }
+    }
+    return best;
 }
 
 int launch_prefill_norm(const float* x, uint32_t splits, const float* residual, const float* gamma0, const float* gamma1,
@@ -492,9 +748,36 @@ int launch_prefill_norm(const float* x, uint32_t splits, const float* residual, 
     return GF_OK;
 }
 
-int launch_prefill_geglu(const float* gate, const float* up, void* a_out, uint32_t rows, uint32_t k, cudaStream_t stream) {
-    if (!gate || !up || !a_out || rows == 0 || rows > kPrefillRows || k % 8u) return fail(GF_ERR_INVALID, "prefill GeGLU: bad arguments");
-    prefill_geglu_kernel<<<dim3(kPrefillRows, (k / 8u + 255u) / 256u), 256, 0, stream>>>(gate, up, static_cast<uint8_t*>(a_out), rows, k);
+int launch_prefill_reduce(float* const* x, const uint64_t* n, uint32_t count, uint32_t splits, uint32_t rows, cudaStream_t stream) {
+    if (!x || !n || count == 0 || count > 3 || splits == 0 || rows == 0 || rows > kPrefillRows) return fail(GF_ERR_INVALID, "prefill reduce: bad arguments");
+    if (splits == 1) return GF_OK;
+    ReduceSet set = {};
+    for (uint32_t i = 0; i < count; ++i) { set.x[i] = x[i]; set.n[i] = (uint32_t)n[i]; }
+    set.count = count; set.splits = splits;
+    prefill_reduce_kernel<<<dim3(rows, 2), 256, 0, stream>>>(set, rows);
+    GF_CUDA(cudaGetLastError());
+    return GF_OK;
+}
+
+int launch_prefill_geglu(const float* gate, const float* up, uint32_t splits, void* a_out, uint32_t rows, uint32_t k, cudaStream_t stream) {
+    if (!gate || !up || !a_out || splits == 0 || rows == 0 || rows > kPrefillRows || k % 8u) return fail(GF_ERR_INVALID, "prefill GeGLU: bad arguments");
+    prefill_geglu_kernel<<<dim3(kPrefillRows, (k / 8u + 255u) / 256u), 256, 0, stream>>>(gate, up, splits, static_cast<uint8_t*>(a_out), rows, k);
+    GF_CUDA(cudaGetLastError());
+    return GF_OK;
+}
+
+bool prefill_attention_supported(const AttentionParams& p) {
+    const uint32_t group = p.kv_heads ? p.heads / p.kv_heads : 0u;
+    return p.kv_f16 && p.head_dim == 256u && p.kv_heads != 0u && p.heads % p.kv_heads == 0u && (group == 1u || group == 2u || group == 4u);
+}
+
+int launch_prefill_attention(const AttentionParams& p, cudaStream_t stream) {
+    if (!prefill_attention_supported(p) || p.rows == 0 || p.rows > kPrefillRows) return fail(GF_ERR_INVALID, "prefill attention: unsupported shape");
+    const uint32_t group = p.heads / p.kv_heads, rows_per_block = 16u / group;
+    const dim3 grid(p.kv_heads, (p.rows + rows_per_block - 1u) / rows_per_block);
+    if (group == 1u) prefill_attention_kernel<1><<<grid, 64 * kAttentionPairs, 0, stream>>>(p);
+    else if (group == 2u) prefill_attention_kernel<2><<<grid, 64 * kAttentionPairs, 0, stream>>>(p);
+    else prefill_attention_kernel<4><<<grid, 64 * kAttentionPairs, 0, stream>>>(p);
     GF_CUDA(cudaGetLastError());
     return GF_OK;
 }
@@ -513,6 +796,25 @@ using namespace gf;
 extern "C" {
 
 size_t gf_prefill_workspace_bytes(uint64_t k) { return tile_major_bytes(k); }
+
+int gf_prefill_attention(const float* q_dev, const void* ring_k_dev, const void* ring_v_dev, const void* private_k_dev,
+                         const void* private_v_dev, float* out_dev, const uint32_t* base_position_dev, uint32_t rows,
+                         uint32_t heads, uint32_t kv_heads, uint32_t head_dim, uint32_t ring_rows, uint32_t window, float scale,
+                         float softcap, void* stream) {
+    if (!q_dev || !ring_k_dev || !ring_v_dev || !private_k_dev || !private_v_dev || !out_dev || !base_position_dev || rows == 0
+        || rows > kPrefillRows || ring_rows == 0 || (ring_rows & (ring_rows - 1u)))
+        return fail(GF_ERR_INVALID, "gf_prefill_attention: bad arguments (ring rows must be a power of two, rows at most %u)", kPrefillRows);
+    const uintptr_t pointers = reinterpret_cast<uintptr_t>(q_dev) | reinterpret_cast<uintptr_t>(ring_k_dev) | reinterpret_cast<uintptr_t>(ring_v_dev)
+        | reinterpret_cast<uintptr_t>(private_k_dev) | reinterpret_cast<uintptr_t>(private_v_dev) | reinterpret_cast<uintptr_t>(out_dev);
+    if (pointers & 15u) return fail(GF_ERR_INVALID, "gf_prefill_attention: device pointers must be 16-byte aligned");
+    AttentionParams p;
+    p.q = q_dev; p.ring_k = ring_k_dev; p.ring_v = ring_v_dev; p.private_k = private_k_dev; p.private_v = private_v_dev;
+    p.out = out_dev; p.partial_out = nullptr; p.partial_ml = nullptr; p.counters = nullptr;
+    p.base_position = base_position_dev;
+    p.rows = rows; p.heads = heads; p.kv_heads = kv_heads; p.head_dim = head_dim;
+    p.ring_mask = ring_rows - 1u; p.window = window; p.target_parts = 1; p.scale = scale; p.softcap = softcap; p.kv_f16 = 1;
+    return launch_prefill_attention(p, as_stream(stream));
+}
 
 int gf_prefill_matmul(int dtype, const void* packed_dev, const float* x_dev, float* y_dev, uint32_t rows, uint64_t k, uint64_t n,
                       void* workspace_dev, void* stream) {
@@ -549,4 +851,3 @@ int gf_prefill_matmul(int dtype, const void* packed_dev, const float* x_dev, flo
 }
 
 }  // extern "C"
-

@@ -53,7 +53,7 @@ struct PrefillGemmLaunch {
 };
 constexpr uint32_t kPrefillMaxSplits = 4;
 int launch_prefill_gemm(const PrefillGemmLaunch& launch, int* error_flag, cudaStream_t stream);
-// K splits that give a single [K, n] matrix about one wave of CTAs (1 for wide outputs).
+// K splits that finish a launch of n output columns (over all its matrices) in the fewest waves of CTAs.
 uint32_t prefill_gemm_splits(uint64_t n, uint64_t k, int dtype);
 
 // Elementwise steps between the GEMMs, each writing the next GEMM's tile-major bf16 operand.
@@ -62,8 +62,14 @@ uint32_t prefill_gemm_splits(uint64_t n, uint64_t k, int dtype);
 // x is the sum, in split order, of `splits` partial results laid [split][128][k].
 int launch_prefill_norm(const float* x, uint32_t splits, const float* residual, const float* gamma0, const float* gamma1,
                         float* residual_out, void* a_out, uint32_t rows, uint32_t k, float eps, int mode, cudaStream_t stream);
-// a = gelu_tanh(gate) * up
-int launch_prefill_geglu(const float* gate, const float* up, void* a_out, uint32_t rows, uint32_t k, cudaStream_t stream);
+// a = gelu_tanh(gate) * up, gate and up each the sum of `splits` partial results
+int launch_prefill_geglu(const float* gate, const float* up, uint32_t splits, void* a_out, uint32_t rows, uint32_t k, cudaStream_t stream);
+// x[i][0][row][:] = sum over splits of x[i][split][row][:], for `count` <= 3 matrices of n[i] columns
+int launch_prefill_reduce(float* const* x, const uint64_t* n, uint32_t count, uint32_t splits, uint32_t rows, cudaStream_t stream);
+// Attention of a chunk's rows over ring + private rows of a binary16 cache with 256-wide heads (f32 output
+// [rows][heads * 256]); other shapes go through the row kernels (launch_attention).
+bool prefill_attention_supported(const struct AttentionParams& p);
+int launch_prefill_attention(const struct AttentionParams& p, cudaStream_t stream);
 // a = x (f32 rows of width k)
 int launch_prefill_pack(const float* x, void* a_out, uint32_t rows, uint32_t k, cudaStream_t stream);
 

@@ -43,6 +43,7 @@ lib.register({
     "gf_qk_norm_rope_store": (i32, [vp, vp, vp, vp, vp, vp, vp, vp, vp, vp, u32, u32, u32, u32, f32, f32, f32, i32, vp]),
     "gf_attention_workspace_bytes": (sz, [u32, u32]),
     "gf_attention": (i32, [vp, vp, vp, vp, vp, vp, vp, vp, u32, u32, u32, u32, u32, u32, f32, f32, i32, vp]),
+    "gf_prefill_attention": (i32, [vp, vp, vp, vp, vp, vp, vp, u32, u32, u32, u32, u32, u32, f32, f32, vp]),
     "gf_gelu_tanh_multiply": (i32, [vp, vp, vp, u64, vp]),
     "gf_kv_scatter": (i32, [vp, vp, vp, vp, vp, u32, u32, u32, i32, vp]),
     "gf_selection_request_bytes": (sz, []),

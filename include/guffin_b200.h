@@ -131,6 +131,16 @@ GF_API int gf_matmul_static_check(void* stream);
 GF_API size_t gf_prefill_workspace_bytes(uint64_t k);
 GF_API int gf_prefill_matmul(int dtype, const void* packed_dev, const float* x_dev, float* y_dev,
                              uint32_t rows, uint64_t k, uint64_t n, void* workspace_dev, void* stream);
+/* Attention of a prompt chunk (up to 128 rows) over the ring and the chunk's private rows of a binary16
+ * cache with 256-wide heads, both contractions on the tensor cores with f16 operands (queries rounded to
+ * f16 after scaling): the reference's flash prefill attention, encode_f16_prefill_attention
+ * (metal_command_context.hpp; MSL metal_kernels.mm:2596-2798).  Same arguments as gf_attention without
+ * the workspace; out_dev is [rows][heads * 256] f32.  Agrees with gf_attention to about 1e-3. */
+GF_API int gf_prefill_attention(const float* q_dev, const void* ring_k_dev, const void* ring_v_dev,
+                                const void* private_k_dev, const void* private_v_dev, float* out_dev,
+                                const uint32_t* base_position_dev, uint32_t rows, uint32_t heads,
+                                uint32_t kv_heads, uint32_t head_dim, uint32_t ring_rows, uint32_t window,
+                                float scale, float softcap, void* stream);
 /* Same product from HOST buffers through an internal context: uploads x, runs, downloads y.
  * `packed_dev` stays device-resident (weights are uploaded once at load time). */
 GF_API int gf_matmul_host(int dtype, const void* packed_dev, const float* x_host, float* y_host,

@@ -86,3 +86,38 @@ def test_tensor_prefill_matches_exact_row_path(gf, gm, oracle, geometry, seed):
         model.publish(2)
         assert model.status() == 0
     assert rel_l2(tensor.logits(1), exact.logits(1)) < 3e-2
+
+
+@pytest.mark.parametrize("base,rows,window,ring_rows,heads,kv_heads,softcap", [
+    (700, 128, 0, 1024, 4, 2, 0.0),         # global layer, a full chunk
+    (300, 37, 64, 128, 4, 2, 0.0),          # sliding window inside the ring (wrapped) and into the private rows
+    (0, 100, 16, 32, 2, 2, 0.0),            # first chunk of a prompt: private rows only, one head per KV head
+    (90, 128, 0, 128, 4, 1, 50.0),          # four heads per KV head, score softcap
+    (5, 3, 4, 8, 4, 2, 0.0),                # a few rows
+])
+def test_prefill_attention_matches_oracle(gf, oracle, base, rows, window, ring_rows, heads, kv_heads, softcap):
+    """The chunk attention kernel against the oracle's row attention over each row's logical key
+    range (causal, sliding window including the row itself, ring slots overwritten by later
+    positions): f16 queries and softmax weights on the tensor cores, tolerance 2e-3."""
+    L = gf.load()
+    hd, kvw = 256, kv_heads * 256
+    rng = np.random.default_rng(base + rows)
+    keys = rng.standard_normal((base + rows, kvw)).astype(np.float16)
+    values = rng.standard_normal((base + rows, kvw)).astype(np.float16)
+    q = rng.standard_normal((rows, heads * hd)).astype(np.float32)
+    ring_k, ring_v = np.zeros((ring_rows, kvw), np.float16), np.zeros((ring_rows, kvw), np.float16)
+    for p in range(base):
+        ring_k[p & (ring_rows - 1)], ring_v[p & (ring_rows - 1)] = keys[p], values[p]
+    bufs = [gf.DeviceBuffer.from_numpy(np.ascontiguousarray(a)) for a in (q, ring_k, ring_v, keys[base:], values[base:])]
+    out = gf.DeviceBuffer(q.nbytes)
+    pos = gf.DeviceBuffer.from_numpy(np.array([base], np.uint32))
+    gf.check(L.gf_prefill_attention(bufs[0].ptr, bufs[1].ptr, bufs[2].ptr, bufs[3].ptr, bufs[4].ptr, out.ptr, pos.ptr,
+                                    rows, heads, kv_heads, hd, ring_rows, window, 0.0625, softcap, None))
+    gf.check(L.gf_stream_synchronize(None))
+    got = out.download(np.float32).reshape(rows, -1)
+    for r in range(rows):
+        p = base + r
+        first = max(0, p + 1 - window) if window else 0
+        want = oracle.attention_row(q[r], keys[first:p + 1].astype(np.float32), values[first:p + 1].astype(np.float32),
+                                    heads, kv_heads, hd, 0.0625, softcap)
+        assert np.abs(got[r] - want).max() <= 2e-3 * max(1.0, np.abs(want).max()), (base, r, window)
