@@ -180,6 +180,53 @@ __global__ void __launch_bounds__(1024) candidate_merge_kernel(const float* __re
     if (threadIdx.x == 0) result.count = retain + history_count;
 }
 
+// Selection requests written on the device: the role of gd_requests (src/engine/gemma3_draft.mm:396-400),
+// which fills VerifierDeviceSelectionRow (target_verifier.hpp:114-121) from the sampler's history row and
+// the drafted tokens, and of the resolve step of encode_verifier_selection_requests.  `base` is
+// { top_k, window_limit, count, tokens[64] }: the repetition window as the host sampler holds it,
+// oldest first.  Row i of `chain` (the root, then the drafted tokens, in device memory) gets the request
+// of the context "window, then chain[0..i]": the window slides over the appended tokens, then its
+// distinct tokens in order of first appearance are the history, and retain = top_k + their number --
+// what Sampler::request_after builds on the host.  One thread per row.
+struct RequestBase { uint32_t top_k, window_limit, count, tokens[kMaxHistory]; };
+
+__global__ void request_rows_kernel(const RequestBase* __restrict__ base, uint32_t root, const uint32_t* __restrict__ chain,
+                                    uint32_t first_row, uint32_t row_count, SelectionRequest* __restrict__ out) {
+    pdl_wait();
+    pdl_launch_dependents();
+    const uint32_t row = first_row + blockIdx.x * blockDim.x + threadIdx.x;
+    if (row >= first_row + row_count) return;
+    const uint32_t limit = min(base->window_limit, kMaxHistory), held = min(base->count, limit);
+    SelectionRequest request;
+    request.history_count = 0;
+    if (limit != 0u) {
+        // The window after the slide: the last `limit` of (held tokens, then chain[0..row]).
+        const uint32_t appended = row + 1u, total = held + appended;
+        const uint32_t skip = total > limit ? total - limit : 0u;
+        for (uint32_t i = skip; i < total; ++i) {
+            const uint32_t token = i < held ? base->tokens[i] : (i == held ? root : chain[i - held]);
+            bool seen = false;
+            for (uint32_t j = 0; j < request.history_count; ++j) seen |= request.history[j] == token;
+            if (!seen) request.history[request.history_count++] = token;
+        }
+    }
+    request.retain = base->top_k + request.history_count;
+    for (uint32_t j = request.history_count; j < kMaxHistory; ++j) request.history[j] = 0u;
+    out[row] = request;
+}
+
+size_t request_base_bytes() { return sizeof(RequestBase); }
+
+// Rows [first_row, first_row + row_count) of `requests_dev` from the base window at `base_dev`; chain[0] is
+// taken from `root` (the host knows it), chain[i > 0] from `chain_dev[i]`.
+int launch_request_rows(const void* base_dev, uint32_t root, const uint32_t* chain_dev, uint32_t first_row, uint32_t row_count,
+                        void* requests_dev, cudaStream_t stream) {
+    if (!base_dev || !chain_dev || !requests_dev || row_count == 0 || first_row + row_count > GF_MAX_ROWS)
+        return fail(GF_ERR_INVALID, "selection request rows: bad arguments");
+    return launch_kernel(request_rows_kernel, dim3(1), dim3(32), 0, stream, false, static_cast<const RequestBase*>(base_dev), root,
+                         chain_dev, first_row, row_count, static_cast<SelectionRequest*>(requests_dev));
+}
+
 size_t candidates_workspace_bytes(uint32_t rows, uint32_t vocab) {
     const uint32_t tiles = (vocab + kTile - 1u) / kTile;
     return (size_t)rows * tiles * kMaxRetain * sizeof(uint64_t);
@@ -207,6 +254,13 @@ extern "C" {
 size_t gf_token_candidates_workspace_bytes(uint32_t rows, uint32_t vocab) { return candidates_workspace_bytes(rows, vocab); }
 size_t gf_selection_request_bytes(void) { return sizeof(SelectionRequest); }
 size_t gf_candidate_result_bytes(void) { return sizeof(CandidateResult); }
+
+size_t gf_selection_base_bytes(void) { return request_base_bytes(); }
+
+int gf_selection_requests(const void* base_dev, uint32_t root, const uint32_t* chain_dev, uint32_t rows, void* requests_dev,
+                          void* stream) {
+    return launch_request_rows(base_dev, root, chain_dev, 0, rows, requests_dev, as_stream(stream));
+}
 
 int gf_token_candidates(const float* logits_dev, uint32_t rows, uint32_t vocab, float softcap, const void* requests_dev,
                         void* workspace_dev, void* results_dev, void* stream) {

@@ -7,6 +7,9 @@
 // turned into an integer CDF with total exactly 2^32; the drafted token is the bin holding the
 // 32-bit proposal word.  The bins, not an idealised softmax, are the law q that the lossless
 // acceptance test divides by, so the sampler and the receipt can never disagree.
+// A support of more than 256 tokens is reported as status 20; the caller then builds the law over
+// the whole vocabulary from the same scores (draft_full.cu), as it does from the start when top_k is
+// disabled or above 64.
 #include "ops.cuh"
 
 namespace gf {
@@ -35,11 +38,13 @@ struct CandidateHead {                // leading fields of the candidate result 
 
 __global__ void __launch_bounds__(256) draft_process_kernel(const float* __restrict__ logits, uint32_t vocab, float temperature,
                                                             float penalty, const uint32_t* __restrict__ history,
-                                                            uint32_t history_count, float* __restrict__ scores,
+                                                            uint32_t history_count, const uint32_t* __restrict__ history_count_dev,
+                                                            float* __restrict__ scores,
                                                             DraftReceipt* receipt, uint32_t* support_count) {
     __shared__ uint32_t hist[64];
     pdl_wait();
     pdl_launch_dependents();
+    if (history_count_dev) history_count = min(*history_count_dev, 64u);       // a request row written on the device
     const bool penalise = penalty != 1.0f && history_count != 0u;
     if (penalise) {
         for (uint32_t i = threadIdx.x; i < history_count && i < 64u; i += blockDim.x) hist[i] = history[i];
@@ -61,15 +66,18 @@ __global__ void __launch_bounds__(256) draft_process_kernel(const float* __restr
 }
 
 __global__ void __launch_bounds__(256) draft_collect_kernel(const float* __restrict__ scores, uint32_t vocab,
-                                                            const CandidateHead* best, uint32_t top_k,
+                                                            const CandidateHead* best, uint32_t top_k, int greedy,
                                                             DraftPair* support, uint32_t* support_count) {
     pdl_wait();
     pdl_launch_dependents();
     const uint32_t have = min(best->count, top_k);
     const float cutoff = have ? best->candidates[have - 1u].logit : INFINITY;
+    // A greedy drafter puts all mass on the argmax, the lowest token id among exact ties (the step CDF
+    // of gd_cdf, gemma3_draft.mm:372-381).
+    const uint32_t only = greedy && have ? best->candidates[0].token : 0xffffffffu;
     for (uint32_t i = blockIdx.x * blockDim.x + threadIdx.x; i < vocab; i += gridDim.x * blockDim.x) {
         const float s = scores[i];
-        if (s >= cutoff) {
+        if (greedy ? i == only : s >= cutoff) {
             const uint32_t slot = atomicAdd(support_count, 1u);
             if (slot < kDraftSupportMax) support[slot] = DraftPair{i, s};
         }
@@ -156,18 +164,35 @@ __global__ void __launch_bounds__(256) draft_law_kernel(const DraftPair* __restr
     }
 }
 
-size_t draft_sampler_workspace_bytes(uint32_t vocab) {
-    return (size_t)vocab * 4 + candidates_workspace_bytes(1, vocab) + 264 + 3080 + kDraftSupportMax * sizeof(DraftPair) + 64
-           + 64 * 4 + 256;
+size_t draft_full_workspace_bytes(uint32_t vocab);
+int launch_draft_law_full(float* scores, uint32_t vocab, float temperature, uint32_t top_k, float top_p, float min_p,
+                          uint32_t word, void* workspace, void* receipt_dev, bool keep_status, uint32_t* out_token_a,
+                          uint32_t* out_token_b, cudaStream_t stream);
+int launch_draft_gather_full(void* workspace, uint32_t vocab, const uint32_t* tokens_host, uint32_t count, uint64_t* intervals_host,
+                             cudaStream_t stream);
+
+static size_t compact_workspace_bytes(uint32_t vocab) {
+    const size_t bytes = (size_t)vocab * 4 + candidates_workspace_bytes(1, vocab) + 264 + 3080 + kDraftSupportMax * sizeof(DraftPair) + 64
+                         + 64 * 4 + 256;
+    return (bytes + 255u) & ~(size_t)255u;
 }
+// The compact sampler's scratch, then the full-vocabulary law's (sorted keys, prefix sums, the CDF).
+size_t draft_sampler_workspace_bytes(uint32_t vocab) { return compact_workspace_bytes(vocab) + draft_full_workspace_bytes(vocab); }
+
+// The compact law serves a tempered drafter with 1 <= top_k <= 64 (Impl::sample's `compact`,
+// gemma3_draft.mm:1022-1024); a greedy drafter is a point mass and takes the same kernels.
+bool draft_law_is_compact(float temperature, uint32_t top_k) { return temperature == 0.0f || (top_k >= 1u && top_k <= 64u); }
 
 // Lays the scratch out inside one allocation and runs the five launches.
+// `history_request_dev` (optional): a selection request row in device memory ({ retain, count, tokens[64] })
+// whose history replaces history_host -- the drafter then penalises drafts the host has not seen yet.
 int launch_draft_sample(const float* logits, uint32_t vocab, float temperature, uint32_t top_k, float top_p, float min_p,
                         float penalty, const uint32_t* history_host, uint32_t history_count, uint32_t word,
                         void* workspace, void* receipt_dev, uint32_t* out_token_a, uint32_t* out_token_b,
-                        cudaStream_t stream) {
-    if (!logits || !workspace || !receipt_dev || vocab == 0 || top_k == 0 || top_k > 64u || history_count > 64u)
-        return fail(GF_ERR_INVALID, "draft sampler: bad arguments (top_k must be 1..64 for the compact law)");
+                        cudaStream_t stream, const uint32_t* history_request_dev) {
+    if (!logits || !workspace || !receipt_dev || vocab == 0 || history_count > 64u)
+        return fail(GF_ERR_INVALID, "draft sampler: bad arguments");
+    const bool compact = draft_law_is_compact(temperature, top_k);
     uint8_t* base = static_cast<uint8_t*>(workspace);
     float* scores = reinterpret_cast<float*>(base); base += (size_t)vocab * 4;
     void* cand_ws = base; base += candidates_workspace_bytes(1, vocab);
@@ -181,20 +206,45 @@ int launch_draft_sample(const float* logits, uint32_t vocab, float temperature, 
     const uint32_t effective_k = temperature == 0.0f ? 1u : top_k;      // a greedy drafter puts all mass on the argmax
     const uint32_t request_words[2] = {effective_k, 0u};
     GF_CUDA(cudaMemcpyAsync(request, request_words, 8, cudaMemcpyHostToDevice, stream));
-    if (history_count && penalty != 1.0f)
+    if (!history_request_dev && history_count && penalty != 1.0f)
         GF_CUDA(cudaMemcpyAsync(history_dev, history_host, history_count * 4u, cudaMemcpyHostToDevice, stream));
+    const uint32_t* history_tokens = history_request_dev ? history_request_dev + 2 : history_dev;
+    const uint32_t* history_count_dev = history_request_dev ? history_request_dev + 1 : nullptr;
     const uint32_t blocks = min((vocab + 255u) / 256u, 1024u);
     int status = launch_kernel(draft_process_kernel, dim3(blocks), dim3(256), 0, stream, false, logits, vocab, temperature,
-                               penalty, (const uint32_t*)history_dev, history_count, scores, receipt, support_count);
+                               penalty, history_tokens, history_count, history_count_dev, scores, receipt, support_count);
     if (status != GF_OK) return status;
+    if (!compact)       // top_k disabled or above 64: the law over the whole vocabulary
+        return launch_draft_law_full(scores, vocab, temperature, top_k, top_p, min_p, word,
+                                     static_cast<uint8_t*>(workspace) + compact_workspace_bytes(vocab), receipt_dev, true,
+                                     out_token_a, out_token_b, stream);
     status = launch_candidates(scores, 1, vocab, 0.0f, request, cand_ws, best, stream, false);
     if (status != GF_OK) return status;
     status = launch_kernel(draft_collect_kernel, dim3(blocks), dim3(256), 0, stream, false, (const float*)scores, vocab,
-                           (const CandidateHead*)best, effective_k, support, support_count);
+                           (const CandidateHead*)best, effective_k, temperature == 0.0f ? 1 : 0, support, support_count);
     if (status != GF_OK) return status;
     return launch_kernel(draft_law_kernel, dim3(1), dim3(256), 0, stream, false, (const DraftPair*)support,
                          (const uint32_t*)support_count, temperature == 0.0f ? 1.0f : top_p, temperature == 0.0f ? 0.0f : min_p,
                          word, receipt, out_token_a, out_token_b);
+}
+
+// After a compact receipt reported status 20 (more than 256 tokens reach the top_k cut-off): builds the
+// full-vocabulary law from the processed scores the compact pass left in `workspace` -- same logits, same
+// proposal word -- and selects the drafted token from it.
+int launch_draft_resolve_overflow(uint32_t vocab, float temperature, uint32_t top_k, float top_p, float min_p, uint32_t word,
+                                  void* workspace, void* receipt_dev, uint32_t* out_token_a, uint32_t* out_token_b,
+                                  cudaStream_t stream) {
+    if (!workspace || !receipt_dev || vocab == 0) return fail(GF_ERR_INVALID, "draft sampler: bad arguments");
+    return launch_draft_law_full(static_cast<float*>(workspace), vocab, temperature, top_k, top_p, min_p, word,
+                                 static_cast<uint8_t*>(workspace) + compact_workspace_bytes(vocab), receipt_dev, true,
+                                 out_token_a, out_token_b, stream);
+}
+
+int launch_draft_gather(void* workspace, uint32_t vocab, const uint32_t* tokens_host, uint32_t count, uint64_t* intervals_host,
+                        cudaStream_t stream) {
+    if (!workspace) return fail(GF_ERR_INVALID, "draft gather: null workspace");
+    return launch_draft_gather_full(static_cast<uint8_t*>(workspace) + compact_workspace_bytes(vocab), vocab, tokens_host, count,
+                                    intervals_host, stream);
 }
 
 }  // namespace gf
@@ -210,7 +260,18 @@ int gf_draft_sample(const float* logits_dev, uint32_t vocab, float temperature, 
                     float repetition_penalty, const uint32_t* history_host, uint32_t history_count, uint32_t word,
                     void* workspace_dev, void* receipt_dev, uint32_t* out_token_dev, void* stream) {
     return launch_draft_sample(logits_dev, vocab, temperature, top_k, top_p, min_p, repetition_penalty, history_host,
-                               history_count, word, workspace_dev, receipt_dev, out_token_dev, nullptr, as_stream(stream));
+                               history_count, word, workspace_dev, receipt_dev, out_token_dev, nullptr, as_stream(stream), nullptr);
+}
+
+int gf_draft_resolve_overflow(uint32_t vocab, float temperature, uint32_t top_k, float top_p, float min_p, uint32_t word,
+                              void* workspace_dev, void* receipt_dev, uint32_t* out_token_dev, void* stream) {
+    return launch_draft_resolve_overflow(vocab, temperature, top_k, top_p, min_p, word, workspace_dev, receipt_dev, out_token_dev,
+                                         nullptr, as_stream(stream));
+}
+
+int gf_draft_gather_full(void* workspace_dev, uint32_t vocab, const uint32_t* tokens_host, uint32_t count,
+                         uint64_t* intervals_host, void* stream) {
+    return launch_draft_gather(workspace_dev, vocab, tokens_host, count, intervals_host, as_stream(stream));
 }
 
 }  // extern "C"

@@ -50,13 +50,18 @@ __device__ __forceinline__ float packed_element(int dtype, const uint8_t* packed
 __device__ __forceinline__ void embedding_rows(int dtype, const uint8_t* __restrict__ packed, uint32_t k, uint32_t vocab,
                                                const uint32_t* __restrict__ tokens, uint32_t rows, float scale,
                                                float* __restrict__ out, uint32_t* status, uint32_t first, uint32_t stride) {
-    const uint32_t units = k / unit_elements(dtype);
+    const uint32_t units = dtype == GF_F16 ? 0u : k / unit_elements(dtype);
     for (uint32_t i = first; i < rows * k; i += stride) {
         const uint32_t row = i / k, e = i % k;
         const uint32_t token = tokens[row];
         if (token >= vocab) {
             if (e == 0) atomicOr(status, kStatusBadToken);
             out[i] = __int_as_float(0x7fc00000);
+            continue;
+        }
+        if (dtype == GF_F16) {      // a binary16 table as stored, [vocab][k] (the retained Gemma 2 9B embedding)
+            const unsigned short bits = reinterpret_cast<const unsigned short*>(packed)[(size_t)token * k + e];
+            out[i] = __fmul_rn(__half2float(__ushort_as_half(bits)), scale);
             continue;
         }
         out[i] = __fmul_rn(packed_element(dtype, packed, units, token, e), scale);

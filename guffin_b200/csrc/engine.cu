@@ -2,6 +2,7 @@
 #include "model.cuh"
 #include "sampler.hpp"
 
+#include <algorithm>
 #include <cstring>
 #include <memory>
 #include <random>
@@ -13,6 +14,14 @@ size_t draft_sampler_workspace_bytes(uint32_t vocab);
 int launch_draft_sample(const float* logits, uint32_t vocab, float temperature, uint32_t top_k, float top_p, float min_p,
                         float penalty, const uint32_t* history_host, uint32_t history_count, uint32_t word,
                         void* workspace, void* receipt_dev, uint32_t* out_token_a, uint32_t* out_token_b,
+                        cudaStream_t stream, const uint32_t* history_request_dev);
+size_t request_base_bytes();
+int launch_request_rows(const void* base_dev, uint32_t root, const uint32_t* chain_dev, uint32_t first_row, uint32_t row_count,
+                        void* requests_dev, cudaStream_t stream);
+int launch_draft_resolve_overflow(uint32_t vocab, float temperature, uint32_t top_k, float top_p, float min_p, uint32_t word,
+                                  void* workspace, void* receipt_dev, uint32_t* out_token_a, uint32_t* out_token_b,
+                                  cudaStream_t stream);
+int launch_draft_gather(void* workspace, uint32_t vocab, const uint32_t* tokens_host, uint32_t count, uint64_t* intervals_host,
                         cudaStream_t stream);
 
 #define GF_TRY(expr) do { const int gf_s_ = (expr); if (gf_s_ != GF_OK) return gf_s_; } while (0)
@@ -28,6 +37,7 @@ static SamplerOptions to_options(const gf_sampler_options& o) {
 struct SelectionRequestRow { uint32_t retain, history_count, history[64]; };
 struct CandidateRow { uint32_t status, count; TokenLogit candidates[384]; };
 struct DraftReceiptRow { uint32_t status, count, token, word, ids[256]; uint64_t cdf[257]; };
+struct RequestBaseRow { uint32_t top_k, window_limit, count, tokens[64]; };      // candidates.cu's RequestBase
 
 static SelectionRequestRow to_request(const SelectionHistory& h) {
     SelectionRequestRow r {};
@@ -66,26 +76,40 @@ public:
     H1Engine(Model& target, Model* draft, const gf_h1_options& options)
         : target_(target), draft_(draft), options_(options), sampler_(to_options(options.sampler)), schedule_(options.schedule_seed) {}
     ~H1Engine() {
-        if (draft_ws_) cudaFree(draft_ws_);
+        for (void* ws : draft_ws_) if (ws) cudaFree(ws);
         if (receipt_dev_) cudaFree(receipt_dev_);
+        if (base_dev_) cudaFree(base_dev_);
+        if (base_host_) cudaFreeHost(base_host_);
         if (results_host_) cudaFreeHost(results_host_);
         if (receipt_host_) cudaFreeHost(receipt_host_);
+        for (cudaEvent_t e : step_done_) if (e) cudaEventDestroy(e);
         if (draft_done_) cudaEventDestroy(draft_done_);
     }
 
     int init() {
         GF_TRY(validate_options(sampler_.options()));
+        horizon_ = options_.horizon == 0 ? 1u : options_.horizon;
         if (options_.speculative) {
             if (!draft_) return fail(GF_ERR_INVALID, "speculative decoding needs a drafter plan");
             if (draft_->config().vocab != target_.config().vocab) return fail(GF_ERR_INVALID, "drafter and target vocabularies differ (direct token ids are required)");
-            if (target_.config().row_capacity < 2 || draft_->config().row_capacity < 2) return fail(GF_ERR_INVALID, "H1 needs two rows per pass in both plans");
-            if (sampler_.options().top_k > 64) return fail(GF_ERR_INVALID, "the compact proposal law supports top_k <= 64");
-            GF_CUDA(cudaMalloc(&draft_ws_, draft_sampler_workspace_bytes(draft_->config().vocab)));
-            GF_CUDA(cudaMalloc(&receipt_dev_, sizeof(DraftReceiptRow)));
-            GF_CUDA(cudaHostAlloc(reinterpret_cast<void**>(&receipt_host_), sizeof(DraftReceiptRow), cudaHostAllocDefault));
+            if (horizon_ > kMaxHorizon) return fail(GF_ERR_INVALID, "horizon %u exceeds %u (a verification pass holds at most %d rows)", horizon_, kMaxHorizon, GF_MAX_ROWS);
+            if (target_.config().row_capacity < horizon_ + 1u)
+                return fail(GF_ERR_INVALID, "horizon %u needs %u rows per target pass (the plan was built for %u)", horizon_, horizon_ + 1u, target_.config().row_capacity);
+            if (draft_->config().row_capacity < std::max(2u, horizon_))
+                return fail(GF_ERR_INVALID, "horizon %u needs %u rows per drafter pass (the plan was built for %u)", horizon_, std::max(2u, horizon_), draft_->config().row_capacity);
+            const size_t ws_bytes = draft_sampler_workspace_bytes(draft_->config().vocab);
+            draft_ws_.assign(horizon_, nullptr);
+            for (uint32_t j = 0; j < horizon_; ++j) GF_CUDA(cudaMalloc(&draft_ws_[j], ws_bytes));     // one per drafted token: an overflowing step is resolved from its own scores
+            GF_CUDA(cudaMalloc(&receipt_dev_, horizon_ * sizeof(DraftReceiptRow)));
+            GF_CUDA(cudaHostAlloc(reinterpret_cast<void**>(&receipt_host_), horizon_ * sizeof(DraftReceiptRow), cudaHostAllocDefault));
             GF_CUDA(cudaEventCreateWithFlags(&draft_done_, cudaEventDisableTiming));
+            if (request_base_bytes() != sizeof(RequestBaseRow)) return fail(GF_ERR_STATE, "selection base layouts differ");
+            GF_CUDA(cudaMalloc(&base_dev_, sizeof(RequestBaseRow)));
+            GF_CUDA(cudaHostAlloc(reinterpret_cast<void**>(&base_host_), sizeof(RequestBaseRow), cudaHostAllocDefault));
+            step_done_.assign(horizon_, nullptr);
+            for (uint32_t j = 0; j < horizon_; ++j) GF_CUDA(cudaEventCreateWithFlags(&step_done_[j], cudaEventDisableTiming));
         }
-        GF_CUDA(cudaHostAlloc(reinterpret_cast<void**>(&results_host_), 2 * sizeof(CandidateRow), cudaHostAllocDefault));
+        GF_CUDA(cudaHostAlloc(reinterpret_cast<void**>(&results_host_), (size_t)(horizon_ + 1u) * sizeof(CandidateRow), cudaHostAllocDefault));
         return GF_OK;
     }
 
@@ -121,12 +145,20 @@ public:
             ++steps;
             const uint32_t room = target_.config().context - target_.position();
             if (room < 2) break;                                            // context exhausted
-            const bool spec = options_.speculative && !draft_exhausted_ && max_tokens - produced >= 2 && room >= 3
-                && draft_->config().context - draft_->position() >= 3;
-            if (spec) {
-                uint32_t tokens[2];
+            // A cycle with h drafts emits up to h + 1 tokens, caches up to h + 1 rows and leaves one more
+            // token to be cached later; the drafter caches its pending token, the root and h - 1 drafts.
+            uint32_t h = 0;
+            if (options_.speculative && !draft_exhausted_) {
+                h = horizon_;
+                h = std::min(h, max_tokens - produced - 1u);
+                h = std::min(h, room - 2u);
+                const uint32_t draft_room = draft_->config().context - draft_->position();
+                h = draft_room >= 3u ? std::min(h, draft_room - 2u) : 0u;
+            }
+            if (h >= 1u) {
+                uint32_t tokens[kMaxHorizon + 1u];
                 uint32_t n = 0;
-                const int status = cycle(tokens, n);
+                const int status = cycle(h, tokens, n);
                 if (status != GF_OK) return status;
                 for (uint32_t i = 0; i < n; ++i) emit(tokens[i]);
             } else {
@@ -144,6 +176,8 @@ public:
     const std::vector<gf_h1_cycle_record>& records() const { return records_; }
 
 private:
+    static constexpr uint32_t kMaxHorizon = GF_MAX_ROWS - 1;
+
     // Selection for one target row through a single-row request, then readback.
     int select_and_read(const SelectionHistory& request, uint32_t logits_row) {
         // The selection kernels read row `r` of the logits for request r; a lone request for a
@@ -193,126 +227,200 @@ private:
         return GF_OK;
     }
 
-    // One H1 cycle.  On entry root_ is selected but not yet in any cache.
-    int cycle(uint32_t (&emitted)[2], uint32_t& emitted_count) {
+    // Drafter steps first..h-1 of a cycle.  Step 0 forwards [pending?, root]; step j > 0 forwards the
+    // token step j - 1 drafted, which the sampler left in the drafter's device token buffer.  Each step
+    // publishes its rows, samples the next draft into row j + 1 of the target's token buffer and sends
+    // its receipt to the host.  `resolve` = step `first` has already run and reported a support larger
+    // than the compact law holds: its law is rebuilt over the whole vocabulary from its own scores.
+    int draft_steps(uint32_t first, uint32_t h, bool resolve, const uint32_t* words, uint32_t* chain, uint32_t (&draft_position)[kMaxHorizon]) {
         const SamplerOptions& so = sampler_.options();
-        const uint32_t r = root_;
-        const uint32_t word = sampler_.preview_proposal_word();
-        // --- drafter: ingest [pending?, r], sample one token from the last row's logits.
-        uint32_t draft_tokens[2];
-        uint32_t draft_rows = 0;
-        if (pending_) draft_tokens[draft_rows++] = pending_token_;
-        draft_tokens[draft_rows++] = r;
-        GF_TRY(draft_->forward(draft_tokens, draft_rows, kForwardLogits));
-        GF_TRY(draft_->publish(draft_rows));
-        const SelectionHistory draft_history = sampler_.request_after(&r, 1);     // repetition window incl. the root
-        GF_TRY(launch_draft_sample(draft_->logits_dev() + (size_t)(draft_rows - 1u) * draft_->config().vocab,
-                                   draft_->config().vocab, so.temperature, so.top_k, so.top_p, so.min_p,
-                                   so.repetition_penalty, draft_history.tokens.data(), draft_history.count, word, draft_ws_,
-                                   receipt_dev_, target_.tokens_dev() + 1, nullptr, draft_->stream()));
-        stats_.sampler_launches += 3;
-        GF_CUDA(cudaMemcpyAsync(receipt_host_, receipt_dev_, sizeof(DraftReceiptRow), cudaMemcpyDeviceToHost, draft_->stream()));
-        GF_CUDA(cudaEventRecord(draft_done_, draft_->stream()));
-        // --- target: verify rows [r, x] in one pass; x never visits the host on this path.
-        GF_TRY(target_.set_device_token(0, r));
-        GF_CUDA(cudaStreamWaitEvent(target_.stream(), draft_done_, 0));
-        GF_TRY(target_.forward(nullptr, 2, kForwardLogits | kForwardDeviceTokens));
-        uint32_t x = 0;
-        bool have_x = false;
-        SelectionRequestRow requests[2];
-        {
-            const uint32_t suffix0[1] = {r};
-            requests[0] = to_request(sampler_.request_after(suffix0, 1));
-            if (so.repetition_penalty != 1.0f) {      // row 1's request names x: read it first
-                GF_CUDA(cudaEventSynchronize(draft_done_));
-                x = receipt_host_->token;
-                have_x = true;
-                const uint32_t suffix1[2] = {r, x};
-                requests[1] = to_request(sampler_.request_after(suffix1, 2));
+        const bool penalised = so.repetition_penalty != 1.0f;
+        const uint32_t vocab = draft_->config().vocab;
+        for (uint32_t j = first; j < h; ++j) {
+            uint32_t* next_draft_token = j + 1u < h ? draft_->tokens_dev() : nullptr;
+            DraftReceiptRow* receipt = static_cast<DraftReceiptRow*>(receipt_dev_) + j;
+            if (j == first && resolve) {
+                GF_TRY(launch_draft_resolve_overflow(vocab, so.temperature, so.top_k, so.top_p, so.min_p, words[j], draft_ws_[j], receipt,
+                                                     target_.tokens_dev() + j + 1u, next_draft_token, draft_->stream()));
+                stats_.sampler_launches += 16;
+                ++stats_.full_law_proposals;
             } else {
-                requests[1] = requests[0];
+                uint32_t rows = 1;
+                if (j == 0) {
+                    uint32_t tokens[2];
+                    rows = 0;
+                    if (pending_) tokens[rows++] = pending_token_;
+                    tokens[rows++] = chain[0];
+                    GF_TRY(draft_->forward(tokens, rows, kForwardLogits));
+                } else {
+                    GF_TRY(draft_->forward(nullptr, 1, kForwardLogits | kForwardDeviceTokens));
+                }
+                GF_TRY(draft_->publish(rows));
+                draft_position[j] = draft_->position();
+                // With a repetition penalty the window names the root and the earlier drafts, which only the
+                // device knows: row j of the target's request rows is written here, on the device, and the
+                // drafter's sampler reads its history from it (the row is also the target's request for row j).
+                const uint32_t* history_row = nullptr;
+                if (penalised) {
+                    GF_TRY(launch_request_rows(base_dev_, chain[0], target_.tokens_dev(), j, 1, target_.requests_dev(), draft_->stream()));
+                    history_row = static_cast<const uint32_t*>(target_.requests_dev()) + (size_t)j * (sizeof(SelectionRequestRow) / 4u);
+                    stats_.sampler_launches += 1;
+                }
+                GF_TRY(launch_draft_sample(draft_->logits_dev() + (size_t)(rows - 1u) * vocab, vocab, so.temperature, so.top_k, so.top_p,
+                                           so.min_p, so.repetition_penalty, nullptr, 0, words[j], draft_ws_[j],
+                                           receipt, target_.tokens_dev() + j + 1u, next_draft_token, draft_->stream(), history_row));
+                stats_.sampler_launches += 3;
             }
+            GF_CUDA(cudaMemcpyAsync(receipt_host_ + j, receipt, sizeof(DraftReceiptRow), cudaMemcpyDeviceToHost, draft_->stream()));
+            GF_CUDA(cudaEventRecord(step_done_[j], draft_->stream()));
         }
-        GF_TRY(target_.select(requests, 2));
-        GF_TRY(target_.read_candidates(results_host_, 2));           // the cycle's one synchronisation
-        GF_CUDA(cudaEventSynchronize(draft_done_));
-        const DraftReceiptRow& receipt = *receipt_host_;
-        if (!have_x) x = receipt.token;
-        if (results_host_[0].status || results_host_[1].status)
-            return fail(GF_ERR_NUMERIC, "candidate selection reported status %u/%u", results_host_[0].status, results_host_[1].status);
-        ++stats_.cycles;
-        if (receipt.status != 0 || x >= target_.config().vocab) {
-            // No usable proposal law (support overflow or a numeric fault in the drafter): finish
-            // the step as ordinary decoding of r from row 0; nothing speculative is published.
-            if (receipt.status != 20u) return fail(GF_ERR_NUMERIC, "drafter sampler reported status %u", receipt.status);
+        if (penalised) {      // the request of the row behind the last draft
+            GF_TRY(launch_request_rows(base_dev_, chain[0], target_.tokens_dev(), h, 1, target_.requests_dev(), draft_->stream()));
+            stats_.sampler_launches += 1;
+        }
+        GF_CUDA(cudaEventRecord(draft_done_, draft_->stream()));
+        return GF_OK;
+    }
+
+    // Draft masses on the prepared target support.  A compact receipt is searched on the host; a
+    // full-vocabulary receipt keeps its CDF on the device and is read through a small gather.
+    int gather_step(uint32_t j, const TokenDistribution& target, GatheredDraft& out) {
+        const DraftReceiptRow& receipt = receipt_host_[j];
+        if (receipt.count != 0xffffffffu) { gather(receipt, target, out); return GF_OK; }
+        uint32_t tokens[kSamplerMaxTopK + 1u];
+        uint64_t intervals[2u * (kSamplerMaxTopK + 1u)];
+        for (uint32_t i = 0; i < target.count; ++i) tokens[i] = target.values[i].token;
+        tokens[target.count] = receipt.token;
+        GF_TRY(launch_draft_gather(draft_ws_[j], draft_->config().vocab, tokens, target.count + 1u, intervals, draft_->stream()));
+        out = GatheredDraft();
+        out.proposal = receipt.token;
+        out.proposal_cdf_begin = intervals[2u * target.count];
+        out.proposal_mass = intervals[2u * target.count + 1u] - intervals[2u * target.count];
+        out.count = target.count;
+        for (uint32_t i = 0; i < target.count; ++i) out.target_mass[i] = intervals[2u * i + 1u] - intervals[2u * i];
+        return GF_OK;
+    }
+
+    // One speculative cycle with h >= 1 drafts (ChainChatVerifier::run with one tile of h proposals and
+    // h + 1 rows, chain_chat.mm:245-543; h = 1 is the H1 cycle).  On entry root_ is selected but not yet
+    // in any cache.
+    int cycle(uint32_t h, uint32_t* emitted, uint32_t& emitted_count) {
+        const SamplerOptions& so = sampler_.options();
+        const bool penalised = so.repetition_penalty != 1.0f;
+        uint32_t chain[kMaxHorizon + 1u] = {root_};        // root, then the drafted tokens as the host learns them
+        uint32_t words[kMaxHorizon];
+        sampler_.preview_proposal_words(words, h);
+        uint32_t draft_position[kMaxHorizon] = {};           // the drafter's position after step j
+        const uint32_t r = root_;
+        uint32_t first = 0;
+        bool resolve = false;
+        if (penalised) {      // the sampler's repetition window, for the request rows the device writes
+            const std::vector<uint32_t>& window = sampler_.history();
+            base_host_->top_k = so.temperature == 0.0f ? 1u : so.top_k;
+            base_host_->window_limit = so.repetition_window;
+            base_host_->count = (uint32_t)window.size();
+            for (size_t i = 0; i < window.size() && i < 64u; ++i) base_host_->tokens[i] = window[i];
+            GF_CUDA(cudaMemcpyAsync(base_dev_, base_host_, sizeof(RequestBaseRow), cudaMemcpyHostToDevice, draft_->stream()));
+        }
+        for (;;) {
+            GF_TRY(draft_steps(first, h, resolve, words, chain, draft_position));
+            // --- target: verify rows [r, x1 .. xh] in one pass; the drafts never visit the host on this path.
+            GF_TRY(target_.set_device_token(0, r));
+            GF_CUDA(cudaStreamWaitEvent(target_.stream(), draft_done_, 0));
+            GF_TRY(target_.forward(nullptr, h + 1u, kForwardLogits | kForwardDeviceTokens));
+            if (penalised) {      // every row's request names the drafts before it: the drafter's stream wrote them
+                GF_TRY(target_.select_device(h + 1u));
+            } else {
+                SelectionRequestRow requests[kMaxHorizon + 1u];
+                requests[0] = to_request(sampler_.request_after(chain, 1));
+                for (uint32_t i = 1; i <= h; ++i) requests[i] = requests[0];
+                GF_TRY(target_.select(requests, h + 1u));
+            }
+            GF_TRY(target_.read_candidates(results_host_, h + 1u));           // the cycle's one synchronisation
+            GF_CUDA(cudaEventSynchronize(draft_done_));
+            // A step whose support outgrew the compact law (status 20) drafted nothing usable: rebuild its
+            // law over the whole vocabulary, redo the steps behind it and verify again.  Nothing of the
+            // first attempt was published on the target, and no random stream has moved.
+            uint32_t overflow = h;
+            for (uint32_t j = first; j < h && overflow == h; ++j) if (receipt_host_[j].status == 20u) overflow = j;
+            if (overflow == h) break;
+            GF_TRY(draft_->truncate(draft_position[overflow]));
+            first = overflow;
+            resolve = true;
             ++stats_.fallback_cycles;
-            GF_TRY(target_.publish(1));
-            sampler_.observe(&r, 1);
-            const SelectionHistory now = sampler_.request_after(nullptr, 0);
-            uint32_t token = 0;
-            GF_TRY(sampler_.sample(results_host_[0].candidates, results_host_[0].count, now, token));
-            pending_ = false;
-            root_ = token;
-            emitted[0] = token;
-            emitted_count = 1;
-            return GF_OK;
         }
-        // --- acceptance (host, double precision).
-        const uint32_t suffix0[1] = {r};
-        const SelectionHistory request0 = sampler_.request_after(suffix0, 1);
-        TokenDistribution prepared;
-        GF_TRY(prepare_distribution(results_host_[0].candidates, results_host_[0].count, so, request0, prepared));
-        GatheredDraft gathered;
-        gather(receipt, prepared, gathered);
-        SpeculativeOutcome outcome;
-        const int law_status = sampler_.sample_speculative(gathered, results_host_[0].candidates, results_host_[0].count, request0, outcome);
-        if (options_.record_cycles) {
-            gf_h1_cycle_record record {};
-            record.root = r; record.proposal = x; record.word = word; record.candidate_count = results_host_[0].count;
-            std::memcpy(record.candidates, results_host_[0].candidates, sizeof(TokenLogit) * results_host_[0].count);
-            record.draft.proposal = gathered.proposal; record.draft.count = gathered.count;
-            record.draft.proposal_mass = gathered.proposal_mass; record.draft.proposal_cdf_begin = gathered.proposal_cdf_begin;
-            std::memcpy(record.draft.target_mass, gathered.target_mass.data(), sizeof(uint64_t) * 256);
-            record.token = outcome.token; record.accepted = outcome.accepted; record.target_draws = outcome.target_draws;
-            record.status = law_status;
-            if (records_.size() < 65536) records_.push_back(record);
+        for (uint32_t j = 0; j < h; ++j) {
+            const DraftReceiptRow& receipt = receipt_host_[j];
+            if (receipt.status != 0 || receipt.token >= target_.config().vocab)
+                return fail(GF_ERR_NUMERIC, "drafter sampler reported status %u at depth %u", receipt.status, j);
+            chain[j + 1u] = receipt.token;
+            if (receipt.count == 0xffffffffu && !resolve) ++stats_.full_law_proposals;
         }
-        if (law_status != GF_OK) return law_status;
-        bool accepted = outcome.accepted;
-        uint32_t corrected = outcome.token;
-        if (options_.forced_schedule) {
-            std::bernoulli_distribution coin(options_.forced_accept_probability);
-            const bool forced = coin(schedule_);
-            if (forced == outcome.accepted) ++stats_.law_agreements;
-            if (!forced && outcome.accepted) {
-                // Scheduled rejection of a proposal the law accepted: continue from an ordinary
-                // sample of the same row, so the control flow (one row published, no carry) matches.
-                GF_TRY(sampler_.sample(results_host_[0].candidates, results_host_[0].count, request0, corrected));
+        for (uint32_t i = 0; i <= h; ++i)
+            if (results_host_[i].status) return fail(GF_ERR_NUMERIC, "candidate selection reported status %u in row %u", results_host_[i].status, i);
+        ++stats_.cycles;
+        stats_.drafted_tokens += h;
+        // --- acceptance (host, double precision), draft by draft until the first rejection.
+        uint32_t matched = 0;
+        uint32_t corrected = 0;
+        for (uint32_t i = 0; i < h; ++i) {
+            const SelectionHistory request = sampler_.request_after(chain, i + 1u);
+            TokenDistribution prepared;
+            GF_TRY(prepare_distribution(results_host_[i].candidates, results_host_[i].count, so, request, prepared));
+            GatheredDraft gathered;
+            GF_TRY(gather_step(i, prepared, gathered));
+            SpeculativeOutcome outcome;
+            const int law_status = sampler_.sample_speculative(gathered, results_host_[i].candidates, results_host_[i].count, request, outcome);
+            if (options_.record_cycles) {
+                gf_h1_cycle_record record {};
+                record.root = chain[i]; record.proposal = chain[i + 1u]; record.word = words[i]; record.candidate_count = results_host_[i].count;
+                std::memcpy(record.candidates, results_host_[i].candidates, sizeof(TokenLogit) * results_host_[i].count);
+                record.draft.proposal = gathered.proposal; record.draft.count = gathered.count;
+                record.draft.proposal_mass = gathered.proposal_mass; record.draft.proposal_cdf_begin = gathered.proposal_cdf_begin;
+                std::memcpy(record.draft.target_mass, gathered.target_mass.data(), sizeof(uint64_t) * 256);
+                record.token = outcome.token; record.accepted = outcome.accepted; record.target_draws = outcome.target_draws;
+                record.status = law_status; record.depth = i; record.horizon = h;
+                if (records_.size() < 65536) records_.push_back(record);
             }
-            accepted = forced;
+            if (law_status != GF_OK) return law_status;
+            bool accepted = outcome.accepted;
+            corrected = outcome.token;
+            if (options_.forced_schedule) {
+                std::bernoulli_distribution coin(options_.forced_accept_probability);
+                const bool forced = coin(schedule_);
+                if (forced == outcome.accepted) ++stats_.law_agreements;
+                if (!forced && outcome.accepted) {
+                    // Scheduled rejection of a proposal the law accepted: continue from an ordinary
+                    // sample of the same row, so the control flow (one row published, no carry) matches.
+                    GF_TRY(sampler_.sample(results_host_[i].candidates, results_host_[i].count, request, corrected));
+                }
+                accepted = forced;
+            }
+            if (!accepted) break;
+            ++matched;
         }
-        if (accepted) {
+        stats_.accepted_tokens += matched;
+        GF_TRY(target_.publish(matched + 1u));           // rows behind the first rejection are never published: the rollback
+        sampler_.observe(chain, matched + 1u);
+        for (uint32_t i = 0; i < matched; ++i) emitted[i] = chain[i + 1u];
+        if (matched == h) {
             ++stats_.accepted;
-            GF_TRY(target_.publish(2));                 // both private rows become durable
-            const uint32_t observed[2] = {r, x};
-            sampler_.observe(observed, 2);
             const SelectionHistory now = sampler_.request_after(nullptr, 0);
             uint32_t next = 0;
-            GF_TRY(sampler_.sample(results_host_[1].candidates, results_host_[1].count, now, next));
-            pending_ = true;                             // x is selected but not yet forwarded by the drafter
-            pending_token_ = x;
+            GF_TRY(sampler_.sample(results_host_[h].candidates, results_host_[h].count, now, next));
+            pending_ = true;                              // the last draft is selected but not yet forwarded by the drafter
+            pending_token_ = chain[h];
             root_ = next;
-            emitted[0] = x; emitted[1] = next;
-            emitted_count = 2;
+            emitted[matched] = next;
         } else {
             ++stats_.rejected;
-            GF_TRY(target_.publish(1));                 // row 1 is simply never published: the rollback
-            sampler_.observe(&r, 1);
-            pending_ = false;                            // the drafter drops its pending token
+            // The drafter has cached the root and drafts 1 .. h-1; it keeps the accepted ones.
+            if (matched + 1u < h) GF_TRY(draft_->truncate(draft_position[matched]));
+            pending_ = false;                             // the rejected draft was never forwarded
             root_ = corrected;
-            emitted[0] = corrected;
-            emitted_count = 1;
+            emitted[matched] = corrected;
         }
+        emitted_count = matched + 1u;
         return GF_OK;
     }
 
@@ -323,10 +431,15 @@ private:
     std::mt19937_64 schedule_;
     gf_h1_stats stats_ {};
     std::vector<gf_h1_cycle_record> records_;
-    void *draft_ws_ = nullptr, *receipt_dev_ = nullptr;
+    std::vector<void*> draft_ws_;
+    void* receipt_dev_ = nullptr;
+    void* base_dev_ = nullptr;
+    RequestBaseRow* base_host_ = nullptr;
     CandidateRow* results_host_ = nullptr;
     DraftReceiptRow* receipt_host_ = nullptr;
     cudaEvent_t draft_done_ = nullptr;
+    std::vector<cudaEvent_t> step_done_;
+    uint32_t horizon_ = 1;
     uint32_t root_ = 0, pending_token_ = 0;
     bool has_root_ = false, pending_ = false, first_emitted_ = false, draft_exhausted_ = false;
 };

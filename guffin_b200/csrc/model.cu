@@ -53,7 +53,38 @@ static int device_alloc(std::vector<void*>& owner, T** out, size_t count) {
     return GF_OK;
 }
 
-int Model::set_matrix(int kind, uint32_t layer, int dtype, const void* native_host, uint64_t k, uint64_t n) {
+int launch_quantize_f16_q8_0(const void* f16_dev, uint64_t block_count, void* q8_dev, uint32_t* status_dev, cudaStream_t stream);
+int launch_requantize_q6k_q4k(const void* q6_dev, uint64_t block_count, void* q4_dev, uint32_t* status_dev, cudaStream_t stream);
+
+// Quantises a binary16 [K, vocab] table already on the device to Q8_0 and packs it as the output head.
+int Model::bind_q8_head_from_f16(const void* f16_dev, uint64_t k, uint64_t n) {
+    if (k % 128u) return fail(GF_ERR_INVALID, "a binary16 head needs K to be a multiple of 128");
+    const uint64_t blocks = n * (k / 32u);
+    const size_t native = (size_t)blocks * 34u, packed = gf_packed_weight_bytes(GF_Q8_0, k, n);
+    if (packed == 0) return GF_ERR_INVALID;
+    uint8_t* staging = nullptr;
+    uint32_t* flag = nullptr;
+    GF_CUDA(cudaMalloc(&staging, native + 16u));
+    flag = reinterpret_cast<uint32_t*>(staging + ((native + 3u) & ~(size_t)3u));
+    uint8_t* data = nullptr;
+    int status = device_alloc(allocations_, &data, packed);
+    uint32_t bad = 0;
+    if (status == GF_OK) status = check_cuda(cudaMemsetAsync(flag, 0, 4, stream_), "clear");
+    if (status == GF_OK) status = launch_quantize_f16_q8_0(f16_dev, blocks, staging, flag, stream_);
+    if (status == GF_OK) status = gf_pack_weight(GF_Q8_0, staging, k, n, data, stream_);
+    if (status == GF_OK) status = check_cuda(cudaMemcpyAsync(&bad, flag, 4, cudaMemcpyDeviceToHost, stream_), "status");
+    if (status == GF_OK) status = check_cuda(cudaStreamSynchronize(stream_), "quantise");
+    cudaFree(staging);
+    if (status != GF_OK) return status;
+    if (bad) return fail(GF_ERR_INVALID, "Q8_0 quantisation of a binary16 table needs finite values");
+    head_ = PackedMatrix{GF_Q8_0, k, n, data, packed, native};
+    weight_bytes_ += packed;
+    native_weight_bytes_ += native;
+    has_head_ = true;
+    return GF_OK;
+}
+
+int Model::set_matrix(int kind, uint32_t layer, int dtype, const void* native_host, uint64_t k, uint64_t n, bool requantize) {
     if (finalized_) return fail(GF_ERR_STATE, "gf_model_set_matrix: the plan is already finalized");
     if (!native_host) return fail(GF_ERR_INVALID, "gf_model_set_matrix: null payload");
     const gf_model_config& c = config_;
@@ -77,20 +108,57 @@ int Model::set_matrix(int kind, uint32_t layer, int dtype, const void* native_ho
         return fail(GF_ERR_INVALID, "gf_model_set_matrix: kind %d expects [%llu, %llu], got [%llu, %llu]", kind,
                     (unsigned long long)want_k, (unsigned long long)want_n, (unsigned long long)k, (unsigned long long)n);
     if (dst->data) return fail(GF_ERR_STATE, "gf_model_set_matrix: tensor kind %d layer %u bound twice", kind, layer);
-    const size_t packed = gf_packed_weight_bytes(dtype, k, n);
-    if (packed == 0) return GF_ERR_INVALID;
-    const size_t native = (size_t)n * (k / block_elements(dtype)) * block_bytes(dtype);
     if (!stream_) GF_CUDA(cudaStreamCreateWithFlags(&stream_, cudaStreamNonBlocking));
+    if (dtype == GF_F16) {
+        // Binary16 tables: the embedding is gathered from the rows as stored; a head becomes Q8_0.
+        if (requantize || (kind != GF_MAT_TOKEN_EMBD && kind != GF_MAT_OUTPUT))
+            return fail(GF_ERR_INVALID, "gf_model_set_matrix: binary16 is accepted for the token embedding and the output head only");
+        const size_t bytes = (size_t)n * k * 2u;
+        if (kind == GF_MAT_TOKEN_EMBD) {
+            uint8_t* data = nullptr;
+            GF_TRY(device_alloc(allocations_, &data, bytes));
+            GF_CUDA(cudaMemcpyAsync(data, native_host, bytes, cudaMemcpyHostToDevice, stream_));
+            GF_CUDA(cudaStreamSynchronize(stream_));
+            *dst = PackedMatrix{GF_F16, k, n, data, bytes, bytes};
+            weight_bytes_ += bytes;
+            native_weight_bytes_ += bytes;
+            return GF_OK;
+        }
+        uint8_t* table = nullptr;
+        GF_CUDA(cudaMalloc(&table, bytes));
+        int status = check_cuda(cudaMemcpyAsync(table, native_host, bytes, cudaMemcpyHostToDevice, stream_), "upload");
+        if (status == GF_OK) status = bind_q8_head_from_f16(table, k, n);
+        cudaFree(table);
+        return status;
+    }
+    if (requantize && dtype != GF_Q6_K) return fail(GF_ERR_INVALID, "gf_model_set_matrix_requantized: the source must be Q6_K");
+    const int stored = requantize ? GF_Q4_K : dtype;
+    const size_t packed = gf_packed_weight_bytes(stored, k, n);
+    if (packed == 0) return GF_ERR_INVALID;
+    const size_t source = (size_t)n * (k / block_elements(dtype)) * block_bytes(dtype);
+    const size_t native = (size_t)n * (k / block_elements(stored)) * block_bytes(stored);
+    // Staging: the source blocks, then (requantised binding) the converted blocks and a status word.
+    const size_t converted_at = (source + 15u) & ~(size_t)15u, flag_at = converted_at + ((native + 15u) & ~(size_t)15u);
     uint8_t* staging = nullptr;
-    GF_CUDA(cudaMalloc(&staging, native));
+    GF_CUDA(cudaMalloc(&staging, requantize ? flag_at + 16u : source));
     uint8_t* data = nullptr;
     int status = device_alloc(allocations_, &data, packed);
-    if (status == GF_OK) status = check_cuda(cudaMemcpyAsync(staging, native_host, native, cudaMemcpyHostToDevice, stream_), "upload");
-    if (status == GF_OK) status = gf_pack_weight(dtype, staging, k, n, data, stream_);
+    if (status == GF_OK) status = check_cuda(cudaMemcpyAsync(staging, native_host, source, cudaMemcpyHostToDevice, stream_), "upload");
+    uint32_t bad = 0;
+    if (requantize) {
+        uint32_t* flag = reinterpret_cast<uint32_t*>(staging + flag_at);
+        if (status == GF_OK) status = check_cuda(cudaMemsetAsync(flag, 0, 4, stream_), "clear");
+        if (status == GF_OK) status = launch_requantize_q6k_q4k(staging, n * (k / 256u), staging + converted_at, flag, stream_);
+        if (status == GF_OK) status = gf_pack_weight(stored, staging + converted_at, k, n, data, stream_);
+        if (status == GF_OK) status = check_cuda(cudaMemcpyAsync(&bad, flag, 4, cudaMemcpyDeviceToHost, stream_), "status");
+    } else if (status == GF_OK) {
+        status = gf_pack_weight(dtype, staging, k, n, data, stream_);
+    }
     if (status == GF_OK) status = check_cuda(cudaStreamSynchronize(stream_), "pack");
     cudaFree(staging);
     if (status != GF_OK) return status;
-    *dst = PackedMatrix{dtype, k, n, data, packed, native};
+    if (bad) return fail(GF_ERR_INVALID, "Q6_K to Q4_K requantisation needs finite decoded values");
+    *dst = PackedMatrix{stored, k, n, data, packed, native};
     weight_bytes_ += packed;
     native_weight_bytes_ += native;
     if (kind == GF_MAT_OUTPUT) has_head_ = true;
@@ -128,6 +196,10 @@ int Model::finalize() {
     if (c.head_dim != 256u) return fail(GF_ERR_INVALID, "head_dim must be 256 (the reference's kernels share this limit)");
     if (c.context == 0 || c.heads % c.kv_heads) return fail(GF_ERR_INVALID, "bad context or head geometry");
     if (!token_embd_.data || !output_norm_) return fail(GF_ERR_STATE, "token embedding or output norm missing");
+    if (!stream_) GF_CUDA(cudaStreamCreateWithFlags(&stream_, cudaStreamNonBlocking));
+    // A binary16 embedding cannot serve as the head: the tied head is its Q8_0 quantisation
+    // (resolve_gemma_output_head_policy, gemma2_metal_plan.cpp:799-828).
+    if (token_embd_.dtype == GF_F16 && !has_head_) GF_TRY(bind_q8_head_from_f16(token_embd_.data, token_embd_.k, token_embd_.n));
     for (uint32_t l = 0; l < c.layers; ++l) {
         const LayerWeights& w = layers_[l];
         if (!w.q.data || !w.k.data || !w.v.data || !w.o.data || !w.gate.data || !w.up.data || !w.down.data || !w.attn_norm
@@ -911,6 +983,9 @@ int gf_model_create(const gf_model_config* config, gf_model** out_model) {
 int gf_model_destroy(gf_model* model) { delete model; return GF_OK; }
 int gf_model_set_matrix(gf_model* m, int kind, uint32_t layer, int dtype, const void* native_host, uint64_t k, uint64_t n) {
     return m ? m->impl.set_matrix(kind, layer, dtype, native_host, k, n) : fail(GF_ERR_INVALID, "null model");
+}
+int gf_model_set_matrix_requantized(gf_model* m, int kind, uint32_t layer, const void* native_q6_k_host, uint64_t k, uint64_t n) {
+    return m ? m->impl.set_matrix(kind, layer, GF_Q6_K, native_q6_k_host, k, n, true) : fail(GF_ERR_INVALID, "null model");
 }
 int gf_model_set_vector(gf_model* m, int kind, uint32_t layer, const float* values_host, uint32_t count) {
     return m ? m->impl.set_vector(kind, layer, values_host, count) : fail(GF_ERR_INVALID, "null model");

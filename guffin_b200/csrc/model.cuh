@@ -49,7 +49,7 @@ public:
     Model(const Model&) = delete;
     Model& operator=(const Model&) = delete;
 
-    int set_matrix(int kind, uint32_t layer, int dtype, const void* native_host, uint64_t k, uint64_t n);
+    int set_matrix(int kind, uint32_t layer, int dtype, const void* native_host, uint64_t k, uint64_t n, bool requantize = false);
     int set_vector(int kind, uint32_t layer, const float* host, uint32_t count);
     int finalize();
 
@@ -108,6 +108,7 @@ private:
         std::vector<AttentionParams> attention_launches;
     };
 
+    int bind_q8_head_from_f16(const void* f16_dev, uint64_t k, uint64_t n);
     int encode_blocks(uint32_t rows, uint32_t flags);
     int run_gemv(struct GemvLaunch& launch, uint32_t rows);
     int emit_embedding(uint32_t rows, float scale);

@@ -207,6 +207,11 @@ uint32_t Sampler::preview_proposal_word() const {
     return static_cast<uint32_t>(cursor() >> 32);
 }
 
+void Sampler::preview_proposal_words(uint32_t* out, uint32_t count) const {
+    std::mt19937_64 cursor = proposal_rng_;
+    for (uint32_t i = 0; i < count; ++i) out[i] = static_cast<uint32_t>(cursor() >> 32);
+}
+
 int Sampler::sample_speculative(const GatheredDraft& draft, const TokenLogit* candidates, uint32_t count,
                                 const SelectionHistory& request, SpeculativeOutcome& out) {
     TokenDistribution target, residual;

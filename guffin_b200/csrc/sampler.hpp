@@ -78,10 +78,13 @@ public:
 
     int sample(const TokenLogit* candidates, uint32_t count, const SelectionHistory& request, uint32_t& token);
     uint32_t preview_proposal_word() const;
+    // The next `count` proposal words without consuming them (preview_proposal_words, sampling.cpp:62-80).
+    void preview_proposal_words(uint32_t* out, uint32_t count) const;
     // Accept/reject `draft.proposal` against the target candidates of the same row; advances both
     // streams only when every check passes (sampling.cpp:896-934).
     int sample_speculative(const GatheredDraft& draft, const TokenLogit* candidates, uint32_t count,
                            const SelectionHistory& request, SpeculativeOutcome& out);
+    const std::vector<uint32_t>& history() const { return history_; }      // the repetition window, oldest first
     uint64_t target_draws() const { return draws_; }
     uint64_t proposal_draws() const { return proposal_draws_; }
 

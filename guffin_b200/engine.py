@@ -33,18 +33,19 @@ class TokenLogitC(C.Structure):
 
 class H1Options(C.Structure):
     _fields_ = [("sampler", SamplerOptions), ("speculative", i32), ("forced_schedule", i32),
-                ("forced_accept_probability", f32), ("schedule_seed", u64), ("record_cycles", i32)]
+                ("forced_accept_probability", f32), ("schedule_seed", u64), ("record_cycles", i32), ("horizon", u32)]
 
 
 class H1Stats(C.Structure):
     _fields_ = [(n, u64) for n in ("cycles", "accepted", "rejected", "ordinary_steps", "fallback_cycles",
-                                   "emitted_tokens", "law_agreements", "sampler_launches")]
+                                   "emitted_tokens", "law_agreements", "sampler_launches", "drafted_tokens",
+                                   "accepted_tokens", "full_law_proposals")]
 
 
 class CycleRecord(C.Structure):
     _fields_ = [("root", u32), ("proposal", u32), ("word", u32), ("candidate_count", u32),
                 ("candidates", TokenLogitC * 384), ("draft", GatheredDraft), ("token", u32), ("accepted", i32),
-                ("target_draws", u32), ("status", i32)]
+                ("target_draws", u32), ("status", i32), ("depth", u32), ("horizon", u32)]
 
 
 class DraftReceipt(C.Structure):
@@ -55,6 +56,10 @@ lib.register({
     "gf_draft_receipt_bytes": (C.c_size_t, []),
     "gf_draft_sample_workspace_bytes": (C.c_size_t, [u32]),
     "gf_draft_sample": (i32, [vp, u32, f32, u32, f32, f32, f32, vp, u32, u32, vp, vp, vp, vp]),
+    "gf_draft_resolve_overflow": (i32, [u32, f32, u32, f32, f32, u32, vp, vp, vp, vp]),
+    "gf_draft_gather_full": (i32, [vp, u32, vp, u32, vp, vp]),
+    "gf_selection_base_bytes": (C.c_size_t, []),
+    "gf_selection_requests": (i32, [vp, u32, vp, u32, vp, vp]),
     "gf_sampler_create": (i32, [C.POINTER(SamplerOptions), C.POINTER(vp)]),
     "gf_sampler_destroy": (i32, [vp]),
     "gf_sampler_observe": (i32, [vp, vp, u32]),
@@ -138,6 +143,40 @@ def gathered_draft(proposal, proposal_mass, cdf_begin, target_mass) -> GatheredD
     for i, mass in enumerate(target_mass):
         draft.target_mass[i] = int(mass)
     return draft
+
+
+def draft_sample_full(logits: np.ndarray, options: SamplerOptions, word: int, history=(), gather=()):
+    """The proposal law over the whole vocabulary: runs the device sampler and, when the compact law
+    overflows (status 20), resolves it from the same scores.  Returns (receipt, intervals) where
+    intervals[i] = (begin, end) of token gather[i] in the full CDF (None for a compact receipt)."""
+    L = load()
+    logits = np.ascontiguousarray(logits, np.float32)
+    history = np.ascontiguousarray(np.array(history, np.uint32))
+    src = lib.DeviceBuffer.from_numpy(logits)
+    ws = lib.DeviceBuffer(L.gf_draft_sample_workspace_bytes(logits.size))
+    receipt = lib.DeviceBuffer(C.sizeof(DraftReceipt))
+    token = lib.DeviceBuffer(16)
+    check(L.gf_draft_sample(src.ptr, logits.size, options.temperature, options.top_k, options.top_p, options.min_p,
+                            options.repetition_penalty, history.ctypes.data if history.size else None, history.size,
+                            word, ws.ptr, receipt.ptr, token.ptr, None))
+    out = DraftReceipt.from_buffer_copy(receipt.download(np.uint8).tobytes())
+    if out.status == 20:
+        check(L.gf_draft_resolve_overflow(logits.size, options.temperature, options.top_k, options.top_p, options.min_p,
+                                          word, ws.ptr, receipt.ptr, token.ptr, None))
+        out = DraftReceipt.from_buffer_copy(receipt.download(np.uint8).tobytes())
+    intervals = None
+    if out.count == 0xffffffff:
+        intervals = []
+        tokens = np.ascontiguousarray(np.array(gather, np.uint32))
+        for begin in range(0, tokens.size, 256):
+            part = np.ascontiguousarray(tokens[begin:begin + 256])
+            got = np.zeros(2 * part.size, np.uint64)
+            check(L.gf_draft_gather_full(ws.ptr, logits.size, part.ctypes.data, part.size, got.ctypes.data, None))
+            intervals.append(got.reshape(-1, 2))
+        intervals = np.concatenate(intervals) if intervals else np.zeros((0, 2), np.uint64)
+    for b in (src, ws, receipt, token):
+        b.free()
+    return out, intervals
 
 
 def draft_sample(logits: np.ndarray, options: SamplerOptions, word: int, history=()) -> DraftReceipt:

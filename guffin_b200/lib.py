@@ -68,6 +68,8 @@ def _declare(L: C.CDLL) -> None:
         "gf_pack_weight": [i32, vp, u64, u64, vp, vp],
         "gf_unpack_weight": [i32, vp, u64, u64, vp, vp],
         "gf_dequantize": [i32, vp, u64, vp, vp],
+        "gf_quantize_f16_q8_0": [vp, u64, vp, vp, vp],
+        "gf_requantize_q6_k_q4_k": [vp, u64, vp, vp, vp],
         "gf_matmul": [i32, vp, vp, vp, u32, u64, u64, vp, vp],
         "gf_matmul_check": [vp],
         "gf_matmul_host": [i32, vp, vp, vp, u32, u64, u64],
@@ -225,6 +227,34 @@ def dequantize(dtype: int, native: np.ndarray) -> np.ndarray:
     src.free()
     dst.free()
     return out
+
+
+def quantize_f16_q8_0(f16_bits: np.ndarray):
+    """Binary16 values (uint16 bits, a multiple of 32) -> (status word, Q8_0 blocks) on the device."""
+    L = load()
+    f16_bits = np.ascontiguousarray(f16_bits, np.uint16).reshape(-1)
+    blocks = f16_bits.size // 32
+    src, dst, flag = DeviceBuffer.from_numpy(f16_bits), DeviceBuffer(blocks * 34), DeviceBuffer(16)
+    flag.zero()
+    check(L.gf_quantize_f16_q8_0(src.ptr, blocks, dst.ptr, flag.ptr, None))
+    out, status = dst.download(np.uint8), int(flag.download(np.uint32)[0])
+    for b in (src, dst, flag):
+        b.free()
+    return status, out
+
+
+def requantize_q6k_q4k(q6k: np.ndarray):
+    """Q6_K blocks -> (status word, Q4_K blocks) on the device, block for block."""
+    L = load()
+    q6k = np.ascontiguousarray(q6k, np.uint8).reshape(-1)
+    blocks = q6k.size // 210
+    src, dst, flag = DeviceBuffer.from_numpy(q6k), DeviceBuffer(blocks * 144), DeviceBuffer(16)
+    flag.zero()
+    check(L.gf_requantize_q6_k_q4_k(src.ptr, blocks, dst.ptr, flag.ptr, None))
+    out, status = dst.download(np.uint8), int(flag.download(np.uint32)[0])
+    for b in (src, dst, flag):
+        b.free()
+    return status, out
 
 
 def matmul(weight: PackedWeight, x: np.ndarray) -> np.ndarray:

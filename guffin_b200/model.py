@@ -53,6 +53,7 @@ lib.register({
     "gf_model_create": (i32, [C.POINTER(ModelConfig), C.POINTER(vp)]),
     "gf_model_destroy": (i32, [vp]),
     "gf_model_set_matrix": (i32, [vp, i32, u32, i32, vp, u64, u64]),
+    "gf_model_set_matrix_requantized": (i32, [vp, i32, u32, vp, u64, u64]),
     "gf_model_set_vector": (i32, [vp, i32, u32, vp, u32]),
     "gf_model_load_gguf": (i32, [vp, C.c_char_p, vp]),
     "gf_model_finalize": (i32, [vp]),
@@ -133,9 +134,12 @@ class Model:
             parts = name.split(".")
             layer, short = (int(parts[1]), parts[2]) if parts[0] == "blk" else (0, parts[0])
             if isinstance(value, tuple):
-                dtype, k, n, data = value
-                data = np.ascontiguousarray(data, np.uint8)
-                check(self.L.gf_model_set_matrix(self.handle, MATRIX_KINDS[short], layer, dtype, data.ctypes.data, k, n))
+                dtype, k, n, data = value[:4]
+                data = np.ascontiguousarray(data).view(np.uint8)
+                if len(value) > 4 and value[4] == "requantize":          # a Q6_K matrix bound as Q4_K
+                    check(self.L.gf_model_set_matrix_requantized(self.handle, MATRIX_KINDS[short], layer, data.ctypes.data, k, n))
+                else:
+                    check(self.L.gf_model_set_matrix(self.handle, MATRIX_KINDS[short], layer, dtype, data.ctypes.data, k, n))
             else:
                 data = np.ascontiguousarray(value, np.float32)
                 check(self.L.gf_model_set_vector(self.handle, VECTOR_KINDS[short], layer, data.ctypes.data, data.size))

@@ -80,6 +80,20 @@ GF_API int gf_unpack_weight(int dtype, const void* packed_dev, uint64_t k, uint6
 GF_API int gf_dequantize(int dtype, const void* native_dev, uint64_t block_count, float* out_dev,
                          void* stream);
 
+/* ---- load-time weight transforms of the Gemma 2 plan (src/engine/gemma2_metal_plan.cpp:301-316,
+ * 495-512), on the device, bit-identical per block to the reference's functions built without
+ * floating-point contraction:
+ *   gf_quantize_f16_q8_0     quantize_f16_gguf_weight_q8_0_into (src/tensor/quantization.cpp:634-673):
+ *                            32 consecutive binary16 values -> one 34-byte Q8_0 block;
+ *   gf_requantize_q6_k_q4_k  requantize_q6_k_gguf_weight_q4_k_into, canonical layout (:752-800):
+ *                            one 210-byte Q6_K block -> one 144-byte Q4_K block.
+ * Blocks keep their order.  *status_dev (optional) gets bit 1 when a source value is not finite
+ * (the reference throws std::invalid_argument). ---- */
+GF_API int gf_quantize_f16_q8_0(const void* f16_dev, uint64_t block_count, void* q8_0_dev,
+                                uint32_t* status_dev, void* stream);
+GF_API int gf_requantize_q6_k_q4_k(const void* q6_k_dev, uint64_t block_count, void* q4_k_dev,
+                                   uint32_t* status_dev, void* stream);
+
 /* ---- quantised GEMV / small-M GEMM: MetalCommandContext::encode_verifier_matmul
  * (metal_command_context.hpp:94-101; kernels metal_kernels.mm:551-986) and the CPU reference
  * matmul_f32_quantized_gguf_weight (cpu_backend.cpp:301-323).
@@ -199,6 +213,15 @@ GF_API int gf_kv_scatter(const void* private_k_dev, const void* private_v_dev, v
  * by (logit descending, token ascending), then the history tokens' logits.
  * Request row (device): { u32 retain; u32 history_count; u32 history[64] }.
  * Result row  (device): { u32 status; u32 count; { u32 token; f32 logit }[384] }. ---- */
+/* Request rows written on the device (gd_requests, src/engine/gemma3_draft.mm:396-400, filling
+ * VerifierDeviceSelectionRow, target_verifier.hpp:114-121): base_dev holds { u32 top_k; u32 window_limit;
+ * u32 count; u32 tokens[64] } -- the sampler's repetition window, oldest first; row i of requests_dev
+ * becomes the request of the context "window, root, chain_dev[1..i]" (the window slides, then its distinct
+ * tokens in order of first appearance), so a verification pass whose drafted tokens exist only in device
+ * memory needs no host round trip for its requests. */
+GF_API size_t gf_selection_base_bytes(void);
+GF_API int gf_selection_requests(const void* base_dev, uint32_t root, const uint32_t* chain_dev, uint32_t rows,
+                                 void* requests_dev, void* stream);
 GF_API size_t gf_selection_request_bytes(void);
 GF_API size_t gf_candidate_result_bytes(void);
 GF_API size_t gf_token_candidates_workspace_bytes(uint32_t rows, uint32_t vocab);
@@ -240,6 +263,14 @@ GF_API int gf_model_set_matrix(gf_model* model, int kind, uint32_t layer, int dt
                                const void* native_host, uint64_t k, uint64_t n);
 GF_API int gf_model_set_vector(gf_model* model, int kind, uint32_t layer, const float* values_host,
                                uint32_t count);
+/* gf_model_set_matrix also takes binary16 tables (dtype GF_F16, [K, vocab]) for the token embedding and the
+ * output head, the form of the retained Gemma 2 9B file: the embedding is gathered from the binary16 rows
+ * as they are, the head -- given, or tied to such an embedding -- is quantised to Q8_0 on the device
+ * (WeightMaterializer::q8_head, gemma2_metal_plan.cpp:310-316; policy :799-828).
+ * gf_model_set_matrix_requantized binds a Q6_K matrix as Q4_K (WeightMaterializer::requantized_down,
+ * gemma2_metal_plan.cpp:301-308: the 9B file's Q6_K ffn_down). */
+GF_API int gf_model_set_matrix_requantized(gf_model* model, int kind, uint32_t layer, const void* native_q6_k_host,
+                                           uint64_t k, uint64_t n);
 /* Binds every tensor of a GGUF v2/v3 file that the block schedule knows (llama.cpp tensor names,
  * F32 vectors and Q8_0 / Q4_K / Q6_K matrices) through the two calls above: the path's share of
  * read_file_backed_gguf_model (model_format/gguf_reader.hpp:85) and of the WeightMaterializer.
@@ -320,17 +351,28 @@ GF_API int gf_model_weight_sweep(gf_model* model, uint32_t rows, uint32_t* out_l
 
 /* ---- drafter proposal law: the device sampler of Gemma3DraftPlan::propose and the receipts
  * Gemma3DraftPlan::gather reads (src/engine/gemma3_draft.mm:995-1167,1528-1581; kernels :191-294).
- * Builds the compact law (top_k <= 64): support = every token whose processed score reaches the
- * top_k-th best, filtered by the ascending-tail top-p rule and min-p, integer CDF of total 2^32
- * in token-id order; the drafted token is the bin holding `word`.
+ * Compact law (temperature > 0 and 1 <= top_k <= 64, or a greedy drafter): support = every token whose
+ * processed score reaches the top_k-th best, filtered by the ascending-tail top-p rule and min-p,
+ * integer CDF of total 2^32 in token-id order; the drafted token is the bin holding `word`.
  * Receipt (device): { u32 status; u32 count; u32 token; u32 word; u32 ids[256]; u64 cdf[257] }.
- * status 20 = support larger than 256 (the caller falls back to ordinary decoding). ---- */
+ * status 20 = the support holds more than 256 tokens: no token was drafted, and the caller builds the
+ * full-vocabulary law from the same scores with gf_draft_resolve_overflow (same workspace, same word).
+ * Full-vocabulary law (gd_full_merge .. gd_select, gemma3_draft.mm:295-395): taken at once when top_k
+ * is 0 or above 64, and by gf_draft_resolve_overflow.  Its receipt has count = 0xffffffff and only the
+ * four leading words; the CDF (vocab + 1 bounds, total 2^32) stays inside the workspace and
+ * gf_draft_gather_full returns the [begin, end) bounds of up to 257 tokens (2 * count words;
+ * synchronises the stream): the non-compact branch of Gemma3DraftPlan::gather (:1528-1581). ---- */
 GF_API size_t gf_draft_receipt_bytes(void);
 GF_API size_t gf_draft_sample_workspace_bytes(uint32_t vocab);
 GF_API int gf_draft_sample(const float* logits_dev, uint32_t vocab, float temperature, uint32_t top_k,
                            float top_p, float min_p, float repetition_penalty,
                            const uint32_t* history_host, uint32_t history_count, uint32_t word,
                            void* workspace_dev, void* receipt_dev, uint32_t* out_token_dev, void* stream);
+GF_API int gf_draft_resolve_overflow(uint32_t vocab, float temperature, uint32_t top_k, float top_p, float min_p,
+                                     uint32_t word, void* workspace_dev, void* receipt_dev,
+                                     uint32_t* out_token_dev, void* stream);
+GF_API int gf_draft_gather_full(void* workspace_dev, uint32_t vocab, const uint32_t* tokens_host, uint32_t count,
+                                uint64_t* intervals_host, void* stream);
 
 /* ---- host sampler and lossless acceptance: TokenSampler / TokenSamplerFork
  * (include/local_gguf_engine/engine/sampling.hpp:184-395, src/engine/sampling.cpp).  Double
@@ -368,10 +410,14 @@ GF_API int gf_sampler_sample_speculative(gf_sampler* sampler, const gf_gathered_
                                          const uint32_t* suffix, uint32_t suffix_count, uint32_t* out_token,
                                          int* out_accepted, uint32_t* out_target_draws);
 
-/* ---- the H1 cycle: draft -> verify -> accept / rollback.  Replaces StandaloneChatPlan::run
- * (src/engine/standalone_chat.cpp:508-615), ChainChatVerifier::run for one 2-row tile
- * (src/engine/chain_chat.mm:245-543) and the H1 branch of the generation loop
- * (src/engine/gemma2_runtime.cpp:1630-1699).  One host synchronisation per cycle. ---- */
+/* ---- the speculative cycle: draft -> verify -> accept / rollback.  Replaces StandaloneChatPlan::run
+ * (src/engine/standalone_chat.cpp:508-615), ChainChatVerifier::run for one tile of `horizon` drafts and
+ * horizon + 1 rows (src/engine/chain_chat.mm:245-543; the unconditional schedule of :64-93) and the
+ * speculative branch of the generation loop (src/engine/gemma2_runtime.cpp:1630-1699).  horizon = 1 is
+ * the H1 cycle; horizons up to GF_MAX_ROWS - 1 draft a chain of tokens, verify them in one pass of the
+ * target and keep the accepted prefix (the drafter rolls back behind it).  One host synchronisation per
+ * cycle: with a repetition penalty the selection requests, which name the drafted tokens, are written on
+ * the device. ---- */
 typedef struct gf_h1 gf_h1;
 typedef struct gf_h1_options {
     gf_sampler_options sampler;          /* target sampler; the drafter reuses it (standalone_chat.cpp:11-32) */
@@ -380,15 +426,20 @@ typedef struct gf_h1_options {
                                             while the real acceptance law still runs and is recorded */
     float forced_accept_probability;
     uint64_t schedule_seed;
-    int32_t record_cycles;               /* keep per-cycle acceptance inputs for exactness checks */
+    int32_t record_cycles;               /* keep the inputs of every acceptance test for exactness checks */
+    uint32_t horizon;                    /* drafts per cycle, 1..GF_MAX_ROWS-1 (0 = 1); the target plan needs
+                                            horizon + 1 rows per pass, the drafter max(2, horizon) */
 } gf_h1_options;
 typedef struct gf_h1_stats {
     uint64_t cycles, accepted, rejected, ordinary_steps, fallback_cycles, emitted_tokens;
     uint64_t law_agreements;             /* cycles whose real decision equals the forced one (forced mode) */
     uint64_t sampler_launches;           /* kernels of the drafter's device sampler (three per proposal); the plans count
                                             their own in gf_model_kernel_launches */
+    uint64_t drafted_tokens, accepted_tokens;   /* over all cycles; accepted / rejected count whole cycles */
+    uint64_t full_law_proposals;         /* proposals drawn from the full-vocabulary law; fallback_cycles counts the
+                                            verification passes repeated after a compact law overflowed */
 } gf_h1_stats;
-typedef struct gf_h1_cycle_record {      /* inputs and result of one real acceptance test */
+typedef struct gf_h1_cycle_record {      /* inputs and result of one real acceptance test (`root` = the row's input token) */
     uint32_t root, proposal, word, candidate_count;
     gf_token_logit candidates[384];
     gf_gathered_draft draft;
@@ -396,6 +447,7 @@ typedef struct gf_h1_cycle_record {      /* inputs and result of one real accept
     int32_t accepted;
     uint32_t target_draws;
     int32_t status;
+    uint32_t depth, horizon;             /* this test's place in its cycle's chain (0 = the root's row) and the cycle's drafts */
 } gf_h1_cycle_record;
 GF_API int gf_h1_create(gf_model* target, gf_model* draft /* may be NULL when speculative == 0 */,
                         const gf_h1_options* options, gf_h1** out_engine);

@@ -636,6 +636,263 @@ uint32_t gfo_draft_law_compact(const float* scores, uint32_t vocab, uint32_t top
     return n;
 }
 
+/* ---- load-time weight transforms of the Gemma 2 plan (src/engine/gemma2_metal_plan.cpp:301-316,495-512) ----
+ * quantize_f16_gguf_weight_q8_0_into (src/tensor/quantization.cpp:634-673): per 32 consecutive F16
+ * values d = max|v| / 127 stored as binary16 (the reference's own conversion, which rounds halves up),
+ * codes round(v * (1 / d)) with halves away from zero.  Returns -1 on a non-finite value. */
+int gfo_quantize_f16_q8_0(const uint16_t* f16, uint64_t block_count, uint8_t* out) {
+    for (uint64_t b = 0; b < block_count; ++b) {
+        float values[32];
+        float amax = 0.0f;
+        for (uint32_t e = 0; e < 32; ++e) {
+            values[e] = gfo_f16_to_f32(f16[b * 32u + e]);
+            if (!isfinite(values[e])) return -1;
+            const float a = fabsf(values[e]);
+            amax = a > amax ? a : amax;
+        }
+        const float scale = amax / 127.0f;
+        const float inverse = scale == 0.0f ? 0.0f : 1.0f / scale;
+        const uint16_t bits = gfo_f32_to_f16_half_up(scale);
+        uint8_t* o = out + b * 34u;
+        o[0] = (uint8_t)(bits & 0xFFu); o[1] = (uint8_t)(bits >> 8);
+        for (uint32_t e = 0; e < 32; ++e) o[2 + e] = (uint8_t)(int8_t)roundf(values[e] * inverse);
+    }
+    return 0;
+}
+
+/* nearest_int (quantization.cpp:99-102): the GGML rounding primitive. */
+static int q4k_nearest_int(float value) {
+    float shifted = value + 12582912.0f;
+    uint32_t bits;
+    memcpy(&bits, &shifted, 4);
+    return (int)(bits & 0x007FFFFFu) - 0x00400000;
+}
+static int clamp_int(int v, int lo, int hi) { return v < lo ? lo : v > hi ? hi : v; }
+
+/* make_q4_k_group (quantization.cpp:110-188): weighted least-squares scale and minimum of one
+ * 32-element group over 21 candidate grids.  Returns the scale; *minimum_magnitude = -minimum. */
+static float q4k_make_group(const float* values, const float* weights, float* minimum_magnitude) {
+    float minimum = values[0], maximum = values[0], weight_sum = weights[0], weighted_value_sum = weights[0] * values[0];
+    for (uint32_t i = 1; i < 32; ++i) {
+        minimum = values[i] < minimum ? values[i] : minimum;
+        maximum = values[i] > maximum ? values[i] : maximum;
+        weight_sum += weights[i];
+        weighted_value_sum += weights[i] * values[i];
+    }
+    minimum = minimum < 0.0f ? minimum : 0.0f;
+    if (maximum == minimum) { *minimum_magnitude = -minimum; return 0.0f; }
+    float inverse_scale = 15 / (maximum - minimum);
+    float scale = 1.0f / inverse_scale;
+    float best_error = 0.0f;
+    for (uint32_t i = 0; i < 32; ++i) {
+        const int level = clamp_int(q4k_nearest_int(inverse_scale * (values[i] - minimum)), 0, 15);
+        const float difference = scale * (float)level + minimum - values[i];
+        best_error += weights[i] * difference * difference;
+    }
+    for (int step = 0; step <= 20; ++step) {
+        uint8_t candidate[32];
+        inverse_scale = (-1.0f + 0.1f * (float)step + 15) / (maximum - minimum);
+        float wl = 0.0f, wl2 = 0.0f, wlv = 0.0f;
+        for (uint32_t i = 0; i < 32; ++i) {
+            const int level = clamp_int(q4k_nearest_int(inverse_scale * (values[i] - minimum)), 0, 15);
+            candidate[i] = (uint8_t)level;
+            const float weighted_level = weights[i] * (float)level;
+            wl += weighted_level;
+            wl2 += weighted_level * (float)level;
+            wlv += weighted_level * values[i];
+        }
+        const float determinant = weight_sum * wl2 - wl * wl;
+        if (determinant <= 0.0f) continue;
+        float candidate_scale = (weight_sum * wlv - weighted_value_sum * wl) / determinant;
+        float candidate_minimum = (wl2 * weighted_value_sum - wl * wlv) / determinant;
+        if (candidate_minimum > 0.0f) { candidate_minimum = 0.0f; candidate_scale = wlv / wl2; }
+        float candidate_error = 0.0f;
+        for (uint32_t i = 0; i < 32; ++i) {
+            const float difference = candidate_scale * (float)candidate[i] + candidate_minimum - values[i];
+            candidate_error += weights[i] * difference * difference;
+        }
+        if (candidate_error < best_error) { best_error = candidate_error; scale = candidate_scale; minimum = candidate_minimum; }
+    }
+    *minimum_magnitude = -minimum;
+    return scale;
+}
+
+/* encode_q4_k_block (quantization.cpp:190-262). */
+static void q4k_encode_block(const float* values, uint8_t* out) {
+    float scales[8], minima[8], maximum_scale = 0.0f, maximum_minimum = 0.0f;
+    for (uint32_t g = 0; g < 8; ++g) {
+        const float* v = values + g * 32u;
+        float sum_squares = 0.0f;
+        for (uint32_t i = 0; i < 32; ++i) sum_squares += v[i] * v[i];
+        const float average = sqrtf(sum_squares / 32.0f);
+        float weights[32];
+        for (uint32_t i = 0; i < 32; ++i) weights[i] = average + fabsf(v[i]);
+        scales[g] = q4k_make_group(v, weights, &minima[g]);
+        maximum_scale = scales[g] > maximum_scale ? scales[g] : maximum_scale;
+        maximum_minimum = minima[g] > maximum_minimum ? minima[g] : maximum_minimum;
+    }
+    memset(out, 0, 144);
+    const float inverse_scale = maximum_scale > 0.0f ? 63.0f / maximum_scale : 0.0f;
+    const float inverse_minimum = maximum_minimum > 0.0f ? 63.0f / maximum_minimum : 0.0f;
+    uint8_t* packed = out + 4;
+    for (uint32_t g = 0; g < 8; ++g) {
+        int si = q4k_nearest_int(inverse_scale * scales[g]); si = si < 63 ? si : 63;
+        int mi = q4k_nearest_int(inverse_minimum * minima[g]); mi = mi < 63 ? mi : 63;
+        const uint8_t sc = (uint8_t)si, mn = (uint8_t)mi;
+        if (g < 4u) { packed[g] = sc; packed[g + 4u] = mn; }
+        else {
+            packed[g + 4u] = (uint8_t)((sc & 0x0Fu) | ((mn & 0x0Fu) << 4));
+            packed[g - 4u] |= (uint8_t)((sc >> 4) << 6);
+            packed[g] |= (uint8_t)((mn >> 4) << 6);
+        }
+    }
+    const uint16_t scale_bits = gfo_f32_to_f16_half_up(maximum_scale / 63.0f);
+    const uint16_t minimum_bits = gfo_f32_to_f16_half_up(maximum_minimum / 63.0f);
+    out[0] = (uint8_t)(scale_bits & 0xFFu); out[1] = (uint8_t)(scale_bits >> 8);
+    out[2] = (uint8_t)(minimum_bits & 0xFFu); out[3] = (uint8_t)(minimum_bits >> 8);
+    const float stored_scale = gfo_f16_to_f32(scale_bits), stored_minimum = gfo_f16_to_f32(minimum_bits);
+    uint8_t levels[256];
+    memset(levels, 0, sizeof levels);
+    for (uint32_t g = 0; g < 8; ++g) {
+        const float group_scale = stored_scale * (float)q4k_scale_min(packed, g, 0);
+        if (group_scale == 0.0f) continue;
+        const float group_minimum = stored_minimum * (float)q4k_scale_min(packed, g, 1);
+        for (uint32_t i = 0; i < 32; ++i)
+            levels[g * 32u + i] = (uint8_t)clamp_int(q4k_nearest_int((values[g * 32u + i] + group_minimum) / group_scale), 0, 15);
+    }
+    uint8_t* quantized = out + 16;
+    for (uint32_t g = 0; g < 4; ++g)
+        for (uint32_t i = 0; i < 32; ++i)
+            quantized[g * 32u + i] = (uint8_t)(levels[g * 64u + i] | (levels[g * 64u + i + 32u] << 4));
+}
+
+/* requantize_q6_k_gguf_weight_q4_k_into, canonical destination (quantization.cpp:752-800): every Q6_K
+ * block decoded as (d * scale_g) * q and re-encoded as Q4_K in place of the same 256 elements.
+ * Note the levels of a group whose stored scale is zero stay zero, and that the level search inside
+ * make_q4_k_group never reaches the output: the codes are recomputed from the stored scales. */
+int gfo_requantize_q6k_q4k(const uint8_t* q6, uint64_t block_count, uint8_t* out) {
+    for (uint64_t b = 0; b < block_count; ++b) {
+        const uint8_t* block = q6 + b * 210u;
+        const uint8_t* ql = block;
+        const uint8_t* qh = block + 128;
+        const int8_t* sc = (const int8_t*)(block + 192);
+        const float d = gfo_f16_to_f32(read_u16(block + 208));
+        float values[256];
+        for (uint32_t g = 0; g < 16; ++g) {
+            const float group_scale = d * (float)sc[g];
+            for (uint32_t lane = 0; lane < 16; ++lane) {
+                const uint32_t e = g * 16u + lane;
+                const uint32_t half = e / 128u, w = e % 128u, l = w % 32u, quarter = w / 32u;
+                const uint8_t lowbyte = ql[half * 64u + (quarter % 2u) * 32u + l];
+                const uint8_t low = (uint8_t)((lowbyte >> (w < 64u ? 0u : 4u)) & 0x0Fu);
+                const uint8_t high = (uint8_t)((qh[half * 32u + l] >> (quarter * 2u)) & 0x03u);
+                const int8_t q = (int8_t)((int16_t)(uint8_t)(low | (high << 4)) - 32);
+                values[e] = group_scale * (float)q;
+                if (!isfinite(values[e])) return -1;
+            }
+        }
+        q4k_encode_block(values, out + b * 144u);
+    }
+    return 0;
+}
+
+/* The full-vocabulary proposal law (src/engine/gemma3_draft.mm:295-395, driven by Impl::sample
+ * :995-1167): taken when the compact support would exceed 256 tokens, or when top_k is 0 or above 64,
+ * or for a greedy drafter.  `scores` are the processed logits (penalty and temperature applied).
+ *   filter (temperature > 0 and any of top_k / top_p / min_p active): all tokens sorted by (score desc,
+ *   token asc); walking from the worst to the best in blocks of 256 (the vocabulary padded at the worst
+ *   end to a multiple of 256), F32 weights exp(score - best) of the tokens at or above the top_k-th
+ *   score are prefix-summed inside each block and the block totals in block order; a token is dropped
+ *   when its tail share is <= 1 - top_p or its weight < min_p, the best token excepted.
+ *   law: maximum over the survivors (lowest id wins ties), weights exp(score - maximum) prefix-summed in
+ *   token-id order in blocks of 256, cdf[i] = u64(clamp(sum_before(i) / total * 2^32)), cdf[vocab] = 2^32.
+ * Greedy (temperature == 0): cdf is a step at the argmax.
+ * cdf has vocab + 1 entries.  Returns 0, or the reference's status code (6 no finite maximum, 7 bad total). */
+typedef struct { uint32_t token; float score; } full_pair;
+static int cmp_full(const void* a, const void* b) {
+    const full_pair* x = (const full_pair*)a; const full_pair* y = (const full_pair*)b;
+    if (x->score > y->score) return -1;
+    if (x->score < y->score) return 1;
+    return x->token < y->token ? -1 : x->token > y->token ? 1 : 0;
+}
+uint32_t gfo_draft_law_full(const float* scores_in, uint32_t vocab, float temperature, uint32_t top_k,
+                            float top_p, float min_p, uint64_t* cdf) {
+    const uint32_t groups = (vocab + 255u) / 256u, padded = groups * 256u;
+    float* scores = (float*)malloc(sizeof(float) * vocab);
+    float* prefix = (float*)malloc(sizeof(float) * padded);
+    float* offsets = (float*)malloc(sizeof(float) * (groups + 1u));
+    memcpy(scores, scores_in, sizeof(float) * vocab);
+    uint32_t status = 0;
+    if (temperature > 0.0f && (top_k != 0 || top_p < 1.0f || min_p > 0.0f)) {
+        full_pair* sorted = (full_pair*)malloc(sizeof(full_pair) * vocab);
+        for (uint32_t t = 0; t < vocab; ++t) { sorted[t].token = t; sorted[t].score = scores[t]; }
+        qsort(sorted, vocab, sizeof(full_pair), cmp_full);
+        const float cutoff = top_k ? sorted[(top_k < vocab ? top_k : vocab) - 1u].score : -INFINITY;
+        const float best = sorted[0].score;
+        /* position i counts from the worst end of the padded order: rank = padded - 1 - i */
+        float sum = 0.0f;
+        offsets[0] = 0.0f;
+        for (uint32_t g = 0; g < groups; ++g) {
+            float s = 0.0f;
+            for (uint32_t j = 0; j < 256u; ++j) {
+                const uint32_t i = g * 256u + j, rank = padded - 1u - i;
+                float w = 0.0f;
+                if (rank < vocab && sorted[rank].score >= cutoff) w = expf(sorted[rank].score - best);
+                s += w;
+                prefix[i] = s;
+            }
+            sum += s;
+            offsets[g + 1u] = sum;
+        }
+        for (uint32_t i = 0; i < padded; ++i) {
+            const uint32_t rank = padded - 1u - i;
+            if (rank >= vocab) continue;
+            int keep = sorted[rank].score >= cutoff;
+            const float tail = (offsets[i / 256u] + prefix[i]) / offsets[groups];
+            if (top_p < 1.0f && tail <= 1.0f - top_p && rank != 0u) keep = 0;
+            if (min_p > 0.0f && expf(sorted[rank].score - best) < min_p && rank != 0u) keep = 0;
+            scores[sorted[rank].token] = keep ? sorted[rank].score : -INFINITY;
+        }
+        free(sorted);
+    }
+    /* maximum of the survivors, lowest token id on ties */
+    float maximum = -INFINITY;
+    uint32_t argmax = 0;
+    for (uint32_t t = 0; t < vocab; ++t)
+        if (scores[t] > maximum) { maximum = scores[t]; argmax = t; }
+    if (!isfinite(maximum)) status = 6;
+    if (temperature == 0.0f) {
+        for (uint32_t i = 0; i <= vocab; ++i) cdf[i] = i <= argmax ? 0ull : 4294967296ull;
+    } else {
+        float sum = 0.0f;
+        offsets[0] = 0.0f;
+        for (uint32_t g = 0; g < groups; ++g) {
+            float s = 0.0f;
+            for (uint32_t j = 0; j < 256u; ++j) {
+                const uint32_t i = g * 256u + j;
+                const float w = (i < vocab && scores[i] > -INFINITY) ? expf(scores[i] - maximum) : 0.0f;
+                s += w;
+                prefix[i] = s;
+            }
+            sum += s;
+            offsets[g + 1u] = sum;
+        }
+        if (!(sum > 0.0f) || !isfinite(sum)) status = status ? status : 7;
+        for (uint32_t i = 0; i <= vocab; ++i) {
+            if (i == 0) { cdf[i] = 0; continue; }
+            if (i == vocab) { cdf[i] = 4294967296ull; continue; }
+            const uint32_t b = i / 256u;
+            const float before = (i % 256u == 0u) ? offsets[b] : offsets[b] + prefix[i - 1u];
+            float scaled = (before / offsets[groups]) * 4294967296.0f;
+            if (scaled < 0.0f) scaled = 0.0f;
+            if (scaled > 4294967296.0f) scaled = 4294967296.0f;
+            cdf[i] = (uint64_t)scaled;
+        }
+    }
+    free(scores); free(prefix); free(offsets);
+    return status;
+}
+
 /* ------------------------------------------------------------------ whole model */
 
 static int g_threads = 1;

@@ -113,6 +113,10 @@ double gfo_uniform_double(gfo_mt19937_64* rng, double a, double b);
 void gfo_make_proposal_rng(const gfo_mt19937_64* target_rng, gfo_mt19937_64* out);
 uint32_t gfo_next_proposal_word(gfo_mt19937_64* rng);
 
+/* ---- load-time weight transforms (src/tensor/quantization.cpp:634-673,752-800) ---- */
+int gfo_quantize_f16_q8_0(const uint16_t* f16, uint64_t block_count, uint8_t* out /* 34 B per block */);
+int gfo_requantize_q6k_q4k(const uint8_t* q6, uint64_t block_count, uint8_t* out /* 144 B per block */);
+
 /* ---- drafter proposal law (src/engine/gemma3_draft.mm:191-203,237-294) ----
  * Compact path: logits already include temperature and repetition processing
  * (gd_process).  Builds the support (every token whose score >= the top_k-th best),
@@ -120,6 +124,8 @@ uint32_t gfo_next_proposal_word(gfo_mt19937_64* rng);
  * order with total exactly 2^32.  Returns support size (0 = overflow >256 / invalid). */
 uint32_t gfo_draft_law_compact(const float* scores, uint32_t vocab, uint32_t top_k, float top_p,
                                float min_p, uint32_t* ids, uint64_t* cdf /* count+1 */);
+uint32_t gfo_draft_law_full(const float* scores, uint32_t vocab, float temperature, uint32_t top_k,
+                            float top_p, float min_p, uint64_t* cdf);
 void gfo_draft_process_logits(const float* logits, uint32_t vocab, float temperature,
                               float repetition_penalty, const uint32_t* history,
                               uint32_t history_count, float* scores);

@@ -128,6 +128,10 @@ class Oracle:
         L.gfo_next_proposal_word.argtypes = [C.POINTER(MT)]
         L.gfo_draft_law_compact.restype = C.c_uint32
         L.gfo_draft_law_compact.argtypes = [_f32p, C.c_uint32, C.c_uint32, C.c_float, C.c_float, _u32p, _u64p]
+        L.gfo_quantize_f16_q8_0.argtypes = [C.c_void_p, C.c_uint64, _u8p]
+        L.gfo_requantize_q6k_q4k.argtypes = [_u8p, C.c_uint64, _u8p]
+        L.gfo_draft_law_full.restype = C.c_uint32
+        L.gfo_draft_law_full.argtypes = [_f32p, C.c_uint32, C.c_float, C.c_uint32, C.c_float, C.c_float, _u64p]
         L.gfo_draft_process_logits.argtypes = [_f32p, C.c_uint32, C.c_float, C.c_float, _u32p, C.c_uint32, _f32p]
         L.gfo_model_create.restype = C.c_void_p
         L.gfo_model_create.argtypes = [C.POINTER(ModelConfig), C.POINTER(Tensor), C.c_void_p,
@@ -283,6 +287,27 @@ class Oracle:
         n = self.lib.gfo_draft_law_compact(scores, scores.size, top_k, top_p, min_p, ids, cdf)
         return ids[:n], cdf[:n + 1]
 
+    def quantize_f16_q8_0(self, f16_bits):
+        """Binary16 values (as uint16 bits, a multiple of 32) -> Q8_0 blocks."""
+        f16_bits = np.ascontiguousarray(f16_bits, np.uint16)
+        out = np.zeros(f16_bits.size // 32 * 34, np.uint8)
+        rc = self.lib.gfo_quantize_f16_q8_0(f16_bits.ctypes.data, f16_bits.size // 32, out)
+        return rc, out
+
+    def requantize_q6k_q4k(self, q6k):
+        """Q6_K blocks (210 B each) -> Q4_K blocks (144 B each), block for block."""
+        q6k = np.ascontiguousarray(q6k, np.uint8).reshape(-1)
+        out = np.zeros(q6k.size // 210 * 144, np.uint8)
+        rc = self.lib.gfo_requantize_q6k_q4k(q6k, q6k.size // 210, out)
+        return rc, out
+
+    def draft_law_full(self, scores, temperature, top_k, top_p, min_p):
+        """Full-vocabulary law: (status, cdf[vocab + 1])."""
+        scores = np.ascontiguousarray(scores, np.float32)
+        cdf = np.zeros(scores.size + 1, np.uint64)
+        status = self.lib.gfo_draft_law_full(scores, scores.size, temperature, top_k, top_p, min_p, cdf)
+        return status, cdf
+
     def set_threads(self, n):
         self.lib.gfo_set_threads(n)
 
@@ -400,6 +425,8 @@ class Reference:
         L.ref_sample.argtypes = [C.c_uint64, C.c_float, C.c_uint32, C.c_float, C.c_float, C.c_float, _u32p,
                                  C.c_uint32, C.c_void_p, C.c_uint32, C.POINTER(C.c_uint32)]
         L.ref_columns8_round_trip.argtypes = [C.c_int, _u8p, C.c_uint64, C.c_uint64]
+        L.ref_quantize_f16_q8_0.argtypes = [C.c_void_p, C.c_uint64, C.c_uint64, _u8p]
+        L.ref_requantize_q6k_q4k.argtypes = [_u8p, C.c_uint64, C.c_uint64, _u8p]
 
     def dequantize(self, dtype, blocks):
         blocks = np.ascontiguousarray(blocks, np.uint8).reshape(-1)
@@ -500,6 +527,18 @@ class Reference:
                                  history if history.size else np.zeros(1, np.uint32), history.size,
                                  candidates.ctypes.data, candidates.size, C.byref(token))
         return rc, token.value
+
+    def quantize_f16_q8_0(self, f16_bits, k, n):
+        f16_bits = np.ascontiguousarray(f16_bits, np.uint16)
+        out = np.zeros(k * n // 32 * 34, np.uint8)
+        rc = self.lib.ref_quantize_f16_q8_0(f16_bits.ctypes.data, k, n, out)
+        return rc, out
+
+    def requantize_q6k_q4k(self, q6k, k, n):
+        q6k = np.ascontiguousarray(q6k, np.uint8).reshape(-1)
+        out = np.zeros(k * n // 256 * 144, np.uint8)
+        rc = self.lib.ref_requantize_q6k_q4k(q6k, k, n, out)
+        return rc, out
 
     def columns8_round_trip(self, dtype, weight, k, n):
         return self.lib.ref_columns8_round_trip(dtype, np.ascontiguousarray(weight, np.uint8).reshape(-1), k, n)

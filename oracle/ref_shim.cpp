@@ -84,6 +84,28 @@ int ref_dequantize(int dtype, const std::uint8_t* blocks, std::uint64_t block_co
     } catch (const std::exception&) { return -1; }
 }
 
+// tensor::quantize_f16_gguf_weight_q8_0  (src/tensor/quantization.cpp:628-673)
+int ref_quantize_f16_q8_0(const std::uint16_t* f16, std::uint64_t k, std::uint64_t n, std::uint8_t* out) {
+    try {
+        const auto descriptor = TensorDescriptor::from(Shape::from({k, n}), DType::f16);
+        const auto source = TensorStorage::from_bytes(descriptor,
+            std::span<const std::uint8_t>(reinterpret_cast<const std::uint8_t*>(f16), descriptor.byte_count));
+        const auto result = tensor::quantize_f16_gguf_weight_q8_0(source.view());
+        std::memcpy(out, result.bytes().data(), result.bytes().size());
+        return 0;
+    } catch (const std::exception&) { return -1; }
+}
+
+// tensor::requantize_q6_k_gguf_weight_q4_k  (src/tensor/quantization.cpp:746-800), canonical layout
+int ref_requantize_q6k_q4k(const std::uint8_t* q6, std::uint64_t k, std::uint64_t n, std::uint8_t* out) {
+    try {
+        const auto source = weight_tensor(14, q6, k, n);
+        const auto result = tensor::requantize_q6_k_gguf_weight_q4_k(source.view());
+        std::memcpy(out, result.bytes().data(), result.bytes().size());
+        return 0;
+    } catch (const std::exception&) { return -1; }
+}
+
 // backends::cpu::matmul_f32_quantized_gguf_weight  (src/tensor/backends/cpu_backend.cpp:301)
 int ref_matmul_quantized(int dtype, const float* x, const std::uint8_t* weight, std::uint32_t rows,
     std::uint64_t k, std::uint64_t n, float* out) {

@@ -11,6 +11,8 @@ Outputs (small, committed):
   ref_ops.npz      seeded inputs and the outputs of the reference's C++ CPU functions
                    (dequantised blocks, quantised matmul, RMSNorm, GeGLU, softcap, softmax,
                    NEOX RoPE, grouped attention), via oracle/_ref.
+  ref_requant.npz  the reference's load-time weight transforms (F16 -> Q8_0, Q6_K -> Q4_K) on seeded blocks,
+                   via oracle/_ref (`--only requant` writes just this file).
   ref_sampling.npz prepared target distributions, speculative accept/reject decisions,
                    proposal words and uniform draws from the reference's sampling.cpp.
   py_target.npz    logits / hidden / K / V of scripts/gemma3_target_reference.py::reference on a
@@ -60,6 +62,30 @@ def ops_inputs():
     data["att_k"] = rng.standard_normal((37, 2 * 256)).astype(np.float32)
     data["att_v"] = rng.standard_normal((37, 2 * 256)).astype(np.float32)
     return data
+
+
+def requant_inputs():
+    """Seeded sources of the load-time transforms: binary16 values over several magnitudes (with an
+    all-zero and a constant block) and Q6_K blocks (with a block of zero sub-scales and one of zero d)."""
+    rng = np.random.default_rng(20240712)
+    k8, n8 = 256, 24
+    values = (rng.standard_normal(k8 * n8) * rng.choice([1e-4, 1e-2, 1.0, 40.0], k8 * n8)).astype(np.float16)
+    values[:32] = 0
+    values[32:64] = np.float16(0.3337)
+    k6, n6 = 1024, 24
+    q6k = np.ascontiguousarray(syn.make_weight(rng, syn.Q6_K, k6, n6, sigma=0.05), np.uint8).reshape(-1, 210).copy()
+    q6k[0, 192:208] = 0
+    q6k[1, 208:210] = 0
+    q6k[2, :192] = 0x55
+    return {"f16": values.view(np.uint16).copy(), "f16_k": k8, "f16_n": n8, "q6k": q6k.reshape(-1), "q6k_k": k6, "q6k_n": n6}
+
+
+def write_requant(ref):
+    d = requant_inputs()
+    rc8, q8 = ref.quantize_f16_q8_0(d["f16"], d["f16_k"], d["f16_n"])
+    rc4, q4 = ref.requantize_q6k_q4k(d["q6k"], d["q6k_k"], d["q6k_n"])
+    assert rc8 == 0 and rc4 == 0
+    np.savez_compressed(HERE / "ref_requant.npz", q8=q8, q4=q4)
 
 
 def sampling_cases(count=64):
@@ -192,6 +218,10 @@ def model_tokens(name):
 
 def main():
     ref = Reference()
+    write_requant(ref)
+    if sys.argv[1:] == ["--only", "requant"]:
+        print("ref_requant.npz written to", HERE)
+        return
     d = ops_inputs()
     out = {}
     for name, dtype in (("q4k", syn.Q4_K), ("q6k", syn.Q6_K), ("q80", syn.Q8_0)):

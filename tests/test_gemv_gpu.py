@@ -31,6 +31,33 @@ def test_pack_round_trip_is_lossless(gf, dtype, n):
                                       gf.PackedWeight(dtype, k, padded, extended).packed.download(np.uint8))
 
 
+def test_weight_transforms_bit_exact(gf, oracle):
+    """The Gemma 2 load-time transforms on the device against the reference's own bytes (the committed
+    fixture made by the compiled reference) and against the CPU oracle on fresh blocks."""
+    want, d = np.load(golden.HERE / "ref_requant.npz"), golden.requant_inputs()
+    status, q8 = gf.quantize_f16_q8_0(d["f16"])
+    assert status == 0
+    np.testing.assert_array_equal(q8, want["q8"])
+    status, q4 = gf.requantize_q6k_q4k(d["q6k"])
+    assert status == 0
+    np.testing.assert_array_equal(q4, want["q4"])
+    rng = np.random.default_rng(5)
+    for sigma in (1e-3, 0.05, 2.0):                                   # 10,000 blocks per scale of d
+        q6k = syn.make_weight(rng, syn.Q6_K, 2560, 1000, sigma=sigma)
+        status, q4 = gf.requantize_q6k_q4k(q6k)
+        rc, q4_cpu = oracle.requantize_q6k_q4k(q6k)
+        assert status == 0 and rc == 0
+        np.testing.assert_array_equal(q4, q4_cpu)
+    values = (rng.standard_normal(3584 * 300) * rng.choice([1e-4, 1e-2, 1.0, 60.0], 3584 * 300)).astype(np.float16)
+    status, q8 = gf.quantize_f16_q8_0(values.view(np.uint16))
+    rc, q8_cpu = oracle.quantize_f16_q8_0(values.view(np.uint16))
+    assert status == 0 and rc == 0
+    np.testing.assert_array_equal(q8, q8_cpu)
+    bad = values.view(np.uint16).copy()
+    bad[77] = 0x7c00                                                  # infinity: the reference throws, the device flags it
+    assert gf.quantize_f16_q8_0(bad)[0] == 1
+
+
 @pytest.mark.parametrize("dtype", DTYPES)
 def test_dequantize_bit_exact(gf, oracle, dtype):
     rng = np.random.default_rng(dtype)

@@ -79,11 +79,41 @@ def test_draft_law_support_overflow_is_reported(gf, ge):
     logits = np.zeros(4096, np.float32)                                    # every token ties with the top-k-th
     receipt = ge.draft_sample(logits, ge.sampler_options(0.7), 5)
     assert receipt.status == 20
+    # greedy: all the mass on the lowest id among the tied maxima (the step CDF of the reference)
+    receipt = ge.draft_sample(logits, ge.sampler_options(0.0), 5)
+    assert receipt.status == 0 and receipt.count == 1 and receipt.token == 0 and receipt.cdf[1] == 1 << 32
+
+
+def test_selection_requests_written_on_the_device(gf, ge):
+    """Request rows built on the device from the sampler's window and a chain of device-resident tokens
+    equal the rows the host sampler would build (window slide, first-appearance order)."""
+    from guffin_b200 import lib
+    from guffin_b200.model import SelectionRequest
+    rng = np.random.default_rng(8)
+    for limit, held, top_k in ((64, 64, 40), (64, 10, 40), (8, 8, 1), (0, 0, 40), (64, 0, 7)):
+        window = rng.integers(0, 30, held).astype(np.uint32)                   # few distinct ids: many repeats
+        chain = rng.integers(0, 30, 8).astype(np.uint32)
+        base = np.zeros(67, np.uint32)
+        base[0], base[1], base[2] = top_k, limit, held
+        base[3:3 + held] = window
+        assert base.nbytes == gf.load().gf_selection_base_bytes()
+        base_dev, chain_dev = lib.DeviceBuffer.from_numpy(base), lib.DeviceBuffer.from_numpy(chain)
+        rows_dev = lib.DeviceBuffer(8 * C.sizeof(SelectionRequest))
+        lib.check(gf.load().gf_selection_requests(base_dev.ptr, int(chain[0]), chain_dev.ptr, 8, rows_dev.ptr, None))
+        rows = rows_dev.download(np.uint32).reshape(8, 66)
+        for i in range(8):
+            context = (list(window) + list(chain[:i + 1]))
+            context = context[len(context) - limit:] if limit else []
+            history = list(dict.fromkeys(int(t) for t in context))
+            assert rows[i, 0] == top_k + len(history) and rows[i, 1] == len(history)
+            assert list(rows[i, 2:2 + len(history)]) == history
+        for b in (base_dev, chain_dev, rows_dev):
+            b.free()
 
 
 # ------------------------------------------------------------------ the H1 loop
 
-def _models(gm, context=192, target_seed=51, draft_seed=52, correlated=False):
+def _models(gm, context=192, target_seed=51, draft_seed=52, correlated=False, rows=2, noise=0.0):
     tc, dc = syn.model_config("tiny-target"), syn.model_config("tiny-draft")
     tw = syn.make_model_weights("tiny-target", target_seed)
     if correlated:
@@ -92,13 +122,17 @@ def _models(gm, context=192, target_seed=51, draft_seed=52, correlated=False):
         dc = dict(tc, kv_f16=0, rope_scale_global=1.0)
         dw = dict(tw)
         dw["output_norm.weight"] = (tw["output_norm.weight"] * 0.8).astype(np.float32)
+        if noise:       # per-channel noise on the final norm: the drafter's best token now differs from the target's at times
+            factors = 1.0 + noise * np.random.default_rng(draft_seed).standard_normal(dw["output_norm.weight"].size)
+            dw["output_norm.weight"] = (dw["output_norm.weight"] * factors).astype(np.float32)
     else:
         dw = syn.make_model_weights("tiny-draft", draft_seed)
-    return (gm.Model(tc, tw, context, 2), gm.Model(dc, dw, context, 2), tc, tw)
+    return (gm.Model(tc, tw, context, rows), gm.Model(dc, dw, context, max(2, rows - 1)), tc, tw)
 
 
-def _options(ge, temperature, seed, speculative=1, forced=0, p=0.7, record=1, penalty=1.0):
-    return ge.H1Options(ge.sampler_options(temperature, seed=seed, repetition_penalty=penalty), speculative, forced, p, 7, record)
+def _options(ge, temperature, seed, speculative=1, forced=0, p=0.7, record=1, penalty=1.0, horizon=1):
+    return ge.H1Options(ge.sampler_options(temperature, seed=seed, repetition_penalty=penalty), speculative, forced, p, 7, record,
+                        horizon)
 
 
 def test_h1_greedy_is_lossless(gf, ge, gm):
@@ -114,7 +148,7 @@ def test_h1_greedy_is_lossless(gf, ge, gm):
     plain.prefill(prompt)
     ordinary = plain.generate(96)
     np.testing.assert_array_equal(speculative, ordinary)
-    assert stats.cycles > 20 and stats.accepted + stats.rejected + stats.fallback_cycles == stats.cycles
+    assert stats.cycles > 20 and stats.accepted + stats.rejected == stats.cycles and stats.fallback_cycles == 0
     assert stats.accepted > 0
     assert target.position == prompt.size + len(speculative) - 1           # every emitted token but the last is cached
     assert target.status() == 0 and draft.status() == 0
@@ -141,6 +175,57 @@ def test_h1_continues_without_the_drafter_when_its_context_fills_first(gf, ge, g
     assert draft.position <= 40 and target.status() == 0
 
 
+def _replay_decisions(oracle, prompt, tokens, records, seed, penalty):
+    """Replays every acceptance test of a sampled run through the oracle's restatement of sampling.cpp
+    with the oracle's own RNG streams; returns the token stream the decisions imply."""
+    options = OracleOptions(0.7, 40, 0.95, 0.05, penalty)
+    target_rng = oracle.rng(seed)
+    proposal_rng = oracle.proposal_rng(target_rng)
+    oracle.lib.gfo_mt_next(C.byref(target_rng))                              # the first token's ordinary draw
+    observed = list(prompt)
+    emitted = [int(tokens[0])]
+    chain = []                                                               # rows of the running cycle accepted so far
+    for record in records:
+        assert record.status == 0 and record.depth == len(chain)
+        assert oracle.next_proposal_word(proposal_rng) == record.word
+        candidates = np.zeros(record.candidate_count, TOKEN_LOGIT)
+        for i in range(record.candidate_count):
+            candidates[i] = (record.candidates[i].token, record.candidates[i].logit)
+        window = (observed + chain + [record.root])[-64:]
+        history = list(dict.fromkeys(window)) if penalty != 1.0 else []
+        rc, prepared = oracle.prepare_distribution(candidates, options, history)
+        assert rc == 0 and prepared.count == record.draft.count
+        q = np.array(record.draft.target_mass[:prepared.count], np.uint64)
+        rc, acceptance, residual = oracle.prepare_speculative(record.proposal, record.draft.proposal_mass, q, prepared)
+        assert rc == 0
+        accept_draw = oracle.uniform(target_rng)
+        residual_draw = oracle.uniform(target_rng) if accept_draw >= acceptance else 0.0
+        rc, token, accepted = oracle.sample_speculative(record.proposal, acceptance, residual, accept_draw, residual_draw)
+        assert (rc, token, accepted) == (0, record.token, bool(record.accepted))
+        chain.append(record.root)
+        if accepted:
+            emitted.append(record.proposal)
+            if record.depth + 1 == record.horizon:                           # the whole chain held
+                oracle.lib.gfo_mt_next(C.byref(target_rng))                  # the next root's ordinary draw
+                observed += chain + [record.proposal]
+                chain = []
+                emitted.append(None)                                         # the next root: no acceptance test produced it
+        else:
+            emitted.append(record.token)
+            observed += chain
+            chain = []
+    return emitted
+
+
+def _check_stream(tokens, emitted):
+    """The emitted tokens are the accepted proposals and corrected tokens in order, with a freely
+    sampled root after every chain that held whole."""
+    got = [int(t) for t in tokens]
+    assert len(emitted) >= len(got) - 1
+    for have, expect in zip(got, emitted):
+        assert expect is None or have == expect
+
+
 @pytest.mark.parametrize("penalty", [1.0, 1.2])
 def test_h1_acceptance_decisions_match_oracle(gf, ge, gm, oracle, penalty):
     """Every accept/reject decision and corrected token of a sampled run, replayed through the
@@ -153,46 +238,161 @@ def test_h1_acceptance_decisions_match_oracle(gf, ge, gm, oracle, penalty):
     tokens = engine.generate(120)
     records, stats = engine.records(), engine.stats()
     assert len(records) == stats.cycles and stats.accepted > 0 and stats.rejected > 0
-    options = OracleOptions(0.7, 40, 0.95, 0.05, penalty)
-    target_rng = oracle.rng(seed)
-    proposal_rng = oracle.proposal_rng(target_rng)
-    oracle.lib.gfo_mt_next(C.byref(target_rng))                              # the first token's ordinary draw
-    observed = list(prompt)
-    emitted = [int(tokens[0])]
-    for record in records:
-        assert record.status == 0
-        assert oracle.next_proposal_word(proposal_rng) == record.word
-        candidates = np.zeros(record.candidate_count, TOKEN_LOGIT)
-        for i in range(record.candidate_count):
-            candidates[i] = (record.candidates[i].token, record.candidates[i].logit)
-        window = (observed + [record.root])[-64:]
-        history = list(dict.fromkeys(window)) if penalty != 1.0 else []
-        rc, prepared = oracle.prepare_distribution(candidates, options, history)
-        assert rc == 0 and prepared.count == record.draft.count
-        q = np.array(record.draft.target_mass[:prepared.count], np.uint64)
-        rc, acceptance, residual = oracle.prepare_speculative(record.proposal, record.draft.proposal_mass, q, prepared)
-        assert rc == 0
-        accept_draw = oracle.uniform(target_rng)
-        residual_draw = oracle.uniform(target_rng) if accept_draw >= acceptance else 0.0
-        rc, token, accepted = oracle.sample_speculative(record.proposal, acceptance, residual, accept_draw, residual_draw)
-        assert (rc, token, accepted) == (0, record.token, bool(record.accepted))
-        if accepted:
-            oracle.lib.gfo_mt_next(C.byref(target_rng))                      # the next root's ordinary draw
-            observed += [record.root, record.proposal]
-            emitted.append(record.proposal)
+    _check_stream(tokens, _replay_decisions(oracle, prompt, tokens, records, seed, penalty))
+
+
+# ------------------------------------------------------------------ horizons above one
+
+def _assert_caches_match_replay(gm, target, draft, tc, tw, prompt, tokens, context):
+    """Whatever was accepted or rolled back, the target's cache must hold exactly the rows of its own
+    token sequence: compare every layer's K/V with a fresh plan fed the same tokens two at a time.
+    The drafter's position must be the rows it was allowed to keep."""
+    cached = target.position
+    sequence = np.concatenate([prompt, tokens])[:cached].astype(np.uint32)
+    fresh = gm.Model(tc, tw, context, 2)
+    fresh.use_tensor_prefill(False)
+    fresh.prefill(sequence)
+    for layer in range(tc["layers"]):
+        window = tc["sliding_window"] if fresh_layer_is_local(tc, layer) else cached
+        first = max(0, cached - window)
+        k0, v0 = target.read_kv(layer, first, cached - first)
+        k1, v1 = fresh.read_kv(layer, first, cached - first)
+        np.testing.assert_allclose(k0, k1, rtol=2e-3, atol=2e-3)            # binary16 rows: within one or two ulps
+        np.testing.assert_allclose(v0, v1, rtol=2e-3, atol=2e-3)
+    assert cached <= draft.position + 2 and draft.position <= cached
+
+
+def fresh_layer_is_local(config, layer):
+    pattern = config["sliding_pattern"]
+    return (layer + 1) % 6 != 0 if pattern == 6 else layer % 2 == 0 if pattern == 2 else False
+
+
+@pytest.mark.parametrize("horizon,noise", [(2, 0.0), (3, 0.5), (7, 0.5), (3, None)])
+def test_chain_greedy_is_lossless(gf, ge, gm, horizon, noise):
+    """A chain of `horizon` drafts verified in one pass of horizon + 1 rows: with a greedy target the
+    emitted tokens are exactly the ordinary decode's, whatever is accepted or rolled back (noise:
+    how far the drafter's final norm is from the target's; None = an unrelated drafter)."""
+    prompt = np.random.default_rng(1).integers(0, 2048, 33).astype(np.uint32)
+    target, draft, tc, tw = _models(gm, correlated=noise is not None, rows=horizon + 1, noise=noise or 0.0)
+    spec = ge.H1(target, draft, _options(ge, 0.0, 5, horizon=horizon))
+    spec.prefill(prompt)
+    speculative = spec.generate(96)
+    stats = spec.stats()
+    target2, _, _, _ = _models(gm)
+    plain = ge.H1(target2, None, _options(ge, 0.0, 5, speculative=0))
+    plain.prefill(prompt)
+    np.testing.assert_array_equal(speculative, plain.generate(96))
+    assert stats.accepted + stats.rejected == stats.cycles and stats.cycles > 5
+    assert stats.drafted_tokens >= stats.accepted_tokens
+    if noise is not None:
+        assert stats.accepted_tokens > stats.cycles                         # chains longer than one draft were kept
+    assert target.position == prompt.size + len(speculative) - 1
+    assert target.status() == 0 and draft.status() == 0
+    _assert_caches_match_replay(gm, target, draft, tc, tw, prompt, speculative, 192)
+
+
+@pytest.mark.parametrize("penalty", [1.0, 1.2])
+def test_chain_acceptance_decisions_match_oracle(gf, ge, gm, oracle, penalty):
+    """Horizon 3, sampled: every acceptance test along every chain replayed through the oracle
+    (one proposal word per test, the target stream advanced only by the tests that ran)."""
+    seed = 4321
+    prompt = np.random.default_rng(5).integers(0, 2048, 20).astype(np.uint32)
+    target, draft, tc, tw = _models(gm, correlated=True, rows=4, noise=0.6)
+    engine = ge.H1(target, draft, _options(ge, 0.7, seed, penalty=penalty, horizon=3))
+    engine.prefill(prompt)
+    tokens = engine.generate(150)
+    records, stats = engine.records(), engine.stats()
+    assert stats.cycles > 10 and len(records) >= stats.cycles and stats.accepted_tokens > 0 and stats.rejected > 0
+    assert max(r.depth for r in records) == 2                               # some chains were verified to their end
+    if penalty == 1.0:
+        assert any(r.depth >= 1 and not r.accepted for r in records)        # and some were cut part way
+    _check_stream(tokens, _replay_decisions(oracle, prompt, tokens, records, seed, penalty))
+    assert target.status() == 0 and draft.status() == 0
+    _assert_caches_match_replay(gm, target, draft, tc, tw, prompt, tokens, 192)
+
+
+def test_chain_forced_schedule(gf, ge, gm):
+    prompt = np.random.default_rng(3).integers(0, 2048, 16).astype(np.uint32)
+    target, draft, _, _ = _models(gm, context=256, rows=4)
+    engine = ge.H1(target, draft, _options(ge, 0.7, 9, forced=1, p=0.7, horizon=3))
+    engine.prefill(prompt)
+    tokens = engine.generate(200)
+    stats = engine.stats()
+    assert len(tokens) == 200 and stats.emitted_tokens == 200
+    rate = stats.accepted_tokens / len(engine.records())                    # Bernoulli(0.7) per acceptance test
+    assert 0.55 < rate < 0.85
+    assert stats.emitted_tokens > 1.8 * stats.cycles                        # 1 + 0.7 + 0.49 + 0.343 tokens per cycle expected
+
+
+# ------------------------------------------------------------------ the law over the whole vocabulary
+
+def test_full_vocabulary_law_known_answers(gf, ge):
+    """The reference's own cases (tests/engine/gemma3_draft_tests.cpp:283-300): equal logits everywhere."""
+    vocab = 262144
+    logits = np.zeros(vocab, np.float32)
+    everything = np.arange(vocab, dtype=np.uint32)
+    options = ge.sampler_options(1.0, top_k=1, top_p=1.0, min_p=0.0)
+    receipt, intervals = ge.draft_sample_full(logits, options, 0xffffffff, gather=everything)
+    assert receipt.status == 0 and receipt.count == 0xffffffff
+    mass = (intervals[:, 1] - intervals[:, 0]).astype(np.int64)
+    assert np.all(mass == 16384) and int(mass.sum()) == 1 << 32             # every cut-off tie survives top-k 1
+    assert receipt.token == vocab - 1 and int(intervals[-1, 0]) == (1 << 32) - 16384
+    options = ge.sampler_options(1.0, top_k=1, top_p=0.5, min_p=0.0)
+    receipt, intervals = ge.draft_sample_full(logits, options, 0, gather=[0, 1, vocab - 2, vocab - 1])
+    mass = (intervals[:, 1] - intervals[:, 0]).astype(np.int64)
+    assert receipt.status == 0 and mass[0] == 32768 and mass[2] == 0 and mass[3] == 0      # ascending-tail nucleus
+    options = ge.sampler_options(1.0, top_k=1, top_p=float(np.finfo(np.float32).smallest_subnormal), min_p=0.0)
+    receipt, intervals = ge.draft_sample_full(logits, options, 0, gather=[0, 1])
+    mass = (intervals[:, 1] - intervals[:, 0]).astype(np.int64)
+    assert receipt.status == 0 and receipt.token == 0 and mass[0] == 1 << 32 and mass[1] == 0
+
+
+@pytest.mark.parametrize("vocab,top_k,top_p,min_p", [(2048, 100, 0.9, 0.02), (6144, 0, 0.8, 0.0), (262144, 200, 0.95, 0.05),
+                                                     (4096, 0, 1.0, 0.0), (2048 + 256, 40, 0.95, 0.05)])
+def test_full_vocabulary_law_matches_oracle(gf, ge, oracle, vocab, top_k, top_p, min_p):
+    rng = np.random.default_rng(vocab + top_k)
+    logits = (rng.standard_normal(vocab) * 2.0).astype(np.float32)
+    if top_k == 40:
+        logits[:] = rng.integers(0, 3, vocab)                               # three distinct values: > 256 ties at the cut-off
+    options = ge.sampler_options(0.7, top_k=top_k, top_p=top_p, min_p=min_p)
+    everything = np.arange(vocab, dtype=np.uint32)
+    scores = oracle.draft_process_logits(logits, 0.7)
+    status, want = oracle.draft_law_full(scores, 0.7, top_k, top_p, min_p)
+    assert status == 0
+    for word in (0, 0x7fffffff, 0xffffffff, int(rng.integers(1 << 32))):
+        receipt, intervals = ge.draft_sample_full(logits, options, word, gather=everything)
+        assert receipt.status == 0 and receipt.count == 0xffffffff and receipt.word == word
+        got = np.concatenate([intervals[:, 0], intervals[-1:, 1]])
+        assert np.array_equal(intervals[1:, 0], intervals[:-1, 1])          # the bins tile [0, 2^32)
+        assert got[0] == 0 and got[-1] == 1 << 32 and np.all(np.diff(got.astype(np.int64)) >= 0)
+        mass, expect = np.diff(got.astype(np.float64)) / TWO32, np.diff(want.astype(np.float64)) / TWO32
+        assert np.abs(mass - expect).max() < 1e-6
+        if top_k or top_p < 1.0 or min_p > 0.0:
+            assert np.array_equal(mass == 0, expect == 0)                   # the same tokens were filtered out
         else:
-            observed.append(record.root)
-            emitted.append(record.token)
-    # The emitted stream is roots and accepted proposals interleaved as the loop defines.
-    assert emitted[:len(records)] == [int(t) for t in _expected_stream(tokens, records)][:len(records)]
+            assert np.all(mass[expect > 1e-6] > 0)                          # unfiltered: only vanishing bins may close
+        index = int(np.searchsorted(got, np.uint64(word), side="right") - 1)
+        assert receipt.token == index
 
 
-def _expected_stream(tokens, records):
-    """First token, then per cycle the accepted proposal or the corrected token."""
-    out = [int(tokens[0])]
-    for record in records:
-        out.append(record.proposal if record.accepted else record.token)
-    return out
+def test_flat_drafter_is_verified_through_the_full_law(gf, ge, gm, oracle):
+    """A drafter whose logits all tie overflows the compact law at every proposal: each cycle then
+    rebuilds the law over the whole vocabulary, verifies again, and the decisions still replay."""
+    seed = 77
+    prompt = np.random.default_rng(6).integers(0, 2048, 12).astype(np.uint32)
+    tc, dc = syn.model_config("tiny-target"), syn.model_config("tiny-draft")
+    tw, dw = syn.make_model_weights("tiny-target", 51), dict(syn.make_model_weights("tiny-draft", 52))
+    dw["output_norm.weight"] = np.zeros_like(dw["output_norm.weight"])       # every logit is exactly zero
+    target, draft = gm.Model(tc, tw, 128, 2), gm.Model(dc, dw, 128, 2)
+    engine = ge.H1(target, draft, _options(ge, 0.7, seed))
+    engine.prefill(prompt)
+    tokens = engine.generate(40)
+    records, stats = engine.records(), engine.stats()
+    assert stats.cycles > 10 and stats.full_law_proposals == stats.cycles and stats.fallback_cycles == stats.cycles
+    assert all(r.draft.proposal_mass > 0 for r in records)
+    masses = {int(m) for r in records for m in r.draft.target_mass[:r.draft.count]}
+    assert len(masses - {0}) == 1                                            # a uniform law over the nucleus
+    _check_stream(tokens, _replay_decisions(oracle, prompt, tokens, records, seed, 1.0))
 
 
 def test_h1_forced_schedule_runs_the_real_law(gf, ge, gm):

