@@ -8,6 +8,7 @@
 #include "pass.cuh"
 #include "prefill.cuh"
 
+#include <memory>
 #include <string>
 #include <vector>
 
@@ -40,6 +41,21 @@ struct LayerCache {
 enum ForwardFlags : uint32_t {
     kForwardLogits = 1u,        // final norm + output head for every row
     kForwardDeviceTokens = 2u,  // token ids are already in the device token buffer
+};
+
+// KV caches of independent conversation streams that share one plan's weights (streams.cu).
+constexpr uint32_t kMaxStreams = 256;
+struct StreamSet {
+    uint32_t count = 0;
+    std::vector<std::vector<void*>> ring_k, ring_v;       // [stream][layer], shaped like the plan's own rings
+    std::vector<uint32_t> positions_host;
+    uint32_t* positions_dev = nullptr;                     // [count]
+    StreamRings* rings_dev = nullptr;                      // [layer][count]
+    StreamPublishLayer* publish_layers_dev = nullptr;      // [layer]: the plan's private rows
+    float* logits = nullptr;                               // [count][vocab]
+    void *candidates_ws = nullptr, *requests_dev = nullptr, *results_dev = nullptr, *requests_pinned = nullptr;
+    std::vector<void*> allocations;
+    ~StreamSet();
 };
 
 class Model {
@@ -89,6 +105,15 @@ public:
     // 2: as 1, but attention always as launches of its own.
     void set_pass_mode(int mode) { if (mode != pass_mode_) invalidate_passes(); pass_mode_ = mode; }
 
+    // Independent streams over this plan's weights (streams.cu).
+    int streams_create(uint32_t count, StreamSet** out);
+    int streams_prefill(StreamSet& set, uint32_t stream, const uint32_t* tokens_host, uint32_t count);
+    int streams_decode(StreamSet& set, const uint32_t* tokens_host);
+    int streams_select(StreamSet& set, const void* requests_host);
+    int streams_read_candidates(StreamSet& set, void* results_host);
+    int streams_read_logits(StreamSet& set, uint32_t stream, float* host);
+    size_t streams_kv_bytes(const StreamSet& set) const;
+
     // Enqueues the selection for rows whose requests already sit in requests_dev().
     int select_device(uint32_t rows);
     // Uploads one token id into the device token buffer slot `row` (asynchronous).
@@ -109,6 +134,8 @@ private:
     };
 
     int bind_q8_head_from_f16(const void* f16_dev, uint64_t k, uint64_t n);
+    int bind_rings(const std::vector<void*>& ring_k, const std::vector<void*>& ring_v, uint32_t position);
+    int encode_stream_group(StreamSet& set, uint32_t first, uint32_t rows);
     int encode_blocks(uint32_t rows, uint32_t flags);
     int run_gemv(struct GemvLaunch& launch, uint32_t rows);
     int emit_embedding(uint32_t rows, float scale);

@@ -2,6 +2,8 @@
 // split-KV grouped-query attention over ring + private rows, and KV publication.
 #include "ops.cuh"
 #include "attention.cuh"
+
+#include <algorithm>
 #include "embedding.cuh"
 
 #include <cmath>
@@ -76,7 +78,7 @@ __global__ void __launch_bounds__(256) rope_store_kernel(RopeStoreParams p) {
         first = __fmul_rn(__fmul_rn(first, inv), gamma[i]);
         second = __fmul_rn(__fmul_rn(second, inv), gamma[i + half]);
     }
-    const uint32_t position = *p.base_position + row;
+    const uint32_t position = p.row_positions ? p.row_positions[row] : *p.base_position + row;
     // Angle in double as the reference forms it (ops/rope.cpp:109-117); the divisor
     // freq_base^(2i/d) comes from a table when the caller has one.  The angle is reduced to
     // [-pi, pi] in double (two-term 2*pi), after which single-precision sine and cosine are
@@ -128,6 +130,61 @@ __global__ void __launch_bounds__(kAttentionMmaWarps * 32) attention_mma_kernel(
     __shared__ AttentionMmaSmem<kAttentionMmaWarps, G * R> sm;
     bool waited = false;
     attention_mma_body<G, R, 1, true, true>(p, blockIdx.x, blockIdx.y, blockIdx.z, sm, LaunchBlock(), waited);
+}
+
+// One query row per conversation stream: block (kv head, partition, stream) runs the single-row body with
+// the stream's rings and position substituted, and its own slice of the private rows and the workspace.
+template <typename KV, int G>
+__device__ __forceinline__ AttentionParams stream_view(AttentionParams p, const StreamRings* rings, const uint32_t* positions, uint32_t s) {
+    const size_t qw = (size_t)p.heads * 256u, kvw = (size_t)p.kv_heads * 256u;
+    p.q += s * qw;
+    p.out += s * qw;
+    p.ring_k = rings[s].ring_k;
+    p.ring_v = rings[s].ring_v;
+    p.private_k = static_cast<const KV*>(p.private_k) + s * kvw;
+    p.private_v = static_cast<const KV*>(p.private_v) + s * kvw;
+    p.partial_out += (size_t)s * p.heads * kMaxAttentionPartitions * 256u;
+    p.partial_ml += (size_t)s * p.heads * kMaxAttentionPartitions * 2u;
+    p.counters += s * p.heads;
+    p.base_position = positions + s;
+    p.rows = 1u;
+    return p;
+}
+
+template <int G>
+__global__ void __launch_bounds__(kAttentionMmaWarps * 32) stream_attention_mma_kernel(AttentionParams p, const StreamRings* rings,
+                                                                                       const uint32_t* positions) {
+    __shared__ AttentionMmaSmem<kAttentionMmaWarps, G> sm;
+    bool waited = false;
+    const AttentionParams view = stream_view<__half, G>(p, rings, positions, blockIdx.z);
+    attention_mma_body<G, 1, 1, true, true>(view, blockIdx.x, blockIdx.y, 0u, sm, LaunchBlock(), waited);
+}
+
+template <int G>
+__global__ void __launch_bounds__(kAttentionWarps * 32) stream_attention_kernel(AttentionParams p, const StreamRings* rings,
+                                                                               const uint32_t* positions) {
+    __shared__ AttentionSmem<kAttentionWarps, G> sm;
+    bool waited = false;
+    const AttentionParams view = stream_view<float, G>(p, rings, positions, blockIdx.z);
+    attention_body<float, G, 1, true>(view, blockIdx.x, blockIdx.y, 0u, sm, LaunchBlock(), waited);
+}
+
+__global__ void __launch_bounds__(128) stream_publish_kernel(const StreamPublishLayer* __restrict__ layers, const StreamRings* __restrict__ rings,
+                                                             uint32_t stride, const uint32_t* __restrict__ positions) {
+    const uint32_t row = blockIdx.x, layer = blockIdx.y;
+    const StreamPublishLayer L = layers[layer];
+    const StreamRings R = rings[(size_t)layer * stride + row];
+    const size_t dst = (size_t)(positions[row] & L.ring_mask) * L.row_bytes, src = (size_t)row * L.row_bytes;
+    uint8_t* ring_k = static_cast<uint8_t*>(const_cast<void*>(R.ring_k));
+    uint8_t* ring_v = static_cast<uint8_t*>(const_cast<void*>(R.ring_v));
+    for (uint32_t b = threadIdx.x * 16u; b < L.row_bytes; b += blockDim.x * 16u) {
+        *reinterpret_cast<uint4*>(ring_k + dst + b) = *reinterpret_cast<const uint4*>(L.private_k + src + b);
+        *reinterpret_cast<uint4*>(ring_v + dst + b) = *reinterpret_cast<const uint4*>(L.private_v + src + b);
+    }
+}
+
+__global__ void advance_positions_kernel(uint32_t* positions, uint32_t rows) {
+    if (threadIdx.x < rows) positions[threadIdx.x] += 1u;
 }
 
 // ------------------------------------------------------------------ GeGLU, KV publication
@@ -259,6 +316,37 @@ static int launch_attention_f16(const AttentionParams& p, cudaStream_t stream, b
     }
     if (group == 4u) return launch_attention_mma_instance<4, 1>(p, stream, pdl);
     return fail(GF_ERR_INVALID, "attention: query/KV head ratio %u unsupported (1, 2, 4)", group);
+}
+
+int launch_stream_attention(const AttentionParams& params, const StreamRings* rings_dev, const uint32_t* positions_dev, cudaStream_t stream) {
+    AttentionParams p = params;
+    if (p.head_dim != 256u || p.kv_heads == 0 || p.heads % p.kv_heads || p.rows == 0 || !rings_dev || !positions_dev)
+        return fail(GF_ERR_INVALID, "stream attention: bad geometry");
+    const uint32_t group = p.heads / p.kv_heads, streams = p.rows;
+    // About two waves of blocks over (kv head, stream) pairs and partitions.
+    const uint32_t per_pair = 2u * (uint32_t)sm_count() / (p.kv_heads * streams);
+    p.target_parts = std::min<uint32_t>(std::max<uint32_t>(per_pair, 1u), (uint32_t)kMaxAttentionPartitions);
+    p.defer_merge = 0u;
+    const dim3 grid(p.kv_heads, p.target_parts, streams);
+    if (p.kv_f16) {
+        if (group == 1u) return launch_kernel(stream_attention_mma_kernel<1>, grid, dim3(kAttentionMmaWarps * 32), 0, stream, false, p, rings_dev, positions_dev);
+        if (group == 2u) return launch_kernel(stream_attention_mma_kernel<2>, grid, dim3(kAttentionMmaWarps * 32), 0, stream, false, p, rings_dev, positions_dev);
+        if (group == 4u) return launch_kernel(stream_attention_mma_kernel<4>, grid, dim3(kAttentionMmaWarps * 32), 0, stream, false, p, rings_dev, positions_dev);
+    } else {
+        if (group == 1u) return launch_kernel(stream_attention_kernel<1>, grid, dim3(kAttentionWarps * 32), 0, stream, false, p, rings_dev, positions_dev);
+        if (group == 2u) return launch_kernel(stream_attention_kernel<2>, grid, dim3(kAttentionWarps * 32), 0, stream, false, p, rings_dev, positions_dev);
+        if (group == 4u) return launch_kernel(stream_attention_kernel<4>, grid, dim3(kAttentionWarps * 32), 0, stream, false, p, rings_dev, positions_dev);
+    }
+    return fail(GF_ERR_INVALID, "stream attention: query/KV head ratio %u unsupported (1, 2, 4)", group);
+}
+
+int launch_stream_publish(const StreamPublishLayer* layers_dev, uint32_t layer_count, const StreamRings* rings_dev, uint32_t stride,
+                          uint32_t* positions_dev, uint32_t rows, cudaStream_t stream) {
+    if (!layers_dev || !rings_dev || !positions_dev || rows == 0 || rows > 32u) return fail(GF_ERR_INVALID, "stream publish: bad arguments");
+    const int status = launch_kernel(stream_publish_kernel, dim3(rows, layer_count), dim3(128), 0, stream, false, layers_dev, rings_dev,
+                                     stride, (const uint32_t*)positions_dev);
+    if (status != GF_OK) return status;
+    return launch_kernel(advance_positions_kernel, dim3(1), dim3(32), 0, stream, false, positions_dev, rows);
 }
 
 int launch_attention(const AttentionParams& p, cudaStream_t stream, bool pdl) {

@@ -31,6 +31,7 @@ struct RopeStoreParams {
     uint32_t rows, heads, kv_heads, head_dim;
     float eps, freq_base, freq_scale;
     int kv_f16;
+    const uint32_t* row_positions = nullptr;   // optional [rows]: row r sits at row_positions[r] instead of base + r (rows of different streams)
 };
 
 struct AttentionParams {
@@ -78,6 +79,17 @@ int launch_rms_norm(const float* x, const float* gamma, const float* residual, f
                     uint32_t hidden, float eps, cudaStream_t stream, bool pdl);
 int launch_rope_store(const RopeStoreParams& p, cudaStream_t stream, bool pdl);
 int launch_attention(const AttentionParams& p, cudaStream_t stream, bool pdl);
+
+// Rows that belong to different conversation streams: row s of the launch is one query row of stream s, at
+// that stream's own position, over that stream's own rings; its private row is row s of private_k / private_v.
+// `p` is laid out for p.rows = streams rows (q, out, private rows, workspace); ring pointers come from the table.
+struct StreamRings { const void* ring_k; const void* ring_v; };
+int launch_stream_attention(const AttentionParams& p, const StreamRings* rings_dev, const uint32_t* positions_dev, cudaStream_t stream);
+// Private row r of every layer into ring slot positions[r] & mask of stream r's rings (rings_dev is
+// [layer][stride] with the launch's streams starting at column 0), then positions[r] += 1.
+struct StreamPublishLayer { const uint8_t *private_k, *private_v; uint32_t ring_mask, row_bytes; };
+int launch_stream_publish(const StreamPublishLayer* layers_dev, uint32_t layer_count, const StreamRings* rings_dev, uint32_t stride,
+                          uint32_t* positions_dev, uint32_t rows, cudaStream_t stream);
 int launch_geglu(const float* gate, const float* up, float* out, uint64_t count, cudaStream_t stream, bool pdl);
 int launch_kv_scatter(const void* private_k, const void* private_v, void* ring_k, void* ring_v,
                       const uint32_t* base_position, uint32_t rows, uint32_t row_width, uint32_t ring_mask,

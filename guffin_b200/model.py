@@ -80,6 +80,16 @@ lib.register({
     "gf_model_use_tensor_prefill": (i32, [vp, i32]),
     "gf_model_prefill_logits_row": (u32, [vp]),
     "gf_model_weight_sweep": (i32, [vp, u32, C.POINTER(u32), C.POINTER(u64)]),
+    "gf_streams_create": (i32, [vp, u32, C.POINTER(vp)]),
+    "gf_streams_destroy": (i32, [vp]),
+    "gf_streams_count": (u32, [vp]),
+    "gf_streams_prefill": (i32, [vp, u32, vp, u32]),
+    "gf_streams_decode": (i32, [vp, vp]),
+    "gf_streams_select": (i32, [vp, vp]),
+    "gf_streams_read_candidates": (i32, [vp, vp]),
+    "gf_streams_read_logits": (i32, [vp, u32, vp]),
+    "gf_streams_position": (i32, [vp, u32, C.POINTER(u32)]),
+    "gf_streams_kv_bytes_per_step": (sz, [vp]),
 })
 
 MATRIX_KINDS = {"token_embd": 0, "output": 1, "attn_q": 2, "attn_k": 3, "attn_v": 4, "attn_output": 5,
@@ -235,6 +245,63 @@ class Model:
     def close(self) -> None:
         if getattr(self, "handle", None):
             self.L.gf_model_destroy(self.handle)
+            self.handle = None
+
+    def __del__(self):
+        try:
+            self.close()
+        except Exception:
+            pass
+
+
+class Streams:
+    """Independent conversation streams that share one plan's weights (gf_streams_*)."""
+
+    def __init__(self, model: Model, count: int):
+        self.L = load()
+        self.model, self.count = model, count
+        handle = vp()
+        check(self.L.gf_streams_create(model.handle, count, C.byref(handle)))
+        self.handle = handle.value
+
+    def prefill(self, stream: int, tokens) -> None:
+        tokens = np.ascontiguousarray(tokens, np.uint32)
+        check(self.L.gf_streams_prefill(self.handle, stream, tokens.ctypes.data, tokens.size))
+
+    def decode(self, tokens) -> None:
+        tokens = np.ascontiguousarray(tokens, np.uint32)
+        assert tokens.size == self.count
+        check(self.L.gf_streams_decode(self.handle, tokens.ctypes.data))
+
+    def logits(self, stream: int) -> np.ndarray:
+        out = np.empty(self.model.cfg.vocab, np.float32)
+        check(self.L.gf_streams_read_logits(self.handle, stream, out.ctypes.data))
+        return out
+
+    def select(self, requests) -> list:
+        assert len(requests) == self.count
+        array = (SelectionRequest * self.count)(*requests)
+        check(self.L.gf_streams_select(self.handle, C.byref(array)))
+        results = (CandidateResult * self.count)()
+        check(self.L.gf_streams_read_candidates(self.handle, C.byref(results)))
+        return list(results)
+
+    def greedy(self) -> np.ndarray:
+        """The best token of every stream's current logits (one selection over all rows)."""
+        results = self.select([selection_request(1)] * self.count)
+        return np.array([r.candidates[0].token for r in results], np.uint32)
+
+    def position(self, stream: int) -> int:
+        out = u32()
+        check(self.L.gf_streams_position(self.handle, stream, C.byref(out)))
+        return out.value
+
+    def kv_bytes_per_step(self) -> int:
+        return self.L.gf_streams_kv_bytes_per_step(self.handle)
+
+    def close(self) -> None:
+        if getattr(self, "handle", None):
+            self.L.gf_streams_destroy(self.handle)
             self.handle = None
 
     def __del__(self):

@@ -349,6 +349,31 @@ GF_API int gf_model_use_pass_kernel(gf_model* model, int mode);
  * reused as inputs; results are not meaningful. */
 GF_API int gf_model_weight_sweep(gf_model* model, uint32_t rows, uint32_t* out_launches, uint64_t* out_weight_bytes);
 
+/* ---- independent conversation streams on one GPU.  No counterpart as a type in the reference, which decodes
+ * one conversation per process; each row of a step computes the reference's decode graph
+ * (run_gemma2_metal_resident_decode_step, src/engine/gemma2_runtime.cpp:250-418; block schedule
+ * gemma_target_runtime.cpp:13-221) for its own conversation.  `count` KV caches shaped like the plan's own share
+ * the plan's weights; a decode step takes one token per stream and runs the streams in groups of up to
+ * row_capacity rows, so the weights are streamed once per group instead of once per stream, while every row is
+ * rotated at its stream's position, attends its stream's rings and is published into them.  A stream's results
+ * do not depend on which streams share its pass.  Streams are the unit that is spread over the GPUs of a node:
+ * one process and one replica of the weights per GPU, no collective.
+ * gf_streams_prefill ingests a prompt into one stream through gf_model_prefill's paths (its last token's logits
+ * become that stream's row); gf_streams_decode leaves logits for every stream, gf_streams_select /
+ * gf_streams_read_candidates run candidate selection over all rows (`count` request / result rows). ---- */
+typedef struct gf_streams gf_streams;
+GF_API int gf_streams_create(gf_model* model, uint32_t count, gf_streams** out_streams);
+GF_API int gf_streams_destroy(gf_streams* streams);
+GF_API uint32_t gf_streams_count(const gf_streams* streams);
+GF_API int gf_streams_prefill(gf_streams* streams, uint32_t stream, const uint32_t* tokens_host, uint32_t count);
+GF_API int gf_streams_decode(gf_streams* streams, const uint32_t* tokens_host /* one id per stream */);
+GF_API int gf_streams_select(gf_streams* streams, const void* requests_host);
+GF_API int gf_streams_read_candidates(gf_streams* streams, void* results_host);
+GF_API int gf_streams_read_logits(gf_streams* streams, uint32_t stream, float* logits_host);
+GF_API int gf_streams_position(const gf_streams* streams, uint32_t stream, uint32_t* out_position);
+/* K and V bytes one decode step reads at the streams' current positions. */
+GF_API size_t gf_streams_kv_bytes_per_step(const gf_streams* streams);
+
 /* ---- drafter proposal law: the device sampler of Gemma3DraftPlan::propose and the receipts
  * Gemma3DraftPlan::gather reads (src/engine/gemma3_draft.mm:995-1167,1528-1581; kernels :191-294).
  * Compact law (temperature > 0 and 1 <= top_k <= 64, or a greedy drafter): support = every token whose
