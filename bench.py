@@ -4,6 +4,7 @@ decode (one drafted token, two-row verification, lossless acceptance), on synthe
 weights of those geometries.
 
     python bench.py [--gpus N] [--steps K] [--warmup W] [--impl ours|reference]
+    python bench.py --workload streams [--streams S] [--prefix P] [--steps K] [--gpus N]
     python bench.py --case matmul <dtype 8|12|14> <K> <N> <rows> [launches]
     python bench.py --case attention <cached rows> <rows> <heads> <kv_heads> <window> <kv_f16 0|1> [launches]
     python bench.py --case prefill <12b|270m> <tokens> [tensor path 0|1]
@@ -22,6 +23,13 @@ device time.
 `--impl reference` times the reference's own CPU matmul (its compiled sources, one call per
 column slice on every host core) on a bounded sample of the same cycle and scales it by
 multiply-add count; where the compiled reference is absent it times the CPU restatement instead.
+
+`--workload streams` is the second workload of the list (configs[4]): the Gemma-2-9B geometry (Q4_K body,
+Q8_0 head, binary16 cache, softcaps), S independent conversation streams per GPU that share one replica of
+the weights, each with a P-token seeded prefix ingested through the tensor-core prompt path, then K greedy
+decode steps for all streams; streams are spread over the ranks with no collective.  Its line reports
+whole-job decode tok/s and the HBM bytes a step reads (weights once per group of eight streams, every
+stream's cache once).
 
 `--case` runs one small single-kernel case a few times through the C ABI: the command to put
 under a profiler.
@@ -309,7 +317,7 @@ def run_ours(args) -> dict:
         "data": "synthetic",
         "config": {"workload": "configs[3]: Gemma-3-12B Q4_K_M + 270M Q8_0 drafter, H1, context 2048, T=0.7 top-k 40 "
                                "top-p 0.95 min-p 0.05, 2-row verification, seeded Bernoulli(0.7) accept schedule",
-                   "schedule": {None: "decode pass kernel (default)", 0: "kernel per operator", 1: "decode pass kernel",
+                   "schedule": {None: "kernel per operator (default)", 0: "kernel per operator", 1: "decode pass kernel",
                                 2: "decode pass kernel, attention launched separately"}[args.schedule],
                    "streams_per_gpu": 1, "parallelism": f"independent streams x{world} (no collective)",
                    "l2_policy": "inputs larger than L2: every pass streams 7.3 GB of distinct weights",
@@ -342,6 +350,91 @@ def run_ours(args) -> dict:
     if world == 1 and not args.no_cpu_baseline:
         result["cpu_baseline"], result["parity"] = cpu_baseline_with_parity(target)
     return result
+
+
+def run_streams(args) -> dict:
+    """configs[4]: independent streams of the Gemma-2-9B geometry, data parallel over the ranks."""
+    from guffin_b200 import lib, model as gm, synthetic as syn
+    world, rank, local = distributed()
+    dist = None
+    if world > 1:
+        import torch
+        import torch.distributed as dist
+        torch.cuda.set_device(local)
+        dist.init_process_group("nccl", device_id=torch.device("cuda", local))
+    L = lib.load()
+    lib.check(L.gf_set_device(local))
+    name = "gemma2-9b"
+    config = syn.model_config(name)
+    per_gpu, prefix = args.streams, args.prefix
+    steps, warmup = args.steps, max(args.warmup, 3)
+    context = prefix + warmup + steps + 8
+    t0 = time.time()
+    plan = gm.Model(config, syn.iter_model_weights(name, SEEDS["target"]), context, PREFILL_ROWS)
+    load_s = time.time() - t0
+    streams = gm.Streams(plan, per_gpu)
+    t0 = time.time()
+    for s in range(per_gpu):
+        tokens = np.random.default_rng(SEEDS["prompt"] + 1000 * rank + s).integers(0, config["vocab"], prefix).astype(np.uint32)
+        streams.prefill(s, tokens)
+    plan.synchronize()
+    prefill_s = time.time() - t0
+
+    def barrier():
+        plan.synchronize()
+        if dist is not None:
+            dist.barrier()
+
+    def step():
+        streams.decode(streams.greedy())            # one selection + readback, then one token per stream
+
+    for _ in range(warmup):
+        step()
+    barrier()
+    launches_before = plan.kernel_launches()
+    kv_bytes = streams.kv_bytes_per_step()
+    start, end = lib.Event(), lib.Event()
+    with ClockSampler(local) as clocks:
+        start.record(plan.stream)
+        wall0 = time.perf_counter()
+        for _ in range(steps):
+            step()
+        end.record(plan.stream)
+        end.synchronize()
+        wall = time.perf_counter() - wall0
+        device_ms = start.elapsed_ms(end)
+    launches = plan.kernel_launches() - launches_before
+    barrier()
+    status = plan.status()
+    produced, produced_e2e, elapsed_ms, e2e_s = aggregate_streams(
+        dist, float(per_gpu * steps), float(per_gpu * steps), device_ms, wall, "cuda" if dist is not None else None)
+    if rank != 0:
+        return {}
+    peak, peak_kind = load_peaks()
+    groups = (per_gpu + PREFILL_ROWS - 1) // PREFILL_ROWS
+    step_bytes = groups * plan.weight_bytes(True) + kv_bytes
+    achieved = step_bytes / (elapsed_ms / steps * 1e-3) / 1e9
+    return {
+        "metric": "Gemma-2-9B Q4_K decode tok/s, independent streams (whole job)",
+        "value": produced / (elapsed_ms * 1e-3), "unit": "tok/s", "n_gpus": world, "steps": steps, "warmup": warmup,
+        "ms_per_step": elapsed_ms / steps, "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
+        "dtype": "u4/u8 blocks -> f32, binary16 cache", "data": "synthetic",
+        "config": {"workload": f"configs[4]: Gemma-2-9B Q4_K body + Q8_0 head, {per_gpu} independent streams per GPU, "
+                               f"{prefix}-token seeded prefixes (tensor-core ingestion), greedy decode",
+                   "streams_per_gpu": per_gpu, "streams": per_gpu * world, "prefix": prefix,
+                   "parallelism": f"independent streams x{world} ranks (no collective)",
+                   "l2_policy": "inputs larger than L2: a step streams the weights once per group of eight streams and every stream's cache",
+                   "load_s": round(load_s, 1), "prefill_s": round(prefill_s, 2),
+                   "prefill_tok_s": round(per_gpu * prefix / prefill_s, 1), "status_word": int(status)},
+        "e2e": {"value": produced_e2e / e2e_s, "unit": "tok/s", "h2d_bytes_per_step": per_gpu * (4 + 264),
+                "d2h_bytes_per_step": per_gpu * 3080, "ms_per_step": e2e_s * 1e3 / steps},
+        "gpu_launches": int(launches),
+        "roofline": {"bound": "hbm", "achieved": achieved, "peak": peak, "unit": "GB/s", "frac": achieved / peak,
+                     "peak_source": f"of {peak_kind}", "traffic": None,
+                     "kernel": "one decode step: weight_stream_kernel per group of streams + stream attention over every cache",
+                     "step_bytes": step_bytes, "kv_bytes": kv_bytes, "weight_passes": groups},
+        "clocks": clocks.summary(),
+    }
 
 
 # ----------------------------------------------------------------------------------------- CPU arm
@@ -589,13 +682,20 @@ def main():
     parser.add_argument("--no-cpu-baseline", action="store_true", help="skip the CPU baseline / parity leg of the default arm")
     parser.add_argument("--no-shapes", action="store_true", help="skip the per-shape GB/s table of the default arm")
     parser.add_argument("--schedule", type=int, choices=(0, 1, 2), default=None,
-                        help="0: one kernel per operator (CUDA graph); 1: persistent decode pass kernel (default); "
+                        help="0: one kernel per operator (CUDA graph, the default); 1: persistent decode pass kernel; "
                              "2: pass kernel with attention launched separately")
     parser.add_argument("--case", nargs="+", default=None, help="run one single-kernel case instead of the benchmark")
+    parser.add_argument("--workload", choices=("h1", "streams"), default="h1", help="h1: the headline (configs[3]); streams: configs[4]")
+    parser.add_argument("--streams", type=int, default=8, help="streams per GPU of the streams workload (64 over eight GPUs)")
+    parser.add_argument("--prefix", type=int, default=8192, help="prefix tokens per stream of the streams workload")
     args = parser.parse_args()
     if args.case:
         sys.exit(run_case(args.case))
-    if args.impl == "reference":
+    if args.workload == "streams" and args.impl == "ours":
+        args.steps = 64 if args.steps is None else args.steps
+        args.warmup = 3 if args.warmup is None else args.warmup
+        result = run_streams(args)
+    elif args.impl == "reference":
         args.steps = 3 if args.steps is None else args.steps
         args.warmup = 2 if args.warmup is None else args.warmup
         result = run_reference(args)
