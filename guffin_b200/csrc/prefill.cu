@@ -177,9 +177,10 @@ __device__ __forceinline__ void mbar_arrive(uint64_t* bar) {
 // Warp-specialised, no block-wide barrier in the loop.  Warps 0..15 dequantise: two warps share a column pair
 // of the tile, a lane takes one column of one lane slot; for every 64-element K block they wait until the
 // stage is free, write their part of the bf16 weight tile and arrive on the stage's "written" barrier.  One
-// thread of warp 16 requests the copies (packed weights two K units ahead, activation blocks two stages
-// ahead) and, once a stage's activations have landed and its weights are written, issues the four
-// tensor-core products of the stage; their completion frees the stage.  Every wait is bounded and gives up
+// thread of warp 17 requests the copies (packed weights two K units ahead, activation blocks two stages
+// ahead); one thread of warp 16, once a stage's activations have landed and its weights are written, issues
+// the four tensor-core products of the stage; their completion frees the stage.  (With one thread doing
+// both, its serial waits, copy requests and issues took longer per stage than the dequantisation.)  Every wait is bounded and gives up
 // early once any warp has; the CTA always reaches the end, releases its tensor memory and sets the error word.
 __global__ void __launch_bounds__(kPrefillThreads, 1) prefill_gemm_kernel(const __grid_constant__ PrefillGemmParams p) {
     extern __shared__ __align__(1024) uint8_t smem[];
@@ -222,7 +223,8 @@ __global__ void __launch_bounds__(kPrefillThreads, 1) prefill_gemm_kernel(const 
     const uint32_t tmem = tmem_slot;
     bool ok = true;
 
-    if (warp == kDequantWarps) {
+    if (warp == kDequantWarps + 1u) {
+        // The copy warp: packed weights two K units ahead, activation blocks kAhead stages ahead.
         if (lane == 0) {
             uint32_t requested_units = 0, requested_blocks = 0;
             auto request_weights = [&](uint32_t j) {          // j counts this split's units
@@ -242,7 +244,7 @@ __global__ void __launch_bounds__(kPrefillThreads, 1) prefill_gemm_kernel(const 
             for (uint32_t j = 0; j < 2u && j < unit_count; ++j) request_weights(j);
             for (uint32_t step = 0; step < kAhead && step < steps; ++step) request_block(step);
             for (uint32_t step = 0; step < steps && ok; ++step) {
-                const uint32_t stage = step % kStages, use = step / kStages, j = step / subs;
+                const uint32_t j = step / subs;
                 if (step % subs == 0u && j + 2u < unit_count) {
                     // The buffer two units on held unit j - 1: every dequantising warp must be done with it.
                     if (j >= 1u && !wait_or_abort(&weight_free[(j + 2u) % kWeightBufs], ((j - 1u) / kWeightBufs) & 1u, abort)) { ok = false; break; }
@@ -253,19 +255,12 @@ __global__ void __launch_bounds__(kPrefillThreads, 1) prefill_gemm_kernel(const 
                     if (next_use > 0u && !wait_or_abort(&stage_free[next % kStages], (next_use - 1u) & 1u, abort)) { ok = false; break; }
                     request_block(next);
                 }
-                if (!wait_or_abort(&a_full[stage], use & 1u, abort) || !wait_or_abort(&b_full[stage], use & 1u, abort)) { ok = false; break; }
-                tc_fence_after_sync();
-                const uint32_t a_address = smem_u32(smem + kOffA + stage * kAStageBytes), b_address = smem_u32(smem + kOffB + stage * kBStageBytes);
-#pragma unroll
-                for (uint32_t kk = 0; kk < kPrefillBlockK / 16u; ++kk)
-                    mma_bf16(tmem, operand_descriptor(a_address + kk * 256u), operand_descriptor(b_address + kk * 256u),
-                             (step | kk) != 0u ? 1u : 0u);
-                mma_commit(&stage_free[stage]);
             }
-            if (ok) mma_commit(done_bar);
-            else {
+            // Whether this warp gave up or another did: copies already requested get a bounded chance to
+            // land before the shared memory is released (after a clean run every copy has been consumed).
+            if (!ok || !wait_or_abort(done_bar, 0u, abort)) {
+                ok = false;
                 abort_flag = 1u;
-                // Copies already requested get a bounded chance to land before the shared memory is released.
                 for (uint32_t j = 0; j < unit_count; ++j) {
                     if (j + kWeightBufs < requested_units) continue;
                     if (j >= requested_units) break;
@@ -277,6 +272,24 @@ __global__ void __launch_bounds__(kPrefillThreads, 1) prefill_gemm_kernel(const 
                     mbar_wait(&a_full[step % kStages], (step / kStages) & 1u, 1u << 16);
                 }
             }
+        }
+    } else if (warp == kDequantWarps) {
+        // The issuing warp: once a stage's activations have landed and its weights are written, the four
+        // tensor-core products of the stage; their completion frees the stage.
+        if (lane == 0) {
+            for (uint32_t step = 0; step < steps && ok; ++step) {
+                const uint32_t stage = step % kStages, use = step / kStages;
+                if (!wait_or_abort(&a_full[stage], use & 1u, abort) || !wait_or_abort(&b_full[stage], use & 1u, abort)) { ok = false; break; }
+                tc_fence_after_sync();
+                const uint32_t a_address = smem_u32(smem + kOffA + stage * kAStageBytes), b_address = smem_u32(smem + kOffB + stage * kBStageBytes);
+#pragma unroll
+                for (uint32_t kk = 0; kk < kPrefillBlockK / 16u; ++kk)
+                    mma_bf16(tmem, operand_descriptor(a_address + kk * 256u), operand_descriptor(b_address + kk * 256u),
+                             (step | kk) != 0u ? 1u : 0u);
+                mma_commit(&stage_free[stage]);
+            }
+            if (ok) mma_commit(done_bar);
+            else abort_flag = 1u;
         }
     } else {
         // Dequantisation: warp w takes column pair w % 8 of the tile and the column g + 8 * (w / 8) of each lane slot.

@@ -20,7 +20,7 @@ namespace gf {
 constexpr uint32_t kPrefillRows = 128;          // rows of one chunk = M of the tensor-core instruction
 constexpr uint32_t kPrefillTile = 128;          // output columns per CTA
 constexpr uint32_t kPrefillBlockK = 64;         // K elements per shared-memory stage
-constexpr uint32_t kPrefillThreads = 544;          // sixteen dequantising warps and the warp that issues copies and products
+constexpr uint32_t kPrefillThreads = 576;          // sixteen dequantising warps, the warp that issues the products and the warp that requests the copies
 constexpr uint32_t kPrefillBlockBytes = kPrefillRows * kPrefillBlockK * 2u;      // one tile-major activation block
 
 // Byte offset of element (row, k) in a tile-major bf16 activation buffer.
