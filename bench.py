@@ -373,6 +373,8 @@ def run_streams(args) -> dict:
     plan = gm.Model(config, syn.iter_model_weights(name, SEEDS["target"]), context, PREFILL_ROWS)
     load_s = time.time() - t0
     streams = gm.Streams(plan, per_gpu)
+    if args.tensor_decode:
+        streams.set_mode(1)
     t0 = time.time()
     for s in range(per_gpu):
         tokens = np.random.default_rng(SEEDS["prompt"] + 1000 * rank + s).integers(0, config["vocab"], prefix).astype(np.uint32)
@@ -411,7 +413,7 @@ def run_streams(args) -> dict:
     if rank != 0:
         return {}
     peak, peak_kind = load_peaks()
-    groups = (per_gpu + PREFILL_ROWS - 1) // PREFILL_ROWS
+    groups = 1 if args.tensor_decode else (per_gpu + PREFILL_ROWS - 1) // PREFILL_ROWS
     step_bytes = groups * plan.weight_bytes(True) + kv_bytes
     achieved = step_bytes / (elapsed_ms / steps * 1e-3) / 1e9
     return {
@@ -422,6 +424,8 @@ def run_streams(args) -> dict:
         "config": {"workload": f"configs[4]: Gemma-2-9B Q4_K body + Q8_0 head, {per_gpu} independent streams per GPU, "
                                f"{prefix}-token seeded prefixes (tensor-core ingestion), greedy decode",
                    "streams_per_gpu": per_gpu, "streams": per_gpu * world, "prefix": prefix,
+                   "decode_projections": "one bf16 tensor-core pass over all streams" if args.tensor_decode
+                   else "exact row passes in groups of eight streams",
                    "parallelism": f"independent streams x{world} ranks (no collective)",
                    "l2_policy": "inputs larger than L2: a step streams the weights once per group of eight streams and every stream's cache",
                    "load_s": round(load_s, 1), "prefill_s": round(prefill_s, 2),
@@ -688,6 +692,8 @@ def main():
     parser.add_argument("--workload", choices=("h1", "streams"), default="h1", help="h1: the headline (configs[3]); streams: configs[4]")
     parser.add_argument("--streams", type=int, default=8, help="streams per GPU of the streams workload (64 over eight GPUs)")
     parser.add_argument("--prefix", type=int, default=8192, help="prefix tokens per stream of the streams workload")
+    parser.add_argument("--tensor-decode", action="store_true",
+                        help="streams workload: every step as one bf16 tensor-core pass over all streams instead of exact row passes")
     args = parser.parse_args()
     if args.case:
         sys.exit(run_case(args.case))

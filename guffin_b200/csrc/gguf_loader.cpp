@@ -202,8 +202,18 @@ extern "C" int gf_model_load_gguf(gf_model* model, const char* path, uint32_t* o
             return fail(GF_ERR_INVALID, "gf_model_load_gguf: tensor %s lies outside the file", e.name.c_str());
         bindings.push_back(Binding{&e, known, layer, elements});
     }
+    // Source I/O of the next tensor overlaps the upload and repack of the current one (the reference hints
+    // the next block's byte range the same way, gemma2_metal_plan.cpp:427-461).
+    auto read_ahead = [&](const Binding& binding) {
+        const uint64_t begin = data_start + binding.entry->offset, bytes = tensor_bytes(binding.entry->type, binding.elements);
+        const uint64_t page = 4096u, first = begin & ~(page - 1u);
+        madvise(const_cast<uint8_t*>(file.data) + first, (size_t)(begin + bytes - first), MADV_WILLNEED);
+    };
     uint32_t bound = 0;
-    for (const Binding& binding : bindings) {
+    for (size_t index = 0; index < bindings.size(); ++index) {
+        const Binding& binding = bindings[index];
+        if (index == 0) read_ahead(binding);
+        if (index + 1 < bindings.size()) read_ahead(bindings[index + 1]);
         const Entry& e = *binding.entry;
         const uint8_t* payload = file.data + data_start + e.offset;
         int status;

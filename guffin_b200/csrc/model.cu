@@ -24,6 +24,7 @@ Model::Model(const gf_model_config& config) : config_(config) {
 }
 
 Model::~Model() {
+    release_stager();
     for (auto& per_rows : graphs_)
         for (auto& graph : per_rows)
             if (graph) cudaGraphExecDestroy(graph);
@@ -51,6 +52,65 @@ static int device_alloc(std::vector<void*>& owner, T** out, size_t count) {
     owner.push_back(p);
     *out = static_cast<T*>(p);
     return GF_OK;
+}
+
+// Copies `bytes` of native blocks into a device staging buffer without blocking on the device: the host
+// fills one pinned chunk while the other is in flight; the staging buffer alternates between tensors, and is
+// only overwritten once the repack that read it has finished.
+int Model::stage_upload(const void* native_host, size_t bytes, uint8_t** out_staging, uint32_t* out_slot) {
+    WeightStager& st = stager_;
+    if (!st.ready) {
+        GF_CUDA(cudaStreamCreateWithFlags(&st.copy_stream, cudaStreamNonBlocking));
+        for (int i = 0; i < 2; ++i) {
+            GF_CUDA(cudaHostAlloc(reinterpret_cast<void**>(&st.pinned[i]), WeightStager::kChunkBytes, cudaHostAllocDefault));
+            GF_CUDA(cudaEventCreateWithFlags(&st.chunk_done[i], cudaEventDisableTiming));
+            GF_CUDA(cudaEventCreateWithFlags(&st.uploaded[i], cudaEventDisableTiming));
+            GF_CUDA(cudaEventCreateWithFlags(&st.packed[i], cudaEventDisableTiming));
+        }
+        st.ready = true;
+    }
+    const uint32_t slot = st.next;
+    st.next ^= 1u;
+    if (bytes > st.staging_bytes[slot]) {
+        GF_CUDA(cudaEventSynchronize(st.packed[slot]));          // nothing reads the old buffer any more
+        if (st.staging[slot]) GF_CUDA(cudaFree(st.staging[slot]));
+        st.staging[slot] = nullptr;
+        st.staging_bytes[slot] = 0;
+        GF_CUDA(cudaMalloc(reinterpret_cast<void**>(&st.staging[slot]), bytes));
+        st.staging_bytes[slot] = bytes;
+    }
+    GF_CUDA(cudaStreamWaitEvent(st.copy_stream, st.packed[slot], 0));
+    const uint8_t* src = static_cast<const uint8_t*>(native_host);
+    for (size_t done = 0; done < bytes; done += WeightStager::kChunkBytes) {
+        const size_t part = std::min(WeightStager::kChunkBytes, bytes - done);
+        const uint32_t c = st.chunk;
+        st.chunk ^= 1u;
+        GF_CUDA(cudaEventSynchronize(st.chunk_done[c]));
+        std::memcpy(st.pinned[c], src + done, part);
+        GF_CUDA(cudaMemcpyAsync(st.staging[slot] + done, st.pinned[c], part, cudaMemcpyHostToDevice, st.copy_stream));
+        GF_CUDA(cudaEventRecord(st.chunk_done[c], st.copy_stream));
+    }
+    GF_CUDA(cudaEventRecord(st.uploaded[slot], st.copy_stream));
+    GF_CUDA(cudaStreamWaitEvent(stream_, st.uploaded[slot], 0));
+    *out_staging = st.staging[slot];
+    *out_slot = slot;
+    return GF_OK;
+}
+
+void Model::release_stager() {
+    WeightStager& st = stager_;
+    if (!st.ready) return;
+    if (st.copy_stream) cudaStreamSynchronize(st.copy_stream);
+    if (stream_) cudaStreamSynchronize(stream_);
+    for (int i = 0; i < 2; ++i) {
+        if (st.pinned[i]) cudaFreeHost(st.pinned[i]);
+        if (st.staging[i]) cudaFree(st.staging[i]);
+        if (st.chunk_done[i]) cudaEventDestroy(st.chunk_done[i]);
+        if (st.uploaded[i]) cudaEventDestroy(st.uploaded[i]);
+        if (st.packed[i]) cudaEventDestroy(st.packed[i]);
+    }
+    if (st.copy_stream) cudaStreamDestroy(st.copy_stream);
+    st = WeightStager();
 }
 
 int launch_quantize_f16_q8_0(const void* f16_dev, uint64_t block_count, void* q8_dev, uint32_t* status_dev, cudaStream_t stream);
@@ -137,10 +197,25 @@ int Model::set_matrix(int kind, uint32_t layer, int dtype, const void* native_ho
     if (packed == 0) return GF_ERR_INVALID;
     const size_t source = (size_t)n * (k / block_elements(dtype)) * block_bytes(dtype);
     const size_t native = (size_t)n * (k / block_elements(stored)) * block_bytes(stored);
-    // Staging: the source blocks, then (requantised binding) the converted blocks and a status word.
+    if (!requantize) {
+        // The common case: upload through the pinned pipeline, repack on the plan's stream, no wait here.
+        uint8_t* data = nullptr;
+        GF_TRY(device_alloc(allocations_, &data, packed));
+        uint8_t* staged = nullptr;
+        uint32_t slot = 0;
+        GF_TRY(stage_upload(native_host, source, &staged, &slot));
+        GF_TRY(gf_pack_weight(dtype, staged, k, n, data, stream_));
+        GF_CUDA(cudaEventRecord(stager_.packed[slot], stream_));
+        *dst = PackedMatrix{stored, k, n, data, packed, native};
+        weight_bytes_ += packed;
+        native_weight_bytes_ += native;
+        if (kind == GF_MAT_OUTPUT) has_head_ = true;
+        return GF_OK;
+    }
+    // Staging: the source blocks, then the converted blocks and a status word.
     const size_t converted_at = (source + 15u) & ~(size_t)15u, flag_at = converted_at + ((native + 15u) & ~(size_t)15u);
     uint8_t* staging = nullptr;
-    GF_CUDA(cudaMalloc(&staging, requantize ? flag_at + 16u : source));
+    GF_CUDA(cudaMalloc(&staging, flag_at + 16u));
     uint8_t* data = nullptr;
     int status = device_alloc(allocations_, &data, packed);
     if (status == GF_OK) status = check_cuda(cudaMemcpyAsync(staging, native_host, source, cudaMemcpyHostToDevice, stream_), "upload");
@@ -197,6 +272,7 @@ int Model::finalize() {
     if (c.context == 0 || c.heads % c.kv_heads) return fail(GF_ERR_INVALID, "bad context or head geometry");
     if (!token_embd_.data || !output_norm_) return fail(GF_ERR_STATE, "token embedding or output norm missing");
     if (!stream_) GF_CUDA(cudaStreamCreateWithFlags(&stream_, cudaStreamNonBlocking));
+    release_stager();          // waits for the last uploads and repacks, frees the staging buffers
     // A binary16 embedding cannot serve as the head: the tied head is its Q8_0 quantisation
     // (resolve_gemma_output_head_policy, gemma2_metal_plan.cpp:799-828).
     if (token_embd_.dtype == GF_F16 && !has_head_) GF_TRY(bind_q8_head_from_f16(token_embd_.data, token_embd_.k, token_embd_.n));

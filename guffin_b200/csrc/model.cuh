@@ -52,9 +52,16 @@ struct StreamSet {
     uint32_t* positions_dev = nullptr;                     // [count]
     StreamRings* rings_dev = nullptr;                      // [layer][count]
     StreamPublishLayer* publish_layers_dev = nullptr;      // [layer]: the plan's private rows
-    float* logits = nullptr;                               // [count][vocab]
+    StreamPublishLayer* wide_publish_layers_dev = nullptr; // [layer]: the private rows of the 128-row arena (tensor-core steps)
+    float* logits = nullptr;                               // [max(count, 128)][vocab]
+    int mode = 0;                                          // 0: exact row passes in groups; 1: one tensor-core pass over all streams
+    cudaGraphExec_t wide_graph = nullptr;
+    uint32_t wide_launches = 0;
     void *candidates_ws = nullptr, *requests_dev = nullptr, *results_dev = nullptr, *requests_pinned = nullptr;
     std::vector<void*> allocations;
+    // One recorded CUDA graph per group of streams (a group's pointers are fixed): [group] -> executable, rows.
+    std::vector<cudaGraphExec_t> group_graphs;
+    std::vector<uint32_t> group_launches;
     ~StreamSet();
 };
 
@@ -109,6 +116,7 @@ public:
     int streams_create(uint32_t count, StreamSet** out);
     int streams_prefill(StreamSet& set, uint32_t stream, const uint32_t* tokens_host, uint32_t count);
     int streams_decode(StreamSet& set, const uint32_t* tokens_host);
+    int streams_set_mode(StreamSet& set, int mode);
     int streams_select(StreamSet& set, const void* requests_host);
     int streams_read_candidates(StreamSet& set, void* results_host);
     int streams_read_logits(StreamSet& set, uint32_t stream, float* host);
@@ -136,6 +144,7 @@ private:
     int bind_q8_head_from_f16(const void* f16_dev, uint64_t k, uint64_t n);
     int bind_rings(const std::vector<void*>& ring_k, const std::vector<void*>& ring_v, uint32_t position);
     int encode_stream_group(StreamSet& set, uint32_t first, uint32_t rows);
+    int encode_stream_batch(StreamSet& set);
     int encode_blocks(uint32_t rows, uint32_t flags);
     int run_gemv(struct GemvLaunch& launch, uint32_t rows);
     int emit_embedding(uint32_t rows, float scale);
@@ -163,6 +172,25 @@ private:
     } prefill_;
     bool tensor_prefill_ = true;
     uint32_t prefill_logits_row_ = 0;
+
+    // Weight upload at load time: native blocks travel through two pinned host chunks into one of two device
+    // staging buffers on a copy stream, while the repack of the previous tensor runs on the plan's stream
+    // (the reference overlaps source I/O of the next block with packing of the current one,
+    // gemma2_metal_plan.cpp:427-461).  Released by finalize().
+    struct WeightStager {
+        static constexpr size_t kChunkBytes = 32u << 20;
+        cudaStream_t copy_stream = nullptr;
+        uint8_t* pinned[2] = {nullptr, nullptr};
+        cudaEvent_t chunk_done[2] = {nullptr, nullptr};       // the chunk's device copy has read the pinned buffer
+        uint8_t* staging[2] = {nullptr, nullptr};
+        size_t staging_bytes[2] = {0, 0};
+        cudaEvent_t uploaded[2] = {nullptr, nullptr};         // the tensor is complete in staging[i]
+        cudaEvent_t packed[2] = {nullptr, nullptr};           // the repack has finished reading staging[i]
+        uint32_t next = 0, chunk = 0;
+        bool ready = false;
+    } stager_;
+    int stage_upload(const void* native_host, size_t bytes, uint8_t** out_staging, uint32_t* out_slot);
+    void release_stager();
 
     gf_model_config config_;
     bool finalized_ = false, use_graph_ = true, poisoned_ = false;

@@ -184,7 +184,8 @@ __global__ void __launch_bounds__(128) stream_publish_kernel(const StreamPublish
 }
 
 __global__ void advance_positions_kernel(uint32_t* positions, uint32_t rows) {
-    if (threadIdx.x < rows) positions[threadIdx.x] += 1u;
+    const uint32_t i = blockIdx.x * blockDim.x + threadIdx.x;
+    if (i < rows) positions[i] += 1u;
 }
 
 // ------------------------------------------------------------------ GeGLU, KV publication
@@ -342,11 +343,11 @@ int launch_stream_attention(const AttentionParams& params, const StreamRings* ri
 
 int launch_stream_publish(const StreamPublishLayer* layers_dev, uint32_t layer_count, const StreamRings* rings_dev, uint32_t stride,
                           uint32_t* positions_dev, uint32_t rows, cudaStream_t stream) {
-    if (!layers_dev || !rings_dev || !positions_dev || rows == 0 || rows > 32u) return fail(GF_ERR_INVALID, "stream publish: bad arguments");
+    if (!layers_dev || !rings_dev || !positions_dev || rows == 0) return fail(GF_ERR_INVALID, "stream publish: bad arguments");
     const int status = launch_kernel(stream_publish_kernel, dim3(rows, layer_count), dim3(128), 0, stream, false, layers_dev, rings_dev,
                                      stride, (const uint32_t*)positions_dev);
     if (status != GF_OK) return status;
-    return launch_kernel(advance_positions_kernel, dim3(1), dim3(32), 0, stream, false, positions_dev, rows);
+    return launch_kernel(advance_positions_kernel, dim3((rows + 127u) / 128u), dim3(128), 0, stream, false, positions_dev, rows);
 }
 
 int launch_attention(const AttentionParams& p, cudaStream_t stream, bool pdl) {

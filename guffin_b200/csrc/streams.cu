@@ -26,6 +26,8 @@ int launch_candidates(const float* logits, uint32_t rows, uint32_t vocab, float 
                       void* workspace, void* results, cudaStream_t stream, bool pdl);
 
 StreamSet::~StreamSet() {
+    for (cudaGraphExec_t exec : group_graphs) if (exec) cudaGraphExecDestroy(exec);
+    if (wide_graph) cudaGraphExecDestroy(wide_graph);
     for (void* p : allocations) cudaFree(p);
     if (requests_pinned) cudaFreeHost(requests_pinned);
 }
@@ -69,7 +71,7 @@ int Model::streams_create(uint32_t count, StreamSet** out) {
     GF_TRY(stream_alloc(*set, &set->rings_dev, rings.size()));
     GF_TRY(stream_alloc(*set, &set->publish_layers_dev, layers.size()));
     GF_TRY(stream_alloc(*set, &set->positions_dev, count));
-    GF_TRY(stream_alloc(*set, &set->logits, (size_t)count * c.vocab));
+    GF_TRY(stream_alloc(*set, &set->logits, (size_t)std::max(count, kPrefillRows) * c.vocab));      // a tensor-core step writes 128 rows
     uint8_t* bytes = nullptr;
     GF_TRY(stream_alloc(*set, &bytes, candidates_workspace_bytes(count, c.vocab))); set->candidates_ws = bytes;
     GF_TRY(stream_alloc(*set, &bytes, (size_t)count * gf_selection_request_bytes())); set->requests_dev = bytes;
@@ -204,6 +206,109 @@ int Model::encode_stream_group(StreamSet& set, uint32_t first, uint32_t rows) {
     return GF_OK;
 }
 
+// A step's other form: every stream of the set (up to 128) in ONE pass whose projections are the prompt path's
+// bf16 tensor-core GEMMs, so the weights are read and dequantised once per step however many streams there
+// are.  Results differ from the exact row passes by the bf16 rounding of activations and weights (about 1e-2
+// relative L2 on logits), which is why it is a mode the caller chooses.
+int Model::streams_set_mode(StreamSet& set, int mode) {
+    if (mode != 0 && mode != 1) return fail(GF_ERR_INVALID, "stream decode mode %d (0: exact row passes, 1: one tensor-core pass)", mode);
+    if (mode == 1) {
+        if (set.count > kPrefillRows) return fail(GF_ERR_INVALID, "a tensor-core step holds at most %u streams", kPrefillRows);
+        const gf_model_config& c = config_;
+        if ((has_head_ ? head_ : token_embd_).n % kPrefillTile) return fail(GF_ERR_INVALID, "the tensor-core head needs a vocabulary that is a multiple of %u", kPrefillTile);
+        GF_TRY(ensure_prefill_arena());
+        if (!set.wide_publish_layers_dev) {
+            const size_t element = c.kv_f16 ? 2 : 4, kvw = (size_t)c.kv_heads * c.head_dim;
+            std::vector<StreamPublishLayer> layers(c.layers);
+            for (uint32_t l = 0; l < c.layers; ++l)
+                layers[l] = StreamPublishLayer{static_cast<const uint8_t*>(prefill_.private_k[l]), static_cast<const uint8_t*>(prefill_.private_v[l]),
+                                               caches_[l].ring_rows - 1u, (uint32_t)(kvw * element)};
+            GF_TRY(stream_alloc(set, &set.wide_publish_layers_dev, layers.size()));
+            GF_CUDA(cudaMemcpyAsync(set.wide_publish_layers_dev, layers.data(), layers.size() * sizeof(StreamPublishLayer), cudaMemcpyHostToDevice, stream_));
+            GF_CUDA(cudaStreamSynchronize(stream_));
+        }
+    }
+    set.mode = mode;
+    return GF_OK;
+}
+
+int Model::encode_stream_batch(StreamSet& set) {
+    const gf_model_config& c = config_;
+    PrefillArena& a = prefill_;
+    const uint32_t rows = set.count, qw = c.heads * c.head_dim;
+    GF_TRY(launch_embedding(token_embd_.dtype, token_embd_.data, c.hidden, c.vocab, a.tokens, rows, sqrtf((float)c.hidden), a.residual,
+                            status_dev_, stream_, false));
+    launches_ += 1;
+    auto gemm = [&](std::initializer_list<std::pair<const PackedMatrix*, float*>> matrices, const void* operand, uint64_t k, uint32_t splits = 1) -> int {
+        PrefillGemmLaunch launch;
+        launch.count = 0;
+        launch.splits = splits;
+        for (const auto& entry : matrices) launch.matrices[launch.count++] = {entry.first->dtype, entry.first->data, entry.second, entry.first->n};
+        launch.k = k;
+        launch.a = operand;
+        ++launches_;
+        return launch_prefill_gemm(launch, error_flag_, stream_);
+    };
+    uint32_t down_splits = 1;
+    for (uint32_t l = 0; l < c.layers; ++l) {
+        const LayerWeights& w = layers_[l];
+        const LayerCache& cache = caches_[l];
+        if (l == 0) GF_TRY(launch_prefill_norm(a.residual, 1, nullptr, nullptr, w.attn_norm, nullptr, a.a_hidden, rows, c.hidden, c.rms_eps, 0, stream_));
+        else GF_TRY(launch_prefill_norm(a.projected, down_splits, a.residual2, layers_[l - 1].post_ffw_norm, w.attn_norm, a.residual, a.a_hidden, rows,
+                                        c.hidden, c.rms_eps, 1, stream_));
+        if (unit_elements(w.q.dtype) == unit_elements(w.v.dtype)) {
+            const uint32_t splits = prefill_gemm_splits(w.q.n + w.k.n + w.v.n, c.hidden, w.q.dtype);
+            GF_TRY(gemm({{&w.q, a.raw_q}, {&w.k, a.raw_k}, {&w.v, a.raw_v}}, a.a_hidden, c.hidden, splits));
+            float* parts[3] = {a.raw_q, a.raw_k, a.raw_v};
+            const uint64_t widths[3] = {w.q.n, w.k.n, w.v.n};
+            GF_TRY(launch_prefill_reduce(parts, widths, 3, splits, rows, stream_));
+        } else {
+            GF_TRY(gemm({{&w.q, a.raw_q}, {&w.k, a.raw_k}}, a.a_hidden, c.hidden));
+            GF_TRY(gemm({{&w.v, a.raw_v}}, a.a_hidden, c.hidden));
+        }
+        RopeStoreParams rp{a.raw_q, a.raw_k, a.raw_v, c.uses_qk_norm ? w.q_norm : nullptr, c.uses_qk_norm ? w.k_norm : nullptr, a.query,
+                           a.private_k[l], a.private_v[l], state_dev_, status_dev_, cache.rope_divisors, rows, c.heads, c.kv_heads,
+                           c.head_dim, c.rms_eps, cache.rope_base, cache.rope_scale, c.kv_f16};
+        rp.row_positions = set.positions_dev;
+        GF_TRY(launch_rope_store(rp, stream_, false));
+        AttentionParams ap;
+        ap.q = a.query; ap.ring_k = nullptr; ap.ring_v = nullptr; ap.private_k = a.private_k[l]; ap.private_v = a.private_v[l];
+        ap.out = a.attention_out;
+        ap.partial_out = static_cast<float*>(a.attention_ws);
+        ap.partial_ml = ap.partial_out + (size_t)kPrefillRows * c.heads * kMaxAttentionPartitions * 256u;
+        ap.counters = attention_counters(a.attention_ws, kPrefillRows, c.heads);
+        ap.base_position = set.positions_dev; ap.rows = rows; ap.heads = c.heads; ap.kv_heads = c.kv_heads; ap.head_dim = c.head_dim;
+        ap.ring_mask = cache.ring_rows - 1u; ap.window = cache.window; ap.scale = c.attention_scale;
+        ap.softcap = c.attn_softcap; ap.kv_f16 = c.kv_f16;
+        GF_TRY(launch_stream_attention(ap, set.rings_dev + (size_t)l * set.count, set.positions_dev, stream_));
+        GF_TRY(launch_prefill_pack(a.attention_out, a.a_q, rows, qw, stream_));
+        const uint32_t o_splits = prefill_gemm_splits(w.o.n, w.o.k, w.o.dtype);
+        GF_TRY(gemm({{&w.o, a.projected}}, a.a_q, qw, o_splits));
+        GF_TRY(launch_prefill_norm(a.projected, o_splits, a.residual, w.post_attention_norm, w.ffn_norm, a.residual2, a.a_hidden, rows, c.hidden,
+                                   c.rms_eps, 1, stream_));
+        uint32_t ffn_splits = 1;
+        if (unit_elements(w.gate.dtype) == unit_elements(w.up.dtype)) {
+            ffn_splits = prefill_gemm_splits(w.gate.n + w.up.n, c.hidden, w.gate.dtype);
+            GF_TRY(gemm({{&w.gate, a.gate}, {&w.up, a.up}}, a.a_hidden, c.hidden, ffn_splits));
+        } else {
+            GF_TRY(gemm({{&w.gate, a.gate}}, a.a_hidden, c.hidden));
+            GF_TRY(gemm({{&w.up, a.up}}, a.a_hidden, c.hidden));
+        }
+        GF_TRY(launch_prefill_geglu(a.gate, a.up, ffn_splits, a.a_ffn, rows, c.ffn, stream_));
+        down_splits = prefill_gemm_splits(w.down.n, w.down.k, w.down.dtype);
+        GF_TRY(gemm({{&w.down, a.projected}}, a.a_ffn, c.ffn, down_splits));
+        launches_ += 8;
+    }
+    // Final norm and the head: one GEMM over all rows into the set's logits.
+    GF_TRY(launch_prefill_norm(a.projected, down_splits, a.residual2, layers_[c.layers - 1].post_ffw_norm, output_norm_, a.residual, a.a_hidden, rows,
+                               c.hidden, c.rms_eps, 1, stream_));
+    const PackedMatrix& table = has_head_ ? head_ : token_embd_;
+    GF_TRY(gemm({{&table, set.logits}}, a.a_hidden, c.hidden));
+    GF_TRY(launch_stream_publish(set.wide_publish_layers_dev, c.layers, set.rings_dev, set.count, set.positions_dev, rows, stream_));
+    launches_ += 3;
+    return GF_OK;
+}
+
 // One token per stream for every stream: groups of up to row_capacity streams share a pass over the weights.
 int Model::streams_decode(StreamSet& set, const uint32_t* tokens_host) {
     if (!finalized_) return fail(GF_ERR_STATE, "plan is not finalized");
@@ -213,13 +318,62 @@ int Model::streams_decode(StreamSet& set, const uint32_t* tokens_host) {
         if (tokens_host[s] >= config_.vocab) return fail(GF_ERR_INVALID, "token id %u outside the vocabulary", tokens_host[s]);
         if (set.positions_host[s] >= config_.context) return fail(GF_ERR_INVALID, "stream %u has filled its context (%u)", s, config_.context);
     }
+    if (set.mode == 1) {
+        GF_CUDA(cudaMemcpyAsync(prefill_.tokens, tokens_host, set.count * sizeof(uint32_t), cudaMemcpyHostToDevice, stream_));      // pageable: staged by the driver
+        if (!use_graph_) {
+            GF_TRY(encode_stream_batch(set));
+        } else {
+            if (!set.wide_graph) {
+                const uint32_t before = launches_;
+                cudaGraph_t graph = nullptr;
+                GF_CUDA(cudaStreamBeginCapture(stream_, cudaStreamCaptureModeThreadLocal));
+                const int status = encode_stream_batch(set);
+                const cudaError_t end = cudaStreamEndCapture(stream_, &graph);
+                set.wide_launches = launches_ - before;
+                launches_ = before;
+                if (status != GF_OK) { if (graph) cudaGraphDestroy(graph); return status; }
+                GF_CUDA(end);
+                const cudaError_t inst = cudaGraphInstantiate(&set.wide_graph, graph, 0);
+                cudaGraphDestroy(graph);
+                GF_CUDA(inst);
+            }
+            GF_CUDA(cudaGraphLaunch(set.wide_graph, stream_));
+            launches_ += set.wide_launches;
+        }
+        for (uint32_t s = 0; s < set.count; ++s) ++set.positions_host[s];
+        return GF_OK;
+    }
     for (uint32_t first = 0; first < set.count; first += config_.row_capacity) {
         const uint32_t rows = std::min(config_.row_capacity, set.count - first);
         GF_CUDA(cudaEventSynchronize(tokens_copied_));
         std::memcpy(tokens_pinned_, tokens_host + first, rows * sizeof(uint32_t));
         GF_CUDA(cudaMemcpyAsync(tokens_dev_, tokens_pinned_, rows * sizeof(uint32_t), cudaMemcpyHostToDevice, stream_));
         GF_CUDA(cudaEventRecord(tokens_copied_, stream_));
-        GF_TRY(encode_stream_group(set, first, rows));
+        const uint32_t group = first / config_.row_capacity;
+        if (!use_graph_) {
+            GF_TRY(encode_stream_group(set, first, rows));
+        } else {
+            // The group's pass is recorded once and replayed: every pointer it uses is fixed, and positions
+            // and token ids are read from device memory.
+            if (set.group_graphs.size() <= group) { set.group_graphs.resize(group + 1u, nullptr); set.group_launches.resize(group + 1u, 0u); }
+            cudaGraphExec_t& exec = set.group_graphs[group];
+            if (!exec) {
+                const uint32_t before = launches_;
+                cudaGraph_t graph = nullptr;
+                GF_CUDA(cudaStreamBeginCapture(stream_, cudaStreamCaptureModeThreadLocal));
+                const int status = encode_stream_group(set, first, rows);
+                const cudaError_t end = cudaStreamEndCapture(stream_, &graph);
+                set.group_launches[group] = launches_ - before;
+                launches_ = before;
+                if (status != GF_OK) { if (graph) cudaGraphDestroy(graph); return status; }
+                GF_CUDA(end);
+                const cudaError_t inst = cudaGraphInstantiate(&exec, graph, 0);
+                cudaGraphDestroy(graph);
+                GF_CUDA(inst);
+            }
+            GF_CUDA(cudaGraphLaunch(exec, stream_));
+            launches_ += set.group_launches[group];
+        }
         for (uint32_t r = 0; r < rows; ++r) ++set.positions_host[first + r];
     }
     return GF_OK;
@@ -288,6 +442,9 @@ int gf_streams_prefill(gf_streams* s, uint32_t stream, const uint32_t* tokens_ho
 }
 int gf_streams_decode(gf_streams* s, const uint32_t* tokens_host) {
     return s ? s->model->impl.streams_decode(*s->set, tokens_host) : fail(GF_ERR_INVALID, "null streams");
+}
+int gf_streams_set_mode(gf_streams* s, int mode) {
+    return s ? s->model->impl.streams_set_mode(*s->set, mode) : fail(GF_ERR_INVALID, "null streams");
 }
 int gf_streams_select(gf_streams* s, const void* requests_host) {
     return s ? s->model->impl.streams_select(*s->set, requests_host) : fail(GF_ERR_INVALID, "null streams");

@@ -85,6 +85,7 @@ lib.register({
     "gf_streams_count": (u32, [vp]),
     "gf_streams_prefill": (i32, [vp, u32, vp, u32]),
     "gf_streams_decode": (i32, [vp, vp]),
+    "gf_streams_set_mode": (i32, [vp, i32]),
     "gf_streams_select": (i32, [vp, vp]),
     "gf_streams_read_candidates": (i32, [vp, vp]),
     "gf_streams_read_logits": (i32, [vp, u32, vp]),
@@ -267,6 +268,10 @@ class Streams:
     def prefill(self, stream: int, tokens) -> None:
         tokens = np.ascontiguousarray(tokens, np.uint32)
         check(self.L.gf_streams_prefill(self.handle, stream, tokens.ctypes.data, tokens.size))
+
+    def set_mode(self, mode: int) -> None:
+        """0: exact row passes in groups; 1: one tensor-core pass over all streams (bf16 operands)."""
+        check(self.L.gf_streams_set_mode(self.handle, mode))
 
     def decode(self, tokens) -> None:
         tokens = np.ascontiguousarray(tokens, np.uint32)

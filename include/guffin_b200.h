@@ -367,6 +367,12 @@ GF_API int gf_streams_destroy(gf_streams* streams);
 GF_API uint32_t gf_streams_count(const gf_streams* streams);
 GF_API int gf_streams_prefill(gf_streams* streams, uint32_t stream, const uint32_t* tokens_host, uint32_t count);
 GF_API int gf_streams_decode(gf_streams* streams, const uint32_t* tokens_host /* one id per stream */);
+/* How a step computes its projections.  0 (default): the exact row passes described above.  1: ONE pass over
+ * all streams of the set (at most 128) whose projections are the prompt path's bf16 tensor-core GEMMs
+ * (gf_prefill_matmul): the weights are read and dequantised once per step however many streams there are,
+ * and results differ from mode 0 by the bf16 rounding of activations and weights (about 1e-2 relative L2 on
+ * logits), the trade the reference makes for its Gemma 2 prompt path (gemma2_runtime.cpp:893-1170). */
+GF_API int gf_streams_set_mode(gf_streams* streams, int mode);
 GF_API int gf_streams_select(gf_streams* streams, const void* requests_host);
 GF_API int gf_streams_read_candidates(gf_streams* streams, void* results_host);
 GF_API int gf_streams_read_logits(gf_streams* streams, uint32_t stream, float* logits_host);
