@@ -630,7 +630,7 @@ def run_case(argv) -> int:
         launches = numbers[4] if len(numbers) > 4 else 3
         weight = lib.PackedWeight(dtype, k, n, syn.make_weight(rng, dtype, k, n))
         x = lib.DeviceBuffer.from_numpy(rng.standard_normal((rows, k)).astype(np.float32))
-        y = lib.DeviceBuffer(128 * n * 4)
+        y = lib.DeviceBuffer((rows + 127) // 128 * 128 * n * 4)          # results come in whole halves of 128 rows
         ws = lib.DeviceBuffer(L.gf_prefill_workspace_bytes(k))
         for _ in range(launches):
             lib.check(L.gf_prefill_matmul(dtype, weight.packed.ptr, x.ptr, y.ptr, rows, k, n, ws.ptr, None))

@@ -830,6 +830,7 @@ int Model::prefill_chunk(const uint32_t* tokens_host, uint32_t rows) {
         for (const auto& entry : set) launch.matrices[launch.count++] = {entry.first->dtype, entry.first->data, entry.second, entry.first->n};
         launch.k = k;
         launch.a = operand;
+        launch.rows = rows;
         ++launches_;
         return launch_prefill_gemm(launch, error_flag_, stream_);
     };

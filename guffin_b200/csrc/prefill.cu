@@ -10,13 +10,14 @@ namespace gf {
 
 namespace {
 
-constexpr uint32_t kStages = 4;                                         // shared-memory stages of 64 K elements
+constexpr uint32_t kStages = 3;                                         // shared-memory stages of 64 K elements
 constexpr uint32_t kAhead = 2;                                          // stages the activation copies run ahead of the dequantisation
 constexpr uint32_t kWeightBufs = 3;                                     // K units of packed weights in shared memory (two in flight)
 constexpr uint32_t kPairs = kPrefillTile / 16u;                         // column pairs (16 columns) per CTA
 constexpr uint32_t kMaxPairRow = 3360u;                                 // Q6_K
 constexpr uint32_t kWeightBufBytes = kPairs * kMaxPairRow;
-constexpr uint32_t kAStageBytes = kPrefillBlockBytes;                   // 128 rows x 64 K bf16
+constexpr uint32_t kAStageBytes = kPrefillBlockBytes;                   // 256 rows x 64 K bf16
+constexpr uint32_t kAHalfBytes = kPrefillHalf * kPrefillBlockK * 2u;    // the rows of one accumulator
 constexpr uint32_t kBStageBytes = kPrefillTile * kPrefillBlockK * 2u;   // 128 columns x 64 K bf16
 constexpr uint32_t kOffA = 0u, kOffB = kStages * kAStageBytes, kOffW = kOffB + kStages * kBStageBytes;
 constexpr uint32_t kOffBars = kOffW + kWeightBufs * kWeightBufBytes;
@@ -44,7 +45,8 @@ __device__ __forceinline__ uint64_t operand_descriptor(uint32_t smem_address) {
     return (uint64_t)((smem_address >> 4) & 0x3fffu) | ((uint64_t)(128u >> 4) << 16) | ((uint64_t)(1024u >> 4) << 32) | (1ull << 46);
 }
 // Instruction descriptor: f32 accumulator, bf16 x bf16, both operands K-major, M = 128, N = kPrefillTile.
-constexpr uint32_t kInstruction = (1u << 4) | (1u << 7) | (1u << 10) | ((kPrefillTile >> 3) << 17) | ((kPrefillRows >> 4) << 24);
+constexpr uint32_t kInstruction = (1u << 4) | (1u << 7) | (1u << 10) | ((kPrefillTile >> 3) << 17) | ((kPrefillHalf >> 4) << 24);
+constexpr uint32_t kTmemColumns = 2u * kPrefillTile;                    // one accumulator of kPrefillTile columns per half of the rows
 
 __device__ __forceinline__ void mma_bf16(uint32_t tmem_d, uint64_t a_desc, uint64_t b_desc, uint32_t accumulate) {
     asm volatile(
@@ -216,7 +218,7 @@ __global__ void __launch_bounds__(kPrefillThreads, 1) prefill_gemm_kernel(const 
         mbar_init(done_bar, 1);
         fence_barrier_init();
     }
-    if (warp == 0) tmem_alloc(&tmem_slot, kPrefillTile);
+    if (warp == 0) tmem_alloc(&tmem_slot, kTmemColumns);
     tc_fence_before_sync();
     __syncthreads();
     tc_fence_after_sync();
@@ -238,8 +240,8 @@ __global__ void __launch_bounds__(kPrefillThreads, 1) prefill_gemm_kernel(const 
             auto request_block = [&](uint32_t step) {         // the stage must be free
                 requested_blocks = step + 1u;
                 const uint32_t stage = step % kStages;
-                mbar_expect_tx(&a_full[stage], kAStageBytes);
-                bulk_load(smem + kOffA + stage * kAStageBytes, blocks + (size_t)step * kPrefillBlockBytes, kAStageBytes, &a_full[stage]);
+                mbar_expect_tx(&a_full[stage], p.halves * kAHalfBytes);          // rows 0-127 lie in the block's first half
+                bulk_load(smem + kOffA + stage * kAStageBytes, blocks + (size_t)step * kPrefillBlockBytes, p.halves * kAHalfBytes, &a_full[stage]);
             };
             for (uint32_t j = 0; j < 2u && j < unit_count; ++j) request_weights(j);
             for (uint32_t step = 0; step < kAhead && step < steps; ++step) request_block(step);
@@ -282,10 +284,11 @@ __global__ void __launch_bounds__(kPrefillThreads, 1) prefill_gemm_kernel(const 
                 if (!wait_or_abort(&a_full[stage], use & 1u, abort) || !wait_or_abort(&b_full[stage], use & 1u, abort)) { ok = false; break; }
                 tc_fence_after_sync();
                 const uint32_t a_address = smem_u32(smem + kOffA + stage * kAStageBytes), b_address = smem_u32(smem + kOffB + stage * kBStageBytes);
+                for (uint32_t h = 0; h < p.halves; ++h)
 #pragma unroll
-                for (uint32_t kk = 0; kk < kPrefillBlockK / 16u; ++kk)
-                    mma_bf16(tmem, operand_descriptor(a_address + kk * 256u), operand_descriptor(b_address + kk * 256u),
-                             (step | kk) != 0u ? 1u : 0u);
+                    for (uint32_t kk = 0; kk < kPrefillBlockK / 16u; ++kk)
+                        mma_bf16(tmem + h * kPrefillTile, operand_descriptor(a_address + h * kAHalfBytes + kk * 256u),
+                                 operand_descriptor(b_address + kk * 256u), (step | kk) != 0u ? 1u : 0u);
                 mma_commit(&stage_free[stage]);
             }
             if (ok) mma_commit(done_bar);
@@ -318,20 +321,23 @@ __global__ void __launch_bounds__(kPrefillThreads, 1) prefill_gemm_kernel(const 
     const bool failed = __syncthreads_or(ok ? 0 : 1) != 0;
     if (!failed && warp < kDequantWarps) {
         tc_fence_after_sync();
-        // Warp w reads accumulator lanes 32 * (w % 4) .. +31 (its quarter of the rows) and a quarter of the columns.
-        const uint32_t row = (warp & 3u) * 32u + lane, column0 = (warp >> 2) * (kPrefillTile / 4u);
-        float* out = mat.out + (size_t)blockIdx.y * kPrefillRows * mat.n + (size_t)row * mat.n + (size_t)tile * kPrefillTile + column0;
-        float v[32];
-        tmem_load_32(tmem + (((warp & 3u) * 32u) << 16) + column0, v);
+        // Warp w reads accumulator lanes 32 * (w % 4) .. +31 (its quarter of a half's rows) and a quarter of the columns.
+        const uint32_t column0 = (warp >> 2) * (kPrefillTile / 4u);
+        for (uint32_t h = 0; h < p.halves; ++h) {
+            const uint32_t row = h * kPrefillHalf + (warp & 3u) * 32u + lane;
+            float* out = mat.out + (size_t)blockIdx.y * kPrefillRows * mat.n + (size_t)row * mat.n + (size_t)tile * kPrefillTile + column0;
+            float v[32];
+            tmem_load_32(tmem + (((warp & 3u) * 32u) << 16) + h * kPrefillTile + column0, v);
 #pragma unroll
-        for (uint32_t i = 0; i < 32u; i += 4u)
-            *reinterpret_cast<float4*>(out + i) = make_float4(v[i], v[i + 1], v[i + 2], v[i + 3]);
+            for (uint32_t i = 0; i < 32u; i += 4u)
+                *reinterpret_cast<float4*>(out + i) = make_float4(v[i], v[i + 1], v[i + 2], v[i + 3]);
+        }
         tc_fence_before_sync();
     } else if (failed && tid == 0) {
         atomicExch(p.error_flag, 1);
     }
     __syncthreads();
-    if (warp == 0) tmem_dealloc(tmem, kPrefillTile);
+    if (warp == 0) tmem_dealloc(tmem, kTmemColumns);
 }
 
 // ---- elementwise steps.  A thread handles eight consecutive K elements of one row: two 16-byte loads per
@@ -722,6 +728,8 @@ int launch_prefill_gemm(const PrefillGemmLaunch& launch, int* error_flag, cudaSt
     if (launch.splits == 0 || launch.splits > p.units) return fail(GF_ERR_INVALID, "prefill GEMM: K splits must be between 1 and the number of K units");
     p.a = static_cast<const uint8_t*>(launch.a);
     p.error_flag = error_flag;
+    if (launch.rows == 0 || launch.rows > kPrefillRows) return fail(GF_ERR_INVALID, "prefill GEMM: rows outside [1, %u]", kPrefillRows);
+    p.halves = prefill_padded_rows(launch.rows) / kPrefillHalf;
     static std::once_flag once[64];
     int device = 0;
     cudaGetDevice(&device);
@@ -755,7 +763,7 @@ int launch_prefill_norm(const float* x, uint32_t splits, const float* residual, 
     if (!x || splits == 0 || rows == 0 || rows > kPrefillRows || k == 0 || k % 8u || k > kNormPieces * 256u * 8u
         || (mode == 0 && (!gamma1 || !a_out)) || (mode == 1 && (!residual || !gamma0 || !residual_out)))
         return fail(GF_ERR_INVALID, "prefill norm: bad arguments");
-    const uint32_t blocks = a_out ? kPrefillRows : rows;
+    const uint32_t blocks = a_out ? prefill_padded_rows(rows) : rows;
     prefill_norm_kernel<<<blocks, 256, 0, stream>>>(x, splits, residual, gamma0, gamma1, residual_out, static_cast<uint8_t*>(a_out), rows, k, eps, mode);
     GF_CUDA(cudaGetLastError());
     return GF_OK;
@@ -774,7 +782,7 @@ int launch_prefill_reduce(float* const* x, const uint64_t* n, uint32_t count, ui
 
 int launch_prefill_geglu(const float* gate, const float* up, uint32_t splits, void* a_out, uint32_t rows, uint32_t k, cudaStream_t stream) {
     if (!gate || !up || !a_out || splits == 0 || rows == 0 || rows > kPrefillRows || k % 8u) return fail(GF_ERR_INVALID, "prefill GeGLU: bad arguments");
-    prefill_geglu_kernel<<<dim3(kPrefillRows, (k / 8u + 255u) / 256u), 256, 0, stream>>>(gate, up, splits, static_cast<uint8_t*>(a_out), rows, k);
+    prefill_geglu_kernel<<<dim3(prefill_padded_rows(rows), (k / 8u + 255u) / 256u), 256, 0, stream>>>(gate, up, splits, static_cast<uint8_t*>(a_out), rows, k);
     GF_CUDA(cudaGetLastError());
     return GF_OK;
 }
@@ -797,7 +805,7 @@ int launch_prefill_attention(const AttentionParams& p, cudaStream_t stream) {
 
 int launch_prefill_pack(const float* x, void* a_out, uint32_t rows, uint32_t k, cudaStream_t stream) {
     if (!x || !a_out || rows == 0 || rows > kPrefillRows || k % 8u) return fail(GF_ERR_INVALID, "prefill pack: bad arguments");
-    prefill_pack_kernel<<<dim3(kPrefillRows, (k / 8u + 255u) / 256u), 256, 0, stream>>>(x, static_cast<uint8_t*>(a_out), rows, k);
+    prefill_pack_kernel<<<dim3(prefill_padded_rows(rows), (k / 8u + 255u) / 256u), 256, 0, stream>>>(x, static_cast<uint8_t*>(a_out), rows, k);
     GF_CUDA(cudaGetLastError());
     return GF_OK;
 }
@@ -851,6 +859,7 @@ int gf_prefill_matmul(int dtype, const void* packed_dev, const float* x_dev, flo
     launch.count = 1;
     launch.k = k;
     launch.a = workspace_dev;
+    launch.rows = rows;
     const int launched = launch_prefill_gemm(launch, flags[device], s);
     if (launched != GF_OK) return launched;
     int value = 0;

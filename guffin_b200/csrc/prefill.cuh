@@ -1,8 +1,9 @@
 // Prompt ingestion as a dense contraction on the fifth-generation tensor cores (tcgen05 + TMEM).
 //
-// A chunk of up to 128 prompt rows goes through each projection as ONE GEMM
-//     C[128, N] = A[128, K] (bf16 activations) x deq(W)[N, K]^T (bf16, dequantised in shared memory)
-// so the quantised weights are read once per 128 rows instead of once per row pair
+// A chunk of up to 256 prompt rows goes through each projection as ONE GEMM
+//     C[256, N] = A[256, K] (bf16 activations) x deq(W)[N, K]^T (bf16, dequantised in shared memory)
+// issued as two M = 128 products per dequantised weight tile (one accumulator per half of the rows), so the
+// quantised weights are read and dequantised once per 256 rows instead of once per row pair
 // (run_gemma3_resident_prefill, src/engine/gemma_target_runtime.cpp:420-455; the reference's matrix
 // kernel is gemma3_matmul_f32_kquant_matrix_impl, metal_kernels.mm:1031-1199).
 //
@@ -17,7 +18,8 @@
 
 namespace gf {
 
-constexpr uint32_t kPrefillRows = 128;          // rows of one chunk = M of the tensor-core instruction
+constexpr uint32_t kPrefillHalf = 128;          // M of the tensor-core instruction
+constexpr uint32_t kPrefillRows = 256;          // rows of one chunk: two accumulators share every dequantised weight tile
 constexpr uint32_t kPrefillTile = 128;          // output columns per CTA
 constexpr uint32_t kPrefillBlockK = 64;         // K elements per shared-memory stage
 constexpr uint32_t kPrefillThreads = 576;          // sixteen dequantising warps, the warp that issues the products and the warp that requests the copies
@@ -30,9 +32,12 @@ __host__ __device__ inline size_t tile_major_offset(uint32_t row, uint32_t k) {
 }
 inline size_t tile_major_bytes(uint64_t k) { return (size_t)((k + kPrefillBlockK - 1u) / kPrefillBlockK) * kPrefillBlockBytes; }
 
+// Rows a chunk of `rows` occupies in operands and results: whole halves.
+__host__ __device__ inline uint32_t prefill_padded_rows(uint32_t rows) { return (rows + kPrefillHalf - 1u) / kPrefillHalf * kPrefillHalf; }
+
 struct PrefillMatrix {
     const uint8_t* weight;      // streaming layout (the same bytes the decode kernels read)
-    float* out;                 // [128][n] f32
+    float* out;                 // [padded rows][n] f32
     uint32_t n, dtype, first_tile;
 };
 
@@ -42,6 +47,7 @@ struct PrefillGemmParams {
     uint32_t k, units, unit_elems;
     const uint8_t* a;           // tile-major bf16 activations, `k` wide
     int* error_flag;
+    uint32_t halves;            // 1 or 2: halves of the chunk that hold rows
 };
 
 struct PrefillGemmLaunch {
@@ -49,7 +55,8 @@ struct PrefillGemmLaunch {
     uint32_t count = 1;
     uint64_t k = 0;
     const void* a = nullptr;
-    uint32_t splits = 1;       // K is cut into this many parts; part s writes [128][n] floats at out + s * 128 * n
+    uint32_t splits = 1;       // K is cut into this many parts; part s writes its rows at out + s * kPrefillRows * n
+    uint32_t rows = kPrefillRows;      // rows of the chunk (results are written for whole halves)
 };
 constexpr uint32_t kPrefillMaxSplits = 4;
 int launch_prefill_gemm(const PrefillGemmLaunch& launch, int* error_flag, cudaStream_t stream);
@@ -59,7 +66,7 @@ uint32_t prefill_gemm_splits(uint64_t n, uint64_t k, int dtype);
 // Elementwise steps between the GEMMs, each writing the next GEMM's tile-major bf16 operand.
 // mode 0: a = rmsnorm(x; gamma1)
 // mode 1: r = residual + rmsnorm(x; gamma0) -> residual_out;  a = rmsnorm(r; gamma1)     (gamma1 null: only residual_out)
-// x is the sum, in split order, of `splits` partial results laid [split][128][k].
+// x is the sum, in split order, of `splits` partial results laid [split][kPrefillRows][k].
 int launch_prefill_norm(const float* x, uint32_t splits, const float* residual, const float* gamma0, const float* gamma1,
                         float* residual_out, void* a_out, uint32_t rows, uint32_t k, float eps, int mode, cudaStream_t stream);
 // a = gelu_tanh(gate) * up, gate and up each the sum of `splits` partial results

@@ -71,7 +71,7 @@ int Model::streams_create(uint32_t count, StreamSet** out) {
     GF_TRY(stream_alloc(*set, &set->rings_dev, rings.size()));
     GF_TRY(stream_alloc(*set, &set->publish_layers_dev, layers.size()));
     GF_TRY(stream_alloc(*set, &set->positions_dev, count));
-    GF_TRY(stream_alloc(*set, &set->logits, (size_t)std::max(count, kPrefillRows) * c.vocab));      // a tensor-core step writes 128 rows
+    GF_TRY(stream_alloc(*set, &set->logits, (size_t)prefill_padded_rows(count) * c.vocab));      // a tensor-core step writes whole halves of 128 rows
     uint8_t* bytes = nullptr;
     GF_TRY(stream_alloc(*set, &bytes, candidates_workspace_bytes(count, c.vocab))); set->candidates_ws = bytes;
     GF_TRY(stream_alloc(*set, &bytes, (size_t)count * gf_selection_request_bytes())); set->requests_dev = bytes;
@@ -246,6 +246,7 @@ int Model::encode_stream_batch(StreamSet& set) {
         for (const auto& entry : matrices) launch.matrices[launch.count++] = {entry.first->dtype, entry.first->data, entry.second, entry.first->n};
         launch.k = k;
         launch.a = operand;
+        launch.rows = rows;
         ++launches_;
         return launch_prefill_gemm(launch, error_flag_, stream_);
     };

@@ -277,15 +277,17 @@ def matmul(weight: PackedWeight, x: np.ndarray) -> np.ndarray:
 
 
 def prefill_matmul(weight: PackedWeight, x: np.ndarray) -> np.ndarray:
-    """y = x @ deq(W)^T for up to 128 rows on the tensor cores (bf16 operands, f32 accumulation)."""
+    """y = x @ deq(W)^T for up to 256 rows on the tensor cores (bf16 operands, f32 accumulation); the
+    result has 128 or 256 rows (whole halves), rows beyond the live ones zero."""
     L = load()
     x = np.ascontiguousarray(x, np.float32).reshape(-1, weight.k)
     rows = x.shape[0]
     xd = DeviceBuffer.from_numpy(x)
-    yd = DeviceBuffer(128 * weight.n * 4)
+    padded = (rows + 127) // 128 * 128
+    yd = DeviceBuffer(padded * weight.n * 4)
     ws = DeviceBuffer(L.gf_prefill_workspace_bytes(weight.k))
     check(L.gf_prefill_matmul(weight.dtype, weight.packed.ptr, xd.ptr, yd.ptr, rows, weight.k, weight.n, ws.ptr, None))
-    y = yd.download(np.float32).reshape(128, weight.n)
+    y = yd.download(np.float32).reshape(padded, weight.n)
     for b in (xd, yd, ws):
         b.free()
     return y

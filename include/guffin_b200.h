@@ -133,19 +133,20 @@ GF_API size_t gf_matmul_static_capacity(void);
 GF_API int gf_matmul_static(int dtype, const void* packed_dev, const float* x_dev, float* y_dev,
                             uint32_t rows, uint64_t k, uint64_t n, void* stream);
 GF_API int gf_matmul_static_check(void* stream);
-/* The same product for up to 128 rows at once as a dense contraction on the tensor cores: bf16
+/* The same product for up to 256 rows at once as a dense contraction on the tensor cores: bf16
  * activations, weights dequantised to bf16 in shared memory, f32 accumulation (tcgen05 / TMEM).  The
  * prompt-ingestion shape of encode_verifier_matmul with allow_prefill_matrix
  * (metal_command_context.hpp:94-101; MSL gemma3_matmul_f32_kquant_matrix_impl, metal_kernels.mm:1031-1199;
  * the reference's Gemma 2 path uses half operands the same way, gemma2_runtime.cpp:893-1170).
- * y_dev holds 128 rows of n floats (rows beyond `rows` are written as zeros); n must be a multiple of 128,
+ * y_dev holds 128 rows of n floats, 256 when rows > 128 (rows beyond `rows` are written as zeros: every dequantised
+ * weight tile feeds one 128-row product per half of the rows in use); n must be a multiple of 128,
  * k of 256 (128 for Q8_0); workspace_dev holds gf_prefill_workspace_bytes(k) bytes (the activations in the
  * tensor core's operand order).  Synchronises the stream and returns GF_ERR_TIMEOUT if a bounded wait
  * gave up.  Differs from gf_matmul by the bf16 rounding of both operands (about 4e-3 relative L2). */
 GF_API size_t gf_prefill_workspace_bytes(uint64_t k);
 GF_API int gf_prefill_matmul(int dtype, const void* packed_dev, const float* x_dev, float* y_dev,
                              uint32_t rows, uint64_t k, uint64_t n, void* workspace_dev, void* stream);
-/* Attention of a prompt chunk (up to 128 rows) over the ring and the chunk's private rows of a binary16
+/* Attention of a prompt chunk (up to 256 rows) over the ring and the chunk's private rows of a binary16
  * cache with 256-wide heads, both contractions on the tensor cores with f16 operands (queries rounded to
  * f16 after scaling): the reference's flash prefill attention, encode_f16_prefill_attention
  * (metal_command_context.hpp; MSL metal_kernels.mm:2596-2798).  Same arguments as gf_attention without
@@ -297,7 +298,7 @@ GF_API int gf_model_publish(gf_model* model, uint32_t rows);
  * gemma_target_runtime.cpp:420); logits are produced for the last token only. */
 GF_API int gf_model_prefill(gf_model* model, const uint32_t* tokens_host, uint32_t count);
 GF_API int gf_model_truncate(gf_model* model, uint32_t position);
-/* gf_model_prefill ingests prompts of 65 tokens or more in chunks of up to 128 rows, every projection of
+/* gf_model_prefill ingests prompts of 65 tokens or more in chunks of up to 256 rows, every projection of
  * a chunk as one bf16 tensor-core GEMM (run_gemma3_resident_prefill's 128-row chunks,
  * gemma_target_runtime.cpp:420-455; the last layer of a chunk stops after its K/V rows, :59-61,125), and
  * the last prompt token as an ordinary one-row pass.  K/V rows and logits then differ from the exact row
@@ -368,7 +369,7 @@ GF_API uint32_t gf_streams_count(const gf_streams* streams);
 GF_API int gf_streams_prefill(gf_streams* streams, uint32_t stream, const uint32_t* tokens_host, uint32_t count);
 GF_API int gf_streams_decode(gf_streams* streams, const uint32_t* tokens_host /* one id per stream */);
 /* How a step computes its projections.  0 (default): the exact row passes described above.  1: ONE pass over
- * all streams of the set (at most 128) whose projections are the prompt path's bf16 tensor-core GEMMs
+ * all streams of the set (at most 256) whose projections are the prompt path's bf16 tensor-core GEMMs
  * (gf_prefill_matmul): the weights are read and dequantised once per step however many streams there are,
  * and results differ from mode 0 by the bf16 rounding of activations and weights (about 1e-2 relative L2 on
  * logits), the trade the reference makes for its Gemma 2 prompt path (gemma2_runtime.cpp:893-1170). */

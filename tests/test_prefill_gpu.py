@@ -1,4 +1,4 @@
-"""Prompt ingestion on the tensor cores: the 128-row bf16 GEMM with in-kernel dequantisation
+"""Prompt ingestion on the tensor cores: the 256-row bf16 GEMM (two 128-row products per dequantised weight tile) with in-kernel dequantisation
 (tcgen05 / TMEM) against the CPU oracle, and chunked prefill against token-at-a-time decoding."""
 import numpy as np
 import pytest
@@ -21,7 +21,8 @@ def rel_l2(got, want):
 
 @pytest.mark.parametrize("dtype,k,n,rows", [(syn.Q4_K, 512, 128, 128), (syn.Q4_K, 3840, 256, 37), (syn.Q6_K, 1024, 384, 128),
                                              (syn.Q6_K, 256, 128, 1), (syn.Q8_0, 640, 256, 100), (syn.Q8_0, 128, 128, 128),
-                                             (syn.Q4_K, 15360, 128, 128)])
+                                             (syn.Q4_K, 15360, 128, 128), (syn.Q4_K, 3840, 256, 200), (syn.Q6_K, 1024, 384, 256),
+                                             (syn.Q8_0, 640, 128, 129)])
 def test_prefill_matmul_matches_bf16_reference_and_oracle(gf, oracle, dtype, k, n, rows):
     """Against the same product with both operands rounded to bf16 and summed in double precision the
     kernel may differ only by its f32 accumulation (5e-5: a layout or descriptor mistake shows as an
@@ -32,7 +33,7 @@ def test_prefill_matmul_matches_bf16_reference_and_oracle(gf, oracle, dtype, k, 
     weight = gf.PackedWeight(dtype, k, n, native)
     x = rng.standard_normal((rows, k)).astype(np.float32)
     got = gf.prefill_matmul(weight, x)
-    assert got.shape == (128, n)
+    assert got.shape == ((rows + 127) // 128 * 128, n)
     w = oracle.dequantize(dtype, native).reshape(n, k)
     exact = bf16_round(x).astype(np.float64) @ bf16_round(w).astype(np.float64).T
     assert rel_l2(got[:rows], exact) < 5e-5                                  # 1.8e-5 at K = 15360: the accumulator does not round to nearest
