@@ -96,6 +96,34 @@ __device__ __forceinline__ float code_float(uint32_t word, uint32_t i, float bia
     return __fsub_rn(__uint_as_float(__byte_perm(word, 0x4B000000u, 0x7540u + i)), bias);
 }
 
+// The same two values at a time with the packed f32x2 instructions (each half rounds like the scalar
+// instruction, so the values are bit for bit those of the scalar form): typedef and helpers as in gemv.cuh.
+typedef unsigned long long pf2;
+__device__ __forceinline__ pf2 pf2_make(float lo, float hi) {
+    pf2 r;
+    asm("mov.b64 %0, {%1, %2};" : "=l"(r) : "r"(__float_as_uint(lo)), "r"(__float_as_uint(hi)));
+    return r;
+}
+__device__ __forceinline__ pf2 pf2_mul(pf2 a, pf2 b) { pf2 r; asm("mul.rn.f32x2 %0, %1, %2;" : "=l"(r) : "l"(a), "l"(b)); return r; }
+__device__ __forceinline__ pf2 pf2_add(pf2 a, pf2 b) { pf2 r; asm("add.rn.f32x2 %0, %1, %2;" : "=l"(r) : "l"(a), "l"(b)); return r; }
+__device__ __forceinline__ uint32_t pf2_bf16(pf2 v) {              // both halves rounded to bf16, low half in the low 16 bits
+    uint32_t lo, hi, r;
+    asm("mov.b64 {%0, %1}, %2;" : "=r"(lo), "=r"(hi) : "l"(v));
+    asm("cvt.rn.bf16x2.f32 %0, %1, %2;" : "=r"(r) : "r"(hi), "r"(lo));
+    return r;
+}
+// Bytes i and i + 1 of `word` as floats, minus (bias - 2^23) each; neg_bias = {-bias, -bias}.
+__device__ __forceinline__ pf2 code_pair(uint32_t word, uint32_t i, pf2 neg_bias) {
+    pf2 raw;
+    asm("mov.b64 %0, {%1, %2};" : "=l"(raw) : "r"(__byte_perm(word, 0x4B000000u, 0x7540u + i)), "r"(__byte_perm(word, 0x4B000000u, 0x7541u + i)));
+    return pf2_add(raw, neg_bias);
+}
+// Four consecutive K elements of column n of the B stage from two packed pairs.
+__device__ __forceinline__ void store_b4_pairs(uint8_t* stage, uint32_t n, uint32_t k, pf2 v01, pf2 v23) {
+    uint8_t* dst = stage + (n >> 3) * 1024u + (k >> 3) * 128u + (n & 7u) * 16u + (k & 7u) * 2u;
+    *reinterpret_cast<uint2*>(dst) = make_uint2(pf2_bf16(v01), pf2_bf16(v23));
+}
+
 __device__ __forceinline__ void dequant_q4k(const uint8_t* row, uint32_t sub, uint32_t lane, uint32_t col, uint32_t n, uint8_t* stage) {
     const uint32_t g = lane >> 2, t = lane & 3u;
     const uint2 words = *reinterpret_cast<const uint2*>(row + sub * 512u + lane * 16u + col * 8u);      // this column's {w0, w1}
@@ -105,17 +133,18 @@ __device__ __forceinline__ void dequant_q4k(const uint8_t* row, uint32_t sub, ui
     const uint32_t scales = sub < 2u ? (h.y & 0x3f3f3f3fu) : ((h.w & 0x0f0f0f0fu) | ((h.y >> 2) & 0x30303030u));
     const uint32_t minima = sub < 2u ? (h.z & 0x3f3f3f3fu) : (((h.w >> 4) & 0x0f0f0f0fu) | ((h.z >> 2) & 0x30303030u));
     const uint32_t first = (sub & 1u) * 2u;
+    const pf2 neg_bias = pf2_make(-8388608.0f, -8388608.0f);
 #pragma unroll
     for (uint32_t nib = 0; nib < 2u; ++nib) {
         const float ds = __fmul_rn(d, (float)byte_of(scales, first + nib));
         const float dm = __fmul_rn(dmin, (float)byte_of(minima, first + nib));
+        const pf2 ds2 = pf2_make(ds, ds), neg_dm2 = pf2_make(-dm, -dm);       // d * sc * q - dmin * mn, each step rounded once
 #pragma unroll
         for (uint32_t w = 0; w < 2u; ++w) {
             const uint32_t codes = ((w == 0u ? words.x : words.y) >> (4u * nib)) & 0x0f0f0f0fu;
-            float v[4];
-#pragma unroll
-            for (uint32_t i = 0; i < 4u; ++i) v[i] = __fsub_rn(__fmul_rn(ds, code_float(codes, i, 8388608.0f)), dm);
-            store_b4(stage, n, 32u * nib + 16u * w + 4u * t, v);
+            const pf2 v01 = pf2_add(pf2_mul(ds2, code_pair(codes, 0u, neg_bias)), neg_dm2);
+            const pf2 v23 = pf2_add(pf2_mul(ds2, code_pair(codes, 2u, neg_bias)), neg_dm2);
+            store_b4_pairs(stage, n, 32u * nib + 16u * w + 4u * t, v01, v23);
         }
     }
 }
@@ -135,10 +164,9 @@ __device__ __forceinline__ void dequant_q6k(const uint8_t* row, uint32_t sub, ui
             const uint32_t quarter = 2u * upper + qq;
             const float ds = __fmul_rn(d, (float)(int)(signed char)scale_bytes[8u * half + 2u * quarter + s]);
             const uint32_t codes = (((qq ? odd : even) >> (4u * upper)) & 0x0f0f0f0fu) | (((high >> (2u * quarter)) & 0x03030303u) << 4);
-            float v[4];
-#pragma unroll
-            for (uint32_t i = 0; i < 4u; ++i) v[i] = __fmul_rn(ds, code_float(codes, i, 8388608.0f + 32.0f));
-            store_b4(stage, n, 32u * qq + 16u * s + 4u * t, v);
+            const pf2 ds2 = pf2_make(ds, ds), neg_bias = pf2_make(-(8388608.0f + 32.0f), -(8388608.0f + 32.0f));
+            store_b4_pairs(stage, n, 32u * qq + 16u * s + 4u * t, pf2_mul(ds2, code_pair(codes, 0u, neg_bias)),
+                           pf2_mul(ds2, code_pair(codes, 2u, neg_bias)));
         }
     }
 }
@@ -153,10 +181,9 @@ __device__ __forceinline__ void dequant_q80(const uint8_t* row, uint32_t sub, ui
 #pragma unroll
         for (uint32_t w = 0; w < 2u; ++w) {
             const uint32_t codes = (w == 0u ? words.x : words.y) ^ 0x80808080u;        // int8 + 128
-            float v[4];
-#pragma unroll
-            for (uint32_t i = 0; i < 4u; ++i) v[i] = __fmul_rn(d, code_float(codes, i, 8388608.0f + 128.0f));
-            store_b4(stage, n, 32u * bb + 16u * w + 4u * t, v);
+            const pf2 d2 = pf2_make(d, d), neg_bias = pf2_make(-(8388608.0f + 128.0f), -(8388608.0f + 128.0f));
+            store_b4_pairs(stage, n, 32u * bb + 16u * w + 4u * t, pf2_mul(d2, code_pair(codes, 0u, neg_bias)),
+                           pf2_mul(d2, code_pair(codes, 2u, neg_bias)));
         }
     }
 }
