@@ -218,7 +218,8 @@ def run_ours(args) -> dict:
     L = lib.load()
     lib.check(L.gf_set_device(local))
     steps, warmup = args.steps, max(args.warmup, 3)
-    context = CONTEXT + 2 * (warmup + 2 * steps) + 64          # at most two tokens per cycle, two timed loops
+    horizon = max(1, args.horizon)
+    context = CONTEXT + (horizon + 1) * (warmup + 2 * steps) + 64          # at most horizon + 1 tokens per cycle, two timed loops
 
     t0 = time.time()
     tc, dc = syn.model_config(TARGET), syn.model_config(DRAFT)
@@ -229,7 +230,7 @@ def run_ours(args) -> dict:
         target.use_pass_kernel(args.schedule)
         draft.use_pass_kernel(args.schedule)
     options = ge.H1Options(ge.sampler_options(0.7, 40, 0.95, 0.05, 1.0, seed=SEEDS["sampler"] + rank), 1, 1, ACCEPT_P,
-                           SEEDS["schedule"] + rank, 0)
+                           SEEDS["schedule"] + rank, 0, horizon)
     engine = ge.H1(target, draft, options)
     # Prompt ingestion of both plans, twice: the first call also allocates the 128-row arena and loads
     # the kernels, the second is what a session pays per prompt.
@@ -315,10 +316,13 @@ def run_ours(args) -> dict:
         "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
         "dtype": "u4/u6/u8 blocks -> f32",
         "data": "synthetic",
-        "config": {"workload": "configs[3]: Gemma-3-12B Q4_K_M + 270M Q8_0 drafter, H1, context 2048, T=0.7 top-k 40 "
-                               "top-p 0.95 min-p 0.05, 2-row verification, seeded Bernoulli(0.7) accept schedule",
+        "config": {"workload": ("configs[3]: Gemma-3-12B Q4_K_M + 270M Q8_0 drafter, H1, context 2048, T=0.7 top-k 40 "
+                                "top-p 0.95 min-p 0.05, 2-row verification, seeded Bernoulli(0.7) accept schedule") if horizon == 1 else
+                               (f"configs[3] with chains of {horizon} drafts per cycle ({horizon + 1}-row verification, one Bernoulli(0.7) "
+                                "draw per draft): not the headline"),
                    "schedule": {None: "kernel per operator (default)", 0: "kernel per operator", 1: "decode pass kernel",
                                 2: "decode pass kernel, attention launched separately"}[args.schedule],
+                   "horizon": horizon,
                    "streams_per_gpu": 1, "parallelism": f"independent streams x{world} (no collective)",
                    "l2_policy": "inputs larger than L2: every pass streams 7.3 GB of distinct weights",
                    "assumed_accept_probability": ACCEPT_P,
@@ -330,7 +334,7 @@ def run_ours(args) -> dict:
                    "prefill_tok_s": round(CONTEXT / prefill_s, 1),
                    "status_word": int(status)},
         "e2e": {"value": produced_e2e / e2e_s, "unit": "tok/s",
-                "h2d_bytes_per_step": 4 + 2 * 264, "d2h_bytes_per_step": 2 * 3080 + 3096,
+                "h2d_bytes_per_step": 4 + (horizon + 1) * 264, "d2h_bytes_per_step": (horizon + 1) * 3080 + horizon * 3096,
                 "ms_per_step": e2e_s * 1e3 / steps, "wall_s_first_loop": wall},
         "gpu_launches": int(launches),
         "roofline": {"bound": "hbm", "achieved": achieved, "peak": peak, "unit": "GB/s", "frac": achieved / peak,
@@ -690,6 +694,7 @@ def main():
                              "2: pass kernel with attention launched separately")
     parser.add_argument("--case", nargs="+", default=None, help="run one single-kernel case instead of the benchmark")
     parser.add_argument("--workload", choices=("h1", "streams"), default="h1", help="h1: the headline (configs[3]); streams: configs[4]")
+    parser.add_argument("--horizon", type=int, default=1, help="drafts per cycle of the h1 workload (1 = the headline; 2..7 = chains)")
     parser.add_argument("--streams", type=int, default=8, help="streams per GPU of the streams workload (64 over eight GPUs)")
     parser.add_argument("--prefix", type=int, default=8192, help="prefix tokens per stream of the streams workload")
     parser.add_argument("--tensor-decode", action="store_true",
