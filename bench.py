@@ -255,7 +255,8 @@ def run_ours(args) -> dict:
     # ---- warm-up, then K cycles timed on the device (events on the target's stream; the drafter's
     # work is ordered into it every cycle), bracketed by barrier + synchronise.  Both measured loops
     # restart the accept schedule from the same seed, so they see the same outcomes.
-    engine.generate_steps(warmup)
+    token_room = lambda cycles: (horizon + 1) * cycles + 2          # a cycle emits at most horizon + 1 tokens
+    engine.generate_steps(warmup, token_room(warmup))
     barrier()
     loop_seed = 1000 + SEEDS["schedule"] + rank
     engine.reseed_schedule(loop_seed)
@@ -265,7 +266,7 @@ def run_ours(args) -> dict:
     with ClockSampler(local) as clocks:
         start.record(target.stream)
         wall0 = time.perf_counter()
-        tokens = engine.generate_steps(steps)
+        tokens = engine.generate_steps(steps, token_room(steps))
         end.record(target.stream)
         end.synchronize()
         wall = time.perf_counter() - wall0
@@ -278,7 +279,7 @@ def run_ours(args) -> dict:
         barrier()
         engine.reseed_schedule(loop_seed)
         e2e0 = time.perf_counter()
-        tokens_e2e = engine.generate_steps(steps)
+        tokens_e2e = engine.generate_steps(steps, token_room(steps))
         target.synchronize()
         e2e_wall = time.perf_counter() - e2e0
         # ---- roofline of the dominant kernel: exactly one verify pass's weight GEMVs, alone.
