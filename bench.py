@@ -55,7 +55,7 @@ ACCEPT_P = 0.7
 PREFILL_ROWS = 8          # rows per prompt-ingestion pass (verification passes stay two rows wide)
 # dram__bytes_read.sum + dram__bytes_write.sum over the weight bytes of one captured GEMV launch
 # (profiles/weight_stream_kernel_q4k_k3840_n65536_rows2.md).
-TRAFFIC_PER_ALGORITHMIC_BYTE = (141.66 + 3.65) / 141.56
+TRAFFIC_PER_ALGORITHMIC_BYTE = (141.66 + 3.08) / 141.56
 SEEDS = dict(target=1201, draft=2701, prompt=31, sampler=41, schedule=7, shapes=17)
 
 
@@ -341,7 +341,7 @@ def run_ours(args) -> dict:
         "roofline": {"bound": "hbm", "achieved": achieved, "peak": peak, "unit": "GB/s", "frac": achieved / peak,
                      "peak_source": f"of {peak_kind}",
                      # DRAM bytes per launch: the read+write bytes ncu counted on one launch of the same kernel
-                     # (Q4_K, K = 3840, N = 65536, two rows: 145.31 MB for 141.56 MB of weights), scaled by bytes.
+                     # (Q4_K, K = 3840, N = 65536, two rows: 144.74 MB for 141.56 MB of weights), scaled by bytes.
                      "traffic": TRAFFIC_PER_ALGORITHMIC_BYTE * sweep_bytes / sweep_launches,
                      "kernel": "weight_stream_kernel (Q4_K/Q6_K, rows=2): one verify pass's weight products run alone",
                      "bytes_per_launch": sweep_bytes / sweep_launches, "launches": sweep_launches,
