@@ -127,6 +127,7 @@ const Known* classify(const std::string& name, uint32_t& layer) {
 uint64_t tensor_bytes(uint32_t type, uint64_t elements) {
     switch (type) {
         case 0: return elements * 4u;                                   // F32
+        case 1: return elements * 2u;                                   // F16 (embedding / head tables of the retained Gemma 2 file)
         case GF_Q8_0: return elements % 32u ? 0 : elements / 32u * 34u;
         case GF_Q4_K: return elements % 256u ? 0 : elements / 256u * 144u;
         case GF_Q6_K: return elements % 256u ? 0 : elements / 256u * 210u;

@@ -167,7 +167,8 @@ GF_API int gf_matmul_host(int dtype, const void* packed_dev, const float* x_host
 /* MetalCommandContext::encode_embedding (metal_command_context.hpp:75-82; kernels
  * metal_kernels.mm:235-255,452-474): gathers rows of the packed [K, vocab] matrix, dequantises
  * with the reference's rounding and multiplies by `scale` (sqrt(hidden)).  A token id >= vocab
- * sets status bit 1 and yields NaN for that row. */
+ * sets status bit 1 and yields NaN for that row.  dtype GF_F16: `packed_dev` is a binary16 table
+ * [vocab][k] exactly as the file stores it (the retained Gemma 2 9B embedding). */
 GF_API int gf_embedding(int dtype, const void* packed_dev, uint32_t k, uint32_t vocab,
                         const uint32_t* tokens_dev, uint32_t rows, float scale, float* out_dev,
                         uint32_t* status_dev, void* stream);
@@ -273,7 +274,7 @@ GF_API int gf_model_set_vector(gf_model* model, int kind, uint32_t layer, const 
 GF_API int gf_model_set_matrix_requantized(gf_model* model, int kind, uint32_t layer, const void* native_q6_k_host,
                                            uint64_t k, uint64_t n);
 /* Binds every tensor of a GGUF v2/v3 file that the block schedule knows (llama.cpp tensor names,
- * F32 vectors and Q8_0 / Q4_K / Q6_K matrices) through the two calls above: the path's share of
+ * F32 vectors, Q8_0 / Q4_K / Q6_K matrices and binary16 embedding / head tables) through the two calls above: the path's share of
  * read_file_backed_gguf_model (model_format/gguf_reader.hpp:85) and of the WeightMaterializer.
  * The geometry still comes from gf_model_config; *out_bound_tensors (optional) counts the
  * tensors taken.  Call gf_model_finalize afterwards. */

@@ -454,6 +454,25 @@ def test_gguf_file_loads_like_the_tensor_dictionary(gf, gm, tmp_path, geometry, 
         assert error.value.status == gf.GF_ERR_INVALID
 
 
+def test_gguf_file_with_a_binary16_table(gf, gm, tmp_path):
+    """A file in the form of the retained Gemma 2 9B -- one binary16 token_embd, no output tensor -- binds
+    through gf_model_load_gguf like the same tensors handed over one by one."""
+    config = syn.model_config("tiny-gemma2")
+    weights = dict(syn.make_model_weights("tiny-gemma2", 63))
+    del weights["output.weight"]
+    H, V = config["hidden"], config["vocab"]
+    table = (np.random.default_rng(63).standard_normal(V * H) / np.sqrt(H)).astype(np.float16)
+    weights["token_embd.weight"] = (1, H, V, table.view(np.uint16))
+    path = tmp_path / "f16.gguf"
+    _write_gguf(path, weights)
+    from_file, from_dict = gm.Model(config, path, 48, 2), gm.Model(config, weights, 48, 2)
+    assert from_file.bound_tensors == len(weights)
+    tokens = np.random.default_rng(64).integers(0, V, 7).astype(np.uint32)
+    for model in (from_file, from_dict):
+        model.prefill(tokens)
+    np.testing.assert_array_equal(from_file.logits(0), from_dict.logits(0))
+
+
 def test_reset_returns_the_plan_to_its_first_token(gf, gm):
     """gf_model_reset forgets the committed positions: the same prompt gives the same floats again."""
     model, config, _ = _gpu_model(gm, "tiny-target", 71, context=64)
