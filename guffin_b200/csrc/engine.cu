@@ -472,6 +472,11 @@ int gf_sampler_preview_proposal_word(const gf_sampler* s, uint32_t* out_word) {
     *out_word = s->impl.preview_proposal_word();
     return GF_OK;
 }
+int gf_sampler_preview_proposal_words(const gf_sampler* s, uint32_t count, uint32_t* out_words) {
+    if (!s || !out_words || count == 0 || count > 23u) return fail(GF_ERR_INVALID, "between 1 and 23 proposal words");
+    s->impl.preview_proposal_words(out_words, count);
+    return GF_OK;
+}
 int gf_sampler_prepare(const gf_sampler* s, const gf_token_logit* candidates, uint32_t count, const uint32_t* suffix,
                        uint32_t suffix_count, uint32_t* out_tokens, double* out_weights, uint32_t* out_count,
                        double* out_total_weight) {

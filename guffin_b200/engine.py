@@ -64,6 +64,7 @@ lib.register({
     "gf_sampler_destroy": (i32, [vp]),
     "gf_sampler_observe": (i32, [vp, vp, u32]),
     "gf_sampler_preview_proposal_word": (i32, [vp, C.POINTER(u32)]),
+    "gf_sampler_preview_proposal_words": (i32, [vp, u32, vp]),
     "gf_sampler_prepare": (i32, [vp, vp, u32, vp, u32, vp, vp, C.POINTER(u32), C.POINTER(C.c_double)]),
     "gf_sampler_sample": (i32, [vp, vp, u32, vp, u32, C.POINTER(u32)]),
     "gf_sampler_sample_speculative": (i32, [vp, C.POINTER(GatheredDraft), vp, u32, vp, u32, C.POINTER(u32),
@@ -97,6 +98,11 @@ class Sampler:
         out = u32()
         check(self.L.gf_sampler_preview_proposal_word(self.handle, C.byref(out)))
         return out.value
+
+    def proposal_words(self, count: int) -> np.ndarray:
+        out = np.zeros(count, np.uint32)
+        check(self.L.gf_sampler_preview_proposal_words(self.handle, count, out.ctypes.data))
+        return out
 
     def prepare(self, candidates, suffix=()):
         candidates = np.ascontiguousarray(candidates, TOKEN_LOGIT)

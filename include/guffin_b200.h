@@ -430,6 +430,9 @@ GF_API int gf_sampler_create(const gf_sampler_options* options, gf_sampler** out
 GF_API int gf_sampler_destroy(gf_sampler* sampler);
 GF_API int gf_sampler_observe(gf_sampler* sampler, const uint32_t* tokens, uint32_t count);    /* observe_tokens */
 GF_API int gf_sampler_preview_proposal_word(const gf_sampler* sampler, uint32_t* out_word);   /* preview_proposal_words(1) */
+/* The next `count` (<= 23, the reference's largest horizon) words of the proposal stream without consuming them:
+ * word i is the one the i-th acceptance test of a cycle will check (preview_proposal_words, sampling.cpp:62-80,936). */
+GF_API int gf_sampler_preview_proposal_words(const gf_sampler* sampler, uint32_t count, uint32_t* out_words);
 /* prepare_distribution (sampling.cpp:394-499) for the row whose context is the observed history
  * plus `suffix`: writes the support tokens and their sampling weights. */
 GF_API int gf_sampler_prepare(const gf_sampler* sampler, const gf_token_logit* candidates, uint32_t count,

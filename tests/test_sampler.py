@@ -42,6 +42,16 @@ def test_sampler_matches_reference_fixture_bit_exact():
     assert accepted_seen == {True, False}
 
 
+def test_proposal_words_of_a_whole_chain_match_the_reference_fixture():
+    """The words a chain of drafts is sampled with are the next words of the proposal stream in order
+    (the reference's preview_proposal_words for seed 42), and previewing consumes nothing."""
+    want = np.load(golden.HERE / "ref_sampling.npz")["words_seed_42"]
+    sampler = ge.Sampler(ge.sampler_options(0.7, seed=42))
+    assert list(sampler.proposal_words(len(want))) == [int(w) for w in want]
+    assert sampler.proposal_word() == int(want[0])
+    assert list(sampler.proposal_words(3)) == [int(w) for w in want[:3]]
+
+
 def test_sampler_streams_advance_like_the_oracle(oracle):
     """After a speculative draw both streams have moved: the next word and the next ordinary
     sample equal the oracle's restatement of the two mt19937_64 streams."""
