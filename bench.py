@@ -446,6 +446,111 @@ def run_streams(args) -> dict:
     }
 
 
+def run_tensor_parallel(args) -> dict:
+    """One stream of the 12B target sharded over the ranks (guffin_b200.tensor_parallel): the latency of the
+    two-row verification pass with an NCCL all-reduce behind every O and down projection.  One rank runs the
+    unsharded plan, so the same command gives the single-GPU figure it is compared with."""
+    from guffin_b200 import lib, model as gm, synthetic as syn, tensor_parallel as tp
+    world, rank, local = distributed()
+    dist = None
+    if world > 1:
+        import torch
+        import torch.distributed as dist
+        torch.cuda.set_device(local)
+        dist.init_process_group("nccl", device_id=torch.device("cuda", local))
+    L = lib.load()
+    lib.check(L.gf_set_device(local))
+    name = "gemma3-12b"
+    config = syn.model_config(name)
+    steps, warmup = args.steps, max(args.warmup, 3)
+    prefix = min(args.prefix, 2040)
+    context = prefix + 2 * (warmup + steps) + 16
+    rng = np.random.default_rng(SEEDS["prompt"])
+    prompt = rng.integers(0, config["vocab"], prefix).astype(np.uint32)
+    pairs = rng.integers(0, config["vocab"], (warmup + steps + 1, 2)).astype(np.uint32)
+    reducer = None
+    t0 = time.time()
+    if world > 1:
+        def exchange(ident):
+            box = [ident]
+            dist.broadcast_object_list(box, src=0)
+            return box[0]
+        reducer = tp.NcclReducer(rank, world, exchange)
+        shard = tp.Shard(config, syn.iter_model_weights(name, SEEDS["target"]), context, rank, world, reducer.hook, PREFILL_ROWS)
+        plan = shard.model
+    else:
+        plan = gm.Model(config, syn.iter_model_weights(name, SEEDS["target"]), context, PREFILL_ROWS)
+    load_s = time.time() - t0
+    t0 = time.time()
+    plan.prefill(prompt)
+    plan.synchronize()
+    prefill_s = time.time() - t0
+
+    def barrier():
+        plan.synchronize()
+        if dist is not None:
+            dist.barrier()
+
+    def step(i):
+        plan.forward(pairs[i])
+        plan.publish(1)
+
+    for i in range(warmup):
+        step(i)
+    barrier()
+    launches_before = plan.kernel_launches()
+    start, end = lib.Event(), lib.Event()
+    with ClockSampler(local) as clocks:
+        start.record(plan.stream)
+        wall0 = time.perf_counter()
+        for i in range(steps):
+            step(warmup + i)
+        end.record(plan.stream)
+        end.synchronize()
+        wall = time.perf_counter() - wall0
+        device_ms = start.elapsed_ms(end)
+    launches = plan.kernel_launches() - launches_before
+    barrier()
+    # the last pass once more with the logits read back: the shards' slices side by side are the full rows
+    plan.forward(pairs[warmup + steps])
+    logits = np.stack([plan.logits(0), plan.logits(1)])
+    status = plan.status()
+    checksum = None
+    if dist is not None:
+        import torch
+        mine = torch.from_numpy(logits).cuda()
+        gathered = [torch.empty_like(mine) for _ in range(world)]
+        dist.all_gather(gathered, mine)
+        full = torch.cat(gathered, dim=1).cpu().numpy()
+        slowest = torch.tensor([device_ms, wall], dtype=torch.float64, device="cuda")
+        dist.all_reduce(slowest, op=dist.ReduceOp.MAX)
+        device_ms, wall = slowest.tolist()
+    else:
+        full = logits
+    if rank != 0:
+        return {}
+    checksum = {"argmax": [int(v) for v in full.argmax(axis=1)], "l2": [float(np.linalg.norm(row)) for row in full]}
+    peak, peak_kind = load_peaks()
+    pass_bytes = plan.weight_bytes(True) * world
+    achieved = pass_bytes / (device_ms / steps * 1e-3) / 1e9
+    return {
+        "metric": "Gemma3-12B Q4_K_M two-row verification passes/s, one stream sharded over the GPUs", "value": steps / (device_ms * 1e-3),
+        "unit": "passes/s", "n_gpus": world, "steps": steps, "warmup": warmup, "ms_per_step": device_ms / steps,
+        "higher_is_better": True, "scaling": "strong", "vs_baseline": None, "dtype": "u4/u8 blocks -> f32, binary16 cache",
+        "data": "synthetic",
+        "config": {"workload": f"one Gemma3-12B stream at {prefix} committed tokens, two-row pass + publish, "
+                               + (f"row-sharded over {world} GPUs, NCCL all-reduce behind every O and down projection" if world > 1 else "unsharded plan"),
+                   "parallelism": f"tp{world}", "l2_policy": "inputs larger than L2: a pass streams every weight once",
+                   "load_s": round(load_s, 1), "prefill_s": round(prefill_s, 2), "status_word": int(status),
+                   "reductions_per_pass": 2 * config["layers"] if world > 1 else 0, "last_pass_logits": checksum},
+        "e2e": {"value": steps / wall, "unit": "passes/s", "h2d_bytes_per_step": 8, "d2h_bytes_per_step": 0, "ms_per_step": wall * 1e3 / steps},
+        "gpu_launches": int(launches),
+        "roofline": {"bound": "hbm", "achieved": achieved, "peak": peak * world, "unit": "GB/s", "frac": achieved / (peak * world),
+                     "peak_source": f"of {peak_kind} x {world} GPUs", "traffic": None, "kernel": "one two-row pass over every shard"},
+        "clocks": clocks.summary(),
+    }
+
+
 # ----------------------------------------------------------------------------------------- CPU arm
 
 def cpu_port_cycles(threads: int, cycles: int, warmup: int, gpu_target=None):
@@ -694,7 +799,8 @@ def main():
                         help="0: one kernel per operator (CUDA graph, the default); 1: persistent decode pass kernel; "
                              "2: pass kernel with attention launched separately")
     parser.add_argument("--case", nargs="+", default=None, help="run one single-kernel case instead of the benchmark")
-    parser.add_argument("--workload", choices=("h1", "streams"), default="h1", help="h1: the headline (configs[3]); streams: configs[4]")
+    parser.add_argument("--workload", choices=("h1", "streams", "tp"), default="h1",
+                        help="h1: the headline (configs[3]); streams: configs[4]; tp: one 12B stream sharded over the GPUs")
     parser.add_argument("--horizon", type=int, default=1, help="drafts per cycle of the h1 workload (1 = the headline; 2..7 = chains)")
     parser.add_argument("--streams", type=int, default=8, help="streams per GPU of the streams workload (64 over eight GPUs)")
     parser.add_argument("--prefix", type=int, default=8192, help="prefix tokens per stream of the streams workload")
@@ -707,6 +813,10 @@ def main():
         args.steps = 64 if args.steps is None else args.steps
         args.warmup = 3 if args.warmup is None else args.warmup
         result = run_streams(args)
+    elif args.workload == "tp" and args.impl == "ours":
+        args.steps = 100 if args.steps is None else args.steps
+        args.warmup = 5 if args.warmup is None else args.warmup
+        result = run_tensor_parallel(args)
     elif args.impl == "reference":
         args.steps = 3 if args.steps is None else args.steps
         args.warmup = 2 if args.warmup is None else args.warmup

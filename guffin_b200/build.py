@@ -55,6 +55,26 @@ def build(force: bool = False, verbose: bool = False, testing: bool = False) -> 
     return lib
 
 
+TP_LIB = os.path.join(HERE, "libguffin_tp.so")
+
+
+def build_tp(force: bool = False) -> str | None:
+    """The NCCL reduction hook of the optional tensor-parallel mode (libguffin_tp.so); None where NCCL's
+    header or library is not installed."""
+    src = os.path.join(HERE, "csrc_tp", "tp_nccl.cpp")
+    if not force and os.path.exists(TP_LIB) and os.path.getmtime(TP_LIB) >= os.path.getmtime(src):
+        return TP_LIB
+    cuda = os.path.dirname(os.path.dirname(NVCC))
+    cmd = [os.environ.get("CXX", "g++"), "-O2", "-std=c++17", "-shared", "-fPIC", "-fvisibility=hidden", f"-I{cuda}/include", src,
+           "-o", TP_LIB, f"-L{cuda}/lib64", "-lnccl", "-lcudart"]
+    done = subprocess.run(cmd, stdout=subprocess.PIPE, stderr=subprocess.STDOUT, text=True)
+    if done.returncode != 0:
+        sys.stderr.write("libguffin_tp.so not built (NCCL absent?):\n" + done.stdout[-600:])
+        return None
+    return TP_LIB
+
+
 if __name__ == "__main__":
     print(build(force="--force" in sys.argv, verbose="-v" in sys.argv))
     print(build(force="--force" in sys.argv, verbose="-v" in sys.argv, testing=True))
+    print(build_tp(force="--force" in sys.argv))

@@ -153,7 +153,7 @@ int Model::set_matrix(int kind, uint32_t layer, int dtype, const void* native_ho
     PackedMatrix* dst = nullptr;
     if (kind >= GF_MAT_ATTN_Q && layer >= c.layers) return fail(GF_ERR_INVALID, "gf_model_set_matrix: layer %u out of range", layer);
     switch (kind) {
-        case GF_MAT_TOKEN_EMBD: dst = &token_embd_; want_k = c.hidden; want_n = c.vocab; break;
+        case GF_MAT_TOKEN_EMBD: dst = &token_embd_; want_k = c.hidden; want_n = token_vocab(); break;
         case GF_MAT_OUTPUT: dst = &head_; want_k = c.hidden; want_n = c.vocab; break;
         case GF_MAT_ATTN_Q: dst = &layers_[layer].q; want_k = c.hidden; want_n = qw; break;
         case GF_MAT_ATTN_K: dst = &layers_[layer].k; want_k = c.hidden; want_n = kvw; break;
@@ -275,6 +275,7 @@ int Model::finalize() {
     release_stager();          // waits for the last uploads and repacks, frees the staging buffers
     // A binary16 embedding cannot serve as the head: the tied head is its Q8_0 quantisation
     // (resolve_gemma_output_head_policy, gemma2_metal_plan.cpp:799-828).
+    if (!has_head_ && token_vocab() != config_.vocab) return fail(GF_ERR_STATE, "a token table wider than the head needs its own output matrix");
     if (token_embd_.dtype == GF_F16 && !has_head_) GF_TRY(bind_q8_head_from_f16(token_embd_.data, token_embd_.k, token_embd_.n));
     for (uint32_t l = 0; l < c.layers; ++l) {
         const LayerWeights& w = layers_[l];
@@ -449,19 +450,28 @@ int Model::run_gemv(GemvLaunch& launch, uint32_t rows) {
     return gemv_launch(launch, matmul_counters_, static_cast<float*>(matmul_ws_), matmul_ws_bytes_, error_flag_, stream_, true);
 }
 
+// Tensor-parallel shards (a plan built on 1 / G of the heads and of the FFN width) leave partial sums behind
+// their O and down projections; the host's hook turns them into the full sums on the plan's stream.
+int Model::reduce_partial(float* buffer, size_t count) {
+    if (!reduce_hook_) return GF_OK;
+    if (recording_) { recording_failed_ = true; return GF_OK; }          // the pass kernel has no phase for it
+    const int status = reduce_hook_(reduce_user_, buffer, (uint64_t)count, stream_);
+    return status == GF_OK ? GF_OK : fail(status, "the partial-sum reduction hook failed (%d)", status);
+}
+
 int Model::emit_embedding(uint32_t rows, float scale) {
     const gf_model_config& c = config_;
     if (recording_) {
         PassPhase phase {};
         phase.kind = kPhaseEmbedding;
-        phase.embedding = EmbeddingPhase{token_embd_.data, tokens_dev_, residual_, status_dev_, token_embd_.dtype, c.hidden, c.vocab, rows, scale};
+        phase.embedding = EmbeddingPhase{token_embd_.data, tokens_dev_, residual_, status_dev_, token_embd_.dtype, c.hidden, token_vocab(), rows, scale};
         recording_->push_back(phase);
         recording_breaks_.push_back(pending_break_);
         pending_break_ = -1;
         return GF_OK;
     }
     ++launches_;
-    return launch_embedding(token_embd_.dtype, token_embd_.data, c.hidden, c.vocab, tokens_dev_, rows, scale, residual_, status_dev_, stream_, false);
+    return launch_embedding(token_embd_.dtype, token_embd_.data, c.hidden, token_vocab(), tokens_dev_, rows, scale, residual_, status_dev_, stream_, false);
 }
 
 int Model::emit_attention(const AttentionParams& params) {
@@ -643,12 +653,14 @@ int Model::encode_blocks(uint32_t rows, uint32_t flags) {
         o.prologue = kPrologueMerge; o.in = ap.partial_out; o.residual = ap.partial_ml;
         GemvLaunch gu = gate_up_weights(l);
         GF_TRY(run_gemv(o, rows));
+        GF_TRY(reduce_partial(projected_, (size_t)rows * c.hidden));            // a tensor-parallel shard holds a partial sum here
         gu.prologue = kPrologueAddNorm; gu.in = projected_; gu.residual = x; gu.gamma0 = w.post_attention_norm;
         gu.residual_out = x2; gu.gamma1 = w.ffn_norm;
         GemvLaunch down = down_weights(l);
         GF_TRY(run_gemv(gu, rows));
         down.prologue = kPrologueGeglu; down.in = gate_; down.residual = up_;
         GF_TRY(run_gemv(down, rows));
+        GF_TRY(reduce_partial(projected_, (size_t)rows * c.hidden));
     }
     if (flags & kForwardLogits) {
         GemvLaunch head = head_weights();
@@ -697,7 +709,7 @@ int Model::forward(const uint32_t* tokens_host, uint32_t rows, uint32_t flags) {
     if (!(flags & kForwardDeviceTokens)) {
         if (!tokens_host) return fail(GF_ERR_INVALID, "null token ids");
         for (uint32_t r = 0; r < rows; ++r)
-            if (tokens_host[r] >= config_.vocab) return fail(GF_ERR_INVALID, "token id %u outside the vocabulary", tokens_host[r]);
+            if (tokens_host[r] >= token_vocab()) return fail(GF_ERR_INVALID, "token id %u outside the vocabulary", tokens_host[r]);
         // The previous upload may still be reading the pinned staging words: wait for that copy only.
         GF_CUDA(cudaEventSynchronize(tokens_copied_));
         std::memcpy(tokens_pinned_, tokens_host, rows * sizeof(uint32_t));
@@ -737,14 +749,14 @@ int Model::prefill(const uint32_t* tokens_host, uint32_t count) {
     if (!tokens_host || count == 0) return fail(GF_ERR_INVALID, "empty prompt");
     if (!finalized_) return fail(GF_ERR_STATE, "plan is not finalized");
     uint32_t done = 0;
-    if (tensor_prefill_ && count - 1u >= kTensorPrefillMinRows) {
+    if (tensor_prefill_ && !reduce_hook_ && count - 1u >= kTensorPrefillMinRows) {      // a shard's partial sums go through the row passes
         // All rows but the last as 128-row chunks through the tensor cores (K/V only: no chunk needs
         // logits, so the last layer stops after its K/V rows, gemma_target_runtime.cpp:59-61,125); the
         // last prompt token then runs as an ordinary one-row pass, which yields the logits.
         if (position_ > config_.context || count > config_.context - position_)
             return fail(GF_ERR_INVALID, "prompt exceeds the bound context (%u + %u > %u)", position_, count, config_.context);
         for (uint32_t i = 0; i < count; ++i)
-            if (tokens_host[i] >= config_.vocab) return fail(GF_ERR_INVALID, "token id %u outside the vocabulary", tokens_host[i]);
+            if (tokens_host[i] >= token_vocab()) return fail(GF_ERR_INVALID, "token id %u outside the vocabulary", tokens_host[i]);
         GF_TRY(ensure_prefill_arena());
         while (done < count - 1u) {
             const uint32_t rows = std::min(prefill_.chunk_rows, count - 1u - done);
@@ -820,7 +832,7 @@ int Model::prefill_chunk(const uint32_t* tokens_host, uint32_t rows) {
     PrefillArena& a = prefill_;
     const uint32_t qw = c.heads * c.head_dim;
     GF_CUDA(cudaMemcpyAsync(a.tokens, tokens_host, rows * sizeof(uint32_t), cudaMemcpyHostToDevice, stream_));
-    GF_TRY(launch_embedding(token_embd_.dtype, token_embd_.data, c.hidden, c.vocab, a.tokens, rows, sqrtf((float)c.hidden), a.residual,
+    GF_TRY(launch_embedding(token_embd_.dtype, token_embd_.data, c.hidden, token_vocab(), a.tokens, rows, sqrtf((float)c.hidden), a.residual,
                             status_dev_, stream_, false));
     launches_ += 1;
     auto gemm = [&](std::initializer_list<std::pair<const PackedMatrix*, float*>> set, const void* operand, uint64_t k, uint32_t splits = 1) -> int {
@@ -940,7 +952,7 @@ int Model::encode_sweep(uint32_t rows, uint32_t* out_launches, uint64_t* out_byt
 }
 
 int Model::set_device_token(uint32_t row, uint32_t token) {
-    if (row >= GF_MAX_ROWS || token >= config_.vocab) return fail(GF_ERR_INVALID, "bad device token slot or id");
+    if (row >= GF_MAX_ROWS || token >= token_vocab()) return fail(GF_ERR_INVALID, "bad device token slot or id");
     GF_CUDA(cudaEventSynchronize(tokens_copied_));
     tokens_pinned_[row] = token;
     GF_CUDA(cudaMemcpyAsync(tokens_dev_ + row, tokens_pinned_ + row, sizeof(uint32_t), cudaMemcpyHostToDevice, stream_));
@@ -1063,6 +1075,12 @@ int gf_model_set_matrix(gf_model* m, int kind, uint32_t layer, int dtype, const 
 }
 int gf_model_set_matrix_requantized(gf_model* m, int kind, uint32_t layer, const void* native_q6_k_host, uint64_t k, uint64_t n) {
     return m ? m->impl.set_matrix(kind, layer, GF_Q6_K, native_q6_k_host, k, n, true) : fail(GF_ERR_INVALID, "null model");
+}
+int gf_model_set_token_table_vocab(gf_model* m, uint32_t vocab) {
+    return m ? m->impl.set_token_table_vocab(vocab) : fail(GF_ERR_INVALID, "null model");
+}
+int gf_model_set_reduce_hook(gf_model* m, gf_reduce_fn hook, void* user) {
+    return m ? m->impl.set_reduce_hook(hook, user) : fail(GF_ERR_INVALID, "null model");
 }
 int gf_model_set_vector(gf_model* m, int kind, uint32_t layer, const float* values_host, uint32_t count) {
     return m ? m->impl.set_vector(kind, layer, values_host, count) : fail(GF_ERR_INVALID, "null model");

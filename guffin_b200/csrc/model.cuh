@@ -122,6 +122,24 @@ public:
     int streams_read_logits(StreamSet& set, uint32_t stream, float* host);
     size_t streams_kv_bytes(const StreamSet& set) const;
 
+    // Tensor-parallel shards: the token table may cover more ids than the (sharded) head, and partial sums
+    // behind the O and down projections go through the host's reduction hook.
+    int set_token_table_vocab(uint32_t vocab) {
+        if (token_embd_.data) return fail(GF_ERR_STATE, "set the token table's vocabulary before binding it");
+        if (vocab < config_.vocab) return fail(GF_ERR_INVALID, "the token table cannot be narrower than the head");
+        token_table_vocab_ = vocab;
+        return GF_OK;
+    }
+    int set_reduce_hook(gf_reduce_fn hook, void* user) {
+        reduce_hook_ = hook; reduce_user_ = user;
+        for (auto& per_rows : graphs_)
+            for (cudaGraphExec_t& exec : per_rows)
+                if (exec) { cudaGraphExecDestroy(exec); exec = nullptr; }
+        invalidate_passes();
+        return GF_OK;
+    }
+    uint32_t token_vocab() const { return token_table_vocab_ ? token_table_vocab_ : config_.vocab; }
+
     // Enqueues the selection for rows whose requests already sit in requests_dev().
     int select_device(uint32_t rows);
     // Uploads one token id into the device token buffer slot `row` (asynchronous).
@@ -141,6 +159,10 @@ private:
         std::vector<AttentionParams> attention_launches;
     };
 
+    int reduce_partial(float* buffer, size_t count);
+    uint32_t token_table_vocab_ = 0;
+    gf_reduce_fn reduce_hook_ = nullptr;
+    void* reduce_user_ = nullptr;
     int bind_q8_head_from_f16(const void* f16_dev, uint64_t k, uint64_t n);
     int bind_rings(const std::vector<void*>& ring_k, const std::vector<void*>& ring_v, uint32_t position);
     int encode_stream_group(StreamSet& set, uint32_t first, uint32_t rows);

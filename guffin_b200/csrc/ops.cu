@@ -245,6 +245,11 @@ int launch_kv_publish(const KvPublishLayer* layers_dev, uint32_t layer_count, ui
     return launch_kernel(advance_position_kernel, dim3(1), dim3(32), 0, stream, false, base_position, rows);
 }
 
+__global__ void __launch_bounds__(256) add_kernel(const float* __restrict__ left, const float* __restrict__ right, float* __restrict__ out, uint64_t count) {
+    for (uint64_t i = blockIdx.x * (uint64_t)blockDim.x + threadIdx.x; i < count; i += (uint64_t)gridDim.x * blockDim.x)
+        out[i] = __fadd_rn(left[i], right[i]);
+}
+
 // ------------------------------------------------------------------ launchers
 
 int launch_embedding(int dtype, const void* packed, uint32_t k, uint32_t vocab, const uint32_t* tokens, uint32_t rows,
@@ -377,6 +382,13 @@ using namespace gf;
 // ------------------------------------------------------------------ C entry points (operator level)
 
 extern "C" {
+
+int gf_add(const float* left_dev, const float* right_dev, float* out_dev, uint64_t count, void* stream) {
+    if (!left_dev || !right_dev || !out_dev) return fail(GF_ERR_INVALID, "gf_add: null buffer");
+    if (count == 0) return GF_OK;
+    const uint32_t blocks = (uint32_t)std::min<uint64_t>((count + 255u) / 256u, 4096u);
+    return launch_kernel(add_kernel, dim3(blocks), dim3(256), 0, as_stream(stream), false, left_dev, right_dev, out_dev, count);
+}
 
 int gf_embedding(int dtype, const void* packed_dev, uint32_t k, uint32_t vocab, const uint32_t* tokens_dev,
                  uint32_t rows, float scale, float* out_dev, uint32_t* status_dev, void* stream) {

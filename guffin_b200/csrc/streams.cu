@@ -43,6 +43,7 @@ static int stream_alloc(StreamSet& set, T** out, size_t count) {
 
 int Model::streams_create(uint32_t count, StreamSet** out) {
     if (!finalized_) return fail(GF_ERR_STATE, "plan is not finalized");
+    if (reduce_hook_) return fail(GF_ERR_STATE, "conversation streams are not offered on a tensor-parallel shard");
     if (!out || count == 0 || count > kMaxStreams) return fail(GF_ERR_INVALID, "between 1 and %u streams", kMaxStreams);
     const gf_model_config& c = config_;
     std::unique_ptr<StreamSet> set(new StreamSet());
@@ -236,7 +237,7 @@ int Model::encode_stream_batch(StreamSet& set) {
     const gf_model_config& c = config_;
     PrefillArena& a = prefill_;
     const uint32_t rows = set.count, qw = c.heads * c.head_dim;
-    GF_TRY(launch_embedding(token_embd_.dtype, token_embd_.data, c.hidden, c.vocab, a.tokens, rows, sqrtf((float)c.hidden), a.residual,
+    GF_TRY(launch_embedding(token_embd_.dtype, token_embd_.data, c.hidden, token_vocab(), a.tokens, rows, sqrtf((float)c.hidden), a.residual,
                             status_dev_, stream_, false));
     launches_ += 1;
     auto gemm = [&](std::initializer_list<std::pair<const PackedMatrix*, float*>> matrices, const void* operand, uint64_t k, uint32_t splits = 1) -> int {
@@ -316,7 +317,7 @@ int Model::streams_decode(StreamSet& set, const uint32_t* tokens_host) {
     if (poisoned_) return fail(GF_ERR_STATE, "plan is poisoned after an unknown GPU outcome; reset it");
     if (!tokens_host) return fail(GF_ERR_INVALID, "null token ids");
     for (uint32_t s = 0; s < set.count; ++s) {
-        if (tokens_host[s] >= config_.vocab) return fail(GF_ERR_INVALID, "token id %u outside the vocabulary", tokens_host[s]);
+        if (tokens_host[s] >= token_vocab()) return fail(GF_ERR_INVALID, "token id %u outside the vocabulary", tokens_host[s]);
         if (set.positions_host[s] >= config_.context) return fail(GF_ERR_INVALID, "stream %u has filled its context (%u)", s, config_.context);
     }
     if (set.mode == 1) {

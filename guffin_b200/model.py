@@ -56,6 +56,9 @@ lib.register({
     "gf_model_set_matrix_requantized": (i32, [vp, i32, u32, vp, u64, u64]),
     "gf_model_set_vector": (i32, [vp, i32, u32, vp, u32]),
     "gf_model_load_gguf": (i32, [vp, C.c_char_p, vp]),
+    "gf_model_set_reduce_hook": (i32, [vp, vp, vp]),
+    "gf_model_set_token_table_vocab": (i32, [vp, u32]),
+    "gf_add": (i32, [vp, vp, vp, u64, vp]),
     "gf_model_finalize": (i32, [vp]),
     "gf_model_reset": (i32, [vp]),
     "gf_model_position": (i32, [vp, C.POINTER(u32)]),
@@ -123,13 +126,15 @@ class Model:
     guffin_b200.synthetic.make_model_weights (GGUF tensor names), any iterable of
     (name, value) pairs such as synthetic.iter_model_weights, or the path of a GGUF file."""
 
-    def __init__(self, config: dict, weights, context: int, row_capacity: int = 2):
+    def __init__(self, config: dict, weights, context: int, row_capacity: int = 2, before_binding=None):
         self.L = load()
         self.config = dict(config)
         self.cfg = make_config(config, context, row_capacity)
         handle = vp()
         check(self.L.gf_model_create(C.byref(self.cfg), C.byref(handle)))
         self.handle = handle.value
+        if before_binding is not None:          # options that must precede the weights (guffin_b200.tensor_parallel)
+            before_binding(self)
         if isinstance(weights, (str, bytes)) or hasattr(weights, "__fspath__"):     # a GGUF file
             import os
             bound = u32()

@@ -203,6 +203,8 @@ GF_API int gf_attention(const float* q_dev, const void* ring_k_dev, const void* 
 /* encode_gelu_tanh_multiply (metal_command_context.hpp:289-295; ops/elementwise.cpp:79). */
 GF_API int gf_gelu_tanh_multiply(const float* gate_dev, const float* up_dev, float* out_dev,
                                  uint64_t count, void* stream);
+/* encode_add (metal_command_context.hpp:301-306; ops/elementwise.cpp): out = left + right, elementwise. */
+GF_API int gf_add(const float* left_dev, const float* right_dev, float* out_dev, uint64_t count, void* stream);
 /* encode_verifier_kv_scatter (metal_command_context.hpp:269-279): publishes private rows
  * 0..rows-1 to ring slots (base + row) & (ring_rows - 1). */
 GF_API int gf_kv_scatter(const void* private_k_dev, const void* private_v_dev, void* ring_k_dev,
@@ -273,6 +275,19 @@ GF_API int gf_model_set_vector(gf_model* model, int kind, uint32_t layer, const 
  * gemma2_metal_plan.cpp:301-308: the 9B file's Q6_K ffn_down). */
 GF_API int gf_model_set_matrix_requantized(gf_model* model, int kind, uint32_t layer, const void* native_q6_k_host,
                                            uint64_t k, uint64_t n);
+/* ---- optional tensor parallelism for one stream's latency.  No counterpart in the reference (one device).  A
+ * shard is an ordinary plan built on 1 / G of the query and KV heads, of the FFN width and of the head's
+ * vocabulary: Q/K/V, gate and up are split by output column, O and down by input row, so a shard's O and down
+ * projections leave PARTIAL sums of the full hidden vector.  The plan calls `hook(user, buffer_dev, count,
+ * stream)` behind each of them (2 x layers times per pass); the host sums the buffers of all shards in place,
+ * in stream order -- an NCCL all-reduce over NVLink in the multi-process bench, any fixed-order sum elsewhere.
+ * The hook is recorded into the plan's CUDA graphs when what it enqueues can be captured (NCCL can).
+ * gf_model_set_token_table_vocab lets the token embedding cover the full vocabulary while the head (config.vocab
+ * columns, bound as GF_MAT_OUTPUT) is this shard's slice; call it before binding the table.  Candidate ids of a
+ * shard are local to its slice. ---- */
+typedef int (*gf_reduce_fn)(void* user, float* buffer_dev, uint64_t count, void* stream);
+GF_API int gf_model_set_reduce_hook(gf_model* model, gf_reduce_fn hook, void* user);
+GF_API int gf_model_set_token_table_vocab(gf_model* model, uint32_t vocab);
 /* Binds every tensor of a GGUF v2/v3 file that the block schedule knows (llama.cpp tensor names,
  * F32 vectors, Q8_0 / Q4_K / Q6_K matrices and binary16 embedding / head tables) through the two calls above: the path's share of
  * read_file_backed_gguf_model (model_format/gguf_reader.hpp:85) and of the WeightMaterializer.

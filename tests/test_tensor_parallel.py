@@ -1,0 +1,131 @@
+"""The optional tensor-parallel mode (guffin_b200.tensor_parallel): weight sharding and candidate merging on
+the CPU against the oracle; on a GPU, two shards of a model on one device (each driven by its own host thread,
+partial sums summed in rank order) against the unsharded plan."""
+import threading
+
+import numpy as np
+import pytest
+
+from guffin_b200 import synthetic as syn
+from guffin_b200 import tensor_parallel as tp
+
+
+def test_shard_config_and_errors():
+    config = syn.model_config("gemma3-12b")
+    local = tp.shard_config(config, 2)
+    assert (local["heads"], local["kv_heads"], local["ffn"], local["vocab"], local["hidden"]) == (8, 4, 7680, 131072, 3840)
+    with pytest.raises(ValueError):
+        tp.shard_config(syn.model_config("gemma3-270m"), 2)          # one KV head does not split
+    with pytest.raises(ValueError):
+        tp.shard_config(config, 3)
+
+
+@pytest.mark.parametrize("dtype", [syn.Q4_K, syn.Q6_K, syn.Q8_0])
+def test_shards_of_a_matrix_against_the_oracle(dtype):
+    """Column shards reproduce their columns of the full product bit for bit; row shards sum to it."""
+    from oracle.pyoracle import Oracle
+    oracle = Oracle()
+    rng = np.random.default_rng(5)
+    k, n, size = 1024, 48, 2
+    native = syn.make_weight(rng, dtype, k, n)
+    x = rng.standard_normal((2, k)).astype(np.float32)
+    full = oracle.matmul(dtype, x, native, k, n)
+    columns = [oracle.matmul(dtype, x, tp._columns((dtype, k, n, native), r, size)[3], k, n // size) for r in range(size)]
+    assert np.array_equal(np.concatenate(columns, axis=1), full)
+    partial = [oracle.matmul(dtype, np.ascontiguousarray(x[:, r * k // size:(r + 1) * k // size]),
+                             tp._rows((dtype, k, n, native), r, size)[3], k // size, n) for r in range(size)]
+    total = partial[0].astype(np.float64) + partial[1]
+    assert np.linalg.norm(total - full) <= 1e-6 * np.linalg.norm(full)
+
+
+def test_shard_weights_names_and_shapes():
+    config = syn.model_config("tiny-target")
+    weights = syn.make_model_weights("tiny-target", 3)
+    shard = dict(tp.shard_weights(weights, 1, 2))
+    assert shard["blk.0.attn_q.weight"][1:3] == (512, 512) and shard["blk.0.attn_k.weight"][1:3] == (512, 256)
+    assert shard["blk.0.attn_output.weight"][1:3] == (512, 512) and shard["blk.0.ffn_down.weight"][1:3] == (512, 512)
+    assert shard["blk.0.ffn_gate.weight"][1:3] == (512, 512)
+    assert shard["token_embd.weight"][2] == config["vocab"] and shard["output.weight"][2] == config["vocab"] // 2
+    assert np.array_equal(shard["blk.0.attn_norm.weight"], weights["blk.0.attn_norm.weight"])
+
+
+def test_merge_candidates_is_the_full_top_k():
+    rng = np.random.default_rng(2)
+    logits = rng.standard_normal(4096).astype(np.float32)
+    logits[100] = logits[3000] = logits.max() + 1.0                   # a tie across the two shards
+    pair = np.dtype([("token", np.uint32), ("logit", np.float32)])
+    lists = []
+    for rank in range(2):
+        part = logits[rank * 2048:(rank + 1) * 2048]
+        order = np.lexsort((np.arange(2048), -part.astype(np.float64)))[:64]
+        lists.append(np.array([(o + rank * 2048, part[o]) for o in order], pair))
+    merged = tp.merge_candidates(lists, 64)
+    order = np.lexsort((np.arange(4096), -logits.astype(np.float64)))[:64]
+    assert np.array_equal(merged["token"], order.astype(np.uint32)) and merged["token"][0] == 100 and merged["token"][1] == 3000
+
+
+@pytest.mark.gpu
+@pytest.mark.parametrize("name", ["tiny-target", "tiny-gemma2"])
+def test_two_shards_on_one_device_match_the_unsharded_plan(name):
+    from guffin_b200 import model as gm
+    config = syn.model_config(name)
+    weights = syn.make_model_weights(name, 11)
+    rng = np.random.default_rng(4)
+    prompt = rng.integers(0, config["vocab"], 21).astype(np.uint32)
+    steps = [rng.integers(0, config["vocab"], 2).astype(np.uint32) for _ in range(3)]
+    request = gm.SelectionRequest(retain=64, history_count=0)
+
+    full = gm.Model(config, weights, 64, 8)
+    full.prefill(prompt)
+    want = [(full.logits(full.prefill_logits_row), None)]
+    for tokens in steps:
+        full.forward(tokens)
+        picked = full.select([request, request])
+        want.append((np.stack([full.logits(0), full.logits(1)]), [p.pairs() for p in picked]))
+        full.publish(1)
+    want_kv = full.read_kv(1, 0, full.position)
+
+    size = 2
+    reducer = tp.ThreadReducer(size, 8 * config["hidden"])
+    shards = [tp.Shard(config, weights, 64, rank, size, reducer.hook(rank), row_capacity=8) for rank in range(size)]
+    for shard in shards:
+        shard.model.use_graph(False)
+    got = [[] for _ in range(size)]
+    errors = []
+
+    def drive(rank):
+        try:
+            model = shards[rank].model
+            model.prefill(prompt)
+            got[rank].append((model.logits(model.prefill_logits_row), None))
+            for tokens in steps:
+                model.forward(tokens)
+                picked = model.select([request, request])
+                got[rank].append((np.stack([model.logits(0), model.logits(1)]), [shards[rank].global_candidates(p) for p in picked]))
+                model.publish(1)
+            assert model.status() == 0
+        except Exception as error:          # a failed shard must not leave the other at the barrier
+            reducer.barrier.abort()
+            errors.append(error)
+
+    threads = [threading.Thread(target=drive, args=(rank,)) for rank in range(size)]
+    for t in threads:
+        t.start()
+    for t in threads:
+        t.join(timeout=300)
+    assert not errors, errors
+    assert reducer.calls == 2 * config["layers"] * (3 + len(steps))           # 21 prompt tokens = 3 passes of up to 8 rows
+    for step, (logits, candidates) in enumerate(want):
+        merged = np.concatenate([got[r][step][0] for r in range(size)], axis=-1)
+        assert np.linalg.norm(merged - logits) <= 2e-5 * np.linalg.norm(logits), step
+        if candidates is not None:
+            for row in range(2):
+                both = tp.merge_candidates([got[r][step][1][row] for r in range(size)], 64)
+                assert np.array_equal(both["token"][:8], candidates[row]["token"][:8])
+                assert np.allclose(both["logit"], candidates[row]["logit"], rtol=1e-4, atol=1e-5)
+    # each shard's KV ring holds its own heads of the unsharded ring
+    kv_width = config["kv_heads"] * config["head_dim"] // size
+    for rank in range(size):
+        k, v = shards[rank].model.read_kv(1, 0, shards[rank].model.position)
+        assert np.allclose(k, want_kv[0][:, rank * kv_width:(rank + 1) * kv_width], rtol=2e-3, atol=2e-3)
+        assert np.allclose(v, want_kv[1][:, rank * kv_width:(rank + 1) * kv_width], rtol=2e-3, atol=2e-3)
