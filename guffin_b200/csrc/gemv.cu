@@ -116,14 +116,14 @@ size_t gemv_counter_bytes(const GemvLaunch& launch) {
     return counters_bytes(plan);
 }
 
-template <int ROWS>
+template <int ROWS, bool TP = false>
 static int launch_instance(const WeightStreamParams& p, const GemvPlan& plan, cudaStream_t stream, bool programmatic) {
     static std::once_flag once[64];
     int device = 0;
     cudaGetDevice(&device);
     cudaError_t attr_error = cudaSuccess;
     std::call_once(once[device & 63], [&] {
-        attr_error = cudaFuncSetAttribute(weight_stream_kernel<ROWS>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)kGemvSmemLimit);
+        attr_error = cudaFuncSetAttribute(weight_stream_kernel<ROWS, TP>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)kGemvSmemLimit);
     });
     GF_CUDA(attr_error);
     cudaLaunchConfig_t config = {};
@@ -136,7 +136,7 @@ static int launch_instance(const WeightStreamParams& p, const GemvPlan& plan, cu
     attribute.val.programmaticStreamSerializationAllowed = 1;
     config.attrs = &attribute;
     config.numAttrs = programmatic ? 1 : 0;
-    GF_CUDA(cudaLaunchKernelEx(&config, weight_stream_kernel<ROWS>, p));
+    GF_CUDA(cudaLaunchKernelEx(&config, weight_stream_kernel<ROWS, TP>, p));
     return GF_OK;
 }
 
@@ -144,7 +144,11 @@ int gemv_prepare(const GemvLaunch& launch, uint32_t* counters, float* partial, s
                  WeightStreamParams& p, GemvPlan& plan) {
     const int status = gemv_plan(launch, plan);
     if (status != GF_OK) return status;
-    if (!launch.in || !error_flag) return fail(GF_ERR_INVALID, "gf_matmul: null buffer");
+    if ((!launch.in && launch.gather.count == 0u) || !error_flag) return fail(GF_ERR_INVALID, "gf_matmul: null buffer");
+    if (launch.gather.count > (uint32_t)kGemvMaxShards || launch.scatter.count >= (uint32_t)kGemvMaxShards
+        || (launch.gather.count != 0u && (launch.prologue != kPrologueAddNorm || !launch.gather.arrived || !launch.gather.passed))
+        || (launch.scatter.count != 0u && launch.count != 1u))
+        return fail(GF_ERR_INVALID, "gf_matmul: bad shard exchange");
     // The activation prologue reads four floats at a time.
     auto aligned = [](const void* ptr) { return (reinterpret_cast<uintptr_t>(ptr) & 15u) == 0u; };
     if (!aligned(launch.in) || !aligned(launch.residual) || !aligned(launch.gamma0) || !aligned(launch.gamma1) || !aligned(launch.residual_out))
@@ -194,6 +198,8 @@ int gemv_prepare(const GemvLaunch& launch, uint32_t* counters, float* partial, s
     p.residual_out = launch.residual_out;
     p.eps = launch.eps;
     p.error_flag = error_flag;
+    p.scatter = launch.scatter;
+    p.gather = launch.gather;
     if (launch.heads.rotation) {
         const GemvLaunch::Heads& h = launch.heads;
         if (launch.count != 3 || !h.q_out || !h.private_k || !h.private_v || !h.base_position || !h.status || !h.head_counters
@@ -220,6 +226,14 @@ int gemv_launch(const GemvLaunch& launch, uint32_t* counters, float* partial, si
     GemvPlan plan;
     const int status = gemv_prepare(launch, counters, partial, partial_bytes, error_flag, p, plan);
     if (status != GF_OK) return status;
+    if (p.scatter.count != 0u || p.gather.count != 0u)        // a tensor-parallel shard's exchange rides on the launch
+        switch (launch.rows) {
+            case 1: return launch_instance<1, true>(p, plan, stream, programmatic);
+            case 2: return launch_instance<2, true>(p, plan, stream, programmatic);
+            case 3: return launch_instance<3, true>(p, plan, stream, programmatic);
+            case 4: return launch_instance<4, true>(p, plan, stream, programmatic);
+            default: return launch_instance<8, true>(p, plan, stream, programmatic);
+        }
     switch (launch.rows) {
         case 1: return launch_instance<1>(p, plan, stream, programmatic);
         case 2: return launch_instance<2>(p, plan, stream, programmatic);

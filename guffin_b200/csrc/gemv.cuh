@@ -45,6 +45,8 @@ enum GemvPrologue : uint32_t {
                              // unnormalised outputs, `residual` the (maximum, sum) pair of every slot (empty: sum 0)
 };
 
+constexpr int kGemvMaxShards = 8;
+
 struct GemvMatrix {
     const uint8_t* weight;   // streaming layout
     float* out;              // [rows][n]
@@ -84,6 +86,24 @@ struct WeightStreamParams {
     float* partial;            // [chunks][rows][total_pairs * 16] when chunks > 1
     uint32_t* counters;        // [total_pairs] arrival counts, zero between launches
     int* error_flag;           // set to 1 when a bounded wait gives up
+    // Tensor-parallel shards (the TP instantiation only; both off when their count is 0).  A shard's O and down
+    // projections hold partial sums of the hidden rows.  The producing launch mirrors every output value it writes
+    // into the same place of each peer GPU's copy (plain stores over NVLink) and, as each CTA ends, adds one to
+    // each peer's arrival word.  The consuming launch waits (bounded) until its own arrival word shows every CTA
+    // of every peer, then reads its input as the sum of all shards' parts in shard order, so every shard holds
+    // the same bits; the CTA that is last through the wait clears the word for its next use.
+    struct Scatter {
+        float* out[kGemvMaxShards - 1];          // matrix 0's output [rows][n] in each peer's memory
+        uint32_t* arrived[kGemvMaxShards - 1];   // each peer's arrival word
+        uint32_t count;                          // peers
+    } scatter;
+    struct Gather {
+        const float* parts[kGemvMaxShards];      // this GPU's copies of every shard's part, own included, in shard order
+        uint32_t* arrived;                       // this GPU's arrival word: peers' CTAs add to it
+        uint32_t* passed;                        // CTAs of this launch that are through the wait
+        uint32_t count, expected;                // shards; peers x CTAs of the producing launch
+        uint32_t wait_limit;                     // polls before the wait gives up
+    } gather;
 };
 
 // Columns of the B operand kept per 32-element group: four signed bytes per row, in whole n-tiles
@@ -449,6 +469,22 @@ template <bool FROM_L2>
 __device__ __forceinline__ void load8f_act(const float* p, float (&v)[8]) {
     if (FROM_L2) load8f_cg(p, v); else load8f(p, v);
 }
+// The input rows of a launch: `in`, or on a tensor-parallel shard the sum of every shard's part in shard order
+// (parts written by peer GPUs arrive in L2: read there).
+template <bool FROM_L2, bool TP>
+__device__ __forceinline__ void load8f_in(const WeightStreamParams& p, size_t offset, float (&v)[8]) {
+    if (TP && p.gather.count != 0u) {
+        load8f_cg(p.gather.parts[0] + offset, v);
+        for (uint32_t s = 1; s < p.gather.count; ++s) {
+            float w[8];
+            load8f_cg(p.gather.parts[s] + offset, w);
+#pragma unroll
+            for (int i = 0; i < 8; ++i) v[i] = __fadd_rn(v[i], w[i]);
+        }
+        return;
+    }
+    load8f_act<FROM_L2>(p.in + offset, v);
+}
 __device__ __forceinline__ void store8f(float* p, const float (&v)[8]) {
     *reinterpret_cast<float4*>(p) = make_float4(v[0], v[1], v[2], v[3]);
     *reinterpret_cast<float4*>(p + 4) = make_float4(v[4], v[5], v[6], v[7]);
@@ -605,7 +641,7 @@ __device__ __forceinline__ void merge_head_piece(const WeightStreamParams& p, ui
 // memory (a few tens of KB out of L2).  In the register-resident case everything a thread needs
 // of the launch ahead's output is loaded once and kept in registers through both norms (the rest
 // came in with stage_early); otherwise the row is re-read for each pass.
-template <int ROWS, bool PASS>
+template <int ROWS, bool PASS, bool TP = false>
 __device__ __forceinline__ void stage_activations(const WeightStreamParams& p, uint32_t first, uint32_t count,
                                                   const GemvStage& st, float* scratch, GemvEarly<ROWS>& early) {
     const bool norms = p.prologue == kPrologueNorm || p.prologue == kPrologueAddNorm;
@@ -625,7 +661,7 @@ __device__ __forceinline__ void stage_activations(const WeightStreamParams& p, u
         if (live) {
 #pragma unroll
             for (int r = 0; r < ROWS; ++r)
-                if ((uint32_t)r < p.active_rows) load8f_act<PASS>(p.in + (size_t)r * p.k + o, x[r]);
+                if ((uint32_t)r < p.active_rows) load8f_in<PASS, TP>(p, (size_t)r * p.k + o, x[r]);
         }
         float ss[ROWS];
 #pragma unroll
@@ -664,7 +700,7 @@ __device__ __forceinline__ void stage_activations(const WeightStreamParams& p, u
             ss[r] = 0.0f;
             for (uint32_t c = threadIdx.x; c < row_pieces && (uint32_t)r < p.active_rows; c += blockDim.x) {
                 float x[8];
-                load8f_act<PASS>(p.in + (size_t)r * p.k + c * 8u, x);
+                load8f_in<PASS, TP>(p, (size_t)r * p.k + c * 8u, x);
                 ss[r] = sum_squares(x, ss[r]);
             }
         }
@@ -678,7 +714,7 @@ __device__ __forceinline__ void stage_activations(const WeightStreamParams& p, u
                 ss[r] = 0.0f;
                 for (uint32_t c = threadIdx.x; c < row_pieces && (uint32_t)r < p.active_rows; c += blockDim.x) {
                     float x[8], a[8], gm[8];
-                    load8f_act<PASS>(p.in + (size_t)r * p.k + c * 8u, x);
+                    load8f_in<PASS, TP>(p, (size_t)r * p.k + c * 8u, x);
                     load8f_act<PASS>(p.residual + (size_t)r * p.k + c * 8u, a);
                     load8f(p.gamma0 + c * 8u, gm);
 #pragma unroll
@@ -707,7 +743,7 @@ __device__ __forceinline__ void stage_activations(const WeightStreamParams& p, u
             float i0 = 1.0f, i1 = 1.0f;
 #pragma unroll
             for (int rr = 0; rr < ROWS; ++rr) if (rr == (int)r) { i0 = inv0[rr]; i1 = inv1[rr]; }
-            load8f_act<PASS>(p.in + gi, v);
+            load8f_in<PASS, TP>(p, gi, v);
             if (p.prologue == kPrologueNorm) {
                 float gm[8];
                 load8f(p.gamma1 + c, gm);
@@ -1223,11 +1259,45 @@ __device__ __forceinline__ WeightRing ring_open(const StreamSmem& sm, uint32_t s
     return ring;
 }
 
+// ---- system-scope words shared with peer GPUs (tensor-parallel shards).
+__device__ __forceinline__ uint32_t load_acquire_system(const uint32_t* word) {
+    uint32_t value;
+    asm volatile("ld.acquire.sys.global.u32 %0, [%1];" : "=r"(value) : "l"(word) : "memory");
+    return value;
+}
+__device__ __forceinline__ void red_release_system(uint32_t* word, uint32_t value) {
+    asm volatile("red.release.sys.global.add.u32 [%0], %1;" ::"l"(word), "r"(value) : "memory");
+}
+__device__ __forceinline__ void store_relaxed_system(uint32_t* word, uint32_t value) {
+    asm volatile("st.relaxed.sys.global.u32 [%0], %1;" ::"l"(word), "r"(value) : "memory");
+}
+// The consuming side of the shard exchange: thread 0 polls this GPU's arrival word until every CTA of every
+// peer's producing launch is counted, or the poll limit runs out (the error word is set and the launch goes on
+// with what has arrived: a dead peer costs a wrong pass, never a hung GPU).  The CTA that is last through
+// clears the word and the count: the next exchange on this word starts only after the peers have consumed an
+// exchange on the other word, which this launch's successor has to feed.
+__device__ __forceinline__ void shard_parts_wait(const WeightStreamParams& p) {
+    if (threadIdx.x == 0) {
+        uint32_t polls = 0;
+        while (load_acquire_system(p.gather.arrived) < p.gather.expected) {
+            if (++polls > p.gather.wait_limit) { atomicExch(p.error_flag, 1); break; }
+            if (polls > 64u) __nanosleep(200);
+        }
+        __threadfence();
+        if (atomicAdd(p.gather.passed, 1u) == gridDim.x - 1u) {
+            *p.gather.passed = 0u;
+            store_relaxed_system(p.gather.arrived, 0u);
+        }
+    }
+    __syncthreads();
+}
+
 // The launch of its own: one matrix set per kernel, the schedule replayed as a CUDA graph.  Its body is
 // kept apart from stream_phase (the pass kernel's phase) although the two decompose and compute alike:
 // with everything a launch needs in the constant bank and in registers this form measured 2.3 % faster
 // over a 12B pass than the shared one.
-template <int ROWS>
+// TP: the instantiation tensor-parallel shards launch (WeightStreamParams::scatter / gather); the plain one carries none of it.
+template <int ROWS, bool TP = false>
 __global__ void __launch_bounds__(kGemvWarps * 32, 1) weight_stream_kernel(const __grid_constant__ WeightStreamParams p) {
     constexpr int NT = (4 * ROWS + 7) / 8;
     constexpr uint32_t NCP = gemv_fragment_columns(ROWS);
@@ -1306,8 +1376,9 @@ __global__ void __launch_bounds__(kGemvWarps * 32, 1) weight_stream_kernel(const
     stage_early<ROWS, false>(p, intra ? 0u : first_unit * p.unit_elems, early_inputs);
 
     pdl_wait();
+    if (TP && p.gather.count != 0u) shard_parts_wait(p);
     const GemvStage stage{frags, sums, block_scales, &bad_rows, padded};
-    stage_activations<ROWS, false>(p, intra ? 0u : first_unit * p.unit_elems, intra ? p.k : chunk_count * p.unit_elems, stage, scratch, early_inputs);
+    stage_activations<ROWS, false, TP>(p, intra ? 0u : first_unit * p.unit_elems, intra ? p.k : chunk_count * p.unit_elems, stage, scratch, early_inputs);
     __syncthreads();
     pdl_launch_dependents();
 
@@ -1418,6 +1489,11 @@ __global__ void __launch_bounds__(kGemvWarps * 32, 1) weight_stream_kernel(const
                 if (L.t == (uint32_t)(r & 3) && (uint32_t)r < p.active_rows) {
                     if (columnA < mat.n) mat.out[(size_t)r * mat.n + columnA] = totalA[r];
                     if (columnB < mat.n) mat.out[(size_t)r * mat.n + columnB] = totalB[r];
+                    if (TP)
+                        for (uint32_t s = 0; s < p.scatter.count; ++s) {
+                            if (columnA < mat.n) p.scatter.out[s][(size_t)r * mat.n + columnA] = totalA[r];
+                            if (columnB < mat.n) p.scatter.out[s][(size_t)r * mat.n + columnB] = totalB[r];
+                        }
                 }
             if (p.heads.enabled) head_pair_done<ROWS>(p, mat, matrix_of(pair), local_pair, lane);
             continue;
@@ -1445,11 +1521,21 @@ __global__ void __launch_bounds__(kGemvWarps * 32, 1) weight_stream_kernel(const
                 for (uint32_t c = 0; c < p.chunks; ++c)
                     sum += __ldcg(&p.partial[((size_t)c * ROWS + r) * width + (size_t)pair * 16u + col]);
                 const uint32_t out_column = local_pair * 16u + col;
-                if (out_column < mat.n && r < p.active_rows) mat.out[(size_t)r * mat.n + out_column] = sum;
+                if (out_column < mat.n && r < p.active_rows) {
+                    mat.out[(size_t)r * mat.n + out_column] = sum;
+                    if (TP)
+                        for (uint32_t s = 0; s < p.scatter.count; ++s) p.scatter.out[s][(size_t)r * mat.n + out_column] = sum;
+                }
             }
             if (lane == 0) p.counters[pair] = 0u;
             if (p.heads.enabled) head_pair_done<ROWS>(p, mat, matrix_of(pair), local_pair, lane);
         }
+    }
+    if (TP && p.scatter.count != 0u) {
+        // Every value this CTA sent to the peers is visible there before its arrival is counted.
+        __threadfence_system();
+        __syncthreads();
+        if (threadIdx.x < p.scatter.count) red_release_system(p.scatter.arrived[threadIdx.x], 1u);
     }
     if (failed) {
         // Give outstanding copies a bounded chance to land before the shared memory is released.
@@ -1483,6 +1569,9 @@ struct GemvLaunch {
         uint32_t table_rows = 0;
         int kv_f16 = 0;
     } heads;
+    // Shard exchange of a tensor-parallel plan (see WeightStreamParams): off when the counts are 0.
+    WeightStreamParams::Scatter scatter = {};
+    WeightStreamParams::Gather gather = {};
 };
 struct GemvPlan { uint32_t units, unit_elems, total_pairs, chunks, chunk_units, grid, smem, slot_bytes, slot_units, intra, staged_units; };
 

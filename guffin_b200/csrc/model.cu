@@ -30,6 +30,9 @@ Model::~Model() {
             if (graph) cudaGraphExecDestroy(graph);
     invalidate_passes();
     for (void* p : allocations_) cudaFree(p);
+    for (uint32_t s = 0; s < shard_.size; ++s)
+        if (shard_.opened[s]) cudaIpcCloseMemHandle(shard_.mapped[s]);
+    if (shard_.arena) cudaFree(shard_.arena);
     if (tokens_copied_) cudaEventDestroy(tokens_copied_);
     if (requests_copied_) cudaEventDestroy(requests_copied_);
     if (tokens_pinned_) cudaFreeHost(tokens_pinned_);
@@ -459,6 +462,103 @@ int Model::reduce_partial(float* buffer, size_t count) {
     return status == GF_OK ? GF_OK : fail(status, "the partial-sum reduction hook failed (%d)", status);
 }
 
+// ---- the exchange fused into the projection launches (see WeightStreamParams::Scatter / Gather)
+
+int Model::shard_prepare(uint32_t rank, uint32_t size, void* ipc_handle_out) {
+    if (size == 0 || size > (uint32_t)kGemvMaxShards || rank >= size) return fail(GF_ERR_INVALID, "shard %u of %u", rank, size);
+    if (shard_.arena) return fail(GF_ERR_STATE, "this plan already has an exchange arena");
+    ShardExchange& x = shard_;
+    x.rank = rank; x.size = size;
+    x.part_floats = (((size_t)config_.row_capacity * config_.hidden) + 63u) & ~(size_t)63u;
+    x.words_offset = 2u * size * x.part_floats * sizeof(float);
+    x.bytes = x.words_offset + 2u * 256u;
+    void* base = nullptr;
+    GF_CUDA(cudaMalloc(&base, x.bytes));                 // an allocation of its own: peers map exactly this
+    GF_CUDA(cudaMemset(base, 0, x.bytes));
+    x.arena = static_cast<uint8_t*>(base);
+    x.mapped[rank] = x.arena;
+    if (ipc_handle_out) {
+        static_assert(sizeof(cudaIpcMemHandle_t) == 64, "the exported handle travels as 64 bytes");
+        cudaIpcMemHandle_t handle;
+        GF_CUDA(cudaIpcGetMemHandle(&handle, base));
+        std::memcpy(ipc_handle_out, &handle, sizeof handle);
+    }
+    return GF_OK;
+}
+
+int Model::shard_connect(void* const* arenas) {
+    ShardExchange& x = shard_;
+    if (!x.arena) return fail(GF_ERR_STATE, "prepare the exchange arena first");
+    if (!arenas) return fail(GF_ERR_INVALID, "null arena list");
+    int mine = 0;
+    GF_CUDA(cudaGetDevice(&mine));
+    for (uint32_t s = 0; s < x.size; ++s) {
+        if (s == x.rank) continue;
+        if (!arenas[s]) return fail(GF_ERR_INVALID, "shard %u has no arena", s);
+        if (!x.opened[s]) {       // a pointer of this process: its device must be reachable from this one
+            cudaPointerAttributes attributes;
+            GF_CUDA(cudaPointerGetAttributes(&attributes, arenas[s]));
+            if (attributes.device != mine) {
+                int reachable = 0;
+                GF_CUDA(cudaDeviceCanAccessPeer(&reachable, mine, attributes.device));
+                if (!reachable) return fail(GF_ERR_STATE, "device %d cannot address device %d", mine, attributes.device);
+                const cudaError_t enabled = cudaDeviceEnablePeerAccess(attributes.device, 0);
+                if (enabled != cudaSuccess && enabled != cudaErrorPeerAccessAlreadyEnabled) GF_CUDA(enabled);
+                cudaGetLastError();
+            }
+        }
+        x.mapped[s] = static_cast<uint8_t*>(arenas[s]);
+    }
+    x.connected = true;
+    drop_graphs();
+    return GF_OK;
+}
+
+int Model::shard_connect_ipc(const void* handles) {
+    ShardExchange& x = shard_;
+    if (!x.arena) return fail(GF_ERR_STATE, "prepare the exchange arena first");
+    if (!handles) return fail(GF_ERR_INVALID, "null handle list");
+    void* arenas[8] = {};
+    for (uint32_t s = 0; s < x.size; ++s) {
+        if (s == x.rank) { arenas[s] = x.arena; continue; }
+        cudaIpcMemHandle_t handle;
+        std::memcpy(&handle, static_cast<const uint8_t*>(handles) + (size_t)s * sizeof handle, sizeof handle);
+        GF_CUDA(cudaIpcOpenMemHandle(&arenas[s], handle, cudaIpcMemLazyEnablePeerAccess));
+        x.opened[s] = true;
+    }
+    return shard_connect(arenas);
+}
+
+// The producing side: the launch writes its part into this shard's slot of its own arena and mirrors it into the
+// same slot of every peer's.
+int Model::shard_scatter(GemvLaunch& launch, uint32_t rows, uint32_t word, uint32_t& producer_ctas) {
+    const ShardExchange& x = shard_;
+    launch.matrices[0].out = x.part(x.arena, word, x.rank);
+    launch.scatter.count = 0;
+    for (uint32_t s = 0; s < x.size; ++s) {
+        if (s == x.rank) continue;
+        launch.scatter.out[launch.scatter.count] = x.part(x.mapped[s], word, x.rank);
+        launch.scatter.arrived[launch.scatter.count] = x.arrived(x.mapped[s], word);
+        ++launch.scatter.count;
+    }
+    launch.rows = rows;
+    GemvPlan plan;
+    GF_TRY(gemv_plan(launch, plan));
+    producer_ctas = plan.grid;
+    return GF_OK;
+}
+
+void Model::shard_gather(GemvLaunch& launch, uint32_t word, uint32_t producer_ctas) {
+    const ShardExchange& x = shard_;
+    launch.in = nullptr;
+    launch.gather.count = x.size;
+    for (uint32_t s = 0; s < x.size; ++s) launch.gather.parts[s] = x.part(x.arena, word, s);
+    launch.gather.arrived = x.arrived(x.arena, word);
+    launch.gather.passed = x.passed(x.arena, word);
+    launch.gather.expected = (x.size - 1u) * producer_ctas;
+    launch.gather.wait_limit = x.wait_limit;
+}
+
 int Model::emit_embedding(uint32_t rows, float scale) {
     const gf_model_config& c = config_;
     if (recording_) {
@@ -612,6 +712,9 @@ int Model::encode_blocks(uint32_t rows, uint32_t flags) {
     };
     auto down_weights = [&](uint32_t l) { GemvLaunch g; g.k = c.ffn; g.matrices[0] = desc(layers_[l].down, projected_); return g; };
     auto head_weights = [&]() { GemvLaunch g; g.k = c.hidden; g.matrices[0] = desc(has_head_ ? head_ : token_embd_, logits_); return g; };
+    const bool fused_exchange = shard_.connected;
+    if (fused_exchange && recording_) { recording_failed_ = true; return GF_OK; }      // the pass kernel has no phase for it
+    uint32_t o_ctas = 0, down_ctas = 0;
     for (uint32_t l = 0; l < c.layers; ++l) {
         const LayerWeights& w = layers_[l];
         const LayerCache& cache = caches_[l];
@@ -621,6 +724,7 @@ int Model::encode_blocks(uint32_t rows, uint32_t flags) {
         else {
             qkv.prologue = kPrologueAddNorm; qkv.in = projected_; qkv.residual = x2; qkv.gamma0 = layers_[l - 1].post_ffw_norm;
             qkv.residual_out = x; qkv.gamma1 = w.attn_norm;
+            if (fused_exchange) shard_gather(qkv, 1u, down_ctas);
         }
         GemvLaunch o = o_weights(l);
         const bool fused_heads = cache.rope_rotation != nullptr;
@@ -652,21 +756,30 @@ int Model::encode_blocks(uint32_t rows, uint32_t flags) {
         GF_TRY(emit_attention(ap));
         o.prologue = kPrologueMerge; o.in = ap.partial_out; o.residual = ap.partial_ml;
         GemvLaunch gu = gate_up_weights(l);
+        if (fused_exchange) GF_TRY(shard_scatter(o, rows, 0u, o_ctas));          // a tensor-parallel shard holds a partial sum here:
         GF_TRY(run_gemv(o, rows));
-        GF_TRY(reduce_partial(projected_, (size_t)rows * c.hidden));            // a tensor-parallel shard holds a partial sum here
+        if (!fused_exchange) GF_TRY(reduce_partial(projected_, (size_t)rows * c.hidden));     // summed in the launches, or by the host's hook
         gu.prologue = kPrologueAddNorm; gu.in = projected_; gu.residual = x; gu.gamma0 = w.post_attention_norm;
         gu.residual_out = x2; gu.gamma1 = w.ffn_norm;
+        if (fused_exchange) shard_gather(gu, 0u, o_ctas);
         GemvLaunch down = down_weights(l);
         GF_TRY(run_gemv(gu, rows));
         down.prologue = kPrologueGeglu; down.in = gate_; down.residual = up_;
+        if (fused_exchange) GF_TRY(shard_scatter(down, rows, 1u, down_ctas));
         GF_TRY(run_gemv(down, rows));
-        GF_TRY(reduce_partial(projected_, (size_t)rows * c.hidden));
+        if (!fused_exchange) GF_TRY(reduce_partial(projected_, (size_t)rows * c.hidden));
     }
     if (flags & kForwardLogits) {
         GemvLaunch head = head_weights();
         head.prologue = kPrologueAddNorm; head.in = projected_; head.residual = x2;
         head.gamma0 = layers_[c.layers - 1].post_ffw_norm; head.residual_out = x; head.gamma1 = output_norm_;
+        if (fused_exchange) shard_gather(head, 1u, down_ctas);
         GF_TRY(run_gemv(head, rows));
+    } else if (fused_exchange && shard_.size > 1u) {
+        // Nobody reads the last down projection of a pass without logits: take its arrivals off word 1 all the
+        // same, so that the words keep alternating from one pass into the next.
+        ++launches_;
+        GF_TRY(launch_shard_drain(shard_.arrived(shard_.arena, 1u), (shard_.size - 1u) * down_ctas, shard_.wait_limit, error_flag_, stream_, true));
     }
     return GF_OK;
 }
@@ -749,7 +862,7 @@ int Model::prefill(const uint32_t* tokens_host, uint32_t count) {
     if (!tokens_host || count == 0) return fail(GF_ERR_INVALID, "empty prompt");
     if (!finalized_) return fail(GF_ERR_STATE, "plan is not finalized");
     uint32_t done = 0;
-    if (tensor_prefill_ && !reduce_hook_ && count - 1u >= kTensorPrefillMinRows) {      // a shard's partial sums go through the row passes
+    if (tensor_prefill_ && !sharded() && count - 1u >= kTensorPrefillMinRows) {      // a shard's partial sums go through the row passes
         // All rows but the last as 128-row chunks through the tensor cores (K/V only: no chunk needs
         // logits, so the last layer stops after its K/V rows, gemma_target_runtime.cpp:59-61,125); the
         // last prompt token then runs as an ordinary one-row pass, which yields the logits.
@@ -1078,6 +1191,21 @@ int gf_model_set_matrix_requantized(gf_model* m, int kind, uint32_t layer, const
 }
 int gf_model_set_token_table_vocab(gf_model* m, uint32_t vocab) {
     return m ? m->impl.set_token_table_vocab(vocab) : fail(GF_ERR_INVALID, "null model");
+}
+int gf_model_shard_prepare(gf_model* m, uint32_t rank, uint32_t size, void* ipc_handle_out) {
+    return m ? m->impl.shard_prepare(rank, size, ipc_handle_out) : fail(GF_ERR_INVALID, "null model");
+}
+void* gf_model_shard_arena(gf_model* m) { return m ? m->impl.shard_arena() : nullptr; }
+int gf_model_shard_connect(gf_model* m, void* const* arenas) {
+    return m ? m->impl.shard_connect(arenas) : fail(GF_ERR_INVALID, "null model");
+}
+int gf_model_shard_connect_ipc(gf_model* m, const void* handles) {
+    return m ? m->impl.shard_connect_ipc(handles) : fail(GF_ERR_INVALID, "null model");
+}
+int gf_model_shard_set_wait_limit(gf_model* m, uint32_t polls) {
+    if (!m) return fail(GF_ERR_INVALID, "null model");
+    m->impl.shard_set_wait_limit(polls);
+    return GF_OK;
 }
 int gf_model_set_reduce_hook(gf_model* m, gf_reduce_fn hook, void* user) {
     return m ? m->impl.set_reduce_hook(hook, user) : fail(GF_ERR_INVALID, "null model");

@@ -130,15 +130,28 @@ public:
         token_table_vocab_ = vocab;
         return GF_OK;
     }
-    int set_reduce_hook(gf_reduce_fn hook, void* user) {
-        reduce_hook_ = hook; reduce_user_ = user;
+    void drop_graphs() {
         for (auto& per_rows : graphs_)
             for (cudaGraphExec_t& exec : per_rows)
                 if (exec) { cudaGraphExecDestroy(exec); exec = nullptr; }
         invalidate_passes();
+    }
+    int set_reduce_hook(gf_reduce_fn hook, void* user) {
+        reduce_hook_ = hook; reduce_user_ = user;
+        drop_graphs();
         return GF_OK;
     }
     uint32_t token_vocab() const { return token_table_vocab_ ? token_table_vocab_ : config_.vocab; }
+    bool sharded() const { return reduce_hook_ != nullptr || shard_.connected; }
+    // The exchange fused into the projection launches (no host hook, no separate reduction launch): every
+    // shard owns an arena its peers write into over NVLink.  shard_prepare allocates it (and exports it for
+    // other processes), shard_connect takes every shard's arena as mapped in this process, shard_connect_ipc
+    // maps the exported ones first.
+    int shard_prepare(uint32_t rank, uint32_t size, void* ipc_handle_out);
+    void* shard_arena() const { return shard_.arena; }
+    int shard_connect(void* const* arenas);
+    int shard_connect_ipc(const void* handles);
+    void shard_set_wait_limit(uint32_t polls) { shard_.wait_limit = polls; drop_graphs(); }
 
     // Enqueues the selection for rows whose requests already sit in requests_dev().
     int select_device(uint32_t rows);
@@ -160,6 +173,25 @@ private:
     };
 
     int reduce_partial(float* buffer, size_t count);
+    // This shard's side of the fused exchange.  Arena: parts [2 words][size shards][row_capacity x hidden] f32,
+    // then per word an arrival count and a passed count, each on a line of its own.  The O projections use
+    // word 0, the down projections word 1, so consecutive exchanges never share a word.
+    struct ShardExchange {
+        uint32_t rank = 0, size = 0;
+        bool connected = false;
+        uint8_t* arena = nullptr;
+        uint8_t* mapped[8] = {};          // every shard's arena as addressed from this process (own at [rank])
+        bool opened[8] = {};              // mapped from an exported handle: closed with the plan
+        size_t part_floats = 0, words_offset = 0, bytes = 0;
+        uint32_t wait_limit = 1u << 22;   // polls of about a microsecond: a few seconds
+        float* part(uint8_t* base, uint32_t word, uint32_t shard) const {
+            return reinterpret_cast<float*>(base) + ((size_t)word * size + shard) * part_floats;
+        }
+        uint32_t* arrived(uint8_t* base, uint32_t word) const { return reinterpret_cast<uint32_t*>(base + words_offset + word * 256u); }
+        uint32_t* passed(uint8_t* base, uint32_t word) const { return reinterpret_cast<uint32_t*>(base + words_offset + word * 256u + 128u); }
+    } shard_;
+    int shard_scatter(struct GemvLaunch& launch, uint32_t rows, uint32_t word, uint32_t& producer_ctas);
+    void shard_gather(struct GemvLaunch& launch, uint32_t word, uint32_t producer_ctas);
     uint32_t token_table_vocab_ = 0;
     gf_reduce_fn reduce_hook_ = nullptr;
     void* reduce_user_ = nullptr;

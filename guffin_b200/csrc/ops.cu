@@ -250,7 +250,28 @@ __global__ void __launch_bounds__(256) add_kernel(const float* __restrict__ left
         out[i] = __fadd_rn(left[i], right[i]);
 }
 
+// Takes the peers' arrivals off a shard-exchange word that no launch of this pass consumes (bounded, like the
+// consuming launches' own wait: gemv.cuh, shard_parts_wait).
+__global__ void __launch_bounds__(32) shard_drain_kernel(uint32_t* arrived, uint32_t expected, uint32_t wait_limit, int* error_flag) {
+    pdl_wait();
+    pdl_launch_dependents();
+    if (threadIdx.x != 0) return;
+    uint32_t polls = 0;
+    for (;;) {
+        uint32_t seen;
+        asm volatile("ld.acquire.sys.global.u32 %0, [%1];" : "=r"(seen) : "l"(arrived) : "memory");
+        if (seen >= expected) break;
+        if (++polls > wait_limit) { atomicExch(error_flag, 1); break; }
+        if (polls > 64u) __nanosleep(200);
+    }
+    asm volatile("st.relaxed.sys.global.u32 [%0], %1;" ::"l"(arrived), "r"(0u) : "memory");
+}
+
 // ------------------------------------------------------------------ launchers
+
+int launch_shard_drain(uint32_t* arrived, uint32_t expected, uint32_t wait_limit, int* error_flag, cudaStream_t stream, bool pdl) {
+    return launch_kernel(shard_drain_kernel, dim3(1), dim3(32), 0, stream, pdl, arrived, expected, wait_limit, error_flag);
+}
 
 int launch_embedding(int dtype, const void* packed, uint32_t k, uint32_t vocab, const uint32_t* tokens, uint32_t rows,
                      float scale, float* out, uint32_t* status, cudaStream_t stream, bool pdl) {

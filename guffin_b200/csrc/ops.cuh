@@ -95,6 +95,8 @@ int launch_kv_scatter(const void* private_k, const void* private_v, void* ring_k
                       const uint32_t* base_position, uint32_t rows, uint32_t row_width, uint32_t ring_mask,
                       int kv_f16, cudaStream_t stream, bool pdl);
 
+int launch_shard_drain(uint32_t* arrived, uint32_t expected, uint32_t wait_limit, int* error_flag, cudaStream_t stream, bool pdl);
+
 // Launch helper: optional programmatic stream serialisation (PDL).
 template <typename Kernel, typename... Args>
 int launch_kernel(Kernel kernel, dim3 grid, dim3 block, size_t smem, cudaStream_t stream, bool pdl, Args... args) {

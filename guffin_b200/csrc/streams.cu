@@ -43,7 +43,7 @@ static int stream_alloc(StreamSet& set, T** out, size_t count) {
 
 int Model::streams_create(uint32_t count, StreamSet** out) {
     if (!finalized_) return fail(GF_ERR_STATE, "plan is not finalized");
-    if (reduce_hook_) return fail(GF_ERR_STATE, "conversation streams are not offered on a tensor-parallel shard");
+    if (sharded()) return fail(GF_ERR_STATE, "conversation streams are not offered on a tensor-parallel shard");
     if (!out || count == 0 || count > kMaxStreams) return fail(GF_ERR_INVALID, "between 1 and %u streams", kMaxStreams);
     const gf_model_config& c = config_;
     std::unique_ptr<StreamSet> set(new StreamSet());

@@ -58,6 +58,11 @@ lib.register({
     "gf_model_load_gguf": (i32, [vp, C.c_char_p, vp]),
     "gf_model_set_reduce_hook": (i32, [vp, vp, vp]),
     "gf_model_set_token_table_vocab": (i32, [vp, u32]),
+    "gf_model_shard_prepare": (i32, [vp, u32, u32, vp]),
+    "gf_model_shard_arena": (vp, [vp]),
+    "gf_model_shard_connect": (i32, [vp, vp]),
+    "gf_model_shard_connect_ipc": (i32, [vp, vp]),
+    "gf_model_shard_set_wait_limit": (i32, [vp, u32]),
     "gf_add": (i32, [vp, vp, vp, u64, vp]),
     "gf_model_finalize": (i32, [vp]),
     "gf_model_reset": (i32, [vp]),

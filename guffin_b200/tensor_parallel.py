@@ -95,22 +95,49 @@ def shard_weights(weights, rank: int, size: int):
 
 
 class Shard:
-    """One shard's plan.  `reduce` is a (function pointer, user pointer) pair for gf_model_set_reduce_hook:
-    REDUCE_FN(python_callable) for an in-process sum, or (libguffin_tp.gf_tp_reduce, communicator)."""
+    """One shard's plan.  The partial sums behind O and down are summed either
+      * inside the projection launches over peer memory (reduce=None, the default): call `exported()` /
+        `arena` on every shard, then `connect_exported(handles)` (shards in different processes) or
+        `connect(arenas)` (one process, one GPU per shard) on every shard, then a host barrier; or
+      * by a host hook: `reduce` is a (function pointer, user pointer) pair for gf_model_set_reduce_hook --
+        REDUCE_FN(python_callable) for an in-process sum, or (libguffin_tp.gf_tp_reduce, communicator)."""
 
-    def __init__(self, config: dict, weights, context: int, rank: int, size: int, reduce, row_capacity: int = 2):
+    def __init__(self, config: dict, weights, context: int, rank: int, size: int, reduce=None, row_capacity: int = 2):
         self.rank, self.size = rank, size
         self.full_vocab = config["vocab"]
         self.local_vocab = config["vocab"] // size
         self._reduce = reduce           # keeps a ctypes callback alive as long as the plan
-        function, user = reduce
 
         def before_binding(model):
             check(model.L.gf_model_set_token_table_vocab(model.handle, self.full_vocab))
-            check(model.L.gf_model_set_reduce_hook(model.handle, C.cast(function, C.c_void_p), user))
+            if reduce is not None:
+                function, user = reduce
+                check(model.L.gf_model_set_reduce_hook(model.handle, C.cast(function, C.c_void_p), user))
 
         self.model = Model(shard_config(config, size), shard_weights(weights, rank, size), context, row_capacity,
                            before_binding=before_binding)
+        self._handle = None
+        if reduce is None:
+            handle = C.create_string_buffer(64)
+            check(self.model.L.gf_model_shard_prepare(self.model.handle, rank, size, handle))
+            self._handle = handle.raw
+
+    def exported(self) -> bytes:
+        """The 64-byte handle other processes map this shard's arena with."""
+        return self._handle
+
+    @property
+    def arena(self) -> int:
+        return self.model.L.gf_model_shard_arena(self.model.handle)
+
+    def connect(self, arenas) -> None:
+        table = (C.c_void_p * self.size)(*arenas)
+        check(self.model.L.gf_model_shard_connect(self.model.handle, table))
+
+    def connect_exported(self, handles) -> None:
+        blob = b"".join(handles)
+        assert len(blob) == 64 * self.size
+        check(self.model.L.gf_model_shard_connect_ipc(self.model.handle, blob))
 
     def global_candidates(self, result: CandidateResult) -> np.ndarray:
         """A shard's candidates with ids moved into the full vocabulary."""

@@ -288,6 +288,26 @@ GF_API int gf_model_set_matrix_requantized(gf_model* model, int kind, uint32_t l
 typedef int (*gf_reduce_fn)(void* user, float* buffer_dev, uint64_t count, void* stream);
 GF_API int gf_model_set_reduce_hook(gf_model* model, gf_reduce_fn hook, void* user);
 GF_API int gf_model_set_token_table_vocab(gf_model* model, uint32_t vocab);
+/* The same sum without a hook and without a launch of its own: the exchange rides on the projection launches.
+ * Each shard owns an arena in its GPU's memory.  The O / down launch writes its part there and mirrors it into
+ * the same slot of every peer's arena with plain stores over NVLink, then counts its CTAs into the peers'
+ * arrival words; the launch that consumes the projection (the next fused Q/K/V, gate/up or head launch) waits
+ * for the peers' CTAs -- a bounded wait: when it runs out the plan's error word is set, the pass goes on with what
+ * has arrived and gf_model_synchronize reports GF_ERR_TIMEOUT -- and reads its input as the sum of all parts in
+ * shard order, so every shard holds the same bits.  Shards are one per GPU; two shards must never share a GPU
+ * (their launches would wait on one another inside one device).
+ *   gf_model_shard_prepare      allocates this shard's arena; `ipc_handle_out` (64 bytes, may be null) receives
+ *                               the handle another PROCESS maps it with
+ *   gf_model_shard_arena        the arena's device pointer, for shards that live in one process
+ *   gf_model_shard_connect      `arenas[size]`: every shard's arena as addressable in this process (own ignored)
+ *   gf_model_shard_connect_ipc  `handles`: size x 64 bytes, every shard's exported handle (own ignored)
+ *   gf_model_shard_set_wait_limit  polls (about a microsecond each) before a wait for the peers gives up
+ * Connect every shard, and let the host see that all have (a barrier), before the first pass. */
+GF_API int gf_model_shard_prepare(gf_model* model, uint32_t rank, uint32_t size, void* ipc_handle_out);
+GF_API void* gf_model_shard_arena(gf_model* model);
+GF_API int gf_model_shard_connect(gf_model* model, void* const* arenas);
+GF_API int gf_model_shard_connect_ipc(gf_model* model, const void* handles);
+GF_API int gf_model_shard_set_wait_limit(gf_model* model, uint32_t polls);
 /* Binds every tensor of a GGUF v2/v3 file that the block schedule knows (llama.cpp tensor names,
  * F32 vectors, Q8_0 / Q4_K / Q6_K matrices and binary16 embedding / head tables) through the two calls above: the path's share of
  * read_file_backed_gguf_model (model_format/gguf_reader.hpp:85) and of the WeightMaterializer.

@@ -129,3 +129,109 @@ def test_two_shards_on_one_device_match_the_unsharded_plan(name):
         k, v = shards[rank].model.read_kv(1, 0, shards[rank].model.position)
         assert np.allclose(k, want_kv[0][:, rank * kv_width:(rank + 1) * kv_width], rtol=2e-3, atol=2e-3)
         assert np.allclose(v, want_kv[1][:, rank * kv_width:(rank + 1) * kv_width], rtol=2e-3, atol=2e-3)
+
+
+@pytest.mark.gpu
+def test_single_shard_exchange_is_the_plain_plan():
+    """One shard of one: the exchange-carrying launches (parts read through the arena, nothing to wait for) must
+    give the plain plan's bits."""
+    from guffin_b200 import model as gm
+    config = syn.model_config("tiny-target")
+    weights = syn.make_model_weights("tiny-target", 11)
+    rng = np.random.default_rng(4)
+    prompt = rng.integers(0, config["vocab"], 21).astype(np.uint32)
+    pair = rng.integers(0, config["vocab"], 2).astype(np.uint32)
+    plain = gm.Model(config, weights, 64, 8)
+    shard = tp.Shard(config, weights, 64, 0, 1, row_capacity=8)
+    shard.connect([shard.arena])
+    for graph in (False, True):
+        results = []
+        for model in (plain, shard.model):
+            model.reset()
+            model.use_graph(graph)
+            model.prefill(prompt)
+            first = model.logits(model.prefill_logits_row)
+            model.forward(pair)
+            results.append((first, model.logits(0), model.logits(1)))
+            model.publish(2)
+            assert model.status() == 0
+        for want, got in zip(*results):
+            assert np.array_equal(want, got)
+    k0, v0 = plain.read_kv(3, 0, plain.position)
+    k1, v1 = shard.model.read_kv(3, 0, shard.model.position)
+    assert np.array_equal(k0, k1) and np.array_equal(v0, v1)
+
+
+def _two_devices():
+    from guffin_b200 import lib
+    return lib.device_count() >= 2
+
+
+@pytest.mark.gpu
+@pytest.mark.parametrize("name", ["tiny-target", "tiny-gemma2"])
+def test_two_shards_on_two_devices_exchange_inside_the_launches(name):
+    """Two shards in one process, one GPU each, every shard driven by its own host thread; the partial sums
+    cross NVLink inside the projection launches.  Checked against the unsharded plan."""
+    from guffin_b200 import lib, model as gm
+    if not _two_devices():
+        pytest.skip("needs two GPUs")
+    L = lib.load()
+    config = syn.model_config(name)
+    weights = syn.make_model_weights(name, 11)
+    rng = np.random.default_rng(4)
+    prompt = rng.integers(0, config["vocab"], 21).astype(np.uint32)
+    steps = [rng.integers(0, config["vocab"], 2).astype(np.uint32) for _ in range(6)]
+    lib.check(L.gf_set_device(0))
+    full = gm.Model(config, weights, 64, 8)
+    full.prefill(prompt)
+    want = [full.logits(full.prefill_logits_row)[None, :]]
+    for tokens in steps:
+        full.forward(tokens)
+        want.append(np.stack([full.logits(0), full.logits(1)]))
+        full.publish(1)
+    want_kv = full.read_kv(1, 0, full.position)
+
+    size = 2
+    shards = []
+    for rank in range(size):
+        lib.check(L.gf_set_device(rank))
+        shards.append(tp.Shard(config, weights, 64, rank, size, row_capacity=8))
+    arenas = [shard.arena for shard in shards]
+    for rank in range(size):
+        lib.check(L.gf_set_device(rank))
+        shards[rank].connect(arenas)
+        lib.check(L.gf_model_shard_set_wait_limit(shards[rank].model.handle, 1 << 20))      # about a second per wait
+    lib.check(L.gf_set_device(0))
+    got = [[] for _ in range(size)]
+    kv = [None] * size
+    errors = []
+
+    def drive(rank):
+        try:
+            lib.check(L.gf_set_device(rank))
+            model = shards[rank].model
+            model.prefill(prompt)
+            got[rank].append(model.logits(model.prefill_logits_row)[None, :])
+            for tokens in steps:
+                model.forward(tokens)
+                got[rank].append(np.stack([model.logits(0), model.logits(1)]))
+                model.publish(1)
+            kv[rank] = model.read_kv(1, 0, model.position)
+            assert model.status() == 0
+            model.synchronize()
+        except Exception as error:
+            errors.append(error)
+
+    threads = [threading.Thread(target=drive, args=(rank,)) for rank in range(size)]
+    for t in threads:
+        t.start()
+    for t in threads:
+        t.join(timeout=300)
+    assert not errors, errors
+    for step, logits in enumerate(want):
+        merged = np.concatenate([got[r][step] for r in range(size)], axis=-1)
+        assert np.linalg.norm(merged - logits) <= 2e-5 * np.linalg.norm(logits), step
+    kv_width = config["kv_heads"] * config["head_dim"] // size
+    for rank in range(size):
+        assert np.allclose(kv[rank][0], want_kv[0][:, rank * kv_width:(rank + 1) * kv_width], rtol=2e-3, atol=2e-3)
+        assert np.allclose(kv[rank][1], want_kv[1][:, rank * kv_width:(rank + 1) * kv_width], rtol=2e-3, atol=2e-3)
