@@ -475,8 +475,15 @@ def run_tensor_parallel(args) -> dict:
             box = [ident]
             dist.broadcast_object_list(box, src=0)
             return box[0]
-        reducer = tp.NcclReducer(rank, world, exchange)
-        shard = tp.Shard(config, syn.iter_model_weights(name, SEEDS["target"]), context, rank, world, reducer.hook, PREFILL_ROWS)
+        if args.exchange == "nccl":
+            reducer = tp.NcclReducer(rank, world, exchange)
+            shard = tp.Shard(config, syn.iter_model_weights(name, SEEDS["target"]), context, rank, world, reducer.hook, PREFILL_ROWS)
+        else:
+            shard = tp.Shard(config, syn.iter_model_weights(name, SEEDS["target"]), context, rank, world, None, PREFILL_ROWS)
+            handles = [None] * world
+            dist.all_gather_object(handles, shard.exported())
+            shard.connect_exported(handles)
+            dist.barrier()                  # every shard is connected before any pass starts
         plan = shard.model
     else:
         plan = gm.Model(config, syn.iter_model_weights(name, SEEDS["target"]), context, PREFILL_ROWS)
@@ -539,10 +546,11 @@ def run_tensor_parallel(args) -> dict:
         "higher_is_better": True, "scaling": "strong", "vs_baseline": None, "dtype": "u4/u8 blocks -> f32, binary16 cache",
         "data": "synthetic",
         "config": {"workload": f"one Gemma3-12B stream at {prefix} committed tokens, two-row pass + publish, "
-                               + (f"row-sharded over {world} GPUs, NCCL all-reduce behind every O and down projection" if world > 1 else "unsharded plan"),
+                               + ((f"row-sharded over {world} GPUs, " + ("NCCL all-reduce behind every O and down projection" if args.exchange == "nccl"
+                                  else "partial sums exchanged inside the projection launches over peer memory")) if world > 1 else "unsharded plan"),
                    "parallelism": f"tp{world}", "l2_policy": "inputs larger than L2: a pass streams every weight once",
                    "load_s": round(load_s, 1), "prefill_s": round(prefill_s, 2), "status_word": int(status),
-                   "reductions_per_pass": 2 * config["layers"] if world > 1 else 0, "last_pass_logits": checksum},
+                   "reductions_per_pass": 2 * config["layers"] if world > 1 else 0, "exchange": args.exchange if world > 1 else None, "last_pass_logits": checksum},
         "e2e": {"value": steps / wall, "unit": "passes/s", "h2d_bytes_per_step": 8, "d2h_bytes_per_step": 0, "ms_per_step": wall * 1e3 / steps},
         "gpu_launches": int(launches),
         "roofline": {"bound": "hbm", "achieved": achieved, "peak": peak * world, "unit": "GB/s", "frac": achieved / (peak * world),
@@ -804,6 +812,8 @@ def main():
     parser.add_argument("--horizon", type=int, default=1, help="drafts per cycle of the h1 workload (1 = the headline; 2..7 = chains)")
     parser.add_argument("--streams", type=int, default=8, help="streams per GPU of the streams workload (64 over eight GPUs)")
     parser.add_argument("--prefix", type=int, default=8192, help="prefix tokens per stream of the streams workload")
+    parser.add_argument("--exchange", choices=("peer", "nccl"), default="peer",
+                        help="tp workload: partial sums exchanged inside the projection launches over peer memory, or by NCCL all-reduces between them")
     parser.add_argument("--tensor-decode", action="store_true",
                         help="streams workload: every step as one bf16 tensor-core pass over all streams instead of exact row passes")
     args = parser.parse_args()

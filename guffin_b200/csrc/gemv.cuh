@@ -1532,8 +1532,9 @@ __global__ void __launch_bounds__(kGemvWarps * 32, 1) weight_stream_kernel(const
         }
     }
     if (TP && p.scatter.count != 0u) {
-        // Every value this CTA sent to the peers is visible there before its arrival is counted.
-        __threadfence_system();
+        // Every value this CTA sent to the peers is visible there before its arrival is counted: the barrier orders
+        // the CTA's stores before the counting thread, whose release at system scope carries them along (one
+        // release per peer instead of a system fence in every thread).
         __syncthreads();
         if (threadIdx.x < p.scatter.count) red_release_system(p.scatter.arrived[threadIdx.x], 1u);
     }
