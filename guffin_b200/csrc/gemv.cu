@@ -146,8 +146,8 @@ int gemv_prepare(const GemvLaunch& launch, uint32_t* counters, float* partial, s
     if (status != GF_OK) return status;
     if ((!launch.in && launch.gather.count == 0u) || !error_flag) return fail(GF_ERR_INVALID, "gf_matmul: null buffer");
     if (launch.gather.count > (uint32_t)kGemvMaxShards || launch.scatter.count >= (uint32_t)kGemvMaxShards
-        || (launch.gather.count != 0u && (launch.prologue != kPrologueAddNorm || !launch.gather.arrived || !launch.gather.passed))
-        || (launch.scatter.count != 0u && launch.count != 1u))
+        || (launch.gather.count != 0u && (launch.prologue != kPrologueAddNorm || !launch.gather.own || !launch.gather.tick || launch.gather.self >= launch.gather.count))
+        || (launch.scatter.count != 0u && (launch.count != 1u || !launch.scatter.tick || launch.scatter.site == 0u || launch.scatter.site > 255u)))
         return fail(GF_ERR_INVALID, "gf_matmul: bad shard exchange");
     // The activation prologue reads four floats at a time.
     auto aligned = [](const void* ptr) { return (reinterpret_cast<uintptr_t>(ptr) & 15u) == 0u; };

@@ -88,21 +88,21 @@ struct WeightStreamParams {
     int* error_flag;           // set to 1 when a bounded wait gives up
     // Tensor-parallel shards (the TP instantiation only; both off when their count is 0).  A shard's O and down
     // projections hold partial sums of the hidden rows.  The producing launch mirrors every output value it writes
-    // into the same place of each peer GPU's copy (plain stores over NVLink) and, as each CTA ends, adds one to
-    // each peer's arrival word.  The consuming launch waits (bounded) until its own arrival word shows every CTA
-    // of every peer, then reads its input as the sum of all shards' parts in shard order, so every shard holds
-    // the same bits; the CTA that is last through the wait clears the word for its next use.
+    // into each peer GPU's arena as an 8-byte (value, stamp) pair -- one plain store over NVLink, the stamp naming
+    // the pass and the projection -- and the consuming launch reads its input as the sum of all shards' parts in
+    // shard order (so every shard holds the same bits), polling each peer's pairs until they carry the stamp it
+    // expects.  No fence, flag or extra launch: a value is usable the moment it lands.  The polls are bounded.
     struct Scatter {
-        float* out[kGemvMaxShards - 1];          // matrix 0's output [rows][n] in each peer's memory
-        uint32_t* arrived[kGemvMaxShards - 1];   // each peer's arrival word
-        uint32_t count;                          // peers
+        uint2* out[kGemvMaxShards - 1];          // matrix 0's output [rows][n] as stamped pairs in each peer's arena
+        const uint32_t* tick;                    // this GPU's pass counter
+        uint32_t count, site;                    // peers; which projection of the pass (1 ..)
     } scatter;
     struct Gather {
-        const float* parts[kGemvMaxShards];      // this GPU's copies of every shard's part, own included, in shard order
-        uint32_t* arrived;                       // this GPU's arrival word: peers' CTAs add to it
-        uint32_t* passed;                        // CTAs of this launch that are through the wait
-        uint32_t count, expected;                // shards; peers x CTAs of the producing launch
-        uint32_t wait_limit;                     // polls before the wait gives up
+        const uint2* parts[kGemvMaxShards];      // the peers' stamped parts in this GPU's arena, by shard (own entry unused)
+        const float* own;                        // this shard's part
+        const uint32_t* tick;
+        uint32_t count, self, site;              // shards; this shard's index; the producing projection
+        uint32_t wait_limit;                     // polls before a wait for a peer's value gives up
     } gather;
 };
 
@@ -469,17 +469,41 @@ template <bool FROM_L2>
 __device__ __forceinline__ void load8f_act(const float* p, float (&v)[8]) {
     if (FROM_L2) load8f_cg(p, v); else load8f(p, v);
 }
-// The input rows of a launch: `in`, or on a tensor-parallel shard the sum of every shard's part in shard order
-// (parts written by peer GPUs arrive in L2: read there).
-template <bool FROM_L2, bool TP>
-__device__ __forceinline__ void load8f_in(const WeightStreamParams& p, size_t offset, float (&v)[8]) {
-    if (TP && p.gather.count != 0u) {
-        load8f_cg(p.gather.parts[0] + offset, v);
-        for (uint32_t s = 1; s < p.gather.count; ++s) {
-            float w[8];
-            load8f_cg(p.gather.parts[s] + offset, w);
+__device__ __forceinline__ uint4 load_volatile16(const uint4* p) {
+    uint4 v;
+    asm volatile("ld.volatile.global.v4.u32 {%0, %1, %2, %3}, [%4];" : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w) : "l"(p) : "memory");
+    return v;
+}
+// The stamp of projection `site` of the pass the counter names: distinct from the stamp of whatever the same place
+// of the arena held before (the previous projection of this pass, or of the pass before).
+__device__ __forceinline__ uint32_t shard_stamp(const uint32_t* tick, uint32_t site) { return (__ldcg(tick) << 8) | site; }
+// Eight consecutive values of a peer's part: polled until all eight pairs carry `stamp` (8-byte stores arrive whole).
+__device__ __forceinline__ void load8f_stamped(const WeightStreamParams& p, const uint2* src, uint32_t stamp, float (&v)[8]) {
+    const uint4* quads = reinterpret_cast<const uint4*>(src);
+    uint4 q[4];
+    for (uint32_t polls = 0;; ++polls) {
 #pragma unroll
-            for (int i = 0; i < 8; ++i) v[i] = __fadd_rn(v[i], w[i]);
+        for (int i = 0; i < 4; ++i) q[i] = load_volatile16(quads + i);
+        bool landed = true;
+#pragma unroll
+        for (int i = 0; i < 4; ++i) landed = landed && q[i].y == stamp && q[i].w == stamp;
+        if (landed) break;
+        if (polls > p.gather.wait_limit) { atomicExch(p.error_flag, 1); break; }      // a dead peer costs a wrong pass, never a hung GPU
+        if (polls > 32u) __nanosleep(100);
+    }
+#pragma unroll
+    for (int i = 0; i < 4; ++i) { v[2 * i] = __uint_as_float(q[i].x); v[2 * i + 1] = __uint_as_float(q[i].z); }
+}
+// The input rows of a launch: `in`, or on a tensor-parallel shard the sum of every shard's part in shard order.
+template <bool FROM_L2, bool TP>
+__device__ __forceinline__ void load8f_in(const WeightStreamParams& p, size_t offset, uint32_t stamp, float (&v)[8]) {
+    if (TP && p.gather.count != 0u) {
+        for (uint32_t s = 0; s < p.gather.count; ++s) {
+            float w[8];
+            if (s == p.gather.self) load8f_cg(p.gather.own + offset, w);
+            else load8f_stamped(p, p.gather.parts[s] + offset, stamp, w);
+#pragma unroll
+            for (int i = 0; i < 8; ++i) v[i] = s == 0u ? w[i] : __fadd_rn(v[i], w[i]);
         }
         return;
     }
@@ -643,7 +667,7 @@ __device__ __forceinline__ void merge_head_piece(const WeightStreamParams& p, ui
 // came in with stage_early); otherwise the row is re-read for each pass.
 template <int ROWS, bool PASS, bool TP = false>
 __device__ __forceinline__ void stage_activations(const WeightStreamParams& p, uint32_t first, uint32_t count,
-                                                  const GemvStage& st, float* scratch, GemvEarly<ROWS>& early) {
+                                                  const GemvStage& st, float* scratch, GemvEarly<ROWS>& early, uint32_t stamp = 0u) {
     const bool norms = p.prologue == kPrologueNorm || p.prologue == kPrologueAddNorm;
     const uint32_t row_pieces = p.k / 8u;
     if (early.cached) {
@@ -661,7 +685,7 @@ __device__ __forceinline__ void stage_activations(const WeightStreamParams& p, u
         if (live) {
 #pragma unroll
             for (int r = 0; r < ROWS; ++r)
-                if ((uint32_t)r < p.active_rows) load8f_in<PASS, TP>(p, (size_t)r * p.k + o, x[r]);
+                if ((uint32_t)r < p.active_rows) load8f_in<PASS, TP>(p, (size_t)r * p.k + o, stamp, x[r]);
         }
         float ss[ROWS];
 #pragma unroll
@@ -700,7 +724,7 @@ __device__ __forceinline__ void stage_activations(const WeightStreamParams& p, u
             ss[r] = 0.0f;
             for (uint32_t c = threadIdx.x; c < row_pieces && (uint32_t)r < p.active_rows; c += blockDim.x) {
                 float x[8];
-                load8f_in<PASS, TP>(p, (size_t)r * p.k + c * 8u, x);
+                load8f_in<PASS, TP>(p, (size_t)r * p.k + c * 8u, stamp, x);
                 ss[r] = sum_squares(x, ss[r]);
             }
         }
@@ -714,7 +738,7 @@ __device__ __forceinline__ void stage_activations(const WeightStreamParams& p, u
                 ss[r] = 0.0f;
                 for (uint32_t c = threadIdx.x; c < row_pieces && (uint32_t)r < p.active_rows; c += blockDim.x) {
                     float x[8], a[8], gm[8];
-                    load8f_in<PASS, TP>(p, (size_t)r * p.k + c * 8u, x);
+                    load8f_in<PASS, TP>(p, (size_t)r * p.k + c * 8u, stamp, x);
                     load8f_act<PASS>(p.residual + (size_t)r * p.k + c * 8u, a);
                     load8f(p.gamma0 + c * 8u, gm);
 #pragma unroll
@@ -743,7 +767,7 @@ __device__ __forceinline__ void stage_activations(const WeightStreamParams& p, u
             float i0 = 1.0f, i1 = 1.0f;
 #pragma unroll
             for (int rr = 0; rr < ROWS; ++rr) if (rr == (int)r) { i0 = inv0[rr]; i1 = inv1[rr]; }
-            load8f_in<PASS, TP>(p, gi, v);
+            load8f_in<PASS, TP>(p, gi, stamp, v);
             if (p.prologue == kPrologueNorm) {
                 float gm[8];
                 load8f(p.gamma1 + c, gm);
@@ -1259,39 +1283,6 @@ __device__ __forceinline__ WeightRing ring_open(const StreamSmem& sm, uint32_t s
     return ring;
 }
 
-// ---- system-scope words shared with peer GPUs (tensor-parallel shards).
-__device__ __forceinline__ uint32_t load_acquire_system(const uint32_t* word) {
-    uint32_t value;
-    asm volatile("ld.acquire.sys.global.u32 %0, [%1];" : "=r"(value) : "l"(word) : "memory");
-    return value;
-}
-__device__ __forceinline__ void red_release_system(uint32_t* word, uint32_t value) {
-    asm volatile("red.release.sys.global.add.u32 [%0], %1;" ::"l"(word), "r"(value) : "memory");
-}
-__device__ __forceinline__ void store_relaxed_system(uint32_t* word, uint32_t value) {
-    asm volatile("st.relaxed.sys.global.u32 [%0], %1;" ::"l"(word), "r"(value) : "memory");
-}
-// The consuming side of the shard exchange: thread 0 polls this GPU's arrival word until every CTA of every
-// peer's producing launch is counted, or the poll limit runs out (the error word is set and the launch goes on
-// with what has arrived: a dead peer costs a wrong pass, never a hung GPU).  The CTA that is last through
-// clears the word and the count: the next exchange on this word starts only after the peers have consumed an
-// exchange on the other word, which this launch's successor has to feed.
-__device__ __forceinline__ void shard_parts_wait(const WeightStreamParams& p) {
-    if (threadIdx.x == 0) {
-        uint32_t polls = 0;
-        while (load_acquire_system(p.gather.arrived) < p.gather.expected) {
-            if (++polls > p.gather.wait_limit) { atomicExch(p.error_flag, 1); break; }
-            if (polls > 64u) __nanosleep(200);
-        }
-        __threadfence();
-        if (atomicAdd(p.gather.passed, 1u) == gridDim.x - 1u) {
-            *p.gather.passed = 0u;
-            store_relaxed_system(p.gather.arrived, 0u);
-        }
-    }
-    __syncthreads();
-}
-
 // The launch of its own: one matrix set per kernel, the schedule replayed as a CUDA graph.  Its body is
 // kept apart from stream_phase (the pass kernel's phase) although the two decompose and compute alike:
 // with everything a launch needs in the constant bank and in registers this form measured 2.3 % faster
@@ -1376,9 +1367,11 @@ __global__ void __launch_bounds__(kGemvWarps * 32, 1) weight_stream_kernel(const
     stage_early<ROWS, false>(p, intra ? 0u : first_unit * p.unit_elems, early_inputs);
 
     pdl_wait();
-    if (TP && p.gather.count != 0u) shard_parts_wait(p);
+    const uint32_t gather_stamp = TP && p.gather.count != 0u ? shard_stamp(p.gather.tick, p.gather.site) : 0u;
+    const uint32_t scatter_stamp = TP && p.scatter.count != 0u ? shard_stamp(p.scatter.tick, p.scatter.site) : 0u;
     const GemvStage stage{frags, sums, block_scales, &bad_rows, padded};
-    stage_activations<ROWS, false, TP>(p, intra ? 0u : first_unit * p.unit_elems, intra ? p.k : chunk_count * p.unit_elems, stage, scratch, early_inputs);
+    stage_activations<ROWS, false, TP>(p, intra ? 0u : first_unit * p.unit_elems, intra ? p.k : chunk_count * p.unit_elems, stage, scratch, early_inputs,
+                                       gather_stamp);
     __syncthreads();
     pdl_launch_dependents();
 
@@ -1491,8 +1484,8 @@ __global__ void __launch_bounds__(kGemvWarps * 32, 1) weight_stream_kernel(const
                     if (columnB < mat.n) mat.out[(size_t)r * mat.n + columnB] = totalB[r];
                     if (TP)
                         for (uint32_t s = 0; s < p.scatter.count; ++s) {
-                            if (columnA < mat.n) p.scatter.out[s][(size_t)r * mat.n + columnA] = totalA[r];
-                            if (columnB < mat.n) p.scatter.out[s][(size_t)r * mat.n + columnB] = totalB[r];
+                            if (columnA < mat.n) p.scatter.out[s][(size_t)r * mat.n + columnA] = make_uint2(__float_as_uint(totalA[r]), scatter_stamp);
+                            if (columnB < mat.n) p.scatter.out[s][(size_t)r * mat.n + columnB] = make_uint2(__float_as_uint(totalB[r]), scatter_stamp);
                         }
                 }
             if (p.heads.enabled) head_pair_done<ROWS>(p, mat, matrix_of(pair), local_pair, lane);
@@ -1524,19 +1517,13 @@ __global__ void __launch_bounds__(kGemvWarps * 32, 1) weight_stream_kernel(const
                 if (out_column < mat.n && r < p.active_rows) {
                     mat.out[(size_t)r * mat.n + out_column] = sum;
                     if (TP)
-                        for (uint32_t s = 0; s < p.scatter.count; ++s) p.scatter.out[s][(size_t)r * mat.n + out_column] = sum;
+                        for (uint32_t s = 0; s < p.scatter.count; ++s)
+                            p.scatter.out[s][(size_t)r * mat.n + out_column] = make_uint2(__float_as_uint(sum), scatter_stamp);
                 }
             }
             if (lane == 0) p.counters[pair] = 0u;
             if (p.heads.enabled) head_pair_done<ROWS>(p, mat, matrix_of(pair), local_pair, lane);
         }
-    }
-    if (TP && p.scatter.count != 0u) {
-        // Every value this CTA sent to the peers is visible there before its arrival is counted: the barrier orders
-        // the CTA's stores before the counting thread, whose release at system scope carries them along (one
-        // release per peer instead of a system fence in every thread).
-        __syncthreads();
-        if (threadIdx.x < p.scatter.count) red_release_system(p.scatter.arrived[threadIdx.x], 1u);
     }
     if (failed) {
         // Give outstanding copies a bounded chance to land before the shared memory is released.

@@ -469,9 +469,10 @@ int Model::shard_prepare(uint32_t rank, uint32_t size, void* ipc_handle_out) {
     if (shard_.arena) return fail(GF_ERR_STATE, "this plan already has an exchange arena");
     ShardExchange& x = shard_;
     x.rank = rank; x.size = size;
-    x.part_floats = (((size_t)config_.row_capacity * config_.hidden) + 63u) & ~(size_t)63u;
-    x.words_offset = 2u * size * x.part_floats * sizeof(float);
-    x.bytes = x.words_offset + 2u * 256u;
+    if (2u * config_.layers > 255u) return fail(GF_ERR_INVALID, "the exchange stamps name at most 127 layers");
+    x.part_values = (((size_t)config_.row_capacity * config_.hidden) + 63u) & ~(size_t)63u;
+    x.tick_offset = 2u * size * x.part_values * sizeof(uint2);
+    x.bytes = x.tick_offset + 256u;
     void* base = nullptr;
     GF_CUDA(cudaMalloc(&base, x.bytes));                 // an allocation of its own: peers map exactly this
     GF_CUDA(cudaMemset(base, 0, x.bytes));
@@ -529,33 +530,27 @@ int Model::shard_connect_ipc(const void* handles) {
     return shard_connect(arenas);
 }
 
-// The producing side: the launch writes its part into this shard's slot of its own arena and mirrors it into the
-// same slot of every peer's.
-int Model::shard_scatter(GemvLaunch& launch, uint32_t rows, uint32_t word, uint32_t& producer_ctas) {
+// The producing side: the launch keeps its part in `projected_` and mirrors it, stamped, into this shard's slot of
+// every peer's arena.  `site` names the projection inside the pass.
+void Model::shard_scatter(GemvLaunch& launch, uint32_t half, uint32_t site) {
     const ShardExchange& x = shard_;
-    launch.matrices[0].out = x.part(x.arena, word, x.rank);
     launch.scatter.count = 0;
     for (uint32_t s = 0; s < x.size; ++s) {
         if (s == x.rank) continue;
-        launch.scatter.out[launch.scatter.count] = x.part(x.mapped[s], word, x.rank);
-        launch.scatter.arrived[launch.scatter.count] = x.arrived(x.mapped[s], word);
-        ++launch.scatter.count;
+        launch.scatter.out[launch.scatter.count++] = x.part(x.mapped[s], half, x.rank);
     }
-    launch.rows = rows;
-    GemvPlan plan;
-    GF_TRY(gemv_plan(launch, plan));
-    producer_ctas = plan.grid;
-    return GF_OK;
+    launch.scatter.tick = x.tick();
+    launch.scatter.site = site;
 }
 
-void Model::shard_gather(GemvLaunch& launch, uint32_t word, uint32_t producer_ctas) {
+void Model::shard_gather(GemvLaunch& launch, uint32_t half, uint32_t site) {
     const ShardExchange& x = shard_;
-    launch.in = nullptr;
     launch.gather.count = x.size;
-    for (uint32_t s = 0; s < x.size; ++s) launch.gather.parts[s] = x.part(x.arena, word, s);
-    launch.gather.arrived = x.arrived(x.arena, word);
-    launch.gather.passed = x.passed(x.arena, word);
-    launch.gather.expected = (x.size - 1u) * producer_ctas;
+    launch.gather.self = x.rank;
+    launch.gather.own = launch.in;
+    for (uint32_t s = 0; s < x.size; ++s) launch.gather.parts[s] = x.part(x.arena, half, s);
+    launch.gather.tick = x.tick();
+    launch.gather.site = site;
     launch.gather.wait_limit = x.wait_limit;
 }
 
@@ -690,6 +685,12 @@ int Model::run_recorded(const RecordedPass& pass, uint32_t rows) {
 int Model::encode_blocks(uint32_t rows, uint32_t flags) {
     const gf_model_config& c = config_;
     const float embedding_scale = sqrtf((float)c.hidden);     // f32, not bf16-rounded (model.cpp:599-605)
+    const bool fused_exchange = shard_.connected;
+    if (fused_exchange) {
+        if (recording_) { recording_failed_ = true; return GF_OK; }      // the pass kernel has no phase for the exchange
+        ++launches_;
+        GF_TRY(launch_shard_tick(shard_.tick(), stream_));                // a new pass: new stamps
+    }
     GF_TRY(emit_embedding(rows, embedding_scale));
     float* x = residual_;          // residual stream entering a layer
     float* x2 = post_attention_;   // residual stream after the attention branch
@@ -712,9 +713,6 @@ int Model::encode_blocks(uint32_t rows, uint32_t flags) {
     };
     auto down_weights = [&](uint32_t l) { GemvLaunch g; g.k = c.ffn; g.matrices[0] = desc(layers_[l].down, projected_); return g; };
     auto head_weights = [&]() { GemvLaunch g; g.k = c.hidden; g.matrices[0] = desc(has_head_ ? head_ : token_embd_, logits_); return g; };
-    const bool fused_exchange = shard_.connected;
-    if (fused_exchange && recording_) { recording_failed_ = true; return GF_OK; }      // the pass kernel has no phase for it
-    uint32_t o_ctas = 0, down_ctas = 0;
     for (uint32_t l = 0; l < c.layers; ++l) {
         const LayerWeights& w = layers_[l];
         const LayerCache& cache = caches_[l];
@@ -724,7 +722,7 @@ int Model::encode_blocks(uint32_t rows, uint32_t flags) {
         else {
             qkv.prologue = kPrologueAddNorm; qkv.in = projected_; qkv.residual = x2; qkv.gamma0 = layers_[l - 1].post_ffw_norm;
             qkv.residual_out = x; qkv.gamma1 = w.attn_norm;
-            if (fused_exchange) shard_gather(qkv, 1u, down_ctas);
+            if (fused_exchange) shard_gather(qkv, 1u, 2u * l);               // the down projection of the layer before
         }
         GemvLaunch o = o_weights(l);
         const bool fused_heads = cache.rope_rotation != nullptr;
@@ -756,16 +754,16 @@ int Model::encode_blocks(uint32_t rows, uint32_t flags) {
         GF_TRY(emit_attention(ap));
         o.prologue = kPrologueMerge; o.in = ap.partial_out; o.residual = ap.partial_ml;
         GemvLaunch gu = gate_up_weights(l);
-        if (fused_exchange) GF_TRY(shard_scatter(o, rows, 0u, o_ctas));          // a tensor-parallel shard holds a partial sum here:
+        if (fused_exchange) shard_scatter(o, 0u, 2u * l + 1u);                    // a tensor-parallel shard holds a partial sum here:
         GF_TRY(run_gemv(o, rows));
         if (!fused_exchange) GF_TRY(reduce_partial(projected_, (size_t)rows * c.hidden));     // summed in the launches, or by the host's hook
         gu.prologue = kPrologueAddNorm; gu.in = projected_; gu.residual = x; gu.gamma0 = w.post_attention_norm;
         gu.residual_out = x2; gu.gamma1 = w.ffn_norm;
-        if (fused_exchange) shard_gather(gu, 0u, o_ctas);
+        if (fused_exchange) shard_gather(gu, 0u, 2u * l + 1u);
         GemvLaunch down = down_weights(l);
         GF_TRY(run_gemv(gu, rows));
         down.prologue = kPrologueGeglu; down.in = gate_; down.residual = up_;
-        if (fused_exchange) GF_TRY(shard_scatter(down, rows, 1u, down_ctas));
+        if (fused_exchange) shard_scatter(down, 1u, 2u * l + 2u);
         GF_TRY(run_gemv(down, rows));
         if (!fused_exchange) GF_TRY(reduce_partial(projected_, (size_t)rows * c.hidden));
     }
@@ -773,13 +771,20 @@ int Model::encode_blocks(uint32_t rows, uint32_t flags) {
         GemvLaunch head = head_weights();
         head.prologue = kPrologueAddNorm; head.in = projected_; head.residual = x2;
         head.gamma0 = layers_[c.layers - 1].post_ffw_norm; head.residual_out = x; head.gamma1 = output_norm_;
-        if (fused_exchange) shard_gather(head, 1u, down_ctas);
+        if (fused_exchange) shard_gather(head, 1u, 2u * c.layers);
         GF_TRY(run_gemv(head, rows));
     } else if (fused_exchange && shard_.size > 1u) {
-        // Nobody reads the last down projection of a pass without logits: take its arrivals off word 1 all the
-        // same, so that the words keep alternating from one pass into the next.
+        // Nobody reads the last down projection of a pass without logits.  Wait for the peers' parts of it all the
+        // same: a peer then cannot start the next pass, whose first exchange reuses half 0, before this shard has
+        // sent that part -- which it does only after it has finished reading half 0.
         ++launches_;
-        GF_TRY(launch_shard_drain(shard_.arrived(shard_.arena, 1u), (shard_.size - 1u) * down_ctas, shard_.wait_limit, error_flag_, stream_, true));
+        ShardDrain drain {};
+        drain.count = 0;
+        for (uint32_t s = 0; s < shard_.size; ++s)
+            if (s != shard_.rank) drain.parts[drain.count++] = shard_.part(shard_.arena, 1u, s);
+        drain.tick = shard_.tick(); drain.site = 2u * c.layers; drain.values = rows * c.hidden;
+        drain.wait_limit = shard_.wait_limit; drain.error_flag = error_flag_;
+        GF_TRY(launch_shard_drain(drain, stream_, true));
     }
     return GF_OK;
 }

@@ -173,25 +173,24 @@ private:
     };
 
     int reduce_partial(float* buffer, size_t count);
-    // This shard's side of the fused exchange.  Arena: parts [2 words][size shards][row_capacity x hidden] f32,
-    // then per word an arrival count and a passed count, each on a line of its own.  The O projections use
-    // word 0, the down projections word 1, so consecutive exchanges never share a word.
+    // This shard's side of the fused exchange.  Arena: [2 halves][size shards][row_capacity x hidden] stamped
+    // (value, stamp) pairs the peers write, then this GPU's pass counter.  The O projections use half 0, the down
+    // projections half 1, so consecutive exchanges never share a half; this shard's own part stays in `projected_`.
     struct ShardExchange {
         uint32_t rank = 0, size = 0;
         bool connected = false;
         uint8_t* arena = nullptr;
         uint8_t* mapped[8] = {};          // every shard's arena as addressed from this process (own at [rank])
         bool opened[8] = {};              // mapped from an exported handle: closed with the plan
-        size_t part_floats = 0, words_offset = 0, bytes = 0;
-        uint32_t wait_limit = 1u << 22;   // polls of about a microsecond: a few seconds
-        float* part(uint8_t* base, uint32_t word, uint32_t shard) const {
-            return reinterpret_cast<float*>(base) + ((size_t)word * size + shard) * part_floats;
+        size_t part_values = 0, tick_offset = 0, bytes = 0;
+        uint32_t wait_limit = 1u << 22;   // polls of a fraction of a microsecond: about a second
+        uint2* part(uint8_t* base, uint32_t half, uint32_t shard) const {
+            return reinterpret_cast<uint2*>(base) + ((size_t)half * size + shard) * part_values;
         }
-        uint32_t* arrived(uint8_t* base, uint32_t word) const { return reinterpret_cast<uint32_t*>(base + words_offset + word * 256u); }
-        uint32_t* passed(uint8_t* base, uint32_t word) const { return reinterpret_cast<uint32_t*>(base + words_offset + word * 256u + 128u); }
+        uint32_t* tick() const { return reinterpret_cast<uint32_t*>(arena + tick_offset); }
     } shard_;
-    int shard_scatter(struct GemvLaunch& launch, uint32_t rows, uint32_t word, uint32_t& producer_ctas);
-    void shard_gather(struct GemvLaunch& launch, uint32_t word, uint32_t producer_ctas);
+    void shard_scatter(struct GemvLaunch& launch, uint32_t half, uint32_t site);
+    void shard_gather(struct GemvLaunch& launch, uint32_t half, uint32_t site);
     uint32_t token_table_vocab_ = 0;
     gf_reduce_fn reduce_hook_ = nullptr;
     void* reduce_user_ = nullptr;

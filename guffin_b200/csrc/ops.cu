@@ -250,27 +250,32 @@ __global__ void __launch_bounds__(256) add_kernel(const float* __restrict__ left
         out[i] = __fadd_rn(left[i], right[i]);
 }
 
-// Takes the peers' arrivals off a shard-exchange word that no launch of this pass consumes (bounded, like the
-// consuming launches' own wait: gemv.cuh, shard_parts_wait).
-__global__ void __launch_bounds__(32) shard_drain_kernel(uint32_t* arrived, uint32_t expected, uint32_t wait_limit, int* error_flag) {
+// Tensor-parallel shards: the pass counter behind the exchange stamps (gemv.cuh, WeightStreamParams::Scatter).
+__global__ void shard_tick_kernel(uint32_t* tick) { *tick += 1u; }
+
+// Waits (bounded, like the consuming launches' own polls) until every value of the peers' parts of the pass's last
+// projection carries its stamp; nothing is read out.
+__global__ void __launch_bounds__(256) shard_drain_kernel(const ShardDrain d) {
     pdl_wait();
     pdl_launch_dependents();
-    if (threadIdx.x != 0) return;
-    uint32_t polls = 0;
-    for (;;) {
-        uint32_t seen;
-        asm volatile("ld.acquire.sys.global.u32 %0, [%1];" : "=r"(seen) : "l"(arrived) : "memory");
-        if (seen >= expected) break;
-        if (++polls > wait_limit) { atomicExch(error_flag, 1); break; }
-        if (polls > 64u) __nanosleep(200);
-    }
-    asm volatile("st.relaxed.sys.global.u32 [%0], %1;" ::"l"(arrived), "r"(0u) : "memory");
+    const uint32_t stamp = (__ldcg(d.tick) << 8) | d.site;
+    for (uint32_t s = 0; s < d.count; ++s)
+        for (uint32_t i = threadIdx.x; i < d.values; i += blockDim.x) {
+            const volatile uint32_t* word = reinterpret_cast<const volatile uint32_t*>(d.parts[s] + i) + 1;
+            for (uint32_t polls = 0; *word != stamp; ++polls) {
+                if (polls > d.wait_limit) { atomicExch(d.error_flag, 1); break; }
+                if (polls > 32u) __nanosleep(100);
+            }
+        }
 }
 
 // ------------------------------------------------------------------ launchers
 
-int launch_shard_drain(uint32_t* arrived, uint32_t expected, uint32_t wait_limit, int* error_flag, cudaStream_t stream, bool pdl) {
-    return launch_kernel(shard_drain_kernel, dim3(1), dim3(32), 0, stream, pdl, arrived, expected, wait_limit, error_flag);
+int launch_shard_tick(uint32_t* tick, cudaStream_t stream) {
+    return launch_kernel(shard_tick_kernel, dim3(1), dim3(1), 0, stream, false, tick);
+}
+int launch_shard_drain(const ShardDrain& drain, cudaStream_t stream, bool pdl) {
+    return launch_kernel(shard_drain_kernel, dim3(1), dim3(256), 0, stream, pdl, drain);
 }
 
 int launch_embedding(int dtype, const void* packed, uint32_t k, uint32_t vocab, const uint32_t* tokens, uint32_t rows,

@@ -95,7 +95,15 @@ int launch_kv_scatter(const void* private_k, const void* private_v, void* ring_k
                       const uint32_t* base_position, uint32_t rows, uint32_t row_width, uint32_t ring_mask,
                       int kv_f16, cudaStream_t stream, bool pdl);
 
-int launch_shard_drain(uint32_t* arrived, uint32_t expected, uint32_t wait_limit, int* error_flag, cudaStream_t stream, bool pdl);
+// Tensor-parallel shards: the pass counter of the exchange stamps, and the wait for a projection nobody reads.
+struct ShardDrain {
+    const uint2* parts[7];        // the peers' stamped parts in this GPU's arena
+    const uint32_t* tick;
+    uint32_t count, site, values, wait_limit;
+    int* error_flag;
+};
+int launch_shard_tick(uint32_t* tick, cudaStream_t stream);
+int launch_shard_drain(const ShardDrain& drain, cudaStream_t stream, bool pdl);
 
 // Launch helper: optional programmatic stream serialisation (PDL).
 template <typename Kernel, typename... Args>

@@ -289,19 +289,20 @@ typedef int (*gf_reduce_fn)(void* user, float* buffer_dev, uint64_t count, void*
 GF_API int gf_model_set_reduce_hook(gf_model* model, gf_reduce_fn hook, void* user);
 GF_API int gf_model_set_token_table_vocab(gf_model* model, uint32_t vocab);
 /* The same sum without a hook and without a launch of its own: the exchange rides on the projection launches.
- * Each shard owns an arena in its GPU's memory.  The O / down launch writes its part there and mirrors it into
- * the same slot of every peer's arena with plain stores over NVLink, then counts its CTAs into the peers'
- * arrival words; the launch that consumes the projection (the next fused Q/K/V, gate/up or head launch) waits
- * for the peers' CTAs -- a bounded wait: when it runs out the plan's error word is set, the pass goes on with what
- * has arrived and gf_model_synchronize reports GF_ERR_TIMEOUT -- and reads its input as the sum of all parts in
- * shard order, so every shard holds the same bits.  Shards are one per GPU; two shards must never share a GPU
- * (their launches would wait on one another inside one device).
+ * Each shard owns an arena in its GPU's memory.  The O / down launch mirrors every value it writes into its slot
+ * of every peer's arena as an 8-byte (value, stamp) pair -- plain stores over NVLink; the stamp names the pass and
+ * the projection -- and the launch that consumes the projection (the next fused Q/K/V, gate/up or head launch)
+ * reads its input as the sum of all parts in shard order, so every shard holds the same bits, polling the peers'
+ * pairs until they carry the stamp it expects.  The polls are bounded: when they run out the plan's error word is
+ * set, the pass goes on with what has arrived and gf_model_synchronize reports GF_ERR_TIMEOUT.  Shards are one per
+ * GPU and run the same passes in the same order; two shards must never share a GPU (their launches would wait
+ * on one another inside one device).
  *   gf_model_shard_prepare      allocates this shard's arena; `ipc_handle_out` (64 bytes, may be null) receives
  *                               the handle another PROCESS maps it with
  *   gf_model_shard_arena        the arena's device pointer, for shards that live in one process
  *   gf_model_shard_connect      `arenas[size]`: every shard's arena as addressable in this process (own ignored)
  *   gf_model_shard_connect_ipc  `handles`: size x 64 bytes, every shard's exported handle (own ignored)
- *   gf_model_shard_set_wait_limit  polls (about a microsecond each) before a wait for the peers gives up
+ *   gf_model_shard_set_wait_limit  polls (a fraction of a microsecond each) before a wait for a peer's value gives up
  * Connect every shard, and let the host see that all have (a barrier), before the first pass. */
 GF_API int gf_model_shard_prepare(gf_model* model, uint32_t rank, uint32_t size, void* ipc_handle_out);
 GF_API void* gf_model_shard_arena(gf_model* model);
