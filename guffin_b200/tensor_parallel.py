@@ -1,8 +1,9 @@
-"""Optional tensor parallelism for one stream's latency: G processes (one per GPU) each hold 1 / G of every
-matrix of one model and run the same pass; the partial sums behind the O and down projections are summed
-across the shards by the plan's reduction hook (gf_model_set_reduce_hook).  The reference runs on one device
-and has no counterpart; the single-GPU plan stays the product path and the parity anchor, and this mode is
-checked against it.
+"""Optional tensor parallelism for one stream's latency: G shards (one per GPU) each hold 1 / G of every
+matrix of one model and run the same passes; the partial sums behind the O and down projections are summed
+across the shards inside the projection launches over peer memory (gf_model_shard_*), or by a host reduction
+hook (gf_model_set_reduce_hook: NCCL, or an in-process sum).  The reference runs on one device and has no
+counterpart; the single-GPU plan stays the product path and the parity anchor, and this mode is checked
+against it.
 
 Sharding (GGUF matrices are [K inputs] x [N output columns], stored column after column, each column K / block
 native blocks):
