@@ -89,8 +89,8 @@ __global__ void __launch_bounds__(256) rope_store_kernel(RopeStoreParams p) {
     const double reduced = fma(-turns, 2.4492935982947064e-16, fma(-turns, 6.283185307179586, angle));
     float s, c;
     sincosf((float)reduced, &s, &c);
-    const float r0 = __fsub_rn(__fmul_rn(first, c), __fmul_rn(second, s));
-    const float r1 = __fadd_rn(__fmul_rn(first, s), __fmul_rn(second, c));
+    const float r0 = p.rotate ? __fsub_rn(__fmul_rn(first, c), __fmul_rn(second, s)) : first;      // unrotated values keep their bits (-0 too)
+    const float r1 = p.rotate ? __fadd_rn(__fmul_rn(first, s), __fmul_rn(second, c)) : second;
     if (is_query) {
         float* dst = p.q_out + ((size_t)row * p.heads + head) * p.head_dim;
         dst[i] = r0;
@@ -106,7 +106,7 @@ __global__ void __launch_bounds__(256) rope_store_kernel(RopeStoreParams p) {
         const __half k0 = __float2half_rn(r0), k1 = __float2half_rn(r1), h0 = __float2half_rn(v0), h1 = __float2half_rn(v1);
         kd[i] = k0; kd[i + half] = k1; vd[i] = h0; vd[i + half] = h1;
         if (!isfinite(__half2float(k0)) || !isfinite(__half2float(k1)) || !isfinite(__half2float(h0)) || !isfinite(__half2float(h1)))
-            atomicOr(p.status, kStatusKvNonFinite);
+            if (p.status) atomicOr(p.status, kStatusKvNonFinite);
     } else {
         float* kd = static_cast<float*>(p.private_k) + o;
         float* vd = static_cast<float*>(p.private_v) + o;
@@ -447,6 +447,20 @@ int gf_qk_norm_rope_store(const float* raw_q_dev, const float* raw_k_dev, const 
         return fail(GF_ERR_INVALID, "gf_qk_norm_rope_store: bad arguments");
     RopeStoreParams p{raw_q_dev, raw_k_dev, raw_v_dev, q_norm_dev, k_norm_dev, q_out_dev, private_k_dev, private_v_dev,
                       base_position_dev, status_dev, nullptr, rows, heads, kv_heads, head_dim, eps, freq_base, freq_scale, kv_f16};
+    return launch_rope_store(p, as_stream(stream), false);
+}
+
+int gf_rope_store_rows(const float* raw_q_dev, const float* raw_k_dev, const float* raw_v_dev, const float* q_norm_dev,
+                       const float* k_norm_dev, float* q_out_dev, void* private_k_dev, void* private_v_dev,
+                       const uint32_t* row_positions_dev, uint32_t* status_dev, uint32_t rows, uint32_t heads, uint32_t kv_heads,
+                       uint32_t head_dim, uint32_t rotary_dim, float eps, float freq_base, float freq_scale, int kv_f16, void* stream) {
+    if (!row_positions_dev || rows == 0 || heads + kv_heads == 0 || !(freq_base > 0.0f) || (rotary_dim != 0 && rotary_dim != head_dim)
+        || (heads != 0 && (!raw_q_dev || !q_out_dev)) || (kv_heads != 0 && (!raw_k_dev || !raw_v_dev || !private_k_dev || !private_v_dev)))
+        return fail(GF_ERR_INVALID, "gf_rope_store_rows: bad arguments (rotary_dim is 0 or head_dim)");
+    RopeStoreParams p{raw_q_dev, raw_k_dev, raw_v_dev, q_norm_dev, k_norm_dev, q_out_dev, private_k_dev, private_v_dev,
+                      nullptr, status_dev, nullptr, rows, heads, kv_heads, head_dim, eps, freq_base, freq_scale, kv_f16};
+    p.row_positions = row_positions_dev;
+    p.rotate = rotary_dim != 0 ? 1u : 0u;
     return launch_rope_store(p, as_stream(stream), false);
 }
 

@@ -32,6 +32,7 @@ struct RopeStoreParams {
     float eps, freq_base, freq_scale;
     int kv_f16;
     const uint32_t* row_positions = nullptr;   // optional [rows]: row r sits at row_positions[r] instead of base + r (rows of different streams)
+    uint32_t rotate = 1;                       // 0: norm and store only (the reference's rope_dimension_count = 0)
 };
 
 struct AttentionParams {

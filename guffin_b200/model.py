@@ -41,6 +41,7 @@ lib.register({
     "gf_rms_norm": (i32, [vp, vp, vp, u32, u32, f32, vp]),
     "gf_rms_norm_add": (i32, [vp, vp, vp, vp, u32, u32, f32, vp]),
     "gf_qk_norm_rope_store": (i32, [vp, vp, vp, vp, vp, vp, vp, vp, vp, vp, u32, u32, u32, u32, f32, f32, f32, i32, vp]),
+    "gf_rope_store_rows": (i32, [vp, vp, vp, vp, vp, vp, vp, vp, vp, vp, u32, u32, u32, u32, u32, f32, f32, f32, i32, vp]),
     "gf_attention_workspace_bytes": (sz, [u32, u32]),
     "gf_attention": (i32, [vp, vp, vp, vp, vp, vp, vp, vp, u32, u32, u32, u32, u32, u32, f32, f32, i32, vp]),
     "gf_prefill_attention": (i32, [vp, vp, vp, vp, vp, vp, vp, u32, u32, u32, u32, u32, u32, f32, f32, vp]),

@@ -189,6 +189,17 @@ GF_API int gf_qk_norm_rope_store(const float* raw_q_dev, const float* raw_k_dev,
                                  const uint32_t* base_position_dev, uint32_t* status_dev, uint32_t rows,
                                  uint32_t heads, uint32_t kv_heads, uint32_t head_dim, float eps,
                                  float freq_base, float freq_scale, int kv_f16, void* stream);
+/* encode_verifier_rope and encode_verifier_kv_store as the reference calls them, with one position per row
+ * (metal_command_context.hpp:239-263; kernels metal_kernels.mm:1915-1930,2406-2517): row r sits at
+ * row_positions_dev[r].  heads = 0 skips the queries, kv_heads = 0 the cache rows; rotary_dim = 0 stores without
+ * rotating (values keep their bits before the narrowing), rotary_dim = head_dim rotates whole heads; other
+ * values are GF_ERR_INVALID.  status_dev may be NULL when nobody reads the non-finite bit. */
+GF_API int gf_rope_store_rows(const float* raw_q_dev, const float* raw_k_dev, const float* raw_v_dev,
+                              const float* q_norm_dev, const float* k_norm_dev, float* q_out_dev,
+                              void* private_k_dev, void* private_v_dev, const uint32_t* row_positions_dev,
+                              uint32_t* status_dev, uint32_t rows, uint32_t heads, uint32_t kv_heads,
+                              uint32_t head_dim, uint32_t rotary_dim, float eps, float freq_base,
+                              float freq_scale, int kv_f16, void* stream);
 /* encode_verifier_attention (metal_command_context.hpp:245-268; kernels
  * metal_kernels.mm:3070-3382): grouped-query attention of rows 0..rows-1 at positions base+row
  * over the committed ring rows inside each row's window followed by the private rows of its

@@ -7,8 +7,11 @@
 //     gf_download;
 //   * the methods of class MetalCommandContext that the packed-row projection tests call
 //     (src/tensor/backends/metal/metal_command_context.hpp:54-369): construction, restart, write_u32s,
-//     encode_verifier_matmul, encode_target_head_rows, encode_rms_norm, encode_gelu_tanh_multiply,
+//     encode_verifier_matmul, encode_target_head_rows, encode_gelu_tanh_multiply,
 //     commit / wait_until_completed / commit_and_wait;
+//   * the operator methods the reference's tensor tests drive one by one: encode_embedding, encode_rms_norm,
+//     encode_rms_norm_add, encode_head_rms_norm, encode_verifier_rope, encode_verifier_kv_store (with its
+//     numerical status word), read_verifier_status, encode_token_candidates / read_token_candidates;
 //   * availability (src/tensor/backends/metal_backend.hpp: is_available, unavailable_reason).
 // A maintainer porting the engine would grow this file into the real CUDA command context; here it
 // proves that the reference's portable C++ drives the library through its own interface.
@@ -24,7 +27,9 @@
 
 #include <algorithm>
 #include <cstring>
+#include <map>
 #include <mutex>
+#include <vector>
 #include <stdexcept>
 #include <string>
 
@@ -174,6 +179,18 @@ struct MetalCommandContext::Impl {
     std::size_t workspace_bytes = 0;
     bool committed = false;
     MetalCommandStats stats;
+    void* spare_status = nullptr;                       // where unobserved device status bits go
+    // Selection results of the library, keyed by the reference workspace they were encoded for.
+    struct Selection { void* requests = nullptr; void* results = nullptr; void* workspace = nullptr; std::size_t workspace_bytes = 0; };
+    std::map<const void*, Selection> selections;
+
+    void encoding() const {
+        if (committed) throw std::logic_error("the command has been committed: restart it first");
+    }
+    std::uint32_t* status_word() {
+        if (!spare_status) { check(gf_malloc(&spare_status, 16U)); check(gf_memset(spare_status, 0, 16U, stream)); }
+        return static_cast<std::uint32_t*>(spare_status);
+    }
 
     void* scratch(std::size_t bytes) {
         if (bytes > workspace_bytes) {
@@ -227,6 +244,12 @@ MetalCommandContext::~MetalCommandContext() {
     if (!impl_) return;
     if (impl_->stream) { gf_stream_synchronize(impl_->stream); gf_stream_destroy(impl_->stream); }
     if (impl_->workspace) gf_free(impl_->workspace);
+    if (impl_->spare_status) gf_free(impl_->spare_status);
+    for (auto& [key, selection] : impl_->selections) {
+        if (selection.requests) gf_free(selection.requests);
+        if (selection.results) gf_free(selection.results);
+        if (selection.workspace) gf_free(selection.workspace);
+    }
 }
 
 MetalCommandContext::MetalCommandContext(MetalCommandContext&&) noexcept = default;
@@ -272,6 +295,142 @@ void MetalCommandContext::encode_gelu_tanh_multiply(const BackendBuffer& gate, c
     check(gf_gelu_tanh_multiply(static_cast<const float*>(g.data()), static_cast<const float*>(device_storage(up).data()),
                                 static_cast<float*>(device_storage(output).data()), count, impl_->stream));
     ++impl_->stats.compute_dispatch_count;
+}
+
+namespace {
+
+const float* floats(const BackendBuffer& buffer) {
+    const auto& storage = device_storage(buffer);
+    if (storage.descriptor().dtype != DType::f32) throw std::invalid_argument("an F32 buffer is required");
+    return static_cast<const float*>(storage.data());
+}
+float* mutable_floats(const BackendBuffer& buffer) { return const_cast<float*>(floats(buffer)); }
+// Words the reference keeps in F32-typed shared buffers (token ids, positions, status).
+std::uint32_t* words_of(const BackendBuffer& buffer) { return static_cast<std::uint32_t*>(device_storage(buffer).data()); }
+
+}  // namespace
+
+void MetalCommandContext::encode_embedding(const BackendBuffer& token_ids, const BackendBuffer& weight, const BackendBuffer& output,
+    float scale, std::uint32_t token_offset, std::uint32_t token_count) {
+    impl_->encoding();
+    const auto& w = device_storage(weight);
+    const auto& wd = w.descriptor();
+    if (wd.shape.rank() != 2U) throw std::invalid_argument("the embedding table is a [K, vocabulary] matrix");
+    const auto k = static_cast<std::uint32_t>(wd.shape.dimension(0)), vocabulary = static_cast<std::uint32_t>(wd.shape.dimension(1));
+    const auto available = static_cast<std::uint32_t>(device_storage(token_ids).descriptor().element_count);
+    const std::uint32_t rows = token_count ? token_count : available - token_offset;
+    if (token_offset > available || rows > available - token_offset || std::uint64_t(rows) * k > device_storage(output).descriptor().element_count)
+        throw std::invalid_argument("embedding rows exceed the bound buffers");
+    check(gf_embedding(gguf_type(wd.dtype), w.packed_weight(), k, vocabulary, words_of(token_ids) + token_offset, rows, scale,
+                       mutable_floats(output), impl_->status_word(), impl_->stream));
+    ++impl_->stats.compute_dispatch_count;
+}
+
+void MetalCommandContext::encode_rms_norm(const BackendBuffer& input, const BackendBuffer& weight, const BackendBuffer& output, float epsilon,
+    std::uint32_t row_count, std::uint32_t input_row_start, const BackendBuffer*) {
+    impl_->encoding();
+    const auto hidden = static_cast<std::uint32_t>(device_storage(weight).descriptor().element_count);
+    const std::uint32_t rows = row_count ? row_count : static_cast<std::uint32_t>(device_storage(input).descriptor().element_count / hidden);
+    check(gf_rms_norm(floats(input) + std::uint64_t(input_row_start) * hidden, floats(weight), mutable_floats(output), rows, hidden, epsilon, impl_->stream));
+    ++impl_->stats.compute_dispatch_count;
+}
+
+void MetalCommandContext::encode_rms_norm_add(const BackendBuffer& input, const BackendBuffer& weight, const BackendBuffer& residual,
+    const BackendBuffer& output, float epsilon, std::uint32_t row_count) {
+    impl_->encoding();
+    const auto hidden = static_cast<std::uint32_t>(device_storage(weight).descriptor().element_count);
+    const std::uint32_t rows = row_count ? row_count : static_cast<std::uint32_t>(device_storage(input).descriptor().element_count / hidden);
+    check(gf_rms_norm_add(floats(input), floats(weight), floats(residual), mutable_floats(output), rows, hidden, epsilon, impl_->stream));
+    ++impl_->stats.compute_dispatch_count;
+}
+
+// One RMS norm per (row, head): rows x heads vectors of `head_dimension` under one weight vector.
+void MetalCommandContext::encode_head_rms_norm(const BackendBuffer& input, const BackendBuffer& weight, const BackendBuffer& output, float epsilon,
+    std::uint32_t row_count, std::uint32_t head_count, std::uint32_t head_dimension) {
+    impl_->encoding();
+    if (device_storage(weight).descriptor().element_count != head_dimension) throw std::invalid_argument("one norm weight per head dimension");
+    check(gf_rms_norm(floats(input), floats(weight), mutable_floats(output), row_count * head_count, head_dimension, epsilon, impl_->stream));
+    ++impl_->stats.compute_dispatch_count;
+}
+
+void MetalCommandContext::encode_verifier_rope(const BackendBuffer& input, const BackendBuffer& positions, const BackendBuffer& output,
+    std::uint32_t row_count, std::uint32_t head_count, std::uint32_t head_dimension, std::uint32_t rope_dimension_count,
+    float frequency_base, float frequency_scale) {
+    impl_->encoding();
+    check(gf_rope_store_rows(floats(input), nullptr, nullptr, nullptr, nullptr, mutable_floats(output), nullptr, nullptr, words_of(positions),
+                             nullptr, row_count, head_count, 0U, head_dimension, rope_dimension_count, 1.0e-6F, frequency_base, frequency_scale,
+                             0, impl_->stream));
+    ++impl_->stats.compute_dispatch_count;
+}
+
+void MetalCommandContext::encode_verifier_kv_store(const BackendBuffer& raw_key, const BackendBuffer& raw_value, const BackendBuffer& positions,
+    const BackendBuffer& private_key, const BackendBuffer& private_value, std::uint32_t row_count, std::uint32_t head_count,
+    std::uint32_t head_dimension, std::uint32_t rope_dimension_count, float frequency_base, float frequency_scale,
+    const BackendBuffer* numerical_status) {
+    impl_->encoding();
+    const auto& key = device_storage(private_key);
+    const auto& value = device_storage(private_value);
+    const auto dtype = key.descriptor().dtype;
+    if (value.descriptor().dtype != dtype || (dtype != DType::f32 && dtype != DType::f16))
+        throw std::invalid_argument("the private cache rows are both F32 or both F16");
+    if (numerical_status && (dtype != DType::f16 || device_storage(*numerical_status).descriptor().dtype != DType::f32))
+        throw std::invalid_argument("a numerical status word belongs to a binary16 cache and is a 32-bit word");
+    check(gf_rope_store_rows(nullptr, floats(raw_key), floats(raw_value), nullptr, nullptr, nullptr, key.data(), value.data(), words_of(positions),
+                             numerical_status ? words_of(*numerical_status) : nullptr, row_count, 0U, head_count, head_dimension,
+                             rope_dimension_count, 1.0e-6F, frequency_base, frequency_scale, dtype == DType::f16 ? 1 : 0, impl_->stream));
+    ++impl_->stats.compute_dispatch_count;
+}
+
+std::uint32_t MetalCommandContext::read_verifier_status(const BackendBuffer& status) const {
+    std::uint32_t word = 0U;
+    check(gf_download(&word, device_storage(status).data(), sizeof word, impl_->stream));
+    check(gf_stream_synchronize(impl_->stream));
+    return word;
+}
+
+// The library's request row: { retain, history count, history[64] } (include/guffin_b200.h); `retain` is what the
+// reference calls base_candidate_count (top-k plus the distinct history tokens).
+std::uint32_t MetalCommandContext::encode_token_candidates(const BackendBuffer& logits, const engine::Gemma2MetalSelectionWorkspace& workspace,
+    const engine::TokenSelectionRequest& request, float softcap) {
+    impl_->encoding();
+    if (request.history_token_count > 64U || request.base_candidate_count == 0U || request.base_candidate_count + request.history_token_count > engine::token_sampler_max_candidates)
+        throw std::invalid_argument("selection request outside the compact candidate bounds");
+    const auto vocabulary = static_cast<std::uint32_t>(device_storage(logits).descriptor().element_count);
+    auto& selection = impl_->selections[&backend_buffer_storage(workspace.compact_result)];
+    if (!selection.requests) check(gf_malloc(&selection.requests, gf_selection_request_bytes()));
+    if (!selection.results) check(gf_malloc(&selection.results, gf_candidate_result_bytes()));
+    const std::size_t need = gf_token_candidates_workspace_bytes(1U, vocabulary);
+    if (need > selection.workspace_bytes) {
+        if (selection.workspace) { check(gf_stream_synchronize(impl_->stream)); gf_free(selection.workspace); selection.workspace = nullptr; }
+        check(gf_malloc(&selection.workspace, need));
+        selection.workspace_bytes = need;
+    }
+    std::vector<std::uint32_t> row(gf_selection_request_bytes() / sizeof(std::uint32_t), 0U);
+    row[0] = request.base_candidate_count;
+    row[1] = request.history_token_count;
+    std::copy_n(request.history_token_ids.begin(), request.history_token_count, row.begin() + 2);
+    check(gf_upload(selection.requests, row.data(), row.size() * sizeof(std::uint32_t), impl_->stream));
+    check(gf_stream_synchronize(impl_->stream));          // `row` leaves scope
+    check(gf_token_candidates(floats(logits), 1U, vocabulary, softcap, selection.requests, selection.workspace, selection.results, impl_->stream));
+    impl_->stats.compute_dispatch_count += 2U;
+    return static_cast<std::uint32_t>(2U * sizeof(std::uint32_t) + (request.base_candidate_count + request.history_token_count) * sizeof(engine::TokenLogit));
+}
+
+engine::CompactTokenCandidates MetalCommandContext::read_token_candidates(const engine::Gemma2MetalSelectionWorkspace& workspace) const {
+    const auto found = impl_->selections.find(&backend_buffer_storage(workspace.compact_result));
+    if (found == impl_->selections.end()) throw std::logic_error("no selection was encoded for this workspace");
+    std::vector<std::uint32_t> row(gf_candidate_result_bytes() / sizeof(std::uint32_t));
+    check(gf_download(row.data(), found->second.results, row.size() * sizeof(std::uint32_t), impl_->stream));
+    check(gf_stream_synchronize(impl_->stream));
+    if (row[0] != 0U) throw std::invalid_argument("the device rejected the selection request");
+    engine::CompactTokenCandidates result;
+    result.count = row[1];
+    for (std::uint32_t i = 0U; i < result.count; ++i) {
+        result.values[i].token = row[2U + 2U * i];
+        std::memcpy(&result.values[i].logit, &row[3U + 2U * i], sizeof(float));
+    }
+    result.readback_bytes = static_cast<std::uint32_t>(2U * sizeof(std::uint32_t) + result.count * sizeof(engine::TokenLogit));
+    return result;
 }
 
 void MetalCommandContext::encode_memory_barrier() { ++impl_->stats.memory_barrier_count; }     // one in-order stream: nothing to do
