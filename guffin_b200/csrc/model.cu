@@ -1151,7 +1151,7 @@ int Model::status_word(uint32_t* out) {
     GF_CUDA(cudaMemcpyAsync(&host[1], error_flag_, 4, cudaMemcpyDeviceToHost, stream_));
     GF_TRY(synchronize());
     if (out) *out = host[0];
-    if (host[1] != 0) { poisoned_ = true; return fail(GF_ERR_TIMEOUT, "a weight-streaming wait gave up"); }
+    if (host[1] != 0) { poisoned_ = true; return fail(GF_ERR_TIMEOUT, "a bounded device wait gave up (a weight copy, or a peer shard's values)"); }
     if (host[0] & kStatusKvNonFinite) { poisoned_ = true; return fail(GF_ERR_NUMERIC, "non-finite F16 K/V (status %u)", host[0]); }
     if (host[0] & kStatusBadPosition) { poisoned_ = true; return fail(GF_ERR_STATE, "a pass ran beyond the tabulated positions (status %u)", host[0]); }
     return GF_OK;
@@ -1201,6 +1201,7 @@ int gf_model_shard_prepare(gf_model* m, uint32_t rank, uint32_t size, void* ipc_
     return m ? m->impl.shard_prepare(rank, size, ipc_handle_out) : fail(GF_ERR_INVALID, "null model");
 }
 void* gf_model_shard_arena(gf_model* m) { return m ? m->impl.shard_arena() : nullptr; }
+size_t gf_model_shard_arena_bytes(gf_model* m) { return m ? m->impl.shard_arena_bytes() : 0; }
 int gf_model_shard_connect(gf_model* m, void* const* arenas) {
     return m ? m->impl.shard_connect(arenas) : fail(GF_ERR_INVALID, "null model");
 }

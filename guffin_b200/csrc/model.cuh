@@ -149,6 +149,7 @@ public:
     // maps the exported ones first.
     int shard_prepare(uint32_t rank, uint32_t size, void* ipc_handle_out);
     void* shard_arena() const { return shard_.arena; }
+    size_t shard_arena_bytes() const { return shard_.bytes; }
     int shard_connect(void* const* arenas);
     int shard_connect_ipc(const void* handles);
     void shard_set_wait_limit(uint32_t polls) { shard_.wait_limit = polls; drop_graphs(); }

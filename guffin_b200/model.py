@@ -61,6 +61,7 @@ lib.register({
     "gf_model_set_token_table_vocab": (i32, [vp, u32]),
     "gf_model_shard_prepare": (i32, [vp, u32, u32, vp]),
     "gf_model_shard_arena": (vp, [vp]),
+    "gf_model_shard_arena_bytes": (sz, [vp]),
     "gf_model_shard_connect": (i32, [vp, vp]),
     "gf_model_shard_connect_ipc": (i32, [vp, vp]),
     "gf_model_shard_set_wait_limit": (i32, [vp, u32]),

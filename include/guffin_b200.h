@@ -305,18 +305,20 @@ GF_API int gf_model_set_token_table_vocab(gf_model* model, uint32_t vocab);
  * the projection -- and the launch that consumes the projection (the next fused Q/K/V, gate/up or head launch)
  * reads its input as the sum of all parts in shard order, so every shard holds the same bits, polling the peers'
  * pairs until they carry the stamp it expects.  The polls are bounded: when they run out the plan's error word is
- * set, the pass goes on with what has arrived and gf_model_synchronize reports GF_ERR_TIMEOUT.  Shards are one per
+ * set, the pass goes on with what has arrived and gf_model_status reports GF_ERR_TIMEOUT (the plan is poisoned
+ * until gf_model_reset).  Shards are one per
  * GPU and run the same passes in the same order; two shards must never share a GPU (their launches would wait
  * on one another inside one device).
  *   gf_model_shard_prepare      allocates this shard's arena; `ipc_handle_out` (64 bytes, may be null) receives
  *                               the handle another PROCESS maps it with
- *   gf_model_shard_arena        the arena's device pointer, for shards that live in one process
+ *   gf_model_shard_arena        the arena's device pointer (and _bytes its size), for shards that live in one process
  *   gf_model_shard_connect      `arenas[size]`: every shard's arena as addressable in this process (own ignored)
  *   gf_model_shard_connect_ipc  `handles`: size x 64 bytes, every shard's exported handle (own ignored)
  *   gf_model_shard_set_wait_limit  polls (a fraction of a microsecond each) before a wait for a peer's value gives up
  * Connect every shard, and let the host see that all have (a barrier), before the first pass. */
 GF_API int gf_model_shard_prepare(gf_model* model, uint32_t rank, uint32_t size, void* ipc_handle_out);
 GF_API void* gf_model_shard_arena(gf_model* model);
+GF_API size_t gf_model_shard_arena_bytes(gf_model* model);
 GF_API int gf_model_shard_connect(gf_model* model, void* const* arenas);
 GF_API int gf_model_shard_connect_ipc(gf_model* model, const void* handles);
 GF_API int gf_model_shard_set_wait_limit(gf_model* model, uint32_t polls);

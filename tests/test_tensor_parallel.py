@@ -235,3 +235,34 @@ def test_two_shards_on_two_devices_exchange_inside_the_launches(name):
     for rank in range(size):
         assert np.allclose(kv[rank][0], want_kv[0][:, rank * kv_width:(rank + 1) * kv_width], rtol=2e-3, atol=2e-3)
         assert np.allclose(kv[rank][1], want_kv[1][:, rank * kv_width:(rank + 1) * kv_width], rtol=2e-3, atol=2e-3)
+
+
+@pytest.mark.gpu
+def test_a_silent_peer_costs_a_timeout_not_a_hang():
+    """One shard of two whose peer never runs: its arena is a zeroed buffer nothing writes.  Every poll for the
+    peer's values runs out after its (shortened) limit, the pass completes, the status call reports
+    GF_ERR_TIMEOUT, the poisoned plan refuses further passes, and a reset makes it usable again."""
+    from guffin_b200 import lib, model as gm
+    L = lib.load()
+    config = syn.model_config("tiny-target")
+    weights = syn.make_model_weights("tiny-target", 11)
+    shard = tp.Shard(config, weights, 64, 0, 2)
+    silent = lib.DeviceBuffer(L.gf_model_shard_arena_bytes(shard.model.handle))
+    silent.zero()
+    shard.connect([shard.arena, silent.ptr])
+    lib.check(L.gf_model_shard_set_wait_limit(shard.model.handle, 500))
+    model = shard.model
+    model.use_graph(False)
+    tokens = np.array([5, 9], np.uint32)
+    model.forward(tokens)                                   # enqueues; every wait for the peer gives up on the device
+    with pytest.raises(lib.GuffinError) as error:
+        model.status()
+    assert error.value.status == lib.GF_ERR_TIMEOUT
+    with pytest.raises(lib.GuffinError) as error:
+        model.forward(tokens)
+    assert error.value.status == lib.GF_ERR_STATE
+    model.reset()
+    model.forward(tokens)                                   # usable again (and times out again: the peer is still silent)
+    with pytest.raises(lib.GuffinError) as error:
+        model.status()
+    assert error.value.status == lib.GF_ERR_TIMEOUT
