@@ -230,7 +230,7 @@ def run_ours(args) -> dict:
         target.use_pass_kernel(args.schedule)
         draft.use_pass_kernel(args.schedule)
     options = ge.H1Options(ge.sampler_options(0.7, 40, 0.95, 0.05, 1.0, seed=SEEDS["sampler"] + rank), 1, 1, ACCEPT_P,
-                           SEEDS["schedule"] + rank, 0, horizon)
+                           SEEDS["schedule"] + rank, 0, horizon, int(args.conditional))
     engine = ge.H1(target, draft, options)
     # Prompt ingestion of both plans, twice: the first call also allocates the 128-row arena and loads
     # the kernels, the second is what a session pays per prompt.
@@ -323,7 +323,7 @@ def run_ours(args) -> dict:
                                 "draw per draft): not the headline"),
                    "schedule": {None: "kernel per operator (default)", 0: "kernel per operator", 1: "decode pass kernel",
                                 2: "decode pass kernel, attention launched separately"}[args.schedule],
-                   "horizon": horizon,
+                   "horizon": horizon, "verification": "conditional tiles" if args.conditional and horizon > 2 else "one pass",
                    "streams_per_gpu": 1, "parallelism": f"independent streams x{world} (no collective)",
                    "l2_policy": "inputs larger than L2: every pass streams 7.3 GB of distinct weights",
                    "assumed_accept_probability": ACCEPT_P,
@@ -810,6 +810,8 @@ def main():
     parser.add_argument("--workload", choices=("h1", "streams", "tp"), default="h1",
                         help="h1: the headline (configs[3]); streams: configs[4]; tp: one 12B stream sharded over the GPUs")
     parser.add_argument("--horizon", type=int, default=1, help="drafts per cycle of the h1 workload (1 = the headline; 2..7 = chains)")
+    parser.add_argument("--conditional", action="store_true",
+                        help="h1 workload with --horizon > 2: verify the chain as a cascade of passes (the reference's conditional tiles)")
     parser.add_argument("--streams", type=int, default=8, help="streams per GPU of the streams workload (64 over eight GPUs)")
     parser.add_argument("--prefix", type=int, default=8192, help="prefix tokens per stream of the streams workload")
     parser.add_argument("--exchange", choices=("peer", "nccl"), default="peer",

@@ -93,8 +93,12 @@ public:
             if (!draft_) return fail(GF_ERR_INVALID, "speculative decoding needs a drafter plan");
             if (draft_->config().vocab != target_.config().vocab) return fail(GF_ERR_INVALID, "drafter and target vocabularies differ (direct token ids are required)");
             if (horizon_ > kMaxHorizon) return fail(GF_ERR_INVALID, "horizon %u exceeds %u (a verification pass holds at most %d rows)", horizon_, kMaxHorizon, GF_MAX_ROWS);
-            if (target_.config().row_capacity < horizon_ + 1u)
-                return fail(GF_ERR_INVALID, "horizon %u needs %u rows per target pass (the plan was built for %u)", horizon_, horizon_ + 1u, target_.config().row_capacity);
+            VerifyTile tiles[kMaxTiles];
+            const uint32_t tile_count = verification_tiles(horizon_, tiles);
+            uint32_t widest = 0;
+            for (uint32_t t = 0; t < tile_count; ++t) widest = std::max(widest, tiles[t].rows);
+            if (target_.config().row_capacity < widest)
+                return fail(GF_ERR_INVALID, "horizon %u needs %u rows per target pass (the plan was built for %u)", horizon_, widest, target_.config().row_capacity);
             if (draft_->config().row_capacity < std::max(2u, horizon_))
                 return fail(GF_ERR_INVALID, "horizon %u needs %u rows per drafter pass (the plan was built for %u)", horizon_, std::max(2u, horizon_), draft_->config().row_capacity);
             const size_t ws_bytes = draft_sampler_workspace_bytes(draft_->config().vocab);
@@ -177,6 +181,29 @@ public:
 
 private:
     static constexpr uint32_t kMaxHorizon = GF_MAX_ROWS - 1;
+    static constexpr uint32_t kMaxTiles = 4;
+
+    // How a cycle's h drafts are verified.  Unconditional: one pass of h + 1 rows.  Conditional
+    // (chain_chat.mm:63-88): a cascade of passes, each run only when every draft before it was accepted; a tile
+    // tests `edges` drafts with `edges` rows, the last one carries one more row for the token that follows a
+    // fully accepted chain.  The partitions are the reference's registered ones
+    // (make_registered_conditional_chain_schedule, speculative_controller.cpp:590-623: 3 = 2 + 1, 4 = 2 + 2,
+    // 7 = 4 + 3) and its pairs for other lengths.
+    struct VerifyTile { uint32_t edges, rows; };
+    uint32_t verification_tiles(uint32_t h, VerifyTile (&tiles)[kMaxTiles]) const {
+        uint32_t parts[kMaxTiles] = {h, 0, 0, 0}, count = 1;
+        if (options_.conditional && h >= 2u) {
+            if (h == 3u) { parts[0] = 2; parts[1] = 1; count = 2; }
+            else if (h == 4u) { parts[0] = 2; parts[1] = 2; count = 2; }
+            else if (h == 7u) { parts[0] = 4; parts[1] = 3; count = 2; }
+            else {
+                count = 0;
+                for (uint32_t remaining = h; remaining;) { const uint32_t take = std::min(remaining, 2u); parts[count++] = take; remaining -= take; }
+            }
+        }
+        for (uint32_t t = 0; t < count; ++t) tiles[t] = VerifyTile{parts[t], parts[t] + (t + 1u == count ? 1u : 0u)};
+        return count;
+    }
 
     // Selection for one target row through a single-row request, then readback.
     int select_and_read(const SelectionHistory& request, uint32_t logits_row) {
@@ -314,6 +341,8 @@ private:
         const uint32_t r = root_;
         uint32_t first = 0;
         bool resolve = false;
+        VerifyTile tiles[kMaxTiles];
+        const uint32_t tile_count = verification_tiles(h, tiles);
         if (penalised) {      // the sampler's repetition window, for the request rows the device writes
             const std::vector<uint32_t>& window = sampler_.history();
             base_host_->top_k = so.temperature == 0.0f ? 1u : so.top_k;
@@ -327,16 +356,17 @@ private:
             // --- target: verify rows [r, x1 .. xh] in one pass; the drafts never visit the host on this path.
             GF_TRY(target_.set_device_token(0, r));
             GF_CUDA(cudaStreamWaitEvent(target_.stream(), draft_done_, 0));
-            GF_TRY(target_.forward(nullptr, h + 1u, kForwardLogits | kForwardDeviceTokens));
+            GF_TRY(target_.forward(nullptr, tiles[0].rows, kForwardLogits | kForwardDeviceTokens));
+            ++stats_.verify_passes;
             if (penalised) {      // every row's request names the drafts before it: the drafter's stream wrote them
-                GF_TRY(target_.select_device(h + 1u));
+                GF_TRY(target_.select_device(tiles[0].rows));
             } else {
                 SelectionRequestRow requests[kMaxHorizon + 1u];
                 requests[0] = to_request(sampler_.request_after(chain, 1));
-                for (uint32_t i = 1; i <= h; ++i) requests[i] = requests[0];
-                GF_TRY(target_.select(requests, h + 1u));
+                for (uint32_t i = 1; i < tiles[0].rows; ++i) requests[i] = requests[0];
+                GF_TRY(target_.select(requests, tiles[0].rows));
             }
-            GF_TRY(target_.read_candidates(results_host_, h + 1u));           // the cycle's one synchronisation
+            GF_TRY(target_.read_candidates(results_host_, tiles[0].rows));    // the cycle's one synchronisation (one more per further tile)
             GF_CUDA(cudaEventSynchronize(draft_done_));
             // A step whose support outgrew the compact law (status 20) drafted nothing usable: rebuild its
             // law over the whole vocabulary, redo the steps behind it and verify again.  Nothing of the
@@ -356,25 +386,47 @@ private:
             chain[j + 1u] = receipt.token;
             if (receipt.count == 0xffffffffu && !resolve) ++stats_.full_law_proposals;
         }
-        for (uint32_t i = 0; i <= h; ++i)
-            if (results_host_[i].status) return fail(GF_ERR_NUMERIC, "candidate selection reported status %u in row %u", results_host_[i].status, i);
+        auto check_rows = [&](uint32_t rows) {
+            for (uint32_t i = 0; i < rows; ++i)
+                if (results_host_[i].status) return fail(GF_ERR_NUMERIC, "candidate selection reported status %u in row %u", results_host_[i].status, i);
+            return (int)GF_OK;
+        };
+        GF_TRY(check_rows(tiles[0].rows));
         ++stats_.cycles;
         stats_.drafted_tokens += h;
         // --- acceptance (host, double precision), draft by draft until the first rejection.
         uint32_t matched = 0;
         uint32_t corrected = 0;
+        uint32_t tile = 0, tile_start = 0;                   // the tile whose candidates are on the host, and its first draft
         for (uint32_t i = 0; i < h; ++i) {
+            if (i == tile_start + tiles[tile].edges) {
+                // Every draft of the tile was accepted: its rows are final, and the next tile's pass runs on the
+                // tokens the host now knows (rows chain[i] .., which continue the published cache).
+                GF_TRY(target_.publish(tiles[tile].edges));
+                tile_start = i;
+                ++tile;
+                const uint32_t rows = tiles[tile].rows;
+                GF_TRY(target_.forward(chain + tile_start, rows, kForwardLogits));
+                ++stats_.verify_passes;
+                SelectionRequestRow requests[kMaxHorizon + 1u];
+                for (uint32_t k = 0; k < rows; ++k)
+                    requests[k] = penalised || k == 0 ? to_request(sampler_.request_after(chain, tile_start + k + 1u)) : requests[0];
+                GF_TRY(target_.select(requests, rows));
+                GF_TRY(target_.read_candidates(results_host_, rows));
+                GF_TRY(check_rows(rows));
+            }
+            const CandidateRow& row = results_host_[i - tile_start];
             const SelectionHistory request = sampler_.request_after(chain, i + 1u);
             TokenDistribution prepared;
-            GF_TRY(prepare_distribution(results_host_[i].candidates, results_host_[i].count, so, request, prepared));
+            GF_TRY(prepare_distribution(row.candidates, row.count, so, request, prepared));
             GatheredDraft gathered;
             GF_TRY(gather_step(i, prepared, gathered));
             SpeculativeOutcome outcome;
-            const int law_status = sampler_.sample_speculative(gathered, results_host_[i].candidates, results_host_[i].count, request, outcome);
+            const int law_status = sampler_.sample_speculative(gathered, row.candidates, row.count, request, outcome);
             if (options_.record_cycles) {
                 gf_h1_cycle_record record {};
-                record.root = chain[i]; record.proposal = chain[i + 1u]; record.word = words[i]; record.candidate_count = results_host_[i].count;
-                std::memcpy(record.candidates, results_host_[i].candidates, sizeof(TokenLogit) * results_host_[i].count);
+                record.root = chain[i]; record.proposal = chain[i + 1u]; record.word = words[i]; record.candidate_count = row.count;
+                std::memcpy(record.candidates, row.candidates, sizeof(TokenLogit) * row.count);
                 record.draft.proposal = gathered.proposal; record.draft.count = gathered.count;
                 record.draft.proposal_mass = gathered.proposal_mass; record.draft.proposal_cdf_begin = gathered.proposal_cdf_begin;
                 std::memcpy(record.draft.target_mass, gathered.target_mass.data(), sizeof(uint64_t) * 256);
@@ -392,7 +444,7 @@ private:
                 if (!forced && outcome.accepted) {
                     // Scheduled rejection of a proposal the law accepted: continue from an ordinary
                     // sample of the same row, so the control flow (one row published, no carry) matches.
-                    GF_TRY(sampler_.sample(results_host_[i].candidates, results_host_[i].count, request, corrected));
+                    GF_TRY(sampler_.sample(row.candidates, row.count, request, corrected));
                 }
                 accepted = forced;
             }
@@ -400,14 +452,14 @@ private:
             ++matched;
         }
         stats_.accepted_tokens += matched;
-        GF_TRY(target_.publish(matched + 1u));           // rows behind the first rejection are never published: the rollback
+        GF_TRY(target_.publish(matched - tile_start + 1u));   // rows behind the first rejection are never published: the rollback
         sampler_.observe(chain, matched + 1u);
         for (uint32_t i = 0; i < matched; ++i) emitted[i] = chain[i + 1u];
         if (matched == h) {
             ++stats_.accepted;
             const SelectionHistory now = sampler_.request_after(nullptr, 0);
             uint32_t next = 0;
-            GF_TRY(sampler_.sample(results_host_[h].candidates, results_host_[h].count, now, next));
+            GF_TRY(sampler_.sample(results_host_[h - tile_start].candidates, results_host_[h - tile_start].count, now, next));
             pending_ = true;                              // the last draft is selected but not yet forwarded by the drafter
             pending_token_ = chain[h];
             root_ = next;

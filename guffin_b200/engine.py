@@ -33,13 +33,13 @@ class TokenLogitC(C.Structure):
 
 class H1Options(C.Structure):
     _fields_ = [("sampler", SamplerOptions), ("speculative", i32), ("forced_schedule", i32),
-                ("forced_accept_probability", f32), ("schedule_seed", u64), ("record_cycles", i32), ("horizon", u32)]
+                ("forced_accept_probability", f32), ("schedule_seed", u64), ("record_cycles", i32), ("horizon", u32), ("conditional", i32)]
 
 
 class H1Stats(C.Structure):
     _fields_ = [(n, u64) for n in ("cycles", "accepted", "rejected", "ordinary_steps", "fallback_cycles",
                                    "emitted_tokens", "law_agreements", "sampler_launches", "drafted_tokens",
-                                   "accepted_tokens", "full_law_proposals")]
+                                   "accepted_tokens", "full_law_proposals", "verify_passes")]
 
 
 class CycleRecord(C.Structure):

@@ -514,6 +514,11 @@ typedef struct gf_h1_options {
     int32_t record_cycles;               /* keep the inputs of every acceptance test for exactness checks */
     uint32_t horizon;                    /* drafts per cycle, 1..GF_MAX_ROWS-1 (0 = 1); the target plan needs
                                             horizon + 1 rows per pass, the drafter max(2, horizon) */
+    int32_t conditional;                 /* 1: verify a cycle's drafts as a cascade of passes, each run only when every
+                                            draft before it was accepted (chain_chat.mm:63-88; partitions of
+                                            make_registered_conditional_chain_schedule, speculative_controller.cpp:590-623:
+                                            3 = 2 + 1, 4 = 2 + 2, 7 = 4 + 3, pairs otherwise).  Same tokens as the single
+                                            pass, fewer rows after an early rejection, one more pass and host wait per tile */
 } gf_h1_options;
 typedef struct gf_h1_stats {
     uint64_t cycles, accepted, rejected, ordinary_steps, fallback_cycles, emitted_tokens;
@@ -523,6 +528,8 @@ typedef struct gf_h1_stats {
     uint64_t drafted_tokens, accepted_tokens;   /* over all cycles; accepted / rejected count whole cycles */
     uint64_t full_law_proposals;         /* proposals drawn from the full-vocabulary law; fallback_cycles counts the
                                             verification passes repeated after a compact law overflowed */
+    uint64_t verify_passes;              /* target passes run by speculative cycles (one per cycle; one per tile reached
+                                            under a conditional schedule) */
 } gf_h1_stats;
 typedef struct gf_h1_cycle_record {      /* inputs and result of one real acceptance test (`root` = the row's input token) */
     uint32_t root, proposal, word, candidate_count;

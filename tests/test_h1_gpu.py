@@ -130,9 +130,9 @@ def _models(gm, context=192, target_seed=51, draft_seed=52, correlated=False, ro
     return (gm.Model(tc, tw, context, rows), gm.Model(dc, dw, context, max(2, rows - 1)), tc, tw)
 
 
-def _options(ge, temperature, seed, speculative=1, forced=0, p=0.7, record=1, penalty=1.0, horizon=1):
+def _options(ge, temperature, seed, speculative=1, forced=0, p=0.7, record=1, penalty=1.0, horizon=1, conditional=0):
     return ge.H1Options(ge.sampler_options(temperature, seed=seed, repetition_penalty=penalty), speculative, forced, p, 7, record,
-                        horizon)
+                        horizon, conditional)
 
 
 def test_h1_greedy_is_lossless(gf, ge, gm):
@@ -322,6 +322,40 @@ def test_chain_forced_schedule(gf, ge, gm):
     rate = stats.accepted_tokens / len(engine.records())                    # Bernoulli(0.7) per acceptance test
     assert 0.55 < rate < 0.85
     assert stats.emitted_tokens > 1.8 * stats.cycles                        # 1 + 0.7 + 0.49 + 0.343 tokens per cycle expected
+
+
+@pytest.mark.parametrize("horizon,penalty,forced", [(3, 1.0, 0), (4, 1.2, 0), (7, 1.0, 1), (5, 1.2, 1), (2, 1.0, 0)])
+def test_conditional_tiles_emit_the_single_pass_tokens(gf, ge, gm, oracle, horizon, penalty, forced):
+    """A cycle's drafts verified as a cascade of passes (the reference's conditional chain schedule: 3 = 2 + 1,
+    4 = 2 + 2, 7 = 4 + 3, pairs otherwise) must reproduce the single-pass cycle test for test: the same words,
+    candidates, decisions and tokens, the same caches -- only the number of target passes differs."""
+    seed = 777
+    prompt = np.random.default_rng(8).integers(0, 2048, 20).astype(np.uint32)
+    runs = []
+    for conditional in (0, 1):
+        target, draft, tc, tw = _models(gm, context=256, correlated=True, rows=8, noise=0.6)
+        engine = ge.H1(target, draft, _options(ge, 0.7, seed, penalty=penalty, horizon=horizon, conditional=conditional, forced=forced))
+        engine.prefill(prompt)
+        tokens = engine.generate(160)
+        runs.append((tokens, engine.records(), engine.stats(), target, draft, tc, tw))
+        assert target.status() == 0 and draft.status() == 0
+    (single_tokens, single_records, single_stats, *_), (tokens, records, stats, target, draft, tc, tw) = runs
+    np.testing.assert_array_equal(tokens, single_tokens)
+    assert len(records) == len(single_records)
+    for a, b in zip(records, single_records):
+        assert (a.root, a.proposal, a.word, a.token, a.accepted, a.depth, a.horizon, a.candidate_count) == \
+               (b.root, b.proposal, b.word, b.token, b.accepted, b.depth, b.horizon, b.candidate_count)
+        assert bytes(a.candidates)[:8 * a.candidate_count] == bytes(b.candidates)[:8 * b.candidate_count]      # row-count invariant logits
+    assert single_stats.verify_passes == single_stats.cycles
+    if horizon == 2:            # one tile of two drafts and three rows: the single pass itself
+        assert stats.verify_passes == stats.cycles
+    else:
+        assert stats.cycles < stats.verify_passes <= 2 * stats.cycles + (stats.cycles if horizon == 5 else 0)
+    assert (stats.cycles, stats.accepted, stats.rejected, stats.accepted_tokens) == \
+           (single_stats.cycles, single_stats.accepted, single_stats.rejected, single_stats.accepted_tokens)
+    if not forced:
+        _check_stream(tokens, _replay_decisions(oracle, prompt, tokens, records, seed, penalty))
+    _assert_caches_match_replay(gm, target, draft, tc, tw, prompt, tokens, 256)
 
 
 # ------------------------------------------------------------------ the law over the whole vocabulary
