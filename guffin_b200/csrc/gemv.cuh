@@ -469,11 +469,6 @@ template <bool FROM_L2>
 __device__ __forceinline__ void load8f_act(const float* p, float (&v)[8]) {
     if (FROM_L2) load8f_cg(p, v); else load8f(p, v);
 }
-__device__ __forceinline__ uint4 load_volatile16(const uint4* p) {
-    uint4 v;
-    asm volatile("ld.volatile.global.v4.u32 {%0, %1, %2, %3}, [%4];" : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w) : "l"(p) : "memory");
-    return v;
-}
 // The stamp of projection `site` of the pass the counter names: distinct from the stamp of whatever the same place
 // of the arena held before (the previous projection of this pass, or of the pass before).
 __device__ __forceinline__ uint32_t shard_stamp(const uint32_t* tick, uint32_t site) { return (__ldcg(tick) << 8) | site; }

@@ -470,7 +470,8 @@ int Model::shard_prepare(uint32_t rank, uint32_t size, void* ipc_handle_out) {
     ShardExchange& x = shard_;
     x.rank = rank; x.size = size;
     if (2u * config_.layers > 255u) return fail(GF_ERR_INVALID, "the exchange stamps name at most 127 layers");
-    x.part_values = (((size_t)config_.row_capacity * config_.hidden) + 63u) & ~(size_t)63u;
+    // A slot holds the rows of a pass, or of a whole prompt chunk on the tensor-core path.
+    x.part_values = (((size_t)std::max<uint32_t>(config_.row_capacity, kPrefillRows) * config_.hidden) + 63u) & ~(size_t)63u;
     x.tick_offset = 2u * size * x.part_values * sizeof(uint2);
     x.bytes = x.tick_offset + 256u;
     void* base = nullptr;
@@ -867,7 +868,8 @@ int Model::prefill(const uint32_t* tokens_host, uint32_t count) {
     if (!tokens_host || count == 0) return fail(GF_ERR_INVALID, "empty prompt");
     if (!finalized_) return fail(GF_ERR_STATE, "plan is not finalized");
     uint32_t done = 0;
-    if (tensor_prefill_ && !sharded() && count - 1u >= kTensorPrefillMinRows) {      // a shard's partial sums go through the row passes
+    // A shard that sums through a host hook keeps to the row passes (the hook sits behind their launches).
+    if (tensor_prefill_ && (!reduce_hook_ || shard_.connected) && count - 1u >= kTensorPrefillMinRows) {
         // All rows but the last as 128-row chunks through the tensor cores (K/V only: no chunk needs
         // logits, so the last layer stops after its K/V rows, gemma_target_runtime.cpp:59-61,125); the
         // last prompt token then runs as an ordinary one-row pass, which yields the logits.
@@ -953,6 +955,23 @@ int Model::prefill_chunk(const uint32_t* tokens_host, uint32_t rows) {
     GF_TRY(launch_embedding(token_embd_.dtype, token_embd_.data, c.hidden, token_vocab(), a.tokens, rows, sqrtf((float)c.hidden), a.residual,
                             status_dev_, stream_, false));
     launches_ += 1;
+    const bool fused_exchange = shard_.connected;
+    if (fused_exchange) { ++launches_; GF_TRY(launch_shard_tick(shard_.tick(), stream_)); }
+    // A shard's O and down products are partial sums: the chunk's rows are summed over the shards in one launch.
+    auto exchange = [&](uint32_t& splits, uint32_t half, uint32_t site) -> int {
+        const ShardExchange& x = shard_;
+        ShardBulk bulk {};
+        bulk.x = a.projected; bulk.splits = splits; bulk.slab = kPrefillRows * c.hidden; bulk.values = rows * c.hidden;
+        bulk.shards = x.size; bulk.self = x.rank; bulk.peers = 0;
+        for (uint32_t s = 0; s < x.size; ++s) {
+            bulk.parts[s] = x.part(x.arena, half, s);
+            if (s != x.rank) bulk.out[bulk.peers++] = x.part(x.mapped[s], half, x.rank);
+        }
+        bulk.tick = x.tick(); bulk.site = site; bulk.wait_limit = x.wait_limit; bulk.error_flag = error_flag_;
+        splits = 1;
+        ++launches_;
+        return launch_shard_bulk_exchange(bulk, stream_);
+    };
     auto gemm = [&](std::initializer_list<std::pair<const PackedMatrix*, float*>> set, const void* operand, uint64_t k, uint32_t splits = 1) -> int {
         PrefillGemmLaunch launch;
         launch.count = 0;
@@ -1000,8 +1019,9 @@ int Model::prefill_chunk(const uint32_t* tokens_host, uint32_t rows) {
         if (prefill_attention_supported(ap)) GF_TRY(launch_prefill_attention(ap, stream_));
         else GF_TRY(launch_attention(ap, stream_, false));
         GF_TRY(launch_prefill_pack(a.attention_out, a.a_q, rows, qw, stream_));
-        const uint32_t o_splits = prefill_gemm_splits(w.o.n, w.o.k, w.o.dtype);
+        uint32_t o_splits = prefill_gemm_splits(w.o.n, w.o.k, w.o.dtype);
         GF_TRY(gemm({{&w.o, a.projected}}, a.a_q, qw, o_splits));
+        if (fused_exchange) GF_TRY(exchange(o_splits, 0u, 2u * l + 1u));
         GF_TRY(launch_prefill_norm(a.projected, o_splits, a.residual, w.post_attention_norm, w.ffn_norm, a.residual2, a.a_hidden, rows, c.hidden,
                                    c.rms_eps, 1, stream_));
         uint32_t ffn_splits = 1;
@@ -1015,6 +1035,7 @@ int Model::prefill_chunk(const uint32_t* tokens_host, uint32_t rows) {
         GF_TRY(launch_prefill_geglu(a.gate, a.up, ffn_splits, a.a_ffn, rows, c.ffn, stream_));
         down_splits = prefill_gemm_splits(w.down.n, w.down.k, w.down.dtype);
         GF_TRY(gemm({{&w.down, a.projected}}, a.a_ffn, c.ffn, down_splits));
+        if (fused_exchange) GF_TRY(exchange(down_splits, 1u, 2u * l + 2u));
         launches_ += 5;
     }
     GF_TRY(launch_kv_publish(a.publish_layers, c.layers, state_dev_, rows, stream_));

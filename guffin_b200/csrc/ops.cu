@@ -269,8 +269,57 @@ __global__ void __launch_bounds__(256) shard_drain_kernel(const ShardDrain d) {
         }
 }
 
+__global__ void __launch_bounds__(256) shard_bulk_exchange_kernel(const ShardBulk p) {
+    const uint32_t stamp = (__ldcg(p.tick) << 8) | p.site;
+    const uint32_t quads = p.values / 4u, stride = gridDim.x * blockDim.x, first = blockIdx.x * blockDim.x + threadIdx.x;
+    float4* own = reinterpret_cast<float4*>(p.x);
+    // Every thread first sends all of its values, then waits for the peers' copies of the same values: no thread
+    // waits for another thread of its own GPU, and every peer sends before it waits.
+    for (uint32_t q = first; q < quads; q += stride) {
+        float4 v = own[q];
+        for (uint32_t s = 1; s < p.splits; ++s) {
+            const float4 w = reinterpret_cast<const float4*>(p.x + (size_t)s * p.slab)[q];
+            v.x = __fadd_rn(v.x, w.x); v.y = __fadd_rn(v.y, w.y); v.z = __fadd_rn(v.z, w.z); v.w = __fadd_rn(v.w, w.w);
+        }
+        own[q] = v;
+        for (uint32_t g = 0; g < p.peers; ++g) {
+            uint2* dst = p.out[g] + (size_t)q * 4u;      // 8-byte stores arrive whole
+            dst[0] = make_uint2(__float_as_uint(v.x), stamp); dst[1] = make_uint2(__float_as_uint(v.y), stamp);
+            dst[2] = make_uint2(__float_as_uint(v.z), stamp); dst[3] = make_uint2(__float_as_uint(v.w), stamp);
+        }
+    }
+    for (uint32_t q = first; q < quads; q += stride) {
+        const float4 mine = own[q];
+        float4 total = mine;
+        for (uint32_t s = 0; s < p.shards; ++s) {
+            float4 w = mine;
+            if (s != p.self) {
+                const uint4* src = reinterpret_cast<const uint4*>(p.parts[s] + (size_t)q * 4u);
+                uint4 a, b;
+                for (uint32_t polls = 0;; ++polls) {
+                    a = load_volatile16(src);
+                    b = load_volatile16(src + 1);
+                    if (a.y == stamp && a.w == stamp && b.y == stamp && b.w == stamp) break;
+                    if (polls > p.wait_limit) { atomicExch(p.error_flag, 1); break; }
+                    if (polls > 32u) __nanosleep(100);
+                }
+                w = make_float4(__uint_as_float(a.x), __uint_as_float(a.z), __uint_as_float(b.x), __uint_as_float(b.z));
+            }
+            if (s == 0u) total = w;
+            else { total.x = __fadd_rn(total.x, w.x); total.y = __fadd_rn(total.y, w.y); total.z = __fadd_rn(total.z, w.z); total.w = __fadd_rn(total.w, w.w); }
+        }
+        own[q] = total;
+    }
+}
+
 // ------------------------------------------------------------------ launchers
 
+int launch_shard_bulk_exchange(const ShardBulk& bulk, cudaStream_t stream) {
+    if (!bulk.x || bulk.splits == 0 || bulk.values == 0 || (bulk.values & 3u) || bulk.shards == 0 || bulk.shards > 8u || !bulk.tick || !bulk.error_flag)
+        return fail(GF_ERR_INVALID, "shard bulk exchange: bad arguments");
+    const uint32_t blocks = std::min<uint32_t>((bulk.values / 4u + 255u) / 256u, 2u * (uint32_t)sm_count());
+    return launch_kernel(shard_bulk_exchange_kernel, dim3(blocks), dim3(256), 0, stream, false, bulk);
+}
 int launch_shard_tick(uint32_t* tick, cudaStream_t stream) {
     return launch_kernel(shard_tick_kernel, dim3(1), dim3(1), 0, stream, false, tick);
 }

@@ -103,6 +103,21 @@ struct ShardDrain {
     uint32_t count, site, values, wait_limit;
     int* error_flag;
 };
+// The exchange of a whole prompt chunk's partial sums (the tensor-core prompt path of a shard): x holds `splits`
+// partial results laid [split][slab]; the kernel adds them in split order, mirrors the sums into the peers'
+// arenas as stamped pairs, polls (bounded) the peers' pairs of the same values and leaves the total of all
+// shards, added in shard order, in split 0.
+struct ShardBulk {
+    float* x;
+    uint32_t splits, slab, values;      // floats between splits; rows x width, a multiple of 4
+    uint2* out[7];                      // this shard's slot in each peer's arena
+    const uint2* parts[8];              // the peers' slots in this GPU's arena, by shard (own entry unused)
+    uint32_t shards, self, peers;
+    const uint32_t* tick;
+    uint32_t site, wait_limit;
+    int* error_flag;
+};
+int launch_shard_bulk_exchange(const ShardBulk& bulk, cudaStream_t stream);
 int launch_shard_tick(uint32_t* tick, cudaStream_t stream);
 int launch_shard_drain(const ShardDrain& drain, cudaStream_t stream, bool pdl);
 

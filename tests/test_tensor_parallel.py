@@ -162,6 +162,28 @@ def test_single_shard_exchange_is_the_plain_plan():
     assert np.array_equal(k0, k1) and np.array_equal(v0, v1)
 
 
+@pytest.mark.gpu
+def test_single_shard_prompt_chunks_are_the_plain_plan():
+    """The tensor-core prompt path of a shard (a chunk's O and down products summed over the shards in one launch),
+    one shard of one: the same bits as the plain plan's chunks."""
+    from guffin_b200 import model as gm
+    config = syn.model_config("tiny-target")
+    weights = syn.make_model_weights("tiny-target", 11)
+    prompt = np.random.default_rng(6).integers(0, config["vocab"], 150).astype(np.uint32)
+    plain = gm.Model(config, weights, 256, 8)
+    shard = tp.Shard(config, weights, 256, 0, 1, row_capacity=8)
+    shard.connect([shard.arena])
+    results = []
+    for model in (plain, shard.model):
+        model.prefill(prompt)
+        results.append((model.logits(model.prefill_logits_row), model.read_kv(5, 0, model.position),       # the global layer: every row
+                        model.read_kv(6, model.position - 8, 8)))                                            # a sliding layer: the rows still in its ring
+        assert model.status() == 0
+    assert np.array_equal(results[0][0], results[1][0])
+    for layer in (1, 2):
+        assert np.array_equal(results[0][layer][0], results[1][layer][0]) and np.array_equal(results[0][layer][1], results[1][layer][1])
+
+
 def _two_devices():
     from guffin_b200 import lib
     return lib.device_count() >= 2
@@ -182,7 +204,7 @@ def test_two_shards_on_two_devices_exchange_inside_the_launches(name):
     prompt = rng.integers(0, config["vocab"], 21).astype(np.uint32)
     steps = [rng.integers(0, config["vocab"], 2).astype(np.uint32) for _ in range(6)]
     lib.check(L.gf_set_device(0))
-    full = gm.Model(config, weights, 64, 8)
+    full = gm.Model(config, weights, 256, 8)
     full.prefill(prompt)
     want = [full.logits(full.prefill_logits_row)[None, :]]
     for tokens in steps:
@@ -195,7 +217,7 @@ def test_two_shards_on_two_devices_exchange_inside_the_launches(name):
     shards = []
     for rank in range(size):
         lib.check(L.gf_set_device(rank))
-        shards.append(tp.Shard(config, weights, 64, rank, size, row_capacity=8))
+        shards.append(tp.Shard(config, weights, 256, rank, size, row_capacity=8))
     arenas = [shard.arena for shard in shards]
     for rank in range(size):
         lib.check(L.gf_set_device(rank))
@@ -235,6 +257,39 @@ def test_two_shards_on_two_devices_exchange_inside_the_launches(name):
     for rank in range(size):
         assert np.allclose(kv[rank][0], want_kv[0][:, rank * kv_width:(rank + 1) * kv_width], rtol=2e-3, atol=2e-3)
         assert np.allclose(kv[rank][1], want_kv[1][:, rank * kv_width:(rank + 1) * kv_width], rtol=2e-3, atol=2e-3)
+
+    # A prompt long enough for the tensor-core path: each chunk's O and down products cross NVLink in one launch.
+    long_prompt = np.random.default_rng(9).integers(0, config["vocab"], 200).astype(np.uint32)
+    full.reset()
+    full.prefill(long_prompt)
+    want_long = full.logits(full.prefill_logits_row)
+    global_layer = 5 if config["sliding_pattern"] == 6 else 1                 # a layer whose ring keeps every row
+    want_long_kv = full.read_kv(global_layer, 0, full.position)
+    got_long, kv_long = [None] * size, [None] * size
+
+    def ingest(rank):
+        try:
+            lib.check(L.gf_set_device(rank))
+            model = shards[rank].model
+            model.reset()
+            model.prefill(long_prompt)
+            got_long[rank] = model.logits(model.prefill_logits_row)
+            kv_long[rank] = model.read_kv(global_layer, 0, model.position)
+            assert model.status() == 0
+        except Exception as error:
+            errors.append(error)
+
+    threads = [threading.Thread(target=ingest, args=(rank,)) for rank in range(size)]
+    for t in threads:
+        t.start()
+    for t in threads:
+        t.join(timeout=300)
+    assert not errors, errors
+    merged = np.concatenate(got_long)
+    assert np.linalg.norm(merged - want_long) <= 3e-2 * np.linalg.norm(want_long)            # bf16 operands on both sides
+    for rank in range(size):
+        ours, theirs = kv_long[rank][0], want_long_kv[0][:, rank * kv_width:(rank + 1) * kv_width]
+        assert np.linalg.norm(ours - theirs) <= 3e-2 * np.linalg.norm(theirs)
 
 
 @pytest.mark.gpu
