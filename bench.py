@@ -446,6 +446,76 @@ def run_streams(args) -> dict:
     }
 
 
+def run_tensor_parallel_h1(args, plan, shard, dist, world, rank, local, context, prompt, load_s, prefill_s) -> dict:
+    """The headline's H1 cycle with the target sharded over the ranks: every rank runs its own engine on its shard
+    and its own replica of the drafter, with the same seeds; the shards' merged candidate rows are identical, so
+    the engines stay in step and emit the same tokens."""
+    from guffin_b200 import engine as ge, lib, model as gm, synthetic as syn
+    steps, warmup = args.steps, max(args.warmup, 3)
+    dc = syn.model_config(DRAFT)
+    draft = gm.Model(dc, syn.iter_model_weights(DRAFT, SEEDS["draft"]), context, PREFILL_ROWS)
+    if shard is not None:
+        shard.global_selection()
+    options = ge.H1Options(ge.sampler_options(0.7, 40, 0.95, 0.05, 1.0, seed=SEEDS["sampler"]), 1, 1, ACCEPT_P, SEEDS["schedule"], 0, 1)
+    engine = ge.H1(plan, draft, options)
+    engine.prefill(prompt)
+
+    def barrier():
+        plan.synchronize()
+        draft.synchronize()
+        if dist is not None:
+            dist.barrier()
+
+    engine.generate_steps(warmup, 2 * warmup + 2)
+    barrier()
+    engine.reseed_schedule(1000 + SEEDS["schedule"])
+    before = engine.stats()
+    launches_before = plan.kernel_launches() + draft.kernel_launches() + int(before.sampler_launches)
+    start, end = lib.Event(), lib.Event()
+    with ClockSampler(local) as clocks:
+        start.record(plan.stream)
+        wall0 = time.perf_counter()
+        tokens = engine.generate_steps(steps, 2 * steps + 2)
+        end.record(plan.stream)
+        end.synchronize()
+        wall = time.perf_counter() - wall0
+        device_ms = start.elapsed_ms(end)
+    after = engine.stats()
+    launches = plan.kernel_launches() + draft.kernel_launches() + int(after.sampler_launches) - launches_before
+    barrier()
+    status = plan.status()
+    digest = int(np.bitwise_xor.reduce(tokens.astype(np.uint64) * np.arange(1, tokens.size + 1, dtype=np.uint64)))
+    if dist is not None:
+        import torch
+        slowest = torch.tensor([device_ms, wall], dtype=torch.float64, device="cuda")
+        dist.all_reduce(slowest, op=dist.ReduceOp.MAX)
+        device_ms, wall = slowest.tolist()
+        digests = [None] * world
+        dist.all_gather_object(digests, digest)
+        in_step = len(set(digests)) == 1
+    else:
+        in_step = True
+    if rank != 0:
+        return {}
+    cycles = int(after.cycles - before.cycles)
+    return {
+        "metric": "Gemma3-12B Q4_K_M+270M H1 decode tok/s, one stream, target sharded over the GPUs", "value": tokens.size / (device_ms * 1e-3),
+        "unit": "tok/s", "n_gpus": world, "steps": steps, "warmup": warmup, "ms_per_step": device_ms / steps,
+        "higher_is_better": True, "scaling": "strong", "vs_baseline": None, "dtype": "u4/u6/u8 blocks -> f32", "data": "synthetic",
+        "config": {"workload": "configs[3] (H1, context 2048, T=0.7 top-k 40 top-p 0.95 min-p 0.05, seeded Bernoulli(0.7) accept schedule) as ONE stream: "
+                               + (f"the 12B target row-sharded over {world} GPUs (partial sums exchanged inside the projection launches), an engine and "
+                                  "a drafter replica per GPU in step" if world > 1 else "unsharded target, one GPU"),
+                   "parallelism": f"tp{world}", "l2_policy": "inputs larger than L2: every pass streams its weights once",
+                   "tokens_per_cycle": round(tokens.size / max(cycles, 1), 3), "cycles": cycles, "engines_in_step": in_step,
+                   "load_s": round(load_s, 1), "prefill_s": round(prefill_s, 3), "status_word": int(status)},
+        "e2e": {"value": tokens.size / wall, "unit": "tok/s", "h2d_bytes_per_step": 4 + 2 * 264, "d2h_bytes_per_step": world * 2 * 3080 + 3096,
+                "ms_per_step": wall * 1e3 / steps},
+        "gpu_launches": int(launches),
+        "roofline": None,
+        "clocks": clocks.summary(),
+    }
+
+
 def run_tensor_parallel(args) -> dict:
     """One stream of the 12B target sharded over the ranks (guffin_b200.tensor_parallel): the latency of the
     two-row verification pass with an NCCL all-reduce behind every O and down projection.  One rank runs the
@@ -505,6 +575,9 @@ def run_tensor_parallel(args) -> dict:
     plan.prefill(prompt)
     plan.synchronize()
     prefill_s = time.time() - t0
+
+    if args.h1:
+        return run_tensor_parallel_h1(args, plan, shard if world > 1 else None, dist, world, rank, local, context, prompt, load_s, prefill_s)
 
     def step(i):
         plan.forward(pairs[i])
@@ -823,6 +896,8 @@ def main():
                         help="h1 workload with --horizon > 2: verify the chain as a cascade of passes (the reference's conditional tiles)")
     parser.add_argument("--streams", type=int, default=8, help="streams per GPU of the streams workload (64 over eight GPUs)")
     parser.add_argument("--prefix", type=int, default=8192, help="prefix tokens per stream of the streams workload")
+    parser.add_argument("--h1", action="store_true",
+                        help="tp workload: the whole H1 cycle on the sharded target (an engine and a drafter replica per rank, in step) instead of bare passes")
     parser.add_argument("--exchange", choices=("peer", "nccl"), default="peer",
                         help="tp workload: partial sums exchanged inside the projection launches over peer memory, or by NCCL all-reduces between them")
     parser.add_argument("--tensor-decode", action="store_true",

@@ -91,7 +91,7 @@ public:
         horizon_ = options_.horizon == 0 ? 1u : options_.horizon;
         if (options_.speculative) {
             if (!draft_) return fail(GF_ERR_INVALID, "speculative decoding needs a drafter plan");
-            if (draft_->config().vocab != target_.config().vocab) return fail(GF_ERR_INVALID, "drafter and target vocabularies differ (direct token ids are required)");
+            if (draft_->config().vocab != target_.token_vocab()) return fail(GF_ERR_INVALID, "drafter and target vocabularies differ (direct token ids are required)");
             if (horizon_ > kMaxHorizon) return fail(GF_ERR_INVALID, "horizon %u exceeds %u (a verification pass holds at most %d rows)", horizon_, kMaxHorizon, GF_MAX_ROWS);
             VerifyTile tiles[kMaxTiles];
             const uint32_t tile_count = verification_tiles(horizon_, tiles);
@@ -381,7 +381,7 @@ private:
         }
         for (uint32_t j = 0; j < h; ++j) {
             const DraftReceiptRow& receipt = receipt_host_[j];
-            if (receipt.status != 0 || receipt.token >= target_.config().vocab)
+            if (receipt.status != 0 || receipt.token >= target_.token_vocab())
                 return fail(GF_ERR_NUMERIC, "drafter sampler reported status %u at depth %u", receipt.status, j);
             chain[j + 1u] = receipt.token;
             if (receipt.count == 0xffffffffu && !resolve) ++stats_.full_law_proposals;

@@ -33,6 +33,7 @@ Model::~Model() {
     for (uint32_t s = 0; s < shard_.size; ++s)
         if (shard_.opened[s]) cudaIpcCloseMemHandle(shard_.mapped[s]);
     if (shard_.arena) cudaFree(shard_.arena);
+    if (shard_.gathered_host) cudaFreeHost(shard_.gathered_host);
     if (tokens_copied_) cudaEventDestroy(tokens_copied_);
     if (requests_copied_) cudaEventDestroy(requests_copied_);
     if (tokens_pinned_) cudaFreeHost(tokens_pinned_);
@@ -47,6 +48,11 @@ bool Model::layer_is_local(uint32_t layer) const {
 }
 
 #define GF_TRY(expr) do { const int gf_s_ = (expr); if (gf_s_ != GF_OK) return gf_s_; } while (0)
+
+// Host views of the selection rows (candidates.cu: SelectionRequest, CandidateResult).
+struct TokenLogit { uint32_t token; float logit; };
+struct SelectionRequestRow { uint32_t retain, history_count, history[64]; };
+struct CandidateRow { uint32_t status, count; TokenLogit candidates[384]; };
 
 template <typename T>
 static int device_alloc(std::vector<void*>& owner, T** out, size_t count) {
@@ -473,7 +479,9 @@ int Model::shard_prepare(uint32_t rank, uint32_t size, void* ipc_handle_out) {
     // A slot holds the rows of a pass, or of a whole prompt chunk on the tensor-core path.
     x.part_values = (((size_t)std::max<uint32_t>(config_.row_capacity, kPrefillRows) * config_.hidden) + 63u) & ~(size_t)63u;
     x.tick_offset = 2u * size * x.part_values * sizeof(uint2);
-    x.bytes = x.tick_offset + 256u;
+    x.rows_offset = x.tick_offset + 256u;
+    x.rows_values = (size_t)config_.row_capacity * (gf_candidate_result_bytes() / sizeof(uint32_t));
+    x.bytes = x.rows_offset + 2u * size * x.rows_values * sizeof(uint2);
     void* base = nullptr;
     GF_CUDA(cudaMalloc(&base, x.bytes));                 // an allocation of its own: peers map exactly this
     GF_CUDA(cudaMemset(base, 0, x.bytes));
@@ -529,6 +537,18 @@ int Model::shard_connect_ipc(const void* handles) {
         x.opened[s] = true;
     }
     return shard_connect(arenas);
+}
+
+int Model::shard_global_selection(bool enable) {
+    ShardExchange& x = shard_;
+    if (enable && !x.connected) return fail(GF_ERR_STATE, "connect the shards first");
+    if (enable && !x.gathered_dev) {
+        const size_t bytes = (size_t)x.size * x.rows_values * sizeof(uint32_t);
+        GF_TRY(device_alloc(allocations_, &x.gathered_dev, (size_t)x.size * x.rows_values));
+        GF_CUDA(cudaHostAlloc(reinterpret_cast<void**>(&x.gathered_host), bytes, cudaHostAllocDefault));
+    }
+    x.global_selection = enable;
+    return GF_OK;
 }
 
 // The producing side: the launch keeps its part in `projected_` and mirrors it, stamped, into this shard's slot of
@@ -1100,6 +1120,8 @@ int Model::set_device_token(uint32_t row, uint32_t token) {
 }
 
 int Model::select_device(uint32_t rows) {
+    if (shard_.global_selection && !selecting_global_)
+        return fail(GF_ERR_STATE, "selection requests written on the device are not offered on a shard with global selection (repetition penalty 1 only)");
     launches_ += 2;
     return launch_candidates(logits_, rows, config_.vocab, config_.final_softcap, requests_dev_, candidates_ws_, results_dev_,
                              stream_, false);
@@ -1111,15 +1133,92 @@ int Model::select(const void* requests_host, uint32_t rows) {
     const size_t bytes = (size_t)rows * gf_selection_request_bytes();
     GF_CUDA(cudaEventSynchronize(requests_copied_));
     std::memcpy(requests_pinned_, requests_host, bytes);
+    if (shard_.global_selection) {
+        // Keep the caller's requests for the merge; this shard selects with the history tokens of its own slice.
+        shard_.global_requests.assign(static_cast<const uint8_t*>(requests_host), static_cast<const uint8_t*>(requests_host) + bytes);
+        const uint32_t first = shard_.rank * config_.vocab;
+        SelectionRequestRow* local = static_cast<SelectionRequestRow*>(requests_pinned_);
+        for (uint32_t r = 0; r < rows; ++r) {
+            const SelectionRequestRow global = local[r];
+            if (global.history_count > 64u) return fail(GF_ERR_INVALID, "selection request names more than 64 history tokens");
+            local[r].history_count = 0;
+            for (uint32_t i = 0; i < global.history_count; ++i) {
+                const uint32_t token = global.history[i];
+                if (token >= token_vocab()) return fail(GF_ERR_INVALID, "history token %u outside the vocabulary", token);
+                if (token >= first && token - first < config_.vocab) local[r].history[local[r].history_count++] = token - first;
+            }
+        }
+    }
     GF_CUDA(cudaMemcpyAsync(requests_dev_, requests_pinned_, bytes, cudaMemcpyHostToDevice, stream_));
     GF_CUDA(cudaEventRecord(requests_copied_, stream_));
-    return select_device(rows);
+    selecting_global_ = true;
+    const int status = select_device(rows);
+    selecting_global_ = false;
+    return status;
 }
 
 int Model::read_candidates(void* results_host, uint32_t rows) {
     if (!results_host || rows == 0 || rows > config_.row_capacity) return fail(GF_ERR_INVALID, "bad candidate readback");
+    if (shard_.global_selection) return read_candidates_global(results_host, rows);
     GF_CUDA(cudaMemcpyAsync(results_host, results_dev_, (size_t)rows * gf_candidate_result_bytes(), cudaMemcpyDeviceToHost, stream_));
     return synchronize();
+}
+
+// Candidate rows of every shard, gathered over peer memory, merged into rows over the whole vocabulary: the best
+// `retain` pairs of all slices by (logit descending, token ascending), then the history tokens' pairs in the
+// request's order, each from the shard that owns the token.
+int Model::read_candidates_global(void* results_host, uint32_t rows) {
+    ShardExchange& x = shard_;
+    if (x.global_requests.size() < (size_t)rows * sizeof(SelectionRequestRow)) return fail(GF_ERR_STATE, "no selection is in flight for these rows");
+    const uint32_t row_words = (uint32_t)(gf_candidate_result_bytes() / sizeof(uint32_t)), words = rows * row_words;
+    ShardGather g {};
+    g.local = static_cast<const uint32_t*>(results_dev_); g.gathered = x.gathered_dev; g.words = words;
+    g.shards = x.size; g.self = x.rank; g.peers = 0;
+    const uint32_t parity = x.gathers & 1u;
+    for (uint32_t s = 0; s < x.size; ++s) {
+        g.parts[s] = x.rows_slot(x.arena, parity, s);
+        if (s != x.rank) g.out[g.peers++] = x.rows_slot(x.mapped[s], parity, x.rank);
+    }
+    g.stamp = ++x.gathers;                  // never 0, the arena's initial content
+    if (x.gathers == 0u) g.stamp = ++x.gathers;
+    g.wait_limit = x.wait_limit; g.error_flag = error_flag_;
+    ++launches_;
+    GF_TRY(launch_shard_gather(g, stream_));
+    for (uint32_t s = 0; s < x.size; ++s)
+        GF_CUDA(cudaMemcpyAsync(x.gathered_host + (size_t)s * words, x.gathered_dev + (size_t)s * words,
+                                (size_t)words * sizeof(uint32_t), cudaMemcpyDeviceToHost, stream_));
+    GF_TRY(synchronize());
+    const SelectionRequestRow* requests = reinterpret_cast<const SelectionRequestRow*>(x.global_requests.data());
+    CandidateRow* out = static_cast<CandidateRow*>(results_host);
+    std::vector<TokenLogit> pool;
+    for (uint32_t r = 0; r < rows; ++r) {
+        const SelectionRequestRow& request = requests[r];
+        const uint32_t retain = request.retain;
+        CandidateRow& merged = out[r];
+        merged.status = 0;
+        pool.clear();
+        uint32_t history_seen[8] = {};       // history pairs consumed so far from each shard's row
+        for (uint32_t s = 0; s < x.size; ++s) {
+            const CandidateRow& theirs = *reinterpret_cast<const CandidateRow*>(x.gathered_host + (size_t)s * words + (size_t)r * row_words);
+            merged.status |= theirs.status;
+            for (uint32_t i = 0; i < retain && i < theirs.count; ++i)
+                if (theirs.candidates[i].token != 0xffffffffu) pool.push_back(TokenLogit{theirs.candidates[i].token + s * config_.vocab, theirs.candidates[i].logit});
+        }
+        std::sort(pool.begin(), pool.end(), [](const TokenLogit& a, const TokenLogit& b) {
+            return a.logit > b.logit || (a.logit == b.logit && a.token < b.token);      // +0 and -0 tie, as on the device
+        });
+        uint32_t count = 0;
+        for (; count < retain && count < pool.size(); ++count) merged.candidates[count] = pool[count];
+        for (; count < retain; ++count) merged.candidates[count] = TokenLogit{0xffffffffu, -INFINITY};
+        for (uint32_t i = 0; i < request.history_count; ++i) {
+            const uint32_t token = request.history[i], owner = token / config_.vocab;
+            const CandidateRow& theirs = *reinterpret_cast<const CandidateRow*>(x.gathered_host + (size_t)owner * words + (size_t)r * row_words);
+            const TokenLogit pair = theirs.candidates[retain + history_seen[owner]++];
+            merged.candidates[count++] = TokenLogit{pair.token == 0xffffffffu ? pair.token : pair.token + owner * config_.vocab, pair.logit};
+        }
+        merged.count = count;
+    }
+    return GF_OK;
 }
 
 int Model::read_logits(uint32_t row, float* host) {
@@ -1228,6 +1327,9 @@ int gf_model_shard_connect(gf_model* m, void* const* arenas) {
 }
 int gf_model_shard_connect_ipc(gf_model* m, const void* handles) {
     return m ? m->impl.shard_connect_ipc(handles) : fail(GF_ERR_INVALID, "null model");
+}
+int gf_model_shard_global_selection(gf_model* m, int enable) {
+    return m ? m->impl.shard_global_selection(enable != 0) : fail(GF_ERR_INVALID, "null model");
 }
 int gf_model_shard_set_wait_limit(gf_model* m, uint32_t polls) {
     if (!m) return fail(GF_ERR_INVALID, "null model");

@@ -153,6 +153,11 @@ public:
     int shard_connect(void* const* arenas);
     int shard_connect_ipc(const void* handles);
     void shard_set_wait_limit(uint32_t polls) { shard_.wait_limit = polls; drop_graphs(); }
+    // With global selection a connected shard's select / read_candidates speak ids of the whole vocabulary: the
+    // request's history tokens go to the shard that owns them, every shard selects in its slice, the candidate rows
+    // of all shards are gathered over peer memory and merged on the host (the same merge on every shard, so the
+    // shards' samplers stay in step).  Requests written on the device are not offered in this mode.
+    int shard_global_selection(bool enable);
 
     // Enqueues the selection for rows whose requests already sit in requests_dev().
     int select_device(uint32_t rows);
@@ -174,6 +179,8 @@ private:
     };
 
     int reduce_partial(float* buffer, size_t count);
+    int read_candidates_global(void* results_host, uint32_t rows);
+    bool selecting_global_ = false;
     // This shard's side of the fused exchange.  Arena: [2 halves][size shards][row_capacity x hidden] stamped
     // (value, stamp) pairs the peers write, then this GPU's pass counter.  The O projections use half 0, the down
     // projections half 1, so consecutive exchanges never share a half; this shard's own part stays in `projected_`.
@@ -183,7 +190,15 @@ private:
         uint8_t* arena = nullptr;
         uint8_t* mapped[8] = {};          // every shard's arena as addressed from this process (own at [rank])
         bool opened[8] = {};              // mapped from an exported handle: closed with the plan
-        size_t part_values = 0, tick_offset = 0, bytes = 0;
+        size_t part_values = 0, tick_offset = 0, rows_offset = 0, rows_values = 0, bytes = 0;
+        bool global_selection = false;
+        uint32_t gathers = 0;             // gathers so far: their stamp, and the parity of the slot they use
+        uint32_t* gathered_dev = nullptr; // [size][rows_values]
+        uint32_t* gathered_host = nullptr;
+        std::vector<uint8_t> global_requests;      // the requests of the selection in flight, as the caller gave them
+        uint2* rows_slot(uint8_t* base, uint32_t parity, uint32_t shard) const {
+            return reinterpret_cast<uint2*>(base + rows_offset) + ((size_t)parity * size + shard) * rows_values;
+        }
         uint32_t wait_limit = 1u << 22;   // polls of a fraction of a microsecond: about a second
         uint2* part(uint8_t* base, uint32_t half, uint32_t shard) const {
             return reinterpret_cast<uint2*>(base) + ((size_t)half * size + shard) * part_values;

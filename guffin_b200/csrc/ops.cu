@@ -312,8 +312,36 @@ __global__ void __launch_bounds__(256) shard_bulk_exchange_kernel(const ShardBul
     }
 }
 
+__global__ void __launch_bounds__(256) shard_gather_kernel(const ShardGather p) {
+    const uint32_t stride = gridDim.x * blockDim.x, first = blockIdx.x * blockDim.x + threadIdx.x;
+    for (uint32_t i = first; i < p.words; i += stride) {          // send everything first, then wait
+        const uint32_t word = p.local[i];
+        p.gathered[(size_t)p.self * p.words + i] = word;
+        for (uint32_t g = 0; g < p.peers; ++g) p.out[g][i] = make_uint2(word, p.stamp);
+    }
+    for (uint32_t i = first; i < p.words; i += stride)
+        for (uint32_t s = 0; s < p.shards; ++s) {
+            if (s == p.self) continue;
+            const volatile unsigned long long* src = reinterpret_cast<const volatile unsigned long long*>(p.parts[s] + i);
+            unsigned long long pair = 0;
+            for (uint32_t polls = 0;; ++polls) {
+                pair = *src;                                       // one 8-byte load: value and stamp together
+                if ((uint32_t)(pair >> 32) == p.stamp) break;
+                if (polls > p.wait_limit) { atomicExch(p.error_flag, 1); break; }
+                if (polls > 32u) __nanosleep(100);
+            }
+            p.gathered[(size_t)s * p.words + i] = (uint32_t)pair;
+        }
+}
+
 // ------------------------------------------------------------------ launchers
 
+int launch_shard_gather(const ShardGather& gather, cudaStream_t stream) {
+    if (!gather.local || !gather.gathered || gather.words == 0 || gather.shards == 0 || gather.shards > 8u || !gather.error_flag)
+        return fail(GF_ERR_INVALID, "shard gather: bad arguments");
+    const uint32_t blocks = std::min<uint32_t>((gather.words + 255u) / 256u, (uint32_t)sm_count());
+    return launch_kernel(shard_gather_kernel, dim3(blocks), dim3(256), 0, stream, false, gather);
+}
 int launch_shard_bulk_exchange(const ShardBulk& bulk, cudaStream_t stream) {
     if (!bulk.x || bulk.splits == 0 || bulk.values == 0 || (bulk.values & 3u) || bulk.shards == 0 || bulk.shards > 8u || !bulk.tick || !bulk.error_flag)
         return fail(GF_ERR_INVALID, "shard bulk exchange: bad arguments");

@@ -118,6 +118,18 @@ struct ShardBulk {
     int* error_flag;
 };
 int launch_shard_bulk_exchange(const ShardBulk& bulk, cudaStream_t stream);
+// Every shard's copy of a few rows of 32-bit words (the candidate rows of a pass), gathered on every shard:
+// gathered[shard][word].  Stamped pairs as above; `stamp` is a count the host keeps (the same on every shard).
+struct ShardGather {
+    const uint32_t* local;
+    uint32_t* gathered;
+    uint32_t words;
+    uint2* out[7];
+    const uint2* parts[8];
+    uint32_t shards, self, peers, stamp, wait_limit;
+    int* error_flag;
+};
+int launch_shard_gather(const ShardGather& gather, cudaStream_t stream);
 int launch_shard_tick(uint32_t* tick, cudaStream_t stream);
 int launch_shard_drain(const ShardDrain& drain, cudaStream_t stream, bool pdl);
 

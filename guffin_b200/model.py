@@ -65,6 +65,7 @@ lib.register({
     "gf_model_shard_connect": (i32, [vp, vp]),
     "gf_model_shard_connect_ipc": (i32, [vp, vp]),
     "gf_model_shard_set_wait_limit": (i32, [vp, u32]),
+    "gf_model_shard_global_selection": (i32, [vp, i32]),
     "gf_add": (i32, [vp, vp, vp, u64, vp]),
     "gf_model_finalize": (i32, [vp]),
     "gf_model_reset": (i32, [vp]),

@@ -140,6 +140,11 @@ class Shard:
         assert len(blob) == 64 * self.size
         check(self.model.L.gf_model_shard_connect_ipc(self.model.handle, blob))
 
+    def global_selection(self, enable: bool = True) -> None:
+        """select / read_candidates in ids of the whole vocabulary, merged over the shards (for an H1 engine per
+        shard running in step)."""
+        check(self.model.L.gf_model_shard_global_selection(self.model.handle, int(enable)))
+
     def global_candidates(self, result: CandidateResult) -> np.ndarray:
         """A shard's candidates with ids moved into the full vocabulary."""
         pairs = result.pairs()

@@ -322,6 +322,13 @@ GF_API size_t gf_model_shard_arena_bytes(gf_model* model);
 GF_API int gf_model_shard_connect(gf_model* model, void* const* arenas);
 GF_API int gf_model_shard_connect_ipc(gf_model* model, const void* handles);
 GF_API int gf_model_shard_set_wait_limit(gf_model* model, uint32_t polls);
+/* With global selection a connected shard's gf_model_select / gf_model_read_candidates speak token ids of the whole
+ * vocabulary: a request's history tokens go to the shard that owns them, every shard selects in its slice, the
+ * candidate rows of all shards are gathered over peer memory and merged on the host -- the same rows on every
+ * shard, so one gf_h1 engine per shard (each with its own replica of the drafter, the same options and seeds) runs
+ * the speculative cycle in step with the others.  Requests written on the device are not offered in this mode,
+ * i.e. engines on shards need a repetition penalty of 1. */
+GF_API int gf_model_shard_global_selection(gf_model* model, int enable);
 /* Binds every tensor of a GGUF v2/v3 file that the block schedule knows (llama.cpp tensor names,
  * F32 vectors, Q8_0 / Q4_K / Q6_K matrices and binary16 embedding / head tables) through the two calls above: the path's share of
  * read_file_backed_gguf_model (model_format/gguf_reader.hpp:85) and of the WeightMaterializer.

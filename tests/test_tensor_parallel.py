@@ -321,3 +321,106 @@ def test_a_silent_peer_costs_a_timeout_not_a_hang():
     with pytest.raises(lib.GuffinError) as error:
         model.status()
     assert error.value.status == lib.GF_ERR_TIMEOUT
+
+
+@pytest.mark.gpu
+def test_single_shard_global_selection_and_engine_are_the_plain_ones():
+    """Global selection on one shard of one: the gathered and merged rows are the plain selection's (history tokens
+    included), and an H1 engine on the shard emits the plain engine's tokens."""
+    from guffin_b200 import engine as ge, model as gm
+    config = syn.model_config("tiny-target")
+    weights = syn.make_model_weights("tiny-target", 11)
+    prompt = np.random.default_rng(4).integers(0, config["vocab"], 21).astype(np.uint32)
+    plain = gm.Model(config, weights, 160, 2)
+    shard = tp.Shard(config, weights, 160, 0, 1)
+    shard.connect([shard.arena])
+    shard.global_selection()
+    requests = [gm.SelectionRequest(retain=40, history_count=0), gm.SelectionRequest(retain=43, history_count=3)]
+    requests[1].history[0], requests[1].history[1], requests[1].history[2] = 7, 2000, 512
+    rows = []
+    for model in (plain, shard.model):
+        model.prefill(prompt)
+        model.forward(np.array([3, 9], np.uint32))
+        for repeat in range(3):          # consecutive gathers alternate their slots
+            picked = model.select(requests)
+        rows.append([p.pairs() for p in picked])
+        assert [p.status for p in picked] == [0, 0]
+    for want, got in zip(*rows):
+        assert np.array_equal(want["token"], got["token"]) and np.array_equal(want["logit"], got["logit"])
+
+    dc = dict(config, kv_f16=0, rope_scale_global=1.0)
+    dw = dict(weights)
+    dw["output_norm.weight"] = (weights["output_norm.weight"] * 0.8).astype(np.float32)
+    emitted = []
+    for sharded in (False, True):
+        if sharded:
+            target_shard = tp.Shard(config, weights, 160, 0, 1)
+            target_shard.connect([target_shard.arena])
+            target_shard.global_selection()
+            target = target_shard.model
+        else:
+            target = gm.Model(config, weights, 160, 2)
+        draft = gm.Model(dc, dw, 160, 2)
+        engine = ge.H1(target, draft, ge.H1Options(ge.sampler_options(0.7, seed=5), 1, 0, 0.7, 7, 0, 1))
+        engine.prefill(prompt)
+        emitted.append(engine.generate(80))
+        assert engine.stats().accepted > 0 and target.status() == 0
+    np.testing.assert_array_equal(emitted[0], emitted[1])
+
+
+@pytest.mark.gpu
+def test_h1_engines_on_two_shards_run_in_step():
+    """One H1 engine per shard (two GPUs, one process, a host thread each; every shard has its own replica of the
+    drafter and the same seeds): the merged candidate rows are the same on both shards, so both engines emit the
+    same tokens, and a greedy run emits the unsharded engine's."""
+    from guffin_b200 import engine as ge, lib, model as gm
+    if not _two_devices():
+        pytest.skip("needs two GPUs")
+    L = lib.load()
+    config = syn.model_config("tiny-target")
+    weights = syn.make_model_weights("tiny-target", 11)
+    dc = dict(config, kv_f16=0, rope_scale_global=1.0)
+    dw = dict(weights)
+    dw["output_norm.weight"] = (weights["output_norm.weight"] * 0.8).astype(np.float32)
+    prompt = np.random.default_rng(4).integers(0, config["vocab"], 90).astype(np.uint32)     # long enough for the chunk path
+    size = 2
+    for temperature in (0.0, 0.7):
+        lib.check(L.gf_set_device(0))
+        single = ge.H1(gm.Model(config, weights, 256, 2), gm.Model(dc, dw, 256, 2), ge.H1Options(ge.sampler_options(temperature, seed=5), 1, 0, 0.7, 7, 0, 1))
+        single.prefill(prompt)
+        want = single.generate(64)
+        shards, drafts = [], []
+        for rank in range(size):
+            lib.check(L.gf_set_device(rank))
+            shards.append(tp.Shard(config, weights, 256, rank, size))
+            drafts.append(gm.Model(dc, dw, 256, 2))
+        arenas = [shard.arena for shard in shards]
+        for rank in range(size):
+            lib.check(L.gf_set_device(rank))
+            shards[rank].connect(arenas)
+            shards[rank].global_selection()
+            lib.check(L.gf_model_shard_set_wait_limit(shards[rank].model.handle, 1 << 20))
+        lib.check(L.gf_set_device(0))
+        emitted, stats, errors = [None] * size, [None] * size, []
+
+        def drive(rank):
+            try:
+                lib.check(L.gf_set_device(rank))
+                engine = ge.H1(shards[rank].model, drafts[rank], ge.H1Options(ge.sampler_options(temperature, seed=5), 1, 0, 0.7, 7, 0, 1))
+                engine.prefill(prompt)
+                emitted[rank] = engine.generate(64)
+                stats[rank] = engine.stats()
+                assert shards[rank].model.status() == 0
+            except Exception as error:
+                errors.append(error)
+
+        threads = [threading.Thread(target=drive, args=(rank,)) for rank in range(size)]
+        for t in threads:
+            t.start()
+        for t in threads:
+            t.join(timeout=300)
+        assert not errors, errors
+        np.testing.assert_array_equal(emitted[0], emitted[1])
+        assert stats[0].cycles == stats[1].cycles and stats[0].accepted == stats[1].accepted and stats[0].accepted > 0
+        if temperature == 0.0:
+            np.testing.assert_array_equal(emitted[0], want)
