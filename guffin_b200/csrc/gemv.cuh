@@ -483,7 +483,8 @@ __device__ __forceinline__ void load8f_stamped(const WeightStreamParams& p, cons
 #pragma unroll
         for (int i = 0; i < 4; ++i) landed = landed && q[i].y == stamp && q[i].w == stamp;
         if (landed) break;
-        if (polls > p.gather.wait_limit) { atomicExch(p.error_flag, 1); break; }      // a dead peer costs a wrong pass, never a hung GPU
+        // A dead peer costs a wrong pass, never a hung GPU; once one wait has given up the others stop waiting too.
+        if (polls > p.gather.wait_limit || ((polls & 255u) == 255u && *reinterpret_cast<volatile int*>(p.error_flag) != 0)) { atomicExch(p.error_flag, 1); break; }
         if (polls > 32u) __nanosleep(100);
     }
 #pragma unroll

@@ -263,7 +263,7 @@ __global__ void __launch_bounds__(256) shard_drain_kernel(const ShardDrain d) {
         for (uint32_t i = threadIdx.x; i < d.values; i += blockDim.x) {
             const volatile uint32_t* word = reinterpret_cast<const volatile uint32_t*>(d.parts[s] + i) + 1;
             for (uint32_t polls = 0; *word != stamp; ++polls) {
-                if (polls > d.wait_limit) { atomicExch(d.error_flag, 1); break; }
+                if (polls > d.wait_limit || ((polls & 255u) == 255u && *reinterpret_cast<volatile int*>(d.error_flag) != 0)) { atomicExch(d.error_flag, 1); break; }
                 if (polls > 32u) __nanosleep(100);
             }
         }
@@ -300,7 +300,7 @@ __global__ void __launch_bounds__(256) shard_bulk_exchange_kernel(const ShardBul
                     a = load_volatile16(src);
                     b = load_volatile16(src + 1);
                     if (a.y == stamp && a.w == stamp && b.y == stamp && b.w == stamp) break;
-                    if (polls > p.wait_limit) { atomicExch(p.error_flag, 1); break; }
+                    if (polls > p.wait_limit || ((polls & 255u) == 255u && *reinterpret_cast<volatile int*>(p.error_flag) != 0)) { atomicExch(p.error_flag, 1); break; }
                     if (polls > 32u) __nanosleep(100);
                 }
                 w = make_float4(__uint_as_float(a.x), __uint_as_float(a.z), __uint_as_float(b.x), __uint_as_float(b.z));
@@ -327,7 +327,7 @@ __global__ void __launch_bounds__(256) shard_gather_kernel(const ShardGather p) 
             for (uint32_t polls = 0;; ++polls) {
                 pair = *src;                                       // one 8-byte load: value and stamp together
                 if ((uint32_t)(pair >> 32) == p.stamp) break;
-                if (polls > p.wait_limit) { atomicExch(p.error_flag, 1); break; }
+                if (polls > p.wait_limit || ((polls & 255u) == 255u && *reinterpret_cast<volatile int*>(p.error_flag) != 0)) { atomicExch(p.error_flag, 1); break; }
                 if (polls > 32u) __nanosleep(100);
             }
             p.gathered[(size_t)s * p.words + i] = (uint32_t)pair;
