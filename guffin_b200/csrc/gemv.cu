@@ -7,7 +7,12 @@
 namespace gf {
 
 // The kernel is compiled for 1, 2, 3, 4 and 8 rows; 5 to 7 rows run the eight-row instance.
-static uint32_t instance_rows(uint32_t rows) { return rows <= 4u ? rows : 8u; }
+#define GF_TRY_STATUS(expr) do { const int gf_s_ = (expr); if (gf_s_ != GF_OK) return gf_s_; } while (0)
+
+// Five to eight rows run as two halves of the four-row instance in one launch (weight_stream_pair_kernel).
+static uint32_t instance_rows(uint32_t rows) { return rows <= 4u ? rows : 4u; }
+static uint32_t launch_halves(uint32_t rows) { return rows <= 4u ? 1u : 2u; }
+static uint32_t planned_instance(const GemvLaunch& launch) { return launch.instance ? launch.instance : instance_rows(launch.rows); }
 
 static uint32_t max_chunk_units(uint32_t rows, uint32_t unit_elems, uint32_t slot_bytes) {
     uint32_t best = 0;
@@ -38,7 +43,7 @@ int gemv_plan(const GemvLaunch& launch, GemvPlan& plan) {
     if (launch.k == 0 || launch.k % plan.unit_elems != 0 || launch.k > (1ull << 24))
         return fail(GF_ERR_INVALID, "gf_matmul: K=%llu must be a positive multiple of %u", (unsigned long long)launch.k, plan.unit_elems);
     plan.units = (uint32_t)(launch.k / plan.unit_elems);
-    const uint32_t limit = max_chunk_units(instance_rows(launch.rows), plan.unit_elems, plan.slot_bytes);
+    const uint32_t limit = max_chunk_units(planned_instance(launch), plan.unit_elems, plan.slot_bytes);
     if (limit == 0) return fail(GF_ERR_INVALID, "gf_matmul: no decomposition fits");
     const uint32_t slots = (uint32_t)sm_count();           // one CTA per SM
     // Critical path of a warp, in pair rows: rounds x (units per item + per-item overhead); the
@@ -84,7 +89,7 @@ int gemv_plan(const GemvLaunch& launch, GemvPlan& plan) {
         }
         if (inside_best != 0u) {
             const uint32_t pair_slots = (uint32_t)kGemvWarps / inside_best;
-            if (instance_rows(launch.rows) <= 4u) {
+            if (planned_instance(launch) <= 4u) {
                 plan.chunks = 1;
                 plan.intra = inside_best;
                 plan.chunk_units = units_best;
@@ -98,22 +103,27 @@ int gemv_plan(const GemvLaunch& launch, GemvPlan& plan) {
             }
         }
     }
-    plan.smem = gemv_smem_layout(instance_rows(launch.rows), plan.staged_units, plan.unit_elems, plan.slot_bytes, plan.intra > 1u).total;
+    plan.smem = gemv_smem_layout(planned_instance(launch), plan.staged_units, plan.unit_elems, plan.slot_bytes, plan.intra > 1u).total;
     return GF_OK;
 }
 
 static size_t counters_bytes(const GemvPlan& plan) { return ((size_t)plan.total_pairs * 4u + 255u) & ~(size_t)255u; }
 
+// Partial sums of one half of a launch (the whole launch up to four rows).
+static size_t half_partial_bytes(const GemvPlan& plan, const GemvLaunch& launch) {
+    return (((size_t)plan.chunks * planned_instance(launch) * plan.total_pairs * 16u * sizeof(float)) + 255u) & ~(size_t)255u;
+}
+
 size_t gemv_partial_bytes(const GemvLaunch& launch) {
     GemvPlan plan;
     if (gemv_plan(launch, plan) != GF_OK || plan.chunks == 1) return 0;
-    return (size_t)plan.chunks * instance_rows(launch.rows) * plan.total_pairs * 16u * sizeof(float);
+    return half_partial_bytes(plan, launch) * launch_halves(launch.rows);
 }
 
 size_t gemv_counter_bytes(const GemvLaunch& launch) {
     GemvPlan plan;
     if (gemv_plan(launch, plan) != GF_OK || plan.chunks == 1) return 0;
-    return counters_bytes(plan);
+    return counters_bytes(plan) * launch_halves(launch.rows);
 }
 
 template <int ROWS, bool TP = false>
@@ -210,9 +220,10 @@ int gemv_prepare(const GemvLaunch& launch, uint32_t* counters, float* partial, s
         p.heads.base_position = h.base_position; p.heads.status = h.status; p.heads.head_counters = h.head_counters;
         p.heads.enabled = 1u; p.heads.table_rows = h.table_rows; p.heads.kv_f16 = h.kv_f16 ? 1u : 0u;
         p.heads.eps = launch.eps;
+        p.heads.row_base = h.row_base;
     }
     if (plan.chunks > 1) {
-        const size_t need = (size_t)plan.chunks * instance_rows(launch.rows) * plan.total_pairs * 16u * sizeof(float);
+        const size_t need = half_partial_bytes(plan, launch);
         if (!counters || !partial || partial_bytes < need) return fail(GF_ERR_INVALID, "gf_matmul: this shape needs a %zu-byte split-K workspace", need);
         p.counters = counters;
         p.partial = partial;
@@ -220,10 +231,85 @@ int gemv_prepare(const GemvLaunch& launch, uint32_t* counters, float* partial, s
     return GF_OK;
 }
 
+// Rows 4.. of a 5..8-row launch as a launch of their own: every row pointer moved on by four rows.
+static GemvLaunch second_half(const GemvLaunch& launch) {
+    GemvLaunch h = launch;
+    const size_t k = launch.k, skip = 4;
+    h.rows = launch.rows - 4u;
+    h.instance = 4;
+    if (launch.prologue == kPrologueMerge) {          // [row][head][32 partitions][256] outputs and [..][32] (maximum, sum) pairs
+        const size_t heads = k / 256u;
+        h.in = launch.in + skip * heads * 32u * 256u;
+        h.residual = launch.residual + skip * heads * 32u * 2u;
+    } else {
+        if (h.in) h.in += skip * k;
+        if (h.residual) h.residual += skip * k;
+    }
+    if (h.residual_out) h.residual_out += skip * k;
+    for (uint32_t i = 0; i < launch.count; ++i) h.matrices[i].out += skip * launch.matrices[i].n;
+    if (launch.heads.rotation) {
+        const size_t element = launch.heads.kv_f16 ? 2u : 4u;
+        h.heads.q_out += skip * launch.matrices[0].n;
+        h.heads.private_k = static_cast<uint8_t*>(launch.heads.private_k) + skip * launch.matrices[1].n * element;
+        h.heads.private_v = static_cast<uint8_t*>(launch.heads.private_v) + skip * launch.matrices[1].n * element;
+        h.heads.head_counters += (launch.matrices[0].n + 2u * launch.matrices[1].n) / 256u;      // arrival counts of its own
+        h.heads.row_base = launch.heads.row_base + 4u;
+    }
+    for (uint32_t g = 0; g < launch.scatter.count; ++g) h.scatter.out[g] += skip * launch.matrices[0].n;
+    if (launch.gather.count) {
+        for (uint32_t s = 0; s < launch.gather.count; ++s) h.gather.parts[s] += skip * k;
+        h.gather.own += skip * k;
+    }
+    return h;
+}
+
+template <bool TP>
+static int launch_pair(const WeightStreamParams& first, const WeightStreamParams& second, const GemvPlan& plan, cudaStream_t stream, bool programmatic) {
+    static std::once_flag once[64];
+    int device = 0;
+    cudaGetDevice(&device);
+    cudaError_t attr_error = cudaSuccess;
+    std::call_once(once[device & 63], [&] {
+        attr_error = cudaFuncSetAttribute(weight_stream_pair_kernel<TP>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)kGemvSmemLimit);
+    });
+    GF_CUDA(attr_error);
+    cudaLaunchConfig_t config = {};
+    config.gridDim = dim3(plan.grid);
+    config.blockDim = dim3(kGemvWarps * 32);
+    config.dynamicSmemBytes = plan.smem;
+    config.stream = stream;
+    cudaLaunchAttribute attribute;
+    attribute.id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attribute.val.programmaticStreamSerializationAllowed = 1;
+    config.attrs = &attribute;
+    config.numAttrs = programmatic ? 1 : 0;
+    GF_CUDA(cudaLaunchKernelEx(&config, weight_stream_pair_kernel<TP>, first, second));
+    return GF_OK;
+}
+
 int gemv_launch(const GemvLaunch& launch, uint32_t* counters, float* partial, size_t partial_bytes, int* error_flag,
                 cudaStream_t stream, bool programmatic) {
     WeightStreamParams p;
     GemvPlan plan;
+    if (launch.rows > 4u && launch.rows <= GF_MAX_ROWS && launch.instance == 0u) {
+        // Two halves of the four-row instance in one launch, each with arrival counts and partial sums of its own.
+        GemvLaunch front = launch;
+        front.rows = 4;
+        front.instance = 4;
+        const GemvLaunch back = second_half(launch);
+        WeightStreamParams q;
+        GemvPlan plan_back;
+        GF_TRY_STATUS(gemv_prepare(front, counters, partial, partial_bytes, error_flag, p, plan));
+        const size_t counter_words = plan.chunks > 1u ? counters_bytes(plan) / sizeof(uint32_t) : 0u;
+        const size_t half_bytes = plan.chunks > 1u ? half_partial_bytes(plan, front) : 0u;
+        GF_TRY_STATUS(gemv_prepare(back, counters ? counters + counter_words : nullptr,
+                                   partial ? reinterpret_cast<float*>(reinterpret_cast<uint8_t*>(partial) + half_bytes) : nullptr,
+                                   partial_bytes >= half_bytes ? partial_bytes - half_bytes : 0u, error_flag, q, plan_back));
+        if (plan_back.grid != plan.grid || plan_back.smem != plan.smem || plan_back.chunks != plan.chunks || plan_back.intra != plan.intra)
+            return fail(GF_ERR_CUDA, "gf_matmul: the two halves of a launch were planned differently");
+        if (p.scatter.count != 0u || p.gather.count != 0u) return launch_pair<true>(p, q, plan, stream, programmatic);
+        return launch_pair<false>(p, q, plan, stream, programmatic);
+    }
     const int status = gemv_prepare(launch, counters, partial, partial_bytes, error_flag, p, plan);
     if (status != GF_OK) return status;
     if (p.scatter.count != 0u || p.gather.count != 0u)        // a tensor-parallel shard's exchange rides on the launch
@@ -232,14 +318,14 @@ int gemv_launch(const GemvLaunch& launch, uint32_t* counters, float* partial, si
             case 2: return launch_instance<2, true>(p, plan, stream, programmatic);
             case 3: return launch_instance<3, true>(p, plan, stream, programmatic);
             case 4: return launch_instance<4, true>(p, plan, stream, programmatic);
-            default: return launch_instance<8, true>(p, plan, stream, programmatic);
+            default: return fail(GF_ERR_INVALID, "gf_matmul: no instance for %u rows", launch.rows);
         }
     switch (launch.rows) {
         case 1: return launch_instance<1>(p, plan, stream, programmatic);
         case 2: return launch_instance<2>(p, plan, stream, programmatic);
         case 3: return launch_instance<3>(p, plan, stream, programmatic);
         case 4: return launch_instance<4>(p, plan, stream, programmatic);
-        default: return launch_instance<8>(p, plan, stream, programmatic);      // 5..8 rows: the eight-row instance
+        default: return fail(GF_ERR_INVALID, "gf_matmul: no instance for %u rows", launch.rows);
     }
 }
 
@@ -289,9 +375,10 @@ int gf_matmul(int dtype, const void* packed_dev, const float* x_dev, float* y_de
     const size_t bytes = gemv_partial_bytes(launch);
     if (bytes && !workspace_dev) return fail(GF_ERR_INVALID, "gf_matmul: this shape needs a split-K workspace");
     // The arrival counters at the head of the workspace must start at zero.
-    if (bytes) GF_CUDA(cudaMemsetAsync(workspace_dev, 0, counters_bytes(plan), as_stream(stream)));
+    const size_t counters = gemv_counter_bytes(launch);          // both halves' of a 5..8-row launch
+    if (bytes) GF_CUDA(cudaMemsetAsync(workspace_dev, 0, counters, as_stream(stream)));
     return gemv_launch(launch, static_cast<uint32_t*>(workspace_dev),
-                       reinterpret_cast<float*>(static_cast<uint8_t*>(workspace_dev) + counters_bytes(plan)), bytes, flag,
+                       reinterpret_cast<float*>(static_cast<uint8_t*>(workspace_dev) + counters), bytes, flag,
                        as_stream(stream), false);
 }
 

@@ -82,6 +82,7 @@ struct WeightStreamParams {
         uint32_t* head_counters;             // [heads + 2 * kv_heads], zero between launches
         uint32_t enabled, table_rows, kv_f16;
         float eps;
+        uint32_t row_base;                   // rows ahead of row 0 of this launch in the pass (the second half of a 5..8-row pass: 4)
     } heads;
     float* partial;            // [chunks][rows][total_pairs * 16] when chunks > 1
     uint32_t* counters;        // [total_pairs] arrival counts, zero between launches
@@ -802,7 +803,7 @@ constexpr uint32_t kGemvStatusBadPosition = 16u;
 template <int ROWS>
 __device__ __forceinline__ void finish_head(const WeightStreamParams& p, const GemvMatrix& mat, uint32_t which, uint32_t head, uint32_t lane) {
     const WeightStreamParams::HeadEpilogue& e = p.heads;
-    const uint32_t base = *e.base_position;
+    const uint32_t base = *e.base_position + e.row_base;
     const float* gamma = which == 0u ? e.q_norm : which == 1u ? e.k_norm : nullptr;
     // The finished values of the first two rows are requested together (the verify pass has two).
     const uint32_t rows = min(p.active_rows, (uint32_t)ROWS);
@@ -1284,8 +1285,10 @@ __device__ __forceinline__ WeightRing ring_open(const StreamSmem& sm, uint32_t s
 // with everything a launch needs in the constant bank and in registers this form measured 2.3 % faster
 // over a 12B pass than the shared one.
 // TP: the instantiation tensor-parallel shards launch (WeightStreamParams::scatter / gather); the plain one carries none of it.
-template <int ROWS, bool TP = false>
-__global__ void __launch_bounds__(kGemvWarps * 32, 1) weight_stream_kernel(const __grid_constant__ WeightStreamParams p) {
+// `again`: the second half of a 5..8-row launch (weight_stream_pair_kernel) -- the CTA's staging area and the
+// warps' barriers are taken over from the first half; `last`: no half follows (the next launch may start its prologue).
+template <int ROWS, bool TP>
+__device__ __forceinline__ void weight_stream_body(const WeightStreamParams& p, const bool again, const bool last, uint32_t& ring_slot, uint32_t& ring_phase) {
     constexpr int NT = (4 * ROWS + 7) / 8;
     constexpr uint32_t NCP = gemv_fragment_columns(ROWS);
     constexpr uint32_t FRAG_STRIDE = gemv_fragment_stride(ROWS);
@@ -1327,16 +1330,17 @@ __global__ void __launch_bounds__(kGemvWarps * 32, 1) weight_stream_kernel(const
         return m;
     };
 
+    if (again) __syncthreads();          // every warp has finished reading the first half's staged rows
     if (threadIdx.x == 0) bad_rows = 0u;
-    if (lane == 0) {
+    if (lane == 0 && !again) {           // the second half carries on in the ring where the first stopped
         for (int s = 0; s < kGemvSlots; ++s) mbar_init(&bar[s], 1);
         fence_barrier_init();
     }
     __syncthreads();
 
     // Producer cursor (lane 0): the next slot-full of pair rows to request, walking items then units.
-    uint32_t prod_item = 0, prod_unit = 0, prod_slot = 0, prod_bytes = 0;
-    bool first_copy = blockIdx.x == 0u && warp == 0u;
+    uint32_t prod_item = 0, prod_unit = 0, prod_slot = ring_slot, prod_bytes = 0;
+    bool first_copy = blockIdx.x == 0u && warp == 0u && !again;
     const uint8_t* prod_src = nullptr;
     auto issue_next = [&]() {   // lane 0 only
         if (prod_item >= my_items) return;
@@ -1369,7 +1373,7 @@ __global__ void __launch_bounds__(kGemvWarps * 32, 1) weight_stream_kernel(const
     stage_activations<ROWS, false, TP>(p, intra ? 0u : first_unit * p.unit_elems, intra ? p.k : chunk_count * p.unit_elems, stage, scratch, early_inputs,
                                        gather_stamp);
     __syncthreads();
-    pdl_launch_dependents();
+    if (last) pdl_launch_dependents();
 
     GemvLane L;
     L.lane = lane; L.g = lane >> 2; L.t = lane & 3u;
@@ -1387,7 +1391,7 @@ __global__ void __launch_bounds__(kGemvWarps * 32, 1) weight_stream_kernel(const
     f32x2 accA[NT], accB[NT];
     float maccA[ROWS], maccB[ROWS];
     bool failed = false;
-    uint32_t slot = 0, phase = 0;
+    uint32_t slot = ring_slot, phase = ring_phase;
     for (uint32_t item = 0; item < my_items && (!failed || intra); ++item) {
         const uint32_t pair = first_pair + item * stride;
         const GemvMatrix& mat = p.m[matrix_of(pair)];
@@ -1526,6 +1530,27 @@ __global__ void __launch_bounds__(kGemvWarps * 32, 1) weight_stream_kernel(const
         if (lane == 0) atomicExch(p.error_flag, 1);
         for (int s = 0; s < kGemvSlots; ++s) mbar_wait(&bar[s], 0, p.wait_limit);
     }
+    ring_slot = slot;
+    ring_phase = phase;
+}
+
+template <int ROWS, bool TP = false>
+__global__ void __launch_bounds__(kGemvWarps * 32, 1) weight_stream_kernel(const __grid_constant__ WeightStreamParams p) {
+    uint32_t slot = 0, phase = 0;
+    weight_stream_body<ROWS, TP>(p, false, true, slot, phase);
+}
+
+// Five to eight rows: the four-row body twice in one launch, rows 0..3 with `first` and the rest with `second`
+// (the same launch with every row pointer moved on by four rows, and counters and partial sums of its own).  The
+// weights are streamed once per half -- the second time mostly out of L2 -- and a row's sums are those of the
+// four-row instance, product for product; the eight-row instance this replaces ran at 1.4 TB/s against the
+// four-row one's 3.4 (its accumulators spilled), so two halves are faster than one whole.
+template <bool TP = false>
+__global__ void __launch_bounds__(kGemvWarps * 32, 1) weight_stream_pair_kernel(const __grid_constant__ WeightStreamParams first,
+                                                                                const __grid_constant__ WeightStreamParams second) {
+    uint32_t slot = 0, phase = 0;          // where the warp's weight ring stands
+    weight_stream_body<4, TP>(first, false, false, slot, phase);
+    weight_stream_body<4, TP>(second, true, true, slot, phase);
 }
 
 #endif  // __CUDACC__
@@ -1552,7 +1577,9 @@ struct GemvLaunch {
         uint32_t* head_counters = nullptr;
         uint32_t table_rows = 0;
         int kv_f16 = 0;
+        uint32_t row_base = 0;               // rows of the pass ahead of this launch's row 0
     } heads;
+    uint32_t instance = 0;                   // kernel instance to plan for (0: the one `rows` names)
     // Shard exchange of a tensor-parallel plan (see WeightStreamParams): off when the counts are 0.
     WeightStreamParams::Scatter scatter = {};
     WeightStreamParams::Gather gather = {};

@@ -348,8 +348,9 @@ int Model::finalize() {
                 GF_CUDA(cudaStreamSynchronize(stream_));
             }
             for (uint32_t l = 0; l < c.layers; ++l) caches_[l].rope_rotation = rotations[layer_is_local(l) ? 0 : 1];
-            GF_TRY(device_alloc(allocations_, &head_counters_, c.heads + 2u * c.kv_heads));
-            GF_CUDA(cudaMemsetAsync(head_counters_, 0, (c.heads + 2u * c.kv_heads) * sizeof(uint32_t), stream_));
+            // Twice: each half of a 5..8-row launch counts its own arrivals.
+            GF_TRY(device_alloc(allocations_, &head_counters_, 2u * (c.heads + 2u * c.kv_heads)));
+            GF_CUDA(cudaMemsetAsync(head_counters_, 0, 2u * (c.heads + 2u * c.kv_heads) * sizeof(uint32_t), stream_));
         }
     }
     {
@@ -434,7 +435,7 @@ int Model::reset() {
     if (matmul_counters_bytes_) GF_CUDA(cudaMemsetAsync(matmul_counters_, 0, matmul_counters_bytes_, stream_));
     GF_CUDA(cudaMemsetAsync(attention_counters(attention_ws_, config_.row_capacity, config_.heads), 0,
                             (size_t)config_.row_capacity * config_.heads * sizeof(uint32_t), stream_));
-    if (head_counters_) GF_CUDA(cudaMemsetAsync(head_counters_, 0, (config_.heads + 2u * config_.kv_heads) * sizeof(uint32_t), stream_));
+    if (head_counters_) GF_CUDA(cudaMemsetAsync(head_counters_, 0, 2u * (config_.heads + 2u * config_.kv_heads) * sizeof(uint32_t), stream_));
     position_ = 0;
     poisoned_ = false;
     return GF_OK;
