@@ -98,11 +98,10 @@ GF_API int gf_requantize_q6_k_q4_k(const void* q6_k_dev, uint64_t block_count, v
  * (metal_command_context.hpp:94-101; kernels metal_kernels.mm:551-986) and the CPU reference
  * matmul_f32_quantized_gguf_weight (cpu_backend.cpp:301-323).
  * y[m, n] = sum_k x[m, k] * deq(W)[n, k], rows m <= GF_MAX_ROWS, f32 accumulate.  Each row's
- * result is bit-identical whether computed alone or beside other rows, for row counts 1 to 4
- * (the decode and verification widths, gemma3_metal_tests.cpp:1223-1256 tests M = 1, 2, 3) and,
- * separately, for row counts 5 to 8: the eight-row instance has less shared memory for its
- * activation slice, so for very wide matrices it may split K differently and then add the same
- * products in another order (differences of a few f32 ulps between the two groups).
+ * result is bit-identical whether computed alone or beside other rows, for every row count from
+ * 1 to 8 (gemma3_metal_tests.cpp:1223-1256 tests M = 1, 2, 3): up to four rows are one instance of
+ * the kernel, five to eight run as two halves of the four-row instance inside one launch, planned
+ * from the shape alone, so the same products are added in the same order whatever the count.
  * `workspace_dev` holds split-K partial sums (gf_matmul_workspace_bytes); it may be NULL when
  * that size is 0. ---- */
 #define GF_MAX_ROWS 8
