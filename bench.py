@@ -5,6 +5,8 @@ weights of those geometries.
 
     python bench.py [--gpus N] [--steps K] [--warmup W] [--impl ours|reference]
     python bench.py --workload streams [--streams S] [--prefix P] [--steps K] [--gpus N]
+    torchrun ... bench.py --gpus N --workload tp [--h1] [--exchange peer|nccl]     one stream, the 12B target sharded over N GPUs
+    python bench.py --horizon H [--conditional]                                   chains of H drafts per cycle
     python bench.py --case matmul <dtype 8|12|14> <K> <N> <rows> [launches]
     python bench.py --case attention <cached rows> <rows> <heads> <kv_heads> <window> <kv_f16 0|1> [launches]
     python bench.py --case prefill <12b|270m> <tokens> [tensor path 0|1]
