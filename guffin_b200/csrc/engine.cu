@@ -71,6 +71,20 @@ static void gather(const DraftReceiptRow& receipt, const TokenDistribution& targ
     }
 }
 
+// Drafts per verification tile of a chain of h <= 7 drafts (at most four tiles): all in one, or the reference's
+// conditional partition (make_registered_conditional_chain_schedule, speculative_controller.cpp:596-604, and the
+// pairs of chain_chat.mm:78-86 for lengths it does not register).
+static uint32_t verification_partition(uint32_t h, bool conditional, uint32_t (&parts)[4]) {
+    parts[0] = h; parts[1] = parts[2] = parts[3] = 0;
+    if (!conditional || h < 2u) return 1;
+    if (h == 3u) { parts[0] = 2; parts[1] = 1; return 2; }
+    if (h == 4u) { parts[0] = 2; parts[1] = 2; return 2; }
+    if (h == 7u) { parts[0] = 4; parts[1] = 3; return 2; }
+    uint32_t count = 0;
+    for (uint32_t remaining = h; remaining && count < 4u;) { const uint32_t take = std::min(remaining, 2u); parts[count++] = take; remaining -= take; }
+    return count;
+}
+
 class H1Engine {
 public:
     H1Engine(Model& target, Model* draft, const gf_h1_options& options)
@@ -191,16 +205,8 @@ private:
     // 7 = 4 + 3) and its pairs for other lengths.
     struct VerifyTile { uint32_t edges, rows; };
     uint32_t verification_tiles(uint32_t h, VerifyTile (&tiles)[kMaxTiles]) const {
-        uint32_t parts[kMaxTiles] = {h, 0, 0, 0}, count = 1;
-        if (options_.conditional && h >= 2u) {
-            if (h == 3u) { parts[0] = 2; parts[1] = 1; count = 2; }
-            else if (h == 4u) { parts[0] = 2; parts[1] = 2; count = 2; }
-            else if (h == 7u) { parts[0] = 4; parts[1] = 3; count = 2; }
-            else {
-                count = 0;
-                for (uint32_t remaining = h; remaining;) { const uint32_t take = std::min(remaining, 2u); parts[count++] = take; remaining -= take; }
-            }
-        }
+        uint32_t parts[kMaxTiles];
+        const uint32_t count = verification_partition(h, options_.conditional != 0, parts);
         for (uint32_t t = 0; t < count; ++t) tiles[t] = VerifyTile{parts[t], parts[t] + (t + 1u == count ? 1u : 0u)};
         return count;
     }
@@ -522,6 +528,14 @@ int gf_sampler_observe(gf_sampler* s, const uint32_t* tokens, uint32_t count) {
 int gf_sampler_preview_proposal_word(const gf_sampler* s, uint32_t* out_word) {
     if (!s || !out_word) return fail(GF_ERR_INVALID, "null argument");
     *out_word = s->impl.preview_proposal_word();
+    return GF_OK;
+}
+int gf_h1_verification_schedule(uint32_t horizon, int conditional, uint32_t* out_drafts, uint32_t* out_rows, uint32_t* out_tiles) {
+    if (!out_drafts || !out_rows || !out_tiles || horizon == 0 || horizon > GF_MAX_ROWS - 1) return fail(GF_ERR_INVALID, "a horizon between 1 and %d", GF_MAX_ROWS - 1);
+    uint32_t parts[4];
+    const uint32_t count = verification_partition(horizon, conditional != 0, parts);
+    for (uint32_t t = 0; t < count; ++t) { out_drafts[t] = parts[t]; out_rows[t] = parts[t] + (t + 1u == count ? 1u : 0u); }
+    *out_tiles = count;
     return GF_OK;
 }
 int gf_sampler_preview_proposal_words(const gf_sampler* s, uint32_t count, uint32_t* out_words) {

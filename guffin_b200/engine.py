@@ -53,6 +53,7 @@ class DraftReceipt(C.Structure):
 
 
 lib.register({
+    "gf_h1_verification_schedule": (i32, [u32, i32, vp, vp, vp]),
     "gf_draft_receipt_bytes": (C.c_size_t, []),
     "gf_draft_sample_workspace_bytes": (C.c_size_t, [u32]),
     "gf_draft_sample": (i32, [vp, u32, f32, u32, f32, f32, f32, vp, u32, u32, vp, vp, vp, vp]),
@@ -256,3 +257,10 @@ class H1:
             self.close()
         except Exception:
             pass
+
+
+def verification_schedule(horizon: int, conditional: bool) -> list:
+    """(drafts, rows) of every verification pass of a cycle with `horizon` drafts."""
+    drafts, rows, tiles = (u32 * 4)(), (u32 * 4)(), u32()
+    check(lib.load().gf_h1_verification_schedule(horizon, int(conditional), drafts, rows, C.byref(tiles)))
+    return [(drafts[t], rows[t]) for t in range(tiles.value)]

@@ -547,6 +547,10 @@ typedef struct gf_h1_cycle_record {      /* inputs and result of one real accept
     int32_t status;
     uint32_t depth, horizon;             /* this test's place in its cycle's chain (0 = the root's row) and the cycle's drafts */
 } gf_h1_cycle_record;
+/* The verification passes of a cycle with `horizon` drafts: tile t tests out_drafts[t] drafts in a pass of
+ * out_rows[t] rows (at most four tiles; ChainVerifierSchedule, speculative_controller.hpp). */
+GF_API int gf_h1_verification_schedule(uint32_t horizon, int conditional, uint32_t* out_drafts, uint32_t* out_rows,
+                                       uint32_t* out_tiles);
 GF_API int gf_h1_create(gf_model* target, gf_model* draft /* may be NULL when speculative == 0 */,
                         const gf_h1_options* options, gf_h1** out_engine);
 GF_API int gf_h1_destroy(gf_h1* engine);

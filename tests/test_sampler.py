@@ -112,3 +112,26 @@ def test_greedy_speculative_accepts_only_the_argmax():
     sampler = ge.Sampler(ge.sampler_options(0.0, seed=3))
     draft = ge.gathered_draft(101, 1 << 32, 0, [0])                # proposes another token: corrected to the argmax
     assert sampler.sample_speculative(draft, candidates) == (0, 100, False, 0)
+
+
+def test_verification_schedule_is_the_reference_partition():
+    """One pass of h + 1 rows, or the reference's conditional tiles: 3 = 2 + 1, 4 = 2 + 2, 7 = 4 + 3
+    (make_registered_conditional_chain_schedule, src/engine/speculative_controller.cpp:596-604) and pairs for the
+    lengths it does not register (src/engine/chain_chat.mm:78-86); the last tile carries the row of the token behind
+    a fully accepted chain."""
+    from guffin_b200 import engine as ge, lib
+    for h in range(1, 8):
+        assert ge.verification_schedule(h, False) == [(h, h + 1)]
+    assert ge.verification_schedule(1, True) == [(1, 2)]
+    assert ge.verification_schedule(2, True) == [(2, 3)]
+    assert ge.verification_schedule(3, True) == [(2, 2), (1, 2)]
+    assert ge.verification_schedule(4, True) == [(2, 2), (2, 3)]
+    assert ge.verification_schedule(5, True) == [(2, 2), (2, 2), (1, 2)]
+    assert ge.verification_schedule(6, True) == [(2, 2), (2, 2), (2, 3)]
+    assert ge.verification_schedule(7, True) == [(4, 4), (3, 4)]
+    for h in range(1, 8):
+        for conditional in (False, True):
+            tiles = ge.verification_schedule(h, conditional)
+            assert sum(d for d, _ in tiles) == h and all(r == d for d, r in tiles[:-1]) and tiles[-1][1] == tiles[-1][0] + 1
+    with pytest.raises(lib.GuffinError):
+        ge.verification_schedule(8, True)
