@@ -424,3 +424,26 @@ def test_h1_engines_on_two_shards_run_in_step():
         assert stats[0].cycles == stats[1].cycles and stats[0].accepted == stats[1].accepted and stats[0].accepted > 0
         if temperature == 0.0:
             np.testing.assert_array_equal(emitted[0], want)
+
+
+def test_shards_of_a_binary16_table_and_of_a_matrix_bound_through_a_transform():
+    """The Gemma 2 file forms: an F16 head / embedding table is cut by vocabulary row, and a Q6_K matrix that the
+    plan requantises at load keeps its marker, so every shard transforms its own slice (the transforms work block by
+    block and column by column, so they commute with the cuts)."""
+    rng = np.random.default_rng(1)
+    k, vocab = 512, 64
+    table = rng.standard_normal((vocab, k)).astype(np.float16)
+    down = syn.make_weight(rng, syn.Q6_K, 1024, 32)
+    weights = {"token_embd.weight": (1, k, vocab, table.view(np.uint8).reshape(-1)),
+               "blk.0.ffn_down.weight": (syn.Q6_K, 1024, 32, down, "requantize"),
+               "output_norm.weight": np.ones(k, np.float32)}
+    for rank in range(2):
+        shard = dict(tp.shard_weights(weights, rank, 2))
+        assert shard["token_embd.weight"][2] == vocab                                   # the gather table stays whole
+        head = shard["output.weight"]                                                   # cut from the tied table
+        assert head[:3] == (1, k, vocab // 2)
+        assert np.array_equal(head[3].view(np.float16).reshape(vocab // 2, k), table[rank * vocab // 2:(rank + 1) * vocab // 2])
+        cut = shard["blk.0.ffn_down.weight"]
+        assert cut[:3] == (syn.Q6_K, 512, 32) and cut[4] == "requantize"
+        blocks = down.reshape(32, 4, 210)
+        assert np.array_equal(cut[3].reshape(32, 2, 210), blocks[:, 2 * rank:2 * rank + 2])
