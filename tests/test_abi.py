@@ -51,3 +51,24 @@ def test_gguf_loader_rejects_missing_arguments_without_a_gpu(tmp_path):
     L.gf_model_load_gguf.restype = ctypes.c_int
     assert L.gf_model_load_gguf(None, str(tmp_path / "absent.gguf").encode(), None) == lib.GF_ERR_INVALID
     assert b"null argument" in L.gf_last_error()
+
+
+def test_binding_argument_counts_match_the_header():
+    """Every entry point the ctypes binding declares takes as many arguments as include/guffin_b200.h gives it (a
+    binding that drifts from the header would pass garbage in the missing slots)."""
+    from guffin_b200 import engine, model  # noqa: F401  (they register their signatures)
+    L = lib.load()
+    text = re.sub(r"/\*.*?\*/", "", open(lib.HEADER_PATH).read(), flags=re.S)
+    declarations = re.findall(r"GF_API\s+[\w\s\*]+?\b(gf_\w+)\s*\(([^;]*?)\)\s*;", text, flags=re.S)
+    assert len(declarations) >= 120
+    checked = 0
+    for name, parameters in declarations:
+        parameters = parameters.strip()
+        expected = 0 if parameters in ("", "void") else len(parameters.split(","))
+        argtypes = getattr(L, name).argtypes
+        if argtypes is None:
+            assert expected == 0 or name in ("gf_last_error", "gf_version"), f"{name} has no declared argument types"
+            continue
+        assert len(argtypes) == expected, f"{name}: the binding passes {len(argtypes)} arguments, the header declares {expected}"
+        checked += 1
+    assert checked >= 110
